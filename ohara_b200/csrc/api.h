@@ -1,0 +1,49 @@
+// Declarations of the torch-free kernel launchers. All pointers are device pointers; every launch
+// goes to the given stream and returns without synchronising.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "host_utils.h"
+
+namespace ob {
+
+// gemm_sm100.cu
+void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int batches, bool a_mn,
+               bool b_mn, int64_t lda, int64_t ldb, int64_t ldc, int64_t strideA, int64_t strideB,
+               int64_t strideC, bool a_batched, bool b_batched, int b_batches, bool out_f32,
+               int splits, bool reduce, float alpha, const int* m_tile_batch,
+               const int* k_offsets, int64_t a_rows, int64_t b_rows, int num_sms,
+               cudaStream_t stream);
+
+// elementwise.cu
+void rmsnorm_fwd(const void* x, const void* delta, const float* w, void* y, void* x_out, float* rstd,
+                 int rows, int d, float eps, cudaStream_t stream);
+void rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* dres,
+                 void* dx, float* dw, int rows, int d, cudaStream_t stream);
+void rope_qk(const void* q, const void* k, void* qo, void* ko, const float* cos_t,
+             const float* sin_t, int B, int T, int H, int Hk, int D, bool inverse,
+             int64_t q_row_stride, int64_t k_row_stride, int64_t qo_row_stride,
+             int64_t ko_row_stride, cudaStream_t stream);
+void swiglu_fwd(const void* g, const void* u, void* a, int64_t rows, int h, int64_t g_pitch,
+                int64_t u_pitch, int64_t a_pitch, cudaStream_t stream);
+void swiglu_bwd(const void* da, const void* g, const void* u, void* dg, void* du, int64_t rows,
+                int h, int64_t da_pitch, int64_t g_pitch, int64_t u_pitch, int64_t dg_pitch,
+                int64_t du_pitch, cudaStream_t stream);
+void cast_f32_bf16(const float* in, void* out, int64_t n, cudaStream_t stream);
+void embedding_fwd(const int64_t* ids, const float* table, void* out, int64_t tokens, int d,
+                   int vocab, cudaStream_t stream);
+void embedding_bwd(const int64_t* ids, const void* dout, float* dtable, int64_t tokens, int d,
+                   int vocab, cudaStream_t stream);
+void adamw_step(float* p, const void* g, bool grad_is_bf16, float* m, float* v, void* shadow,
+                int64_t n, float lr, float beta1, float beta2, float eps, float wd, float bc1,
+                float bc2, float grad_scale, cudaStream_t stream);
+
+// cross_entropy.cu
+void cross_entropy_rows(void* logits, const int64_t* targets, float* row_loss, float* row_lse,
+                        int* row_correct, const float* scale_ptr, int64_t rows, int vocab,
+                        int64_t pitch, int64_t ignore_index, bool write_grad, cudaStream_t stream);
+void scale_by_scalar(void* x, bool is_bf16, const float* scalar, int64_t n, cudaStream_t stream);
+
+}  // namespace ob

@@ -1,0 +1,177 @@
+// Row-wise softmax cross-entropy over a chunk of bf16 logits, used by the chunked linear +
+// cross-entropy op: the logits of one token chunk are produced by the tcgen05 GEMM, this kernel
+// turns them in place into d(loss)/d(logits) and emits per-row loss, so the full (tokens x vocab)
+// logits never exist and no fp32 copy is made.
+//
+// One CTA per row; the row is staged in shared memory so global memory is read once and written
+// once. Rows whose target equals `ignore_index` get zero loss and zero gradient.
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace ob {
+
+namespace {
+
+struct alignas(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ float block_reduce(float v, float* scratch, bool is_max) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, other) : v + other;
+  }
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int nwarps = blockDim.x >> 5;
+  float r = (lane < nwarps) ? scratch[lane] : (is_max ? -INFINITY : 0.f);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, r, o);
+    r = is_max ? fmaxf(r, other) : r + other;
+  }
+  return r;
+}
+
+// logits: (rows, pitch) bf16, first `vocab` columns valid. Writes dlogits in place when
+// `write_grad`, loss per row, and (optionally) lse and whether argmax == target.
+__global__ void ce_rows_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
+                               float* __restrict__ row_loss, float* __restrict__ row_lse,
+                               int* __restrict__ row_correct, const float* __restrict__ scale_ptr,
+                               int vocab, int64_t pitch, int64_t ignore_index, int write_grad) {
+  extern __shared__ __align__(16) uint8_t ce_smem[];
+  __nv_bfloat16* row_s = reinterpret_cast<__nv_bfloat16*>(ce_smem);
+  __shared__ float scratch[32];
+  const int64_t row = blockIdx.x;
+  __nv_bfloat16* src = logits + row * pitch;
+  const int64_t target = targets[row];
+  const bool valid = target != ignore_index && target >= 0 && target < vocab;
+  const int vecs = vocab >> 3;
+
+  if (!valid && !row_correct) {
+    if (threadIdx.x == 0) {
+      row_loss[row] = 0.f;
+      if (row_lse) row_lse[row] = 0.f;
+    }
+    if (write_grad) {
+      bf16x8 z;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) z.v[i] = __floats2bfloat162_rn(0.f, 0.f);
+      for (int v = threadIdx.x; v < vecs; v += blockDim.x) reinterpret_cast<bf16x8*>(src)[v] = z;
+      for (int i = (vecs << 3) + threadIdx.x; i < vocab; i += blockDim.x)
+        src[i] = __float2bfloat16_rn(0.f);
+    }
+    return;
+  }
+
+  float vmax = -INFINITY;
+  int arg = 0;
+  for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+    const bf16x8 x = reinterpret_cast<const bf16x8*>(src)[v];
+    reinterpret_cast<bf16x8*>(row_s)[v] = x;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(x.v[i]);
+      if (f.x > vmax) { vmax = f.x; arg = 8 * v + 2 * i; }
+      if (f.y > vmax) { vmax = f.y; arg = 8 * v + 2 * i + 1; }
+    }
+  }
+  for (int i = (vecs << 3) + threadIdx.x; i < vocab; i += blockDim.x) {
+    const __nv_bfloat16 x = src[i];
+    row_s[i] = x;
+    const float f = __bfloat162float(x);
+    if (f > vmax) { vmax = f; arg = i; }
+  }
+  const float row_max = block_reduce(vmax, scratch, true);
+  if (row_correct) {
+    // Smallest index attaining the maximum, to match torch.argmax tie-breaking.
+    __shared__ int best;
+    if (threadIdx.x == 0) best = 0x7fffffff;
+    __syncthreads();
+    if (vmax == row_max) atomicMin(&best, arg);
+    __syncthreads();
+    if (threadIdx.x == 0) row_correct[row] = (valid && best == (int)target) ? 1 : 0;
+  }
+  __syncthreads();
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x)
+    sum += __expf(__bfloat162float(row_s[i]) - row_max);
+  const float total = block_reduce(sum, scratch, false);
+  const float lse = row_max + logf(total);
+  if (threadIdx.x == 0) {
+    row_loss[row] = valid ? (lse - __bfloat162float(row_s[valid ? target : 0])) : 0.f;
+    if (row_lse) row_lse[row] = lse;
+  }
+  if (write_grad) {
+    const float scale = valid ? (scale_ptr ? *scale_ptr : 1.f) : 0.f;
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      const bf16x8 x = reinterpret_cast<const bf16x8*>(row_s)[v];
+      bf16x8 o;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(x.v[i]);
+        float a = __expf(f.x - lse), b = __expf(f.y - lse);
+        const int c = 8 * v + 2 * i;
+        if (c == target) a -= 1.f;
+        if (c + 1 == target) b -= 1.f;
+        o.v[i] = __floats2bfloat162_rn(a * scale, b * scale);
+      }
+      reinterpret_cast<bf16x8*>(src)[v] = o;
+    }
+    for (int i = (vecs << 3) + threadIdx.x; i < vocab; i += blockDim.x) {
+      float a = __expf(__bfloat162float(row_s[i]) - lse);
+      if (i == target) a -= 1.f;
+      src[i] = __float2bfloat16_rn(a * scale);
+    }
+  }
+}
+
+__global__ void scale_by_device_scalar_bf16(__nv_bfloat16* x, const float* s, int64_t n) {
+  const float k = *s;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x)
+    x[i] = __float2bfloat16_rn(__bfloat162float(x[i]) * k);
+}
+__global__ void scale_by_device_scalar_f32(float* x, const float* s, int64_t n) {
+  const float k = *s;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x)
+    x[i] *= k;
+}
+
+}  // namespace
+
+void cross_entropy_rows(void* logits, const int64_t* targets, float* row_loss, float* row_lse,
+                        int* row_correct, const float* scale_ptr, int64_t rows, int vocab,
+                        int64_t pitch, int64_t ignore_index, bool write_grad, cudaStream_t stream) {
+  if (rows == 0) return;
+  OB_CHECK(pitch % 8 == 0, "cross entropy: logits pitch must be a multiple of 8 elements");
+  const size_t smem = (size_t)((vocab + 7) / 8) * 16;
+  OB_CHECK(smem <= 200 * 1024, "cross entropy: vocabulary too large for the shared-memory row buffer");
+  static bool configured = false;
+  if (!configured) {
+    OB_CUDA_CHECK(cudaFuncSetAttribute(ce_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       200 * 1024));
+    configured = true;
+  }
+  ce_rows_kernel<<<(unsigned)rows, 512, smem, stream>>>((__nv_bfloat16*)logits, targets, row_loss,
+                                                        row_lse, row_correct, scale_ptr, vocab,
+                                                        pitch, ignore_index, write_grad ? 1 : 0);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+void scale_by_scalar(void* x, bool is_bf16, const float* scalar, int64_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  const int threads = 256;
+  const int blocks = (int)std::min<int64_t>((n + threads - 1) / threads, device_sm_count() * 8);
+  if (is_bf16)
+    scale_by_device_scalar_bf16<<<blocks, threads, 0, stream>>>((__nv_bfloat16*)x, scalar, n);
+  else
+    scale_by_device_scalar_f32<<<blocks, threads, 0, stream>>>((float*)x, scalar, n);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace ob

@@ -1,0 +1,437 @@
+// Bandwidth-bound kernels: RMSNorm, RoPE, SwiGLU, casts, embedding, fused optimizers' elementwise
+// parts. All use 16-byte vector accesses and fp32 math; tensors are bf16 unless noted.
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace ob {
+
+namespace {
+
+struct alignas(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void unpack8(const bf16x8& in, float (&out)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(in.v[i]);
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ bf16x8 pack8(const float (&in)[8]) {
+  bf16x8 out;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) out.v[i] = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+  return out;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm forward: y = x * rsqrt(mean(x^2) + eps) * w, optionally with a fused residual add
+// (x = x + delta is written back to `x_out` and normalised). One warp per row.
+// ------------------------------------------------------------------------------------------------
+template <bool HAS_DELTA>
+__global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                   const __nv_bfloat16* __restrict__ delta,
+                                   const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                                   __nv_bfloat16* __restrict__ x_out, float* __restrict__ rstd_out,
+                                   int rows, int d, float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int vecs = d >> 3;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += gridDim.x * warps_per_block) {
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)row * d);
+    const bf16x8* dr = HAS_DELTA ? reinterpret_cast<const bf16x8*>(delta + (size_t)row * d) : nullptr;
+    bf16x8* xo = HAS_DELTA ? reinterpret_cast<bf16x8*>(x_out + (size_t)row * d) : nullptr;
+    float ss = 0.f;
+    for (int v = lane; v < vecs; v += 32) {
+      float f[8];
+      unpack8(xr[v], f);
+      if (HAS_DELTA) {
+        float g[8];
+        unpack8(dr[v], g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] += g[i];
+        bf16x8 packed = pack8(f);
+        xo[v] = packed;
+        unpack8(packed, f);  // normalise exactly what later kernels will read
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)d + eps);
+    if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+    const bf16x8* src = HAS_DELTA ? reinterpret_cast<const bf16x8*>(xo) : xr;
+    bf16x8* yr = reinterpret_cast<bf16x8*>(y + (size_t)row * d);
+    for (int v = lane; v < vecs; v += 32) {
+      float f[8];
+      unpack8(src[v], f);
+      const float4 w0 = reinterpret_cast<const float4*>(w)[2 * v];
+      const float4 w1 = reinterpret_cast<const float4*>(w)[2 * v + 1];
+      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * ww[i];
+      yr[v] = pack8(f);
+    }
+  }
+}
+
+// RMSNorm backward. dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres), dw += sum_rows(dy*xhat).
+// dw is accumulated per CTA in shared memory and flushed with one atomicAdd per column.
+template <bool HAS_DRES>
+__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                   const __nv_bfloat16* __restrict__ x,
+                                   const float* __restrict__ w, const float* __restrict__ rstd,
+                                   const __nv_bfloat16* __restrict__ dres,
+                                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, int rows,
+                                   int d) {
+  extern __shared__ float dw_smem[];
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dw_smem[i] = 0.f;
+  __syncthreads();
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int vecs = d >> 3;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += gridDim.x * warps_per_block) {
+    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + (size_t)row * d);
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)row * d);
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int v = lane; v < vecs; v += 32) {
+      float g[8], f[8];
+      unpack8(dyr[v], g);
+      unpack8(xr[v], f);
+      const float4 w0 = reinterpret_cast<const float4*>(w)[2 * v];
+      const float4 w1 = reinterpret_cast<const float4*>(w)[2 * v + 1];
+      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dot += g[i] * ww[i] * f[i] * r;
+    }
+    dot = warp_sum(dot) / (float)d;
+    bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + (size_t)row * d);
+    const bf16x8* drr =
+        HAS_DRES ? reinterpret_cast<const bf16x8*>(dres + (size_t)row * d) : nullptr;
+    for (int v = lane; v < vecs; v += 32) {
+      float g[8], f[8], o[8];
+      unpack8(dyr[v], g);
+      unpack8(xr[v], f);
+      const float4 w0 = reinterpret_cast<const float4*>(w)[2 * v];
+      const float4 w1 = reinterpret_cast<const float4*>(w)[2 * v + 1];
+      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      float extra[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      if (HAS_DRES) unpack8(drr[v], extra);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xhat = f[i] * r;
+        o[i] = r * (g[i] * ww[i] - xhat * dot) + extra[i];
+        atomicAdd(&dw_smem[8 * v + i], g[i] * xhat);
+      }
+      dxr[v] = pack8(o);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = dw_smem[i];
+    if (v != 0.f) atomicAdd(&dw[i], v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// RoPE on interleaved pairs for q (B,T,H,D) and k (B,T,Hk,D) in one launch. cos/sin are (T, D/2)
+// fp32 rows for the positions being processed. `sign` = -1 rotates by -theta (the backward pass).
+// ------------------------------------------------------------------------------------------------
+__global__ void rope_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                            __nv_bfloat16* __restrict__ qo, __nv_bfloat16* __restrict__ ko,
+                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, int B,
+                            int T, int H, int Hk, int D, float sign, int64_t q_row_stride,
+                            int64_t k_row_stride, int64_t qo_row_stride, int64_t ko_row_stride) {
+  const int vec_per_head = D >> 3;
+  const int64_t q_vecs = (int64_t)B * T * H * vec_per_head;
+  const int64_t total = q_vecs + (int64_t)B * T * Hk * vec_per_head;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const bool is_q = idx < q_vecs;
+    const int64_t local = is_q ? idx : idx - q_vecs;
+    const int heads = is_q ? H : Hk;
+    const int c = (int)(local % vec_per_head);
+    const int h = (int)((local / vec_per_head) % heads);
+    const int64_t bt = local / ((int64_t)vec_per_head * heads);
+    const int t = (int)(bt % T);
+    const __nv_bfloat16* src =
+        (is_q ? q + bt * q_row_stride : k + bt * k_row_stride) + (int64_t)h * D + c * 8;
+    __nv_bfloat16* dst =
+        (is_q ? qo + bt * qo_row_stride : ko + bt * ko_row_stride) + (int64_t)h * D + c * 8;
+    float f[8], o[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(src), f);
+    const float4 cs = *reinterpret_cast<const float4*>(cos_t + (size_t)t * (D >> 1) + c * 4);
+    const float4 sn = *reinterpret_cast<const float4*>(sin_t + (size_t)t * (D >> 1) + c * 4);
+    const float cc[4] = {cs.x, cs.y, cs.z, cs.w};
+    const float ssn[4] = {sn.x * sign, sn.y * sign, sn.z * sign, sn.w * sign};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o[2 * i] = f[2 * i] * cc[i] - f[2 * i + 1] * ssn[i];
+      o[2 * i + 1] = f[2 * i] * ssn[i] + f[2 * i + 1] * cc[i];
+    }
+    *reinterpret_cast<bf16x8*>(dst) = pack8(o);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// SwiGLU: a = silu(g) * u and its backward. g/u/dg/du may be column slices of a wider matrix, so
+// each takes a row pitch.
+// ------------------------------------------------------------------------------------------------
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ g,
+                                  const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ a,
+                                  int64_t rows, int h, int64_t g_pitch, int64_t u_pitch,
+                                  int64_t a_pitch) {
+  const int vecs = h >> 3;
+  const int64_t total = rows * vecs;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / vecs;
+    const int c = (int)(idx - r * vecs) * 8;
+    float gf[8], uf[8], o[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(g + r * g_pitch + c), gf);
+    unpack8(*reinterpret_cast<const bf16x8*>(u + r * u_pitch + c), uf);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = gf[i] / (1.f + __expf(-gf[i])) * uf[i];
+    *reinterpret_cast<bf16x8*>(a + r * a_pitch + c) = pack8(o);
+  }
+}
+
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ da,
+                                  const __nv_bfloat16* __restrict__ g,
+                                  const __nv_bfloat16* __restrict__ u,
+                                  __nv_bfloat16* __restrict__ dg, __nv_bfloat16* __restrict__ du,
+                                  int64_t rows, int h, int64_t da_pitch, int64_t g_pitch,
+                                  int64_t u_pitch, int64_t dg_pitch, int64_t du_pitch) {
+  const int vecs = h >> 3;
+  const int64_t total = rows * vecs;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / vecs;
+    const int c = (int)(idx - r * vecs) * 8;
+    float df[8], gf[8], uf[8], og[8], ou[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(da + r * da_pitch + c), df);
+    unpack8(*reinterpret_cast<const bf16x8*>(g + r * g_pitch + c), gf);
+    unpack8(*reinterpret_cast<const bf16x8*>(u + r * u_pitch + c), uf);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float sig = 1.f / (1.f + __expf(-gf[i]));
+      const float silu = gf[i] * sig;
+      ou[i] = df[i] * silu;
+      og[i] = df[i] * uf[i] * (sig + silu * (1.f - sig));
+    }
+    *reinterpret_cast<bf16x8*>(dg + r * dg_pitch + c) = pack8(og);
+    *reinterpret_cast<bf16x8*>(du + r * du_pitch + c) = pack8(ou);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Casts and embedding
+// ------------------------------------------------------------------------------------------------
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                     int64_t n) {
+  const int64_t vecs = n >> 3;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < vecs;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const float4 a = reinterpret_cast<const float4*>(in)[2 * idx];
+    const float4 b = reinterpret_cast<const float4*>(in)[2 * idx + 1];
+    const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    reinterpret_cast<bf16x8*>(out)[idx] = pack8(f);
+  }
+  if (blockIdx.x == 0) {
+    for (int64_t i = (vecs << 3) + threadIdx.x; i < n; i += blockDim.x)
+      out[i] = __float2bfloat16_rn(in[i]);
+  }
+}
+
+__global__ void embedding_fwd_kernel(const int64_t* __restrict__ ids, const float* __restrict__ table,
+                                     __nv_bfloat16* __restrict__ out, int64_t tokens, int d,
+                                     int vocab) {
+  const int vecs = d >> 3;
+  const int64_t total = tokens * vecs;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / vecs;
+    const int c = (int)(idx - t * vecs);
+    int64_t id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    const float4* src = reinterpret_cast<const float4*>(table + id * d) + 2 * c;
+    const float4 a = src[0], b = src[1];
+    const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    reinterpret_cast<bf16x8*>(out + t * d)[c] = pack8(f);
+  }
+}
+
+__global__ void embedding_bwd_kernel(const int64_t* __restrict__ ids,
+                                     const __nv_bfloat16* __restrict__ dout,
+                                     float* __restrict__ dtable, int64_t tokens, int d, int vocab) {
+  const int vecs = d >> 3;
+  const int64_t total = tokens * vecs;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / vecs;
+    const int c = (int)(idx - t * vecs);
+    const int64_t id = ids[t];
+    if (id < 0 || id >= vocab) continue;
+    float f[8];
+    unpack8(reinterpret_cast<const bf16x8*>(dout + t * d)[c], f);
+    float4* dst = reinterpret_cast<float4*>(dtable + id * d) + 2 * c;
+    atomicAdd(dst, make_float4(f[0], f[1], f[2], f[3]));
+    atomicAdd(dst + 1, make_float4(f[4], f[5], f[6], f[7]));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// AdamW on an fp32 master tensor; optionally refreshes the bf16 compute copy in the same pass.
+// Matches torch.optim.AdamW: decoupled decay, bias-corrected moments, eps added after the sqrt.
+// ------------------------------------------------------------------------------------------------
+template <typename GradT>
+__global__ void adamw_kernel(float* __restrict__ p, const GradT* __restrict__ g,
+                             float* __restrict__ m, float* __restrict__ v,
+                             __nv_bfloat16* __restrict__ shadow, int64_t n, float lr, float beta1,
+                             float beta2, float eps, float wd, float bc1, float bc2,
+                             float grad_scale) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const float grad = static_cast<float>(g[i]) * grad_scale;
+    float param = p[i] * (1.f - lr * wd);
+    const float mi = m[i] + (1.f - beta1) * (grad - m[i]);
+    const float vi = v[i] + (1.f - beta2) * (grad * grad - v[i]);
+    m[i] = mi;
+    v[i] = vi;
+    const float denom = sqrtf(vi / bc2) + eps;
+    param -= (lr / bc1) * mi / denom;
+    p[i] = param;
+    if (shadow != nullptr) shadow[i] = __float2bfloat16_rn(param);
+  }
+}
+
+inline int grid_for(int64_t work_items, int threads, int max_blocks_per_sm = 8) {
+  const int64_t blocks = (work_items + threads - 1) / threads;
+  const int64_t cap = (int64_t)device_sm_count() * max_blocks_per_sm;
+  return (int)std::max<int64_t>(1, std::min<int64_t>(blocks, cap));
+}
+
+}  // namespace
+
+void rmsnorm_fwd(const void* x, const void* delta, const float* w, void* y, void* x_out, float* rstd,
+                 int rows, int d, float eps, cudaStream_t stream) {
+  OB_CHECK(d % 8 == 0, "rmsnorm: width must be a multiple of 8");
+  const int threads = 256;
+  const int blocks = grid_for((int64_t)rows * 32, threads, 8);
+  if (delta != nullptr)
+    rmsnorm_fwd_kernel<true><<<blocks, threads, 0, stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)delta, w, (__nv_bfloat16*)y,
+        (__nv_bfloat16*)x_out, rstd, rows, d, eps);
+  else
+    rmsnorm_fwd_kernel<false><<<blocks, threads, 0, stream>>>(
+        (const __nv_bfloat16*)x, nullptr, w, (__nv_bfloat16*)y, nullptr, rstd, rows, d, eps);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+void rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* dres,
+                 void* dx, float* dw, int rows, int d, cudaStream_t stream) {
+  OB_CHECK(d % 8 == 0, "rmsnorm: width must be a multiple of 8");
+  OB_CHECK(d * sizeof(float) <= 48 * 1024, "rmsnorm backward: width too large for shared memory");
+  const int threads = 256;
+  const int blocks = grid_for((int64_t)rows * 32, threads, 4);
+  if (dres != nullptr)
+    rmsnorm_bwd_kernel<true><<<blocks, threads, d * sizeof(float), stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dres,
+        (__nv_bfloat16*)dx, dw, rows, d);
+  else
+    rmsnorm_bwd_kernel<false><<<blocks, threads, d * sizeof(float), stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, nullptr, (__nv_bfloat16*)dx, dw,
+        rows, d);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+void rope_qk(const void* q, const void* k, void* qo, void* ko, const float* cos_t,
+             const float* sin_t, int B, int T, int H, int Hk, int D, bool inverse,
+             int64_t q_row_stride, int64_t k_row_stride, int64_t qo_row_stride,
+             int64_t ko_row_stride, cudaStream_t stream) {
+  OB_CHECK(D % 8 == 0, "rope: head_dim must be a multiple of 8");
+  const int64_t total = (int64_t)B * T * (H + Hk) * (D / 8);
+  const int threads = 256;
+  rope_kernel<<<grid_for(total, threads), threads, 0, stream>>>(
+      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (__nv_bfloat16*)qo, (__nv_bfloat16*)ko,
+      cos_t, sin_t, B, T, H, Hk, D, inverse ? -1.f : 1.f, q_row_stride, k_row_stride,
+      qo_row_stride, ko_row_stride);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+void swiglu_fwd(const void* g, const void* u, void* a, int64_t rows, int h, int64_t g_pitch,
+                int64_t u_pitch, int64_t a_pitch, cudaStream_t stream) {
+  OB_CHECK(h % 8 == 0, "swiglu: width must be a multiple of 8");
+  const int threads = 256;
+  swiglu_fwd_kernel<<<grid_for(rows * (h / 8), threads), threads, 0, stream>>>(
+      (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (__nv_bfloat16*)a, rows, h, g_pitch,
+      u_pitch, a_pitch);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+void swiglu_bwd(const void* da, const void* g, const void* u, void* dg, void* du, int64_t rows,
+                int h, int64_t da_pitch, int64_t g_pitch, int64_t u_pitch, int64_t dg_pitch,
+                int64_t du_pitch, cudaStream_t stream) {
+  OB_CHECK(h % 8 == 0, "swiglu: width must be a multiple of 8");
+  const int threads = 256;
+  swiglu_bwd_kernel<<<grid_for(rows * (h / 8), threads), threads, 0, stream>>>(
+      (const __nv_bfloat16*)da, (const __nv_bfloat16*)g, (const __nv_bfloat16*)u,
+      (__nv_bfloat16*)dg, (__nv_bfloat16*)du, rows, h, da_pitch, g_pitch, u_pitch, dg_pitch,
+      du_pitch);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+void cast_f32_bf16(const float* in, void* out, int64_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  const int threads = 256;
+  cast_f32_bf16_kernel<<<grid_for((n + 7) / 8, threads), threads, 0, stream>>>(
+      in, (__nv_bfloat16*)out, n);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+void embedding_fwd(const int64_t* ids, const float* table, void* out, int64_t tokens, int d,
+                   int vocab, cudaStream_t stream) {
+  OB_CHECK(d % 8 == 0, "embedding: width must be a multiple of 8");
+  const int threads = 256;
+  embedding_fwd_kernel<<<grid_for(tokens * (d / 8), threads), threads, 0, stream>>>(
+      ids, table, (__nv_bfloat16*)out, tokens, d, vocab);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+void embedding_bwd(const int64_t* ids, const void* dout, float* dtable, int64_t tokens, int d,
+                   int vocab, cudaStream_t stream) {
+  OB_CHECK(d % 8 == 0, "embedding: width must be a multiple of 8");
+  const int threads = 256;
+  embedding_bwd_kernel<<<grid_for(tokens * (d / 8), threads), threads, 0, stream>>>(
+      ids, (const __nv_bfloat16*)dout, dtable, tokens, d, vocab);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+void adamw_step(float* p, const void* g, bool grad_is_bf16, float* m, float* v, void* shadow,
+                int64_t n, float lr, float beta1, float beta2, float eps, float wd, float bc1,
+                float bc2, float grad_scale, cudaStream_t stream) {
+  if (n == 0) return;
+  const int threads = 256;
+  const int blocks = grid_for(n, threads);
+  if (grad_is_bf16)
+    adamw_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+        p, (const __nv_bfloat16*)g, m, v, (__nv_bfloat16*)shadow, n, lr, beta1, beta2, eps, wd, bc1,
+        bc2, grad_scale);
+  else
+    adamw_kernel<float><<<blocks, threads, 0, stream>>>(p, (const float*)g, m, v,
+                                                        (__nv_bfloat16*)shadow, n, lr, beta1, beta2,
+                                                        eps, wd, bc1, bc2, grad_scale);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace ob

@@ -1,0 +1,397 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA-fed shared-memory pipeline, tcgen05.mma
+// with fp32 accumulators in TMEM (double buffered, so the epilogue of tile i overlaps the main loop
+// of tile i+1), epilogue TMEM -> registers -> swizzled smem -> TMA store (or TMA reduce-add for
+// split-K / gradient accumulation).
+//
+//   C[b] (M x N, row major) = alpha * A[b] (M x K) * B[b] (N x K)^T
+//
+// Each operand may be stored K-major (rows indexed by M/N, K contiguous) or MN-major (rows indexed
+// by K, M/N contiguous); together these cover the NT / NN / TN products of a linear layer's forward,
+// input-gradient and weight-gradient without materialising a transpose.
+//
+// Optional ragged modes for mixture-of-experts:
+//   * m_tile_batch : per 128-row tile of A/C, which batch of B to use (grouped forward / dgrad;
+//                    A and C are plain 2-D matrices whose row groups are padded to 128).
+//   * k_offsets    : per output batch, the [begin, end) range of the shared K (token) dimension
+//                    (grouped weight gradient; A and B are plain 2-D matrices).
+//
+// Warp roles (192 threads): warps 0-3 epilogue (TMEM lane quarter = warp index), warp 4 TMA
+// producer, warp 5 MMA issuer + TMEM allocator.
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace ob {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int kNumThreads = 192;
+
+struct GemmParams {
+  int M, N, K;
+  int batches;
+  int a_mn, b_mn;
+  int a_batched, b_batched;
+  int splits;
+  int reduce;
+  float alpha;
+  const int* m_tile_batch;
+  const int* k_offsets;
+  int* status;
+};
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStagingBytes = 4 /*warps*/ * 2 /*buffers*/ * 4096;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
+};
+
+template <int BN, bool OUT_F32>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  using L = SmemLayout<BN>;
+  constexpr int kStages = L::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* stage_base = smem;
+  uint8_t* staging = smem + kStages * L::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + L::kStagingBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* tmem_full = bars + 2 * kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const WaitCtx wctx{abort_flag, p.status};
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int m_tiles = (p.M + BM - 1) / BM;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int tiles_per_batch = m_tiles * n_tiles * p.splits;
+  const int total_tiles = tiles_per_batch * p.batches;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tmem_full[0], 1);
+    mbar_init(&tmem_full[1], 1);
+    mbar_init(&tmem_empty[0], 4);
+    mbar_init(&tmem_empty[1], 4);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 4 && lane == 0) {
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    prefetch_tmap(&tmC);
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Decode a linear tile index. n fastest so CTAs running together share A rows through L2.
+  auto decode = [&](int tile, int& batch, int& mt, int& nt, int& kb_begin, int& kb_count,
+                    int& k_elem_begin) {
+    batch = tile / tiles_per_batch;
+    int r = tile - batch * tiles_per_batch;
+    int split = r / (m_tiles * n_tiles);
+    r -= split * (m_tiles * n_tiles);
+    mt = r / n_tiles;
+    nt = r - mt * n_tiles;
+    int k_lo = 0, k_hi = p.K;
+    if (p.k_offsets != nullptr) {
+      k_lo = p.k_offsets[batch];
+      k_hi = p.k_offsets[batch + 1];
+    }
+    int kb_total = (k_hi - k_lo + BK - 1) / BK;
+    int per = (kb_total + p.splits - 1) / p.splits;
+    kb_begin = split * per;
+    int kb_end = min(kb_begin + per, kb_total);
+    kb_count = max(kb_end - kb_begin, 0);
+    k_elem_begin = k_lo;
+  };
+
+  if (warp == 4) {
+    // ------------------------------- TMA producer -------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int batch, mt, nt, kb_begin, kb_count, k0;
+        decode(tile, batch, mt, nt, kb_begin, kb_count, k0);
+        int b_batch = batch;
+        if (p.m_tile_batch != nullptr) {
+          b_batch = p.m_tile_batch[mt];
+          if (b_batch < 0) continue;  // padding tile: nothing to compute
+        }
+        const int za = p.a_batched ? batch : 0;
+        const int zb = p.b_batched ? b_batch : 0;
+        for (int kb = 0; kb < kb_count; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = (it / kStages) & 1;
+          if (!mbar_wait(&empty_bar[s], phase ^ 1, wctx, kTimeoutEmptyBarrier)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = stage_base + s * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          mbar_expect_tx(&full_bar[s], L::kStageBytes);
+          const int k = k0 + (kb_begin + kb) * BK;
+          if (p.a_mn) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_3d(sa + j * (BK * 128), &tmA, &full_bar[s], mt * BM + j * 64, k, za);
+          } else {
+            tma_load_3d(sa, &tmA, &full_bar[s], k, mt * BM, za);
+          }
+          if (p.b_mn) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sb + j * (BK * 128), &tmB, &full_bar[s], nt * BN + j * 64, k, zb);
+          } else {
+            tma_load_3d(sb, &tmB, &full_bar[s], k, nt * BN, zb);
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------- MMA issuer ----------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn != 0, p.b_mn != 0);
+      uint32_t it = 0;
+      uint32_t tile_iter = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int batch, mt, nt, kb_begin, kb_count, k0;
+        decode(tile, batch, mt, nt, kb_begin, kb_count, k0);
+        if (p.m_tile_batch != nullptr && p.m_tile_batch[mt] < 0) continue;
+        const uint32_t acc = tile_iter & 1;
+        const uint32_t acc_phase = (tile_iter >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, wctx, kTimeoutTmemEmpty)) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_acc = tmem_base + acc * BN;
+        for (int kb = 0; kb < kb_count; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = (it / kStages) & 1;
+          if (!mbar_wait(&full_bar[s], phase, wctx, kTimeoutFullBarrier)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(stage_base + s * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = p.a_mn ? make_smem_desc_sw128(sa + k * 2048, BK * 128, 1024)
+                                       : make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t db = p.b_mn ? make_smem_desc_sw128(sb + k * 2048, BK * 128, 1024)
+                                       : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            umma_bf16_ss(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+        }
+        if (!ok) break;
+        tcgen05_commit(&tmem_full[acc]);
+        ++tile_iter;
+      }
+    }
+  } else {
+    // ------------------------------- Epilogue (warps 0..3) -----------------------------------
+    uint8_t* my_staging = staging + warp * 2 * 4096;
+    uint32_t tile_iter = 0;
+    uint32_t store_iter = 0;
+    constexpr int kColsPerStore = OUT_F32 ? 32 : 64;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      int batch, mt, nt, kb_begin, kb_count, k0;
+      decode(tile, batch, mt, nt, kb_begin, kb_count, k0);
+      if (p.m_tile_batch != nullptr && p.m_tile_batch[mt] < 0) continue;
+      const uint32_t acc = tile_iter & 1;
+      const uint32_t acc_phase = (tile_iter >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, wctx, kTimeoutTmemFull)) break;
+      tcgen05_fence_after();
+      const bool skip_store = (kb_count == 0) && p.reduce;
+      const uint32_t taddr_row = tmem_base + acc * BN + (static_cast<uint32_t>(warp * 32) << 16);
+      const int row0 = mt * BM + warp * 32;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += kColsPerStore) {
+        const int col0 = nt * BN + c0;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint8_t* buf = my_staging + (store_iter & 1) * 4096;
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* my_row = buf + lane * 128;
+        if constexpr (OUT_F32) {
+          uint32_t v[32];
+          if (kb_count > 0) {
+            tmem_ld_32x32(taddr_row + c0, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 o;
+            o.x = __uint_as_float(v[4 * j + 0]) * p.alpha;
+            o.y = __uint_as_float(v[4 * j + 1]) * p.alpha;
+            o.z = __uint_as_float(v[4 * j + 2]) * p.alpha;
+            o.w = __uint_as_float(v[4 * j + 3]) * p.alpha;
+            *reinterpret_cast<float4*>(my_row + ((j ^ (lane & 7)) << 4)) = o;
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t v[32];
+            if (kb_count > 0) {
+              tmem_ld_32x32(taddr_row + c0 + h * 32, v);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = 0;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(v[8 * j + 0]) * p.alpha,
+                              __uint_as_float(v[8 * j + 1]) * p.alpha);
+              o.y = pack_bf16(__uint_as_float(v[8 * j + 2]) * p.alpha,
+                              __uint_as_float(v[8 * j + 3]) * p.alpha);
+              o.z = pack_bf16(__uint_as_float(v[8 * j + 4]) * p.alpha,
+                              __uint_as_float(v[8 * j + 5]) * p.alpha);
+              o.w = pack_bf16(__uint_as_float(v[8 * j + 6]) * p.alpha,
+                              __uint_as_float(v[8 * j + 7]) * p.alpha);
+              const int chunk = h * 4 + j;
+              *reinterpret_cast<uint4*>(my_row + ((chunk ^ (lane & 7)) << 4)) = o;
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && !skip_store && row0 < p.M) {
+          if (p.reduce)
+            tma_reduce_add_3d(&tmC, buf, col0, row0, batch);
+          else
+            tma_store_3d(&tmC, buf, col0, row0, batch);
+          tma_store_commit();
+        }
+        ++store_iter;
+      }
+      // All TMEM reads of this accumulator are complete (tmem_ld_wait above): hand it back.
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      ++tile_iter;
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+
+  // ------------------------------- Teardown ---------------------------------------------------
+  if (*abort_flag) {
+    // Give copies that are still in flight time to land before shared memory is released.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 1000000ull) __nanosleep(1000);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+template <int BN, bool OUT_F32>
+void launch_variant(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC,
+                    const GemmParams& p, int grid, cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  auto kernel = gemm_bf16_kernel<BN, OUT_F32>;
+  static bool configured = false;
+  if (!configured) {
+    OB_CUDA_CHECK(
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    configured = true;
+  }
+  kernel<<<grid, kNumThreads, L::kTotal, stream>>>(tA, tB, tC, p);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace
+
+// Host entry point. Pointers are device pointers; `ld*` are row pitches in elements of the stored
+// matrices; `stride*` are elements between consecutive batches (ignored when not batched).
+void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int batches, bool a_mn,
+               bool b_mn, int64_t lda, int64_t ldb, int64_t ldc, int64_t strideA, int64_t strideB,
+               int64_t strideC, bool a_batched, bool b_batched, int b_batches, bool out_f32,
+               int splits, bool reduce, float alpha, const int* m_tile_batch,
+               const int* k_offsets, int64_t a_rows, int64_t b_rows, int num_sms,
+               cudaStream_t stream) {
+  OB_CHECK(M > 0 && N > 0 && K >= 0 && batches > 0, "gemm_bf16: bad problem size");
+  OB_CHECK(!reduce || out_f32, "gemm_bf16: reduce-add epilogue needs an fp32 output");
+  OB_CHECK(splits >= 1 && (splits == 1 || reduce), "gemm_bf16: split-K needs the reduce epilogue");
+  const int BN = (N > 128) ? 256 : 128;
+
+  GemmParams p;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.batches = batches;
+  p.a_mn = a_mn;
+  p.b_mn = b_mn;
+  p.a_batched = a_batched;
+  p.b_batched = b_batched;
+  p.splits = splits;
+  p.reduce = reduce;
+  p.alpha = alpha;
+  p.m_tile_batch = m_tile_batch;
+  p.k_offsets = k_offsets;
+  p.status = status_ptr();
+
+  // Stored shapes: K-major operand is (rows = M or N, inner = K); MN-major is (rows = K, inner =
+  // M or N). `a_rows` / `b_rows` give the number of stored rows (the full token count in the
+  // ragged weight-gradient mode, where K is per batch).
+  CUtensorMap tA, tB, tC;
+  const uint64_t a_inner = a_mn ? (uint64_t)M : (uint64_t)K;
+  const uint64_t b_inner = b_mn ? (uint64_t)N : (uint64_t)K;
+  const int a_nb = a_batched ? batches : 1;
+  const int b_nb = b_batched ? b_batches : 1;
+  make_tmap_3d(&tA, A, TmapDtype::BF16, a_inner, (uint64_t)a_rows, (uint64_t)a_nb, lda, strideA, 64,
+               a_mn ? BK : BM, TmapSwizzle::B128);
+  make_tmap_3d(&tB, B, TmapDtype::BF16, b_inner, (uint64_t)b_rows, (uint64_t)b_nb, ldb, strideB, 64,
+               b_mn ? BK : BN, TmapSwizzle::B128);
+  make_tmap_3d(&tC, C, out_f32 ? TmapDtype::F32 : TmapDtype::BF16, (uint64_t)N, (uint64_t)M,
+               (uint64_t)batches, ldc, strideC, out_f32 ? 32 : 64, 32, TmapSwizzle::B128);
+
+  const int m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = (N + BN - 1) / BN;
+  const long long total = (long long)m_tiles * n_tiles * splits * batches;
+  const int grid = (int)std::min<long long>(total, num_sms);
+  if (BN == 256) {
+    if (out_f32)
+      launch_variant<256, true>(tA, tB, tC, p, grid, stream);
+    else
+      launch_variant<256, false>(tA, tB, tC, p, grid, stream);
+  } else {
+    if (out_f32)
+      launch_variant<128, true>(tA, tB, tC, p, grid, stream);
+    else
+      launch_variant<128, false>(tA, tB, tC, p, grid, stream);
+  }
+}
+
+}  // namespace ob

@@ -1,0 +1,57 @@
+// Host-side helpers shared by the kernel launchers: error checks and TMA descriptor construction.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <algorithm>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+
+namespace ob {
+
+#define OB_CHECK(cond, msg)                                                     \
+  do {                                                                          \
+    if (!(cond)) {                                                              \
+      std::ostringstream oss__;                                                 \
+      oss__ << "ohara_b200: " << msg << " (" << #cond << ") at " << __FILE__    \
+            << ":" << __LINE__;                                                 \
+      throw std::runtime_error(oss__.str());                                    \
+    }                                                                           \
+  } while (0)
+
+#define OB_CUDA_CHECK(expr)                                                      \
+  do {                                                                          \
+    cudaError_t err__ = (expr);                                                 \
+    if (err__ != cudaSuccess) {                                                 \
+      std::ostringstream oss__;                                                 \
+      oss__ << "ohara_b200: CUDA error " << cudaGetErrorString(err__) << " in " \
+            << #expr << " at " << __FILE__ << ":" << __LINE__;                  \
+      throw std::runtime_error(oss__.str());                                    \
+    }                                                                           \
+  } while (0)
+
+enum class TmapDtype { BF16, F32, U8 };
+enum class TmapSwizzle { NONE, B128 };
+
+// Up to 5-D tiled tensor map. dims[0] is the contiguous dimension; strides_bytes[i] is the byte
+// stride of dims[i+1] (rank-1 entries, each a multiple of 16).
+void make_tmap(CUtensorMap* out, const void* base, TmapDtype dtype, int rank, const uint64_t* dims,
+               const uint64_t* strides_bytes, const uint32_t* box, TmapSwizzle swizzle);
+
+// (inner, rows, batches) view of a row-pitched, batch-strided matrix. `pitch` and `batch_stride`
+// are in elements.
+void make_tmap_3d(CUtensorMap* out, const void* base, TmapDtype dtype, uint64_t inner,
+                  uint64_t rows, uint64_t batches, int64_t pitch, int64_t batch_stride,
+                  uint32_t box_inner, uint32_t box_rows, TmapSwizzle swizzle);
+
+int device_sm_count();
+
+// Device status word (see status.cpp): [0] first error code, [1] block that reported it, [2] number
+// of waits that ran out of time.
+int* status_ptr();
+void status_read(int out[4], bool clear);
+
+}  // namespace ob

@@ -1,0 +1,83 @@
+"""Scaled dot-product attention with native grouped-query heads.
+
+Layout is ``(batch, seq, heads, head_dim)`` throughout — the layout the QKV projections produce —
+so no transposes or KV head expansion are materialised. ``causal=True`` aligns the mask to the
+*end* of the key sequence (query ``i`` of ``T`` sees keys ``<= S - T + i``), which is plain causal
+attention when ``S == T`` and the KV-cache rule ``key_pos <= query_pos`` when ``S > T``.
+
+CUDA bf16 inputs run the flash-attention kernels (forward and backward); everything else runs the
+fp32 reference below, which is also the kernels' test oracle (reference slow path:
+ohara/models/llama.py:124-135).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import Tensor
+
+from ._ext import ext
+
+
+def attention_reference(q: Tensor, k: Tensor, v: Tensor, causal: bool = True,
+                        scale: float | None = None, dropout_p: float = 0.0,
+                        training: bool = False) -> Tensor:
+    """fp32 softmax(QK^T * scale + mask) V with grouped-query expansion. Shapes as in `attention`."""
+    b, t, h, d = q.shape
+    s, hk = k.shape[1], k.shape[2]
+    group = h // hk
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    qf = q.float().permute(0, 2, 1, 3)  # (b, h, t, d)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(group, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(group, dim=1)
+    scores = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        qpos = torch.arange(t, device=q.device) + (s - t)
+        kpos = torch.arange(s, device=q.device)
+        scores = scores.masked_fill(~(kpos[None, :] <= qpos[:, None]), float("-inf"))
+    probs = torch.softmax(scores, dim=-1)
+    if dropout_p > 0.0 and training:
+        probs = torch.nn.functional.dropout(probs, dropout_p)
+    out = torch.matmul(probs, vf)
+    return out.permute(0, 2, 1, 3).to(q.dtype)
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q: Tensor, k: Tensor, v: Tensor, causal: bool, scale: float):
+        out, lse = ext().flash_attn_fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.causal = causal
+        ctx.scale = scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout: Tensor):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = ext().flash_attn_bwd(dout.contiguous(), q, k, v, out, lse, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def _kernel_ok(q: Tensor, k: Tensor, v: Tensor) -> bool:
+    d = q.shape[-1]
+    return (
+        q.is_cuda
+        and q.dtype == k.dtype == v.dtype == torch.bfloat16
+        and d in (64, 128)
+        and q.shape[2] % k.shape[2] == 0
+    )
+
+
+def attention(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, scale: float | None = None,
+              dropout_p: float = 0.0, training: bool = False) -> Tensor:
+    """``q (B,T,H,D)``, ``k/v (B,S,Hk,D)`` → ``(B,T,H,D)``."""
+    if q.dim() != 4 or k.dim() != 4 or v.shape != k.shape:
+        raise ValueError("attention expects (batch, seq, heads, head_dim) tensors")
+    if q.shape[2] % k.shape[2] != 0:
+        raise ValueError("number of query heads must be a multiple of the number of KV heads")
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    use_dropout = dropout_p > 0.0 and training
+    if _kernel_ok(q, k, v) and not use_dropout:
+        return _FlashAttnFn.apply(q, k, v, causal, float(scale))
+    return attention_reference(q, k, v, causal, scale, dropout_p, training)
