@@ -40,6 +40,12 @@ void adamw_step(float* p, const void* g, bool grad_is_bf16, float* m, float* v, 
                 int64_t n, float lr, float beta1, float beta2, float eps, float wd, float bc1,
                 float bc2, float grad_scale, cudaStream_t stream);
 
+// attention_fwd_sm100.cu
+void flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T,
+                    int S, int H, int Hk, int D, bool causal, float scale, int64_t q_tok_stride,
+                    int64_t k_tok_stride, int64_t v_tok_stride, int64_t q_batch_stride,
+                    int64_t k_batch_stride, int64_t v_batch_stride, cudaStream_t stream);
+
 // cross_entropy.cu
 void cross_entropy_rows(void* logits, const int64_t* targets, float* row_loss, float* row_lse,
                         int* row_correct, const float* scale_ptr, int64_t rows, int vocab,

@@ -292,6 +292,35 @@ void scale_by_scalar(Tensor& x, const Tensor& scalar) {
   ob::scale_by_scalar(x.data_ptr(), bf16, scalar.data_ptr<float>(), x.numel(), current_stream());
 }
 
+// (B, T, H, D) tensors whose (heads, D) block is contiguous; token and batch strides are free.
+bool attn_layout_ok(const Tensor& t) {
+  return t.dim() == 4 && t.stride(3) == 1 && t.stride(2) == t.size(3) &&
+         (t.stride(1) * 2) % 16 == 0 && (t.stride(0) * 2) % 16 == 0 &&
+         reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0;
+}
+
+std::vector<Tensor> flash_attn_fwd(const Tensor& q_in, const Tensor& k_in, const Tensor& v_in,
+                                   bool causal, double scale) {
+  check_bf16(q_in, "q");
+  check_bf16(k_in, "k");
+  check_bf16(v_in, "v");
+  Tensor q = attn_layout_ok(q_in) ? q_in : q_in.contiguous();
+  Tensor k = attn_layout_ok(k_in) ? k_in : k_in.contiguous();
+  Tensor v = attn_layout_ok(v_in) ? v_in : v_in.contiguous();
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int64_t B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3);
+  const int64_t S = k.size(1), Hk = k.size(2);
+  TORCH_CHECK(k.size(0) == B && v.size(0) == B && k.size(3) == D && v.sizes() == k.sizes(),
+              "attention operand shapes do not match");
+  Tensor o = torch::empty({B, T, H, D}, q.options());
+  Tensor lse = torch::empty({B, H, T}, q.options().dtype(torch::kFloat32));
+  ob::flash_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(),
+                     (int)B, (int)T, (int)S, (int)H, (int)Hk, (int)D, causal, (float)scale,
+                     q.stride(1), k.stride(1), v.stride(1), q.stride(0), k.stride(0), v.stride(0),
+                     current_stream());
+  return {o, lse};
+}
+
 std::vector<int64_t> status(bool clear) {
   int out[4];
   ob::status_read(out, clear);
@@ -314,5 +343,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_step", &adamw_step);
   m.def("cross_entropy_rows", &cross_entropy_rows);
   m.def("scale_by_scalar", &scale_by_scalar);
+  m.def("flash_attn_fwd", &flash_attn_fwd);
   m.def("status", &status);
 }

@@ -1,0 +1,369 @@
+"""Llama-style decoder (dense, loop-MoE or grouped-MoE feed-forwards) — the product model.
+
+Public surface and checkpoint layout follow the reference model (ohara/models/llama.py:16-478):
+``Config``, ``Llama.forward(ids[, kv_cache, position_ids]) -> logits``, ``build_kv_cache``,
+``num_scaling_params``, ``active_matmul_parameters``, ``estimate_flops`` and state-dict keys
+``token_emb, layers.N.attn.{key,query,value,proj}, layers.N.ff.*, layers.N.norm{1,2}, norm,
+vocab_proj, freq_cos, freq_sin``.
+
+What is different underneath: every hot op goes through :mod:`ohara_b200.ops`. On a CUDA device in
+bf16 autocast the block runs as fused sm_100a kernels in the projection layout ``(B, T, H, D)``
+(no head transposes, no KV head expansion for GQA, no mask tensors), activations stay bf16, and
+``loss_sum`` fuses the output projection with the cross-entropy so logits are never materialised.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+from torch import Tensor
+
+from ohara_b200 import ops
+from ohara_b200.embeddings_pos.rotary import apply_rope, precompute_freqs_cis
+from ohara_b200.modules.kv_cache import KVCache
+from ohara_b200.modules.mlp import Linear, SwiGLU
+from ohara_b200.modules.moe import MoE
+from ohara_b200.modules.moe_grouped import GroupedMoE
+from ohara_b200.modules.norm import RMSNorm
+
+
+@dataclass
+class Config:
+    vocab_size: int = 65
+    max_sequence_length: int = 64
+    hidden_size: int = 128
+    intermediate_size: int = 256
+    num_attention_heads: int = 4
+    num_key_value_heads: int = 0  # 0 = multi-head attention (one KV head per query head)
+    num_hidden_layers: int = 4
+    dropout: float = 0.2
+    multiple_of: int = 4
+    bias: bool = False
+    weight_tying: bool = False
+    rope_theta: float = 100000
+    init_style: str = "standard"
+    # Mixture of experts: 0 experts keeps every feed-forward dense; with interval N every N-th
+    # layer (layer_idx % N == 0) is an MoE.
+    moe_num_experts: int = 0
+    moe_experts_per_tok: int = 2
+    moe_layer_interval: int = 1
+    moe_gate_fn: str = "softmax"
+    moe_quantile_balancing: bool = True
+    moe_grouped: bool = False
+    moe_num_shared_experts: int = 0
+    moe_normalize_weights: bool = True
+    # Extensions over the reference Config (defaults keep its behaviour): Switch-style auxiliary
+    # loss coefficient and expert capacity factor for the grouped MoE.
+    moe_aux_loss_coef: float = 0.0
+    moe_capacity_factor: float | None = None
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_attention_heads
+
+    @property
+    def kv_heads(self) -> int:
+        return self.num_key_value_heads or self.num_attention_heads
+
+
+def validate_config(cfg: Config) -> None:
+    if cfg.vocab_size < 2:
+        raise ValueError("vocab_size must be at least 2")
+    if cfg.hidden_size < 1 or cfg.num_hidden_layers < 1:
+        raise ValueError("hidden_size and num_hidden_layers must be positive")
+    if cfg.intermediate_size < 1:
+        raise ValueError("intermediate_size must be positive")
+    if cfg.num_attention_heads < 1 or cfg.hidden_size % cfg.num_attention_heads != 0:
+        raise ValueError("hidden_size must be divisible by num_attention_heads")
+    if (cfg.hidden_size // cfg.num_attention_heads) % 2 != 0:
+        raise ValueError("attention head dimension must be even for rotary embeddings")
+    if cfg.max_sequence_length < 2:
+        raise ValueError("max_sequence_length must be at least 2")
+    kv_heads = cfg.num_key_value_heads or cfg.num_attention_heads
+    if kv_heads < 1 or cfg.num_attention_heads % kv_heads != 0:
+        raise ValueError("num_key_value_heads must divide num_attention_heads")
+    if not 0.0 <= cfg.dropout < 1.0:
+        raise ValueError("dropout must be in [0, 1)")
+    if cfg.init_style not in {"standard", "nanochat"}:
+        raise ValueError("init_style must be 'standard' or 'nanochat'")
+    if cfg.init_style == "nanochat" and cfg.weight_tying:
+        raise ValueError("nanochat initialization requires untied embeddings")
+    if cfg.moe_num_experts < 0 or cfg.moe_num_shared_experts < 0:
+        raise ValueError("MoE expert counts cannot be negative")
+    if cfg.moe_layer_interval < 1:
+        raise ValueError("moe_layer_interval must be positive")
+    if cfg.moe_gate_fn not in {"softmax", "sigmoid"}:
+        raise ValueError("moe_gate_fn must be 'softmax' or 'sigmoid'")
+    if cfg.moe_grouped and cfg.moe_num_experts == 0:
+        raise ValueError("moe_grouped requires moe_num_experts > 0")
+    if cfg.moe_num_shared_experts > 0 and not cfg.moe_grouped:
+        raise ValueError("shared experts require moe_grouped")
+    if not cfg.moe_normalize_weights and not cfg.moe_grouped:
+        raise ValueError("moe_normalize_weights only applies to grouped MoE")
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: Config):
+        super().__init__()
+        d = cfg.hidden_size
+        self.num_attention_heads = cfg.num_attention_heads
+        self.head_dim = d // cfg.num_attention_heads
+        self.num_key_value_heads = cfg.num_key_value_heads or cfg.num_attention_heads
+        assert self.num_attention_heads % self.num_key_value_heads == 0
+        self.num_queries_per_kv = self.num_attention_heads // self.num_key_value_heads
+        self.key = Linear(d, self.head_dim * self.num_key_value_heads, cfg.bias)
+        self.query = Linear(d, self.head_dim * self.num_attention_heads, cfg.bias)
+        self.value = Linear(d, self.head_dim * self.num_key_value_heads, cfg.bias)
+        self.proj = Linear(self.head_dim * self.num_attention_heads, d, cfg.bias)
+        self.attn_dropout = nn.Dropout(cfg.dropout)
+        self.res_dropout = nn.Dropout(cfg.dropout)
+
+    def forward(self, x: Tensor, mask: Tensor | None, freqs_cis, kv_cache: KVCache | None = None,
+                position_ids: int | None = None) -> Tensor:
+        batch, seq_len, _ = x.shape
+        # Local head counts are derived from the projection widths so a tensor-parallel shard of
+        # this module (fewer output features) needs no patching.
+        heads = self.query.weight.shape[0] // self.head_dim
+        kv_heads = self.key.weight.shape[0] // self.head_dim
+        q = self.query(x).view(batch, seq_len, heads, self.head_dim)
+        k = self.key(x).view(batch, seq_len, kv_heads, self.head_dim)
+        v = self.value(x).view(batch, seq_len, kv_heads, self.head_dim)
+        q, k = apply_rope(q, k, freqs_cis)
+        if kv_cache is not None:
+            assert position_ids is not None
+            k, v = kv_cache.forward(k, v.to(k.dtype), position_ids)
+        out = ops.attention(
+            q, k.to(q.dtype), v.to(q.dtype), causal=True,
+            dropout_p=self.attn_dropout.p, training=self.training,
+        )
+        out = out.reshape(batch, seq_len, heads * self.head_dim)
+        return self.res_dropout(self.proj(out))
+
+
+def uses_moe(cfg: Config, layer_idx: int) -> bool:
+    """Whether layer ``layer_idx`` has a mixture-of-experts feed-forward."""
+    return cfg.moe_num_experts >= 1 and layer_idx % cfg.moe_layer_interval == 0
+
+
+class Block(nn.Module):
+    def __init__(self, cfg: Config, layer_idx: int = 0):
+        super().__init__()
+        self.attn = Attention(cfg)
+        self.is_moe = uses_moe(cfg, layer_idx)
+        if self.is_moe and cfg.moe_grouped:
+            self.ff = GroupedMoE(
+                dim=cfg.hidden_size, hidden_dim=cfg.intermediate_size,
+                num_experts=cfg.moe_num_experts, num_experts_per_tok=cfg.moe_experts_per_tok,
+                num_shared_experts=cfg.moe_num_shared_experts, gate_fn=cfg.moe_gate_fn,
+                normalize_weights=cfg.moe_normalize_weights,
+                quantile_balancing=cfg.moe_quantile_balancing,
+                aux_loss_coef=getattr(cfg, "moe_aux_loss_coef", 0.0),
+                capacity_factor=getattr(cfg, "moe_capacity_factor", None),
+            )
+        elif self.is_moe:
+            self.ff = MoE(
+                dim=cfg.hidden_size, hidden_dim=cfg.intermediate_size,
+                num_experts=cfg.moe_num_experts, num_experts_per_tok=cfg.moe_experts_per_tok,
+                gate_fn=cfg.moe_gate_fn, quantile_balancing=cfg.moe_quantile_balancing,
+            )
+        else:
+            self.ff = SwiGLU(dim=cfg.hidden_size, hidden_dim=cfg.intermediate_size,
+                             dropout=cfg.dropout, bias=cfg.bias)
+        self.norm1 = RMSNorm(cfg.hidden_size)
+        self.norm2 = RMSNorm(cfg.hidden_size)
+
+    def forward(self, x, mask, freqs_cis, kv_cache: KVCache | None = None,
+                position_ids: int | None = None):
+        x = x + self.attn(self.norm1(x), mask, freqs_cis, kv_cache, position_ids).to(x.dtype)
+        x = x + self.ff(self.norm2(x)).to(x.dtype)
+        return x
+
+
+class Llama(nn.Module):
+    def __init__(self, cfg: Config, *args, **kwargs) -> None:
+        super().__init__(*args, **kwargs)
+        validate_config(cfg)
+        self.config = cfg
+        self.token_emb = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
+        self.layers = nn.ModuleList([Block(cfg, i) for i in range(cfg.num_hidden_layers)])
+        self.norm = RMSNorm(cfg.hidden_size)
+        self.vocab_proj = Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
+        if cfg.weight_tying:
+            self.token_emb.weight = self.vocab_proj.weight
+        cos, sin = precompute_freqs_cis(cfg.head_dim, cfg.max_sequence_length * 2, cfg.rope_theta)
+        self.register_buffer("freq_cos", cos)
+        self.register_buffer("freq_sin", sin)
+        self.mask = None  # kept for API parity; masks are never materialised here
+        self.apply(self._init_weights)
+        if cfg.init_style == "nanochat":
+            self._init_nanochat_weights()
+
+    # -- forward --------------------------------------------------------------------------------
+    def _check_inputs(self, x: Tensor, kv_cache, position_ids) -> int:
+        if x.ndim != 2:
+            raise ValueError("input token IDs must have shape (batch, sequence)")
+        if isinstance(position_ids, Tensor):
+            if position_ids.numel() != 1:
+                raise ValueError("position_ids must be a scalar cache position")
+            position_ids = int(position_ids.item())
+        start = 0
+        if kv_cache is not None:
+            if len(kv_cache) != len(self.layers):
+                raise ValueError("KV cache must contain one entry per model layer")
+            if position_ids is None or position_ids < 0:
+                raise ValueError("a non-negative position_ids is required with KV cache")
+            start = position_ids
+        elif position_ids is not None:
+            raise ValueError("position_ids is only valid when using a KV cache")
+        if x.size(1) < 1:
+            raise ValueError("input sequence cannot be empty")
+        if start + x.size(1) > self.config.max_sequence_length:
+            raise ValueError("input exceeds max_sequence_length")
+        return start
+
+    def forward_hidden(self, x: Tensor, kv_cache: list[KVCache] | None = None,
+                       position_ids: int | Tensor | None = None) -> Tensor:
+        """Final-norm hidden states ``(B, T, hidden)`` (everything except the output projection)."""
+        start = self._check_inputs(x, kv_cache, position_ids)
+        seq = x.size(1)
+        h = ops.embedding(x, self.token_emb.weight)
+        freqs = (self.freq_cos[start : start + seq], self.freq_sin[start : start + seq])
+        for idx, layer in enumerate(self.layers):
+            cache = kv_cache[idx] if kv_cache is not None else None
+            h = layer(h, None, freqs, cache, start if cache is not None else None)
+        return self.norm(h)
+
+    def forward(self, x: Tensor, kv_cache: list[KVCache] | None = None,
+                position_ids: int | Tensor | None = None) -> Tensor:
+        return self.vocab_proj(self.forward_hidden(x, kv_cache, position_ids))
+
+    def loss_sum(self, x: Tensor, targets: Tensor, ignore_index: int = -1,
+                 scale: Tensor | float | None = None) -> Tensor:
+        """``scale * Σ CE(logits, targets)`` over supervised targets, with the output projection
+        fused into the loss (no logits tensor). Adds any MoE auxiliary losses (also scaled)."""
+        hidden = self.forward_hidden(x)
+        loss = ops.linear_cross_entropy(hidden, self.vocab_proj.weight, targets, ignore_index, scale)
+        aux = self.auxiliary_loss()
+        if aux is not None:
+            valid = (targets != ignore_index).sum().clamp_min(1).to(loss.dtype)
+            aux = aux * valid  # per-token coefficient under a sum-reduced loss
+            loss = loss + (aux if scale is None else aux * scale)
+        return loss
+
+    def auxiliary_loss(self) -> Tensor | None:
+        terms = [
+            layer.ff.aux_loss
+            for layer in self.layers
+            if getattr(layer.ff, "aux_loss", None) is not None and self.training
+        ]
+        return torch.stack(terms).sum() if terms else None
+
+    def build_kv_cache(self, batch_size: int = 1, int8: bool = False) -> list[KVCache]:
+        """One empty cache per layer, on the model's device and dtype."""
+        if batch_size < 1:
+            raise ValueError("batch_size must be at least 1")
+        cfg = self.config
+        shape = (batch_size, cfg.max_sequence_length, cfg.kv_heads, cfg.head_dim)
+        weight = self.token_emb.weight
+        dtype = weight.dtype
+        if weight.is_cuda and dtype == torch.float32 and torch.is_autocast_enabled("cuda"):
+            dtype = torch.get_autocast_dtype("cuda")
+        return [
+            KVCache(shape, cfg.max_sequence_length, idx, device=weight.device, dtype=dtype, int8=int8)
+            for idx in range(cfg.num_hidden_layers)
+        ]
+
+    # -- accounting -----------------------------------------------------------------------------
+    def num_scaling_params(self) -> dict[str, int]:
+        """Parameter groups used by compute-optimal scaling analysis."""
+        token_embeddings = self.token_emb.weight.numel()
+        lm_head = 0 if self.vocab_proj.weight is self.token_emb.weight else self.vocab_proj.weight.numel()
+        matrices = sum(p.numel() for layer in self.layers for p in layer.parameters() if p.ndim >= 2)
+        total = sum(p.numel() for p in self.parameters())
+        rest = total - token_embeddings - lm_head - matrices
+        if rest < 0:
+            raise RuntimeError("parameter groups overlap")
+        return {
+            "token_embeddings": token_embeddings,
+            "lm_head": lm_head,
+            "transformer_matrices": matrices,
+            "norms_and_scalars": rest,
+            "total": total,
+            "effective": matrices + lm_head,
+        }
+
+    def active_matmul_parameters(self) -> int:
+        """Matrix parameters one token passes through (routed experts count k of E)."""
+        total = 0
+        for block in self.layers:
+            total += sum(p.numel() for p in block.attn.parameters() if p.ndim >= 2)
+            ff = block.ff
+            if isinstance(ff, GroupedMoE):
+                per_expert = ff.dim * ff.hidden_dim * 3
+                total += per_expert * (ff.num_experts_per_tok + ff.num_shared_experts)
+                total += ff.router.weight.numel()
+            elif block.is_moe:
+                per_expert = sum(p.numel() for p in ff.experts[0].parameters() if p.ndim >= 2)
+                total += per_expert * ff.num_experts_per_tok + ff.gate.weight.numel()
+            else:
+                total += sum(p.numel() for p in ff.parameters() if p.ndim >= 2)
+        return total
+
+    def estimate_flops(self, sequence_length: int | None = None) -> float:
+        """Forward+backward FLOPs per token: 6·(active matmul params + head) + 12·L·H·D·T."""
+        cfg = self.config
+        sequence_length = sequence_length or cfg.max_sequence_length
+        if not 1 <= sequence_length <= cfg.max_sequence_length:
+            raise ValueError("sequence_length must be within the configured context window")
+        matmul = self.active_matmul_parameters() + self.vocab_proj.weight.numel()
+        attention = 12 * cfg.num_hidden_layers * cfg.num_attention_heads * cfg.head_dim * sequence_length
+        return float(6 * matmul + attention)
+
+    # -- init -----------------------------------------------------------------------------------
+    def _init_weights(self, module: nn.Module) -> None:
+        if isinstance(module, nn.Linear):
+            nn.init.normal_(module.weight, mean=0.0, std=0.02)
+            if module.bias is not None:
+                nn.init.zeros_(module.bias)
+        elif isinstance(module, nn.Embedding):
+            nn.init.normal_(module.weight, mean=0.0, std=0.02)
+        elif isinstance(module, GroupedMoE):
+            for w in (module.w_gate, module.w_up, module.w_down):
+                nn.init.normal_(w, mean=0.0, std=0.02)
+            module.router_bias.zero_()
+
+    @torch.no_grad()
+    def _init_nanochat_weights(self) -> None:
+        """Width-transferable init: wide embedding, tiny head, uniform q/k/v and gate/up, zero
+        output projections so every block starts as the identity on the residual stream."""
+        nn.init.normal_(self.token_emb.weight, mean=0.0, std=0.8)
+        nn.init.normal_(self.vocab_proj.weight, mean=0.0, std=0.001)
+        bound = math.sqrt(3.0) * self.config.hidden_size**-0.5
+        for block in self.layers:
+            for proj in (block.attn.query, block.attn.key, block.attn.value):
+                nn.init.uniform_(proj.weight, -bound, bound)
+            nn.init.zeros_(block.attn.proj.weight)
+            if isinstance(block.ff, GroupedMoE):
+                block.ff.reset_parameters()
+            else:
+                experts = block.ff.experts if block.is_moe else [block.ff]
+                for expert in experts:
+                    nn.init.uniform_(expert.up.weight, -0.4 * bound, 0.4 * bound)
+                    nn.init.uniform_(expert.gate.weight, -0.4 * bound, 0.4 * bound)
+                    nn.init.zeros_(expert.down.weight)
+                if block.is_moe:
+                    nn.init.normal_(block.ff.gate.weight, mean=0.0, std=self.config.hidden_size**-0.5)
+                    block.ff.router_bias.zero_()
+            block.norm1.reset_parameters()
+            block.norm2.reset_parameters()
+        self.norm.reset_parameters()
+
+    @classmethod
+    def from_pretrained(cls, hf_name: str):
+        raise NotImplementedError(
+            "Llama.from_pretrained is not implemented yet. "
+            "Use a model-specific loader or initialize `Llama(Config(...))` directly."
+        )

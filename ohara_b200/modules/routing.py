@@ -1,0 +1,126 @@
+"""Top-k routing and quantile balancing shared by the loop and grouped mixture-of-experts layers.
+
+Routing rule (reference: ohara/modules/moe.py:65-154, ohara/modules/moe_grouped.py:122-147,
+232-257): router logits are fp32; experts are *selected* by ``logits + router_bias`` but *weighted*
+by the unbiased logits; with quantile balancing the (k+1)-th biased logit of each token is its
+threshold ``alpha``. After each optimizer step the bias is re-solved in closed form from the
+per-expert quantile of ``logit - alpha`` (no auxiliary loss).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch import Tensor
+
+
+def router_logits(flat: Tensor, weight: Tensor) -> Tensor:
+    """fp32 router scores ``flat @ weight.T`` regardless of any surrounding autocast region."""
+    with torch.autocast(device_type=flat.device.type, enabled=False):
+        return torch.nn.functional.linear(flat.float(), weight.float())
+
+
+def route_tokens(logits: Tensor, router_bias: Tensor, k: int, gate_fn: str,
+                 quantile_balancing: bool, normalize_sigmoid: bool = False):
+    """Return ``(expert_indices (N,k), expert_weights (N,k) fp32, alpha (N,1) | None)``."""
+    alpha = None
+    if quantile_balancing:
+        top = torch.topk(logits + router_bias, k + 1, dim=-1)
+        alpha = top.values[:, -1:]
+        indices = top.indices[:, :k]
+    else:
+        indices = torch.topk(logits, k, dim=-1).indices
+    chosen = logits.gather(-1, indices)
+    if gate_fn == "softmax":
+        weights = chosen.softmax(dim=-1)
+    else:
+        weights = torch.sigmoid(chosen)
+        if normalize_sigmoid:
+            weights = weights / weights.sum(dim=-1, keepdim=True).clamp_min(1e-9)
+    return indices, weights, alpha
+
+
+def load_balance_aux_loss(logits: Tensor, indices: Tensor, num_experts: int) -> Tensor:
+    """Switch-style auxiliary loss ``E * sum_e f_e * p_e`` (f = routed fraction, p = mean softmax
+    probability). An extension over the reference's ``ohara`` package, which balances only through
+    the router bias; the same loss appears in experiments/deepseek_moe/dsmoe.py:211-225."""
+    probs = logits.softmax(dim=-1).mean(dim=0)
+    counts = torch.bincount(indices.reshape(-1), minlength=num_experts).to(probs.dtype)
+    fraction = counts / max(indices.numel(), 1)
+    return num_experts * torch.sum(fraction * probs)
+
+
+class QuantileBalancedRouter(nn.Module):
+    """Mixin holding the router bias and the balancing statistics buffers."""
+
+    num_experts: int
+    num_experts_per_tok: int
+    quantile_balancing: bool
+
+    def _register_balancing_buffers(self) -> None:
+        e = self.num_experts
+        self.register_buffer("router_bias", torch.zeros(e))
+        self.register_buffer("qb_beta_sum", torch.zeros(e), persistent=False)
+        self.register_buffer("qb_beta_count", torch.zeros(()), persistent=False)
+        self.register_buffer("expert_counts", torch.zeros(e, dtype=torch.long), persistent=False)
+
+    @torch.no_grad()
+    def _accumulate_qb(self, logits: Tensor, alpha: Tensor) -> None:
+        margin = logits - alpha  # expert e wins a token when its margin is positive
+        tokens = margin.size(0)
+        fair_share = max(1, tokens * self.num_experts_per_tok // self.num_experts)
+        fair_share = min(fair_share, tokens)
+        beta = torch.topk(margin.t(), fair_share, dim=-1).values[:, -1]
+        self.qb_beta_sum += beta
+        self.qb_beta_count += 1
+
+    @torch.no_grad()
+    def _record_load(self, indices: Tensor) -> None:
+        self.expert_counts += torch.bincount(indices.reshape(-1), minlength=self.num_experts)
+
+    @torch.no_grad()
+    def apply_qb_update(self, group=None) -> None:
+        """Fold the statistics of this optimizer step into ``router_bias`` (mean-zero)."""
+        if float(self.qb_beta_count) == 0:
+            return
+        beta = self.qb_beta_sum / self.qb_beta_count
+        if dist.is_available() and dist.is_initialized():
+            dist.all_reduce(beta, op=dist.ReduceOp.SUM, group=group)
+            beta /= dist.get_world_size(group=group)
+        bias = -beta
+        self.router_bias.copy_(bias - bias.mean())
+        self.qb_beta_sum.zero_()
+        self.qb_beta_count.zero_()
+
+    @torch.no_grad()
+    def expert_load(self, reset: bool = True) -> Tensor:
+        counts = self.expert_counts.clone()
+        if reset:
+            self.expert_counts.zero_()
+        return counts
+
+
+def apply_qb_update(model: nn.Module) -> None:
+    """Run ``apply_qb_update`` on every balancing MoE layer of ``model``."""
+    for module in model.modules():
+        if isinstance(module, QuantileBalancedRouter) and module.quantile_balancing:
+            module.apply_qb_update()
+
+
+def expert_load(model: nn.Module, reset: bool = True) -> list[Tensor]:
+    """Tokens routed to each expert since the last reset, one tensor per MoE layer."""
+    return [
+        module.expert_load(reset=reset)
+        for module in model.modules()
+        if isinstance(module, QuantileBalancedRouter)
+    ]
+
+
+def maximal_violation(counts: Tensor) -> float:
+    """MaxVio = max_e load_e / mean load − 1; zero means perfectly balanced."""
+    counts = counts.float()
+    mean = counts.mean()
+    if mean <= 0:
+        return 0.0
+    return float((counts.max() - mean) / mean)
