@@ -46,6 +46,14 @@ void flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float*
                     int64_t k_tok_stride, int64_t v_tok_stride, int64_t q_batch_stride,
                     int64_t k_batch_stride, int64_t v_batch_stride, cudaStream_t stream);
 
+// attention_bwd_sm100.cu
+void attn_delta(const void* o, const void* d_o, float* delta, int B, int T, int H, int D,
+                int64_t do_tok_stride, int64_t do_batch_stride, cudaStream_t stream);
+void flash_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, float* dq,
+                    void* dk, void* dv, const float* lse, const float* delta, int B, int T, int S,
+                    int H, int Hk, int D, bool causal, float scale, const int64_t* strides,
+                    cudaStream_t stream);
+
 // cross_entropy.cu
 void cross_entropy_rows(void* logits, const int64_t* targets, float* row_loss, float* row_lse,
                         int* row_correct, const float* scale_ptr, int64_t rows, int vocab,

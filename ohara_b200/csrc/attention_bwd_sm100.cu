@@ -1,0 +1,543 @@
+// Flash-attention backward for sm_100a (causal or full, grouped-query heads).
+//
+// One CTA owns one 128-key tile of one (batch, kv-head) and walks over every 64-query tile (of
+// every query head in the group) that can see it. All five products run on tcgen05.mma with
+// M = 128; the score-shaped ones are computed *transposed* so that a thread (= TMEM lane) owns a
+// key row and the per-query statistics (log-sum-exp and delta = rowsum(dO*O)) are plain broadcast
+// reads:
+//     S^T  = K  Q^T          (128 keys x 64 queries)      dP^T = V dO^T
+//     P^T  = exp2(S^T*c - lse),  dS^T = P^T o (dP^T - delta) * scale      (4 warps, registers)
+//     dV  += P^T dO          dK += dS^T Q                 (accumulate in TMEM over all q tiles)
+//     dQ^T = K^T dS^T        (head_dim x 64) -> transposed through smem -> TMA reduce-add (fp32)
+// dK and dV are written once at the end (no atomics, GQA groups are summed inside the CTA); dQ is
+// accumulated across key tiles in an fp32 buffer with the TMA reduce-add engine.
+//
+// Warp roles (192 threads): 0-3 softmax / drain / epilogue, 4 TMA producer, 5 MMA issuer.
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace ob {
+
+namespace {
+
+constexpr int kKeys = 128;
+constexpr int kQRows = 64;
+constexpr int kThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct BwdParams {
+  int B, T, S, H, Hk;
+  int causal;
+  float scale;       // softmax scale
+  float scale_log2;  // scale * log2(e)
+  const float* lse;    // (B, H, T) natural log
+  const float* delta;  // (B, H, T)
+  int* status;
+};
+
+template <int D>
+struct BwdSmem {
+  static constexpr int kKVBytes = kKeys * D * 2;   // K or V tile
+  static constexpr int kQBytes = kQRows * D * 2;   // Q or dO tile
+  static constexpr int kPBytes = kKeys * kQRows * 2;
+  static constexpr int kDQBytes = kQRows * D * 4;
+  static constexpr int kK = 0;
+  static constexpr int kV = kK + kKVBytes;
+  static constexpr int kQ = kV + kKVBytes;          // 2 stages of (Q, dO)
+  static constexpr int kP = kQ + 4 * kQBytes;
+  static constexpr int kdS = kP + kPBytes;
+  static constexpr int kDQ = kdS + kPBytes;
+  static constexpr int kStats = kDQ + kDQBytes;     // 2 x (64 lse + 64 delta) floats
+  static constexpr int kBars = kStats + 2 * 128 * 4;
+  static constexpr int kNeeded = kBars + 256 + 1024;
+  static constexpr int kTotal = kNeeded > 120 * 1024 ? kNeeded : 120 * 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                 const __grid_constant__ CUtensorMap tmdQ, const __grid_constant__ CUtensorMap tmdK,
+                 const __grid_constant__ CUtensorMap tmdV, const BwdParams p) {
+  using L = BwdSmem<D>;
+  constexpr int kDSub = D / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sK = smem + L::kK;
+  uint8_t* sV = smem + L::kV;
+  uint8_t* sQdO = smem + L::kQ;  // stage s: Q at s*2*kQBytes, dO right after it
+  uint8_t* sP = smem + L::kP;
+  uint8_t* sdS = smem + L::kdS;
+  float* sDQ = reinterpret_cast<float*>(smem + L::kDQ);
+  float* sStats = reinterpret_cast<float*>(smem + L::kStats);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
+  uint64_t* kv_full = bars;        // 1
+  uint64_t* qdo_full = bars + 1;   // 2
+  uint64_t* qdo_empty = bars + 3;  // 2
+  uint64_t* s_full = bars + 5;     // 1
+  uint64_t* sd_empty = bars + 6;   // 1 (count 4)
+  uint64_t* ps_full = bars + 7;    // 1 (count 4)
+  uint64_t* mma_done = bars + 8;   // 1
+  uint64_t* grp_bar = bars + 9;    // 1 (count 128): bounded barrier among the softmax warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const WaitCtx wctx{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // Block -> (key tile, batch, kv head); low key tiles (most work under a causal mask) first.
+  int bid = blockIdx.x;
+  const int hk = bid % p.Hk;
+  bid /= p.Hk;
+  const int b = bid % p.B;
+  const int kt = bid / p.B;
+  const int kv0 = kt * kKeys;
+  const int group = p.H / p.Hk;
+  const int offset = p.S - p.T;
+  const int q_tiles = (p.T + kQRows - 1) / kQRows;
+  int qt_begin = 0;
+  if (p.causal) qt_begin = max(0, kv0 - offset) / kQRows;
+  const int tiles_per_head = max(q_tiles - qt_begin, 0);
+  const int n_iters = tiles_per_head * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qdo_full[i], 1);
+      mbar_init(&qdo_empty[i], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(sd_empty, 4);
+    mbar_init(ps_full, 4);
+    mbar_init(mma_done, 1);
+    mbar_init(grp_bar, 128);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 4 && lane == 0) {
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmdO);
+    prefetch_tmap(&tmdQ);
+    prefetch_tmap(&tmdK);
+    prefetch_tmap(&tmdV);
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_S = tmem_base;          // 64 columns
+  const uint32_t tm_dP = tmem_base + 64;    // 64 columns
+  const uint32_t tm_dV = tmem_base + 128;   // D columns
+  const uint32_t tm_dK = tmem_base + 256;   // D columns
+  const uint32_t tm_dQ = tmem_base + 384;   // 64 columns (transposed: lane = head_dim index)
+
+  auto iter_coords = [&](int it, int& h, int& tq0) {
+    const int g = it / tiles_per_head;
+    const int qt = qt_begin + (it - g * tiles_per_head);
+    h = hk * group + g;
+    tq0 = qt * kQRows;
+  };
+
+  if (warp == 4) {
+    // ------------------------------ TMA producer ---------------------------------------------
+    if (lane == 0 && n_iters > 0) {
+      mbar_expect_tx(kv_full, 2 * L::kKVBytes);
+#pragma unroll
+      for (int s = 0; s < kDSub; ++s) {
+        tma_load_4d(sK + s * 16384, &tmK, kv_full, s * 64, hk, kv0, b);
+        tma_load_4d(sV + s * 16384, &tmV, kv_full, s * 64, hk, kv0, b);
+      }
+      for (int it = 0; it < n_iters; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&qdo_empty[st], ph ^ 1, wctx, kTimeoutEmptyBarrier)) break;
+        int h, tq0;
+        iter_coords(it, h, tq0);
+        uint8_t* q_dst = sQdO + st * 2 * L::kQBytes;
+        uint8_t* do_dst = q_dst + L::kQBytes;
+        mbar_expect_tx(&qdo_full[st], 2 * L::kQBytes);
+#pragma unroll
+        for (int s = 0; s < kDSub; ++s) {
+          tma_load_4d(q_dst + s * 8192, &tmQ, &qdo_full[st], s * 64, h, tq0, b);
+          tma_load_4d(do_dst + s * 8192, &tmdO, &qdo_full[st], s * 64, h, tq0, b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------ MMA issuer -----------------------------------------------
+    if (lane == 0 && n_iters > 0) {
+      const uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);  // S^T, dP^T
+      const uint32_t idesc_dv = make_idesc_bf16(128, D, false, true);    // dV, dK
+      const uint32_t idesc_dq = make_idesc_bf16(128, 64, true, true);    // dQ^T
+      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      const uint32_t pa = smem_u32(sP), dsa = smem_u32(sdS);
+      auto issue_scores = [&](int it) -> bool {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&qdo_full[st], ph, wctx, kTimeoutFullBarrier)) return false;
+        tcgen05_fence_after();
+        const uint32_t qa = smem_u32(sQdO + st * 2 * L::kQBytes);
+        const uint32_t doa = qa + L::kQBytes;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t offA = (k / 4) * 16384 + (k % 4) * 32;
+          const uint32_t offB = (k / 4) * 8192 + (k % 4) * 32;
+          umma_bf16_ss(tm_S, make_smem_desc_sw128(ka + offA, 16, 1024),
+                       make_smem_desc_sw128(qa + offB, 16, 1024), idesc_st, k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t offA = (k / 4) * 16384 + (k % 4) * 32;
+          const uint32_t offB = (k / 4) * 8192 + (k % 4) * 32;
+          umma_bf16_ss(tm_dP, make_smem_desc_sw128(va + offA, 16, 1024),
+                       make_smem_desc_sw128(doa + offB, 16, 1024), idesc_st, k > 0 ? 1u : 0u);
+        }
+        tcgen05_commit(s_full);
+        return true;
+      };
+      bool ok = mbar_wait(kv_full, 0, wctx, kTimeoutFullBarrier);
+      if (ok) ok = issue_scores(0);
+      for (int it = 0; it < n_iters && ok; ++it) {
+        const int st = it & 1;
+        if (it + 1 < n_iters) {
+          if (!mbar_wait(sd_empty, it & 1, wctx, kTimeoutSoftmax)) break;
+          if (!issue_scores(it + 1)) break;
+        }
+        if (!mbar_wait(ps_full, it & 1, wctx, kTimeoutSoftmax)) break;
+        tcgen05_fence_after();
+        const uint32_t qa = smem_u32(sQdO + st * 2 * L::kQBytes);
+        const uint32_t doa = qa + L::kQBytes;
+        // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 queries)
+#pragma unroll
+        for (int k = 0; k < kQRows / 16; ++k) {
+          umma_bf16_ss(tm_dV, make_smem_desc_sw128(pa + k * 32, 16, 1024),
+                       make_smem_desc_sw128(doa + k * 2048, 8192, 1024), idesc_dv,
+                       (it > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < kQRows / 16; ++k) {
+          umma_bf16_ss(tm_dK, make_smem_desc_sw128(dsa + k * 32, 16, 1024),
+                       make_smem_desc_sw128(qa + k * 2048, 8192, 1024), idesc_dv,
+                       (it > 0 || k > 0) ? 1u : 0u);
+        }
+        // dQ^T = K^T dS^T (contraction over the 128 keys). For D = 64 the second 64 rows of the
+        // M = 128 operand alias the first (leading offset 0) and are never read back.
+#pragma unroll
+        for (int k = 0; k < kKeys / 16; ++k) {
+          umma_bf16_ss(tm_dQ, make_smem_desc_sw128(ka + k * 2048, D == 128 ? 16384 : 0, 1024),
+                       make_smem_desc_sw128(dsa + k * 2048, 16, 1024), idesc_dq, k > 0 ? 1u : 0u);
+        }
+        tcgen05_commit(mma_done);
+        tcgen05_commit(&qdo_empty[st]);
+      }
+    }
+  } else {
+    // ------------------------------ Softmax / drain / epilogue -------------------------------
+    const int row = warp * 32 + lane;  // key row within the tile == TMEM lane
+    const int key = kv0 + row;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    bool ok = true;
+    uint32_t grp_phase = 0;
+    // Barrier among the 128 softmax threads, built on an mbarrier so that it cannot outlive the
+    // wait limit if some warp has already abandoned the tile.
+    auto group_sync = [&]() -> bool {
+      mbar_arrive(grp_bar);
+      const bool done = mbar_wait(grp_bar, grp_phase & 1, wctx, kTimeoutSoftmax);
+      ++grp_phase;
+      return done;
+    };
+
+    // Moves dQ^T of iteration `it` from TMEM to the fp32 gradient with a TMA reduce-add.
+    auto drain_dq = [&](int it) -> bool {
+      int h, tq0;
+      iter_coords(it, h, tq0);
+      if (threadIdx.x == 0) tma_store_wait_read<0>();
+      if (!group_sync()) return false;
+      if (row < D) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tm_dQ + lane_addr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sDQ[(c * 32 + i) * D + row] = __uint_as_float(v[i]);
+        }
+      }
+      tcgen05_fence_before();
+      fence_proxy_async_smem();
+      if (!group_sync()) return false;
+      if (threadIdx.x == 0) {
+        tma_reduce_add_4d(&tmdQ, sDQ, 0, h, tq0, b);
+        tma_store_commit();
+      }
+      return true;
+    };
+
+    for (int it = 0; it < n_iters; ++it) {
+      int h, tq0;
+      iter_coords(it, h, tq0);
+      // Per-query statistics for this tile -> shared memory (double buffered by iteration parity).
+      float* stats = sStats + (it & 1) * 128;
+      {
+        const int idx = threadIdx.x;  // 0..127
+        const int tq = tq0 + (idx & 63);
+        const size_t base = ((size_t)b * p.H + h) * p.T;
+        float val;
+        if (idx < 64)
+          val = (tq < p.T) ? p.lse[base + tq] * kLog2e : INFINITY;
+        else
+          val = (tq < p.T) ? p.delta[base + tq] : 0.f;
+        stats[idx] = val;
+      }
+      if (!group_sync()) {
+        ok = false;
+        break;
+      }
+      if (!mbar_wait(s_full, it & 1, wctx, kTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after();
+      float s[64], dp[64];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tm_S + lane_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]);
+        tmem_ld_32x32(tm_dP + lane_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dp[c * 32 + i] = __uint_as_float(v[i]);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sd_empty);
+
+      const bool need_mask = (p.causal && (kv0 + kKeys - 1 > tq0 + offset)) ||
+                             (kv0 + kKeys > p.S) || (tq0 + kQRows > p.T);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        float pv = exp2f(s[i] * p.scale_log2 - stats[i]);
+        if (need_mask) {
+          const int tq = tq0 + i;
+          const bool visible = (key < p.S) && (tq < p.T) && (!p.causal || key <= tq + offset);
+          pv = visible ? pv : 0.f;
+        }
+        s[i] = pv;
+        dp[i] = pv * (dp[i] - stats[64 + i]) * p.scale;
+      }
+
+      // The previous iteration's MMAs must be finished with sP / sdS; its dQ^T is then ready.
+      if (it > 0) {
+        if (!mbar_wait(mma_done, (it - 1) & 1, wctx, kTimeoutTmemFull)) {
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        if (!drain_dq(it - 1)) {
+          ok = false;
+          break;
+        }
+      }
+      uint8_t* prow = sP + row * 128;
+      uint8_t* dsrow = sdS + row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint4 o, d;
+        o.x = pack_bf16(s[8 * c + 0], s[8 * c + 1]);
+        o.y = pack_bf16(s[8 * c + 2], s[8 * c + 3]);
+        o.z = pack_bf16(s[8 * c + 4], s[8 * c + 5]);
+        o.w = pack_bf16(s[8 * c + 6], s[8 * c + 7]);
+        d.x = pack_bf16(dp[8 * c + 0], dp[8 * c + 1]);
+        d.y = pack_bf16(dp[8 * c + 2], dp[8 * c + 3]);
+        d.z = pack_bf16(dp[8 * c + 4], dp[8 * c + 5]);
+        d.w = pack_bf16(dp[8 * c + 6], dp[8 * c + 7]);
+        const int sw = ((c ^ (row & 7)) << 4);
+        *reinterpret_cast<uint4*>(prow + sw) = o;
+        *reinterpret_cast<uint4*>(dsrow + sw) = d;
+      }
+      fence_proxy_async_smem();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ps_full);
+    }
+
+    if (ok && n_iters > 0) {
+      ok = mbar_wait(mma_done, (n_iters - 1) & 1, wctx, kTimeoutTmemFull);
+      if (ok) {
+        tcgen05_fence_after();
+        ok = drain_dq(n_iters - 1);
+      }
+    }
+    // ---- epilogue: dK, dV (TMEM fp32) -> bf16 -> swizzled smem (over K / V tiles) -> TMA store --
+    if (ok) {
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t tm_src = which == 0 ? tm_dK : tm_dV;
+        uint8_t* dst = (which == 0 ? sK : sV) + row * 128;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          if (n_iters > 0) {
+            tmem_ld_32x32(tm_src + lane_addr + c * 32, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0;
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(v[8 * q4 + 0]), __uint_as_float(v[8 * q4 + 1]));
+            o.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
+            o.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
+            o.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
+            const int chunk = c * 4 + q4;
+            *reinterpret_cast<uint4*>(dst + (chunk >> 3) * 16384 + (((chunk & 7) ^ (row & 7)) << 4)) = o;
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && kv0 + warp * 32 < p.S) {
+#pragma unroll
+        for (int s2 = 0; s2 < kDSub; ++s2) {
+          tma_store_4d(&tmdK, sK + s2 * 16384 + warp * 32 * 128, s2 * 64, hk, kv0 + warp * 32, b);
+          tma_store_4d(&tmdV, sV + s2 * 16384 + warp * 32 * 128, s2 * 64, hk, kv0 + warp * 32, b);
+        }
+        tma_store_commit();
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+
+  if (*abort_flag) {
+    const uint64_t w0 = global_timer_ns();
+    while (global_timer_ns() - w0 < 1000000ull) __nanosleep(1000);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b, h, t] = sum_d O[b, t, h, d] * dO[b, t, h, d]; one warp per (b, t, h) row.
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
+                                  const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                                  int B, int T, int H, int D, int64_t do_tok_stride,
+                                  int64_t do_batch_stride) {
+  const int warps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = (int64_t)B * T * H;
+  for (int64_t r = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); r < rows;
+       r += (int64_t)gridDim.x * warps) {
+    const int h = (int)(r % H);
+    const int64_t bt = r / H;
+    const int t = (int)(bt % T);
+    const int b = (int)(bt / T);
+    const __nv_bfloat16* orow = o + r * D;
+    const __nv_bfloat16* drow = d_o + (int64_t)b * do_batch_stride + (int64_t)t * do_tok_stride + (int64_t)h * D;
+    float acc = 0.f;
+    for (int i = lane * 2; i < D; i += 64) {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(orow + i));
+      const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(drow + i));
+      acc += a.x * g.x + a.y * g.y;
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) delta[((size_t)b * H + h) * T + t] = acc;
+  }
+}
+
+template <int D>
+void launch_bwd(const void* q, const void* k, const void* v, const void* d_o, float* dq, void* dk,
+                void* dv, const float* lse, const float* delta, int B, int T, int S, int H, int Hk,
+                bool causal, float scale, const int64_t* strides, cudaStream_t stream) {
+  using L = BwdSmem<D>;
+  CUtensorMap tQ, tK, tV, tdO, tdQ, tdK, tdV;
+  auto make4 = [&](CUtensorMap* tm, const void* base, TmapDtype dt, int heads, int len,
+                   int64_t tok_stride, int64_t batch_stride, uint32_t box_inner, uint32_t box_rows,
+                   TmapSwizzle sw) {
+    const uint64_t esz = dt == TmapDtype::F32 ? 4 : 2;
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)heads, (uint64_t)len, (uint64_t)B};
+    uint64_t st[3] = {(uint64_t)D * esz, (uint64_t)tok_stride * esz, (uint64_t)batch_stride * esz};
+    uint32_t box[4] = {box_inner, 1, box_rows, 1};
+    make_tmap(tm, base, dt, 4, dims, st, box, sw);
+  };
+  make4(&tQ, q, TmapDtype::BF16, H, T, strides[0], strides[1], 64, kQRows, TmapSwizzle::B128);
+  make4(&tK, k, TmapDtype::BF16, Hk, S, strides[2], strides[3], 64, kKeys, TmapSwizzle::B128);
+  make4(&tV, v, TmapDtype::BF16, Hk, S, strides[4], strides[5], 64, kKeys, TmapSwizzle::B128);
+  make4(&tdO, d_o, TmapDtype::BF16, H, T, strides[6], strides[7], 64, kQRows, TmapSwizzle::B128);
+  make4(&tdQ, dq, TmapDtype::F32, H, T, (int64_t)H * D, (int64_t)T * H * D, D, kQRows,
+        TmapSwizzle::NONE);
+  make4(&tdK, dk, TmapDtype::BF16, Hk, S, (int64_t)Hk * D, (int64_t)S * Hk * D, 64, 32,
+        TmapSwizzle::B128);
+  make4(&tdV, dv, TmapDtype::BF16, Hk, S, (int64_t)Hk * D, (int64_t)S * Hk * D, 64, 32,
+        TmapSwizzle::B128);
+  BwdParams p;
+  p.B = B;
+  p.T = T;
+  p.S = S;
+  p.H = H;
+  p.Hk = Hk;
+  p.causal = causal ? 1 : 0;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  p.lse = lse;
+  p.delta = delta;
+  p.status = status_ptr();
+  auto kernel = flash_bwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    OB_CUDA_CHECK(
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    configured = true;
+  }
+  const int k_tiles = (S + kKeys - 1) / kKeys;
+  const long long grid = (long long)k_tiles * B * Hk;
+  kernel<<<(unsigned)grid, kThreads, L::kTotal, stream>>>(tQ, tK, tV, tdO, tdQ, tdK, tdV, p);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace
+
+void attn_delta(const void* o, const void* d_o, float* delta, int B, int T, int H, int D,
+                int64_t do_tok_stride, int64_t do_batch_stride, cudaStream_t stream) {
+  const int threads = 256;
+  const int64_t rows = (int64_t)B * T * H;
+  const int blocks = (int)std::min<int64_t>((rows + 7) / 8, (int64_t)device_sm_count() * 16);
+  attn_delta_kernel<<<std::max(blocks, 1), threads, 0, stream>>>(
+      (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, T, H, D, do_tok_stride,
+      do_batch_stride);
+  OB_CUDA_CHECK(cudaGetLastError());
+}
+
+// strides = {q_tok, q_batch, k_tok, k_batch, v_tok, v_batch, do_tok, do_batch} in elements.
+// dq: zero-initialised fp32 (B, T, H, D); dk, dv: bf16 (B, S, Hk, D) contiguous.
+void flash_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, float* dq,
+                    void* dk, void* dv, const float* lse, const float* delta, int B, int T, int S,
+                    int H, int Hk, int D, bool causal, float scale, const int64_t* strides,
+                    cudaStream_t stream) {
+  OB_CHECK(D == 64 || D == 128, "flash attention supports head_dim 64 or 128");
+  OB_CHECK(H % Hk == 0, "query heads must be a multiple of KV heads");
+  if (D == 128)
+    launch_bwd<128>(q, k, v, d_o, dq, dk, dv, lse, delta, B, T, S, H, Hk, causal, scale, strides,
+                    stream);
+  else
+    launch_bwd<64>(q, k, v, d_o, dq, dk, dv, lse, delta, B, T, S, H, Hk, causal, scale, strides,
+                   stream);
+}
+
+}  // namespace ob

@@ -321,6 +321,35 @@ std::vector<Tensor> flash_attn_fwd(const Tensor& q_in, const Tensor& k_in, const
   return {o, lse};
 }
 
+std::vector<Tensor> flash_attn_bwd(const Tensor& dout_in, const Tensor& q_in, const Tensor& k_in,
+                                   const Tensor& v_in, const Tensor& out, const Tensor& lse,
+                                   bool causal, double scale) {
+  check_bf16(dout_in, "dout");
+  check_bf16(out, "out");
+  check_f32(lse, "lse");
+  Tensor q = attn_layout_ok(q_in) ? q_in : q_in.contiguous();
+  Tensor k = attn_layout_ok(k_in) ? k_in : k_in.contiguous();
+  Tensor v = attn_layout_ok(v_in) ? v_in : v_in.contiguous();
+  Tensor d_o = attn_layout_ok(dout_in) ? dout_in : dout_in.contiguous();
+  TORCH_CHECK(out.is_contiguous() && lse.is_contiguous());
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int64_t B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3);
+  const int64_t S = k.size(1), Hk = k.size(2);
+  Tensor delta = torch::empty({B, H, T}, lse.options());
+  ob::attn_delta(out.data_ptr(), d_o.data_ptr(), delta.data_ptr<float>(), (int)B, (int)T, (int)H,
+                 (int)D, d_o.stride(1), d_o.stride(0), current_stream());
+  Tensor dq32 = torch::zeros({B, T, H, D}, q.options().dtype(torch::kFloat32));
+  Tensor dk = torch::empty({B, S, Hk, D}, k.options());
+  Tensor dv = torch::empty({B, S, Hk, D}, k.options());
+  const int64_t strides[8] = {q.stride(1), q.stride(0), k.stride(1), k.stride(0),
+                              v.stride(1), v.stride(0), d_o.stride(1), d_o.stride(0)};
+  ob::flash_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr(),
+                     dq32.data_ptr<float>(), dk.data_ptr(), dv.data_ptr(), lse.data_ptr<float>(),
+                     delta.data_ptr<float>(), (int)B, (int)T, (int)S, (int)H, (int)Hk, (int)D,
+                     causal, (float)scale, strides, current_stream());
+  return {dq32.to(torch::kBFloat16), dk, dv};
+}
+
 std::vector<int64_t> status(bool clear) {
   int out[4];
   ob::status_read(out, clear);
@@ -344,5 +373,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cross_entropy_rows", &cross_entropy_rows);
   m.def("scale_by_scalar", &scale_by_scalar);
   m.def("flash_attn_fwd", &flash_attn_fwd);
+  m.def("flash_attn_bwd", &flash_attn_bwd);
   m.def("status", &status);
 }
