@@ -15,7 +15,7 @@ void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int b
                int64_t strideC, bool a_batched, bool b_batched, int b_batches, bool out_f32,
                int splits, bool reduce, float alpha, const int* m_tile_batch,
                const int* k_offsets, int64_t a_rows, int64_t b_rows, int num_sms,
-               cudaStream_t stream);
+               const void* R, int64_t ldr, int64_t strideR, float beta, cudaStream_t stream);
 
 // elementwise.cu
 void rmsnorm_fwd(const void* x, const void* delta, const float* w, void* y, void* x_out, float* rstd,

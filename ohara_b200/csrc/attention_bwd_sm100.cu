@@ -508,7 +508,7 @@ void launch_bwd(const void* q, const void* k, const void* v, const void* d_o, fl
   const int k_tiles = (S + kKeys - 1) / kKeys;
   const long long grid = (long long)k_tiles * B * Hk;
   kernel<<<(unsigned)grid, kThreads, L::kTotal, stream>>>(tQ, tK, tV, tdO, tdQ, tdK, tdV, p);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 }  // namespace
@@ -521,7 +521,7 @@ void attn_delta(const void* o, const void* d_o, float* delta, int B, int T, int 
   attn_delta_kernel<<<std::max(blocks, 1), threads, 0, stream>>>(
       (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, T, H, D, do_tok_stride,
       do_batch_stride);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 // strides = {q_tok, q_batch, k_tok, k_batch, v_tok, v_batch, do_tok, do_batch} in elements.

@@ -385,7 +385,7 @@ void launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   const int q_tiles = (T + kBlockQ - 1) / kBlockQ;
   const long long grid = (long long)q_tiles * B * H;
   kernel<<<(unsigned)grid, kThreads, L::kTotal, stream>>>(tQ, tK, tV, tO, p);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 }  // namespace

@@ -31,7 +31,8 @@ void check_rowmajor(const Tensor& t, const char* name) {
 // *stored* matrices: (rows, inner) or (batch, rows, inner) with unit inner stride.
 void gemm(const Tensor& a, const Tensor& b, Tensor& c, int64_t M, int64_t N, int64_t K, bool a_mn,
           bool b_mn, int64_t splits, bool reduce, double alpha,
-          const c10::optional<Tensor>& m_tile_batch, const c10::optional<Tensor>& k_offsets) {
+          const c10::optional<Tensor>& m_tile_batch, const c10::optional<Tensor>& k_offsets,
+          const c10::optional<Tensor>& residual, double beta) {
   check_bf16(a, "a");
   check_bf16(b, "b");
   check_cuda(c, "c");
@@ -76,11 +77,23 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& c, int64_t M, int64_t N, int
     TORCH_CHECK(k_offsets->numel() >= batches + 1, "k_offsets is too short");
     koff = k_offsets->data_ptr<int>();
   }
+  const void* res_ptr = nullptr;
+  int64_t ldr = 0, stride_r = 0;
+  if (residual.has_value()) {
+    check_bf16(*residual, "residual");
+    check_rowmajor(*residual, "residual");
+    TORCH_CHECK(residual->dim() == c.dim() && residual->size(-2) == M && residual->size(-1) == N,
+                "residual must have the shape of c");
+    TORCH_CHECK(!c_batched || residual->size(0) == batches, "residual batch count mismatch");
+    res_ptr = residual->data_ptr();
+    ldr = residual->stride(-2);
+    stride_r = c_batched ? residual->stride(0) : 0;
+  }
   ob::gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K, (int)batches,
                 a_mn, b_mn, a.stride(-2), b.stride(-2), c.stride(-2), a_batched ? a.stride(0) : 0,
                 b_batched ? b.stride(0) : 0, c_batched ? c.stride(0) : 0, a_batched, b_batched,
                 (int)b_batches, out_f32, (int)splits, reduce, (float)alpha, mtb, koff, a_rows,
-                b_rows, ob::device_sm_count(), current_stream());
+                b_rows, ob::device_sm_count(), res_ptr, ldr, stride_r, (float)beta, current_stream());
 }
 
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& delta, const Tensor& w,
@@ -360,7 +373,11 @@ std::vector<int64_t> status(bool clear) {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "ohara_b200 sm_100a kernels";
-  m.def("gemm", &gemm);
+  m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("M"), py::arg("N"),
+        py::arg("K"), py::arg("a_mn"), py::arg("b_mn"), py::arg("splits") = 1,
+        py::arg("reduce") = false, py::arg("alpha") = 1.0, py::arg("m_tile_batch") = py::none(),
+        py::arg("k_offsets") = py::none(), py::arg("residual") = py::none(),
+        py::arg("beta") = 1.0);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("rope", &rope);
@@ -375,4 +392,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("flash_attn_fwd", &flash_attn_fwd);
   m.def("flash_attn_bwd", &flash_attn_bwd);
   m.def("status", &status);
+  m.def("launch_count", []() { return (int64_t)ob::launch_count(); });
 }

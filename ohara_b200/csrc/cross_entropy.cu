@@ -160,7 +160,7 @@ void cross_entropy_rows(void* logits, const int64_t* targets, float* row_loss, f
   ce_rows_kernel<<<(unsigned)rows, 512, smem, stream>>>((__nv_bfloat16*)logits, targets, row_loss,
                                                         row_lse, row_correct, scale_ptr, vocab,
                                                         pitch, ignore_index, write_grad ? 1 : 0);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 void scale_by_scalar(void* x, bool is_bf16, const float* scalar, int64_t n, cudaStream_t stream) {
@@ -171,7 +171,7 @@ void scale_by_scalar(void* x, bool is_bf16, const float* scalar, int64_t n, cuda
     scale_by_device_scalar_bf16<<<blocks, threads, 0, stream>>>((__nv_bfloat16*)x, scalar, n);
   else
     scale_by_device_scalar_f32<<<blocks, threads, 0, stream>>>((float*)x, scalar, n);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 }  // namespace ob

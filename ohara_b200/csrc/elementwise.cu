@@ -335,7 +335,7 @@ void rmsnorm_fwd(const void* x, const void* delta, const float* w, void* y, void
   else
     rmsnorm_fwd_kernel<false><<<blocks, threads, 0, stream>>>(
         (const __nv_bfloat16*)x, nullptr, w, (__nv_bfloat16*)y, nullptr, rstd, rows, d, eps);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 void rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* dres,
@@ -352,7 +352,7 @@ void rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rst
     rmsnorm_bwd_kernel<false><<<blocks, threads, d * sizeof(float), stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, nullptr, (__nv_bfloat16*)dx, dw,
         rows, d);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 void rope_qk(const void* q, const void* k, void* qo, void* ko, const float* cos_t,
@@ -366,7 +366,7 @@ void rope_qk(const void* q, const void* k, void* qo, void* ko, const float* cos_
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (__nv_bfloat16*)qo, (__nv_bfloat16*)ko,
       cos_t, sin_t, B, T, H, Hk, D, inverse ? -1.f : 1.f, q_row_stride, k_row_stride,
       qo_row_stride, ko_row_stride);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 void swiglu_fwd(const void* g, const void* u, void* a, int64_t rows, int h, int64_t g_pitch,
@@ -376,7 +376,7 @@ void swiglu_fwd(const void* g, const void* u, void* a, int64_t rows, int h, int6
   swiglu_fwd_kernel<<<grid_for(rows * (h / 8), threads), threads, 0, stream>>>(
       (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (__nv_bfloat16*)a, rows, h, g_pitch,
       u_pitch, a_pitch);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 void swiglu_bwd(const void* da, const void* g, const void* u, void* dg, void* du, int64_t rows,
@@ -388,7 +388,7 @@ void swiglu_bwd(const void* da, const void* g, const void* u, void* dg, void* du
       (const __nv_bfloat16*)da, (const __nv_bfloat16*)g, (const __nv_bfloat16*)u,
       (__nv_bfloat16*)dg, (__nv_bfloat16*)du, rows, h, da_pitch, g_pitch, u_pitch, dg_pitch,
       du_pitch);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 void cast_f32_bf16(const float* in, void* out, int64_t n, cudaStream_t stream) {
@@ -396,7 +396,7 @@ void cast_f32_bf16(const float* in, void* out, int64_t n, cudaStream_t stream) {
   const int threads = 256;
   cast_f32_bf16_kernel<<<grid_for((n + 7) / 8, threads), threads, 0, stream>>>(
       in, (__nv_bfloat16*)out, n);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 void embedding_fwd(const int64_t* ids, const float* table, void* out, int64_t tokens, int d,
@@ -405,7 +405,7 @@ void embedding_fwd(const int64_t* ids, const float* table, void* out, int64_t to
   const int threads = 256;
   embedding_fwd_kernel<<<grid_for(tokens * (d / 8), threads), threads, 0, stream>>>(
       ids, table, (__nv_bfloat16*)out, tokens, d, vocab);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 void embedding_bwd(const int64_t* ids, const void* dout, float* dtable, int64_t tokens, int d,
@@ -414,7 +414,7 @@ void embedding_bwd(const int64_t* ids, const void* dout, float* dtable, int64_t 
   const int threads = 256;
   embedding_bwd_kernel<<<grid_for(tokens * (d / 8), threads), threads, 0, stream>>>(
       ids, (const __nv_bfloat16*)dout, dtable, tokens, d, vocab);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 void adamw_step(float* p, const void* g, bool grad_is_bf16, float* m, float* v, void* shadow,
@@ -431,7 +431,7 @@ void adamw_step(float* p, const void* g, bool grad_is_bf16, float* m, float* v, 
     adamw_kernel<float><<<blocks, threads, 0, stream>>>(p, (const float*)g, m, v,
                                                         (__nv_bfloat16*)shadow, n, lr, beta1, beta2,
                                                         eps, wd, bc1, bc2, grad_scale);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 }  // namespace ob

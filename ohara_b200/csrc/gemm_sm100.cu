@@ -39,6 +39,11 @@ struct GemmParams {
   const int* m_tile_batch;
   const int* k_offsets;
   int* status;
+  // Optional residual: C = alpha * A*B + beta * R, R bf16 with the geometry of C.
+  const __nv_bfloat16* R;
+  long long ldr;
+  long long strideR;
+  float beta;
 };
 
 template <int BN>
@@ -51,6 +56,33 @@ struct SmemLayout {
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
 };
+
+// beta * R[row, col0 .. col0+N) as floats (zeros when there is no residual or out of range).
+template <int N>
+__device__ __forceinline__ void load_residual(const GemmParams& p, int batch, int row, int col0,
+                                              float (&out)[N]) {
+#pragma unroll
+  for (int i = 0; i < N; ++i) out[i] = 0.f;
+  if (p.R == nullptr || row >= p.M) return;
+  const __nv_bfloat16* src = p.R + (long long)batch * p.strideR + (long long)row * p.ldr + col0;
+  if (col0 + N <= p.N && ((p.ldr & 7) == 0)) {
+#pragma unroll
+    for (int j = 0; j < N / 8; ++j) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + 8 * j);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(h2[q]);
+        out[8 * j + 2 * q] = f.x * p.beta;
+        out[8 * j + 2 * q + 1] = f.y * p.beta;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      if (col0 + i < p.N) out[i] = __bfloat162float(src[i]) * p.beta;
+  }
+}
 
 template <int BN, bool OUT_F32>
 __global__ void __launch_bounds__(kNumThreads, 1)
@@ -246,13 +278,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0;
           }
+          float res[32];
+          load_residual<32>(p, batch, row0 + lane, col0, res);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             float4 o;
-            o.x = __uint_as_float(v[4 * j + 0]) * p.alpha;
-            o.y = __uint_as_float(v[4 * j + 1]) * p.alpha;
-            o.z = __uint_as_float(v[4 * j + 2]) * p.alpha;
-            o.w = __uint_as_float(v[4 * j + 3]) * p.alpha;
+            o.x = __uint_as_float(v[4 * j + 0]) * p.alpha + res[4 * j + 0];
+            o.y = __uint_as_float(v[4 * j + 1]) * p.alpha + res[4 * j + 1];
+            o.z = __uint_as_float(v[4 * j + 2]) * p.alpha + res[4 * j + 2];
+            o.w = __uint_as_float(v[4 * j + 3]) * p.alpha + res[4 * j + 3];
             *reinterpret_cast<float4*>(my_row + ((j ^ (lane & 7)) << 4)) = o;
           }
         } else {
@@ -266,17 +300,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] = 0;
             }
+            float res[32];
+            load_residual<32>(p, batch, row0 + lane, col0 + h * 32, res);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 o;
-              o.x = pack_bf16(__uint_as_float(v[8 * j + 0]) * p.alpha,
-                              __uint_as_float(v[8 * j + 1]) * p.alpha);
-              o.y = pack_bf16(__uint_as_float(v[8 * j + 2]) * p.alpha,
-                              __uint_as_float(v[8 * j + 3]) * p.alpha);
-              o.z = pack_bf16(__uint_as_float(v[8 * j + 4]) * p.alpha,
-                              __uint_as_float(v[8 * j + 5]) * p.alpha);
-              o.w = pack_bf16(__uint_as_float(v[8 * j + 6]) * p.alpha,
-                              __uint_as_float(v[8 * j + 7]) * p.alpha);
+              o.x = pack_bf16(__uint_as_float(v[8 * j + 0]) * p.alpha + res[8 * j + 0],
+                              __uint_as_float(v[8 * j + 1]) * p.alpha + res[8 * j + 1]);
+              o.y = pack_bf16(__uint_as_float(v[8 * j + 2]) * p.alpha + res[8 * j + 2],
+                              __uint_as_float(v[8 * j + 3]) * p.alpha + res[8 * j + 3]);
+              o.z = pack_bf16(__uint_as_float(v[8 * j + 4]) * p.alpha + res[8 * j + 4],
+                              __uint_as_float(v[8 * j + 5]) * p.alpha + res[8 * j + 5]);
+              o.w = pack_bf16(__uint_as_float(v[8 * j + 6]) * p.alpha + res[8 * j + 6],
+                              __uint_as_float(v[8 * j + 7]) * p.alpha + res[8 * j + 7]);
               const int chunk = h * 4 + j;
               *reinterpret_cast<uint4*>(my_row + ((chunk ^ (lane & 7)) << 4)) = o;
             }
@@ -328,7 +364,7 @@ void launch_variant(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensor
     configured = true;
   }
   kernel<<<grid, kNumThreads, L::kTotal, stream>>>(tA, tB, tC, p);
-  OB_CUDA_CHECK(cudaGetLastError());
+  OB_LAUNCH_CHECK();
 }
 
 }  // namespace
@@ -340,7 +376,7 @@ void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int b
                int64_t strideC, bool a_batched, bool b_batched, int b_batches, bool out_f32,
                int splits, bool reduce, float alpha, const int* m_tile_batch,
                const int* k_offsets, int64_t a_rows, int64_t b_rows, int num_sms,
-               cudaStream_t stream) {
+               const void* R, int64_t ldr, int64_t strideR, float beta, cudaStream_t stream) {
   OB_CHECK(M > 0 && N > 0 && K >= 0 && batches > 0, "gemm_bf16: bad problem size");
   OB_CHECK(!reduce || out_f32, "gemm_bf16: reduce-add epilogue needs an fp32 output");
   OB_CHECK(splits >= 1 && (splits == 1 || reduce), "gemm_bf16: split-K needs the reduce epilogue");
@@ -361,6 +397,11 @@ void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int b
   p.m_tile_batch = m_tile_batch;
   p.k_offsets = k_offsets;
   p.status = status_ptr();
+  p.R = static_cast<const __nv_bfloat16*>(R);
+  p.ldr = ldr;
+  p.strideR = strideR;
+  p.beta = beta;
+  OB_CHECK(R == nullptr || !reduce, "gemm_bf16: a residual cannot be combined with the reduce epilogue");
 
   // Stored shapes: K-major operand is (rows = M or N, inner = K); MN-major is (rows = K, inner =
   // M or N). `a_rows` / `b_rows` give the number of stored rows (the full token count in the

@@ -1,5 +1,6 @@
 #include "host_utils.h"
 
+#include <atomic>
 #include <mutex>
 
 namespace ob {
@@ -92,6 +93,12 @@ void make_tmap_3d(CUtensorMap* out, const void* base, TmapDtype dtype, uint64_t 
   uint32_t box[3] = {box_inner, box_rows, 1};
   make_tmap(out, base, dtype, 3, dims, strides, box, swizzle);
 }
+
+namespace {
+std::atomic<long long> g_launches{0};
+}
+long long launch_count() { return g_launches.load(); }
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int device_sm_count() {
   static int cached[64] = {0};

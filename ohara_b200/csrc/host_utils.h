@@ -33,6 +33,16 @@ namespace ob {
     }                                                                           \
   } while (0)
 
+// Counts kernel launches issued by this library (read by benchmarks through `launch_count`).
+long long launch_count();
+void count_launch();
+
+#define OB_LAUNCH_CHECK()                    \
+  do {                                       \
+    ::ob::count_launch();                    \
+    OB_CUDA_CHECK(cudaGetLastError());       \
+  } while (0)
+
 enum class TmapDtype { BF16, F32, U8 };
 enum class TmapSwizzle { NONE, B128 };
 

@@ -236,8 +236,15 @@ class Llama(nn.Module):
             h = layer(h, None, freqs, cache, start if cache is not None else None)
         return self.norm(h)
 
+    supports_fused_loss = True
+
     def forward(self, x: Tensor, kv_cache: list[KVCache] | None = None,
-                position_ids: int | Tensor | None = None) -> Tensor:
+                position_ids: int | Tensor | None = None, *, targets: Tensor | None = None,
+                ignore_index: int = -1, loss_scale: Tensor | float | None = None) -> Tensor:
+        """Logits ``(B, T, V)``; with ``targets`` the (scaled) summed cross-entropy instead, so a
+        wrapper that only forwards ``__call__`` (DDP) can still use the fused loss."""
+        if targets is not None:
+            return self.loss_sum(x, targets, ignore_index, loss_scale)
         return self.vocab_proj(self.forward_hidden(x, kv_cache, position_ids))
 
     def loss_sum(self, x: Tensor, targets: Tensor, ignore_index: int = -1,

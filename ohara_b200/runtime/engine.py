@@ -1,0 +1,472 @@
+"""``OharaEngine``: the runtime facade the trainer talks to.
+
+Same surface as the reference engine (ohara/runtime/engine.py:57-499) — ``launch``, ``prepare`` /
+``setup`` aliases, ``prepare_dataloaders``, ``to_device``, ``autocast_context``, ``backward``,
+``no_backward_sync``, ``clip_gradients``, ``optimizer_step``, collectives, atomic ``save`` /
+``load``, ``log_dict`` — with a different engine room:
+
+* one process per GPU; c10d (NCCL, or gloo without CUDA) is the control plane;
+* process groups exist for every parallel dimension (data, tensor, context, expert), built from
+  :class:`ParallelTopology` arithmetic rather than a DeviceMesh;
+* tensor parallelism replaces the matched linears by sharded modules (no DTensor);
+* data parallelism is DDP or the sharded-optimizer strategy (``StrategyType.FSDP``), whose
+  reduce-scatter / optimizer / all-gather run as fused peer-memory kernels when enabled;
+* batches move host→device through pinned staging on a side stream.
+"""
+
+from __future__ import annotations
+
+import os
+from collections.abc import Callable, Mapping
+from contextlib import nullcontext
+from datetime import timedelta
+from pathlib import Path
+from typing import Any
+
+import torch
+import torch.distributed as dist
+from torch.optim import Optimizer
+from torch.utils.data import DataLoader, DistributedSampler, IterableDataset, RandomSampler
+
+from .config import EngineConfig
+from .enums import Backend, PrecisionMode, ReduceType, StrategyType
+from .strategy import BaseStrategy, DDPStrategy, FSDPStrategy, SingleStrategy
+from .tensor_parallel import (
+    TensorParallelPlan,
+    apply_tensor_parallel,
+    gather_tensor_parallel_state,
+)
+from .topology import ParallelTopology
+
+
+class _DeviceDataLoader:
+    """Iterates a dataloader and yields batches already on the engine's device."""
+
+    def __init__(self, dataloader: DataLoader, engine: "OharaEngine") -> None:
+        self.dataloader = dataloader
+        self.engine = engine
+        self.epoch = 0
+
+    def __iter__(self):
+        sampler = getattr(self.dataloader, "sampler", None)
+        if isinstance(sampler, DistributedSampler):
+            sampler.set_epoch(self.epoch)
+            self.epoch += 1
+        for batch in self.dataloader:
+            yield self.engine.to_device(batch)
+
+    def __len__(self) -> int:
+        return len(self.dataloader)
+
+    def __getattr__(self, name: str) -> Any:
+        return getattr(self.dataloader, name)
+
+
+_REDUCE_OPS = {
+    ReduceType.SUM: "SUM",
+    ReduceType.MEAN: "SUM",
+    ReduceType.MAX: "MAX",
+    ReduceType.MIN: "MIN",
+}
+
+
+class OharaEngine:
+    def __init__(self, config: EngineConfig | None = None, loggers: list[Any] | None = None) -> None:
+        self.config = config or EngineConfig()
+        self.loggers = loggers or []
+        self._launched = False
+        self._device = torch.device("cpu")
+        self._strategy: BaseStrategy = SingleStrategy()
+        try:
+            self.topology = ParallelTopology.from_config(1, self.config.parallel)
+        except ValueError:
+            self.topology = ParallelTopology(1, 1, 1, 1, 1, 1, 1)
+        self._scaler = self._build_grad_scaler(False)
+        self._groups: dict[str, Any] = {}
+        self._dp_world_size = 1
+        self._dp_rank = 0
+
+    # -- properties ----------------------------------------------------------------------------
+    @staticmethod
+    def _build_grad_scaler(enabled: bool):
+        return torch.amp.GradScaler("cuda", enabled=enabled)
+
+    @property
+    def launched(self) -> bool:
+        return self._launched
+
+    @property
+    def device(self) -> torch.device:
+        return self._device
+
+    @property
+    def world_size(self) -> int:
+        return self.topology.world_size
+
+    @property
+    def global_rank(self) -> int:
+        return self.topology.global_rank
+
+    @property
+    def is_global_zero(self) -> bool:
+        return self.global_rank == 0
+
+    @property
+    def data_parallel_rank(self) -> int:
+        """Rank used to shard input data; tensor/context-parallel peers share it."""
+        return self.topology.dp_rank
+
+    @property
+    def data_parallel_world_size(self) -> int:
+        return self.topology.dp_world_size
+
+    @property
+    def strategy(self) -> BaseStrategy:
+        return self._strategy
+
+    def group(self, name: str):
+        """Process group of a parallel dimension: ``"dp"``, ``"tp"``, ``"cp"`` or ``"ep"``
+        (``None`` = the default world group, or no group when not distributed)."""
+        return self._groups.get(name)
+
+    # -- launch --------------------------------------------------------------------------------
+    def launch(self, function: Callable[..., Any] | None = None, *args: Any, **kwargs: Any) -> Any:
+        if not self._launched:
+            self._do_launch()
+        if function is not None:
+            return function(*args, **kwargs)
+        return None
+
+    def _do_launch(self) -> None:
+        world_size = int(os.environ.get("WORLD_SIZE", "1"))
+        wants_dist = world_size > 1 or int(os.environ.get("RANK", "0")) > 0
+        backend_name: str | None = None
+        if wants_dist and not dist.is_initialized():
+            backend = self.config.distributed.backend
+            if backend == Backend.NCCL and not torch.cuda.is_available():
+                backend = Backend.GLOO
+            if torch.cuda.is_available() and backend == Backend.NCCL:
+                local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+                if local_rank < torch.cuda.device_count():
+                    torch.cuda.set_device(local_rank)
+            dist.init_process_group(
+                backend=backend.value,
+                timeout=timedelta(seconds=self.config.distributed.timeout_seconds),
+            )
+        if dist.is_initialized():
+            world_size = dist.get_world_size()
+            backend_name = dist.get_backend()
+        self.topology = ParallelTopology.from_config(world_size, self.config.parallel)
+
+        if torch.cuda.is_available() and (not wants_dist or backend_name == Backend.NCCL.value):
+            self._device = torch.device(f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}")
+            torch.cuda.set_device(self._device)
+        elif torch.backends.mps.is_available():
+            self._device = torch.device("mps")
+        else:
+            self._device = torch.device("cpu")
+
+        strategy = self.config.strategy
+        if strategy == StrategyType.AUTO:
+            strategy = StrategyType.DDP if self.topology.dp_enabled else StrategyType.SINGLE
+        if strategy in (StrategyType.DDP, StrategyType.FSDP) and not self.topology.distributed_enabled:
+            strategy = StrategyType.SINGLE if strategy == StrategyType.DDP else strategy
+        self._build_groups()
+        data_parallel = strategy in (StrategyType.DDP, StrategyType.FSDP)
+        self._dp_world_size = self.topology.dp_world_size if data_parallel else 1
+        self._dp_rank = self.topology.dp_rank if data_parallel else 0
+        if strategy == StrategyType.DDP:
+            self._strategy = DDPStrategy(init_sync=not self.topology.tp_enabled)
+        elif strategy == StrategyType.FSDP:
+            fused = self.config.fused_collectives and self._device.type == "cuda"
+            self._strategy = FSDPStrategy(fused=fused, init_sync=not self.topology.tp_enabled)
+        else:
+            self._strategy = SingleStrategy()
+        use_scaler = (
+            self.config.precision.mode == PrecisionMode.FP16_MIXED and self._device.type == "cuda"
+        )
+        self._scaler = self._build_grad_scaler(use_scaler)
+        self._launched = True
+
+    def _build_groups(self) -> None:
+        """Create one process group per parallel dimension that is larger than 1. Every rank calls
+        ``new_group`` for every group of a dimension (a c10d requirement)."""
+        self._groups = {}
+        topo = self.topology
+        if not dist.is_initialized() or topo.world_size <= 1:
+            return
+        dims = {
+            "dp": (("dp_replicate", "dp_shard"), topo.dp_world_size),
+            "tp": (("tp",), topo.tp),
+            "cp": (("cp",), topo.cp),
+            "ep": (("ep",), topo.ep),
+            "pp": (("pp",), topo.pp),
+        }
+        me = topo.global_rank
+        for name, (axes, size) in dims.items():
+            if size <= 1:
+                continue
+            if size == topo.world_size:
+                self._groups[name] = None  # the default group
+                continue
+            for ranks in topo.iter_groups(axes):
+                pg = dist.new_group(ranks=ranks)
+                if me in ranks:
+                    self._groups[name] = pg
+
+    # -- prepare -------------------------------------------------------------------------------
+    def prepare(self, module: torch.nn.Module, *optimizers: Optimizer):
+        module = self.prepare_module(module)
+        if not optimizers:
+            return module
+        wrapped = self.prepare_optimizers(*optimizers)
+        if len(wrapped) == 1:
+            return module, wrapped[0]
+        return (module, *wrapped)
+
+    def prepare_module(self, module: torch.nn.Module, *, move_to_device: bool = True) -> torch.nn.Module:
+        self.launch()
+        if move_to_device:
+            if self.config.precision.mode == PrecisionMode.BF16_TRUE:
+                module = module.to(device=self._device, dtype=torch.bfloat16)
+            else:
+                module = module.to(self._device)
+        module = self._maybe_apply_tensor_parallel(module)
+        module = self._strategy.setup_module(
+            module, device=self._device, process_group=self._groups.get("dp")
+        )
+        self._module = module
+        return module
+
+    def prepare_optimizers(self, *optimizers: Optimizer):
+        self.launch()
+        module = getattr(self, "_module", None)
+        return tuple(self._strategy.setup_optimizer(opt, module) for opt in optimizers)
+
+    # Fabric-style aliases
+    def setup(self, module: torch.nn.Module, *optimizers: Optimizer):
+        return self.prepare(module, *optimizers)
+
+    def setup_module(self, module: torch.nn.Module, *, move_to_device: bool = True):
+        return self.prepare_module(module, move_to_device=move_to_device)
+
+    def setup_optimizers(self, *optimizers: Optimizer):
+        return self.prepare_optimizers(*optimizers)
+
+    def setup_dataloaders(self, *dataloaders: DataLoader):
+        return self.prepare_dataloaders(*dataloaders)
+
+    def _resolve_tensor_parallel_plan(self, module: torch.nn.Module) -> TensorParallelPlan:
+        plan = self.config.tensor_parallel
+        if not self.topology.tp_enabled:
+            return plan
+        if plan.degree in (0, 1):
+            plan = TensorParallelPlan.llama_default(self.topology.tp, plan.sequence_parallel)
+        if plan.degree != self.topology.tp:
+            raise ValueError(
+                f"TensorParallelPlan.degree={plan.degree} does not match topology.tp={self.topology.tp}"
+            )
+        plan.validate(hidden_size=getattr(getattr(module, "config", None), "hidden_size", None))
+        return plan
+
+    def _maybe_apply_tensor_parallel(self, module: torch.nn.Module) -> torch.nn.Module:
+        if not self.topology.tp_enabled:
+            return module
+        plan = self._resolve_tensor_parallel_plan(module)
+        return apply_tensor_parallel(
+            module, self._groups.get("tp"), plan, tp_rank=self.topology.tp_rank,
+            tp_world=self.topology.tp,
+        )
+
+    # -- data ----------------------------------------------------------------------------------
+    def _replace_sampler(self, dataloader: DataLoader) -> DataLoader:
+        dataset = getattr(dataloader, "dataset", None)
+        if dataset is None or isinstance(dataset, IterableDataset):
+            return dataloader
+        if isinstance(getattr(dataloader, "sampler", None), DistributedSampler):
+            return dataloader
+        if dataloader.batch_size is None:
+            return dataloader
+        sampler = DistributedSampler(
+            dataset, num_replicas=self._dp_world_size, rank=self._dp_rank,
+            shuffle=isinstance(dataloader.sampler, RandomSampler), drop_last=dataloader.drop_last,
+        )
+        kwargs: dict[str, Any] = dict(
+            dataset=dataset, batch_size=dataloader.batch_size, sampler=sampler,
+            num_workers=dataloader.num_workers, collate_fn=dataloader.collate_fn,
+            pin_memory=dataloader.pin_memory, drop_last=dataloader.drop_last,
+            timeout=dataloader.timeout, worker_init_fn=dataloader.worker_init_fn,
+            persistent_workers=dataloader.persistent_workers,
+        )
+        if dataloader.num_workers > 0:
+            kwargs["prefetch_factor"] = dataloader.prefetch_factor
+        return DataLoader(**kwargs)
+
+    def prepare_dataloaders(self, *dataloaders: DataLoader):
+        self.launch()
+        if not dataloaders:
+            raise ValueError("At least one dataloader is required")
+        loaders = [
+            self._replace_sampler(dl) if self._dp_world_size > 1 else dl for dl in dataloaders
+        ]
+        wrapped = [
+            dl if isinstance(dl, _DeviceDataLoader) else _DeviceDataLoader(dl, self)
+            for dl in loaders
+        ]
+        return tuple(wrapped) if len(wrapped) > 1 else wrapped[0]
+
+    def to_device(self, value: Any) -> Any:
+        """Recursively move the tensors of a nested batch to the compute device. CPU tensors going
+        to a CUDA device are staged through pinned memory so the copy is asynchronous."""
+        if isinstance(value, torch.Tensor):
+            if value.device == self._device:
+                return value
+            if self._device.type == "cuda" and value.device.type == "cpu":
+                if not value.is_pinned():
+                    value = value.pin_memory()
+                return value.to(self._device, non_blocking=True)
+            return value.to(self._device)
+        if isinstance(value, Mapping):
+            moved = {key: self.to_device(item) for key, item in value.items()}
+            try:
+                return type(value)(moved)
+            except TypeError:
+                return moved
+        if isinstance(value, tuple) and hasattr(value, "_fields"):
+            return type(value)(*(self.to_device(item) for item in value))
+        if isinstance(value, tuple):
+            return tuple(self.to_device(item) for item in value)
+        if isinstance(value, list):
+            return [self.to_device(item) for item in value]
+        return value
+
+    # -- step helpers --------------------------------------------------------------------------
+    def autocast_context(self):
+        mode = self.config.precision.mode
+        if self._device.type != "cuda":
+            return nullcontext()
+        if mode == PrecisionMode.FP16_MIXED:
+            return torch.autocast(device_type="cuda", dtype=torch.float16)
+        if mode == PrecisionMode.BF16_MIXED:
+            return torch.autocast(device_type="cuda", dtype=torch.bfloat16)
+        return nullcontext()
+
+    def backward(self, loss: torch.Tensor) -> None:
+        if self._scaler.is_enabled():
+            self._scaler.scale(loss).backward()
+        else:
+            loss.backward()
+
+    def no_sync(self, module: torch.nn.Module, enabled: bool = True):
+        return self._strategy.no_sync(module, enabled=enabled)
+
+    def no_backward_sync(self, module: torch.nn.Module, enabled: bool = True):
+        return self.no_sync(module, enabled=enabled)
+
+    def clip_gradients(self, model: torch.nn.Module, optimizer: Optimizer, max_norm: float) -> torch.Tensor:
+        if self._scaler.is_enabled():
+            self._scaler.unscale_(optimizer)
+        clip = getattr(optimizer, "clip_grad_norm_", None)
+        if callable(clip):  # sharded optimizers know how to form the global norm
+            return clip(model, max_norm)
+        return torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=max_norm)
+
+    def optimizer_step(self, optimizer: Optimizer) -> None:
+        if self._scaler.is_enabled():
+            self._scaler.step(optimizer)
+            self._scaler.update()
+        else:
+            optimizer.step()
+
+    # -- collectives ---------------------------------------------------------------------------
+    def barrier(self) -> None:
+        if dist.is_initialized():
+            if dist.get_backend() == Backend.NCCL.value and self._device.type == "cuda":
+                dist.barrier(device_ids=[self._device.index])
+            else:
+                dist.barrier()
+
+    def synchronize(self) -> None:
+        if self._device.type == "cuda":
+            torch.cuda.synchronize(self._device)
+
+    def broadcast(self, obj: Any, src: int = 0) -> Any:
+        if not dist.is_initialized():
+            return obj
+        payload = [obj]
+        dist.broadcast_object_list(payload, src=src)
+        return payload[0]
+
+    def all_reduce(self, tensor: torch.Tensor, reduce_type: ReduceType | str = ReduceType.MEAN, *,
+                   group: Any | None = None, reduce_op: ReduceType | str | None = None) -> torch.Tensor:
+        selected = reduce_op if reduce_op is not None else reduce_type
+        if isinstance(selected, str):
+            selected = ReduceType(selected)
+        if selected not in _REDUCE_OPS:
+            raise ValueError(f"Unsupported reduce type: {selected}")
+        if not dist.is_initialized():
+            return tensor
+        dist.all_reduce(tensor, op=getattr(dist.ReduceOp, _REDUCE_OPS[selected]), group=group)
+        if selected == ReduceType.MEAN:
+            tensor /= dist.get_world_size(group=group) if group is not None else self.world_size
+        return tensor
+
+    def all_gather(self, tensor: torch.Tensor, group: Any | None = None) -> list[torch.Tensor]:
+        if not dist.is_initialized():
+            return [tensor]
+        world = dist.get_world_size(group=group) if group is not None else self.world_size
+        gathered = [torch.zeros_like(tensor) for _ in range(world)]
+        dist.all_gather(gathered, tensor, group=group)
+        return gathered
+
+    # -- checkpoints ---------------------------------------------------------------------------
+    def full_state_dict(self, module: torch.nn.Module) -> dict[str, torch.Tensor]:
+        """Unsharded, wrapper-free state dict of ``module`` (collective when TP/FSDP is active):
+        what the reference's ``Llama`` can load directly."""
+        inner = module.module if hasattr(module, "module") else module
+        sync = getattr(getattr(self, "_sharded_optimizer", None), "sync_master_weights", None)
+        if callable(sync):
+            sync()
+        if self.topology.tp_enabled:
+            return gather_tensor_parallel_state(inner, self._groups.get("tp"))
+        return inner.state_dict()
+
+    def save(self, path: str | Path, state: dict[str, Any]) -> None:
+        """Rank 0 writes ``state`` atomically (temp file + rename), then everyone meets at a
+        barrier. Collective state (sharded optimizers) must be materialised by the caller."""
+        path = Path(path)
+        if self.is_global_zero:
+            path.parent.mkdir(parents=True, exist_ok=True)
+            temporary = path.with_name(f".{path.name}.tmp-{os.getpid()}")
+            try:
+                torch.save(state, temporary)
+                os.replace(temporary, path)
+            finally:
+                temporary.unlink(missing_ok=True)
+        self.barrier()
+
+    def load(self, path: str | Path, state: dict[str, Any] | None = None) -> dict[str, Any]:
+        payload: dict[str, Any] = torch.load(Path(path), map_location=self._device, weights_only=False)
+        if state is None:
+            return payload
+        for key, obj in state.items():
+            if key not in payload:
+                continue
+            if hasattr(obj, "load_state_dict"):
+                obj.load_state_dict(payload[key])
+            else:
+                state[key] = payload[key]
+        return payload
+
+    def log_dict(self, payload: dict[str, Any], step: int | None = None) -> None:
+        if not self.is_global_zero:
+            return
+        for logger in self.loggers:
+            if hasattr(logger, "log_metrics"):
+                logger.log_metrics(payload, step=step)
+            elif hasattr(logger, "log_dict"):
+                logger.log_dict(payload, step=step)
+
+    def close(self) -> None:
+        if dist.is_initialized():
+            dist.destroy_process_group()

@@ -1,0 +1,258 @@
+"""Tensor-parallel plan and the sharded linear layers that implement it.
+
+The plan object and ``llama_default`` rules match the reference (ohara/runtime/tensor_parallel.py:
+14-90): fnmatch patterns mapping module names to COLWISE / ROWWISE. The implementation does not use
+DTensor: matched ``nn.Linear`` modules are replaced in place by :class:`ColumnParallelLinear` /
+:class:`RowParallelLinear`, which keep the local weight shard under the same state-dict key and
+place the collectives explicitly (identity/all-reduce pairs, or all-gather/reduce-scatter pairs on
+the sequence dimension when ``sequence_parallel`` is on). Attention derives its local head count
+from the projection width, so query and KV heads are split across ranks (GQA included).
+"""
+
+from __future__ import annotations
+
+import fnmatch
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch import Tensor
+
+from .enums import TensorParallelStyle
+
+
+@dataclass
+class TensorParallelRule:
+    module_pattern: str
+    style: TensorParallelStyle
+
+
+@dataclass
+class TensorParallelPlan:
+    degree: int = 1
+    sequence_parallel: bool = False
+    rules: list[TensorParallelRule] = field(default_factory=list)
+
+    def validate(self, hidden_size: int | None = None) -> None:
+        if self.degree < 1:
+            raise ValueError("tensor parallel degree must be >= 1")
+        if hidden_size is not None and hidden_size % self.degree != 0:
+            raise ValueError(
+                f"hidden_size={hidden_size} must be divisible by tensor parallel degree={self.degree}"
+            )
+
+    @classmethod
+    def llama_default(cls, degree: int, sequence_parallel: bool = False) -> "TensorParallelPlan":
+        col, row = TensorParallelStyle.COLWISE, TensorParallelStyle.ROWWISE
+        return cls(
+            degree=degree,
+            sequence_parallel=sequence_parallel,
+            rules=[
+                TensorParallelRule("layers.*.attn.query", col),
+                TensorParallelRule("layers.*.attn.key", col),
+                TensorParallelRule("layers.*.attn.value", col),
+                TensorParallelRule("layers.*.attn.proj", row),
+                TensorParallelRule("layers.*.ff.up", col),
+                TensorParallelRule("layers.*.ff.gate", col),
+                TensorParallelRule("layers.*.ff.down", row),
+            ],
+        )
+
+    def style_for(self, module_fqn: str) -> TensorParallelStyle | None:
+        for rule in self.rules:
+            if fnmatch.fnmatch(module_fqn, rule.module_pattern):
+                return rule.style
+        return None
+
+
+# --------------------------------------------------------------------------------------------------
+# Collective autograd pairs
+# --------------------------------------------------------------------------------------------------
+class _CopyToGroup(torch.autograd.Function):
+    """Identity forward, all-reduce(sum) backward: entry of a column-parallel region."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, grad: Tensor):
+        grad = grad.contiguous()
+        dist.all_reduce(grad, group=ctx.group)
+        return grad, None
+
+
+class _ReduceFromGroup(torch.autograd.Function):
+    """All-reduce(sum) forward, identity backward: exit of a row-parallel region."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group):
+        x = x.contiguous()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, grad: Tensor):
+        return grad, None
+
+
+class _GatherSequence(torch.autograd.Function):
+    """All-gather along dim 1 forward, reduce-scatter backward (sequence-parallel entry)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group):
+        ctx.group = group
+        world = dist.get_world_size(group)
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        return torch.cat(parts, dim=1)
+
+    @staticmethod
+    def backward(ctx, grad: Tensor):
+        world = dist.get_world_size(ctx.group)
+        chunks = [c.contiguous() for c in grad.chunk(world, dim=1)]
+        out = torch.empty_like(chunks[0])
+        dist.reduce_scatter(out, chunks, group=ctx.group)
+        return out, None
+
+
+class _ScatterSequence(torch.autograd.Function):
+    """Reduce-scatter along dim 1 forward, all-gather backward (sequence-parallel exit)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group):
+        ctx.group = group
+        world = dist.get_world_size(group)
+        chunks = [c.contiguous() for c in x.chunk(world, dim=1)]
+        out = torch.empty_like(chunks[0])
+        dist.reduce_scatter(out, chunks, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad: Tensor):
+        world = dist.get_world_size(ctx.group)
+        parts = [torch.empty_like(grad) for _ in range(world)]
+        dist.all_gather(parts, grad.contiguous(), group=ctx.group)
+        return torch.cat(parts, dim=1), None
+
+
+# --------------------------------------------------------------------------------------------------
+# Sharded linears
+# --------------------------------------------------------------------------------------------------
+class _ParallelLinear(nn.Module):
+    def __init__(self, source: nn.Linear, group, rank: int, world: int, shard_dim: int,
+                 sequence_parallel: bool) -> None:
+        super().__init__()
+        full = source.weight.shape[shard_dim]
+        if full % world != 0:
+            raise ValueError(
+                f"cannot shard a dimension of {full} over tensor parallel degree {world}"
+            )
+        self.group = group
+        self.tp_rank = rank
+        self.tp_world = world
+        self.sequence_parallel = sequence_parallel
+        self.in_features = source.in_features
+        self.out_features = source.out_features
+        self.shard_dim = shard_dim
+        shard = source.weight.detach().chunk(world, dim=shard_dim)[rank].clone()
+        self.weight = nn.Parameter(shard, requires_grad=source.weight.requires_grad)
+        self.weight.tensor_parallel_dim = shard_dim
+        self.bias = None
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, "
+                f"tp={self.tp_world}, local_weight={tuple(self.weight.shape)}")
+
+
+class ColumnParallelLinear(_ParallelLinear):
+    """Output features split over the group; input replicated (or sequence-sharded with SP)."""
+
+    def __init__(self, source: nn.Linear, group, rank: int, world: int,
+                 sequence_parallel: bool = False) -> None:
+        super().__init__(source, group, rank, world, 0, sequence_parallel)
+        if source.bias is not None:
+            self.bias = nn.Parameter(source.bias.detach().chunk(world)[rank].clone())
+            self.bias.tensor_parallel_dim = 0
+
+    def forward(self, x: Tensor) -> Tensor:
+        from ohara_b200 import ops
+
+        if self.sequence_parallel:
+            x = _GatherSequence.apply(x, self.group)
+        else:
+            x = _CopyToGroup.apply(x, self.group)
+        return ops.linear(x, self.weight, self.bias)
+
+
+class RowParallelLinear(_ParallelLinear):
+    """Input features split over the group; partial outputs summed (or reduce-scattered)."""
+
+    def __init__(self, source: nn.Linear, group, rank: int, world: int,
+                 sequence_parallel: bool = False) -> None:
+        super().__init__(source, group, rank, world, 1, sequence_parallel)
+        if source.bias is not None:
+            self.bias = nn.Parameter(source.bias.detach().clone())
+
+    def forward(self, x: Tensor) -> Tensor:
+        from ohara_b200 import ops
+
+        y = ops.linear(x, self.weight, None)
+        if self.sequence_parallel:
+            y = _ScatterSequence.apply(y, self.group)
+        else:
+            y = _ReduceFromGroup.apply(y, self.group)
+        if self.bias is not None:
+            y = y + self.bias.to(y.dtype)
+        return y
+
+
+def apply_tensor_parallel(module: nn.Module, tp_group, plan: TensorParallelPlan,
+                          tp_rank: int | None = None, tp_world: int | None = None) -> nn.Module:
+    """Replace every ``nn.Linear`` matched by ``plan`` with its sharded counterpart, in place."""
+    plan.validate()
+    world = tp_world if tp_world is not None else dist.get_world_size(tp_group)
+    rank = tp_rank if tp_rank is not None else dist.get_rank(tp_group)
+    if plan.degree not in (0, 1, world):
+        raise ValueError(f"plan degree {plan.degree} does not match the group size {world}")
+    replaced = 0
+    for fqn, child in list(module.named_modules()):
+        if not fqn or not isinstance(child, nn.Linear):
+            continue
+        style = plan.style_for(fqn)
+        if style is None:
+            continue
+        cls = ColumnParallelLinear if style == TensorParallelStyle.COLWISE else RowParallelLinear
+        parent_name, _, leaf = fqn.rpartition(".")
+        parent = module.get_submodule(parent_name) if parent_name else module
+        setattr(parent, leaf, cls(child, tp_group, rank, world, plan.sequence_parallel))
+        replaced += 1
+    if replaced == 0:
+        raise ValueError(
+            "No modules matched tensor parallel rules. "
+            "Provide matching TensorParallelRule patterns for your model."
+        )
+    module.tensor_parallel_degree = world
+    return module
+
+
+def gather_tensor_parallel_state(module: nn.Module, tp_group) -> dict[str, Tensor]:
+    """Full (unsharded) state dict of a tensor-parallel module: shards are all-gathered along the
+    dimension recorded on each parameter, so the result loads into a single-device model."""
+    world = dist.get_world_size(tp_group)
+    sharded = {
+        name: getattr(param, "tensor_parallel_dim")
+        for name, param in module.named_parameters()
+        if hasattr(param, "tensor_parallel_dim")
+    }
+    full: dict[str, Tensor] = {}
+    for name, tensor in module.state_dict().items():
+        if name in sharded:
+            parts = [torch.empty_like(tensor) for _ in range(world)]
+            dist.all_gather(parts, tensor.contiguous(), group=tp_group)
+            full[name] = torch.cat(parts, dim=sharded[name])
+        else:
+            full[name] = tensor
+    return full
