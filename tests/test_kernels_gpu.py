@@ -1,0 +1,256 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from ohara_b200.ops._ext import ext
+
+    return ext()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(C):
+    yield
+    torch.cuda.synchronize()
+    code, block, count, _ = C.status(True)
+    assert code == 0, f"kernel wait timed out: code={code} block={block} count={count}"
+
+
+def rel_err(got, ref):
+    return (got.float() - ref.float()).abs().max().item() / (ref.float().abs().max().item() + 1e-12)
+
+
+def bf(*shape):
+    return torch.randn(*shape, device="cuda").bfloat16()
+
+
+# -- GEMM -----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (512, 384, 256), (1000, 776, 520), (4096, 768, 768)])
+def test_gemm_nt(C, m, n, k):
+    a, b = bf(m, k), bf(n, k)
+    c = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    C.gemm(a, b, c, m, n, k, False, False)
+    assert rel_err(c, a.float() @ b.float().T) < 1e-2
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 384, 256), (2048, 768, 2048)])
+def test_gemm_nn(C, m, n, k):
+    a, b = bf(m, k), bf(k, n)
+    c = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    C.gemm(a, b, c, m, n, k, False, True)
+    assert rel_err(c, a.float() @ b.float()) < 1e-2
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(256, 256, 512, 1), (768, 768, 8192, 8), (776, 520, 1000, 3)])
+def test_gemm_tn_splitk_reduce(C, m, n, k, splits):
+    a, b = bf(k, m), bf(k, n)
+    c = torch.zeros(m, n, device="cuda", dtype=torch.float32)
+    C.gemm(a, b, c, m, n, k, True, True, splits, True)
+    assert rel_err(c, a.float().T @ b.float()) < 2e-3
+    # reduce epilogue accumulates into existing contents
+    C.gemm(a, b, c, m, n, k, True, True, splits, True)
+    assert rel_err(c, 2 * (a.float().T @ b.float())) < 2e-3
+
+
+def test_gemm_batched_alpha_residual(C):
+    a, b, r = bf(5, 256, 192), bf(5, 320, 192), bf(5, 256, 320)
+    c = torch.empty(5, 256, 320, device="cuda", dtype=torch.bfloat16)
+    C.gemm(a, b, c, 256, 320, 192, False, False, alpha=0.5, residual=r, beta=-2.0)
+    ref = 0.5 * torch.bmm(a.float(), b.float().transpose(1, 2)) - 2.0 * r.float()
+    assert rel_err(c, ref) < 1e-2
+
+
+def test_matmul_wrappers_match_linear_grads():
+    from ohara_b200 import ops
+
+    x = bf(384, 256).requires_grad_()
+    w = (torch.randn(512, 256, device="cuda") * 0.05).requires_grad_()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = ops.linear(x, w)
+    dy = bf(384, 512)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().bfloat16().float().requires_grad_()
+    (xr @ wr.T).backward(dy.float())
+    assert rel_err(y, xr @ wr.T) < 1e-2
+    assert rel_err(x.grad, xr.grad) < 1e-2
+    assert rel_err(w.grad, wr.grad) < 5e-3
+    assert w.grad.dtype == torch.float32
+
+
+# -- elementwise ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,d", [(1000, 768), (33, 256), (4096, 2048)])
+def test_rmsnorm_forward_backward(rows, d):
+    from ohara_b200 import ops
+    from ohara_b200.modules.norm import rms_norm_reference
+
+    x = bf(rows, d).requires_grad_()
+    w = (1 + 0.1 * torch.randn(d, device="cuda")).requires_grad_()
+    y = ops.rms_norm(x, w, 1e-5)
+    dy = bf(rows, d)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().clone().requires_grad_()
+    yr = rms_norm_reference(xr, wr, 1e-5)
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < 1e-2
+    assert rel_err(x.grad, xr.grad) < 2e-2
+    assert rel_err(w.grad, wr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim", [(6, 6, 128), (16, 4, 64)])
+def test_rope_forward_backward(heads, kv_heads, dim):
+    from ohara_b200 import ops
+    from ohara_b200.embeddings_pos.rotary import precompute_freqs_cis, rope_reference
+
+    b, t = 3, 77
+    cos, sin = (v.cuda() for v in precompute_freqs_cis(dim, 128, 10000.0))
+    q, k = bf(b, t, heads, dim).requires_grad_(), bf(b, t, kv_heads, dim).requires_grad_()
+    qo, ko = ops.rope_qk(q, k, cos, sin)
+    gq, gk = bf(b, t, heads, dim), bf(b, t, kv_heads, dim)
+    torch.autograd.backward([qo, ko], [gq, gk])
+    assert rel_err(qo, rope_reference(q.detach().float(), cos, sin)) < 1e-2
+    assert rel_err(ko, rope_reference(k.detach().float(), cos, sin)) < 1e-2
+    # The gradient of a rotation is the inverse rotation of the incoming gradient.
+    assert rel_err(q.grad, rope_reference(gq.float(), cos, sin, inverse=True)) < 1e-2
+    assert rel_err(k.grad, rope_reference(gk.float(), cos, sin, inverse=True)) < 1e-2
+
+
+def test_swiglu_forward_backward():
+    from ohara_b200 import ops
+
+    g, u = bf(513, 1024).requires_grad_(), bf(513, 1024).requires_grad_()
+    a = ops.swiglu(g, u)
+    da = bf(513, 1024)
+    a.backward(da)
+    gr, ur = g.detach().float().requires_grad_(), u.detach().float().requires_grad_()
+    ar = F.silu(gr) * ur
+    ar.backward(da.float())
+    assert rel_err(a, ar) < 1e-2
+    assert rel_err(g.grad, gr.grad) < 1e-2
+    assert rel_err(u.grad, ur.grad) < 1e-2
+
+
+def test_embedding_forward_backward():
+    from ohara_b200 import ops
+
+    table = torch.randn(1000, 256, device="cuda", requires_grad=True)
+    ids = torch.randint(0, 1000, (4, 300), device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = ops.embedding(ids, table)
+    assert out.dtype == torch.bfloat16
+    dout = bf(4, 300, 256)
+    out.backward(dout)
+    ref = table.detach().clone().requires_grad_()
+    F.embedding(ids, ref).backward(dout.float())
+    assert rel_err(out, F.embedding(ids, ref)) < 1e-2
+    assert rel_err(table.grad, ref.grad) < 1e-3
+
+
+def test_fused_adamw_matches_torch():
+    from ohara_b200.optimizer import FusedAdamW
+
+    torch.manual_seed(0)
+    p1 = torch.randn(1000, 64, device="cuda", requires_grad=True)
+    p2 = p1.detach().clone().requires_grad_()
+    ours = FusedAdamW([p1], lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
+    ref = torch.optim.AdamW([p2], lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
+    for _ in range(5):
+        g = torch.randn_like(p1)
+        p1.grad, p2.grad = g.clone(), g.clone()
+        ours.step()
+        ref.step()
+    assert torch.allclose(p1, p2, rtol=1e-5, atol=1e-6)
+
+
+# -- loss -------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tokens,dim,vocab", [(300, 128, 1000), (2048, 256, 5003 // 8 * 8), (700, 768, 50304)])
+def test_linear_cross_entropy(tokens, dim, vocab):
+    from ohara_b200 import ops
+
+    h = (0.5 * torch.randn(tokens, dim, device="cuda")).bfloat16().requires_grad_()
+    w = (0.05 * torch.randn(vocab, dim, device="cuda")).requires_grad_()
+    t = torch.randint(0, vocab, (tokens,), device="cuda")
+    t[::7] = -1
+    scale = 1.0 / float((t != -1).sum())
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        loss = ops.linear_cross_entropy(h, w, t, -1, scale)
+    loss.backward()
+    hr = h.detach().float().requires_grad_()
+    wr = w.detach().bfloat16().float().requires_grad_()
+    ref = F.cross_entropy(hr @ wr.T, t, ignore_index=-1, reduction="sum") * scale
+    ref.backward()
+    assert abs(float(loss) - float(ref)) / float(ref) < 5e-3
+    assert rel_err(h.grad, hr.grad) < 3e-2
+    assert rel_err(w.grad, wr.grad) < 3e-2
+
+
+# -- attention --------------------------------------------------------------------------------------
+ATTN_CASES = [
+    (1, 128, 128, 1, 1, 128, True),
+    (2, 384, 384, 4, 2, 64, True),
+    (1, 200, 200, 2, 1, 128, True),
+    (2, 100, 356, 2, 2, 128, True),
+    (1, 1, 300, 4, 4, 128, True),
+    (1, 512, 512, 8, 2, 64, False),
+    (2, 1024, 1024, 6, 6, 128, True),
+]
+
+
+@pytest.mark.parametrize("b,t,s,h,hk,d,causal", ATTN_CASES)
+def test_flash_attention_forward_backward(b, t, s, h, hk, d, causal):
+    from ohara_b200.ops.attention import attention, attention_reference
+
+    q, k, v = bf(b, t, h, d).requires_grad_(), bf(b, s, hk, d).requires_grad_(), bf(b, s, hk, d).requires_grad_()
+    out = attention(q, k, v, causal)
+    do = bf(b, t, h, d)
+    out.backward(do)
+    qr, kr, vr = (x.detach().float().requires_grad_() for x in (q, k, v))
+    ref = attention_reference(qr, kr, vr, causal)
+    ref.backward(do.float())
+    assert rel_err(out, ref) < 2e-2
+    assert rel_err(q.grad, qr.grad) < 2e-2
+    assert rel_err(k.grad, kr.grad) < 2e-2
+    assert rel_err(v.grad, vr.grad) < 2e-2
+
+
+# -- optimizer --------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape", [(4, 256, 256), (3, 512, 256), (2, 256, 768)])
+def test_newton_schulz_kernels_match_fp32(shape):
+    from ohara_b200.optimizer import _polar_express
+
+    g = torch.randn(*shape, device="cuda")
+    got = _polar_express(g, 5).float()
+    ref = _polar_express(g.cpu(), 5)
+    # bf16 iteration vs fp32: compare the property that matters (near-orthogonality) and closeness.
+    assert rel_err(got.cpu(), ref) < 0.08
+    small = min(shape[1], shape[2])
+    gram = got @ got.mT if shape[1] <= shape[2] else got.mT @ got
+    eye = torch.eye(small, device="cuda")
+    assert (gram - eye).abs().max().item() < 0.35
+
+
+def test_grouped_moe_matches_reference_dispatch():
+    from ohara_b200.modules.moe_grouped import GroupedMoE
+
+    torch.manual_seed(0)
+    moe = GroupedMoE(dim=128, hidden_dim=64, num_experts=8, num_experts_per_tok=2,
+                     num_shared_experts=1, gate_fn="softmax").cuda()
+    with torch.no_grad():
+        moe.w_down.normal_(std=0.05)
+        moe.shared_down.weight.normal_(std=0.05)
+    x = bf(2, 200, 128)
+    flat = x.reshape(-1, 128)
+    idx, wts, _, _ = moe._route(flat)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        got = moe._dispatch_grouped(flat, idx, wts)
+    ref = moe._dispatch_reference(flat.float(), idx, wts.float())
+    assert rel_err(got, ref) < 3e-2
