@@ -84,63 +84,82 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
 }
 
 // RMSNorm backward. dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres), dw += sum_rows(dy*xhat).
-// dw is accumulated per CTA in shared memory and flushed with one atomicAdd per column.
-template <bool HAS_DRES>
-__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
-                                   const __nv_bfloat16* __restrict__ x,
-                                   const float* __restrict__ w, const float* __restrict__ rstd,
-                                   const __nv_bfloat16* __restrict__ dres,
-                                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, int rows,
-                                   int d) {
-  extern __shared__ float dw_smem[];
+// One warp per row; every lane owns the same VPL 8-element column groups for all of its rows, so
+// x, dy and the dw partial sums stay in registers. Per-warp partials are combined through shared
+// memory and flushed with one atomicAdd per column per CTA.
+template <int VPL, bool HAS_DRES>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const float* __restrict__ w, const float* __restrict__ rstd,
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw, int rows, int d) {
+  extern __shared__ float dw_smem[];  // d floats
   for (int i = threadIdx.x; i < d; i += blockDim.x) dw_smem[i] = 0.f;
   __syncthreads();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int vecs = d >> 3;
+  float wreg[VPL][8];
+  float acc[VPL][8];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int v = lane + 32 * j;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      acc[j][i] = 0.f;
+      wreg[j][i] = (v < vecs) ? w[8 * v + i] : 0.f;
+    }
+  }
   for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows;
        row += gridDim.x * warps_per_block) {
     const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + (size_t)row * d);
     const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)row * d);
     const float r = rstd[row];
+    float g[VPL][8], xh[VPL][8];
     float dot = 0.f;
-    for (int v = lane; v < vecs; v += 32) {
-      float g[8], f[8];
-      unpack8(dyr[v], g);
-      unpack8(xr[v], f);
-      const float4 w0 = reinterpret_cast<const float4*>(w)[2 * v];
-      const float4 w1 = reinterpret_cast<const float4*>(w)[2 * v + 1];
-      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dot += g[i] * ww[i] * f[i] * r;
+    for (int j = 0; j < VPL; ++j) {
+      const int v = lane + 32 * j;
+      if (v < vecs) {
+        unpack8(dyr[v], g[j]);
+        unpack8(xr[v], xh[j]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[j][i] *= r;
+          dot += g[j][i] * wreg[j][i] * xh[j][i];
+        }
+      }
     }
     dot = warp_sum(dot) / (float)d;
     bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + (size_t)row * d);
     const bf16x8* drr =
         HAS_DRES ? reinterpret_cast<const bf16x8*>(dres + (size_t)row * d) : nullptr;
-    for (int v = lane; v < vecs; v += 32) {
-      float g[8], f[8], o[8];
-      unpack8(dyr[v], g);
-      unpack8(xr[v], f);
-      const float4 w0 = reinterpret_cast<const float4*>(w)[2 * v];
-      const float4 w1 = reinterpret_cast<const float4*>(w)[2 * v + 1];
-      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-      float extra[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      if (HAS_DRES) unpack8(drr[v], extra);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float xhat = f[i] * r;
-        o[i] = r * (g[i] * ww[i] - xhat * dot) + extra[i];
-        atomicAdd(&dw_smem[8 * v + i], g[i] * xhat);
+    for (int j = 0; j < VPL; ++j) {
+      const int v = lane + 32 * j;
+      if (v < vecs) {
+        float o[8];
+        float extra[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (HAS_DRES) unpack8(drr[v], extra);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          o[i] = r * (g[j][i] * wreg[j][i] - xh[j][i] * dot) + extra[i];
+          acc[j][i] += g[j][i] * xh[j][i];
+        }
+        dxr[v] = pack8(o);
       }
-      dxr[v] = pack8(o);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int v = lane + 32 * j;
+    if (v < vecs) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(&dw_smem[8 * v + i], acc[j][i]);
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    const float v = dw_smem[i];
-    if (v != 0.f) atomicAdd(&dw[i], v);
-  }
+  for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(&dw[i], dw_smem[i]);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -338,21 +357,35 @@ void rmsnorm_fwd(const void* x, const void* delta, const float* w, void* y, void
   OB_LAUNCH_CHECK();
 }
 
-void rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* dres,
-                 void* dx, float* dw, int rows, int d, cudaStream_t stream) {
-  OB_CHECK(d % 8 == 0, "rmsnorm: width must be a multiple of 8");
-  OB_CHECK(d * sizeof(float) <= 48 * 1024, "rmsnorm backward: width too large for shared memory");
+template <int VPL>
+void launch_rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd,
+                        const void* dres, void* dx, float* dw, int rows, int d,
+                        cudaStream_t stream) {
   const int threads = 256;
-  const int blocks = grid_for((int64_t)rows * 32, threads, 4);
+  const int blocks = std::min((rows + 7) / 8, device_sm_count() * 4);
   if (dres != nullptr)
-    rmsnorm_bwd_kernel<true><<<blocks, threads, d * sizeof(float), stream>>>(
+    rmsnorm_bwd_kernel<VPL, true><<<std::max(blocks, 1), threads, d * sizeof(float), stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dres,
         (__nv_bfloat16*)dx, dw, rows, d);
   else
-    rmsnorm_bwd_kernel<false><<<blocks, threads, d * sizeof(float), stream>>>(
+    rmsnorm_bwd_kernel<VPL, false><<<std::max(blocks, 1), threads, d * sizeof(float), stream>>>(
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, rstd, nullptr, (__nv_bfloat16*)dx, dw,
         rows, d);
   OB_LAUNCH_CHECK();
+}
+
+void rmsnorm_bwd(const void* dy, const void* x, const float* w, const float* rstd, const void* dres,
+                 void* dx, float* dw, int rows, int d, cudaStream_t stream) {
+  OB_CHECK(d % 8 == 0, "rmsnorm: width must be a multiple of 8");
+  OB_CHECK(d <= 8192, "rmsnorm backward supports widths up to 8192");
+  const int vpl = (d / 8 + 31) / 32;
+  if (vpl <= 1) launch_rmsnorm_bwd<1>(dy, x, w, rstd, dres, dx, dw, rows, d, stream);
+  else if (vpl <= 2) launch_rmsnorm_bwd<2>(dy, x, w, rstd, dres, dx, dw, rows, d, stream);
+  else if (vpl <= 3) launch_rmsnorm_bwd<3>(dy, x, w, rstd, dres, dx, dw, rows, d, stream);
+  else if (vpl <= 4) launch_rmsnorm_bwd<4>(dy, x, w, rstd, dres, dx, dw, rows, d, stream);
+  else if (vpl <= 8) launch_rmsnorm_bwd<8>(dy, x, w, rstd, dres, dx, dw, rows, d, stream);
+  else if (vpl <= 16) launch_rmsnorm_bwd<16>(dy, x, w, rstd, dres, dx, dw, rows, d, stream);
+  else launch_rmsnorm_bwd<32>(dy, x, w, rstd, dres, dx, dw, rows, d, stream);
 }
 
 void rope_qk(const void* q, const void* k, void* qo, void* ko, const float* cos_t,

@@ -41,6 +41,17 @@ size_t dtype_size(TmapDtype d) {
 void make_tmap(CUtensorMap* out, const void* base, TmapDtype dtype, int rank, const uint64_t* dims,
                const uint64_t* strides_bytes, const uint32_t* box, TmapSwizzle swizzle) {
   OB_CHECK(rank >= 1 && rank <= 5, "tensor map rank must be 1..5");
+  // The encoder is a driver-API entry point and needs a CUDA context bound to the calling thread.
+  // A thread that has only ever seen the runtime's default device (autograd worker threads, for
+  // example) may not have one yet; cudaSetDevice on the current device initialises the runtime
+  // for this thread and binds the primary context.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    int dev = 0;
+    OB_CUDA_CHECK(cudaGetDevice(&dev));
+    OB_CUDA_CHECK(cudaSetDevice(dev));
+    context_bound = true;
+  }
   OB_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base address must be 16-byte aligned");
   cuuint64_t gdims[5];
   cuuint64_t gstrides[4];

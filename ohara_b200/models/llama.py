@@ -181,6 +181,20 @@ class Block(nn.Module):
         x = x + self.ff(self.norm2(x)).to(x.dtype)
         return x
 
+    def forward_deferred(self, x, pending, freqs_cis, kv_cache: KVCache | None = None,
+                         position_ids: int | None = None):
+        """Same block, with the residual adds folded into the norms that follow them.
+
+        Takes the residual stream ``x`` plus a branch output ``pending`` that has not been added
+        yet (``None`` for the first block) and returns the updated stream and this block's own
+        not-yet-added feed-forward output. Mathematically identical to :meth:`forward`; on the
+        CUDA fast path each ``add + norm`` pair is one kernel, forward and backward.
+        """
+        h, x = ops.add_rms_norm(x, pending, self.norm1.weight, self.norm1.eps)
+        attn_out = self.attn(h, None, freqs_cis, kv_cache, position_ids)
+        h, x = ops.add_rms_norm(x, attn_out, self.norm2.weight, self.norm2.eps)
+        return x, self.ff(h)
+
 
 class Llama(nn.Module):
     def __init__(self, cfg: Config, *args, **kwargs) -> None:
@@ -231,10 +245,13 @@ class Llama(nn.Module):
         seq = x.size(1)
         h = ops.embedding(x, self.token_emb.weight)
         freqs = (self.freq_cos[start : start + seq], self.freq_sin[start : start + seq])
+        pending = None
         for idx, layer in enumerate(self.layers):
             cache = kv_cache[idx] if kv_cache is not None else None
-            h = layer(h, None, freqs, cache, start if cache is not None else None)
-        return self.norm(h)
+            h, pending = layer.forward_deferred(
+                h, pending, freqs, cache, start if cache is not None else None
+            )
+        return ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[0]
 
     supports_fused_loss = True
 

@@ -21,6 +21,7 @@ from torch import Tensor
 from ._ext import ext
 
 __all__ = [
+    "add_rms_norm",
     "attention",
     "bf16_weight",
     "embedding",
@@ -236,6 +237,41 @@ class _RMSNormFn(torch.autograd.Function):
         dy16 = (dy if dy.dtype == torch.bfloat16 else dy.to(torch.bfloat16)).contiguous()
         dx, dw = ext().rmsnorm_bwd(dy16, x16, w32, rstd, None)
         return dx.to(ctx.x_dtype), dw.to(ctx.w_dtype), None
+
+
+class _AddRMSNormFn(torch.autograd.Function):
+    """``s = x + delta; y = rms_norm(s)`` in one kernel; backward folds the residual gradient
+    into the norm backward (``ds = norm_bwd(dy) + d_s``), so neither add is a separate pass."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, delta: Tensor, weight: Tensor, eps: float):
+        x16 = (x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)).contiguous()
+        d16 = (delta if delta.dtype == torch.bfloat16 else delta.to(torch.bfloat16)).contiguous()
+        w32 = weight.detach().float().contiguous()
+        y, rstd, summed = ext().rmsnorm_fwd(x16, d16, w32, eps)
+        ctx.save_for_backward(summed, w32, rstd)
+        ctx.dtypes = (x.dtype, delta.dtype, weight.dtype)
+        return y, summed
+
+    @staticmethod
+    def backward(ctx, dy: Tensor, dsum: Tensor | None):
+        summed, w32, rstd = ctx.saved_tensors
+        dy16 = (dy if dy.dtype == torch.bfloat16 else dy.to(torch.bfloat16)).contiguous()
+        if dsum is not None:
+            dsum = (dsum if dsum.dtype == torch.bfloat16 else dsum.to(torch.bfloat16)).contiguous()
+        ds, dw = ext().rmsnorm_bwd(dy16, summed, w32, rstd, dsum)
+        return ds.to(ctx.dtypes[0]), ds.to(ctx.dtypes[1]), dw.to(ctx.dtypes[2]), None
+
+
+def add_rms_norm(x: Tensor, delta: Tensor | None, weight: Tensor,
+                 eps: float = 1e-5) -> tuple[Tensor, Tensor]:
+    """Return ``(rms_norm(x + delta), x + delta)``; ``delta=None`` means no residual to add."""
+    if delta is None:
+        return rms_norm(x, weight, eps), x
+    if fast_path(x) and x.shape[-1] % 8 == 0 and x.shape == delta.shape:
+        return _AddRMSNormFn.apply(x, delta, weight, eps)
+    summed = x + delta.to(x.dtype)
+    return rms_norm(summed, weight, eps), summed
 
 
 def rms_norm(x: Tensor, weight: Tensor, eps: float = 1e-5) -> Tensor:

@@ -254,3 +254,25 @@ def test_grouped_moe_matches_reference_dispatch():
         got = moe._dispatch_grouped(flat, idx, wts)
     ref = moe._dispatch_reference(flat.float(), idx, wts.float())
     assert rel_err(got, ref) < 3e-2
+
+
+def test_add_rms_norm_fused_residual():
+    from ohara_b200 import ops
+    from ohara_b200.modules.norm import rms_norm_reference
+
+    x, delta = bf(500, 768).requires_grad_(), bf(500, 768).requires_grad_()
+    w = (1 + 0.1 * torch.randn(768, device="cuda")).requires_grad_()
+    y, s = ops.add_rms_norm(x, delta, w, 1e-5)
+    dy, ds = bf(500, 768), bf(500, 768)
+    torch.autograd.backward([y, s], [dy, ds])
+    xr, dr = x.detach().float().requires_grad_(), delta.detach().float().requires_grad_()
+    wr = w.detach().clone().requires_grad_()
+    sr = (xr + dr).bfloat16().float() + 0 * (xr + dr)  # value rounded like the kernel, grads intact
+    sr = xr + dr
+    yr = rms_norm_reference(sr, wr, 1e-5)
+    torch.autograd.backward([yr, sr], [dy.float(), ds.float()])
+    assert rel_err(s, sr) < 1e-2
+    assert rel_err(y, yr) < 2e-2
+    assert rel_err(x.grad, xr.grad) < 2e-2
+    assert torch.equal(x.grad, delta.grad)
+    assert rel_err(w.grad, wr.grad) < 2e-2
