@@ -541,3 +541,155 @@ void flash_attn_bwd(const void* q, const void* k, const void* v, const void* d_o
 }
 
 }  // namespace ob
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant (see noalloc.h for who needs it and the contract).
+// ------------------------------------------------------------------------------------------------
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "api.h"
+#include "noalloc.h"
+
+namespace ob {
+namespace {
+
+constexpr size_t kNoallocDqBytes = (size_t)OB_NOALLOC_MAX_DQ_ELEMS * sizeof(float);
+constexpr size_t kNoallocDeltaBytes = (size_t)OB_NOALLOC_MAX_ROWS * sizeof(float);
+
+// Scratch that the regular entry point would allocate: [fp32 dQ accumulators | fp32 delta].
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoallocDqBytes + kNoallocDeltaBytes];
+
+std::mutex g_noalloc_mutex;
+unsigned char* g_noalloc_base[64] = {nullptr};  // device address of the array, per device
+bool g_noalloc_configured[64][2] = {{false}};   // kernel attribute set, per device and head_dim
+
+int noalloc_fail(int code, const char* message, char* err, size_t err_len) {
+  if (err != nullptr && err_len > 0) {
+    std::strncpy(err, message, err_len - 1);
+    err[err_len - 1] = '\0';
+  }
+  return code;
+}
+
+template <int D>
+cudaError_t noalloc_launch(const void* q, const void* k, const void* v, const void* d_o, float* dq32,
+                           void* dk, void* dv, const float* lse, const float* delta, int B, int T,
+                           int S, int H, int Hk, bool causal, float scale, int* status,
+                           bool configure, cudaStream_t stream) {
+  using L = BwdSmem<D>;
+  CUtensorMap tQ, tK, tV, tdO, tdQ, tdK, tdV;
+  auto make4 = [&](CUtensorMap* tm, const void* base, TmapDtype dt, int heads, int len,
+                   uint32_t box_inner, uint32_t box_rows, TmapSwizzle sw) {
+    const uint64_t esz = dt == TmapDtype::F32 ? 4 : 2;
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)heads, (uint64_t)len, (uint64_t)B};
+    uint64_t st[3] = {(uint64_t)D * esz, (uint64_t)heads * D * esz, (uint64_t)len * heads * D * esz};
+    uint32_t box[4] = {box_inner, 1, box_rows, 1};
+    make_tmap(tm, base, dt, 4, dims, st, box, sw);
+  };
+  make4(&tQ, q, TmapDtype::BF16, H, T, 64, kQRows, TmapSwizzle::B128);
+  make4(&tK, k, TmapDtype::BF16, Hk, S, 64, kKeys, TmapSwizzle::B128);
+  make4(&tV, v, TmapDtype::BF16, Hk, S, 64, kKeys, TmapSwizzle::B128);
+  make4(&tdO, d_o, TmapDtype::BF16, H, T, 64, kQRows, TmapSwizzle::B128);
+  make4(&tdQ, dq32, TmapDtype::F32, H, T, D, kQRows, TmapSwizzle::NONE);
+  make4(&tdK, dk, TmapDtype::BF16, Hk, S, 64, 32, TmapSwizzle::B128);
+  make4(&tdV, dv, TmapDtype::BF16, Hk, S, 64, 32, TmapSwizzle::B128);
+  BwdParams p;
+  p.B = B;
+  p.T = T;
+  p.S = S;
+  p.H = H;
+  p.Hk = Hk;
+  p.causal = causal ? 1 : 0;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  p.lse = lse;
+  p.delta = delta;
+  p.status = status;
+  auto kernel = flash_bwd_kernel<D>;
+  if (configure) {
+    cudaError_t rc =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (rc != cudaSuccess) return rc;
+  }
+  const int k_tiles = (S + kKeys - 1) / kKeys;
+  const long long grid = (long long)k_tiles * B * Hk;
+  kernel<<<(unsigned)grid, kThreads, L::kTotal, stream>>>(tQ, tK, tV, tdO, tdQ, tdK, tdV, p);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace
+}  // namespace ob
+
+extern "C" int ob_flash_attn_bwd_noalloc(const void* q, const void* k, const void* v,
+                                         const void* out, const void* dout, const float* lse,
+                                         void* dq, void* dk, void* dv, int B, int T, int S, int H,
+                                         int Hk, int D, int causal, float scale, void* stream_ptr,
+                                         int* status, char* err, size_t err_len) {
+  using namespace ob;
+  char msg[256];
+  if (!q || !k || !v || !out || !dout || !lse || !dq || !dk || !dv)
+    return noalloc_fail(-1, "ob_flash_attn_bwd_noalloc: null tensor pointer", err, err_len);
+  if (B < 1 || T < 1 || S < 1 || H < 1 || Hk < 1 || H % Hk != 0 || (D != 64 && D != 128))
+    return noalloc_fail(-1, "ob_flash_attn_bwd_noalloc: bad shape (need D in {64,128}, H % Hk == 0)",
+                        err, err_len);
+  if (causal && S < T)
+    return noalloc_fail(-1, "ob_flash_attn_bwd_noalloc: causal attention needs S >= T", err, err_len);
+  const long long dq_elems = (long long)B * T * H * D;
+  const long long rows = (long long)B * H * T;
+  if (dq_elems > OB_NOALLOC_MAX_DQ_ELEMS || rows > OB_NOALLOC_MAX_ROWS) {
+    std::snprintf(msg, sizeof(msg),
+                  "ob_flash_attn_bwd_noalloc: problem needs %lld dQ elements and %lld rows but the "
+                  "built-in scratch holds at most %lld and %lld; use the allocating entry point",
+                  dq_elems, rows, (long long)OB_NOALLOC_MAX_DQ_ELEMS, (long long)OB_NOALLOC_MAX_ROWS);
+    return noalloc_fail(-2, msg, err, err_len);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  int dev = 0;
+  cudaError_t rc = cudaGetDevice(&dev);
+  if (rc != cudaSuccess || dev < 0 || dev >= 64)
+    return noalloc_fail(-3, "ob_flash_attn_bwd_noalloc: cannot query the current device", err, err_len);
+
+  // One-time set-up for this device: resolve the device address of the static array.
+  unsigned char* base = nullptr;
+  bool configure = false;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_base[dev] == nullptr) {
+      void* ptr = nullptr;
+      rc = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+      if (rc != cudaSuccess || ptr == nullptr) {
+        std::snprintf(msg, sizeof(msg), "ob_flash_attn_bwd_noalloc: cudaGetSymbolAddress failed: %s",
+                      cudaGetErrorString(rc));
+        return noalloc_fail(-3, msg, err, err_len);
+      }
+      g_noalloc_base[dev] = static_cast<unsigned char*>(ptr);
+    }
+    base = g_noalloc_base[dev];
+    const int slot = D == 128 ? 1 : 0;
+    configure = !g_noalloc_configured[dev][slot];
+    g_noalloc_configured[dev][slot] = true;
+  }
+  float* dq32 = reinterpret_cast<float*>(base);
+  float* delta = reinterpret_cast<float*>(base + kNoallocDqBytes);
+
+  try {
+    // The accumulators keep whatever the previous call left: clear what this call will add into.
+    rc = cudaMemsetAsync(dq32, 0, (size_t)dq_elems * sizeof(float), stream);
+    if (rc != cudaSuccess) throw std::runtime_error(cudaGetErrorString(rc));
+    attn_delta(out, dout, delta, B, T, H, D, (int64_t)H * D, (int64_t)T * H * D, stream);
+    rc = (D == 128) ? noalloc_launch<128>(q, k, v, dout, dq32, dk, dv, lse, delta, B, T, S, H, Hk,
+                                          causal != 0, scale, status, configure, stream)
+                    : noalloc_launch<64>(q, k, v, dout, dq32, dk, dv, lse, delta, B, T, S, H, Hk,
+                                         causal != 0, scale, status, configure, stream);
+    if (rc != cudaSuccess) throw std::runtime_error(cudaGetErrorString(rc));
+    cast_f32_bf16(dq32, dq, dq_elems, stream);
+  } catch (const std::exception& e) {
+    std::snprintf(msg, sizeof(msg), "ob_flash_attn_bwd_noalloc: %s", e.what());
+    return noalloc_fail(-3, msg, err, err_len);
+  }
+  return 0;
+}
