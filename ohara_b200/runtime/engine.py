@@ -241,7 +241,11 @@ class OharaEngine:
     def prepare_optimizers(self, *optimizers: Optimizer):
         self.launch()
         module = getattr(self, "_module", None)
-        return tuple(self._strategy.setup_optimizer(opt, module) for opt in optimizers)
+        wrapped = tuple(self._strategy.setup_optimizer(opt, module) for opt in optimizers)
+        for opt in wrapped:
+            if callable(getattr(opt, "sync_master_weights", None)):
+                self._sharded_optimizer = opt
+        return wrapped
 
     # Fabric-style aliases
     def setup(self, module: torch.nn.Module, *optimizers: Optimizer):
