@@ -54,6 +54,19 @@ void flash_attn_bwd(const void* q, const void* k, const void* v, const void* d_o
                     int H, int Hk, int D, bool causal, float scale, const int64_t* strides,
                     cudaStream_t stream);
 
+// peer.cu
+void* peer_alloc(size_t bytes, char handle_out[64]);
+void* peer_open(const char handle_in[64]);
+void peer_close(void* ptr);
+void peer_free(void* ptr);
+void peer_barrier_launch(const int64_t* pads, int rank, int world, uint32_t epoch,
+                         uint64_t limit_ns, cudaStream_t stream);
+void peer_reduce_scatter_mean(const int64_t* grads, const int64_t* pads, float* out, int64_t region,
+                              int rank, int world, uint32_t epoch, uint64_t limit_ns,
+                              cudaStream_t stream);
+void peer_all_gather(const int64_t* weights, const int64_t* pads, int64_t region_bytes, int rank,
+                     int world, uint32_t epoch, uint64_t limit_ns, cudaStream_t stream);
+
 // cross_entropy.cu
 void cross_entropy_rows(void* logits, const int64_t* targets, float* row_loss, float* row_lse,
                         int* row_correct, const float* scale_ptr, int64_t rows, int vocab,

@@ -363,6 +363,53 @@ std::vector<Tensor> flash_attn_bwd(const Tensor& dout_in, const Tensor& q_in, co
   return {dq32.to(torch::kBFloat16), dk, dv};
 }
 
+// ---- peer memory ---------------------------------------------------------------------------------
+// Allocates `bytes` of device memory outside the caching allocator and returns (tensor view as
+// uint8, IPC handle bytes). The memory lives until peer_free(tensor.data_ptr()).
+std::pair<Tensor, py::bytes> peer_alloc(int64_t bytes, int64_t device_index) {
+  const c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_index));
+  char handle[64];
+  void* ptr = ob::peer_alloc((size_t)bytes, handle);
+  auto options = torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, device_index);
+  Tensor view = torch::from_blob(ptr, {bytes}, options);
+  return {view, py::bytes(handle, 64)};
+}
+
+// Opens a peer's handle; returns a uint8 view of the peer's memory addressable from this device.
+Tensor peer_open(const std::string& handle, int64_t bytes, int64_t device_index) {
+  TORCH_CHECK(handle.size() == 64, "IPC handle must be 64 bytes");
+  const c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_index));
+  void* ptr = ob::peer_open(handle.data());
+  auto options = torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, device_index);
+  return torch::from_blob(ptr, {bytes}, options);
+}
+
+void peer_close(int64_t ptr) { ob::peer_close(reinterpret_cast<void*>(ptr)); }
+void peer_free(int64_t ptr) { ob::peer_free(reinterpret_cast<void*>(ptr)); }
+
+void peer_barrier(const std::vector<int64_t>& pads, int64_t rank, int64_t epoch, double limit_s) {
+  ob::peer_barrier_launch(pads.data(), (int)rank, (int)pads.size(), (uint32_t)epoch,
+                          (uint64_t)(limit_s * 1e9), current_stream());
+}
+
+void peer_reduce_scatter_mean(const std::vector<int64_t>& grads, const std::vector<int64_t>& pads,
+                              Tensor& out, int64_t region, int64_t rank, int64_t epoch,
+                              double limit_s) {
+  check_f32(out, "out");
+  TORCH_CHECK(out.is_contiguous() && out.numel() >= region && grads.size() == pads.size());
+  const c10::cuda::CUDAGuard guard(out.device());
+  ob::peer_reduce_scatter_mean(grads.data(), pads.data(), out.data_ptr<float>(), region, (int)rank,
+                               (int)grads.size(), (uint32_t)epoch, (uint64_t)(limit_s * 1e9),
+                               current_stream());
+}
+
+void peer_all_gather(const std::vector<int64_t>& weights, const std::vector<int64_t>& pads,
+                     int64_t region_bytes, int64_t rank, int64_t epoch, double limit_s) {
+  TORCH_CHECK(weights.size() == pads.size());
+  ob::peer_all_gather(weights.data(), pads.data(), region_bytes, (int)rank, (int)weights.size(),
+                      (uint32_t)epoch, (uint64_t)(limit_s * 1e9), current_stream());
+}
+
 std::vector<int64_t> status(bool clear) {
   int out[4];
   ob::status_read(out, clear);
@@ -391,6 +438,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("scale_by_scalar", &scale_by_scalar);
   m.def("flash_attn_fwd", &flash_attn_fwd);
   m.def("flash_attn_bwd", &flash_attn_bwd);
+  m.def("peer_alloc", &peer_alloc);
+  m.def("peer_open", &peer_open);
+  m.def("peer_close", &peer_close);
+  m.def("peer_free", &peer_free);
+  m.def("peer_barrier", &peer_barrier);
+  m.def("peer_reduce_scatter_mean", &peer_reduce_scatter_mean);
+  m.def("peer_all_gather", &peer_all_gather);
   m.def("status", &status);
   m.def("launch_count", []() { return (int64_t)ob::launch_count(); });
 }

@@ -1,0 +1,114 @@
+"""Peer-memory buffers and collectives for GPUs on one NVLink / NVSwitch node.
+
+``SymmetricBuffer`` is one logical buffer that exists on every rank of a process group: each rank
+allocates its copy outside the caching allocator, exports a CUDA IPC handle, and opens the handles
+of its peers (exchanged through the c10d object collective, i.e. the control plane). Kernels then
+take the table of per-rank base addresses and move data with plain loads and stores over NVLink.
+
+``PeerBuffers`` applies this to the sharded optimizer: the flat gradient and weight buffers become
+symmetric, and the per-step reduce-scatter (bf16 -> fp32 sum, mean) and all-gather run as the
+kernels in ``csrc/peer.cu`` instead of c10d collectives. Cross-rank ordering is the flag barrier
+executed at the start of each kernel; its wait is bounded (``wait_limit_s``) and a timeout
+surfaces through ``ops.check_status()`` rather than hanging the device.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ohara_b200.ops._ext import ext
+
+
+class SymmetricBuffer:
+    """``nbytes`` of device memory per rank, addressable from every rank of ``group``."""
+
+    def __init__(self, nbytes: int, group=None, device: torch.device | None = None) -> None:
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.nbytes = int(nbytes)
+        index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.local, handle = ext().peer_alloc(self.nbytes, index)
+        handles: list[bytes | None] = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        self.views: list[torch.Tensor] = []
+        for r, peer_handle in enumerate(handles):
+            if r == self.rank:
+                self.views.append(self.local)
+            else:
+                self.views.append(ext().peer_open(peer_handle, self.nbytes, index))
+        self.pointers = [v.data_ptr() for v in self.views]
+
+    def typed(self, dtype: torch.dtype, rank: int | None = None) -> torch.Tensor:
+        """This rank's (or ``rank``'s) copy viewed as a 1-D tensor of ``dtype``."""
+        view = self.local if rank is None else self.views[rank]
+        return view.view(dtype)
+
+
+class PeerRuntime:
+    """Signal pads + a monotonically increasing barrier epoch shared by all collectives of a
+    group. Every rank must issue the same sequence of collectives."""
+
+    def __init__(self, group=None, wait_limit_s: float = 10.0) -> None:
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.wait_limit_s = wait_limit_s
+        self.pads = SymmetricBuffer(4096, group)
+        self.epoch = 0
+        # Everyone has opened everyone's pad before the first kernel may signal.
+        dist.barrier(group=group)
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def barrier(self) -> None:
+        ext().peer_barrier(self.pads.pointers, self.rank, self.next_epoch(), self.wait_limit_s)
+
+
+class PeerBuffers:
+    """Symmetric gradient / weight buffers of a :class:`ShardedOptimizer` and their collectives."""
+
+    def __init__(self, optimizer, group) -> None:
+        self.runtime = PeerRuntime(group)
+        self.region = optimizer.region
+        self.world = optimizer.world
+        self.rank = optimizer.rank
+        elements = optimizer.region * optimizer.world
+        itemsize = torch.empty((), dtype=optimizer.wire_dtype).element_size()
+        self.grads = SymmetricBuffer(elements * itemsize, group)
+        self.weights = SymmetricBuffer(elements * itemsize, group)
+        self.itemsize = itemsize
+        grad_flat = self.grads.typed(optimizer.wire_dtype)
+        weight_flat = self.weights.typed(optimizer.wire_dtype)
+        weight_flat.copy_(optimizer.weight_flat)
+        optimizer.grad_flat = grad_flat
+        optimizer.weight_flat = weight_flat
+        optimizer._bind_shadows()
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    @classmethod
+    def create(cls, optimizer, group):
+        if optimizer.wire_dtype != torch.bfloat16:
+            return None
+        if optimizer.world > 16:
+            return None
+        return cls(optimizer, group)
+
+    def reduce_scatter_mean(self, grad_flat: torch.Tensor, out: torch.Tensor) -> None:
+        assert grad_flat.data_ptr() == self.grads.local.data_ptr()
+        ext().peer_reduce_scatter_mean(
+            self.grads.pointers, self.runtime.pads.pointers, out, self.region, self.rank,
+            self.runtime.next_epoch(), self.runtime.wait_limit_s,
+        )
+
+    def all_gather(self, weight_flat: torch.Tensor) -> None:
+        assert weight_flat.data_ptr() == self.weights.local.data_ptr()
+        ext().peer_all_gather(
+            self.weights.pointers, self.runtime.pads.pointers, self.region * self.itemsize,
+            self.rank, self.runtime.next_epoch(), self.runtime.wait_limit_s,
+        )
