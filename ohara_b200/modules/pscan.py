@@ -1,0 +1,68 @@
+"""Parallel scan for first-order linear recurrences ``h[t] = a[t] * h[t-1] + x[t]`` (``h[-1] = 0``).
+
+Used by Mamba's selective scan and the RG-LRU. The reference carries a Blelloch up/down-sweep
+(ohara/modules/pscan.py:63-258); this implementation uses the Hillis-Steele doubling form, which
+needs ``ceil(log2 L)`` passes of whole-tensor operations, no padding to a power of two and no
+in-place tricks, with an explicit backward that is itself a (reversed) scan:
+
+    dx[t] = dh[t] + a[t+1] * dx[t+1]        da[t] = dx[t] * h[t-1]
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+
+def _scan_forward(a: Tensor, x: Tensor) -> Tensor:
+    """Inclusive scan along dim 1 of ``(B, L, ...)`` tensors."""
+    length = a.shape[1]
+    coeff, value = a, x
+    shift = 1
+    while shift < length:
+        # Compose element t with element t - shift: (c2, v2) o (c1, v1) = (c1*c2, c2*v1 + v2).
+        prev_value = torch.zeros_like(value)
+        prev_value[:, shift:] = value[:, :-shift]
+        prev_coeff = torch.ones_like(coeff)
+        prev_coeff[:, shift:] = coeff[:, :-shift]
+        value = coeff * prev_value + value
+        coeff = coeff * prev_coeff
+        shift *= 2
+    return value
+
+
+class PScan(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a: Tensor, x: Tensor) -> Tensor:
+        h = _scan_forward(a, x)
+        ctx.save_for_backward(a, h)
+        return h
+
+    @staticmethod
+    def backward(ctx, grad_h: Tensor):
+        a, h = ctx.saved_tensors
+        # Reverse-time recurrence with the coefficient of the *next* step.
+        a_next = torch.zeros_like(a)
+        a_next[:, :-1] = a[:, 1:]
+        dx = _scan_forward(a_next.flip(1), grad_h.flip(1)).flip(1)
+        h_prev = torch.zeros_like(h)
+        h_prev[:, 1:] = h[:, :-1]
+        return dx * h_prev, dx
+
+
+def pscan(A: Tensor, X: Tensor) -> Tensor:
+    """``H`` with ``H[:, t] = A[:, t] * H[:, t-1] + X[:, t]`` for ``(B, L, D, N)`` (or any
+    ``(B, L, ...)``) inputs of equal shape."""
+    if A.shape != X.shape:
+        raise ValueError("pscan expects coefficient and input tensors of the same shape")
+    return PScan.apply(A, X)
+
+
+def sequential_scan(A: Tensor, X: Tensor) -> Tensor:
+    """Step-by-step oracle for :func:`pscan`."""
+    h = torch.zeros_like(X[:, 0])
+    out = []
+    for t in range(X.shape[1]):
+        h = A[:, t] * h + X[:, t]
+        out.append(h)
+    return torch.stack(out, dim=1)
