@@ -204,8 +204,9 @@ def evaluate_example(idx, model, tokenizer, data, device, task_meta) -> bool:
         cropped = []
         for row, start, end in zip(tokens, starts, ends):
             cut = max(len(row) - limit, 0)
-            if cut and (start - cut < 0 or end - cut < 0):
-                return False  # the answer span itself was cropped away
+            if cut and (start - cut < 1 or end - cut < 1):
+                # the answer span, or the token that predicts its first token, was cropped away
+                return False
             cropped.append((row[cut:], start - cut, end - cut))
         tokens, starts, ends = (list(x) for x in zip(*cropped))
 

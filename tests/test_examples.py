@@ -1,0 +1,135 @@
+"""The example programs: finetuning checkpoint loader, safetensors export, status dashboard and a
+short end-to-end pretraining run. (Reference suite for the loader: tests/test_train_sft.py:48-124.)"""
+
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+import threading
+import urllib.request
+from pathlib import Path
+
+import pytest
+import torch
+
+from helpers import chat_tokenizer, tiny_llama
+from test_data import EXAMPLES, load_example
+
+
+@pytest.fixture(scope="module")
+def sft():
+    return load_example("train_sft")
+
+
+def save(model, path, prefix=""):
+    torch.save({"model": {prefix + k: v for k, v in model.state_dict().items()}, "idx": 11}, path)
+    return path
+
+
+def test_loader_rebuilds_the_base_and_grows_the_vocabulary(sft, tmp_path):
+    tok = chat_tokenizer()
+    base = tiny_llama(len(tok) - 4, context=32, num_key_value_heads=1, weight_tying=False)
+    path = save(base, tmp_path / "base.pt")
+    model, config, old_vocab = sft.load_pretrained(path, len(tok), None)
+    assert old_vocab == len(tok) - 4 and model.token_emb.weight.shape[0] == len(tok)
+    assert config.num_key_value_heads == 1 and config.max_sequence_length == 32
+    assert torch.equal(model.token_emb.weight[:old_vocab], base.token_emb.weight)
+    assert torch.equal(model.layers[1].ff.down.weight, base.layers[1].ff.down.weight)
+    wider, _, _ = sft.load_pretrained(save(tiny_llama(len(tok) + 16), tmp_path / "w.pt"), len(tok), None)
+    assert wider.token_emb.weight.shape[0] == len(tok) + 16, "spare padded rows are kept"
+
+
+def test_loader_keeps_tying_and_handles_context_and_prefixes(sft, tmp_path):
+    tok = chat_tokenizer()
+    tied = save(tiny_llama(len(tok) - 2, context=32, weight_tying=True), tmp_path / "tied.pt")
+    model, _, _ = sft.load_pretrained(tied, len(tok), 16)
+    assert model.vocab_proj.weight is model.token_emb.weight
+    assert model.config.max_sequence_length == 16
+    assert model(torch.randint(0, len(tok), (1, 16))).shape == (1, 16, len(tok))
+    with pytest.raises(ValueError, match="exceeds the pretrained context"):
+        sft.load_pretrained(tied, len(tok), 64)
+    with pytest.raises(FileNotFoundError):
+        sft.load_pretrained(tmp_path / "absent.pt", len(tok), None)
+    wrapped = save(tiny_llama(len(tok)), tmp_path / "wrapped.pt", prefix="_orig_mod.module.")
+    assert sft.load_pretrained(wrapped, len(tok), None)[1].vocab_size == len(tok)
+
+
+def test_safetensors_export_round_trips(tmp_path):
+    from safetensors.torch import load_file
+
+    export = load_example("export_safetensors")
+    model = tiny_llama(48, weight_tying=True, moe_num_experts=4, moe_experts_per_tok=2, moe_grouped=True)
+    path = save(model, tmp_path / "moe.pt")
+    summary = export.export(path, tmp_path / "out", moe_experts_per_tok=2)
+    config = json.loads((tmp_path / "out" / "config.json").read_text())
+    assert config["moe_num_experts"] == 4 and config["moe_grouped"] and config["iteration"] == 11
+    tensors = load_file(tmp_path / "out" / "model.safetensors")
+    assert summary["tensors"] == len(tensors)
+    assert not any(name.endswith(export.DERIVED_BUFFERS) for name in tensors)
+    assert torch.equal(tensors["token_emb.weight"], model.token_emb.weight)
+    kept = export.export(path, tmp_path / "full", keep_derived_buffers=True)
+    assert kept["tensors"] > summary["tensors"]
+
+
+def test_status_dashboard_reads_a_multi_stage_log(tmp_path):
+    status = load_example("train_status")
+    log = tmp_path / "speedrun.log"
+    log.write_text(
+        "[3/4] pretraining -> ckpt/base.pt\n"
+        " budget: 1,000,000 tokens over 40 iters, batch 1024 tokens (accum 1)\n"
+        "device=cuda:0 precision=bf16_mixed params=1,234,567 tokens/step/rank=1,024\n"
+        + "".join(f"iter: {i} | loss: {5 - i * 0.1:.4f} | lr: 1.0e-02 | time: 0.5000s | "
+                  f"tok/s: 2,048.00 | mfu: 41.20% | eta: {(40 - i) * 0.5 / 60:.1f}m\n" for i in range(1, 11))
+        + "iter: 10 | val_loss: 4.1000 | val_ppl: 60.3 | val_bits/token: 5.9 | val_acc: 0.2100 | "
+          "val_bpb: 1.3100 | lr: 1.0e-02\n")
+    state = status.parse_log(log)
+    assert state["stage"].startswith("pretraining") and state["total_iters"] == 40
+    assert state["iter"] == 10 and state["percent"] == 25.0 and state["params"] == 1_234_567
+    assert state["median_step_seconds"] == 0.5 and state["remaining_minutes"] == 0.2
+    assert state["tokens_per_sec"] == 2048 and state["mfu"] == 41.2 and len(state["history"]) == 10
+    assert state["val"] == [{"iter": 10, "loss": 4.1, "acc": 0.21, "bpb": 1.31}]
+    with open(log, "a") as handle:
+        handle.write("[4/4] supervised finetuning -> ckpt/sft.pt\nbefore SFT: val_loss=4.0\n"
+                     "iter: 1 | loss: 3.0000 | lr: 1.0e-02 | time: 0.2000s\nafter SFT: val_loss=2.0\n")
+    state = status.parse_log(log, total_override=4)
+    assert state["stage"].startswith("supervised") and state["finished"] and state["percent"] == 100.0
+    assert len(state["history"]) == 1
+    assert status.parse_log(tmp_path / "absent.log")["error"]
+
+    server = status.create_server(log, "127.0.0.1", 0)
+    thread = threading.Thread(target=server.serve_forever, daemon=True)
+    thread.start()
+    try:
+        base = f"http://127.0.0.1:{server.server_address[1]}"
+        with urllib.request.urlopen(base + "/api/status", timeout=10) as reply:
+            assert json.loads(reply.read())["finished"] is True
+        with urllib.request.urlopen(base + "/", timeout=10) as reply:
+            assert b"ohara_b200" in reply.read()
+    finally:
+        server.shutdown()
+        server.server_close()
+        thread.join(timeout=5)
+
+
+def test_pretraining_example_trains_saves_and_resumes(tmp_path):
+    checkpoint, result = tmp_path / "ckpt" / "model.pt", tmp_path / "result.json"
+    command = [sys.executable, str(EXAMPLES / "train_llama_engine.py"), "--synthetic",
+               "--synthetic-vocab", "256", "--seq-len", "32", "--hidden-size", "32",
+               "--intermediate-size", "64", "--num-layers", "2", "--num-heads", "2",
+               "--batch-size", "2", "--grad-accum-steps", "2", "--warmup-iters", "1",
+               "--eval-every", "2", "--eval-batches", "1", "--save-every", "2", "--logger", "none",
+               "--precision", "fp32", "--no-weight-tying", "--checkpoint-path", str(checkpoint),
+               "--result-json", str(result)]
+    first = subprocess.run(command + ["--max-iters", "2"], capture_output=True, text=True, timeout=300)
+    assert first.returncode == 0, first.stderr[-2000:]
+    assert checkpoint.exists() and "final val_loss=" in first.stdout
+    report = json.loads(result.read_text())
+    assert report["num_iterations"] == 2 and report["total_batch_size"] == 2 * 32 * 2
+    assert report["params_total"] == report["params_effective"] + report["params_token_embeddings"] \
+        + report["params_norms_and_scalars"]
+    second = subprocess.run(command + ["--max-iters", "4", "--resume"], capture_output=True,
+                            text=True, timeout=300)
+    assert second.returncode == 0, second.stderr[-2000:]
+    assert "resumed checkpoint" in second.stdout and "iter: 3 |" in second.stdout
+    assert "iter: 1 |" not in second.stdout
