@@ -55,6 +55,18 @@ def sample_next_token(logits: torch.Tensor, config: SamplingConfig,
     dropped when the mass *before* it already exceeds ``top_p`` (so the most likely token always
     survives) → renormalise → multinomial.
     """
+    if logits.is_cuda:
+        # One fused kernel per step (mask, top-k, softmax, top-p, draw) instead of sort + cumsum +
+        # multinomial; the draw uses one uniform number per row from `generator`.
+        from ohara_b200.ops.decode import sample
+
+        last = logits[:, -1]
+        uniforms = None
+        if config.temperature > 0:
+            uniforms = torch.rand(last.size(0), device=last.device, dtype=torch.float32,
+                                  generator=generator)
+        return sample(last, temperature=config.temperature, top_k=config.top_k,
+                      top_p=config.top_p, uniforms=uniforms)
     last = logits[:, -1].float()
     if config.temperature == 0:
         return last.argmax(dim=-1, keepdim=True)
@@ -279,10 +291,17 @@ class ChatEngine:
 
     @torch.inference_mode()
     def generate_batch(self, prompt_ids: torch.Tensor, config: SamplingConfig | None = None, *,
-                       seed: int | None = None, stop_on_end: bool = False) -> torch.Tensor:
+                       seed: int | None = None, stop_on_end: bool = False,
+                       cuda_graph: bool = True) -> torch.Tensor:
         """Decode ``max_new_tokens`` tokens for a ``(batch, prompt_len)`` tensor of prompts of
-        equal length. Returns ``(batch, new_tokens)`` ids. Nothing is copied to the host inside
-        the loop unless ``stop_on_end`` asks for early exit once every row has finished."""
+        equal length. Returns ``(batch, new_tokens)`` ids.
+
+        On CUDA (bf16 model, no early stop) the prompt is prefilled once and every further step —
+        model forward, sampling, writing the token back as the next input, advancing the position —
+        runs without the host: positions and the step counter live on the device and the step is
+        replayed from a CUDA graph (``cuda_graph=False`` issues the same kernels eagerly). Otherwise
+        a plain loop is used; it copies to the host only when ``stop_on_end`` asks for an early exit
+        once every row has finished."""
         config = config or SamplingConfig()
         prompt_ids = prompt_ids.to(self.device)
         batch, prompt_len = prompt_ids.shape
@@ -294,6 +313,8 @@ class ChatEngine:
         if seed is not None:
             generator = torch.Generator(device=self.device).manual_seed(seed)
         cache = self.model.build_kv_cache(batch_size=batch)
+        if self._device_loop_supported() and not stop_on_end:
+            return self._generate_on_device(prompt_ids, cache, config, steps, generator, cuda_graph)
         out = torch.empty(batch, steps, dtype=torch.long, device=self.device)
         finished = torch.zeros(batch, dtype=torch.bool, device=self.device)
         step_input, position = prompt_ids, 0
@@ -308,4 +329,58 @@ class ChatEngine:
                     finished |= step_input[:, 0] == self.eos_token_id
                 if bool(finished.all()):
                     return out[:, : step + 1]
+        return out
+
+    def _device_loop_supported(self) -> bool:
+        cfg = self.model.config
+        return (self.device.type == "cuda" and self.dtype == torch.bfloat16
+                and cfg.head_dim in (64, 128)
+                and cfg.num_attention_heads // cfg.kv_heads in (1, 2, 4, 8))
+
+    def _generate_on_device(self, prompt_ids, cache, config: SamplingConfig, steps: int,
+                            generator, cuda_graph: bool) -> torch.Tensor:
+        from ohara_b200.ops.decode import sample
+
+        batch, prompt_len = prompt_ids.shape
+        device = self.device
+        out = torch.empty(batch, steps, dtype=torch.long, device=device)
+        token = torch.empty(batch, 1, dtype=torch.long, device=device)
+        # [step, position of the token about to be fed, rows finished in the current step]
+        counters = torch.tensor([0, prompt_len - 1, 0], dtype=torch.int32, device=device)
+        position = counters[1:2]
+        uniforms = None
+        if config.temperature > 0:
+            uniforms = torch.rand(steps, batch, device=device, dtype=torch.float32,
+                                  generator=generator)
+        draw = dict(temperature=config.temperature, top_k=config.top_k, top_p=config.top_p,
+                    valid_vocab=self.tokenizer_vocab_size, uniforms=uniforms, out=out,
+                    next_input=token.view(-1), counters=counters)
+
+        logits = self.model(prompt_ids, cache, 0)
+        sample(logits[:, -1], **draw)  # writes column 0; position becomes prompt_len
+
+        def step() -> None:
+            step_logits = self.model(token, cache, position)
+            sample(step_logits[:, -1], **draw)
+
+        remaining = steps - 1
+        if remaining > 0 and cuda_graph and remaining > 2:
+            step()  # eager warm-up: lazy initialisation must not happen during capture
+            remaining -= 1
+            graph = torch.cuda.CUDAGraph()
+            try:
+                with torch.cuda.graph(graph):
+                    step()
+            except RuntimeError:
+                graph = None  # something in the step cannot be captured: fall back to eager
+            if graph is not None:
+                remaining -= 1  # capture does not run the step; the first replay does
+                graph.replay()
+                for _ in range(remaining):
+                    graph.replay()
+                remaining = 0
+        for _ in range(remaining):
+            step()
+        for layer_cache in cache:
+            layer_cache.set_length(prompt_len + steps - 1, batch)
         return out

@@ -73,4 +73,35 @@ void cross_entropy_rows(void* logits, const int64_t* targets, float* row_loss, f
                         int64_t pitch, int64_t ignore_index, bool write_grad, cudaStream_t stream);
 void scale_by_scalar(void* x, bool is_bf16, const float* scalar, int64_t n, cudaStream_t stream);
 
+// moe.cu
+void route_topk(const float* logits, const float* bias, int* indices, float* weights, float* alpha,
+                int* counts, int tokens, int experts, int k, bool sigmoid_gate, bool normalize,
+                bool want_alpha, cudaStream_t stream);
+void moe_plan(const int* indices, const int* counts, int* seg_start, int* k_offsets,
+              int* tile_expert, int* cursor, int* dest_row, int* row_pair, int64_t pairs,
+              int experts, int tile, int num_tiles, cudaStream_t stream);
+void moe_scatter_rows(const void* src, const int* dest_row, const float* scale,
+                      const int* row_pair, int64_t padded_rows, void* dst, int64_t pairs, int k,
+                      int d, cudaStream_t stream);
+void moe_gather_combine(const void* rows, const int* dest_row, const float* scale, const void* other,
+                        void* out, float* dot, int64_t tokens, int k, int d, cudaStream_t stream);
+void qb_quantile(const float* logits, const float* alpha, float* beta_sum, int tokens, int experts,
+                 int rank, cudaStream_t stream);
+
+// decode.cu
+void rope_append(const void* q, const void* k, const void* v, void* q_out, void* cache_k,
+                 void* cache_v, float* k_scale, float* k_min, float* v_scale, float* v_min,
+                 const float* cos_t, const float* sin_t, int B, int T, int H, int Hk, int D, int pos,
+                 const int* pos_dev, int cache_len, int table_len, bool int8, cudaStream_t stream);
+int decode_attention_splits(int B, int Hk, int len);
+void decode_attention(const void* q, const void* cache_k, const void* cache_v, const float* k_scale,
+                      const float* k_min, const float* v_scale, const float* v_min, void* out,
+                      float* partial, int B, int H, int Hk, int D, int cache_len, int len,
+                      const int* pos_dev, int splits, float scale, bool int8, cudaStream_t stream);
+void sample_tokens(const void* logits, bool logits_bf16, int64_t row_stride, int rows, int vocab,
+                   int valid_vocab, float temperature, int top_k, float top_p,
+                   const float* uniforms, int64_t* out_tokens, int64_t out_stride,
+                   int64_t* next_input, int* step_dev, int* pos_dev, unsigned int* done,
+                   float* workspace, cudaStream_t stream);
+
 }  // namespace ob

@@ -410,6 +410,263 @@ void peer_all_gather(const std::vector<int64_t>& weights, const std::vector<int6
                       (uint32_t)epoch, (uint64_t)(limit_s * 1e9), current_stream());
 }
 
+// -- mixture of experts ---------------------------------------------------------------------------
+void check_i32(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous(), name,
+              " must be a contiguous int32 CUDA tensor");
+}
+
+// logits (N, E) fp32 -> indices (N, k) int32, weights (N, k) fp32, alpha (N) fp32 (empty when not
+// requested), counts (E) int32 (accumulated into; the caller zeroes it).
+std::vector<Tensor> route_topk(const Tensor& logits, const c10::optional<Tensor>& bias, int64_t k,
+                               bool sigmoid_gate, bool normalize, bool want_alpha, Tensor& counts) {
+  check_f32(logits, "logits");
+  check_i32(counts, "counts");
+  TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous());
+  const c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t n = logits.size(0), e = logits.size(1);
+  TORCH_CHECK(counts.numel() == e, "counts must have one entry per expert");
+  const float* bias_ptr = nullptr;
+  if (bias.has_value()) {
+    check_f32(*bias, "bias");
+    TORCH_CHECK(bias->numel() == e && bias->is_contiguous());
+    bias_ptr = bias->data_ptr<float>();
+  }
+  Tensor indices = torch::empty({n, k}, logits.options().dtype(torch::kInt32));
+  Tensor weights = torch::empty({n, k}, logits.options());
+  Tensor alpha = torch::empty({want_alpha ? n : 0}, logits.options());
+  ob::route_topk(logits.data_ptr<float>(), bias_ptr, indices.data_ptr<int>(),
+                 weights.data_ptr<float>(), want_alpha ? alpha.data_ptr<float>() : nullptr,
+                 counts.data_ptr<int>(), (int)n, (int)e, (int)k, sigmoid_gate, normalize, want_alpha,
+                 current_stream());
+  return {indices, weights, alpha};
+}
+
+// indices (N, k) int32 + counts (E) -> dest_row (N*k), row_pair (padded_rows, -1 on padding rows),
+// tile_expert (padded_rows / tile), k_offsets (E + 1). padded_rows is a static upper bound.
+std::vector<Tensor> moe_plan(const Tensor& indices, const Tensor& counts, int64_t tile) {
+  check_i32(indices, "indices");
+  check_i32(counts, "counts");
+  const c10::cuda::CUDAGuard guard(indices.device());
+  const int64_t pairs = indices.numel(), experts = counts.numel();
+  const int64_t padded_rows = (pairs + experts * (tile - 1)) / tile * tile + tile;
+  const int64_t num_tiles = padded_rows / tile;
+  auto opts = indices.options();
+  Tensor dest_row = torch::empty({pairs}, opts);
+  Tensor row_pair = torch::full({padded_rows}, -1, opts);
+  Tensor tile_expert = torch::empty({num_tiles}, opts);
+  Tensor k_offsets = torch::empty({experts + 1}, opts);
+  Tensor scratch = torch::empty({2 * experts}, opts);  // segment starts, placement cursors
+  ob::moe_plan(indices.data_ptr<int>(), counts.data_ptr<int>(), scratch.data_ptr<int>(),
+               k_offsets.data_ptr<int>(), tile_expert.data_ptr<int>(),
+               scratch.data_ptr<int>() + experts, dest_row.data_ptr<int>(),
+               row_pair.data_ptr<int>(), pairs, (int)experts, (int)tile, (int)num_tiles,
+               current_stream());
+  return {dest_row, row_pair, tile_expert, k_offsets};
+}
+
+// dst[dest_row[j]] = scale[j] * src[j / k]. With `row_pair` (one entry per row of dst, negative for
+// rows no pair maps to) those rows are zeroed; without it they are left untouched.
+void moe_scatter_rows(const Tensor& src, const Tensor& dest_row, const c10::optional<Tensor>& scale,
+                      const c10::optional<Tensor>& row_pair, Tensor& dst, int64_t k) {
+  check_bf16(src, "src");
+  check_bf16(dst, "dst");
+  check_i32(dest_row, "dest_row");
+  TORCH_CHECK(src.is_contiguous() && dst.is_contiguous() && src.dim() == 2 && dst.dim() == 2);
+  TORCH_CHECK(src.size(1) == dst.size(1) && dest_row.numel() == src.size(0) * k);
+  const float* scale_ptr = nullptr;
+  if (scale.has_value()) {
+    check_f32(*scale, "scale");
+    TORCH_CHECK(scale->is_contiguous() && scale->numel() == dest_row.numel());
+    scale_ptr = scale->data_ptr<float>();
+  }
+  const int* pair_ptr = nullptr;
+  if (row_pair.has_value()) {
+    check_i32(*row_pair, "row_pair");
+    TORCH_CHECK(row_pair->numel() == dst.size(0), "row_pair must have one entry per row of dst");
+    pair_ptr = row_pair->data_ptr<int>();
+  }
+  const c10::cuda::CUDAGuard guard(src.device());
+  ob::moe_scatter_rows(src.data_ptr(), dest_row.data_ptr<int>(), scale_ptr, pair_ptr, dst.size(0),
+                       dst.data_ptr(), dest_row.numel(), (int)k, (int)src.size(1), current_stream());
+}
+
+// out[t] = sum_i scale[t, i] * rows[dest_row[t*k + i]]; with `other` (tokens, d) also returns
+// dot[t, i] = <rows[dest_row[t*k+i]], other[t]>.
+std::vector<Tensor> moe_gather_combine(const Tensor& rows, const Tensor& dest_row,
+                                       const c10::optional<Tensor>& scale,
+                                       const c10::optional<Tensor>& other, int64_t k,
+                                       bool want_out) {
+  check_bf16(rows, "rows");
+  check_i32(dest_row, "dest_row");
+  TORCH_CHECK(rows.is_contiguous() && rows.dim() == 2 && dest_row.numel() % k == 0);
+  const c10::cuda::CUDAGuard guard(rows.device());
+  const int64_t tokens = dest_row.numel() / k, d = rows.size(1);
+  const float* scale_ptr = nullptr;
+  if (scale.has_value()) {
+    check_f32(*scale, "scale");
+    TORCH_CHECK(scale->is_contiguous() && scale->numel() == dest_row.numel());
+    scale_ptr = scale->data_ptr<float>();
+  }
+  Tensor out, dot;
+  const void* other_ptr = nullptr;
+  if (other.has_value()) {
+    check_bf16(*other, "other");
+    TORCH_CHECK(other->is_contiguous() && other->numel() == tokens * d);
+    other_ptr = other->data_ptr();
+    dot = torch::empty({tokens, k}, rows.options().dtype(torch::kFloat32));
+  }
+  if (want_out) out = torch::empty({tokens, d}, rows.options());
+  ob::moe_gather_combine(rows.data_ptr(), dest_row.data_ptr<int>(), scale_ptr, other_ptr,
+                         want_out ? out.data_ptr() : nullptr,
+                         other.has_value() ? dot.data_ptr<float>() : nullptr, tokens, (int)k, (int)d,
+                         current_stream());
+  return {out, dot};
+}
+
+// beta_sum[e] += rank-th largest of (logits[:, e] - alpha)
+void qb_quantile(const Tensor& logits, const Tensor& alpha, Tensor& beta_sum, int64_t rank) {
+  check_f32(logits, "logits");
+  check_f32(alpha, "alpha");
+  check_f32(beta_sum, "beta_sum");
+  TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous() && alpha.is_contiguous());
+  TORCH_CHECK(alpha.numel() == logits.size(0) && beta_sum.numel() == logits.size(1));
+  const c10::cuda::CUDAGuard guard(logits.device());
+  ob::qb_quantile(logits.data_ptr<float>(), alpha.data_ptr<float>(), beta_sum.data_ptr<float>(),
+                  (int)logits.size(0), (int)logits.size(1), (int)rank, current_stream());
+}
+
+// -- serving --------------------------------------------------------------------------------------
+const int* optional_i32(const c10::optional<Tensor>& t, const char* name) {
+  if (!t.has_value()) return nullptr;
+  check_i32(*t, name);
+  return t->data_ptr<int>();
+}
+float* optional_f32(const c10::optional<Tensor>& t, const char* name) {
+  if (!t.has_value()) return nullptr;
+  check_f32(*t, name);
+  TORCH_CHECK(t->is_contiguous(), name, " must be contiguous");
+  return t->data_ptr<float>();
+}
+
+// q (B,T,H,D), k/v (B,T,Hk,D) bf16; cache_k/cache_v (Bmax, L, Hk, D) bf16 or int8 (then stats are
+// four fp32 tensors (Bmax, L, Hk, 1)); cos/sin (positions, D/2) fp32 full tables. Returns rotated q.
+Tensor rope_append(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& cache_k,
+                   Tensor& cache_v, const std::vector<Tensor>& stats, const Tensor& cos_t,
+                   const Tensor& sin_t, int64_t pos, const c10::optional<Tensor>& pos_dev) {
+  check_bf16(q, "q");
+  check_bf16(k, "k");
+  check_bf16(v, "v");
+  check_f32(cos_t, "cos");
+  check_f32(sin_t, "sin");
+  TORCH_CHECK(q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && q.dim() == 4);
+  TORCH_CHECK(cache_k.is_contiguous() && cache_v.is_contiguous() && cache_k.dim() == 4);
+  TORCH_CHECK(cos_t.is_contiguous() && sin_t.is_contiguous());
+  const bool int8 = cache_k.scalar_type() == torch::kInt8;
+  TORCH_CHECK(int8 || cache_k.scalar_type() == torch::kBFloat16, "cache must be bf16 or int8");
+  TORCH_CHECK(cache_v.scalar_type() == cache_k.scalar_type());
+  const int64_t B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hk = k.size(2);
+  TORCH_CHECK(k.sizes() == v.sizes() && k.size(0) == B && k.size(1) == T && k.size(3) == D);
+  TORCH_CHECK(cache_k.size(0) >= B && cache_k.size(2) == Hk && cache_k.size(3) == D,
+              "cache shape does not match the new keys");
+  TORCH_CHECK(cos_t.size(-1) == D / 2 && sin_t.sizes() == cos_t.sizes());
+  float* st[4] = {nullptr, nullptr, nullptr, nullptr};
+  if (int8) {
+    TORCH_CHECK(stats.size() == 4, "an int8 cache needs key/value scale and minimum tensors");
+    for (int i = 0; i < 4; ++i) {
+      check_f32(stats[i], "cache statistics");
+      TORCH_CHECK(stats[i].is_contiguous() && stats[i].numel() == cache_k.numel() / D);
+      st[i] = stats[i].data_ptr<float>();
+    }
+  }
+  const c10::cuda::CUDAGuard guard(q.device());
+  Tensor q_out = torch::empty_like(q);
+  ob::rope_append(q.data_ptr(), k.data_ptr(), v.data_ptr(), q_out.data_ptr(), cache_k.data_ptr(),
+                  cache_v.data_ptr(), st[0], st[1], st[2], st[3], cos_t.data_ptr<float>(),
+                  sin_t.data_ptr<float>(), (int)B, (int)T, (int)H, (int)Hk, (int)D, (int)pos,
+                  optional_i32(pos_dev, "pos_dev"), (int)cache_k.size(1), (int)cos_t.size(0), int8,
+                  current_stream());
+  return q_out;
+}
+
+// q (B, H, D) bf16 against the first `len` cache positions (or *pos_dev + 1). Returns (B, H, D).
+Tensor decode_attention(const Tensor& q, const Tensor& cache_k, const Tensor& cache_v,
+                        const std::vector<Tensor>& stats, int64_t len,
+                        const c10::optional<Tensor>& pos_dev, double scale, int64_t splits) {
+  check_bf16(q, "q");
+  TORCH_CHECK(q.is_contiguous() && q.dim() == 3 && cache_k.is_contiguous() && cache_v.is_contiguous());
+  const bool int8 = cache_k.scalar_type() == torch::kInt8;
+  TORCH_CHECK(int8 || cache_k.scalar_type() == torch::kBFloat16, "cache must be bf16 or int8");
+  const int64_t B = q.size(0), H = q.size(1), D = q.size(2), Hk = cache_k.size(2);
+  TORCH_CHECK(cache_k.size(0) >= B && cache_k.size(3) == D && cache_v.sizes() == cache_k.sizes());
+  TORCH_CHECK(pos_dev.has_value() || (len >= 1 && len <= cache_k.size(1)), "length out of range");
+  const float* st[4] = {nullptr, nullptr, nullptr, nullptr};
+  if (int8) {
+    TORCH_CHECK(stats.size() == 4, "an int8 cache needs key/value scale and minimum tensors");
+    for (int i = 0; i < 4; ++i) {
+      check_f32(stats[i], "cache statistics");
+      st[i] = stats[i].data_ptr<float>();
+    }
+  }
+  const c10::cuda::CUDAGuard guard(q.device());
+  if (splits <= 0) {
+    const int64_t assumed = pos_dev.has_value() ? cache_k.size(1) : len;
+    splits = ob::decode_attention_splits((int)B, (int)Hk, (int)assumed);
+  }
+  Tensor out = torch::empty_like(q);
+  Tensor partial;
+  if (splits > 1) partial = torch::empty({B * H * splits * (D + 2)}, q.options().dtype(torch::kFloat32));
+  ob::decode_attention(q.data_ptr(), cache_k.data_ptr(), cache_v.data_ptr(), st[0], st[1], st[2],
+                       st[3], out.data_ptr(), splits > 1 ? partial.data_ptr<float>() : nullptr,
+                       (int)B, (int)H, (int)Hk, (int)D, (int)cache_k.size(1), (int)len,
+                       optional_i32(pos_dev, "pos_dev"), (int)splits, (float)scale, int8,
+                       current_stream());
+  return out;
+}
+
+// logits (rows, vocab) bf16 or fp32 (row stride may exceed vocab); uniforms (steps, rows) fp32 or
+// none (greedy); out_tokens (rows, out_steps) int64. The int32 scalars `step` and `pos` live on
+// the device and are advanced by the kernel when `counters` (three int32: step, pos, done) is given.
+void sample_tokens(const Tensor& logits, int64_t valid_vocab, double temperature, int64_t top_k,
+                   double top_p, const c10::optional<Tensor>& uniforms, Tensor& out_tokens,
+                   const c10::optional<Tensor>& next_input, const c10::optional<Tensor>& counters,
+                   const c10::optional<Tensor>& workspace) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1);
+  const bool bf16 = logits.scalar_type() == torch::kBFloat16;
+  TORCH_CHECK(bf16 || logits.scalar_type() == torch::kFloat32, "logits must be bf16 or fp32");
+  TORCH_CHECK(out_tokens.is_cuda() && out_tokens.scalar_type() == torch::kInt64 &&
+              out_tokens.dim() == 2 && out_tokens.size(0) == logits.size(0) &&
+              out_tokens.stride(1) == 1);
+  const c10::cuda::CUDAGuard guard(logits.device());
+  int64_t* next_ptr = nullptr;
+  if (next_input.has_value()) {
+    TORCH_CHECK(next_input->is_cuda() && next_input->scalar_type() == torch::kInt64 &&
+                next_input->is_contiguous() && next_input->numel() == logits.size(0));
+    next_ptr = next_input->data_ptr<int64_t>();
+  }
+  int* step_ptr = nullptr;
+  int* pos_ptr = nullptr;
+  unsigned int* done_ptr = nullptr;
+  if (counters.has_value()) {
+    check_i32(*counters, "counters");
+    TORCH_CHECK(counters->numel() == 3, "counters holds (step, position, done)");
+    step_ptr = counters->data_ptr<int>();
+    pos_ptr = step_ptr + 1;
+    done_ptr = reinterpret_cast<unsigned int*>(step_ptr + 2);
+  }
+  const float* uni = nullptr;
+  if (uniforms.has_value()) {
+    check_f32(*uniforms, "uniforms");
+    TORCH_CHECK(uniforms->is_contiguous() && uniforms->numel() % logits.size(0) == 0);
+    uni = uniforms->data_ptr<float>();
+  }
+  ob::sample_tokens(logits.data_ptr(), bf16, logits.stride(0), (int)logits.size(0),
+                    (int)logits.size(1), (int)std::min<int64_t>(valid_vocab, logits.size(1)),
+                    (float)temperature, (int)top_k, (float)top_p, uni,
+                    out_tokens.data_ptr<int64_t>(), out_tokens.stride(0), next_ptr, step_ptr, pos_ptr,
+                    done_ptr, optional_f32(workspace, "workspace"), current_stream());
+}
+
 std::vector<int64_t> status(bool clear) {
   int out[4];
   ob::status_read(out, clear);
@@ -445,6 +702,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("peer_barrier", &peer_barrier);
   m.def("peer_reduce_scatter_mean", &peer_reduce_scatter_mean);
   m.def("peer_all_gather", &peer_all_gather);
+  m.def("route_topk", &route_topk);
+  m.def("moe_plan", &moe_plan);
+  m.def("moe_scatter_rows", &moe_scatter_rows);
+  m.def("moe_gather_combine", &moe_gather_combine);
+  m.def("qb_quantile", &qb_quantile);
+  m.def("rope_append", &rope_append);
+  m.def("decode_attention", &decode_attention);
+  m.def("sample_tokens", &sample_tokens);
   m.def("status", &status);
   m.def("launch_count", []() { return (int64_t)ob::launch_count(); });
 }

@@ -25,6 +25,7 @@ from ohara_b200 import ops
 from ohara_b200.embeddings_pos.rotary import apply_rope, precompute_freqs_cis
 from ohara_b200.modules.kv_cache import KVCache
 from ohara_b200.modules.mlp import Linear, SwiGLU
+from ohara_b200.ops import decode as decode_ops
 from ohara_b200.modules.moe import MoE
 from ohara_b200.modules.moe_grouped import GroupedMoE
 from ohara_b200.modules.norm import RMSNorm
@@ -131,7 +132,17 @@ class Attention(nn.Module):
         q = self.query(x).view(batch, seq_len, heads, self.head_dim)
         k = self.key(x).view(batch, seq_len, kv_heads, self.head_dim)
         v = self.value(x).view(batch, seq_len, kv_heads, self.head_dim)
-        q, k = apply_rope(q, k, freqs_cis)
+        if (kv_cache is not None and seq_len == 1 and len(freqs_cis) == 4
+                and decode_ops.fused_decode_supported(q, kv_cache) and v.dtype == q.dtype):
+            # Decode step: RoPE + cache append in one kernel, then attention over the cache in
+            # place (no mask tensor, no head expansion, int8 dequantised on the fly).
+            q = kv_cache.append_decode(q, k, v, freqs_cis[2], freqs_cis[3], position_ids)
+            out = decode_ops.decode_attention(q, kv_cache, position_ids)
+            return self.res_dropout(self.proj(out.reshape(batch, 1, heads * self.head_dim)))
+        if freqs_cis[0] is None:
+            raise ValueError("a device-side position needs the fused decode kernels: bf16 "
+                             "activations on CUDA, head_dim 64 or 128, a bf16 or int8 cache")
+        q, k = apply_rope(q, k, freqs_cis[:2])
         if kv_cache is not None:
             assert position_ids is not None
             k, v = kv_cache.forward(k, v.to(k.dtype), position_ids)
@@ -238,13 +249,40 @@ class Llama(nn.Module):
             raise ValueError("input exceeds max_sequence_length")
         return start
 
+    def _rope_tables_f32(self) -> tuple[Tensor, Tensor]:
+        """Full fp32 rotary tables for the serving kernels (a cached copy when the buffers were
+        converted to a lower precision together with the model)."""
+        cached = getattr(self, "_rope_f32", None)
+        if cached is None or cached[0].device != self.freq_cos.device:
+            cached = (self.freq_cos.float().contiguous(), self.freq_sin.float().contiguous())
+            self._rope_f32 = cached
+        return cached
+
     def forward_hidden(self, x: Tensor, kv_cache: list[KVCache] | None = None,
                        position_ids: int | Tensor | None = None) -> Tensor:
-        """Final-norm hidden states ``(B, T, hidden)`` (everything except the output projection)."""
+        """Final-norm hidden states ``(B, T, hidden)`` (everything except the output projection).
+
+        With a KV cache on CUDA, ``position_ids`` may be a one-element int32 CUDA tensor and ``x``
+        a single token per sequence: the position is then read on the device by the serving
+        kernels and nothing here synchronises with the host, so the step can be captured in a CUDA
+        graph (argument checks that would need the value are skipped)."""
+        device_position = (
+            kv_cache is not None and isinstance(position_ids, Tensor) and position_ids.is_cuda
+            and position_ids.dtype == torch.int32 and position_ids.numel() == 1 and x.size(1) == 1
+        )
+        if device_position:
+            h = ops.embedding(x, self.token_emb.weight)
+            freqs = (None, None, *self._rope_tables_f32())
+            pending = None
+            for idx, layer in enumerate(self.layers):
+                h, pending = layer.forward_deferred(h, pending, freqs, kv_cache[idx], position_ids)
+            return ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[0]
         start = self._check_inputs(x, kv_cache, position_ids)
         seq = x.size(1)
         h = ops.embedding(x, self.token_emb.weight)
         freqs = (self.freq_cos[start : start + seq], self.freq_sin[start : start + seq])
+        if kv_cache is not None and x.is_cuda and seq == 1:
+            freqs = (*freqs, *self._rope_tables_f32())
         pending = None
         for idx, layer in enumerate(self.layers):
             cache = kv_cache[idx] if kv_cache is not None else None

@@ -4,10 +4,12 @@ Parameters: ``w_gate, w_up (E, dim, hidden)``, ``w_down (E, hidden, dim)`` (``x 
 dense shared experts ``shared_{gate,up,down}``, ``router`` and the ``router_bias`` buffer — the
 reference layout (ohara/modules/moe_grouped.py:95-117), so checkpoints interchange.
 
-Dispatch on CUDA: (token, expert) pairs are sorted by expert into a buffer whose per-expert row
-groups are padded to the 128-row GEMM tile; three *grouped* tcgen05 GEMMs (a per-tile expert table
-selects the weight matrix) compute the experts, the SwiGLU kernel fuses the activation, and a
-weighted scatter-add combines. On CPU a readable per-expert loop is used, which is also the oracle.
+On CUDA the router runs as a split-bf16 tensor-core GEMM plus one top-k kernel (indices, gate
+weights, balancing threshold and expert counts in a single launch); (token, expert) pairs are
+placed into a buffer whose per-expert row groups are padded to the 128-row GEMM tile; three
+*grouped* tcgen05 GEMMs (a per-tile expert table selects the weight matrix) compute the experts, the
+SwiGLU kernel fuses the activation, and a gather kernel combines with the gate weights. On CPU a
+readable per-expert loop is used, which is also the oracle.
 
 Extensions over the reference (used by the expert-parallel configuration): an optional Switch-style
 auxiliary load-balancing loss (``aux_loss_coef``) and a capacity factor with drop policy
@@ -22,6 +24,8 @@ import torch.nn.functional as F
 from torch import Tensor
 
 from ohara_b200 import ops
+from ohara_b200.ops import moe as moe_ops
+from ohara_b200.ops.grouped import grouped_swiglu_experts
 from ohara_b200.modules.mlp import Linear
 from ohara_b200.modules.routing import (
     QuantileBalancedRouter,
@@ -98,13 +102,6 @@ class GroupedMoE(QuantileBalancedRouter):
         return weights * keep.to(weights.dtype)
 
     # -- dispatch ----------------------------------------------------------------------------
-    def _dispatch_grouped(self, flat_x: Tensor, indices: Tensor, weights: Tensor) -> Tensor:
-        from ohara_b200.ops.grouped import grouped_swiglu_experts
-
-        return grouped_swiglu_experts(
-            flat_x, indices, weights, self.w_gate, self.w_up, self.w_down
-        )
-
     def _dispatch_reference(self, flat_x: Tensor, indices: Tensor, weights: Tensor) -> Tensor:
         out = torch.zeros_like(flat_x)
         k = self.num_experts_per_tok
@@ -128,11 +125,24 @@ class GroupedMoE(QuantileBalancedRouter):
     def forward(self, x: Tensor) -> Tensor:
         batch, seq, dim = x.shape
         flat_x = x.reshape(batch * seq, dim)
-        indices, weights, logits, alpha = self._route(flat_x)
+        kernels = (ops.fast_path(flat_x) and dim % 8 == 0 and self.hidden_dim % 8 == 0
+                   and self.num_experts <= 256 and self.num_experts_per_tok <= 16)
+        counts = None
+        if kernels and moe_ops.router_logits_supported(flat_x, self.router.weight):
+            flat16 = flat_x if flat_x.dtype == torch.bfloat16 else flat_x.to(torch.bfloat16)
+            logits = moe_ops.router_logits(flat16, self.router.weight)
+            indices, weights, alpha, counts = moe_ops.route(
+                logits, self.router_bias if self.quantile_balancing else None,
+                self.num_experts_per_tok, self.gate_fn, self.normalize_weights,
+                self.quantile_balancing,
+            )
+        else:
+            indices, weights, logits, alpha = self._route(flat_x)
         if self.capacity_factor is not None:
-            weights = self._apply_capacity(indices, weights)
-        if ops.fast_path(flat_x) and dim % 8 == 0 and self.hidden_dim % 8 == 0:
-            out = self._dispatch_grouped(flat_x, indices, weights)
+            weights = self._apply_capacity(indices.long(), weights)
+        if kernels:
+            out = grouped_swiglu_experts(flat_x, indices, weights, self.w_gate, self.w_up,
+                                         self.w_down, counts)
         else:
             out = self._dispatch_reference(flat_x, indices, weights.to(flat_x.dtype))
         if self.num_shared_experts > 0:
@@ -140,11 +150,14 @@ class GroupedMoE(QuantileBalancedRouter):
         if self.training:
             if self.aux_loss_coef > 0.0:
                 self.aux_loss = self.aux_loss_coef * load_balance_aux_loss(
-                    logits, indices, self.num_experts
+                    logits, indices.long(), self.num_experts
                 )
             if self.quantile_balancing:
                 self._accumulate_qb(logits.detach(), alpha.detach())
-            self._record_load(indices.detach())
+            if counts is not None:
+                self.expert_counts += counts
+            else:
+                self._record_load(indices.detach())
         return out.view(batch, seq, dim)
 
     # -- init --------------------------------------------------------------------------------

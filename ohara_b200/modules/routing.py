@@ -67,12 +67,17 @@ class QuantileBalancedRouter(nn.Module):
 
     @torch.no_grad()
     def _accumulate_qb(self, logits: Tensor, alpha: Tensor) -> None:
-        margin = logits - alpha  # expert e wins a token when its margin is positive
-        tokens = margin.size(0)
+        tokens = logits.size(0)
         fair_share = max(1, tokens * self.num_experts_per_tok // self.num_experts)
         fair_share = min(fair_share, tokens)
-        beta = torch.topk(margin.t(), fair_share, dim=-1).values[:, -1]
-        self.qb_beta_sum += beta
+        if logits.is_cuda and logits.dtype == torch.float32:
+            from ohara_b200.ops.moe import accumulate_quantile
+
+            # exact radix select per expert instead of a sort over (experts, tokens)
+            accumulate_quantile(logits, alpha.float(), self.qb_beta_sum, fair_share)
+        else:
+            margin = logits - alpha.view(-1, 1)  # expert e wins a token when its margin is positive
+            self.qb_beta_sum += torch.topk(margin.t(), fair_share, dim=-1).values[:, -1]
         self.qb_beta_count += 1
 
     @torch.no_grad()

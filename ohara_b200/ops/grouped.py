@@ -91,23 +91,23 @@ def grouped_linear(x_pad: Tensor, weight: Tensor, tile_expert: Tensor, k_offsets
 
 
 def grouped_swiglu_experts(flat_x: Tensor, expert_indices: Tensor, expert_weights: Tensor,
-                           w_gate: Tensor, w_up: Tensor, w_down: Tensor) -> Tensor:
-    """Routed SwiGLU experts: permute → 3 grouped GEMMs (+ fused activation) → weighted combine."""
-    from . import swiglu
+                           w_gate: Tensor, w_up: Tensor, w_down: Tensor,
+                           counts: Tensor | None = None) -> Tensor:
+    """Routed SwiGLU experts: permute -> 3 grouped GEMMs (+ fused activation) -> weighted combine.
+    ``counts`` (tokens per expert, int32) comes for free from the routing kernel; without it the
+    indices are counted here."""
+    from . import moe, swiglu
 
     num_experts = w_gate.shape[0]
+    k = expert_indices.shape[1]
     x16 = flat_x if flat_x.dtype == torch.bfloat16 else flat_x.to(torch.bfloat16)
-    token_of_row, dest_row, order, tile_expert, k_offsets, padded_rows = build_dispatch_plan(
-        expert_indices, num_experts
-    )
-    x_pad = torch.zeros(padded_rows, x16.shape[1], device=x16.device, dtype=torch.bfloat16)
-    x_pad = x_pad.index_copy(0, dest_row, x16.index_select(0, token_of_row))
+    indices = expert_indices if expert_indices.dtype == torch.int32 else expert_indices.int()
+    if counts is None:
+        counts = torch.bincount(indices.reshape(-1), minlength=num_experts).int()
+    dest_row, row_pair, tile_expert, k_offsets = moe.dispatch_plan(indices, counts)
+    x_pad = moe.permute_rows(x16, dest_row, row_pair, k)
     gate = grouped_linear(x_pad, w_gate, tile_expert, k_offsets)
     up = grouped_linear(x_pad, w_up, tile_expert, k_offsets)
     hidden = swiglu(gate, up)
     y_pad = grouped_linear(hidden, w_down, tile_expert, k_offsets)
-    pair_weight = expert_weights.reshape(-1)[order].unsqueeze(-1)
-    y = y_pad.index_select(0, dest_row).float() * pair_weight.float()
-    out = torch.zeros(flat_x.shape, device=flat_x.device, dtype=torch.float32)
-    out = out.index_add(0, token_of_row, y)
-    return out.to(flat_x.dtype if flat_x.dtype == torch.bfloat16 else torch.bfloat16)
+    return moe.combine_rows(y_pad, expert_weights, dest_row, row_pair)
