@@ -17,6 +17,42 @@ void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int b
                const int* k_offsets, int64_t a_rows, int64_t b_rows, int num_sms,
                const void* R, int64_t ldr, int64_t strideR, float beta, cudaStream_t stream);
 
+// Fused collective of a GEMM (see gemm_sm100.cu). mode 1: gather the rows of A from `world` peers
+// (`a_maps`: device array of tensor maps built by make_peer_row_maps, `ready`: this rank's flag
+// slots). mode 2: push row block r of C into `c_peer[r]` (row pitch `c_peer_ld` elements).
+struct GemmComm {
+  int mode = 0;
+  int world = 1;
+  int rank = 0;
+  unsigned int epoch = 0;
+  unsigned long long limit_ns = 0;
+  const void* a_maps = nullptr;
+  const unsigned int* ready = nullptr;
+  void* c_peer[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  long long c_peer_ld = 0;
+};
+void gemm_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, int batches,
+                    bool a_mn, bool b_mn, int64_t lda, int64_t ldb, int64_t ldc, int64_t strideA,
+                    int64_t strideB, int64_t strideC, bool a_batched, bool b_batched, int b_batches,
+                    bool out_f32, int splits, bool reduce, float alpha, const int* m_tile_batch,
+                    const int* k_offsets, int64_t a_rows, int64_t b_rows, int num_sms,
+                    const void* R, int64_t ldr, int64_t strideR, float beta, const GemmComm* comm,
+                    cudaStream_t stream);
+// Encodes one (rows x K, K-major, pitch ld) A-operand tensor map per peer buffer into `out`
+// (host memory, 128 bytes each).
+void make_peer_row_maps(const int64_t* bases, int world, int64_t rows, int64_t K, int64_t ld,
+                        void* out);
+
+// tp_comm.cu
+void tp_signal(const int64_t* flag_pads, int slot_base, int rank, int world, unsigned int epoch,
+               cudaStream_t stream);
+void tp_reduce_slots(const void* slots, const unsigned int* flags, const void* residual, void* out,
+                     int64_t rows, int64_t cols, int world, unsigned int epoch,
+                     unsigned long long limit_ns, cudaStream_t stream);
+void tp_gather_rows(const int64_t* bases, const unsigned int* flags, void* out,
+                    int64_t bytes_per_rank, int rank, int world, unsigned int epoch,
+                    unsigned long long limit_ns, cudaStream_t stream);
+
 // elementwise.cu
 void rmsnorm_fwd(const void* x, const void* delta, const float* w, void* y, void* x_out, float* rstd,
                  int rows, int d, float eps, cudaStream_t stream);
@@ -72,6 +108,11 @@ void cross_entropy_rows(void* logits, const int64_t* targets, float* row_loss, f
                         int* row_correct, const float* scale_ptr, int64_t rows, int vocab,
                         int64_t pitch, int64_t ignore_index, bool write_grad, cudaStream_t stream);
 void scale_by_scalar(void* x, bool is_bf16, const float* scalar, int64_t n, cudaStream_t stream);
+
+// gemv.cu
+bool gemv_supported(int M, int N, int K);
+void gemv_bf16(const void* x, const void* w, void* y, int M, int N, int K, int64_t ldx, int64_t ldw,
+               int64_t ldy, cudaStream_t stream);
 
 // moe.cu
 void route_topk(const float* logits, const float* bias, int* indices, float* weights, float* alpha,

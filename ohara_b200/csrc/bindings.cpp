@@ -410,6 +410,26 @@ void peer_all_gather(const std::vector<int64_t>& weights, const std::vector<int6
                       (uint32_t)epoch, (uint64_t)(limit_s * 1e9), current_stream());
 }
 
+// y (M, N) = x (M, K) @ w (N, K)^T for at most 16 rows (decode); returns false when the shape is not
+// supported and nothing was launched.
+bool gemv(const Tensor& x, const Tensor& w, Tensor& y) {
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  check_bf16(y, "y");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && y.dim() == 2 && x.size(1) == w.size(1) &&
+              y.size(0) == x.size(0) && y.size(1) == w.size(0));
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && y.stride(1) == 1);
+  const int64_t M = x.size(0), N = w.size(0), K = x.size(1);
+  auto aligned = [](const Tensor& t) {
+    return reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0 && (t.stride(0) * 2) % 16 == 0;
+  };
+  if (!ob::gemv_supported((int)M, (int)N, (int)K) || !aligned(x) || !aligned(w)) return false;
+  const c10::cuda::CUDAGuard guard(x.device());
+  ob::gemv_bf16(x.data_ptr(), w.data_ptr(), y.data_ptr(), (int)M, (int)N, (int)K, x.stride(0),
+                w.stride(0), y.stride(0), current_stream());
+  return true;
+}
+
 // -- mixture of experts ---------------------------------------------------------------------------
 void check_i32(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous(), name,
@@ -667,6 +687,117 @@ void sample_tokens(const Tensor& logits, int64_t valid_vocab, double temperature
                     done_ptr, optional_f32(workspace, "workspace"), current_stream());
 }
 
+// -- fused tensor-parallel collectives ---------------------------------------------------------------
+// Tensor maps over `bases` (one (rows, K) K-major bf16 matrix of pitch `ld` per rank), uploaded to
+// the device: the A operand of gemm_gather_a. Build once per buffer set and keep the tensor.
+Tensor peer_row_maps(const std::vector<int64_t>& bases, int64_t rows, int64_t K, int64_t ld,
+                     int64_t device_index) {
+  const c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, (c10::DeviceIndex)device_index));
+  Tensor host = torch::empty({(int64_t)bases.size() * 128}, torch::dtype(torch::kUInt8));
+  ob::make_peer_row_maps(bases.data(), (int)bases.size(), rows, K, ld, host.data_ptr());
+  return host.to(c10::Device(c10::kCUDA, (c10::DeviceIndex)device_index));
+}
+
+void check_2d_operand(const Tensor& t, const char* name) {
+  check_bf16(t, name);
+  TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1 && (t.stride(0) * 2) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0,
+              name, " must be a 2-D bf16 matrix with unit inner stride and 16-byte aligned rows");
+}
+
+// c (M, N) = [rows of all ranks] (M, K) @ op(b): the rows of A are read from the peers' staging
+// buffers through `maps` once their ready flags (int32 at address `ready_addr`, one per rank) have
+// reached `epoch`. `a_local` is this rank's staging buffer (rows M / world).
+void gemm_gather_a(const Tensor& maps, const Tensor& a_local, const Tensor& b, Tensor& c, bool b_mn,
+                   int64_t ready_addr, int64_t epoch, int64_t rank, int64_t world, double limit_s) {
+  check_2d_operand(a_local, "a_local");
+  check_2d_operand(b, "b");
+  check_2d_operand(c, "c");
+  TORCH_CHECK(maps.is_cuda() && maps.numel() == world * 128, "maps must hold one tensor map per rank");
+  const int64_t rows = a_local.size(0), K = a_local.size(1), M = rows * world, N = c.size(1);
+  TORCH_CHECK(c.size(0) == M && (b_mn ? (b.size(0) == K && b.size(1) == N)
+                                      : (b.size(0) == N && b.size(1) == K)),
+              "operand shapes do not match");
+  const c10::cuda::CUDAGuard guard(c.device());
+  ob::GemmComm comm;
+  comm.mode = 1;
+  comm.world = (int)world;
+  comm.rank = (int)rank;
+  comm.epoch = (unsigned int)epoch;
+  comm.limit_ns = (unsigned long long)(limit_s * 1e9);
+  comm.a_maps = maps.data_ptr();
+  comm.ready = reinterpret_cast<const unsigned int*>(ready_addr);
+  ob::gemm_bf16_comm(a_local.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K, 1,
+                     false, b_mn, a_local.stride(0), b.stride(0), c.stride(0), 0, 0, 0, false, false,
+                     1, false, 1, false, 1.0f, nullptr, nullptr, rows, b.size(0),
+                     ob::device_sm_count(), nullptr, 0, 0, 0.f, &comm, current_stream());
+}
+
+// Row block r of a (M, K) @ op(b) is stored into the buffer at address dests[r] (row pitch
+// `dest_ld` elements): the receive slot that rank r keeps for this rank.
+void gemm_push_c(const Tensor& a, const Tensor& b, bool b_mn, const std::vector<int64_t>& dests,
+                 int64_t dest_ld, int64_t N, int64_t rank) {
+  check_2d_operand(a, "a");
+  check_2d_operand(b, "b");
+  const int64_t M = a.size(0), K = a.size(1), world = (int64_t)dests.size();
+  TORCH_CHECK(b_mn ? (b.size(0) == K && b.size(1) == N) : (b.size(0) == N && b.size(1) == K),
+              "operand shapes do not match");
+  TORCH_CHECK(world >= 1 && world <= 8 && dest_ld >= N && dest_ld % 8 == 0);
+  const c10::cuda::CUDAGuard guard(a.device());
+  ob::GemmComm comm;
+  comm.mode = 2;
+  comm.world = (int)world;
+  comm.rank = (int)rank;
+  for (int64_t r = 0; r < world; ++r) {
+    TORCH_CHECK(dests[r] % 16 == 0, "receive slots must be 16-byte aligned");
+    comm.c_peer[r] = reinterpret_cast<void*>(dests[r]);
+  }
+  comm.c_peer_ld = dest_ld;
+  // The C tensor map is not used in this mode; describe this rank's own slot so that it is valid.
+  ob::gemm_bf16_comm(a.data_ptr(), b.data_ptr(), reinterpret_cast<void*>(dests[rank]), (int)M, (int)N,
+                     (int)K, 1, false, b_mn, a.stride(0), b.stride(0), dest_ld, 0, 0, 0, false, false,
+                     1, false, 1, false, 1.0f, nullptr, nullptr, M, b.size(0), ob::device_sm_count(),
+                     nullptr, 0, 0, 0.f, &comm, current_stream());
+}
+
+void tp_signal(const std::vector<int64_t>& pads, int64_t slot_base, int64_t rank, int64_t epoch) {
+  ob::tp_signal(pads.data(), (int)slot_base, (int)rank, (int)pads.size(), (unsigned int)epoch,
+                current_stream());
+}
+
+// out (rows, cols) = sum of the `world` slots of `slots` (world, rows, cols) (+ residual) once every
+// flag at `flags_addr` has reached `epoch`.
+Tensor tp_reduce_slots(const Tensor& slots, int64_t flags_addr, const c10::optional<Tensor>& residual,
+                       int64_t epoch, double limit_s) {
+  check_bf16(slots, "slots");
+  TORCH_CHECK(slots.dim() == 3 && slots.is_contiguous());
+  const c10::cuda::CUDAGuard guard(slots.device());
+  Tensor out = torch::empty({slots.size(1), slots.size(2)}, slots.options());
+  const void* res = nullptr;
+  if (residual.has_value()) {
+    check_bf16(*residual, "residual");
+    TORCH_CHECK(residual->is_contiguous() && residual->numel() == out.numel());
+    res = residual->data_ptr();
+  }
+  ob::tp_reduce_slots(slots.data_ptr(), reinterpret_cast<const unsigned int*>(flags_addr), res,
+                      out.data_ptr(), slots.size(1), slots.size(2), (int)slots.size(0),
+                      (unsigned int)epoch, (unsigned long long)(limit_s * 1e9), current_stream());
+  return out;
+}
+
+// out (world * rows, cols) = the staged (rows, cols) blocks at `bases`, in rank order.
+void tp_gather_rows(const std::vector<int64_t>& bases, int64_t flags_addr, Tensor& out, int64_t rank,
+                    int64_t epoch, double limit_s) {
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous());
+  const int64_t world = (int64_t)bases.size();
+  const int64_t bytes = out.numel() * out.element_size();
+  TORCH_CHECK(bytes % (16 * world) == 0, "gathered tensor must split into 16-byte aligned parts");
+  const c10::cuda::CUDAGuard guard(out.device());
+  ob::tp_gather_rows(bases.data(), reinterpret_cast<const unsigned int*>(flags_addr), out.data_ptr(),
+                     bytes / world, (int)rank, (int)world, (unsigned int)epoch,
+                     (unsigned long long)(limit_s * 1e9), current_stream());
+}
+
 std::vector<int64_t> status(bool clear) {
   int out[4];
   ob::status_read(out, clear);
@@ -702,6 +833,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("peer_barrier", &peer_barrier);
   m.def("peer_reduce_scatter_mean", &peer_reduce_scatter_mean);
   m.def("peer_all_gather", &peer_all_gather);
+  m.def("gemv", &gemv);
   m.def("route_topk", &route_topk);
   m.def("moe_plan", &moe_plan);
   m.def("moe_scatter_rows", &moe_scatter_rows);
@@ -710,6 +842,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope_append", &rope_append);
   m.def("decode_attention", &decode_attention);
   m.def("sample_tokens", &sample_tokens);
+  m.def("peer_row_maps", &peer_row_maps);
+  m.def("gemm_gather_a", &gemm_gather_a);
+  m.def("gemm_push_c", &gemm_push_c);
+  m.def("tp_signal", &tp_signal);
+  m.def("tp_reduce_slots", &tp_reduce_slots);
+  m.def("tp_gather_rows", &tp_gather_rows);
   m.def("status", &status);
   m.def("launch_count", []() { return (int64_t)ob::launch_count(); });
 }

@@ -297,50 +297,52 @@ __global__ void decode_merge_kernel(const float* __restrict__ partial, __nv_bflo
 }
 
 // ------------------------------------------------------------------------------------------------
-// Sampler. One CTA per row of logits. Steps, all on fp32 copies held in shared memory when the
-// vocabulary fits (else in a global workspace row):
-//   1. mask ids >= valid_vocab, scale by 1/temperature (temperature 0: plain argmax, lowest id wins)
-//   2. top-k: exact k-th largest value by radix select; smaller values are dropped (ties kept)
+// Sampler. One CTA per row of logits; the row lives in shared memory as fp32 when the vocabulary
+// fits (else in a global workspace row). Steps:
+//   1. mask ids >= valid_vocab; temperature 0 is a plain argmax (lowest id wins)
+//   2. top-k: the exact k-th largest value, found by a two-bits-per-round search on the
+//      order-preserving integer image of the floats; each round is a count of elements at or above
+//      three pivots (no histograms, no atomics). Smaller values are dropped, ties are kept.
 //   3. softmax over what is left
-//   4. top-p: a token is dropped when the probability mass of strictly more likely tokens
-//      already exceeds top_p (so the most likely token always survives); found by a radix select
-//      on probability mass
+//   4. top-p: a token is dropped when the probability mass of the tokens ahead of it (more likely,
+//      or equally likely with a lower id) already exceeds top_p, so the most likely token always
+//      survives. With at most 1024 survivors (the usual case after top-k) every survivor sums the
+//      mass ahead of it directly; otherwise a one-bit-per-round search finds the cut-off
+//      probability (all tokens tied at the cut-off are then kept).
 //   5. inverse-CDF draw over the kept tokens in index order with the caller's uniform number
 // The chosen id goes to out_tokens[row * out_stride + step] and, optionally, next_input[row];
 // the step counter and position are advanced by the last CTA to finish.
 // ------------------------------------------------------------------------------------------------
 constexpr int kSampleThreads = 1024;
+constexpr int kMaxCandidates = 1024;
 
 __device__ __forceinline__ uint32_t ordered_key(float f) {
   const uint32_t u = __float_as_uint(f);
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
-
-__device__ float block_reduce_max(float v, float* scratch) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float r = threadIdx.x < (blockDim.x >> 5) ? scratch[threadIdx.x] : -INFINITY;
-  if (threadIdx.x < 32) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, o));
-    if (threadIdx.x == 0) scratch[32] = r;
-  }
-  __syncthreads();
-  return scratch[32];
+__device__ __forceinline__ float key_to_float(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
 }
-__device__ float block_reduce_sum(float v, float* scratch) {
+
+struct MaxOp {
+  template <typename T> __device__ T operator()(T a, T b) const { return a > b ? a : b; }
+};
+struct SumOp {
+  template <typename T> __device__ T operator()(T a, T b) const { return a + b; }
+};
+
+// Block-wide reduction for 1024 threads; every thread gets the result. `scratch` holds 33 values.
+template <typename T, typename Op>
+__device__ T block_reduce(T v, T identity, Op op, T* scratch) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  __syncthreads();
+  for (int o = 16; o > 0; o >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();  // protects scratch from the previous use
   if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
   __syncthreads();
-  float r = threadIdx.x < (blockDim.x >> 5) ? scratch[threadIdx.x] : 0.f;
   if (threadIdx.x < 32) {
+    T r = threadIdx.x < (blockDim.x >> 5) ? scratch[threadIdx.x] : identity;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    for (int o = 16; o > 0; o >>= 1) r = op(r, __shfl_xor_sync(0xffffffffu, r, o));
     if (threadIdx.x == 0) scratch[32] = r;
   }
   __syncthreads();
@@ -355,13 +357,13 @@ sample_kernel(const LogitT* __restrict__ logits, int64_t row_stride, int vocab, 
               int* __restrict__ step_dev, int* __restrict__ pos_dev, unsigned int* __restrict__ done,
               float* __restrict__ workspace, bool use_smem) {
   extern __shared__ float smem_vals[];
-  __shared__ float scratch[33];
-  __shared__ float hist_f[256];
-  __shared__ int hist_i[256];
-  __shared__ uint32_t prefix_s;
-  __shared__ int remaining_i;
-  __shared__ float remaining_f;
+  __shared__ float scratch_f[33];
+  __shared__ unsigned long long scratch_u[33];
+  __shared__ float cand_p[kMaxCandidates];
+  __shared__ int cand_i[kMaxCandidates];
+  __shared__ int cand_count;
   __shared__ int chosen_s;
+  __shared__ float warp_tot[32];
 
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
@@ -381,7 +383,7 @@ sample_kernel(const LogitT* __restrict__ logits, int64_t row_stride, int vocab, 
       best_i = i;
     }
   }
-  const float vmax = block_reduce_max(best, scratch);
+  const float vmax = block_reduce(best, -INFINITY, MaxOp(), scratch_f);
   int token;
   if (temperature <= 0.f) {
     if (tid == 0) chosen_s = 0x7fffffff;
@@ -391,116 +393,113 @@ sample_kernel(const LogitT* __restrict__ logits, int64_t row_stride, int vocab, 
     token = chosen_s;
   } else {
     const float inv_t = 1.f / temperature;
-    // 2. top-k threshold on the raw values (monotone in value / temperature)
+    // 2. top-k threshold: the largest key T with count(key >= T) >= k, two bits per round.
     float threshold = -INFINITY;
     if (top_k > 0 && top_k < n) {
-      if (tid == 0) {
-        prefix_s = 0;
-        remaining_i = top_k;
-      }
-      for (int pass = 0; pass < 4; ++pass) {
-        const int shift = 24 - 8 * pass;
-        if (tid < 256) hist_i[tid] = 0;
-        __syncthreads();
-        const uint32_t prefix = prefix_s;
-        const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+      uint32_t T = 0;
+      for (int bit = 30; bit >= 0; bit -= 2) {
+        const uint32_t p1 = T | (1u << bit), p2 = T | (2u << bit), p3 = T | (3u << bit);
+        unsigned long long packed = 0;  // three 21-bit counters
         for (int i = tid; i < n; i += kSampleThreads) {
           const uint32_t key = ordered_key(vals[i]);
-          if ((key & mask) == prefix) atomicAdd(&hist_i[(key >> shift) & 0xff], 1);
+          packed += (unsigned long long)(key >= p1) + ((unsigned long long)(key >= p2) << 21) +
+                    ((unsigned long long)(key >= p3) << 42);
         }
-        __syncthreads();
-        if (tid == 0) {
-          int remaining = remaining_i, bin = 255;
-          for (; bin > 0; --bin) {
-            if (hist_i[bin] >= remaining) break;
-            remaining -= hist_i[bin];
-          }
-          prefix_s = prefix | ((uint32_t)bin << shift);
-          remaining_i = remaining;
-        }
-        __syncthreads();
+        packed = block_reduce(packed, 0ull, SumOp(), scratch_u);
+        const int c1 = (int)(packed & 0x1fffff), c2 = (int)((packed >> 21) & 0x1fffff),
+                  c3 = (int)((packed >> 42) & 0x1fffff);
+        if (c3 >= top_k) T = p3; else if (c2 >= top_k) T = p2; else if (c1 >= top_k) T = p1;
       }
-      const uint32_t kth = prefix_s;
-      threshold = __uint_as_float((kth & 0x80000000u) ? (kth & 0x7fffffffu) : ~kth);
+      threshold = key_to_float(T);
     }
     // 3. unnormalised probabilities of what survived top-k
     float local = 0.f;
+    int survivors = 0;
     for (int i = tid; i < n; i += kSampleThreads) {
       const float x = vals[i];
       const float p = x >= threshold ? __expf((x - vmax) * inv_t) : 0.f;
       vals[i] = p;
       local += p;
+      survivors += p > 0.f;
     }
-    float total = block_reduce_sum(local, scratch);
-    // 4. top-p on probability mass
+    float total = block_reduce(local, 0.f, SumOp(), scratch_f);
+    // 4. top-p
     if (top_p > 0.f && top_p < 1.f) {
-      // Find the probability value v* with  mass(p > v*) <= top_p * total < mass(p >= v*).
-      if (tid == 0) {
-        prefix_s = 0;
-        remaining_f = top_p * total;
-      }
-      for (int pass = 0; pass < 4; ++pass) {
-        const int shift = 24 - 8 * pass;
-        if (tid < 256) hist_f[tid] = 0.f;
+      const int alive = (int)block_reduce((unsigned long long)survivors, 0ull, SumOp(), scratch_u);
+      const float budget = top_p * total;
+      if (alive <= kMaxCandidates) {
+        if (tid == 0) cand_count = 0;
         __syncthreads();
-        const uint32_t prefix = prefix_s;
-        const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
         for (int i = tid; i < n; i += kSampleThreads) {
           const float p = vals[i];
           if (p > 0.f) {
-            const uint32_t key = __float_as_uint(p);  // positive floats order like their bits
-            if ((key & mask) == prefix) atomicAdd(&hist_f[(key >> shift) & 0xff], p);
+            const int at = atomicAdd(&cand_count, 1);
+            cand_p[at] = p;
+            cand_i[at] = i;
           }
         }
         __syncthreads();
-        if (tid == 0) {
-          float remaining = remaining_f;
-          int bin = 255;
-          for (; bin > 0; --bin) {
-            if (hist_f[bin] > remaining) break;
-            remaining -= hist_f[bin];
+        if (tid < alive) {
+          const float p = cand_p[tid];
+          const int idx = cand_i[tid];
+          float ahead = 0.f;
+          for (int j = 0; j < alive; ++j) {
+            const float pj = cand_p[j];
+            if (pj > p || (pj == p && cand_i[j] < idx)) ahead += pj;
           }
-          prefix_s = prefix | ((uint32_t)bin << shift);
-          remaining_f = remaining;
+          if (ahead > budget) vals[idx] = 0.f;
+        }
+      } else {
+        // Largest probability T (as bits) with mass(p >= T) > budget; tokens below it are dropped.
+        uint32_t T = 0;
+        for (int bit = 30; bit >= 0; --bit) {
+          const uint32_t pivot = T | (1u << bit);
+          float mass = 0.f;
+          for (int i = tid; i < n; i += kSampleThreads) {
+            const float p = vals[i];
+            if (__float_as_uint(p) >= pivot) mass += p;  // positive floats order like their bits
+          }
+          mass = block_reduce(mass, 0.f, SumOp(), scratch_f);
+          if (mass > budget) T = pivot;
+        }
+        // Tokens above the cut-off all stay. Tokens exactly at it stay, in index order, while the
+        // mass ahead of them is within the budget.
+        const float cut = __uint_as_float(T);
+        float above = 0.f;
+        for (int i = tid; i < n; i += kSampleThreads) {
+          const float p = vals[i];
+          if (__float_as_uint(p) > T) above += p;
+        }
+        above = block_reduce(above, 0.f, SumOp(), scratch_f);
+        const int keep_ties = cut > 0.f ? (int)fminf(floorf(fmaxf(budget - above, 0.f) / cut), 2.0e9f) + 1 : 0;
+        const int per = (n + kSampleThreads - 1) / kSampleThreads;
+        const int first = min(tid * per, n), last = min(first + per, n);
+        int ties = 0;
+        for (int i = first; i < last; ++i) ties += __float_as_uint(vals[i]) == T;
+        int incl_t = ties;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, incl_t, o);
+          if ((tid & 31) >= o) incl_t += up;
         }
         __syncthreads();
-      }
-      const float cut = __uint_as_float(prefix_s);
-      // Everything more likely than `cut` stays, everything less likely goes. Tokens exactly at
-      // `cut` stay while the mass ahead of them (the more likely tokens, then earlier ties in
-      // index order) is within the budget; with a single such token nothing needs checking.
-      const float budget = remaining_f;  // mass still allowed when the ties begin
-      if (tid == 0) remaining_i = 0;
-      __syncthreads();
-      int ties = 0;
-      for (int i = tid; i < n; i += kSampleThreads) {
-        const float p = vals[i];
-        if (p < cut) vals[i] = 0.f;
-        else if (p == cut) ++ties;
-      }
-      if (ties) atomicAdd(&remaining_i, ties);
-      __syncthreads();
-      if (remaining_i > 1 && tid == 0) {
-        float ahead = 0.f;
-        for (int i = 0; i < n; ++i) {
-          if (vals[i] == cut) {
-            if (ahead > budget) vals[i] = 0.f;
-            ahead += cut;
-          }
+        if ((tid & 31) == 31) cand_i[tid >> 5] = incl_t;
+        __syncthreads();
+        int tie_rank = incl_t - ties;  // ties before this thread's chunk
+        for (int w = 0; w < (tid >> 5); ++w) tie_rank += cand_i[w];
+        for (int i = first; i < last; ++i) {
+          const uint32_t bits = __float_as_uint(vals[i]);
+          if (bits < T) vals[i] = 0.f;
+          else if (bits == T && tie_rank++ >= keep_ties) vals[i] = 0.f;
         }
       }
       __syncthreads();
-      local = 0.f;
-      for (int i = tid; i < n; i += kSampleThreads) local += vals[i];
-      total = block_reduce_sum(local, scratch);
     }
     // 5. inverse CDF in index order: thread t owns a contiguous chunk
     const int chunk = (n + kSampleThreads - 1) / kSampleThreads;
     const int lo = min(tid * chunk, n), hi = min(lo + chunk, n);
     float mine = 0.f;
     for (int i = lo; i < hi; ++i) mine += vals[i];
-    // inclusive scan of chunk sums across the block
-    __shared__ float warp_tot[32];
     float incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -548,7 +547,6 @@ sample_kernel(const LogitT* __restrict__ logits, int64_t row_stride, int vocab, 
       __syncthreads();
     }
     token = chosen_s;
-    (void)total;
   }
   if (tid == 0) {
     out_tokens[(size_t)row * out_stride + step] = token;
@@ -587,11 +585,11 @@ void rope_append(const void* q, const void* k, const void* v, void* q_out, void*
 }
 
 int decode_attention_splits(int B, int Hk, int len) {
-  // Enough CTAs to cover the machine, at least 64 keys per CTA, at most 32 splits.
+  // Enough CTAs to cover the machine, at least 256 keys per CTA, at most 16 splits.
   const int base = std::max(B * Hk, 1);
-  int splits = (2 * device_sm_count() + base - 1) / base;
-  splits = std::min(splits, std::max(len / 64, 1));
-  return std::max(1, std::min(splits, 32));
+  int splits = (device_sm_count() + base - 1) / base;
+  splits = std::min(splits, std::max(len / 256, 1));
+  return std::max(1, std::min(splits, 16));
 }
 
 template <int D, bool INT8>
@@ -660,9 +658,9 @@ void sample_tokens(const void* logits, bool logits_bf16, int64_t row_stride, int
                    float* workspace, cudaStream_t stream) {
   if (rows == 0) return;
   OB_CHECK(valid_vocab >= 1, "sampler needs at least one valid token");
-  // Static shared memory of the kernel is about 2.5 KB; leave room for it.
+  // Static shared memory of the kernel is about 9 KB; leave room for it.
   const size_t need = (size_t)vocab * sizeof(float);
-  const bool use_smem = need + 4096 <= sample_smem_limit();
+  const bool use_smem = need + 10240 <= sample_smem_limit();
   OB_CHECK(use_smem || workspace != nullptr, "vocabulary too large for shared memory: pass a workspace");
   auto launch = [&](auto kernel, auto* typed) {
     if (use_smem) {

@@ -15,8 +15,20 @@
 //   * k_offsets    : per output batch, the [begin, end) range of the shared K (token) dimension
 //                    (grouped weight gradient; A and B are plain 2-D matrices).
 //
+// Optional fused collectives over NVLink peer memory (tensor / sequence parallel layers):
+//   * gather-A (comm_mode 1): the rows of A are sharded over `world` ranks; the producer reads row
+//     block r through a tensor map over rank r's buffer (a plain, non-multicast TMA load of peer
+//     memory) after that rank's ready flag has reached `epoch`. This is all-gather -> GEMM in one
+//     kernel: local rows are multiplied while remote rows are still arriving.
+//   * push-C (comm_mode 2): the row block of C that rank r owns is stored straight into rank r's
+//     receive slot for this rank (plain 16-byte peer stores from the epilogue registers); a small
+//     reduction kernel on the owner sums the slots. This is GEMM -> reduce-scatter with the
+//     transfer of tile i overlapping the math of tile i+1.
+//   `rotate` shifts the order of the M tiles so that ranks start on different peers.
+//
 // Warp roles (192 threads): warps 0-3 epilogue (TMEM lane quarter = warp index), warp 4 TMA
 // producer, warp 5 MMA issuer + TMEM allocator.
+#include "api.h"
 #include "common.cuh"
 #include "host_utils.h"
 
@@ -44,7 +56,44 @@ struct GemmParams {
   long long ldr;
   long long strideR;
   float beta;
+  // Fused collective (see the header comment). comm_mode 0 = none.
+  int comm_mode;
+  int world, rank, rows_per_rank, rotate;
+  unsigned int epoch;
+  unsigned long long limit_ns;
+  const CUtensorMap* a_maps;      // gather-A: `world` tensor maps in global memory
+  const unsigned int* ready;      // gather-A: this rank's flag slots, one per source rank
+  __nv_bfloat16* c_peer[8];       // push-C: destination of row block r (already offset to my slot)
+  long long c_peer_ld;            // push-C: row pitch of the receive slots, in elements
 };
+
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* addr) {
+  unsigned int value;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(addr) : "memory");
+  return value;
+}
+
+// Bounded wait until `*flag` has reached `epoch` (wrap-safe). On expiry the CTA is told to unwind
+// and the status word records kTimeoutPeerFlag.
+__device__ __forceinline__ bool wait_peer_flag(const unsigned int* flag, unsigned int epoch,
+                                               unsigned long long limit_ns, const WaitCtx& ctx) {
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (static_cast<int>(ld_acquire_sys_u32(flag) - epoch) < 0) {
+    if ((++spins & 0x3f) == 0) {
+      if (*ctx.abort) return false;
+      if (global_timer_ns() - t0 > limit_ns) {
+        *ctx.abort = 1;
+        report_status(ctx.status, kTimeoutPeerFlag);
+        return false;
+      }
+    }
+  }
+  // Data published by the peer was written through the generic proxy; TMA reads it through the
+  // async proxy.
+  asm volatile("fence.proxy.async;" ::: "memory");
+  return true;
+}
 
 template <int BN>
 struct SmemLayout {
@@ -147,6 +196,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     r -= split * (m_tiles * n_tiles);
     mt = r / n_tiles;
     nt = r - mt * n_tiles;
+    if (p.rotate != 0) mt = (mt + p.rotate) % m_tiles;
     int k_lo = 0, k_hi = p.K;
     if (p.k_offsets != nullptr) {
       k_lo = p.k_offsets[batch];
@@ -165,6 +215,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      int ready_src = -1;  // source rank whose rows are known to have arrived
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int batch, mt, nt, kb_begin, kb_count, k0;
         decode(tile, batch, mt, nt, kb_begin, kb_count, k0);
@@ -175,6 +226,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         const int za = p.a_batched ? batch : 0;
         const int zb = p.b_batched ? b_batch : 0;
+        const CUtensorMap* mapA = &tmA;
+        int a_row = mt * BM;
+        if (p.comm_mode == 1) {
+          const int src = a_row / p.rows_per_rank;
+          if (src != ready_src) {
+            if (src != p.rank && !wait_peer_flag(p.ready + src, p.epoch, p.limit_ns, wctx)) {
+              ok = false;
+              break;
+            }
+            ready_src = src;
+          }
+          mapA = p.a_maps + src;
+          a_row -= src * p.rows_per_rank;
+        }
         for (int kb = 0; kb < kb_count; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1;
@@ -191,7 +256,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int j = 0; j < BM / 64; ++j)
               tma_load_3d(sa + j * (BK * 128), &tmA, &full_bar[s], mt * BM + j * 64, k, za);
           } else {
-            tma_load_3d(sa, &tmA, &full_bar[s], k, mt * BM, za);
+            tma_load_3d(sa, mapA, &full_bar[s], k, a_row, za);
           }
           if (p.b_mn) {
 #pragma unroll
@@ -314,13 +379,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               o.w = pack_bf16(__uint_as_float(v[8 * j + 6]) * p.alpha + res[8 * j + 6],
                               __uint_as_float(v[8 * j + 7]) * p.alpha + res[8 * j + 7]);
               const int chunk = h * 4 + j;
-              *reinterpret_cast<uint4*>(my_row + ((chunk ^ (lane & 7)) << 4)) = o;
+              if (p.comm_mode == 2) {
+                // Row block `owner` of C goes to that rank's receive slot: 16-byte peer stores.
+                const int row = row0 + lane;
+                const int owner = row / p.rows_per_rank;
+                const int col = col0 + chunk * 8;
+                if (row < p.M && col < p.N)
+                  *reinterpret_cast<uint4*>(p.c_peer[owner] +
+                                            (long long)(row - owner * p.rows_per_rank) * p.c_peer_ld +
+                                            col) = o;
+              } else {
+                *reinterpret_cast<uint4*>(my_row + ((chunk ^ (lane & 7)) << 4)) = o;
+              }
             }
           }
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && !skip_store && row0 < p.M) {
+        if (lane == 0 && !skip_store && row0 < p.M && p.comm_mode != 2) {
           if (p.reduce)
             tma_reduce_add_3d(&tmC, buf, col0, row0, batch);
           else
@@ -377,6 +453,18 @@ void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int b
                int splits, bool reduce, float alpha, const int* m_tile_batch,
                const int* k_offsets, int64_t a_rows, int64_t b_rows, int num_sms,
                const void* R, int64_t ldr, int64_t strideR, float beta, cudaStream_t stream) {
+  gemm_bf16_comm(A, B, C, M, N, K, batches, a_mn, b_mn, lda, ldb, ldc, strideA, strideB, strideC,
+                 a_batched, b_batched, b_batches, out_f32, splits, reduce, alpha, m_tile_batch,
+                 k_offsets, a_rows, b_rows, num_sms, R, ldr, strideR, beta, nullptr, stream);
+}
+
+void gemm_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, int batches,
+                    bool a_mn, bool b_mn, int64_t lda, int64_t ldb, int64_t ldc, int64_t strideA,
+                    int64_t strideB, int64_t strideC, bool a_batched, bool b_batched, int b_batches,
+                    bool out_f32, int splits, bool reduce, float alpha, const int* m_tile_batch,
+                    const int* k_offsets, int64_t a_rows, int64_t b_rows, int num_sms,
+                    const void* R, int64_t ldr, int64_t strideR, float beta, const GemmComm* comm,
+                    cudaStream_t stream) {
   OB_CHECK(M > 0 && N > 0 && K >= 0 && batches > 0, "gemm_bf16: bad problem size");
   OB_CHECK(!reduce || out_f32, "gemm_bf16: reduce-add epilogue needs an fp32 output");
   OB_CHECK(splits >= 1 && (splits == 1 || reduce), "gemm_bf16: split-K needs the reduce epilogue");
@@ -402,6 +490,47 @@ void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int b
   p.strideR = strideR;
   p.beta = beta;
   OB_CHECK(R == nullptr || !reduce, "gemm_bf16: a residual cannot be combined with the reduce epilogue");
+  p.comm_mode = 0;
+  p.world = 1;
+  p.rank = 0;
+  p.rows_per_rank = M;
+  p.rotate = 0;
+  p.epoch = 0;
+  p.limit_ns = 0;
+  p.a_maps = nullptr;
+  p.ready = nullptr;
+  for (auto& dst : p.c_peer) dst = nullptr;
+  p.c_peer_ld = 0;
+  if (comm != nullptr && comm->mode != 0) {
+    OB_CHECK(comm->world >= 1 && comm->world <= 8 && comm->rank >= 0 && comm->rank < comm->world,
+             "fused collective: bad rank / world");
+    OB_CHECK(batches == 1 && splits == 1 && !reduce && m_tile_batch == nullptr && k_offsets == nullptr,
+             "fused collective: plain 2-D GEMM only");
+    OB_CHECK(M % comm->world == 0 && (M / comm->world) % BM == 0,
+             "fused collective: rows per rank must be a multiple of 128");
+    p.comm_mode = comm->mode;
+    p.world = comm->world;
+    p.rank = comm->rank;
+    p.rows_per_rank = M / comm->world;
+    const int tiles_per_rank = p.rows_per_rank / BM;
+    p.epoch = comm->epoch;
+    p.limit_ns = comm->limit_ns;
+    if (comm->mode == 1) {
+      OB_CHECK(!a_mn && comm->a_maps != nullptr && comm->ready != nullptr,
+               "gather-A needs a K-major A, peer tensor maps and ready flags");
+      p.a_maps = static_cast<const CUtensorMap*>(comm->a_maps);
+      p.ready = comm->ready;
+      p.rotate = comm->rank * tiles_per_rank;  // own rows first: they are already here
+    } else {
+      OB_CHECK(!out_f32 && N % 8 == 0 && R == nullptr, "push-C needs a bf16 output, N % 8 == 0");
+      for (int r = 0; r < comm->world; ++r) {
+        OB_CHECK(comm->c_peer[r] != nullptr, "push-C: missing destination");
+        p.c_peer[r] = static_cast<__nv_bfloat16*>(comm->c_peer[r]);
+      }
+      p.c_peer_ld = comm->c_peer_ld;
+      p.rotate = ((comm->rank + 1) % comm->world) * tiles_per_rank;  // own rows last
+    }
+  }
 
   // Stored shapes: K-major operand is (rows = M or N, inner = K); MN-major is (rows = K, inner =
   // M or N). `a_rows` / `b_rows` give the number of stored rows (the full token count in the
@@ -433,6 +562,14 @@ void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int b
     else
       launch_variant<128, false>(tA, tB, tC, p, grid, stream);
   }
+}
+
+void make_peer_row_maps(const int64_t* bases, int world, int64_t rows, int64_t K, int64_t ld,
+                        void* out) {
+  CUtensorMap* maps = static_cast<CUtensorMap*>(out);
+  for (int r = 0; r < world; ++r)
+    make_tmap_3d(&maps[r], reinterpret_cast<const void*>(bases[r]), TmapDtype::BF16, (uint64_t)K,
+                 (uint64_t)rows, 1, ld, 0, 64, BM, TmapSwizzle::B128);
 }
 
 }  // namespace ob

@@ -76,6 +76,20 @@ def bf16_weight(weight: Tensor) -> Tensor:
     return shadow
 
 
+def _f32_weight(weight: Tensor) -> Tensor:
+    """Contiguous fp32 view of a norm weight; a low-precision parameter (a model converted to bf16
+    for serving) gets a cached fp32 copy that is rebuilt only when the parameter changes."""
+    source = weight.detach()
+    if source.dtype == torch.float32:
+        return source.contiguous()
+    cached = getattr(weight, "_ohara_f32", None)
+    if cached is not None and cached[0] == weight._version and cached[1].device == weight.device:
+        return cached[1]
+    copy = source.float().contiguous()
+    weight._ohara_f32 = (weight._version, copy)
+    return copy
+
+
 def refresh_bf16_weight(weight: Tensor, shadow: Tensor) -> None:
     """Record ``shadow`` as the up-to-date bf16 copy of ``weight`` (called by fused optimizers)."""
     weight._ohara_bf16 = (weight._version, shadow)
@@ -128,6 +142,9 @@ def matmul_nt(a: Tensor, b: Tensor, out: Tensor | None = None, out_dtype=torch.b
     n = b.shape[-2]
     if out is None:
         out = torch.empty((*a.shape[:-2], m, n), device=a.device, dtype=out_dtype)
+    if (m <= 16 and a.dim() == 2 and b.dim() == 2 and alpha == 1.0
+            and out.dtype == torch.bfloat16 and ext().gemv(a, b, out)):
+        return out  # decode-sized input: the weight-streaming kernel beats the tensor-core set-up
     ext().gemm(a, b, out, m, n, k, False, False, 1, False, alpha, None, None)
     return out
 
@@ -224,7 +241,7 @@ class _RMSNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, weight: Tensor, eps: float):
         x16 = (x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)).contiguous()
-        w32 = weight.detach().float().contiguous()
+        w32 = _f32_weight(weight)
         y, rstd = ext().rmsnorm_fwd(x16, None, w32, eps)
         ctx.save_for_backward(x16, w32, rstd)
         ctx.x_dtype = x.dtype
@@ -247,7 +264,7 @@ class _AddRMSNormFn(torch.autograd.Function):
     def forward(ctx, x: Tensor, delta: Tensor, weight: Tensor, eps: float):
         x16 = (x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)).contiguous()
         d16 = (delta if delta.dtype == torch.bfloat16 else delta.to(torch.bfloat16)).contiguous()
-        w32 = weight.detach().float().contiguous()
+        w32 = _f32_weight(weight)
         y, rstd, summed = ext().rmsnorm_fwd(x16, d16, w32, eps)
         ctx.save_for_backward(summed, w32, rstd)
         ctx.dtypes = (x.dtype, delta.dtype, weight.dtype)

@@ -44,7 +44,7 @@ class _RouterLogitsFn(torch.autograd.Function):
         dx = matmul_nn(d16, head) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.needs_input_grad[1]:
-            dw = matmul_tn(d16, x16, out_dtype=torch.float32).to(ctx.weight_dtype)
+            dw = matmul_tn(d16, x16).to(ctx.weight_dtype)
         return dx, dw
 
 

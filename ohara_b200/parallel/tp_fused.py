@@ -1,0 +1,215 @@
+"""Tensor-parallel linears whose collectives run *inside* the tcgen05 GEMM over NVLink peer memory.
+
+Sequence-parallel Megatron-style layers need two patterns, both provided here as autograd ops:
+
+* ``column_parallel_fused``: ``y = all_gather(x_local) @ W_shard^T``. The local rows are copied into
+  a symmetric staging buffer and a flag is published; the GEMM's TMA producer then reads every row
+  block straight from the owning GPU (plain, non-multicast TMA loads of peer memory), starting
+  with its own rows, so remote rows stream in while local tiles are being multiplied. The backward
+  is ``dx_local = reduce_scatter(dy @ W_shard)`` through the other pattern.
+* ``row_parallel_fused``: ``y_local = reduce_scatter(x @ W_shard^T)``. The GEMM epilogue stores each
+  row block of the partial product directly into the owner's receive slot for this rank (16-byte
+  peer stores from the accumulator registers), remote blocks first; after a flag exchange a small
+  kernel on the owner sums the slots. The backward is the first pattern.
+
+Weight gradients need the gathered operand once more; it is pulled from the same staging buffers by
+a copy kernel instead of a second collective call.
+
+Buffers are double-buffered per pattern and recycled under one rule: every staged tensor is
+consumed by a kernel that waits for *all* peers' flags of that epoch, so a rank can be at most one
+fused op ahead of its slowest peer and never overwrites a buffer that is still being read. All
+ranks of the group must issue the same sequence of fused ops. Waits are bounded
+(``wait_limit_s``); a timeout surfaces through ``ops.check_status()``.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from ohara_b200.ops._ext import ext
+from ohara_b200.parallel.peer import SymmetricBuffer
+
+_AG_SLOT = 0   # flag slots [0, world): "my staged rows for epoch e are complete"
+_RS_SLOT = 16  # flag slots [16, 16 + world): "my pushes for epoch e are complete"
+
+
+class StagedRows:
+    """Rows staged in a gather buffer: (workspace buffer index, epoch, shape)."""
+
+    __slots__ = ("buffer", "epoch", "rows", "width")
+
+    def __init__(self, buffer: int, epoch: int, rows: int, width: int) -> None:
+        self.buffer, self.epoch, self.rows, self.width = buffer, epoch, rows, width
+
+
+class TPWorkspace:
+    """Symmetric staging / receive buffers and flags of one tensor-parallel group.
+
+    ``rows_local`` x ``width`` bf16 elements bound the largest per-rank activation block that the
+    fused ops will see (``rows_local`` must be a multiple of 128, the GEMM tile height).
+    """
+
+    def __init__(self, group, rows_local: int, width: int, wait_limit_s: float = 10.0) -> None:
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("fused tensor parallelism supports up to 8 ranks")
+        self.capacity = rows_local * width
+        self.wait_limit_s = wait_limit_s
+        self.flags = SymmetricBuffer(4096, group)
+        self.gather = [SymmetricBuffer(self.capacity * 2, group) for _ in range(2)]
+        self.receive = [SymmetricBuffer(self.capacity * 2 * self.world, group) for _ in range(2)]
+        self.gather_epoch = 0
+        self.scatter_epoch = 0
+        self._maps: dict[tuple[int, int, int], Tensor] = {}
+        self.device = self.flags.device
+        torch.cuda.synchronize()
+        dist.barrier(group=group)  # every rank has opened every buffer before the first signal
+
+    def _flag_address(self, slot: int) -> int:
+        return self.flags.pointers[self.rank] + 4 * slot
+
+    # -- all-gather side ----------------------------------------------------------------------------
+    def stage(self, x_local: Tensor) -> StagedRows:
+        rows, width = x_local.shape
+        if rows % 128 or rows * width > self.capacity:
+            raise ValueError(f"cannot stage a {rows} x {width} block (rows must be a multiple of 128 "
+                             f"and fit {self.capacity} elements)")
+        self.gather_epoch += 1
+        index = self.gather_epoch % 2
+        view = self.gather[index].typed(torch.bfloat16)[: rows * width].view(rows, width)
+        view.copy_(x_local)
+        ext().tp_signal(self.flags.pointers, _AG_SLOT, self.rank, self.gather_epoch)
+        return StagedRows(index, self.gather_epoch, rows, width)
+
+    def gemm_from(self, staged: StagedRows, weight16: Tensor, b_mn: bool, out_features: int) -> Tensor:
+        """``all_gather(staged) @ op(weight16)``: ``(world * rows, out_features)`` bf16."""
+        key = (staged.buffer, staged.rows, staged.width)
+        maps = self._maps.get(key)
+        index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        if maps is None:
+            maps = ext().peer_row_maps(self.gather[staged.buffer].pointers, staged.rows, staged.width,
+                                       staged.width, index)
+            self._maps[key] = maps
+        local = self.gather[staged.buffer].typed(torch.bfloat16)[: staged.rows * staged.width]
+        local = local.view(staged.rows, staged.width)
+        out = torch.empty(staged.rows * self.world, out_features, device=local.device,
+                          dtype=torch.bfloat16)
+        ext().gemm_gather_a(maps, local, weight16, out, b_mn, self._flag_address(_AG_SLOT),
+                            staged.epoch, self.rank, self.world, self.wait_limit_s)
+        return out
+
+    def gather_from(self, staged: StagedRows) -> Tensor:
+        """The gathered ``(world * rows, width)`` tensor itself (operand of a weight gradient)."""
+        out = torch.empty(staged.rows * self.world, staged.width, device=self.device,
+                          dtype=torch.bfloat16)
+        ext().tp_gather_rows(self.gather[staged.buffer].pointers, self._flag_address(_AG_SLOT), out,
+                             self.rank, staged.epoch, self.wait_limit_s)
+        return out
+
+    # -- reduce-scatter side ------------------------------------------------------------------------
+    def gemm_reduce_scatter(self, a16: Tensor, weight16: Tensor, b_mn: bool, out_features: int,
+                            residual: Tensor | None = None) -> Tensor:
+        """``reduce_scatter(a16 @ op(weight16))`` over row blocks: ``(rows / world, out_features)``."""
+        rows = a16.shape[0]
+        if rows % (128 * self.world):
+            raise ValueError("rows per rank must be a multiple of 128")
+        rows_local = rows // self.world
+        if rows_local * out_features > self.capacity:
+            raise ValueError("reduce-scatter block exceeds the workspace")
+        self.scatter_epoch += 1
+        buffer = self.receive[self.scatter_epoch % 2]
+        slot_bytes = rows_local * out_features * 2
+        # Row block r goes to rank r's buffer, into the slot that rank keeps for this rank.
+        destinations = [buffer.pointers[r] + self.rank * slot_bytes for r in range(self.world)]
+        ext().gemm_push_c(a16, weight16, b_mn, destinations, out_features, out_features, self.rank)
+        ext().tp_signal(self.flags.pointers, _RS_SLOT, self.rank, self.scatter_epoch)
+        slots = buffer.typed(torch.bfloat16)[: self.world * rows_local * out_features]
+        slots = slots.view(self.world, rows_local, out_features)
+        return ext().tp_reduce_slots(slots, self._flag_address(_RS_SLOT), residual,
+                                     self.scatter_epoch, self.wait_limit_s)
+
+
+def _bf16(t: Tensor) -> Tensor:
+    t = t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)
+    return t.contiguous()
+
+
+class _ColumnParallelFused(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_local: Tensor, weight: Tensor, workspace: TPWorkspace) -> Tensor:
+        from ohara_b200.ops import bf16_weight
+
+        x16 = _bf16(x_local)
+        staged = workspace.stage(x16)
+        out = workspace.gemm_from(staged, bf16_weight(weight), False, weight.shape[0])
+        ctx.save_for_backward(x16, weight)
+        ctx.workspace = workspace
+        ctx.x_dtype = x_local.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        from ohara_b200.ops import bf16_weight, matmul_tn
+
+        x16, weight = ctx.saved_tensors
+        ws = ctx.workspace
+        dy16 = _bf16(dy)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # dx_local = reduce_scatter(dy @ W): W stored (out_local, in) is the MN-major B here.
+            dx = ws.gemm_reduce_scatter(dy16, bf16_weight(weight), True, weight.shape[1])
+            dx = dx.to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            gathered = ws.gather_from(ws.stage(x16))
+            dw = matmul_tn(dy16, gathered).to(weight.dtype)
+        return dx, dw, None
+
+
+class _RowParallelFused(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, workspace: TPWorkspace) -> Tensor:
+        from ohara_b200.ops import bf16_weight
+
+        x16 = _bf16(x)
+        out = workspace.gemm_reduce_scatter(x16, bf16_weight(weight), False, weight.shape[0])
+        ctx.save_for_backward(x16, weight)
+        ctx.workspace = workspace
+        ctx.x_dtype = x.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dy_local: Tensor):
+        from ohara_b200.ops import bf16_weight, matmul_tn
+
+        x16, weight = ctx.saved_tensors
+        ws = ctx.workspace
+        staged = ws.stage(_bf16(dy_local))
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # dx = all_gather(dy) @ W: W stored (out, in_local) is the MN-major B here.
+            dx = ws.gemm_from(staged, bf16_weight(weight), True, weight.shape[1]).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:
+            dw = matmul_tn(ws.gather_from(staged), x16).to(weight.dtype)
+        elif not ctx.needs_input_grad[0]:
+            ws.gather_from(staged)  # every staged block must be consumed (buffer recycling rule)
+        return dx, dw, None
+
+
+def column_parallel_fused(x_local: Tensor, weight: Tensor, workspace: TPWorkspace) -> Tensor:
+    """``all_gather(x_local) @ weight.T`` for 2-D ``x_local (rows_local, in)`` and a weight shard
+    ``(out_local, in)``; returns ``(world * rows_local, out_local)`` bf16."""
+    return _ColumnParallelFused.apply(x_local, weight, workspace)
+
+
+def row_parallel_fused(x: Tensor, weight: Tensor, workspace: TPWorkspace) -> Tensor:
+    """``reduce_scatter(x @ weight.T)`` for 2-D ``x (rows, in_local)`` and a weight shard
+    ``(out, in_local)``; returns this rank's ``(rows / world, out)`` bf16 block."""
+    return _RowParallelFused.apply(x, weight, workspace)
+
+
+def fused_supported(rows_local: int, in_features: int, out_features: int) -> bool:
+    return rows_local % 128 == 0 and in_features % 8 == 0 and out_features % 8 == 0

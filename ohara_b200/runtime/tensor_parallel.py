@@ -161,6 +161,19 @@ class _ParallelLinear(nn.Module):
         self.weight = nn.Parameter(shard, requires_grad=source.weight.requires_grad)
         self.weight.tensor_parallel_dim = shard_dim
         self.bias = None
+        # Set by ``attach_fused_workspace``: symmetric NVLink buffers shared by the layers of a group.
+        self.workspace = None
+
+    def _use_fused(self, x: Tensor, rows_local: int) -> bool:
+        """Fused collective path: CUDA bf16 fast path, no bias, 128-row aligned token blocks."""
+        if self.workspace is None or self.bias is not None or not x.is_cuda:
+            return False
+        from ohara_b200 import ops
+        from ohara_b200.parallel.tp_fused import fused_supported
+
+        width = max(self.weight.shape[0] if self.shard_dim == 1 else self.weight.shape[1], 1)
+        return (ops.fast_path(x) and fused_supported(rows_local, *self.weight.shape[::-1])
+                and rows_local * width <= self.workspace.capacity)
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, "
@@ -180,6 +193,12 @@ class ColumnParallelLinear(_ParallelLinear):
     def forward(self, x: Tensor) -> Tensor:
         from ohara_b200 import ops
 
+        if self.sequence_parallel and self._use_fused(x, x.numel() // x.shape[-1]):
+            from ohara_b200.parallel.tp_fused import column_parallel_fused
+
+            # Token blocks are gathered along dim 0: (B_local, T, in) -> (world * B_local, T, out).
+            y = column_parallel_fused(x.reshape(-1, x.shape[-1]), self.weight, self.workspace)
+            return y.view(x.shape[0] * self.tp_world, *x.shape[1:-1], self.weight.shape[0])
         if self.sequence_parallel:
             x = _GatherSequence.apply(x, self.group)
         else:
@@ -199,6 +218,15 @@ class RowParallelLinear(_ParallelLinear):
     def forward(self, x: Tensor) -> Tensor:
         from ohara_b200 import ops
 
+        rows = x.numel() // x.shape[-1]
+        if (self.sequence_parallel and rows % self.tp_world == 0 and x.shape[0] % self.tp_world == 0
+                and self._use_fused(x, rows // self.tp_world)):
+            from ohara_b200.parallel.tp_fused import row_parallel_fused
+
+            # The summed product is scattered in token blocks along dim 0:
+            # (B, T, in_local) -> (B / world, T, out).
+            y = row_parallel_fused(x.reshape(-1, x.shape[-1]), self.weight, self.workspace)
+            return y.view(x.shape[0] // self.tp_world, *x.shape[1:-1], self.weight.shape[0])
         y = ops.linear(x, self.weight, None)
         if self.sequence_parallel:
             y = _ScatterSequence.apply(y, self.group)
@@ -236,6 +264,19 @@ def apply_tensor_parallel(module: nn.Module, tp_group, plan: TensorParallelPlan,
         )
     module.tensor_parallel_degree = world
     return module
+
+
+def attach_fused_workspace(module: nn.Module, workspace) -> int:
+    """Give every sharded linear of ``module`` the group's :class:`TPWorkspace`, which switches
+    its sequence-parallel collectives to the in-GEMM NVLink path. In that mode activations are
+    sharded over dim 0 in whole token blocks (``(B / tp, T, d)`` between the parallel regions).
+    Returns the number of layers attached."""
+    attached = 0
+    for child in module.modules():
+        if isinstance(child, _ParallelLinear):
+            child.workspace = workspace
+            attached += 1
+    return attached
 
 
 def gather_tensor_parallel_state(module: nn.Module, tp_group) -> dict[str, Tensor]:

@@ -191,3 +191,19 @@ def test_cached_decoding_matches_a_full_forward():
             stepped = torch.cat(pieces, dim=1).float()
             tolerance = 0.25 if int8 else 0.08
             assert (stepped - full).abs().max() < tolerance * full.abs().max(), int8
+
+
+@pytest.mark.parametrize("rows", [1, 3, 8, 13, 16])
+@pytest.mark.parametrize("features,width", [(768, 768), (2048, 768), (768, 2048), (50304, 768), (100, 136)])
+def test_skinny_gemm_matches_fp32(rows, features, width):
+    from ohara_b200.ops import matmul_nt
+    from ohara_b200.ops._ext import ext
+
+    torch.manual_seed(rows)
+    x = torch.randn(rows, width, device="cuda").bfloat16()
+    w = torch.randn(features, width, device="cuda").bfloat16()
+    out = torch.empty(rows, features, device="cuda", dtype=torch.bfloat16)
+    assert ext().gemv(x, w, out), "decode-sized shapes must take the weight-streaming kernel"
+    ref = x.float() @ w.float().t()
+    assert (out.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+    assert torch.equal(matmul_nt(x, w), out)
