@@ -53,6 +53,10 @@ void tp_gather_rows(const int64_t* bases, const unsigned int* flags, void* out,
                     int64_t bytes_per_rank, int rank, int world, unsigned int epoch,
                     unsigned long long limit_ns, cudaStream_t stream);
 
+// stream_ops.cpp
+void stream_wait_value32(cudaStream_t stream, uint64_t addr, uint32_t value);
+void stream_write_value32(cudaStream_t stream, uint64_t addr, uint32_t value);
+
 // elementwise.cu
 void rmsnorm_fwd(const void* x, const void* delta, const float* w, void* y, void* x_out, float* rstd,
                  int rows, int d, float eps, cudaStream_t stream);

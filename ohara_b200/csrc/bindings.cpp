@@ -760,6 +760,14 @@ void gemm_push_c(const Tensor& a, const Tensor& b, bool b_mn, const std::vector<
                      nullptr, 0, 0, 0.f, &comm, current_stream());
 }
 
+// Stream-ordered "wait until the int32 at `addr` is >= value" / "store value" on the current stream.
+void stream_wait_value32(int64_t addr, int64_t value) {
+  ob::stream_wait_value32(current_stream(), (uint64_t)addr, (uint32_t)value);
+}
+void stream_write_value32(int64_t addr, int64_t value) {
+  ob::stream_write_value32(current_stream(), (uint64_t)addr, (uint32_t)value);
+}
+
 void tp_signal(const std::vector<int64_t>& pads, int64_t slot_base, int64_t rank, int64_t epoch) {
   ob::tp_signal(pads.data(), (int)slot_base, (int)rank, (int)pads.size(), (unsigned int)epoch,
                 current_stream());
@@ -845,6 +853,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("peer_row_maps", &peer_row_maps);
   m.def("gemm_gather_a", &gemm_gather_a);
   m.def("gemm_push_c", &gemm_push_c);
+  m.def("stream_wait_value32", &stream_wait_value32);
+  m.def("stream_write_value32", &stream_write_value32);
   m.def("tp_signal", &tp_signal);
   m.def("tp_reduce_slots", &tp_reduce_slots);
   m.def("tp_gather_rows", &tp_gather_rows);

@@ -379,24 +379,33 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               o.w = pack_bf16(__uint_as_float(v[8 * j + 6]) * p.alpha + res[8 * j + 6],
                               __uint_as_float(v[8 * j + 7]) * p.alpha + res[8 * j + 7]);
               const int chunk = h * 4 + j;
-              if (p.comm_mode == 2) {
-                // Row block `owner` of C goes to that rank's receive slot: 16-byte peer stores.
-                const int row = row0 + lane;
-                const int owner = row / p.rows_per_rank;
-                const int col = col0 + chunk * 8;
-                if (row < p.M && col < p.N)
-                  *reinterpret_cast<uint4*>(p.c_peer[owner] +
-                                            (long long)(row - owner * p.rows_per_rank) * p.c_peer_ld +
-                                            col) = o;
-              } else {
-                *reinterpret_cast<uint4*>(my_row + ((chunk ^ (lane & 7)) << 4)) = o;
-              }
+              *reinterpret_cast<uint4*>(my_row + ((chunk ^ (lane & 7)) << 4)) = o;
             }
           }
         }
+        if (p.comm_mode == 2) {
+          // Row block `owner` of C goes to that rank's receive slot. The 32 x 128-byte chunk is
+          // read back from the staging buffer so that eight lanes store one whole 128-byte row
+          // segment: full-line writes over NVLink instead of 16-byte fragments.
+          __syncwarp();
+          const int owner = row0 / p.rows_per_rank;
+          __nv_bfloat16* slot = p.c_peer[owner] + (long long)(row0 - owner * p.rows_per_rank) * p.c_peer_ld;
+          const int sub = lane & 7;
+          const int col = col0 + sub * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = (lane >> 3) + 4 * i;
+            const uint4 v = *reinterpret_cast<const uint4*>(buf + r * 128 + ((sub ^ (r & 7)) << 4));
+            if (row0 + r < p.M && col < p.N)
+              *reinterpret_cast<uint4*>(slot + (long long)r * p.c_peer_ld + col) = v;
+          }
+          __syncwarp();
+          ++store_iter;
+          continue;
+        }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && !skip_store && row0 < p.M && p.comm_mode != 2) {
+        if (lane == 0 && !skip_store && row0 < p.M) {
           if (p.reduce)
             tma_reduce_add_3d(&tmC, buf, col0, row0, batch);
           else

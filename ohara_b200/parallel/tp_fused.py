@@ -3,17 +3,17 @@
 Sequence-parallel Megatron-style layers need two patterns, both provided here as autograd ops:
 
 * ``column_parallel_fused``: ``y = all_gather(x_local) @ W_shard^T``. The local rows are copied into
-  a symmetric staging buffer and a flag is published; the GEMM's TMA producer then reads every row
-  block straight from the owning GPU (plain, non-multicast TMA loads of peer memory), starting
-  with its own rows, so remote rows stream in while local tiles are being multiplied. The backward
-  is ``dx_local = reduce_scatter(dy @ W_shard)`` through the other pattern.
+  a symmetric staging buffer and a flag is published; the copy engines pull the peers' rows while
+  the GEMM is already multiplying its own rows, and the GEMM's TMA producer waits on a per-block
+  "arrived" flag just before it first needs a remote block. The backward is
+  ``dx_local = reduce_scatter(dy @ W_shard)`` through the other pattern.
 * ``row_parallel_fused``: ``y_local = reduce_scatter(x @ W_shard^T)``. The GEMM epilogue stores each
   row block of the partial product directly into the owner's receive slot for this rank (16-byte
   peer stores from the accumulator registers), remote blocks first; after a flag exchange a small
   kernel on the owner sums the slots. The backward is the first pattern.
 
-Weight gradients need the gathered operand once more; it is pulled from the same staging buffers by
-a copy kernel instead of a second collective call.
+Weight gradients need the gathered operand itself; it is the buffer the copies landed in, so no
+second collective is issued.
 
 Buffers are double-buffered per pattern and recycled under one rule: every staged tensor is
 consumed by a kernel that waits for *all* peers' flags of that epoch, so a rank can be at most one
@@ -36,12 +36,13 @@ _RS_SLOT = 16  # flag slots [16, 16 + world): "my pushes for epoch e are complet
 
 
 class StagedRows:
-    """Rows staged in a gather buffer: (workspace buffer index, epoch, shape)."""
+    """Rows staged for an all-gather: workspace buffer index, epoch, shape and the event that
+    marks the arrival of every peer's rows in the local gathered buffer."""
 
-    __slots__ = ("buffer", "epoch", "rows", "width")
+    __slots__ = ("buffer", "epoch", "rows", "width", "arrived")
 
-    def __init__(self, buffer: int, epoch: int, rows: int, width: int) -> None:
-        self.buffer, self.epoch, self.rows, self.width = buffer, epoch, rows, width
+    def __init__(self, buffer: int, epoch: int, rows: int, width: int, arrived) -> None:
+        self.buffer, self.epoch, self.rows, self.width, self.arrived = buffer, epoch, rows, width, arrived
 
 
 class TPWorkspace:
@@ -49,6 +50,14 @@ class TPWorkspace:
 
     ``rows_local`` x ``width`` bf16 elements bound the largest per-rank activation block that the
     fused ops will see (``rows_local`` must be a multiple of 128, the GEMM tile height).
+
+    All-gather side: each rank copies its rows into a symmetric staging buffer and publishes a
+    flag. A side stream then pulls every peer's rows into a local gathered buffer with the copy
+    engines (no SM is used): a stream-ordered wait on the peer's flag, the peer-to-peer copy, and a
+    stream-ordered write of a local "arrived" flag. The GEMM on the main stream multiplies its own
+    rows first and waits (bounded, in the TMA producer) on the arrived flag of each remote block
+    just before it needs it, so the transfers overlap the math and every remote row crosses NVLink
+    exactly once however many column tiles re-read it.
     """
 
     def __init__(self, group, rows_local: int, width: int, wait_limit_s: float = 10.0) -> None:
@@ -62,15 +71,22 @@ class TPWorkspace:
         self.flags = SymmetricBuffer(4096, group)
         self.gather = [SymmetricBuffer(self.capacity * 2, group) for _ in range(2)]
         self.receive = [SymmetricBuffer(self.capacity * 2 * self.world, group) for _ in range(2)]
+        self.device = self.flags.device
+        self.gathered = [torch.empty(self.world * self.capacity, device=self.device,
+                                     dtype=torch.bfloat16) for _ in range(2)]
+        self.arrived_flags = torch.zeros(64, device=self.device, dtype=torch.int32)
+        self.copy_stream = torch.cuda.Stream(device=self.device, priority=-1)
         self.gather_epoch = 0
         self.scatter_epoch = 0
         self._maps: dict[tuple[int, int, int], Tensor] = {}
-        self.device = self.flags.device
         torch.cuda.synchronize()
         dist.barrier(group=group)  # every rank has opened every buffer before the first signal
 
     def _flag_address(self, slot: int) -> int:
         return self.flags.pointers[self.rank] + 4 * slot
+
+    def _gathered_blocks(self, index: int, rows: int, width: int) -> Tensor:
+        return self.gathered[index][: self.world * rows * width].view(self.world, rows, width)
 
     # -- all-gather side ----------------------------------------------------------------------------
     def stage(self, x_local: Tensor) -> StagedRows:
@@ -79,36 +95,55 @@ class TPWorkspace:
             raise ValueError(f"cannot stage a {rows} x {width} block (rows must be a multiple of 128 "
                              f"and fit {self.capacity} elements)")
         self.gather_epoch += 1
-        index = self.gather_epoch % 2
-        view = self.gather[index].typed(torch.bfloat16)[: rows * width].view(rows, width)
-        view.copy_(x_local)
-        ext().tp_signal(self.flags.pointers, _AG_SLOT, self.rank, self.gather_epoch)
-        return StagedRows(index, self.gather_epoch, rows, width)
+        epoch, index = self.gather_epoch, self.gather_epoch % 2
+        mine = self.gather[index].typed(torch.bfloat16)[: rows * width].view(rows, width)
+        mine.copy_(x_local)
+        ext().tp_signal(self.flags.pointers, _AG_SLOT, self.rank, epoch)
+        main = torch.cuda.current_stream(self.device)
+        staged_event = torch.cuda.Event()
+        staged_event.record(main)
+        # The side stream may touch the gathered buffer only after everything already queued on
+        # the main stream (the previous readers of this buffer) has finished.
+        self.copy_stream.wait_event(staged_event)
+        blocks = self._gathered_blocks(index, rows, width)
+        with torch.cuda.stream(self.copy_stream):
+            for hop in range(1, self.world):
+                src = (self.rank + hop) % self.world
+                ext().stream_wait_value32(self._flag_address(_AG_SLOT + src), epoch)
+                remote = self.gather[index].typed(torch.bfloat16, rank=src)[: rows * width]
+                blocks[src].copy_(remote.view(rows, width))
+                ext().stream_write_value32(self.arrived_flags.data_ptr() + 4 * src, epoch)
+            blocks[self.rank].copy_(mine)  # completes the gathered tensor for weight gradients
+            arrived = torch.cuda.Event()
+            arrived.record(self.copy_stream)
+        return StagedRows(index, epoch, rows, width, arrived)
 
     def gemm_from(self, staged: StagedRows, weight16: Tensor, b_mn: bool, out_features: int) -> Tensor:
         """``all_gather(staged) @ op(weight16)``: ``(world * rows, out_features)`` bf16."""
         key = (staged.buffer, staged.rows, staged.width)
         maps = self._maps.get(key)
         index = self.device.index if self.device.index is not None else torch.cuda.current_device()
-        if maps is None:
-            maps = ext().peer_row_maps(self.gather[staged.buffer].pointers, staged.rows, staged.width,
-                                       staged.width, index)
-            self._maps[key] = maps
         local = self.gather[staged.buffer].typed(torch.bfloat16)[: staged.rows * staged.width]
         local = local.view(staged.rows, staged.width)
+        if maps is None:
+            blocks = self._gathered_blocks(staged.buffer, staged.rows, staged.width)
+            # own rows straight from the staging buffer, remote rows from where the copies land
+            bases = [local.data_ptr() if r == self.rank else blocks[r].data_ptr()
+                     for r in range(self.world)]
+            maps = ext().peer_row_maps(bases, staged.rows, staged.width, staged.width, index)
+            self._maps[key] = maps
         out = torch.empty(staged.rows * self.world, out_features, device=local.device,
                           dtype=torch.bfloat16)
-        ext().gemm_gather_a(maps, local, weight16, out, b_mn, self._flag_address(_AG_SLOT),
+        ext().gemm_gather_a(maps, local, weight16, out, b_mn, self.arrived_flags.data_ptr(),
                             staged.epoch, self.rank, self.world, self.wait_limit_s)
         return out
 
     def gather_from(self, staged: StagedRows) -> Tensor:
-        """The gathered ``(world * rows, width)`` tensor itself (operand of a weight gradient)."""
-        out = torch.empty(staged.rows * self.world, staged.width, device=self.device,
-                          dtype=torch.bfloat16)
-        ext().tp_gather_rows(self.gather[staged.buffer].pointers, self._flag_address(_AG_SLOT), out,
-                             self.rank, staged.epoch, self.wait_limit_s)
-        return out
+        """The gathered ``(world * rows, width)`` tensor itself (operand of a weight gradient).
+        It aliases a workspace buffer that is recycled two stagings later: consume it at once."""
+        torch.cuda.current_stream(self.device).wait_event(staged.arrived)
+        blocks = self._gathered_blocks(staged.buffer, staged.rows, staged.width)
+        return blocks.view(self.world * staged.rows, staged.width)
 
     # -- reduce-scatter side ------------------------------------------------------------------------
     def gemm_reduce_scatter(self, a16: Tensor, weight16: Tensor, b_mn: bool, out_features: int,
@@ -194,8 +229,6 @@ class _RowParallelFused(torch.autograd.Function):
             dx = ws.gemm_from(staged, bf16_weight(weight), True, weight.shape[1]).to(ctx.x_dtype)
         if ctx.needs_input_grad[1]:
             dw = matmul_tn(ws.gather_from(staged), x16).to(weight.dtype)
-        elif not ctx.needs_input_grad[0]:
-            ws.gather_from(staged)  # every staged block must be consumed (buffer recycling rule)
         return dx, dw, None
 
 
