@@ -250,8 +250,10 @@ def test_grouped_moe_matches_reference_dispatch():
     x = bf(2, 200, 128)
     flat = x.reshape(-1, 128)
     idx, wts, _, _ = moe._route(flat)
+    from ohara_b200.ops.grouped import grouped_swiglu_experts
+
     with torch.autocast("cuda", dtype=torch.bfloat16):
-        got = moe._dispatch_grouped(flat, idx, wts)
+        got = grouped_swiglu_experts(flat, idx, wts, moe.w_gate, moe.w_up, moe.w_down)
     ref = moe._dispatch_reference(flat.float(), idx, wts.float())
     assert rel_err(got, ref) < 3e-2
 
