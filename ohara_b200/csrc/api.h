@@ -53,6 +53,21 @@ void tp_gather_rows(const int64_t* bases, const unsigned int* flags, void* out,
                     int64_t bytes_per_rank, int rank, int world, unsigned int epoch,
                     unsigned long long limit_ns, cudaStream_t stream);
 
+// ep.cu
+void ep_publish_counts(const int64_t* tables, const int* counts, int experts, int rank, int world,
+                       cudaStream_t stream);
+void ep_plan(const int* table, const int* indices, int experts, int world, int rank, int tile,
+             int num_tiles, int capacity_rows, int64_t pairs, int* pair_base, int* k_offsets,
+             int* tile_expert, int* fill_begin, int* fill_end, int* cursor, int* rows_used,
+             int* dest_rank, int* dest_row, cudaStream_t stream);
+void ep_zero_fill(const int* fill_begin, const int* fill_end, void* buffer, int local_experts, int d,
+                  int capacity_rows, cudaStream_t stream);
+void ep_push_rows(const void* src, const int* dest_rank, const int* dest_row, const float* scale,
+                  const int64_t* buffers, int world, int64_t pairs, int k, int d, cudaStream_t stream);
+void ep_pull_combine(const int64_t* buffers, int world, const int* dest_rank, const int* dest_row,
+                     const float* scale, const void* other, void* out, float* dot, int64_t tokens,
+                     int k, int d, cudaStream_t stream);
+
 // stream_ops.cpp
 void stream_wait_value32(cudaStream_t stream, uint64_t addr, uint32_t value);
 void stream_write_value32(cudaStream_t stream, uint64_t addr, uint32_t value);
@@ -106,6 +121,10 @@ void peer_reduce_scatter_mean(const int64_t* grads, const int64_t* pads, float* 
                               cudaStream_t stream);
 void peer_all_gather(const int64_t* weights, const int64_t* pads, int64_t region_bytes, int rank,
                      int world, uint32_t epoch, uint64_t limit_ns, cudaStream_t stream);
+
+void peer_all_reduce(const int64_t* bufs, const int64_t* pads, void* out, int64_t n, bool bf16,
+                     float scale, int rank, int world, uint32_t epoch, uint64_t limit_ns,
+                     cudaStream_t stream);
 
 // cross_entropy.cu
 void cross_entropy_rows(void* logits, const int64_t* targets, float* row_loss, float* row_lse,

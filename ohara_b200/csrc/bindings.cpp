@@ -687,6 +687,98 @@ void sample_tokens(const Tensor& logits, int64_t valid_vocab, double temperature
                     done_ptr, optional_f32(workspace, "workspace"), current_stream());
 }
 
+// -- expert parallelism ------------------------------------------------------------------------------
+void ep_publish_counts(const std::vector<int64_t>& tables, const Tensor& counts, int64_t rank) {
+  check_i32(counts, "counts");
+  const c10::cuda::CUDAGuard guard(counts.device());
+  ob::ep_publish_counts(tables.data(), counts.data_ptr<int>(), (int)counts.numel(), (int)rank,
+                        (int)tables.size(), current_stream());
+}
+
+// From the exchanged (world, E) count table and this rank's int32 indices (N, k):
+// (dest_rank (N*k), dest_row (N*k), tile_expert, k_offsets (E/world + 1), fill (2, E/world),
+//  rows_used (1)). `capacity_rows` is the size of every rank's padded buffer.
+std::vector<Tensor> ep_plan(const Tensor& table, const Tensor& indices, int64_t rank, int64_t world,
+                            int64_t tile, int64_t capacity_rows) {
+  check_i32(table, "table");
+  check_i32(indices, "indices");
+  const c10::cuda::CUDAGuard guard(indices.device());
+  const int64_t experts = table.numel() / world, local = experts / world, pairs = indices.numel();
+  TORCH_CHECK(experts * world == table.numel() && local * world == experts && capacity_rows % tile == 0);
+  auto opts = indices.options();
+  const int64_t num_tiles = capacity_rows / tile;
+  Tensor dest_rank = torch::empty({pairs}, opts), dest_row = torch::empty({pairs}, opts);
+  Tensor tile_expert = torch::empty({num_tiles}, opts), k_offsets = torch::empty({local + 1}, opts);
+  Tensor fill = torch::empty({2, local}, opts), rows_used = torch::empty({1}, opts);
+  Tensor scratch = torch::empty({2 * experts}, opts);  // pair bases, placement cursors
+  ob::ep_plan(table.data_ptr<int>(), indices.data_ptr<int>(), (int)experts, (int)world, (int)rank,
+              (int)tile, (int)num_tiles, (int)capacity_rows, pairs, scratch.data_ptr<int>(),
+              k_offsets.data_ptr<int>(), tile_expert.data_ptr<int>(), fill.data_ptr<int>(),
+              fill.data_ptr<int>() + local, scratch.data_ptr<int>() + experts,
+              rows_used.data_ptr<int>(), dest_rank.data_ptr<int>(), dest_row.data_ptr<int>(),
+              current_stream());
+  return {dest_rank, dest_row, tile_expert, k_offsets, fill, rows_used};
+}
+
+void ep_zero_fill(const Tensor& fill, Tensor& buffer, int64_t d, int64_t capacity_rows) {
+  check_i32(fill, "fill");
+  check_bf16(buffer, "buffer");
+  const c10::cuda::CUDAGuard guard(buffer.device());
+  const int64_t local = fill.size(1);
+  ob::ep_zero_fill(fill.data_ptr<int>(), fill.data_ptr<int>() + local, buffer.data_ptr(), (int)local,
+                   (int)d, (int)capacity_rows, current_stream());
+}
+
+void ep_push_rows(const Tensor& src, const Tensor& dest_rank, const Tensor& dest_row,
+                  const c10::optional<Tensor>& scale, const std::vector<int64_t>& buffers, int64_t k) {
+  check_bf16(src, "src");
+  check_i32(dest_rank, "dest_rank");
+  check_i32(dest_row, "dest_row");
+  TORCH_CHECK(src.is_contiguous() && src.dim() == 2 && dest_row.numel() == src.size(0) * k);
+  const float* scale_ptr = nullptr;
+  if (scale.has_value()) {
+    check_f32(*scale, "scale");
+    TORCH_CHECK(scale->is_contiguous() && scale->numel() == dest_row.numel());
+    scale_ptr = scale->data_ptr<float>();
+  }
+  const c10::cuda::CUDAGuard guard(src.device());
+  ob::ep_push_rows(src.data_ptr(), dest_rank.data_ptr<int>(), dest_row.data_ptr<int>(), scale_ptr,
+                   buffers.data(), (int)buffers.size(), dest_row.numel(), (int)k, (int)src.size(1),
+                   current_stream());
+}
+
+std::vector<Tensor> ep_pull_combine(const std::vector<int64_t>& buffers, const Tensor& dest_rank,
+                                    const Tensor& dest_row, const c10::optional<Tensor>& scale,
+                                    const c10::optional<Tensor>& other, int64_t k, int64_t d,
+                                    bool want_out) {
+  check_i32(dest_rank, "dest_rank");
+  check_i32(dest_row, "dest_row");
+  const c10::cuda::CUDAGuard guard(dest_row.device());
+  const int64_t tokens = dest_row.numel() / k;
+  const float* scale_ptr = nullptr;
+  if (scale.has_value()) {
+    check_f32(*scale, "scale");
+    TORCH_CHECK(scale->is_contiguous() && scale->numel() == dest_row.numel());
+    scale_ptr = scale->data_ptr<float>();
+  }
+  auto bf16_opts = dest_row.options().dtype(torch::kBFloat16);
+  Tensor out, dot;
+  const void* other_ptr = nullptr;
+  if (other.has_value()) {
+    check_bf16(*other, "other");
+    TORCH_CHECK(other->is_contiguous() && other->numel() == tokens * d);
+    other_ptr = other->data_ptr();
+    dot = torch::empty({tokens, k}, dest_row.options().dtype(torch::kFloat32));
+  }
+  if (want_out) out = torch::empty({tokens, d}, bf16_opts);
+  ob::ep_pull_combine(buffers.data(), (int)buffers.size(), dest_rank.data_ptr<int>(),
+                      dest_row.data_ptr<int>(), scale_ptr, other_ptr,
+                      want_out ? out.data_ptr() : nullptr,
+                      other.has_value() ? dot.data_ptr<float>() : nullptr, tokens, (int)k, (int)d,
+                      current_stream());
+  return {out, dot};
+}
+
 // -- fused tensor-parallel collectives ---------------------------------------------------------------
 // Tensor maps over `bases` (one (rows, K) K-major bf16 matrix of pitch `ld` per rank), uploaded to
 // the device: the A operand of gemm_gather_a. Build once per buffer set and keep the tensor.
@@ -806,6 +898,18 @@ void tp_gather_rows(const std::vector<int64_t>& bases, int64_t flags_addr, Tenso
                      (unsigned long long)(limit_s * 1e9), current_stream());
 }
 
+// out = scale * sum over ranks of the symmetric buffers `bufs` (first out.numel() elements).
+void peer_all_reduce(const std::vector<int64_t>& bufs, const std::vector<int64_t>& pads, Tensor& out,
+                     double scale, int64_t rank, int64_t epoch, double limit_s) {
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && bufs.size() == pads.size());
+  const bool bf16 = out.scalar_type() == torch::kBFloat16;
+  TORCH_CHECK(bf16 || out.scalar_type() == torch::kFloat32, "all-reduce supports bf16 and fp32");
+  const c10::cuda::CUDAGuard guard(out.device());
+  ob::peer_all_reduce(bufs.data(), pads.data(), out.data_ptr(), out.numel(), bf16, (float)scale,
+                      (int)rank, (int)bufs.size(), (uint32_t)epoch, (uint64_t)(limit_s * 1e9),
+                      current_stream());
+}
+
 std::vector<int64_t> status(bool clear) {
   int out[4];
   ob::status_read(out, clear);
@@ -841,6 +945,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("peer_barrier", &peer_barrier);
   m.def("peer_reduce_scatter_mean", &peer_reduce_scatter_mean);
   m.def("peer_all_gather", &peer_all_gather);
+  m.def("peer_all_reduce", &peer_all_reduce);
   m.def("gemv", &gemv);
   m.def("route_topk", &route_topk);
   m.def("moe_plan", &moe_plan);
@@ -850,6 +955,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope_append", &rope_append);
   m.def("decode_attention", &decode_attention);
   m.def("sample_tokens", &sample_tokens);
+  m.def("ep_publish_counts", &ep_publish_counts);
+  m.def("ep_plan", &ep_plan);
+  m.def("ep_zero_fill", &ep_zero_fill);
+  m.def("ep_push_rows", &ep_push_rows);
+  m.def("ep_pull_combine", &ep_pull_combine);
   m.def("peer_row_maps", &peer_row_maps);
   m.def("gemm_gather_a", &gemm_gather_a);
   m.def("gemm_push_c", &gemm_push_c);

@@ -118,6 +118,25 @@ all_gather_kernel(PeerTable weights, PeerTable pads, int64_t region_bytes, int r
   }
 }
 
+// One-shot all-reduce for small tensors (decode-time tensor parallelism, scalars, norms): every
+// rank has written its vector into its copy of a symmetric buffer; after the flag barrier each rank
+// reads all `world` copies and sums them in fp32. One NVLink round trip, no ring, no chunking.
+template <typename T>
+__global__ void __launch_bounds__(512)
+all_reduce_oneshot_kernel(PeerTable bufs, PeerTable pads, T* __restrict__ out, int64_t n, int rank,
+                          int world, float scale, uint32_t epoch, uint64_t limit_ns, int* status) {
+  if (!peer_barrier(pads, rank, world, epoch, limit_ns, status)) return;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int r = 0; r < world; ++r) {
+      const int src = (rank + r) % world;
+      acc += static_cast<float>(static_cast<const T*>(bufs.ptr[src])[i]);
+    }
+    out[i] = static_cast<T>(acc * scale);
+  }
+}
+
 }  // namespace
 
 // ---- host API -------------------------------------------------------------------------------
@@ -175,6 +194,22 @@ void peer_all_gather(const int64_t* weights, const int64_t* pads, int64_t region
   all_gather_kernel<<<blocks, 512, 0, stream>>>(make_table(weights, world), make_table(pads, world),
                                                 region_bytes, rank, world, epoch, limit_ns,
                                                 status_ptr());
+  OB_LAUNCH_CHECK();
+}
+
+void peer_all_reduce(const int64_t* bufs, const int64_t* pads, void* out, int64_t n, bool bf16,
+                     float scale, int rank, int world, uint32_t epoch, uint64_t limit_ns,
+                     cudaStream_t stream) {
+  if (n == 0) return;
+  const int blocks = (int)std::min<int64_t>((n + 511) / 512, device_sm_count() * 2);
+  if (bf16)
+    all_reduce_oneshot_kernel<__nv_bfloat16><<<blocks, 512, 0, stream>>>(
+        make_table(bufs, world), make_table(pads, world), static_cast<__nv_bfloat16*>(out), n, rank,
+        world, scale, epoch, limit_ns, status_ptr());
+  else
+    all_reduce_oneshot_kernel<float><<<blocks, 512, 0, stream>>>(
+        make_table(bufs, world), make_table(pads, world), static_cast<float*>(out), n, rank, world,
+        scale, epoch, limit_ns, status_ptr());
   OB_LAUNCH_CHECK();
 }
 

@@ -67,6 +67,9 @@ class GroupedMoE(QuantileBalancedRouter):
         self.capacity_factor = capacity_factor
         self.aux_loss: Tensor | None = None
         self.dropped_pairs: Tensor | None = None
+        # Set by ``shard_experts``: the NVLink workspace of the expert-parallel group. The stacked
+        # expert weights then hold only this rank's ``num_experts / world`` experts.
+        self.ep_workspace = None
 
         self.w_gate = nn.Parameter(torch.empty(num_experts, dim, hidden_dim))
         self.w_up = nn.Parameter(torch.empty(num_experts, dim, hidden_dim))
@@ -140,7 +143,14 @@ class GroupedMoE(QuantileBalancedRouter):
             indices, weights, logits, alpha = self._route(flat_x)
         if self.capacity_factor is not None:
             weights = self._apply_capacity(indices.long(), weights)
-        if kernels:
+        if self.ep_workspace is not None:
+            if counts is None:
+                raise RuntimeError("expert parallelism needs the CUDA bf16 path (router kernels)")
+            from ohara_b200.parallel.ep import expert_parallel_swiglu
+
+            out = expert_parallel_swiglu(flat_x, indices, weights, counts, self.w_gate, self.w_up,
+                                         self.w_down, self.ep_workspace)
+        elif kernels:
             out = grouped_swiglu_experts(flat_x, indices, weights, self.w_gate, self.w_up,
                                          self.w_down, counts)
         else:
@@ -159,6 +169,28 @@ class GroupedMoE(QuantileBalancedRouter):
             else:
                 self._record_load(indices.detach())
         return out.view(batch, seq, dim)
+
+    # -- expert parallelism ----------------------------------------------------------------
+    @torch.no_grad()
+    def shard_experts(self, workspace) -> None:
+        """Keep only this rank's slice of the stacked expert weights and route the dispatch /
+        combine through ``workspace`` (:class:`ohara_b200.parallel.ep.EPWorkspace`). The router,
+        its bias and the shared experts stay replicated. Gradients of the expert weights already
+        sum the contributions of every rank's tokens, so they are scaled by ``1 / world`` to match
+        a loss averaged over the ranks, and the parameters are tagged ``expert_parallel`` so that a
+        data-parallel wrapper leaves them alone."""
+        world, rank = workspace.world, workspace.rank
+        if self.num_experts % world or workspace.num_experts != self.num_experts:
+            raise ValueError("the workspace does not match this layer's expert count")
+        local = self.num_experts // world
+        for name in ("w_gate", "w_up", "w_down"):
+            full = getattr(self, name)
+            shard = nn.Parameter(full[rank * local : (rank + 1) * local].detach().clone(),
+                                 requires_grad=full.requires_grad)
+            shard.expert_parallel = True
+            shard.register_hook(lambda grad, scale=1.0 / world: grad * scale)
+            setattr(self, name, shard)
+        self.ep_workspace = workspace
 
     # -- init --------------------------------------------------------------------------------
     @torch.no_grad()

@@ -51,6 +51,8 @@ class PeerRuntime:
     """Signal pads + a monotonically increasing barrier epoch shared by all collectives of a
     group. Every rank must issue the same sequence of collectives."""
 
+    ONE_SHOT_BYTES = 1 << 20
+
     def __init__(self, group=None, wait_limit_s: float = 10.0) -> None:
         self.group = group
         self.world = dist.get_world_size(group)
@@ -58,6 +60,7 @@ class PeerRuntime:
         self.wait_limit_s = wait_limit_s
         self.pads = SymmetricBuffer(4096, group)
         self.epoch = 0
+        self._reduce_buffers = None
         # Everyone has opened everyone's pad before the first kernel may signal.
         dist.barrier(group=group)
 
@@ -67,6 +70,32 @@ class PeerRuntime:
 
     def barrier(self) -> None:
         ext().peer_barrier(self.pads.pointers, self.rank, self.next_epoch(), self.wait_limit_s)
+
+    def all_reduce_(self, tensor: torch.Tensor, average: bool = False) -> torch.Tensor:
+        """In-place one-shot all-reduce of a small contiguous bf16 / fp32 CUDA tensor: every rank
+        writes its values into a symmetric buffer and, after the flag barrier, sums all copies
+        itself (a single NVLink round trip). Falls back to the c10d collective for tensors larger
+        than ``ONE_SHOT_BYTES``, where a bandwidth-optimal algorithm wins."""
+        nbytes = tensor.numel() * tensor.element_size()
+        if (nbytes > self.ONE_SHOT_BYTES or not tensor.is_contiguous()
+                or tensor.dtype not in (torch.bfloat16, torch.float32)):
+            dist.all_reduce(tensor, group=self.group)
+            if average:
+                tensor /= self.world
+            return tensor
+        if self._reduce_buffers is None:
+            self._reduce_buffers = [SymmetricBuffer(self.ONE_SHOT_BYTES, self.group) for _ in range(2)]
+            self._reduce_count = 0
+            dist.barrier(group=self.group)
+        self._reduce_count += 1
+        # Two buffers alternate: a rank can only be one call ahead of a peer (the barrier inside
+        # the kernel), so the buffer it overwrites was last read two calls ago.
+        buffer = self._reduce_buffers[self._reduce_count % 2]
+        buffer.typed(tensor.dtype)[: tensor.numel()].copy_(tensor.view(-1))
+        ext().peer_all_reduce(buffer.pointers, self.pads.pointers, tensor,
+                              1.0 / self.world if average else 1.0, self.rank, self.next_epoch(),
+                              self.wait_limit_s)
+        return tensor
 
 
 class PeerBuffers:
