@@ -129,16 +129,18 @@ class Attention(nn.Module):
         # this module (fewer output features) needs no patching.
         heads = self.query.weight.shape[0] // self.head_dim
         kv_heads = self.key.weight.shape[0] // self.head_dim
-        q = self.query(x).view(batch, seq_len, heads, self.head_dim)
-        k = self.key(x).view(batch, seq_len, kv_heads, self.head_dim)
-        v = self.value(x).view(batch, seq_len, kv_heads, self.head_dim)
+        # -1: with sequence-parallel tensor parallelism the projections gather the token blocks of
+        # every rank, so they return more sequences than came in.
+        q = self.query(x).view(-1, seq_len, heads, self.head_dim)
+        k = self.key(x).view(-1, seq_len, kv_heads, self.head_dim)
+        v = self.value(x).view(-1, seq_len, kv_heads, self.head_dim)
         if (kv_cache is not None and seq_len == 1 and len(freqs_cis) == 4
                 and decode_ops.fused_decode_supported(q, kv_cache) and v.dtype == q.dtype):
             # Decode step: RoPE + cache append in one kernel, then attention over the cache in
             # place (no mask tensor, no head expansion, int8 dequantised on the fly).
             q = kv_cache.append_decode(q, k, v, freqs_cis[2], freqs_cis[3], position_ids)
             out = decode_ops.decode_attention(q, kv_cache, position_ids)
-            return self.res_dropout(self.proj(out.reshape(batch, 1, heads * self.head_dim)))
+            return self.res_dropout(self.proj(out.reshape(-1, 1, heads * self.head_dim)))
         if freqs_cis[0] is None:
             raise ValueError("a device-side position needs the fused decode kernels: bf16 "
                              "activations on CUDA, head_dim 64 or 128, a bf16 or int8 cache")
@@ -150,7 +152,7 @@ class Attention(nn.Module):
             q, k.to(q.dtype), v.to(q.dtype), causal=True,
             dropout_p=self.attn_dropout.p, training=self.training,
         )
-        out = out.reshape(batch, seq_len, heads * self.head_dim)
+        out = out.reshape(-1, seq_len, heads * self.head_dim)
         return self.res_dropout(self.proj(out))
 
 

@@ -107,6 +107,30 @@ class EPWorkspace:
         return out, dots
 
 
+class LazyEPWorkspace:
+    """Creates the group's :class:`EPWorkspace` at the first routed batch, when the number of
+    (token, expert) pairs per rank is known: ``capacity_rows`` is ``capacity_factor`` times a
+    rank's fair share of rows plus the per-expert tile padding. All ranks reach that point
+    together (the layers run in lock step)."""
+
+    def __init__(self, group, num_experts: int, width: int, capacity_factor: float = 2.0,
+                 wait_limit_s: float = 10.0) -> None:
+        self.group, self.num_experts, self.width = group, num_experts, width
+        self.capacity_factor, self.wait_limit_s = capacity_factor, wait_limit_s
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.workspace: EPWorkspace | None = None
+
+    def materialize(self, pairs_per_rank: int) -> EPWorkspace:
+        if self.workspace is None:
+            local = self.num_experts // self.world
+            rows = int(self.capacity_factor * pairs_per_rank) + local * TILE
+            rows = (rows + TILE - 1) // TILE * TILE
+            self.workspace = EPWorkspace(self.group, self.num_experts, rows, self.width,
+                                         self.wait_limit_s)
+        return self.workspace
+
+
 class _DispatchFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x16: Tensor, plan: DispatchPlan, workspace: EPWorkspace) -> Tensor:
@@ -152,6 +176,8 @@ def expert_parallel_swiglu(flat_x: Tensor, indices: Tensor, weights: Tensor, cou
 
     x16 = flat_x if flat_x.dtype == torch.bfloat16 else flat_x.to(torch.bfloat16)
     indices = indices if indices.dtype == torch.int32 else indices.int()
+    if isinstance(workspace, LazyEPWorkspace):
+        workspace = workspace.materialize(indices.numel())
     plan = workspace.plan(indices, counts)
     x_pad = _DispatchFn.apply(x16.contiguous(), plan, workspace)
     gate = grouped_linear(x_pad, w_gate, plan.tile_expert, plan.k_offsets)

@@ -168,6 +168,21 @@ class TPWorkspace:
                                      self.scatter_epoch, self.wait_limit_s)
 
 
+class LazyTPWorkspace:
+    """Creates the group's :class:`TPWorkspace` at the first fused call, when the per-rank token
+    count is known. Every rank reaches that call at the same point of the same step (the layers
+    run in lock step), so the collective buffer set-up inside is safe."""
+
+    def __init__(self, group, width: int, wait_limit_s: float = 10.0) -> None:
+        self.group, self.width, self.wait_limit_s = group, width, wait_limit_s
+        self.workspace: TPWorkspace | None = None
+
+    def materialize(self, rows_local: int) -> TPWorkspace:
+        if self.workspace is None:
+            self.workspace = TPWorkspace(self.group, rows_local, self.width, self.wait_limit_s)
+        return self.workspace
+
+
 def _bf16(t: Tensor) -> Tensor:
     t = t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)
     return t.contiguous()

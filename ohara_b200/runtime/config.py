@@ -40,3 +40,6 @@ class EngineConfig:
     # Use the peer-memory (NVLink) fused collectives where available; False keeps every
     # collective on the c10d backend (the A/B baseline and the only choice on CPU/gloo).
     fused_collectives: bool = True
+    # Expert parallelism: rows a rank can receive for its experts in one layer, as a multiple of
+    # its fair share; pairs beyond it are dropped.
+    expert_capacity_factor: float = 2.0

@@ -32,6 +32,7 @@ from .config import EngineConfig
 from .enums import Backend, PrecisionMode, ReduceType, StrategyType
 from .strategy import BaseStrategy, DDPStrategy, FSDPStrategy, SingleStrategy
 from .tensor_parallel import (
+    attach_fused_workspace,
     TensorParallelPlan,
     apply_tensor_parallel,
     gather_tensor_parallel_state,
@@ -53,7 +54,7 @@ class _DeviceDataLoader:
             sampler.set_epoch(self.epoch)
             self.epoch += 1
         for batch in self.dataloader:
-            yield self.engine.to_device(batch)
+            yield self.engine.to_device(self.engine.local_batch(batch))
 
     def __len__(self) -> int:
         return len(self.dataloader)
@@ -113,12 +114,13 @@ class OharaEngine:
 
     @property
     def data_parallel_rank(self) -> int:
-        """Rank used to shard input data; tensor/context-parallel peers share it."""
-        return self.topology.dp_rank
+        """Rank used to shard input data; tensor/context-parallel peers share it, expert-parallel
+        peers do not (they route their own tokens)."""
+        return self.topology.dp_rank * self.topology.ep + self.topology.ep_rank
 
     @property
     def data_parallel_world_size(self) -> int:
-        return self.topology.dp_world_size
+        return self.topology.dp_world_size * self.topology.ep
 
     @property
     def strategy(self) -> BaseStrategy:
@@ -168,13 +170,16 @@ class OharaEngine:
 
         strategy = self.config.strategy
         if strategy == StrategyType.AUTO:
-            strategy = StrategyType.DDP if self.topology.dp_enabled else StrategyType.SINGLE
+            replicas = self.topology.dp_enabled or self.topology.ep > 1
+            strategy = StrategyType.DDP if replicas else StrategyType.SINGLE
         if strategy in (StrategyType.DDP, StrategyType.FSDP) and not self.topology.distributed_enabled:
             strategy = StrategyType.SINGLE if strategy == StrategyType.DDP else strategy
         self._build_groups()
         data_parallel = strategy in (StrategyType.DDP, StrategyType.FSDP)
-        self._dp_world_size = self.topology.dp_world_size if data_parallel else 1
-        self._dp_rank = self.topology.dp_rank if data_parallel else 0
+        # expert-parallel peers route their own tokens: for data they count as replicas
+        self._dp_world_size = self.topology.dp_world_size * self.topology.ep if data_parallel else 1
+        self._dp_rank = (self.topology.dp_rank * self.topology.ep + self.topology.ep_rank
+                         if data_parallel else 0)
         if strategy == StrategyType.DDP:
             self._strategy = DDPStrategy(init_sync=not self.topology.tp_enabled)
         elif strategy == StrategyType.FSDP:
@@ -197,6 +202,7 @@ class OharaEngine:
             return
         dims = {
             "dp": (("dp_replicate", "dp_shard"), topo.dp_world_size),
+            "dp_ep": (("dp_replicate", "dp_shard", "ep"), topo.dp_world_size * topo.ep),
             "tp": (("tp",), topo.tp),
             "cp": (("cp",), topo.cp),
             "ep": (("ep",), topo.ep),
@@ -232,11 +238,54 @@ class OharaEngine:
             else:
                 module = module.to(self._device)
         module = self._maybe_apply_tensor_parallel(module)
-        module = self._strategy.setup_module(
-            module, device=self._device, process_group=self._groups.get("dp")
-        )
+        ignored = self._maybe_apply_expert_parallel(module)
+        if ignored:
+            from torch.nn.parallel import DistributedDataParallel
+
+            DistributedDataParallel._set_params_and_buffers_to_ignore_for_model(module, ignored)
+        group = self._groups.get("dp_ep") if self.topology.ep > 1 else self._groups.get("dp")
+        module = self._strategy.setup_module(module, device=self._device, process_group=group)
         self._module = module
         return module
+
+    def _maybe_apply_expert_parallel(self, module: torch.nn.Module) -> list[str]:
+        """With ``ep > 1`` every grouped mixture-of-experts layer keeps ``E / ep`` experts and
+        exchanges tokens over NVLink peer memory; expert-parallel peers see different data, so for
+        all other parameters they are ordinary data-parallel replicas. Returns the names of the
+        expert parameters, which the data-parallel wrapper must leave alone (their gradients are
+        averaged over the ``dp`` group separately)."""
+        if self.topology.ep <= 1:
+            return []
+        from ohara_b200.modules.moe_grouped import GroupedMoE
+        from ohara_b200.parallel.ep import LazyEPWorkspace
+
+        if self._device.type != "cuda":
+            raise RuntimeError("expert parallelism needs CUDA devices")
+        if isinstance(self._strategy, FSDPStrategy):
+            raise NotImplementedError("expert parallelism is not wired for the sharded optimizer; "
+                                      "use the ddp strategy")
+        layers = [m for m in module.modules() if isinstance(m, GroupedMoE)]
+        if not layers:
+            raise ValueError("ep > 1 but the model has no grouped mixture-of-experts layer")
+        shared: dict[tuple[int, int], LazyEPWorkspace] = {}
+        for layer in layers:
+            key = (layer.num_experts, layer.dim)
+            if key not in shared:
+                shared[key] = LazyEPWorkspace(self._groups.get("ep"), layer.num_experts, layer.dim,
+                                              self.config.expert_capacity_factor)
+            layer.shard_experts(shared[key])
+        self._expert_parallel = True
+        return [name for name, p in module.named_parameters() if getattr(p, "expert_parallel", False)]
+
+    def sync_expert_gradients(self, model: torch.nn.Module) -> None:
+        """Average expert gradients over the data-parallel replicas of each expert shard."""
+        if not getattr(self, "_expert_parallel", False) or self.topology.dp_world_size <= 1:
+            return
+        group, size = self._groups.get("dp"), self.topology.dp_world_size
+        for param in model.parameters():
+            if getattr(param, "expert_parallel", False) and param.grad is not None:
+                dist.all_reduce(param.grad, group=group)
+                param.grad.div_(size)
 
     def prepare_optimizers(self, *optimizers: Optimizer):
         self.launch()
@@ -277,10 +326,57 @@ class OharaEngine:
         if not self.topology.tp_enabled:
             return module
         plan = self._resolve_tensor_parallel_plan(module)
-        return apply_tensor_parallel(
+        module = apply_tensor_parallel(
             module, self._groups.get("tp"), plan, tp_rank=self.topology.tp_rank,
             tp_world=self.topology.tp,
         )
+        if (plan.sequence_parallel and self.config.fused_collectives
+                and self._device.type == "cuda" and self.topology.tp <= 8):
+            # Sequence-parallel layout with the collectives inside the GEMMs: between the
+            # parallel regions every tensor-parallel rank keeps B / tp whole sequences (the
+            # dataloader wrapper hands each rank its slice), the column-parallel projections
+            # gather them and the row-parallel ones scatter the sums back.
+            from ohara_b200.parallel.tp_fused import LazyTPWorkspace
+
+            width = int(getattr(getattr(module, "config", None), "hidden_size", 0)) or max(
+                p.shape[-1] for p in module.parameters() if p.dim() == 2)
+            attach_fused_workspace(module, LazyTPWorkspace(self._groups.get("tp"), width))
+            self._tp_batch_sharding = True
+            self._tp_grads_synced = True
+        return module
+
+    def local_batch(self, batch: Any) -> Any:
+        """With sequence-parallel tensor parallelism each rank of a tensor-parallel group works
+        on its own slice of the group's batch between the parallel regions: take that slice of
+        every tensor of ``batch`` (dim 0). Otherwise the batch is returned unchanged."""
+        if not getattr(self, "_tp_batch_sharding", False):
+            return batch
+        tp, rank = self.topology.tp, self.topology.tp_rank
+        if isinstance(batch, torch.Tensor):
+            if batch.dim() == 0:
+                return batch
+            if batch.shape[0] % tp:
+                raise ValueError(f"batch of {batch.shape[0]} does not split over tp={tp}")
+            per = batch.shape[0] // tp
+            return batch[rank * per : (rank + 1) * per]
+        if isinstance(batch, dict):
+            return {k: self.local_batch(v) for k, v in batch.items()}
+        if isinstance(batch, (tuple, list)):
+            return type(batch)(self.local_batch(v) for v in batch)
+        return batch
+
+    def sync_tensor_parallel_gradients(self, model: torch.nn.Module) -> None:
+        """Under the sequence-parallel layout the ranks of a tensor-parallel group see different
+        tokens, so parameters that are *not* sharded (norms, embeddings, output head, routers)
+        hold partial gradients: sum them over the group. Sharded parameters are already complete,
+        their backward collectives mixed every rank's tokens in."""
+        if not getattr(self, "_tp_batch_sharding", False) or self._tp_grads_synced:
+            return
+        group = self._groups.get("tp")
+        for param in model.parameters():
+            if param.grad is not None and not hasattr(param, "tensor_parallel_dim"):
+                dist.all_reduce(param.grad, group=group)
+        self._tp_grads_synced = True
 
     # -- data ----------------------------------------------------------------------------------
     def _replace_sampler(self, dataloader: DataLoader) -> DataLoader:
@@ -356,6 +452,10 @@ class OharaEngine:
         return nullcontext()
 
     def backward(self, loss: torch.Tensor) -> None:
+        if getattr(self, "_tp_batch_sharding", False):
+            # every rank's loss is a mean over its own slice: the group mean is their average
+            loss = loss / self.topology.tp
+            self._tp_grads_synced = False
         if self._scaler.is_enabled():
             self._scaler.scale(loss).backward()
         else:
@@ -370,12 +470,46 @@ class OharaEngine:
     def clip_gradients(self, model: torch.nn.Module, optimizer: Optimizer, max_norm: float) -> torch.Tensor:
         if self._scaler.is_enabled():
             self._scaler.unscale_(optimizer)
+        self.sync_tensor_parallel_gradients(model)
+        self.sync_expert_gradients(model)
         clip = getattr(optimizer, "clip_grad_norm_", None)
         if callable(clip):  # sharded optimizers know how to form the global norm
             return clip(model, max_norm)
+        if self.launched and (self.topology.tp_enabled or self.topology.ep > 1):
+            return self._clip_sharded(model, max_norm)
         return torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=max_norm)
 
+    def _clip_sharded(self, model: torch.nn.Module, max_norm: float) -> torch.Tensor:
+        """Global gradient norm when parameters are sharded: squared norms of tensor-parallel
+        shards are summed over the ``tp`` group, those of expert shards over the ``ep`` group,
+        replicated parameters are counted once; every rank then applies the same coefficient."""
+        zero = torch.zeros((), device=self._device)
+        parts = {"tp": zero.clone(), "ep": zero.clone(), "whole": zero.clone()}
+        grads = []
+        for p in model.parameters():
+            if p.grad is None:
+                continue
+            kind = ("tp" if hasattr(p, "tensor_parallel_dim")
+                    else "ep" if getattr(p, "expert_parallel", False) else "whole")
+            parts[kind] = parts[kind] + p.grad.float().square().sum()
+            grads.append(p.grad)
+        if not grads:
+            return zero
+        if self.topology.tp_enabled:
+            dist.all_reduce(parts["tp"], group=self._groups.get("tp"))
+        if self.topology.ep > 1:
+            dist.all_reduce(parts["ep"], group=self._groups.get("ep"))
+        total = (parts["tp"] + parts["ep"] + parts["whole"]).sqrt()
+        scale = (max_norm / (total + 1e-6)).clamp(max=1.0)
+        for grad in grads:
+            grad.mul_(scale.to(grad.dtype))
+        return total
+
     def optimizer_step(self, optimizer: Optimizer) -> None:
+        module = getattr(self, "_module", None)
+        if module is not None:
+            self.sync_tensor_parallel_gradients(module)
+            self.sync_expert_gradients(module)
         if self._scaler.is_enabled():
             self._scaler.step(optimizer)
             self._scaler.update()

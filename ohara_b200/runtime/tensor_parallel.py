@@ -169,11 +169,18 @@ class _ParallelLinear(nn.Module):
         if self.workspace is None or self.bias is not None or not x.is_cuda:
             return False
         from ohara_b200 import ops
-        from ohara_b200.parallel.tp_fused import fused_supported
+        from ohara_b200.parallel.tp_fused import LazyTPWorkspace, fused_supported
 
+        if not (ops.fast_path(x) and fused_supported(rows_local, *self.weight.shape[::-1])):
+            return False
+        if isinstance(self.workspace, LazyTPWorkspace):
+            self.workspace = self.workspace.materialize(rows_local)
         width = max(self.weight.shape[0] if self.shard_dim == 1 else self.weight.shape[1], 1)
-        return (ops.fast_path(x) and fused_supported(rows_local, *self.weight.shape[::-1])
-                and rows_local * width <= self.workspace.capacity)
+        if rows_local * width > self.workspace.capacity:
+            raise ValueError(
+                f"a block of {rows_local} x {width} does not fit the tensor-parallel workspace "
+                f"({self.workspace.capacity} elements, sized at the first fused call)")
+        return True
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, "

@@ -125,3 +125,74 @@ def test_one_shot_all_reduce_matches_c10d(tmp_path):
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "AR_OK" in proc.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_engine_expert_parallel_llama_matches_single_device(tmp_path):
+    """ep=2 through the engine (experts sharded, everything else data parallel): loss and gradients
+    of a training step must match the unsharded model on the concatenated batch."""
+    script = """
+        import torch, torch.distributed as dist
+        from ohara_b200 import ops
+        from ohara_b200.models.llama import Config, Llama
+        from ohara_b200.runtime import EngineConfig, OharaEngine, ParallelConfig
+
+        engine = OharaEngine(EngineConfig(parallel=ParallelConfig(ep=2)))
+        engine.launch()
+        rank, world = dist.get_rank(), dist.get_world_size()
+        assert engine.data_parallel_world_size == 2 and engine.data_parallel_rank == rank
+        cfg = Config(vocab_size=512, max_sequence_length=128, hidden_size=256, intermediate_size=128,
+                     num_attention_heads=4, num_hidden_layers=2, dropout=0.0, weight_tying=False,
+                     moe_num_experts=8, moe_experts_per_tok=2, moe_grouped=True, moe_num_shared_experts=1)
+        def build():
+            torch.manual_seed(0)
+            model = Llama(cfg)
+            with torch.no_grad():
+                for block in model.layers:
+                    block.ff.w_down.normal_(std=0.05)
+                    block.ff.shared_down.weight.normal_(std=0.05)
+            return model
+        reference = build().cuda().train()
+        model = engine.prepare(build()).train()
+        inner = model.module
+        assert inner.layers[0].ff.w_gate.shape[0] == 4
+
+        torch.manual_seed(1)
+        ids = torch.randint(0, 512, (world, 2, 129), device="cuda")
+        dist.broadcast(ids, src=0)
+        mine = ids[rank]
+        with engine.autocast_context():
+            loss = model(mine[:, :-1], targets=mine[:, 1:], loss_scale=1.0 / mine[:, 1:].numel())
+        engine.backward(loss)
+        engine.sync_expert_gradients(model)
+        torch.cuda.synchronize(); ops.check_status()
+        everything = ids.view(-1, 129)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            ref_loss = reference(everything[:, :-1], targets=everything[:, 1:],
+                                 loss_scale=1.0 / everything[:, 1:].numel())
+        ref_loss.backward()
+        total = loss.detach().clone()
+        dist.all_reduce(total)
+        assert abs(float(total) / world - float(ref_loss)) < 2e-2 * abs(float(ref_loss))
+        wanted = dict(reference.named_parameters())
+        def close(a, b, tol, rows_allowed=0.02):
+            a, b = a.float().reshape(-1, a.shape[-1]), b.float().reshape(-1, b.shape[-1])
+            bad = ((a - b).abs().amax(dim=1) > tol * (b.abs().max().item() + 1e-8)).float().mean().item()
+            return bad <= rows_allowed
+        for name, param in inner.named_parameters():
+            want = wanted[name].grad
+            if getattr(param, "expert_parallel", False):
+                want = want[rank * 4:(rank + 1) * 4]
+            assert close(param.grad, want, 8e-2), name
+        if rank == 0:
+            print("EP_ENGINE_OK")
+        engine.close()
+    """
+    path = tmp_path / "worker.py"
+    path.write_text(textwrap.dedent(script))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(29850 + os.getpid() % 40), str(path)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "EP_ENGINE_OK" in proc.stdout

@@ -142,3 +142,72 @@ def test_fused_tensor_parallel_mlp_matches_single_device(tmp_path):
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "TP_FUSED_OK" in proc.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_engine_sequence_parallel_llama_matches_single_device(tmp_path):
+    """A Llama prepared by the engine with tp=2 and the sequence-parallel plan (fused collectives)
+    must produce the loss and the gradients of the unsharded model on the whole batch."""
+    script = """
+        import torch, torch.distributed as dist
+        from ohara_b200 import ops
+        from ohara_b200.models.llama import Config, Llama
+        from ohara_b200.runtime import EngineConfig, OharaEngine, ParallelConfig, TensorParallelPlan
+
+        engine = OharaEngine(EngineConfig(parallel=ParallelConfig(tp=2),
+                                          tensor_parallel=TensorParallelPlan.llama_default(2, True)))
+        engine.launch()
+        rank = dist.get_rank()
+        cfg = Config(vocab_size=512, max_sequence_length=128, hidden_size=256, intermediate_size=512,
+                     num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=2, dropout=0.0,
+                     weight_tying=False)
+        torch.manual_seed(0)
+        reference = Llama(cfg).cuda()
+        torch.manual_seed(0)
+        model = engine.prepare(Llama(cfg))
+        assert getattr(engine, "_tp_batch_sharding", False)
+
+        torch.manual_seed(1)
+        ids = torch.randint(0, 512, (4, 129), device="cuda")
+        dist.broadcast(ids, src=0)
+        x, y = ids[:, :-1], ids[:, 1:]
+        for step in range(2):
+            xl, yl = engine.local_batch((x, y))
+            assert xl.shape[0] == 2
+            with engine.autocast_context():
+                loss = model(xl, targets=yl, loss_scale=1.0 / yl.numel())
+            engine.backward(loss)
+            engine.sync_tensor_parallel_gradients(model)
+            torch.cuda.synchronize(); ops.check_status()
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                ref_loss = reference(x, targets=y, loss_scale=1.0 / y.numel())
+            ref_loss.backward()
+            total = loss.detach().clone() / 2
+            dist.all_reduce(total)
+            assert abs(float(total) - float(ref_loss)) < 2e-2 * abs(float(ref_loss)), (float(total), float(ref_loss))
+
+            full = engine.full_state_dict(model)
+            for key, value in reference.state_dict().items():
+                assert torch.equal(full[key].cpu(), value.cpu()), key
+            ref_grads = dict(reference.named_parameters())
+            def close(a, b, tol=6e-2):
+                return (a.float() - b.float()).abs().max().item() <= tol * (b.float().abs().max().item() + 1e-8)
+            for name, param in model.named_parameters():
+                want = ref_grads[name].grad
+                dim = getattr(param, "tensor_parallel_dim", None)
+                if dim is not None:
+                    want = want.chunk(2, dim=dim)[rank]
+                assert close(param.grad, want), name
+            model.zero_grad(); reference.zero_grad()
+        if rank == 0:
+            print("SP_LLAMA_OK")
+        engine.close()
+    """
+    path = tmp_path / "worker.py"
+    path.write_text(textwrap.dedent(script))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(29700 + os.getpid() % 90), str(path)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "SP_LLAMA_OK" in proc.stdout
