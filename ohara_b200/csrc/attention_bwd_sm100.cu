@@ -281,26 +281,29 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       return true;
     };
 
+    // Per-query statistics (64 lse + 64 delta per tile) live in shared memory, double buffered by
+    // iteration parity. The values of tile it+1 are fetched from global memory while tile it is
+    // being processed, so their latency is off the critical path.
+    auto fetch_stat = [&](int it) -> float {
+      int h, tq0;
+      iter_coords(it, h, tq0);
+      const int idx = threadIdx.x;  // 0..127
+      const int tq = tq0 + (idx & 63);
+      const size_t base = ((size_t)b * p.H + h) * p.T;
+      if (idx < 64) return (tq < p.T) ? p.lse[base + tq] * kLog2e : INFINITY;
+      return (tq < p.T) ? p.delta[base + tq] : 0.f;
+    };
+    if (n_iters > 0) sStats[threadIdx.x] = fetch_stat(0);
     for (int it = 0; it < n_iters; ++it) {
       int h, tq0;
       iter_coords(it, h, tq0);
-      // Per-query statistics for this tile -> shared memory (double buffered by iteration parity).
       float* stats = sStats + (it & 1) * 128;
-      {
-        const int idx = threadIdx.x;  // 0..127
-        const int tq = tq0 + (idx & 63);
-        const size_t base = ((size_t)b * p.H + h) * p.T;
-        float val;
-        if (idx < 64)
-          val = (tq < p.T) ? p.lse[base + tq] * kLog2e : INFINITY;
-        else
-          val = (tq < p.T) ? p.delta[base + tq] : 0.f;
-        stats[idx] = val;
-      }
+      // Publishes stats(it) and retires every reader of the other buffer (tile it-1).
       if (!group_sync()) {
         ok = false;
         break;
       }
+      const float next_stat = (it + 1 < n_iters) ? fetch_stat(it + 1) : 0.f;
       if (!mbar_wait(s_full, it & 1, wctx, kTimeoutTmemFull)) {
         ok = false;
         break;
@@ -349,6 +352,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           break;
         }
       }
+      sStats[((it + 1) & 1) * 128 + threadIdx.x] = next_stat;  // visible after the next group_sync
       uint8_t* prow = sP + row * 128;
       uint8_t* dsrow = sdS + row * 128;
 #pragma unroll

@@ -121,6 +121,9 @@ class Attention(nn.Module):
         self.proj = Linear(self.head_dim * self.num_attention_heads, d, cfg.bias)
         self.attn_dropout = nn.Dropout(cfg.dropout)
         self.res_dropout = nn.Dropout(cfg.dropout)
+        # Context parallelism: set by ``Llama.enable_context_parallel``. The sequence is then
+        # sharded in contiguous chunks over the group and this module exchanges keys / values.
+        self.cp_workspace = None
 
     def forward(self, x: Tensor, mask: Tensor | None, freqs_cis, kv_cache: KVCache | None = None,
                 position_ids: int | None = None) -> Tensor:
@@ -145,6 +148,13 @@ class Attention(nn.Module):
             raise ValueError("a device-side position needs the fused decode kernels: bf16 "
                              "activations on CUDA, head_dim 64 or 128, a bf16 or int8 cache")
         q, k = apply_rope(q, k, freqs_cis[:2])
+        if self.cp_workspace is not None and kv_cache is None:
+            from ohara_b200.parallel.cp import context_parallel_attention
+
+            bf = torch.bfloat16
+            out = context_parallel_attention(q.to(bf), k.to(bf), v.to(bf), self.cp_workspace)
+            out = out.reshape(-1, seq_len, heads * self.head_dim)
+            return self.res_dropout(self.proj(out))
         if kv_cache is not None:
             assert position_ids is not None
             k, v = kv_cache.forward(k, v.to(k.dtype), position_ids)
@@ -251,6 +261,15 @@ class Llama(nn.Module):
             raise ValueError("input exceeds max_sequence_length")
         return start
 
+    def enable_context_parallel(self, workspace, rank: int, world: int) -> None:
+        """Shard the sequence over a context-parallel group: this rank then receives chunk
+        ``rank`` of every sequence (``T / world`` tokens), rotary positions are the global ones
+        and every attention layer exchanges keys / values through ``workspace``
+        (:class:`ohara_b200.parallel.cp.CPWorkspace` or its lazy form)."""
+        self._cp = (rank, world)
+        for block in self.layers:
+            block.attn.cp_workspace = workspace
+
     def _rope_tables_f32(self) -> tuple[Tensor, Tensor]:
         """Full fp32 rotary tables for the serving kernels (a cached copy when the buffers were
         converted to a lower precision together with the model)."""
@@ -281,6 +300,11 @@ class Llama(nn.Module):
             return ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[0]
         start = self._check_inputs(x, kv_cache, position_ids)
         seq = x.size(1)
+        cp = getattr(self, "_cp", None)
+        if cp is not None and kv_cache is None:
+            start = cp[0] * seq  # this rank holds chunk `rank` of the sequence
+            if cp[1] * seq > self.config.max_sequence_length:
+                raise ValueError("the full sequence exceeds max_sequence_length")
         h = ops.embedding(x, self.token_emb.weight)
         freqs = (self.freq_cos[start : start + seq], self.freq_sin[start : start + seq])
         if kv_cache is not None and x.is_cuda and seq == 1:

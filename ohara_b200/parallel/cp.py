@@ -105,6 +105,22 @@ class CPWorkspace:
         return total.to(dkv_local.dtype)
 
 
+class LazyCPWorkspace:
+    """Creates the group's :class:`CPWorkspace` at the first attention call, when the size of a
+    key/value chunk is known (all ranks get there together)."""
+
+    def __init__(self, group, wait_limit_s: float = 10.0) -> None:
+        self.group, self.wait_limit_s = group, wait_limit_s
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.workspace: CPWorkspace | None = None
+
+    def materialize(self, chunk_elements: int) -> CPWorkspace:
+        if self.workspace is None:
+            self.workspace = CPWorkspace(self.group, chunk_elements, self.wait_limit_s)
+        return self.workspace
+
+
 def _merge(out_a: Tensor, lse_a: Tensor, out_b: Tensor, lse_b: Tensor):
     """Combine two attention results over disjoint key sets: ``out (B,T,H,D)``, ``lse (B,H,T)``."""
     lse = torch.logaddexp(lse_a, lse_b)
@@ -160,4 +176,6 @@ def context_parallel_attention(q: Tensor, k: Tensor, v: Tensor, workspace: CPWor
     """Causal attention for this rank's chunk: ``q (B, T_local, H, D)``, ``k/v (B, T_local, Hk, D)``
     bf16, already rotated with their global positions. Returns ``(B, T_local, H, D)``."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if isinstance(workspace, LazyCPWorkspace):
+        workspace = workspace.materialize(2 * k.numel())
     return _ContextParallelAttention.apply(q, k, v, workspace, float(scale))

@@ -238,6 +238,7 @@ class OharaEngine:
             else:
                 module = module.to(self._device)
         module = self._maybe_apply_tensor_parallel(module)
+        self._maybe_apply_context_parallel(module)
         ignored = self._maybe_apply_expert_parallel(module)
         if ignored:
             from torch.nn.parallel import DistributedDataParallel
@@ -247,6 +248,20 @@ class OharaEngine:
         module = self._strategy.setup_module(module, device=self._device, process_group=group)
         self._module = module
         return module
+
+    def _maybe_apply_context_parallel(self, module: torch.nn.Module) -> None:
+        """With ``cp > 1`` the ranks of a context-parallel group share a batch and each works on
+        one contiguous chunk of every sequence; attention exchanges keys / values over NVLink."""
+        if self.topology.cp <= 1:
+            return
+        enable = getattr(module, "enable_context_parallel", None)
+        if not callable(enable) or self._device.type != "cuda":
+            raise RuntimeError("cp > 1 needs a CUDA device and a model with enable_context_parallel")
+        from ohara_b200.parallel.cp import LazyCPWorkspace
+
+        enable(LazyCPWorkspace(self._groups.get("cp")), self.topology.cp_rank, self.topology.cp)
+        self._cp_sequence_sharding = True
+        self._replica_grads_synced = True
 
     def _maybe_apply_expert_parallel(self, module: torch.nn.Module) -> list[str]:
         """With ``ep > 1`` every grouped mixture-of-experts layer keeps ``E / ep`` experts and
@@ -349,12 +364,20 @@ class OharaEngine:
         """With sequence-parallel tensor parallelism each rank of a tensor-parallel group works
         on its own slice of the group's batch between the parallel regions: take that slice of
         every tensor of ``batch`` (dim 0). Otherwise the batch is returned unchanged."""
-        if not getattr(self, "_tp_batch_sharding", False):
+        by_batch = getattr(self, "_tp_batch_sharding", False)
+        by_sequence = getattr(self, "_cp_sequence_sharding", False)
+        if not (by_batch or by_sequence):
             return batch
-        tp, rank = self.topology.tp, self.topology.tp_rank
         if isinstance(batch, torch.Tensor):
-            if batch.dim() == 0:
+            if by_sequence and batch.dim() >= 2:
+                cp, rank = self.topology.cp, self.topology.cp_rank
+                if batch.shape[1] % cp:
+                    raise ValueError(f"sequence of {batch.shape[1]} does not split over cp={cp}")
+                per = batch.shape[1] // cp
+                batch = batch[:, rank * per : (rank + 1) * per]
+            if not by_batch or batch.dim() == 0:
                 return batch
+            tp, rank = self.topology.tp, self.topology.tp_rank
             if batch.shape[0] % tp:
                 raise ValueError(f"batch of {batch.shape[0]} does not split over tp={tp}")
             per = batch.shape[0] // tp
@@ -371,12 +394,25 @@ class OharaEngine:
         hold partial gradients: sum them over the group. Sharded parameters are already complete,
         their backward collectives mixed every rank's tokens in."""
         if not getattr(self, "_tp_batch_sharding", False) or self._tp_grads_synced:
+            self.sync_context_parallel_gradients(model)
             return
         group = self._groups.get("tp")
         for param in model.parameters():
             if param.grad is not None and not hasattr(param, "tensor_parallel_dim"):
                 dist.all_reduce(param.grad, group=group)
         self._tp_grads_synced = True
+        self.sync_context_parallel_gradients(model)
+
+    def sync_context_parallel_gradients(self, model: torch.nn.Module) -> None:
+        """Context-parallel ranks see different tokens of the same sequences and no parameter is
+        sharded between them: sum every gradient over the group."""
+        if not getattr(self, "_cp_sequence_sharding", False) or self._replica_grads_synced:
+            return
+        group = self._groups.get("cp")
+        for param in model.parameters():
+            if param.grad is not None:
+                dist.all_reduce(param.grad, group=group)
+        self._replica_grads_synced = True
 
     # -- data ----------------------------------------------------------------------------------
     def _replace_sampler(self, dataloader: DataLoader) -> DataLoader:
@@ -456,6 +492,9 @@ class OharaEngine:
             # every rank's loss is a mean over its own slice: the group mean is their average
             loss = loss / self.topology.tp
             self._tp_grads_synced = False
+        if getattr(self, "_cp_sequence_sharding", False):
+            loss = loss / self.topology.cp
+            self._replica_grads_synced = False
         if self._scaler.is_enabled():
             self._scaler.scale(loss).backward()
         else:

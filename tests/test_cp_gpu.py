@@ -60,3 +60,60 @@ def test_context_parallel_attention_matches_full_sequence(tmp_path):
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "CP_OK" in proc.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_engine_context_parallel_llama_matches_single_device(tmp_path):
+    """cp=2 through the engine: each rank runs half of every sequence; loss and gradients of a
+    training step must match the model on whole sequences."""
+    script = """
+        import torch, torch.distributed as dist
+        from ohara_b200 import ops
+        from ohara_b200.models.llama import Config, Llama
+        from ohara_b200.runtime import EngineConfig, OharaEngine, ParallelConfig
+
+        engine = OharaEngine(EngineConfig(parallel=ParallelConfig(cp=2)))
+        engine.launch()
+        rank = dist.get_rank()
+        cfg = Config(vocab_size=512, max_sequence_length=512, hidden_size=256, intermediate_size=512,
+                     num_attention_heads=2, num_key_value_heads=1, num_hidden_layers=2, dropout=0.0,
+                     weight_tying=False)
+        torch.manual_seed(0)
+        reference = Llama(cfg).cuda()
+        torch.manual_seed(0)
+        model = engine.prepare(Llama(cfg))
+        torch.manual_seed(1)
+        ids = torch.randint(0, 512, (2, 513), device="cuda")
+        dist.broadcast(ids, src=0)
+        x, y = ids[:, :-1], ids[:, 1:]
+        for step in range(2):
+            xl, yl = engine.local_batch((x, y))
+            assert xl.shape == (2, 256)
+            with engine.autocast_context():
+                loss = model(xl, targets=yl, loss_scale=1.0 / yl.numel())
+            engine.backward(loss)
+            engine.sync_tensor_parallel_gradients(model)  # also sums over the context-parallel group
+            torch.cuda.synchronize(); ops.check_status()
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                ref_loss = reference(x, targets=y, loss_scale=1.0 / y.numel())
+            ref_loss.backward()
+            total = loss.detach().clone() / 2
+            dist.all_reduce(total)
+            assert abs(float(total) - float(ref_loss)) < 2e-2 * abs(float(ref_loss)), (float(total), float(ref_loss))
+            wanted = dict(reference.named_parameters())
+            for name, param in model.named_parameters():
+                a, b = param.grad.float(), wanted[name].grad.float()
+                assert (a - b).abs().max().item() <= 6e-2 * (b.abs().max().item() + 1e-8), name
+            model.zero_grad(); reference.zero_grad()
+        if rank == 0:
+            print("CP_ENGINE_OK")
+        engine.close()
+    """
+    path = tmp_path / "worker.py"
+    path.write_text(textwrap.dedent(script))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(29750 + os.getpid() % 40), str(path)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "CP_ENGINE_OK" in proc.stdout
