@@ -12,7 +12,8 @@
 // dK and dV are written once at the end (no atomics, GQA groups are summed inside the CTA); dQ is
 // accumulated across key tiles in an fp32 buffer with the TMA reduce-add engine.
 //
-// Warp roles (192 threads): 0-3 softmax / drain / epilogue, 4 TMA producer, 5 MMA issuer.
+// Warp roles (320 threads): 0-7 softmax / drain / epilogue (two threads per key row: warps 0-3 own
+// queries 0-31 of a tile, warps 4-7 queries 32-63), 8 TMA producer, 9 MMA issuer.
 #include "common.cuh"
 #include "host_utils.h"
 
@@ -22,7 +23,10 @@ namespace {
 
 constexpr int kKeys = 128;
 constexpr int kQRows = 64;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // 8 softmax warps, TMA producer (warp 8), MMA issuer (warp 9)
+constexpr int kSoftmaxThreads = 256;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct BwdParams {
@@ -76,10 +80,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* qdo_full = bars + 1;   // 2
   uint64_t* qdo_empty = bars + 3;  // 2
   uint64_t* s_full = bars + 5;     // 1
-  uint64_t* sd_empty = bars + 6;   // 1 (count 4)
-  uint64_t* ps_full = bars + 7;    // 1 (count 4)
+  uint64_t* sd_empty = bars + 6;   // 1 (one arrival per softmax warp)
+  uint64_t* ps_full = bars + 7;    // 1 (one arrival per softmax warp)
   uint64_t* mma_done = bars + 8;   // 1
-  uint64_t* grp_bar = bars + 9;    // 1 (count 128): bounded barrier among the softmax warps
+  uint64_t* grp_bar = bars + 9;    // 1 (all softmax threads): bounded barrier among them
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx wctx{abort_flag, p.status};
@@ -109,14 +113,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&qdo_empty[i], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(sd_empty, 4);
-    mbar_init(ps_full, 4);
+    mbar_init(sd_empty, kSoftmaxThreads / 32);
+    mbar_init(ps_full, kSoftmaxThreads / 32);
     mbar_init(mma_done, 1);
-    mbar_init(grp_bar, 128);
+    mbar_init(grp_bar, kSoftmaxThreads);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
@@ -125,7 +129,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     prefetch_tmap(&tmdK);
     prefetch_tmap(&tmdV);
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -146,7 +150,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tq0 = qt * kQRows;
   };
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------ TMA producer ---------------------------------------------
     if (lane == 0 && n_iters > 0) {
       mbar_expect_tx(kv_full, 2 * L::kKVBytes);
@@ -171,7 +175,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer -----------------------------------------------
     if (lane == 0 && n_iters > 0) {
       const uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);  // S^T, dP^T
@@ -241,9 +245,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else {
     // ------------------------------ Softmax / drain / epilogue -------------------------------
-    const int row = warp * 32 + lane;  // key row within the tile == TMEM lane
+    // Two threads per key row: warps 0-3 take queries 0-31 of each 64-query tile, warps 4-7 take
+    // queries 32-63. A warp may only touch the TMEM lanes of its quarter (warp % 4), which is what
+    // makes this split possible: both warps of a pair address the same lanes, different columns.
+    const int quarter = warp & 3;
+    const int half = warp >> 2;
+    const int row = quarter * 32 + lane;  // key row within the tile == TMEM lane
     const int key = kv0 + row;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
     uint32_t grp_phase = 0;
     // Barrier among the 128 softmax threads, built on an mbarrier so that it cannot outlive the
@@ -262,14 +271,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (threadIdx.x == 0) tma_store_wait_read<0>();
       if (!group_sync()) return false;
       if (row < D) {
+        uint32_t v[32];
+        tmem_ld_32x32(tm_dQ + lane_addr + half * 32, v);
+        tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(tm_dQ + lane_addr + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) sDQ[(c * 32 + i) * D + row] = __uint_as_float(v[i]);
-        }
+        for (int i = 0; i < 32; ++i) sDQ[(half * 32 + i) * D + row] = __uint_as_float(v[i]);
       }
       tcgen05_fence_before();
       fence_proxy_async_smem();
@@ -287,13 +293,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     auto fetch_stat = [&](int it) -> float {
       int h, tq0;
       iter_coords(it, h, tq0);
-      const int idx = threadIdx.x;  // 0..127
+      const int idx = threadIdx.x & 127;  // threads 128..255 fetch too but do not store
       const int tq = tq0 + (idx & 63);
       const size_t base = ((size_t)b * p.H + h) * p.T;
       if (idx < 64) return (tq < p.T) ? p.lse[base + tq] * kLog2e : INFINITY;
       return (tq < p.T) ? p.delta[base + tq] : 0.f;
     };
-    if (n_iters > 0) sStats[threadIdx.x] = fetch_stat(0);
+    if (n_iters > 0 && threadIdx.x < 128) sStats[threadIdx.x] = fetch_stat(0);
     for (int it = 0; it < n_iters; ++it) {
       int h, tq0;
       iter_coords(it, h, tq0);
@@ -303,24 +309,23 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         ok = false;
         break;
       }
-      const float next_stat = (it + 1 < n_iters) ? fetch_stat(it + 1) : 0.f;
+      const float next_stat = (it + 1 < n_iters && threadIdx.x < 128) ? fetch_stat(it + 1) : 0.f;
       if (!mbar_wait(s_full, it & 1, wctx, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
       tcgen05_fence_after();
-      float s[64], dp[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tm_S + lane_addr + c * 32, v);
+      float s[32], dp[32];
+      {
+        uint32_t vs[32], vd[32];
+        tmem_ld_32x32(tm_S + lane_addr + half * 32, vs);
+        tmem_ld_32x32(tm_dP + lane_addr + half * 32, vd);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]);
-        tmem_ld_32x32(tm_dP + lane_addr + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) dp[c * 32 + i] = __uint_as_float(v[i]);
+        for (int i = 0; i < 32; ++i) {
+          s[i] = __uint_as_float(vs[i]);
+          dp[i] = __uint_as_float(vd[i]);
+        }
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -329,15 +334,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const bool need_mask = (p.causal && (kv0 + kKeys - 1 > tq0 + offset)) ||
                              (kv0 + kKeys > p.S) || (tq0 + kQRows > p.T);
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        float pv = exp2f(s[i] * p.scale_log2 - stats[i]);
+      for (int i = 0; i < 32; ++i) {
+        const int qi = half * 32 + i;  // query within the tile
+        float pv = exp2f(s[i] * p.scale_log2 - stats[qi]);
         if (need_mask) {
-          const int tq = tq0 + i;
+          const int tq = tq0 + qi;
           const bool visible = (key < p.S) && (tq < p.T) && (!p.causal || key <= tq + offset);
           pv = visible ? pv : 0.f;
         }
         s[i] = pv;
-        dp[i] = pv * (dp[i] - stats[64 + i]) * p.scale;
+        dp[i] = pv * (dp[i] - stats[64 + qi]) * p.scale;
       }
 
       // The previous iteration's MMAs must be finished with sP / sdS; its dQ^T is then ready.
@@ -352,11 +358,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           break;
         }
       }
-      sStats[((it + 1) & 1) * 128 + threadIdx.x] = next_stat;  // visible after the next group_sync
+      if (threadIdx.x < 128) sStats[((it + 1) & 1) * 128 + threadIdx.x] = next_stat;  // visible after the next group_sync
       uint8_t* prow = sP + row * 128;
       uint8_t* dsrow = sdS + row * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint4 o, d;
         o.x = pack_bf16(s[8 * c + 0], s[8 * c + 1]);
         o.y = pack_bf16(s[8 * c + 2], s[8 * c + 3]);
@@ -366,7 +372,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         d.y = pack_bf16(dp[8 * c + 2], dp[8 * c + 3]);
         d.z = pack_bf16(dp[8 * c + 4], dp[8 * c + 5]);
         d.w = pack_bf16(dp[8 * c + 6], dp[8 * c + 7]);
-        const int sw = ((c ^ (row & 7)) << 4);
+        const int sw = (((half * 4 + c) ^ (row & 7)) << 4);
         *reinterpret_cast<uint4*>(prow + sw) = o;
         *reinterpret_cast<uint4*>(dsrow + sw) = d;
       }
@@ -391,6 +397,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint8_t* dst = (which == 0 ? sK : sV) + row * 128;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
+          if ((c & 1) != half) continue;  // the two warps of a row pair split the column chunks
           uint32_t v[32];
           if (n_iters > 0) {
             tmem_ld_32x32(tm_src + lane_addr + c * 32, v);
@@ -412,12 +419,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0 && kv0 + warp * 32 < p.S) {
+      ok = group_sync();  // both warps of every row pair have written their chunks
+      if (ok && half == 0 && lane == 0 && kv0 + quarter * 32 < p.S) {
 #pragma unroll
         for (int s2 = 0; s2 < kDSub; ++s2) {
-          tma_store_4d(&tmdK, sK + s2 * 16384 + warp * 32 * 128, s2 * 64, hk, kv0 + warp * 32, b);
-          tma_store_4d(&tmdV, sV + s2 * 16384 + warp * 32 * 128, s2 * 64, hk, kv0 + warp * 32, b);
+          tma_store_4d(&tmdK, sK + s2 * 16384 + quarter * 32 * 128, s2 * 64, hk, kv0 + quarter * 32, b);
+          tma_store_4d(&tmdV, sV + s2 * 16384 + quarter * 32 * 128, s2 * 64, hk, kv0 + quarter * 32, b);
         }
         tma_store_commit();
       }
@@ -431,7 +438,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
