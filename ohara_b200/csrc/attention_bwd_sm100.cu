@@ -23,6 +23,7 @@ namespace {
 
 constexpr int kKeys = 128;
 constexpr int kQRows = 64;
+constexpr int kQStages = 3;  // (Q, dO) tiles in flight: covers the load latency of two tiles ahead
 constexpr int kThreads = 320;  // 8 softmax warps, TMA producer (warp 8), MMA issuer (warp 9)
 constexpr int kSoftmaxThreads = 256;
 constexpr int kProducerWarp = 8;
@@ -47,8 +48,8 @@ struct BwdSmem {
   static constexpr int kDQBytes = kQRows * D * 4;
   static constexpr int kK = 0;
   static constexpr int kV = kK + kKVBytes;
-  static constexpr int kQ = kV + kKVBytes;          // 2 stages of (Q, dO)
-  static constexpr int kP = kQ + 4 * kQBytes;
+  static constexpr int kQ = kV + kKVBytes;          // kQStages stages of (Q, dO)
+  static constexpr int kP = kQ + 2 * kQStages * kQBytes;
   static constexpr int kdS = kP + kPBytes;
   static constexpr int kDQ = kdS + kPBytes;
   static constexpr int kStats = kDQ + kDQBytes;     // 2 x (64 lse + 64 delta) floats
@@ -77,14 +78,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   float* sStats = reinterpret_cast<float*>(smem + L::kStats);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
   uint64_t* kv_full = bars;        // 1
-  uint64_t* qdo_full = bars + 1;   // 2
-  uint64_t* qdo_empty = bars + 3;  // 2
-  uint64_t* s_full = bars + 5;     // 1
-  uint64_t* sd_empty = bars + 6;   // 1 (one arrival per softmax warp)
-  uint64_t* ps_full = bars + 7;    // 1 (one arrival per softmax warp)
-  uint64_t* mma_done = bars + 8;   // 1
-  uint64_t* grp_bar = bars + 9;    // 1 (all softmax threads): bounded barrier among them
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* qdo_full = bars + 1;               // kQStages
+  uint64_t* qdo_empty = bars + 1 + kQStages;   // kQStages
+  uint64_t* s_full = bars + 1 + 2 * kQStages;  // 1
+  uint64_t* sd_empty = s_full + 1;   // 1 (one arrival per softmax warp)
+  uint64_t* ps_full = s_full + 2;    // 1 (one arrival per softmax warp)
+  uint64_t* mma_done = s_full + 3;   // 1
+  uint64_t* grp_bar = s_full + 4;    // 1 (all softmax threads): bounded barrier among them
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 5);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx wctx{abort_flag, p.status};
 
@@ -108,7 +109,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kQStages; ++i) {
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
     }
@@ -141,7 +142,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tm_dP = tmem_base + 64;    // 64 columns
   const uint32_t tm_dV = tmem_base + 128;   // D columns
   const uint32_t tm_dK = tmem_base + 256;   // D columns
-  const uint32_t tm_dQ = tmem_base + 384;   // 64 columns (transposed: lane = head_dim index)
+  // dQ^T (lane = head_dim index) is double buffered by iteration parity, 2 x 64 columns: the MMAs of
+  // tile it+1 write one buffer while the softmax warps still drain the other.
+  const uint32_t tm_dQ = tmem_base + 384;
 
   auto iter_coords = [&](int it, int& h, int& tq0) {
     const int g = it / tiles_per_head;
@@ -160,8 +163,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tma_load_4d(sV + s * 16384, &tmV, kv_full, s * 64, hk, kv0, b);
       }
       for (int it = 0; it < n_iters; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+        const int st = it % kQStages;
+        const uint32_t ph = (it / kQStages) & 1;
         if (!mbar_wait(&qdo_empty[st], ph ^ 1, wctx, kTimeoutEmptyBarrier)) break;
         int h, tq0;
         iter_coords(it, h, tq0);
@@ -184,8 +187,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
       const uint32_t pa = smem_u32(sP), dsa = smem_u32(sdS);
       auto issue_scores = [&](int it) -> bool {
-        const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+        const int st = it % kQStages;
+        const uint32_t ph = (it / kQStages) & 1;
         if (!mbar_wait(&qdo_full[st], ph, wctx, kTimeoutFullBarrier)) return false;
         tcgen05_fence_after();
         const uint32_t qa = smem_u32(sQdO + st * 2 * L::kQBytes);
@@ -210,7 +213,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       bool ok = mbar_wait(kv_full, 0, wctx, kTimeoutFullBarrier);
       if (ok) ok = issue_scores(0);
       for (int it = 0; it < n_iters && ok; ++it) {
-        const int st = it & 1;
+        const int st = it % kQStages;
         if (it + 1 < n_iters) {
           if (!mbar_wait(sd_empty, it & 1, wctx, kTimeoutSoftmax)) break;
           if (!issue_scores(it + 1)) break;
@@ -236,7 +239,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // M = 128 operand alias the first (leading offset 0) and are never read back.
 #pragma unroll
         for (int k = 0; k < kKeys / 16; ++k) {
-          umma_bf16_ss(tm_dQ, make_smem_desc_sw128(ka + k * 2048, D == 128 ? 16384 : 0, 1024),
+          umma_bf16_ss(tm_dQ + (it & 1) * 64,
+                       make_smem_desc_sw128(ka + k * 2048, D == 128 ? 16384 : 0, 1024),
                        make_smem_desc_sw128(dsa + k * 2048, 16, 1024), idesc_dq, k > 0 ? 1u : 0u);
         }
         tcgen05_commit(mma_done);
@@ -272,7 +276,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!group_sync()) return false;
       if (row < D) {
         uint32_t v[32];
-        tmem_ld_32x32(tm_dQ + lane_addr + half * 32, v);
+        tmem_ld_32x32(tm_dQ + (it & 1) * 64 + lane_addr + half * 32, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) sDQ[(half * 32 + i) * D + row] = __uint_as_float(v[i]);
@@ -353,10 +357,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           break;
         }
         tcgen05_fence_after();
-        if (!drain_dq(it - 1)) {
-          ok = false;
-          break;
-        }
       }
       if (threadIdx.x < 128) sStats[((it + 1) & 1) * 128 + threadIdx.x] = next_stat;  // visible after the next group_sync
       uint8_t* prow = sP + row * 128;
@@ -380,6 +380,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(ps_full);
+      // The MMAs of this tile are now free to start; meanwhile move dQ^T of the previous tile out
+      // of its TMEM buffer (the one tile it+1 will overwrite, which cannot be issued before this
+      // loop iteration has ended).
+      if (it > 0 && !drain_dq(it - 1)) {
+        ok = false;
+        break;
+      }
     }
 
     if (ok && n_iters > 0) {
