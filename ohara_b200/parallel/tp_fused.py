@@ -36,8 +36,8 @@ _RS_SLOT = 16  # flag slots [16, 16 + world): "my pushes for epoch e are complet
 
 
 class StagedRows:
-    """Rows staged for an all-gather: workspace buffer index, epoch, shape and the event that
-    marks the arrival of every peer's rows in the local gathered buffer."""
+    """Rows staged for an all-gather: workspace buffer index, epoch, shape and the events that
+    mark the arrival of every peer's rows in the local gathered buffer."""
 
     __slots__ = ("buffer", "epoch", "rows", "width", "arrived")
 
@@ -75,7 +75,10 @@ class TPWorkspace:
         self.gathered = [torch.empty(self.world * self.capacity, device=self.device,
                                      dtype=torch.bfloat16) for _ in range(2)]
         self.arrived_flags = torch.zeros(64, device=self.device, dtype=torch.int32)
-        self.copy_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        # Several copy streams so that the pulls from different peers overlap instead of queueing
+        # behind each other's flag waits.
+        self.copy_streams = [torch.cuda.Stream(device=self.device, priority=-1)
+                             for _ in range(max(1, min(self.world - 1, 4)))]
         self.gather_epoch = 0
         self.scatter_epoch = 0
         self._maps: dict[tuple[int, int, int], Tensor] = {}
@@ -104,18 +107,22 @@ class TPWorkspace:
         staged_event.record(main)
         # The side stream may touch the gathered buffer only after everything already queued on
         # the main stream (the previous readers of this buffer) has finished.
-        self.copy_stream.wait_event(staged_event)
         blocks = self._gathered_blocks(index, rows, width)
-        with torch.cuda.stream(self.copy_stream):
-            for hop in range(1, self.world):
-                src = (self.rank + hop) % self.world
-                ext().stream_wait_value32(self._flag_address(_AG_SLOT + src), epoch)
-                remote = self.gather[index].typed(torch.bfloat16, rank=src)[: rows * width]
-                blocks[src].copy_(remote.view(rows, width))
-                ext().stream_write_value32(self.arrived_flags.data_ptr() + 4 * src, epoch)
-            blocks[self.rank].copy_(mine)  # completes the gathered tensor for weight gradients
-            arrived = torch.cuda.Event()
-            arrived.record(self.copy_stream)
+        arrived = []
+        for lane, stream in enumerate(self.copy_streams):
+            stream.wait_event(staged_event)
+            with torch.cuda.stream(stream):
+                for hop in range(1 + lane, self.world, len(self.copy_streams)):
+                    src = (self.rank + hop) % self.world
+                    ext().stream_wait_value32(self._flag_address(_AG_SLOT + src), epoch)
+                    remote = self.gather[index].typed(torch.bfloat16, rank=src)[: rows * width]
+                    blocks[src].copy_(remote.view(rows, width))
+                    ext().stream_write_value32(self.arrived_flags.data_ptr() + 4 * src, epoch)
+                if lane == 0:
+                    blocks[self.rank].copy_(mine)  # completes the gathered tensor (weight gradients)
+                event = torch.cuda.Event()
+                event.record(stream)
+                arrived.append(event)
         return StagedRows(index, epoch, rows, width, arrived)
 
     def gemm_from(self, staged: StagedRows, weight16: Tensor, b_mn: bool, out_features: int) -> Tensor:
@@ -141,7 +148,8 @@ class TPWorkspace:
     def gather_from(self, staged: StagedRows) -> Tensor:
         """The gathered ``(world * rows, width)`` tensor itself (operand of a weight gradient).
         It aliases a workspace buffer that is recycled two stagings later: consume it at once."""
-        torch.cuda.current_stream(self.device).wait_event(staged.arrived)
+        for event in staged.arrived:
+            torch.cuda.current_stream(self.device).wait_event(event)
         blocks = self._gathered_blocks(staged.buffer, staged.rows, staged.width)
         return blocks.view(self.world * staged.rows, staged.width)
 
