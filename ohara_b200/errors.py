@@ -1,0 +1,5 @@
+"""Exception types shared by the kernels' host wrappers and the runtime."""
+
+
+class CollectiveTimeout(RuntimeError):
+    """A collective (a device-side bounded wait or a c10d operation) did not complete in time."""

@@ -18,6 +18,8 @@ import torch
 import torch.nn.functional as F
 from torch import Tensor
 
+from ohara_b200.errors import CollectiveTimeout
+
 from ._ext import ext
 
 __all__ = [
@@ -108,7 +110,7 @@ def check_status(clear: bool = True) -> None:
             6: "attention hand-off timed out",
             7: "bad kernel argument",
         }
-        raise RuntimeError(
+        raise CollectiveTimeout(
             f"ohara_b200 kernel wait timed out: {names.get(code, code)} "
             f"(first in block {block}, {count} waits abandoned)"
         )

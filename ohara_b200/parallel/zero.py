@@ -31,6 +31,7 @@ into the module, which is what checkpointing calls.
 
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
 from typing import Any
 
@@ -96,7 +97,14 @@ class ShardedOptimizer(Optimizer):
 
     # -- planning ----------------------------------------------------------------------------
     def _plan(self) -> None:
-        world = self.world
+        self.pieces, self.matrix_size, self.elementwise_size = self._compute_plan(self.world)
+        self.region = self.matrix_size + self.elementwise_size
+        self.all_pieces = [piece for per_rank in self.pieces for piece in per_rank]
+
+    def _compute_plan(self, world: int) -> tuple[list[list[_Piece]], int, int]:
+        """Layout for ``world`` ranks: ``(pieces per rank, matrix part size, elementwise part
+        size)``. A pure function of the parameter groups, so the layout a checkpoint was written
+        with can be rebuilt at any other world size."""
         matrix_pieces: list[list[_Piece]] = [[] for _ in range(world)]
         matrix_fill = [0] * world
         counter = 0
@@ -120,25 +128,40 @@ class ShardedOptimizer(Optimizer):
                     matrix_pieces[r].append(_Piece(p, 0, p.numel(), r, matrix_fill[r], gi,
                                                    tuple(p.shape)))
                     matrix_fill[r] += _round_up(p.numel(), 8)
-        self.matrix_size = _round_up(max(matrix_fill) if matrix_fill else 0, ALIGN)
+        matrix_size = _round_up(max(matrix_fill) if matrix_fill else 0, ALIGN)
         total = sum(p.numel() for p, _ in elementwise)
-        self.elementwise_size = _round_up((total + world - 1) // world, ALIGN) if total else 0
+        elementwise_size = _round_up((total + world - 1) // world, ALIGN) if total else 0
         ew_pieces: list[list[_Piece]] = [[] for _ in range(world)]
         cursor = 0
         for p, gi in elementwise:
             done = 0
             while done < p.numel():
-                r = cursor // self.elementwise_size
-                room = (r + 1) * self.elementwise_size - cursor
+                r = cursor // elementwise_size
+                room = (r + 1) * elementwise_size - cursor
                 take = min(room, p.numel() - done)
                 ew_pieces[r].append(_Piece(p, done, take, r,
-                                           self.matrix_size + cursor - r * self.elementwise_size,
+                                           matrix_size + cursor - r * elementwise_size,
                                            gi, None))
                 done += take
                 cursor += take
-        self.region = self.matrix_size + self.elementwise_size
-        self.pieces = [matrix_pieces[r] + ew_pieces[r] for r in range(world)]
-        self.all_pieces = [piece for per_rank in self.pieces for piece in per_rank]
+        pieces = [matrix_pieces[r] + ew_pieces[r] for r in range(world)]
+        return pieces, matrix_size, elementwise_size
+
+    def _local_layout(self, pieces_of_rank: list[_Piece]) -> list[tuple[int, list[list[_Piece]]]]:
+        """Parameters of a rank's shard optimizer, in order: ``[(user group index, [pieces of
+        local parameter 0, pieces of local parameter 1, ...])]``. Adjacent elementwise pieces of
+        one group form a single 1-D local parameter."""
+        layout: list[tuple[int, list[list[_Piece]]]] = []
+        for gi, group in enumerate(self.param_groups):
+            mine = [piece for piece in pieces_of_rank if piece.group == gi]
+            if not mine:
+                continue
+            contiguous = all(a.offset + a.length == b.offset for a, b in zip(mine, mine[1:]))
+            if not _is_matrix_group(group) and len(mine) > 1 and contiguous:
+                layout.append((gi, [mine]))
+            else:
+                layout.append((gi, [[piece] for piece in mine]))
+        return layout
 
     def _allocate(self) -> None:
         n = self.region * self.world
@@ -181,40 +204,25 @@ class ShardedOptimizer(Optimizer):
     def _build_local_optimizer(self) -> None:
         """Shard-sized parameters (views of the fp32 master) grouped like the user's groups."""
         local_groups: list[dict[str, Any]] = []
-        self._local_of_group: list[int | None] = []
-        mine = self.pieces[self.rank]
-        for gi, group in enumerate(self.param_groups):
+        self._local_of_group: list[int | None] = [None] * len(self.param_groups)
+        for gi, entries in self._local_layout(self.pieces[self.rank]):
             shard_params = []
-            for piece in mine:
-                if piece.group != gi:
-                    continue
-                view = self.master[piece.offset : piece.offset + piece.length]
-                if piece.shape is not None:
-                    view = view.view(piece.shape)
+            for entry in entries:
+                first, last = entry[0], entry[-1]
+                view = self.master[first.offset : last.offset + last.length]
+                if len(entry) == 1 and first.shape is not None:
+                    view = view.view(first.shape)
                 param = torch.nn.Parameter(view, requires_grad=True)
-                param._shard_piece = piece
+                if len(entry) == 1:
+                    param._shard_piece = first
+                else:
+                    # Elementwise pieces of one group are adjacent in the region: they are
+                    # updated as one 1-D tensor (identical maths, one kernel).
+                    param._shard_span = (first.offset, last.offset + last.length)
                 shard_params.append(param)
-            if not shard_params:
-                self._local_of_group.append(None)
-                continue
-            if not _is_matrix_group(group) and len(shard_params) > 1:
-                # Elementwise pieces of one group are adjacent in the region: update them as one
-                # 1-D tensor (identical maths, one kernel).
-                first = shard_params[0]._shard_piece
-                last = shard_params[-1]._shard_piece
-                contiguous = all(
-                    a._shard_piece.offset + a._shard_piece.length == b._shard_piece.offset
-                    for a, b in zip(shard_params, shard_params[1:])
-                )
-                if contiguous:
-                    merged = torch.nn.Parameter(
-                        self.master[first.offset : last.offset + last.length], requires_grad=True
-                    )
-                    merged._shard_span = (first.offset, last.offset + last.length)
-                    shard_params = [merged]
-            clone = {k: v for k, v in group.items() if k != "params"}
+            clone = {k: v for k, v in self.param_groups[gi].items() if k != "params"}
             clone["params"] = shard_params
-            self._local_of_group.append(len(local_groups))
+            self._local_of_group[gi] = len(local_groups)
             local_groups.append(clone)
         self.local: Optimizer | None = None
         if local_groups:
@@ -384,38 +392,208 @@ class ShardedOptimizer(Optimizer):
                     p.grad.zero_()
 
     # -- checkpoints ---------------------------------------------------------------------------
-    def state_dict(self) -> dict[str, Any]:
-        """Shard states of every rank, gathered (collective): resumable at the same world size."""
+    def _gather_shards(self) -> list[dict[str, Any]]:
         local = self.local.state_dict() if self.local is not None else None
         payload = {"master": self.master.detach().cpu(), "optimizer": _to_cpu(local)}
         if self.world > 1:
             gathered: list[Any] = [None] * self.world
             dist.all_gather_object(gathered, payload, group=self.group)
-        else:
-            gathered = [payload]
+            return gathered
+        return [payload]
+
+    def _group_metadata(self) -> list[dict[str, Any]]:
+        return [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups]
+
+    def state_dict(self) -> dict[str, Any]:
+        """Shard states of every rank, gathered (collective). ``load_state_dict`` accepts it at
+        any world size: the layout of the writing job is rebuilt from ``world_size``."""
         return {
             "sharded": True,
             "world_size": self.world,
             "region": self.region,
-            "param_groups": [{k: v for k, v in g.items() if k != "params"} for g in self.param_groups],
-            "shards": gathered,
+            "param_groups": self._group_metadata(),
+            "shards": self._gather_shards(),
         }
 
-    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
-        if not state_dict.get("sharded"):
-            raise ValueError("expected a state dict written by ShardedOptimizer.state_dict()")
-        if state_dict["world_size"] != self.world or state_dict["region"] != self.region:
-            raise ValueError(
-                "sharded optimizer state was written with a different world size or layout "
-                f"({state_dict['world_size']} ranks); resume with the same number of ranks"
-            )
-        shard = state_dict["shards"][self.rank]
-        self.master.copy_(shard["master"].to(self.device))
-        if self.local is not None and shard["optimizer"] is not None:
-            self.local.load_state_dict(shard["optimizer"])
-        for saved, group in zip(state_dict["param_groups"], self.param_groups):
-            group.update(saved)
+    def full_state_dict(self) -> dict[str, Any]:
+        """Unsharded optimizer state in the format of the wrapped optimizer's own ``state_dict()``
+        (collective): per-parameter Adam moments, one stacked momentum / second-moment buffer per
+        Muon group keyed on the group's first parameter (ohara/optimizer.py:283-371). A
+        single-process optimizer of the same class can load it."""
+        full, _ = self._assemble_full(self._gather_shards(), self.world)
+        return full
+
+    def _param_indices(self) -> dict[int, int]:
+        index: dict[int, int] = {}
+        for group in self.param_groups:
+            for p in group["params"]:
+                index.setdefault(id(p), len(index))
+        return index
+
+    def _assemble_full(self, shards: list[dict[str, Any]], world: int):
+        """``(full optimizer state dict, {param index: flat fp32 master values})`` from the shard
+        states of a job of ``world`` ranks."""
+        pieces, _, _ = self._compute_plan(world)
+        index_of = self._param_indices()
+        state: dict[int, dict[str, Any]] = {}
+        masters: dict[int, Tensor] = {}
+        for rank in range(world):
+            master = shards[rank]["master"]
+            for piece in pieces[rank]:
+                flat = masters.setdefault(index_of[id(piece.param)],
+                                          torch.zeros(piece.param.numel(), dtype=torch.float32))
+                flat[piece.begin : piece.begin + piece.length] = master[
+                    piece.offset : piece.offset + piece.length]
+            local = shards[rank]["optimizer"]
+            if local is None:
+                continue
+            for li, (gi, entries) in enumerate(self._local_layout(pieces[rank])):
+                group = self.param_groups[gi]
+                packed = local["param_groups"][li]["params"]
+                if group.get("kind") == "muon":
+                    saved = local["state"].get(packed[0])
+                    if not saved:
+                        continue
+                    dest = state.setdefault(index_of[id(group["params"][0])], {})
+                    for key, value in saved.items():
+                        for i, entry in enumerate(entries):
+                            piece, p = entry[0], entry[0].param
+                            if p.ndim == 3:  # an expert stack, split along its first dimension
+                                batch, per = p.shape[0], piece.shape[0]
+                                first = piece.begin // (p.shape[1] * p.shape[2])
+                                rows, source = slice(first, first + per), value
+                            else:
+                                batch = len(group["params"])
+                                j = next(n for n, q in enumerate(group["params"]) if q is p)
+                                rows, source = slice(j, j + 1), value[i : i + 1]
+                            if key not in dest:
+                                dest[key] = torch.zeros((batch, *value.shape[1:]), dtype=value.dtype)
+                            dest[key][rows] = source
+                    continue
+                for entry, pid in zip(entries, packed):
+                    saved = local["state"].get(pid)
+                    if not saved:
+                        continue
+                    span = sum(piece.length for piece in entry)
+                    for piece in entry:
+                        p = piece.param
+                        dest = state.setdefault(index_of[id(p)], {})
+                        for key, value in saved.items():
+                            if isinstance(value, Tensor) and value.ndim >= 1 and value.numel() == span:
+                                if key not in dest:
+                                    dest[key] = torch.zeros(p.numel(), dtype=value.dtype)
+                                lo = piece.offset - entry[0].offset
+                                dest[key][piece.begin : piece.begin + piece.length] = value.reshape(
+                                    -1)[lo : lo + piece.length]
+                            else:
+                                dest[key] = value.clone() if isinstance(value, Tensor) else value
+        shape_of = {index_of[id(p)]: p.shape for g in self.param_groups for p in g["params"]}
+        for idx, entry in state.items():
+            for key, value in entry.items():
+                if isinstance(value, Tensor) and value.ndim == 1 and value.numel() == math.prod(
+                        shape_of[idx]) and "momentum_buffer" not in key:
+                    entry[key] = value.view(shape_of[idx])
+        groups = []
+        for meta, group in zip(self._group_metadata(), self.param_groups):
+            groups.append({**meta, "params": [index_of[id(p)] for p in group["params"]]})
+        return {"state": state, "param_groups": groups}, masters
+
+    def _slice_full(self, full: dict[str, Any]) -> dict[str, Any] | None:
+        """This rank's shard-optimizer state dict cut out of an unsharded state dict."""
+        if self.local is None:
+            return None
+        index_of = self._param_indices()
+        template = self.local.state_dict()
+        state: dict[int, dict[str, Any]] = {}
+        saved_state = {int(k): v for k, v in full["state"].items()}
+        for li, (gi, entries) in enumerate(self._local_layout(self.pieces[self.rank])):
+            group = self.param_groups[gi]
+            packed = template["param_groups"][li]["params"]
+            if group.get("kind") == "muon":
+                saved = saved_state.get(index_of[id(group["params"][0])])
+                if not saved:
+                    continue
+                local: dict[str, Any] = {}
+                for key, value in saved.items():
+                    parts = []
+                    for entry in entries:
+                        piece, p = entry[0], entry[0].param
+                        if p.ndim == 3:
+                            first = piece.begin // (p.shape[1] * p.shape[2])
+                            parts.append(value[first : first + piece.shape[0]])
+                        else:
+                            j = next(n for n, q in enumerate(group["params"]) if q is p)
+                            parts.append(value[j : j + 1])
+                    local[key] = torch.cat(parts).clone()
+                state[packed[0]] = local
+                continue
+            for entry, pid in zip(entries, packed):
+                local = {}
+                for piece in entry:
+                    saved = saved_state.get(index_of[id(piece.param)])
+                    if not saved:
+                        continue
+                    for key, value in saved.items():
+                        if isinstance(value, Tensor) and value.numel() == piece.param.numel() \
+                                and value.ndim >= 1:
+                            cut = value.reshape(-1)[piece.begin : piece.begin + piece.length]
+                            local.setdefault(key, []).append(cut)
+                        else:
+                            local[key] = value
+                if not local:
+                    continue
+                for key, value in list(local.items()):
+                    if isinstance(value, list):
+                        joined = torch.cat(value).clone()
+                        if len(entry) == 1 and entry[0].shape is not None:
+                            joined = joined.view(entry[0].shape)
+                        local[key] = joined
+                state[pid] = local
+        groups = []
+        for li, template_group in enumerate(template["param_groups"]):
+            gi = self._local_of_group.index(li)
+            saved_group = {k: v for k, v in full["param_groups"][gi].items() if k != "params"}
+            groups.append({**template_group, **saved_group, "params": template_group["params"]})
+        return {"state": state, "param_groups": groups}
+
+    @torch.no_grad()
+    def _load_masters(self, masters: dict[int, Tensor] | None) -> None:
+        """Refill the fp32 master shard (from ``masters`` when given, else from the module's
+        current parameters) and republish the compute-precision weights (collective)."""
+        index_of = self._param_indices()
+        for piece in self.pieces[self.rank]:
+            if masters is not None:
+                source = masters[index_of[id(piece.param)]].to(self.device)
+            else:
+                source = piece.param.detach().reshape(-1).float()
+            self.master[piece.offset : piece.offset + piece.length].copy_(
+                source[piece.begin : piece.begin + piece.length])
         self._publish_weights()
+
+    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
+        """Accepts (a) ``state_dict()`` of a sharded job of any world size, (b) an unsharded state
+        dict (``full_state_dict()`` or the wrapped optimizer class run on one process); in case
+        (b) the master weights are taken from the module, which must be loaded first."""
+        if state_dict.get("sharded"):
+            same = state_dict["world_size"] == self.world and state_dict["region"] == self.region
+            if same:
+                shard = state_dict["shards"][self.rank]
+                self.master.copy_(shard["master"].to(self.device))
+                if self.local is not None and shard["optimizer"] is not None:
+                    self.local.load_state_dict(shard["optimizer"])
+                for saved, group in zip(state_dict["param_groups"], self.param_groups):
+                    group.update(saved)
+                self._publish_weights()
+                return
+            full, masters = self._assemble_full(state_dict["shards"], state_dict["world_size"])
+        else:
+            full, masters = state_dict, None
+        local = self._slice_full(full)
+        if self.local is not None and local is not None:
+            self.local.load_state_dict(local)
+        for saved, group in zip(full["param_groups"], self.param_groups):
+            group.update({k: v for k, v in saved.items() if k != "params"})
+        self._load_masters(masters)
 
 
 def _to_cpu(obj: Any) -> Any:

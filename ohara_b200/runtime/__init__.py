@@ -1,4 +1,10 @@
-from .config import DistributedConfig, EngineConfig, ParallelConfig, PrecisionConfig
+from .config import (
+    DistributedConfig,
+    EngineConfig,
+    FaultToleranceConfig,
+    ParallelConfig,
+    PrecisionConfig,
+)
 from .engine import OharaEngine
 from .enums import (
     Backend,
@@ -12,21 +18,27 @@ from .enums import (
 from .pipeline import PipelinePlan, PipelineStageSpec
 from .tensor_parallel import TensorParallelPlan, TensorParallelRule
 from .topology import ParallelTopology
+from .watchdog import CollectiveTimeout, Heartbeat, PeerFailure, StepWatchdog
 
 __all__ = [
     "Backend",
+    "CollectiveTimeout",
     "DistributedConfig",
     "EngineConfig",
+    "FaultToleranceConfig",
+    "Heartbeat",
     "OharaEngine",
     "ParallelConfig",
     "ParallelDimension",
     "ParallelTopology",
+    "PeerFailure",
     "PipelinePlan",
     "PipelineScheduleType",
     "PipelineStageSpec",
     "PrecisionConfig",
     "PrecisionMode",
     "ReduceType",
+    "StepWatchdog",
     "StrategyType",
     "TensorParallelPlan",
     "TensorParallelRule",

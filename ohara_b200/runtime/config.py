@@ -31,12 +31,25 @@ class PrecisionConfig:
 
 
 @dataclass
+class FaultToleranceConfig:
+    """Host-side failure detection (all off by default, like the reference, whose only detector is
+    the process-group timeout). ``heartbeat_interval_s > 0`` starts a heartbeat thread per rank
+    over the rendezvous store; ``step_timeout_s > 0`` arms a deadline around every guarded step."""
+
+    heartbeat_interval_s: float = 0.0
+    heartbeat_timeout_s: float = 30.0
+    step_timeout_s: float = 0.0
+    exit_on_step_timeout: bool = False
+
+
+@dataclass
 class EngineConfig:
     strategy: StrategyType = StrategyType.AUTO
     distributed: DistributedConfig = field(default_factory=DistributedConfig)
     parallel: ParallelConfig = field(default_factory=ParallelConfig)
     precision: PrecisionConfig = field(default_factory=PrecisionConfig)
     tensor_parallel: TensorParallelPlan = field(default_factory=TensorParallelPlan)
+    fault_tolerance: FaultToleranceConfig = field(default_factory=FaultToleranceConfig)
     # Use the peer-memory (NVLink) fused collectives where available; False keeps every
     # collective on the c10d backend (the A/B baseline and the only choice on CPU/gloo).
     fused_collectives: bool = True

@@ -38,6 +38,7 @@ from .tensor_parallel import (
     gather_tensor_parallel_state,
 )
 from .topology import ParallelTopology
+from .watchdog import Heartbeat, StepWatchdog, default_store
 
 
 class _DeviceDataLoader:
@@ -86,6 +87,8 @@ class OharaEngine:
         self._groups: dict[str, Any] = {}
         self._dp_world_size = 1
         self._dp_rank = 0
+        self.heartbeat: Heartbeat | None = None
+        self.watchdog: StepWatchdog | None = None
 
     # -- properties ----------------------------------------------------------------------------
     @staticmethod
@@ -191,7 +194,38 @@ class OharaEngine:
             self.config.precision.mode == PrecisionMode.FP16_MIXED and self._device.type == "cuda"
         )
         self._scaler = self._build_grad_scaler(use_scaler)
+        self._start_failure_detection()
         self._launched = True
+
+    def _start_failure_detection(self) -> None:
+        tolerance = self.config.fault_tolerance
+        store = default_store()
+        if tolerance.heartbeat_interval_s > 0 and store is not None and self.world_size > 1:
+            self.heartbeat = Heartbeat(
+                store, self.global_rank, self.world_size,
+                interval_s=tolerance.heartbeat_interval_s, timeout_s=tolerance.heartbeat_timeout_s,
+            ).start()
+        if tolerance.step_timeout_s > 0:
+            self.watchdog = StepWatchdog(tolerance.step_timeout_s,
+                                         hard_exit=tolerance.exit_on_step_timeout)
+
+    def check_peers(self, *, refresh: bool = False) -> None:
+        """Raise ``PeerFailure`` if a rank of the job is known to be gone. The trainer calls this
+        on the host before it launches a step, so that no kernel or collective is issued that
+        would wait for the missing rank."""
+        if self.heartbeat is not None:
+            self.heartbeat.check(refresh=refresh)
+
+    def guard_step(self, index: int):
+        """Context manager that arms the step watchdog (a no-op when none is configured)."""
+        if self.watchdog is None:
+            return nullcontext()
+        return self.watchdog.step(index)
+
+    def leave(self) -> None:
+        """Announce that this rank stops on purpose (between steps, nothing in flight)."""
+        if self.heartbeat is not None:
+            self.heartbeat.leave()
 
     def _build_groups(self) -> None:
         """Create one process group per parallel dimension that is larger than 1. Every rank calls
@@ -645,5 +679,11 @@ class OharaEngine:
                 logger.log_dict(payload, step=step)
 
     def close(self) -> None:
+        if self.heartbeat is not None:
+            self.heartbeat.stop()
+            self.heartbeat = None
+        if self.watchdog is not None:
+            self.watchdog.close()
+            self.watchdog = None
         if dist.is_initialized():
             dist.destroy_process_group()

@@ -466,9 +466,14 @@ class Trainer:
         while idx < self.max_iters:
             idx += 1
             self.engine.synchronize()
+            check_peers = getattr(self.engine, "check_peers", None)
+            if callable(check_peers):
+                check_peers()  # raises before anything is launched that would wait on a lost rank
+            guard = getattr(self.engine, "guard_step", None)
             started = time.perf_counter()
-            step_loss, lr = self.train_step(idx)
-            self.engine.synchronize()
+            with guard(idx) if callable(guard) else nullcontext():
+                step_loss, lr = self.train_step(idx)
+                self.engine.synchronize()
             elapsed = time.perf_counter() - started
             tokens_per_sec, mfu, eta_seconds, _ = self._compute_perf_metrics(idx, elapsed)
             if idx % self.print_every == 0 and self.engine.is_global_zero:

@@ -1,0 +1,241 @@
+"""Failure detection is exercised entirely on the host: fake stores and clocks for the unit tests,
+gloo ranks on CPU for the multi-process cases. No device is involved."""
+
+from __future__ import annotations
+
+import io
+import os
+import subprocess
+import sys
+import textwrap
+import threading
+import time
+from pathlib import Path
+
+import pytest
+
+from ohara_b200.runtime import (
+    CollectiveTimeout,
+    EngineConfig,
+    FaultToleranceConfig,
+    Heartbeat,
+    OharaEngine,
+    PeerFailure,
+    StepWatchdog,
+)
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+class DictStore:
+    """In-memory stand-in for a c10d store (``add`` is the only call the heartbeat needs)."""
+
+    def __init__(self) -> None:
+        self.values: dict[str, int] = {}
+        self.lock = threading.Lock()
+        self.dropped: set[str] = set()
+
+    def add(self, key: str, amount: int) -> int:
+        with self.lock:
+            if amount and key in self.dropped:  # a message the test loses on purpose
+                return self.values.get(key, 0)
+            self.values[key] = self.values.get(key, 0) + amount
+            return self.values[key]
+
+
+class ManualClock:
+    def __init__(self) -> None:
+        self.now = 0.0
+
+    def __call__(self) -> float:
+        return self.now
+
+
+def test_heartbeat_flags_a_silent_rank_and_recovers_when_it_speaks_again():
+    store, clock = DictStore(), ManualClock()
+    beats = [Heartbeat(store, r, 3, interval_s=1.0, timeout_s=5.0, clock=clock) for r in range(3)]
+    for step in range(4):
+        clock.now = float(step)
+        for hb in beats:
+            hb.beat()
+        for hb in beats:
+            hb.poll()
+    beats[0].check()
+    # rank 2's heartbeats are lost from now on
+    store.dropped.add(beats[2]._beat_key(2))
+    for step in range(4, 12):
+        clock.now = float(step)
+        for hb in beats:
+            hb.beat()
+        beats[0].poll()
+    assert beats[0].failed_ranks == [2]
+    with pytest.raises(PeerFailure) as info:
+        beats[0].check()
+    assert info.value.failed == [2] and "rank(s) [2]" in str(info.value)
+    # the messages get through again: the rank is no longer reported
+    store.dropped.clear()
+    clock.now = 13.0
+    beats[2].beat()
+    beats[0].poll()
+    beats[0].check()
+
+
+def test_heartbeat_departure_is_seen_immediately():
+    store, clock = DictStore(), ManualClock()
+    a = Heartbeat(store, 0, 2, interval_s=1.0, timeout_s=5.0, clock=clock)
+    b = Heartbeat(store, 1, 2, interval_s=1.0, timeout_s=5.0, clock=clock)
+    a.beat(); b.beat(); a.poll()
+    b.leave()
+    with pytest.raises(PeerFailure) as info:
+        a.check(refresh=True)
+    assert info.value.left == [1] and info.value.failed == []
+    assert a.departed_ranks == [1]
+
+
+def test_heartbeat_thread_runs_and_stops():
+    store = DictStore()
+    with Heartbeat(store, 0, 2, interval_s=0.02, timeout_s=0.2) as hb:
+        time.sleep(0.5)
+        assert store.values[hb._beat_key(0)] > 3
+        assert hb.failed_ranks == [1]  # rank 1 never said anything
+    count = store.values[hb._beat_key(0)]
+    time.sleep(0.1)
+    assert store.values[hb._beat_key(0)] == count
+
+
+def test_heartbeat_rejects_bad_timing():
+    with pytest.raises(ValueError):
+        Heartbeat(DictStore(), 0, 2, interval_s=2.0, timeout_s=1.0)
+
+
+def test_step_watchdog_fires_only_for_a_late_step():
+    fired: list[tuple[int, float]] = []
+    stream = io.StringIO()
+    dog = StepWatchdog(0.15, on_timeout=lambda step, elapsed: fired.append((step, elapsed)),
+                       stream=stream, poll_s=0.02)
+    try:
+        with dog.step(1):
+            time.sleep(0.02)
+        time.sleep(0.25)
+        assert fired == []
+        with dog.step(2):
+            time.sleep(0.4)
+        assert [step for step, _ in fired] == [2] and fired[0][1] >= 0.15
+        assert dog.expired_steps == [2]
+        assert "step 2 exceeded" in stream.getvalue()
+    finally:
+        dog.close()
+
+
+def test_collective_timeout_is_a_runtime_error():
+    assert issubclass(CollectiveTimeout, RuntimeError)
+    from ohara_b200 import ops
+
+    assert ops.CollectiveTimeout is CollectiveTimeout
+
+
+def test_engine_guard_is_a_no_op_without_configuration():
+    engine = OharaEngine(EngineConfig())
+    engine.launch()
+    engine.check_peers()
+    with engine.guard_step(1):
+        pass
+    engine.close()
+    engine = OharaEngine(EngineConfig(fault_tolerance=FaultToleranceConfig(step_timeout_s=5.0)))
+    engine.launch()
+    assert engine.watchdog is not None
+    with engine.guard_step(3):
+        pass
+    engine.close()
+    assert engine.watchdog is None
+
+
+def _run_ranks(script: str, world: int, tmp_path, timeout=180):
+    path = tmp_path / "worker.py"
+    path.write_text(textwrap.dedent(script))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(30100 + os.getpid() % 400), str(path)]
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+
+
+def test_ranks_learn_on_the_host_that_a_peer_left_or_died(tmp_path):
+    """Rank 2 announces its departure after step 2; rank 1 exits without a word after step 4. The
+    survivors see both on the host, before they would issue the next collective."""
+    proc = _run_ranks(
+        """
+        import os, sys, time
+        import torch, torch.distributed as dist
+        from ohara_b200.runtime import (EngineConfig, FaultToleranceConfig, OharaEngine,
+                                        ParallelConfig, PeerFailure)
+        engine = OharaEngine(EngineConfig(
+            parallel=ParallelConfig(dp_replicate=3),
+            fault_tolerance=FaultToleranceConfig(heartbeat_interval_s=0.1, heartbeat_timeout_s=1.0)))
+        engine.launch()
+        rank = engine.global_rank
+        value = torch.ones(1)
+        for step in range(1, 3):
+            engine.check_peers()
+            dist.all_reduce(value)
+        assert value.item() == 9.0
+        if rank == 2:
+            engine.leave()          # between steps, nothing in flight
+            os._exit(0)
+        seen_left = seen_dead = False
+        deadline = time.monotonic() + 20
+        while time.monotonic() < deadline:
+            try:
+                engine.check_peers(refresh=True)
+            except PeerFailure as failure:
+                seen_left = failure.left == [2]
+                break
+            time.sleep(0.05)
+        assert seen_left, "departure of rank 2 was not reported"
+        if rank == 1:
+            os._exit(0)             # dies silently
+        deadline = time.monotonic() + 20
+        while time.monotonic() < deadline:
+            try:
+                engine.check_peers(refresh=True)
+            except PeerFailure as failure:
+                if failure.failed == [1]:
+                    seen_dead = True
+                    break
+            time.sleep(0.05)
+        assert seen_dead, "silent death of rank 1 was not reported"
+        print("SURVIVOR_OK", flush=True)
+        os._exit(0)                 # peers are gone: skip the collective teardown
+        """,
+        3, tmp_path,
+    )
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "SURVIVOR_OK" in proc.stdout
+
+
+def test_short_process_group_timeout_ends_a_collective_with_an_error(tmp_path):
+    """A rank never joins the collective: the others get an error after the short timeout
+    instead of waiting forever."""
+    proc = _run_ranks(
+        """
+        import os, time
+        from datetime import timedelta
+        import torch, torch.distributed as dist
+        dist.init_process_group("gloo", timeout=timedelta(seconds=3))
+        rank = dist.get_rank()
+        if rank == 1:
+            time.sleep(8)           # never joins
+            os._exit(0)
+        started = time.monotonic()
+        try:
+            dist.all_reduce(torch.ones(1))
+        except Exception as error:
+            waited = time.monotonic() - started
+            assert waited < 7.5, waited
+            print("TIMEOUT_OK", type(error).__name__, flush=True)
+            os._exit(0)
+        os._exit(3)
+        """,
+        2, tmp_path,
+    )
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "TIMEOUT_OK" in proc.stdout
