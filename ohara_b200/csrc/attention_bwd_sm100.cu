@@ -8,12 +8,16 @@
 //     S^T  = K  Q^T          (128 keys x 64 queries)      dP^T = V dO^T
 //     P^T  = exp2(S^T*c - lse),  dS^T = P^T o (dP^T - delta) * scale      (4 warps, registers)
 //     dV  += P^T dO          dK += dS^T Q                 (accumulate in TMEM over all q tiles)
-//     dQ^T = K^T dS^T        (head_dim x 64) -> transposed through smem -> TMA reduce-add (fp32)
+//     dQ^T = K^T dS^T        (head_dim x 64) -> registers -> red.global.add.f32 (fp32 buffer)
 // dK and dV are written once at the end (no atomics, GQA groups are summed inside the CTA); dQ is
-// accumulated across key tiles in an fp32 buffer with the TMA reduce-add engine.
+// accumulated across key tiles in an fp32 buffer: a thread of the drain owns one head_dim index,
+// so the 32 lanes of a warp add 128 contiguous bytes of one query row per instruction.
 //
 // Warp roles (320 threads): 0-7 softmax / drain / epilogue (two threads per key row: warps 0-3 own
-// queries 0-31 of a tile, warps 4-7 queries 32-63), 8 TMA producer, 9 MMA issuer.
+// queries 0-31 of a tile, warps 4-7 queries 32-63), 8 TMA producer (its lanes also stage the
+// per-query statistics of each tile), 9 MMA issuer. The softmax warps never synchronise with one
+// another inside the loop: P^T / dS^T are double buffered in shared memory and dQ^T in TMEM, and
+// every hand-off is an mbarrier between a warp and the MMA issuer.
 #include "common.cuh"
 #include "host_utils.h"
 
@@ -37,6 +41,7 @@ struct BwdParams {
   float scale_log2;  // scale * log2(e)
   const float* lse;    // (B, H, T) natural log
   const float* delta;  // (B, H, T)
+  float* dq;           // (B, T, H, D) fp32 accumulators, zero-initialised by the caller
   int* status;
 };
 
@@ -45,15 +50,13 @@ struct BwdSmem {
   static constexpr int kKVBytes = kKeys * D * 2;   // K or V tile
   static constexpr int kQBytes = kQRows * D * 2;   // Q or dO tile
   static constexpr int kPBytes = kKeys * kQRows * 2;
-  static constexpr int kDQBytes = kQRows * D * 4;
   static constexpr int kK = 0;
   static constexpr int kV = kK + kKVBytes;
   static constexpr int kQ = kV + kKVBytes;          // kQStages stages of (Q, dO)
-  static constexpr int kP = kQ + 2 * kQStages * kQBytes;
-  static constexpr int kdS = kP + kPBytes;
-  static constexpr int kDQ = kdS + kPBytes;
-  static constexpr int kStats = kDQ + kDQBytes;     // 2 x (64 lse + 64 delta) floats
-  static constexpr int kBars = kStats + 2 * 128 * 4;
+  static constexpr int kP = kQ + 2 * kQStages * kQBytes;   // 2 buffers of P^T
+  static constexpr int kdS = kP + 2 * kPBytes;             // 2 buffers of dS^T
+  static constexpr int kStats = kdS + 2 * kPBytes;  // kQStages x (64 lse*log2e + 64 delta) floats
+  static constexpr int kBars = kStats + kQStages * 128 * 4;
   static constexpr int kNeeded = kBars + 256 + 1024;
   static constexpr int kTotal = kNeeded > 120 * 1024 ? kNeeded : 120 * 1024;
 };
@@ -62,7 +65,7 @@ template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                 const __grid_constant__ CUtensorMap tmdQ, const __grid_constant__ CUtensorMap tmdK,
+                 const __grid_constant__ CUtensorMap tmdK,
                  const __grid_constant__ CUtensorMap tmdV, const BwdParams p) {
   using L = BwdSmem<D>;
   constexpr int kDSub = D / 64;
@@ -74,7 +77,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sQdO = smem + L::kQ;  // stage s: Q at s*2*kQBytes, dO right after it
   uint8_t* sP = smem + L::kP;
   uint8_t* sdS = smem + L::kdS;
-  float* sDQ = reinterpret_cast<float*>(smem + L::kDQ);
   float* sStats = reinterpret_cast<float*>(smem + L::kStats);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBars);
   uint64_t* kv_full = bars;        // 1
@@ -82,10 +84,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* qdo_empty = bars + 1 + kQStages;   // kQStages
   uint64_t* s_full = bars + 1 + 2 * kQStages;  // 1
   uint64_t* sd_empty = s_full + 1;   // 1 (one arrival per softmax warp)
-  uint64_t* ps_full = s_full + 2;    // 1 (one arrival per softmax warp)
-  uint64_t* mma_done = s_full + 3;   // 1
-  uint64_t* grp_bar = s_full + 4;    // 1 (all softmax threads): bounded barrier among them
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 5);
+  // ps_full and mma_done alternate between two barriers by tile parity. Their waiters have
+  // already enabled the *next* completion when they start to wait (the softmax warps arrive on
+  // ps_full before they wait for mma_done of the previous tile; the MMA issuer commits the next
+  // scores before it waits for ps_full), so a single barrier could complete twice before a
+  // delayed waiter looks, and a parity wait cannot tell that from "not yet".
+  uint64_t* ps_full = s_full + 2;    // 2 (one arrival per softmax warp)
+  uint64_t* mma_done = s_full + 4;   // 2
+  uint64_t* grp_bar = s_full + 6;    // 1 (all softmax threads): bounded barrier among them
+  uint64_t* stat_full = s_full + 7;  // kQStages (one arrival per lane of the producer warp)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stat_full + kQStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx wctx{abort_flag, p.status};
 
@@ -112,11 +120,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int i = 0; i < kQStages; ++i) {
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
+      mbar_init(&stat_full[i], 32);
     }
     mbar_init(s_full, 1);
     mbar_init(sd_empty, kSoftmaxThreads / 32);
-    mbar_init(ps_full, kSoftmaxThreads / 32);
-    mbar_init(mma_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&ps_full[i], kSoftmaxThreads / 32);
+      mbar_init(&mma_done[i], 1);
+    }
     mbar_init(grp_bar, kSoftmaxThreads);
     *abort_flag = 0;
     fence_barrier_init();
@@ -126,7 +137,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
     prefetch_tmap(&tmdO);
-    prefetch_tmap(&tmdQ);
     prefetch_tmap(&tmdK);
     prefetch_tmap(&tmdV);
   }
@@ -155,12 +165,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (warp == kProducerWarp) {
     // ------------------------------ TMA producer ---------------------------------------------
-    if (lane == 0 && n_iters > 0) {
-      mbar_expect_tx(kv_full, 2 * L::kKVBytes);
+    // Lane 0 issues the tile loads; all 32 lanes fetch the 64 log-sum-exp and 64 delta values of
+    // the tile (four each) into the stage's statistics slot and arrive on its barrier.
+    if (n_iters > 0) {
+      if (lane == 0) {
+        mbar_expect_tx(kv_full, 2 * L::kKVBytes);
 #pragma unroll
-      for (int s = 0; s < kDSub; ++s) {
-        tma_load_4d(sK + s * 16384, &tmK, kv_full, s * 64, hk, kv0, b);
-        tma_load_4d(sV + s * 16384, &tmV, kv_full, s * 64, hk, kv0, b);
+        for (int s = 0; s < kDSub; ++s) {
+          tma_load_4d(sK + s * 16384, &tmK, kv_full, s * 64, hk, kv0, b);
+          tma_load_4d(sV + s * 16384, &tmV, kv_full, s * 64, hk, kv0, b);
+        }
       }
       for (int it = 0; it < n_iters; ++it) {
         const int st = it % kQStages;
@@ -168,14 +182,28 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!mbar_wait(&qdo_empty[st], ph ^ 1, wctx, kTimeoutEmptyBarrier)) break;
         int h, tq0;
         iter_coords(it, h, tq0);
-        uint8_t* q_dst = sQdO + st * 2 * L::kQBytes;
-        uint8_t* do_dst = q_dst + L::kQBytes;
-        mbar_expect_tx(&qdo_full[st], 2 * L::kQBytes);
+        if (lane == 0) {
+          uint8_t* q_dst = sQdO + st * 2 * L::kQBytes;
+          uint8_t* do_dst = q_dst + L::kQBytes;
+          mbar_expect_tx(&qdo_full[st], 2 * L::kQBytes);
 #pragma unroll
-        for (int s = 0; s < kDSub; ++s) {
-          tma_load_4d(q_dst + s * 8192, &tmQ, &qdo_full[st], s * 64, h, tq0, b);
-          tma_load_4d(do_dst + s * 8192, &tmdO, &qdo_full[st], s * 64, h, tq0, b);
+          for (int s = 0; s < kDSub; ++s) {
+            tma_load_4d(q_dst + s * 8192, &tmQ, &qdo_full[st], s * 64, h, tq0, b);
+            tma_load_4d(do_dst + s * 8192, &tmdO, &qdo_full[st], s * 64, h, tq0, b);
+          }
         }
+        const size_t base = ((size_t)b * p.H + h) * p.T;
+        float* stats = sStats + st * 128;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int qi = lane + 32 * j;
+          const int tq = tq0 + qi;
+          const bool valid = tq < p.T;
+          // Out-of-range queries get +inf / 0: their probabilities come out as exactly zero.
+          stats[qi] = valid ? p.lse[base + tq] * kLog2e : INFINITY;
+          stats[64 + qi] = valid ? p.delta[base + tq] : 0.f;
+        }
+        mbar_arrive(&stat_full[st]);
       }
     }
   } else if (warp == kMmaWarp) {
@@ -185,7 +213,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t idesc_dv = make_idesc_bf16(128, D, false, true);    // dV, dK
       const uint32_t idesc_dq = make_idesc_bf16(128, 64, true, true);    // dQ^T
       const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-      const uint32_t pa = smem_u32(sP), dsa = smem_u32(sdS);
       auto issue_scores = [&](int it) -> bool {
         const int st = it % kQStages;
         const uint32_t ph = (it / kQStages) & 1;
@@ -218,10 +245,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (!mbar_wait(sd_empty, it & 1, wctx, kTimeoutSoftmax)) break;
           if (!issue_scores(it + 1)) break;
         }
-        if (!mbar_wait(ps_full, it & 1, wctx, kTimeoutSoftmax)) break;
+        if (!mbar_wait(&ps_full[it & 1], (it >> 1) & 1, wctx, kTimeoutSoftmax)) break;
         tcgen05_fence_after();
         const uint32_t qa = smem_u32(sQdO + st * 2 * L::kQBytes);
         const uint32_t doa = qa + L::kQBytes;
+        const uint32_t pa = smem_u32(sP + (it & 1) * L::kPBytes);
+        const uint32_t dsa = smem_u32(sdS + (it & 1) * L::kPBytes);
         // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 queries)
 #pragma unroll
         for (int k = 0; k < kQRows / 16; ++k) {
@@ -243,7 +272,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                        make_smem_desc_sw128(ka + k * 2048, D == 128 ? 16384 : 0, 1024),
                        make_smem_desc_sw128(dsa + k * 2048, 16, 1024), idesc_dq, k > 0 ? 1u : 0u);
         }
-        tcgen05_commit(mma_done);
+        tcgen05_commit(&mma_done[it & 1]);
         tcgen05_commit(&qdo_empty[st]);
       }
     }
@@ -268,52 +297,38 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       return done;
     };
 
-    // Moves dQ^T of iteration `it` from TMEM to the fp32 gradient with a TMA reduce-add.
-    auto drain_dq = [&](int it) -> bool {
+    // Adds dQ^T of iteration `it` (TMEM lane = head_dim index, column = query) to the fp32
+    // gradient. The lanes of a warp hold 32 consecutive head_dim indices of the same query, so
+    // each reduction instruction covers 128 contiguous bytes.
+    auto drain_dq = [&](int it) {
+      if (row >= D) return;
       int h, tq0;
       iter_coords(it, h, tq0);
-      if (threadIdx.x == 0) tma_store_wait_read<0>();
-      if (!group_sync()) return false;
-      if (row < D) {
-        uint32_t v[32];
-        tmem_ld_32x32(tm_dQ + (it & 1) * 64 + lane_addr + half * 32, v);
-        tmem_ld_wait();
+      uint32_t v[32];
+      tmem_ld_32x32(tm_dQ + (it & 1) * 64 + lane_addr + half * 32, v);
+      tmem_ld_wait();
+      const int tq_first = tq0 + half * 32;
+      float* dst = p.dq + (((size_t)b * p.T + tq_first) * p.H + h) * D + row;
+      const size_t q_stride = (size_t)p.H * D;
+      if (tq_first + 32 <= p.T) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sDQ[(half * 32 + i) * D + row] = __uint_as_float(v[i]);
+        for (int i = 0; i < 32; ++i) atomicAdd(dst + i * q_stride, __uint_as_float(v[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (tq_first + i < p.T) atomicAdd(dst + i * q_stride, __uint_as_float(v[i]));
       }
-      tcgen05_fence_before();
-      fence_proxy_async_smem();
-      if (!group_sync()) return false;
-      if (threadIdx.x == 0) {
-        tma_reduce_add_4d(&tmdQ, sDQ, 0, h, tq0, b);
-        tma_store_commit();
-      }
-      return true;
     };
 
-    // Per-query statistics (64 lse + 64 delta per tile) live in shared memory, double buffered by
-    // iteration parity. The values of tile it+1 are fetched from global memory while tile it is
-    // being processed, so their latency is off the critical path.
-    auto fetch_stat = [&](int it) -> float {
-      int h, tq0;
-      iter_coords(it, h, tq0);
-      const int idx = threadIdx.x & 127;  // threads 128..255 fetch too but do not store
-      const int tq = tq0 + (idx & 63);
-      const size_t base = ((size_t)b * p.H + h) * p.T;
-      if (idx < 64) return (tq < p.T) ? p.lse[base + tq] * kLog2e : INFINITY;
-      return (tq < p.T) ? p.delta[base + tq] : 0.f;
-    };
-    if (n_iters > 0 && threadIdx.x < 128) sStats[threadIdx.x] = fetch_stat(0);
     for (int it = 0; it < n_iters; ++it) {
       int h, tq0;
       iter_coords(it, h, tq0);
-      float* stats = sStats + (it & 1) * 128;
-      // Publishes stats(it) and retires every reader of the other buffer (tile it-1).
-      if (!group_sync()) {
+      const int st = it % kQStages;
+      const float* stats = sStats + st * 128;
+      if (!mbar_wait(&stat_full[st], (it / kQStages) & 1, wctx, kTimeoutFullBarrier)) {
         ok = false;
         break;
       }
-      const float next_stat = (it + 1 < n_iters && threadIdx.x < 128) ? fetch_stat(it + 1) : 0.f;
       if (!mbar_wait(s_full, it & 1, wctx, kTimeoutTmemFull)) {
         ok = false;
         break;
@@ -350,17 +365,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         dp[i] = pv * (dp[i] - stats[64 + qi]) * p.scale;
       }
 
-      // The previous iteration's MMAs must be finished with sP / sdS; its dQ^T is then ready.
-      if (it > 0) {
-        if (!mbar_wait(mma_done, (it - 1) & 1, wctx, kTimeoutTmemFull)) {
-          ok = false;
-          break;
-        }
-        tcgen05_fence_after();
-      }
-      if (threadIdx.x < 128) sStats[((it + 1) & 1) * 128 + threadIdx.x] = next_stat;  // visible after the next group_sync
-      uint8_t* prow = sP + row * 128;
-      uint8_t* dsrow = sdS + row * 128;
+      // Buffer (it & 1) of P^T / dS^T was last read by the MMAs of tile it-2, whose completion
+      // this warp has already observed when it drained dQ^T of that tile.
+      uint8_t* prow = sP + (it & 1) * L::kPBytes + row * 128;
+      uint8_t* dsrow = sdS + (it & 1) * L::kPBytes + row * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint4 o, d;
@@ -379,21 +387,27 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       fence_proxy_async_smem();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ps_full);
-      // The MMAs of this tile are now free to start; meanwhile move dQ^T of the previous tile out
-      // of its TMEM buffer (the one tile it+1 will overwrite, which cannot be issued before this
-      // loop iteration has ended).
-      if (it > 0 && !drain_dq(it - 1)) {
-        ok = false;
-        break;
+      if (lane == 0) mbar_arrive(&ps_full[it & 1]);
+      // The MMAs of this tile may start as soon as every warp has arrived. Meanwhile move dQ^T of
+      // the previous tile out of its TMEM buffer: tile it+1 overwrites that buffer, and its MMAs
+      // need this warp's arrival on ps_full of tile it+1, which comes after this drain.
+      if (it > 0) {
+        if (!mbar_wait(&mma_done[(it - 1) & 1], ((it - 1) >> 1) & 1, wctx, kTimeoutTmemFull)) {
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        drain_dq(it - 1);
+        tcgen05_fence_before();
       }
     }
 
     if (ok && n_iters > 0) {
-      ok = mbar_wait(mma_done, (n_iters - 1) & 1, wctx, kTimeoutTmemFull);
+      ok = mbar_wait(&mma_done[(n_iters - 1) & 1], ((n_iters - 1) >> 1) & 1, wctx,
+                     kTimeoutTmemFull);
       if (ok) {
         tcgen05_fence_after();
-        ok = drain_dq(n_iters - 1);
+        drain_dq(n_iters - 1);
       }
     }
     // ---- epilogue: dK, dV (TMEM fp32) -> bf16 -> swizzled smem (over K / V tiles) -> TMA store --
@@ -451,31 +465,44 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-// delta[b, h, t] = sum_d O[b, t, h, d] * dO[b, t, h, d]; one warp per (b, t, h) row.
+// delta[b, h, t] = sum_d O[b, t, h, d] * dO[b, t, h, d]. D / 8 lanes share a (b, t, h) row, each
+// with one 16-byte load of O and of dO, so a warp covers 256 / D rows per pass (D in {64, 128}).
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
                                   const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
                                   int B, int T, int H, int D, int64_t do_tok_stride,
                                   int64_t do_batch_stride) {
+  const int lanes_per_row = D >> 3;
+  const int rows_per_warp = 32 / lanes_per_row;
   const int warps = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int sub = lane / lanes_per_row;
+  const int col = (lane % lanes_per_row) * 8;
   const int64_t rows = (int64_t)B * T * H;
-  for (int64_t r = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); r < rows;
-       r += (int64_t)gridDim.x * warps) {
-    const int h = (int)(r % H);
-    const int64_t bt = r / H;
-    const int t = (int)(bt % T);
-    const int b = (int)(bt / T);
-    const __nv_bfloat16* orow = o + r * D;
-    const __nv_bfloat16* drow = d_o + (int64_t)b * do_batch_stride + (int64_t)t * do_tok_stride + (int64_t)h * D;
+  const int64_t first = ((int64_t)blockIdx.x * warps + (threadIdx.x >> 5)) * rows_per_warp;
+  const int64_t step = (int64_t)gridDim.x * warps * rows_per_warp;
+  for (int64_t r0 = first; r0 < rows; r0 += step) {
+    const int64_t r = r0 + sub;
     float acc = 0.f;
-    for (int i = lane * 2; i < D; i += 64) {
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(orow + i));
-      const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(drow + i));
-      acc += a.x * g.x + a.y * g.y;
-    }
+    int h = 0, t = 0, b = 0;
+    if (r < rows) {
+      h = (int)(r % H);
+      const int64_t bt = r / H;
+      t = (int)(bt % T);
+      b = (int)(bt / T);
+      const uint4 a = *reinterpret_cast<const uint4*>(o + r * D + col);
+      const uint4 g = *reinterpret_cast<const uint4*>(
+          d_o + (int64_t)b * do_batch_stride + (int64_t)t * do_tok_stride + (int64_t)h * D + col);
+      const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
 #pragma unroll
-    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-    if (lane == 0) delta[((size_t)b * H + h) * T + t] = acc;
+      for (int i = 0; i < 4; ++i) {
+        const float2 x = __bfloat1622float2(a2[i]);
+        const float2 y = __bfloat1622float2(g2[i]);
+        acc += x.x * y.x + x.y * y.y;
+      }
+    }
+    for (int s = lanes_per_row >> 1; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (r < rows && (lane % lanes_per_row) == 0) delta[((size_t)b * H + h) * T + t] = acc;
   }
 }
 
@@ -484,7 +511,7 @@ void launch_bwd(const void* q, const void* k, const void* v, const void* d_o, fl
                 void* dv, const float* lse, const float* delta, int B, int T, int S, int H, int Hk,
                 bool causal, float scale, const int64_t* strides, cudaStream_t stream) {
   using L = BwdSmem<D>;
-  CUtensorMap tQ, tK, tV, tdO, tdQ, tdK, tdV;
+  CUtensorMap tQ, tK, tV, tdO, tdK, tdV;
   auto make4 = [&](CUtensorMap* tm, const void* base, TmapDtype dt, int heads, int len,
                    int64_t tok_stride, int64_t batch_stride, uint32_t box_inner, uint32_t box_rows,
                    TmapSwizzle sw) {
@@ -498,8 +525,6 @@ void launch_bwd(const void* q, const void* k, const void* v, const void* d_o, fl
   make4(&tK, k, TmapDtype::BF16, Hk, S, strides[2], strides[3], 64, kKeys, TmapSwizzle::B128);
   make4(&tV, v, TmapDtype::BF16, Hk, S, strides[4], strides[5], 64, kKeys, TmapSwizzle::B128);
   make4(&tdO, d_o, TmapDtype::BF16, H, T, strides[6], strides[7], 64, kQRows, TmapSwizzle::B128);
-  make4(&tdQ, dq, TmapDtype::F32, H, T, (int64_t)H * D, (int64_t)T * H * D, D, kQRows,
-        TmapSwizzle::NONE);
   make4(&tdK, dk, TmapDtype::BF16, Hk, S, (int64_t)Hk * D, (int64_t)S * Hk * D, 64, 32,
         TmapSwizzle::B128);
   make4(&tdV, dv, TmapDtype::BF16, Hk, S, (int64_t)Hk * D, (int64_t)S * Hk * D, 64, 32,
@@ -515,6 +540,7 @@ void launch_bwd(const void* q, const void* k, const void* v, const void* d_o, fl
   p.scale_log2 = scale * kLog2e;
   p.lse = lse;
   p.delta = delta;
+  p.dq = dq;
   p.status = status_ptr();
   auto kernel = flash_bwd_kernel<D>;
   static bool configured = false;
@@ -525,7 +551,7 @@ void launch_bwd(const void* q, const void* k, const void* v, const void* d_o, fl
   }
   const int k_tiles = (S + kKeys - 1) / kKeys;
   const long long grid = (long long)k_tiles * B * Hk;
-  kernel<<<(unsigned)grid, kThreads, L::kTotal, stream>>>(tQ, tK, tV, tdO, tdQ, tdK, tdV, p);
+  kernel<<<(unsigned)grid, kThreads, L::kTotal, stream>>>(tQ, tK, tV, tdO, tdK, tdV, p);
   OB_LAUNCH_CHECK();
 }
 
@@ -535,7 +561,9 @@ void attn_delta(const void* o, const void* d_o, float* delta, int B, int T, int 
                 int64_t do_tok_stride, int64_t do_batch_stride, cudaStream_t stream) {
   const int threads = 256;
   const int64_t rows = (int64_t)B * T * H;
-  const int blocks = (int)std::min<int64_t>((rows + 7) / 8, (int64_t)device_sm_count() * 16);
+  const int rows_per_block = (threads / 32) * (256 / D);
+  const int blocks = (int)std::min<int64_t>((rows + rows_per_block - 1) / rows_per_block,
+                                            (int64_t)device_sm_count() * 16);
   attn_delta_kernel<<<std::max(blocks, 1), threads, 0, stream>>>(
       (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, T, H, D, do_tok_stride,
       do_batch_stride);
@@ -598,7 +626,7 @@ cudaError_t noalloc_launch(const void* q, const void* k, const void* v, const vo
                            int S, int H, int Hk, bool causal, float scale, int* status,
                            bool configure, cudaStream_t stream) {
   using L = BwdSmem<D>;
-  CUtensorMap tQ, tK, tV, tdO, tdQ, tdK, tdV;
+  CUtensorMap tQ, tK, tV, tdO, tdK, tdV;
   auto make4 = [&](CUtensorMap* tm, const void* base, TmapDtype dt, int heads, int len,
                    uint32_t box_inner, uint32_t box_rows, TmapSwizzle sw) {
     const uint64_t esz = dt == TmapDtype::F32 ? 4 : 2;
@@ -611,7 +639,6 @@ cudaError_t noalloc_launch(const void* q, const void* k, const void* v, const vo
   make4(&tK, k, TmapDtype::BF16, Hk, S, 64, kKeys, TmapSwizzle::B128);
   make4(&tV, v, TmapDtype::BF16, Hk, S, 64, kKeys, TmapSwizzle::B128);
   make4(&tdO, d_o, TmapDtype::BF16, H, T, 64, kQRows, TmapSwizzle::B128);
-  make4(&tdQ, dq32, TmapDtype::F32, H, T, D, kQRows, TmapSwizzle::NONE);
   make4(&tdK, dk, TmapDtype::BF16, Hk, S, 64, 32, TmapSwizzle::B128);
   make4(&tdV, dv, TmapDtype::BF16, Hk, S, 64, 32, TmapSwizzle::B128);
   BwdParams p;
@@ -625,6 +652,7 @@ cudaError_t noalloc_launch(const void* q, const void* k, const void* v, const vo
   p.scale_log2 = scale * kLog2e;
   p.lse = lse;
   p.delta = delta;
+  p.dq = dq32;
   p.status = status;
   auto kernel = flash_bwd_kernel<D>;
   if (configure) {
@@ -634,7 +662,7 @@ cudaError_t noalloc_launch(const void* q, const void* k, const void* v, const vo
   }
   const int k_tiles = (S + kKeys - 1) / kKeys;
   const long long grid = (long long)k_tiles * B * Hk;
-  kernel<<<(unsigned)grid, kThreads, L::kTotal, stream>>>(tQ, tK, tV, tdO, tdQ, tdK, tdV, p);
+  kernel<<<(unsigned)grid, kThreads, L::kTotal, stream>>>(tQ, tK, tV, tdO, tdK, tdV, p);
   count_launch();
   return cudaGetLastError();
 }
