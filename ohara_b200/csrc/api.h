@@ -86,7 +86,8 @@ void swiglu_fwd(const void* g, const void* u, void* a, int64_t rows, int h, int6
 void swiglu_bwd(const void* da, const void* g, const void* u, void* dg, void* du, int64_t rows,
                 int h, int64_t da_pitch, int64_t g_pitch, int64_t u_pitch, int64_t dg_pitch,
                 int64_t du_pitch, cudaStream_t stream);
-void cast_f32_bf16(const float* in, void* out, int64_t n, cudaStream_t stream);
+// out[i] = bf16(in[i] * scale)
+void cast_f32_bf16(const float* in, void* out, int64_t n, cudaStream_t stream, float scale = 1.f);
 void embedding_fwd(const int64_t* ids, const float* table, void* out, int64_t tokens, int d,
                    int vocab, cudaStream_t stream);
 void embedding_bwd(const int64_t* ids, const void* dout, float* dtable, int64_t tokens, int d,
@@ -104,6 +105,8 @@ void flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float*
 // attention_bwd_sm100.cu
 void attn_delta(const void* o, const void* d_o, float* delta, int B, int T, int H, int D,
                 int64_t do_tok_stride, int64_t do_batch_stride, cudaStream_t stream);
+// `dq` (fp32, zero-initialised by the caller) receives the gradient of Q *without* the softmax
+// scale: multiply by `scale` when converting it (cast_f32_bf16 takes the factor). dk / dv are final.
 void flash_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, float* dq,
                     void* dk, void* dv, const float* lse, const float* delta, int B, int T, int S,
                     int H, int Hk, int D, bool causal, float scale, const int64_t* strides,

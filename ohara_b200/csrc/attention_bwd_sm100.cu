@@ -6,16 +6,20 @@
 // key row and the per-query statistics (log-sum-exp and delta = rowsum(dO*O)) are plain broadcast
 // reads:
 //     S^T  = K  Q^T          (128 keys x 64 queries)      dP^T = V dO^T
-//     P^T  = exp2(S^T*c - lse),  dS^T = P^T o (dP^T - delta) * scale      (4 warps, registers)
+//     P^T  = exp2(S^T*c - lse),  dS^T = P^T o (dP^T - delta)               (registers)
 //     dV  += P^T dO          dK += dS^T Q                 (accumulate in TMEM over all q tiles)
 //     dQ^T = K^T dS^T        (head_dim x 64) -> registers -> red.global.add.f32 (fp32 buffer)
 // dK and dV are written once at the end (no atomics, GQA groups are summed inside the CTA); dQ is
 // accumulated across key tiles in an fp32 buffer: a thread of the drain owns one head_dim index,
 // so the 32 lanes of a warp add 128 contiguous bytes of one query row per instruction.
 //
-// Warp roles (320 threads): 0-7 softmax / drain / epilogue (two threads per key row: warps 0-3 own
-// queries 0-31 of a tile, warps 4-7 queries 32-63), 8 TMA producer (its lanes also stage the
-// per-query statistics of each tile), 9 MMA issuer. The softmax warps never synchronise with one
+// The softmax scale of dS is applied once at the end instead of per element: dK is multiplied in
+// the epilogue, and the dQ accumulators hold the unscaled sum (the caller scales while converting).
+//
+// Warp roles (576 threads): 0-15 softmax / drain / epilogue (four threads per key row: warp w owns
+// TMEM lanes 32*(w%4).. and queries 16*(w/4).. of a tile; the element-wise work is bound by
+// instruction latency, so it is spread over four warps per scheduler), 16 TMA producer (its lanes
+// also stage the per-query statistics of each tile), 17 MMA issuer. The softmax warps never synchronise with one
 // another inside the loop: P^T / dS^T are double buffered in shared memory and dQ^T in TMEM, and
 // every hand-off is an mbarrier between a warp and the MMA issuer.
 #include "common.cuh"
@@ -28,10 +32,11 @@ namespace {
 constexpr int kKeys = 128;
 constexpr int kQRows = 64;
 constexpr int kQStages = 3;  // (Q, dO) tiles in flight: covers the load latency of two tiles ahead
-constexpr int kThreads = 320;  // 8 softmax warps, TMA producer (warp 8), MMA issuer (warp 9)
-constexpr int kSoftmaxThreads = 256;
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
+constexpr int kThreads = 576;  // 16 softmax warps, TMA producer (warp 16), MMA issuer (warp 17)
+constexpr int kSoftmaxThreads = 512;
+constexpr int kProducerWarp = 16;
+constexpr int kMmaWarp = 17;
+constexpr int kSliceCols = 16;  // queries of a tile handled by one thread
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct BwdParams {
@@ -41,7 +46,7 @@ struct BwdParams {
   float scale_log2;  // scale * log2(e)
   const float* lse;    // (B, H, T) natural log
   const float* delta;  // (B, H, T)
-  float* dq;           // (B, T, H, D) fp32 accumulators, zero-initialised by the caller
+  float* dq;           // (B, T, H, D) fp32 accumulators (unscaled), zero-initialised by the caller
   int* status;
 };
 
@@ -100,12 +105,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // Block -> (key tile, batch, kv head); low key tiles (most work under a causal mask) first.
+  // Block -> (batch, kv head, key tile) with the key tile fastest: the CTAs that run at the same
+  // time then belong to a handful of (batch, head) pairs and share their Q / dO tiles and dQ
+  // accumulators through L2 (with the key tile slowest, every resident CTA streamed its own
+  // head's tensors and the kernel was bound by HBM). Within a head the low key tiles, which have
+  // the most work under a causal mask, come first.
   int bid = blockIdx.x;
+  const int k_tiles_total = (p.S + kKeys - 1) / kKeys;
+  const int kt = bid % k_tiles_total;
+  bid /= k_tiles_total;
   const int hk = bid % p.Hk;
-  bid /= p.Hk;
-  const int b = bid % p.B;
-  const int kt = bid / p.B;
+  const int b = bid / p.Hk;
   const int kv0 = kt * kKeys;
   const int group = p.H / p.Hk;
   const int offset = p.S - p.T;
@@ -212,27 +222,38 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);  // S^T, dP^T
       const uint32_t idesc_dv = make_idesc_bf16(128, D, false, true);    // dV, dK
       const uint32_t idesc_dq = make_idesc_bf16(128, 64, true, true);    // dQ^T
-      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      // Descriptors of every operand at offset 0 of its buffer; the loops below only add offsets.
+      const SmemDesc dK_k = make_smem_desc_parts(smem_u32(sK), 16, 1024);    // K, K-major (S^T)
+      const SmemDesc dV_k = make_smem_desc_parts(smem_u32(sV), 16, 1024);    // V, K-major (dP^T)
+      const SmemDesc dK_mn = make_smem_desc_parts(smem_u32(sK), D == 128 ? 16384 : 0, 1024);  // K^T
+      const SmemDesc dQ_k = make_smem_desc_parts(smem_u32(sQdO), 16, 1024);  // Q / dO, K-major
+      const SmemDesc dQ_mn = make_smem_desc_parts(smem_u32(sQdO), 8192, 1024);  // Q / dO as B, MN-major
+      const SmemDesc dP_k = make_smem_desc_parts(smem_u32(sP), 16, 1024);    // P^T, K-major A
+      const SmemDesc dS_k = make_smem_desc_parts(smem_u32(sdS), 16, 1024);   // dS^T, K-major A / B
       auto issue_scores = [&](int it) -> bool {
         const int st = it % kQStages;
         const uint32_t ph = (it / kQStages) & 1;
         if (!mbar_wait(&qdo_full[st], ph, wctx, kTimeoutFullBarrier)) return false;
         tcgen05_fence_after();
-        const uint32_t qa = smem_u32(sQdO + st * 2 * L::kQBytes);
-        const uint32_t doa = qa + L::kQBytes;
+        const uint32_t q_off = st * 2 * L::kQBytes;
+        const uint32_t do_off = q_off + L::kQBytes;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t offA = (k / 4) * 16384 + (k % 4) * 32;
           const uint32_t offB = (k / 4) * 8192 + (k % 4) * 32;
-          umma_bf16_ss(tm_S, make_smem_desc_sw128(ka + offA, 16, 1024),
-                       make_smem_desc_sw128(qa + offB, 16, 1024), idesc_st, k > 0 ? 1u : 0u);
+          if (k == 0)
+            umma_bf16_ss_c<0>(tm_S, smem_desc_at(dK_k, offA), smem_desc_at(dQ_k, q_off + offB), idesc_st);
+          else
+            umma_bf16_ss_c<1>(tm_S, smem_desc_at(dK_k, offA), smem_desc_at(dQ_k, q_off + offB), idesc_st);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t offA = (k / 4) * 16384 + (k % 4) * 32;
           const uint32_t offB = (k / 4) * 8192 + (k % 4) * 32;
-          umma_bf16_ss(tm_dP, make_smem_desc_sw128(va + offA, 16, 1024),
-                       make_smem_desc_sw128(doa + offB, 16, 1024), idesc_st, k > 0 ? 1u : 0u);
+          if (k == 0)
+            umma_bf16_ss_c<0>(tm_dP, smem_desc_at(dV_k, offA), smem_desc_at(dQ_k, do_off + offB), idesc_st);
+          else
+            umma_bf16_ss_c<1>(tm_dP, smem_desc_at(dV_k, offA), smem_desc_at(dQ_k, do_off + offB), idesc_st);
         }
         tcgen05_commit(s_full);
         return true;
@@ -247,30 +268,35 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         if (!mbar_wait(&ps_full[it & 1], (it >> 1) & 1, wctx, kTimeoutSoftmax)) break;
         tcgen05_fence_after();
-        const uint32_t qa = smem_u32(sQdO + st * 2 * L::kQBytes);
-        const uint32_t doa = qa + L::kQBytes;
-        const uint32_t pa = smem_u32(sP + (it & 1) * L::kPBytes);
-        const uint32_t dsa = smem_u32(sdS + (it & 1) * L::kPBytes);
+        const uint32_t q_off = st * 2 * L::kQBytes;
+        const uint32_t do_off = q_off + L::kQBytes;
+        const uint32_t p_off = (it & 1) * L::kPBytes;
         // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 queries)
-#pragma unroll
-        for (int k = 0; k < kQRows / 16; ++k) {
-          umma_bf16_ss(tm_dV, make_smem_desc_sw128(pa + k * 32, 16, 1024),
-                       make_smem_desc_sw128(doa + k * 2048, 8192, 1024), idesc_dv,
-                       (it > 0 || k > 0) ? 1u : 0u);
+        if (it == 0) {
+          umma_bf16_ss_c<0>(tm_dV, smem_desc_at(dP_k, p_off), smem_desc_at(dQ_mn, do_off), idesc_dv);
+          umma_bf16_ss_c<0>(tm_dK, smem_desc_at(dS_k, p_off), smem_desc_at(dQ_mn, q_off), idesc_dv);
+        } else {
+          umma_bf16_ss_c<1>(tm_dV, smem_desc_at(dP_k, p_off), smem_desc_at(dQ_mn, do_off), idesc_dv);
+          umma_bf16_ss_c<1>(tm_dK, smem_desc_at(dS_k, p_off), smem_desc_at(dQ_mn, q_off), idesc_dv);
         }
 #pragma unroll
-        for (int k = 0; k < kQRows / 16; ++k) {
-          umma_bf16_ss(tm_dK, make_smem_desc_sw128(dsa + k * 32, 16, 1024),
-                       make_smem_desc_sw128(qa + k * 2048, 8192, 1024), idesc_dv,
-                       (it > 0 || k > 0) ? 1u : 0u);
+        for (int k = 1; k < kQRows / 16; ++k) {
+          umma_bf16_ss_c<1>(tm_dV, smem_desc_at(dP_k, p_off + k * 32),
+                            smem_desc_at(dQ_mn, do_off + k * 2048), idesc_dv);
+          umma_bf16_ss_c<1>(tm_dK, smem_desc_at(dS_k, p_off + k * 32),
+                            smem_desc_at(dQ_mn, q_off + k * 2048), idesc_dv);
         }
         // dQ^T = K^T dS^T (contraction over the 128 keys). For D = 64 the second 64 rows of the
         // M = 128 operand alias the first (leading offset 0) and are never read back.
+        const uint32_t tm_dQ_it = tm_dQ + (it & 1) * 64;
 #pragma unroll
         for (int k = 0; k < kKeys / 16; ++k) {
-          umma_bf16_ss(tm_dQ + (it & 1) * 64,
-                       make_smem_desc_sw128(ka + k * 2048, D == 128 ? 16384 : 0, 1024),
-                       make_smem_desc_sw128(dsa + k * 2048, 16, 1024), idesc_dq, k > 0 ? 1u : 0u);
+          if (k == 0)
+            umma_bf16_ss_c<0>(tm_dQ_it, smem_desc_at(dK_mn, k * 2048),
+                              smem_desc_at(dS_k, p_off + k * 2048), idesc_dq);
+          else
+            umma_bf16_ss_c<1>(tm_dQ_it, smem_desc_at(dK_mn, k * 2048),
+                              smem_desc_at(dS_k, p_off + k * 2048), idesc_dq);
         }
         tcgen05_commit(&mma_done[it & 1]);
         tcgen05_commit(&qdo_empty[st]);
@@ -278,18 +304,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else {
     // ------------------------------ Softmax / drain / epilogue -------------------------------
-    // Two threads per key row: warps 0-3 take queries 0-31 of each 64-query tile, warps 4-7 take
-    // queries 32-63. A warp may only touch the TMEM lanes of its quarter (warp % 4), which is what
-    // makes this split possible: both warps of a pair address the same lanes, different columns.
+    // Four threads per key row: warp w takes queries 16*(w/4) .. +15 of each 64-query tile. A warp
+    // may only touch the TMEM lanes of its quarter (w % 4), which is what makes this split
+    // possible: the four warps of a quarter address the same lanes, different columns.
     const int quarter = warp & 3;
-    const int half = warp >> 2;
+    const int slice = warp >> 2;
     const int row = quarter * 32 + lane;  // key row within the tile == TMEM lane
     const int key = kv0 + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t col0 = slice * kSliceCols;
     bool ok = true;
     uint32_t grp_phase = 0;
-    // Barrier among the 128 softmax threads, built on an mbarrier so that it cannot outlive the
-    // wait limit if some warp has already abandoned the tile.
+    // Barrier among the softmax threads, built on an mbarrier so that it cannot outlive the wait
+    // limit if some warp has already abandoned the tile.
     auto group_sync = [&]() -> bool {
       mbar_arrive(grp_bar);
       const bool done = mbar_wait(grp_bar, grp_phase & 1, wctx, kTimeoutSoftmax);
@@ -300,23 +327,28 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // Adds dQ^T of iteration `it` (TMEM lane = head_dim index, column = query) to the fp32
     // gradient. The lanes of a warp hold 32 consecutive head_dim indices of the same query, so
     // each reduction instruction covers 128 contiguous bytes.
+    const size_t q_stride = (size_t)p.H * D;
     auto drain_dq = [&](int it) {
       if (row >= D) return;
       int h, tq0;
       iter_coords(it, h, tq0);
-      uint32_t v[32];
-      tmem_ld_32x32(tm_dQ + (it & 1) * 64 + lane_addr + half * 32, v);
+      uint32_t v[16];
+      tmem_ld_32x16(tm_dQ + (it & 1) * 64 + lane_addr + col0, v);
       tmem_ld_wait();
-      const int tq_first = tq0 + half * 32;
+      const int tq_first = tq0 + (int)col0;
       float* dst = p.dq + (((size_t)b * p.T + tq_first) * p.H + h) * D + row;
-      const size_t q_stride = (size_t)p.H * D;
-      if (tq_first + 32 <= p.T) {
+      if (tq_first + kSliceCols <= p.T) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) atomicAdd(dst + i * q_stride, __uint_as_float(v[i]));
+        for (int i = 0; i < kSliceCols; ++i) {
+          atomicAdd(dst, __uint_as_float(v[i]));
+          dst += q_stride;
+        }
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (tq_first + i < p.T) atomicAdd(dst + i * q_stride, __uint_as_float(v[i]));
+        for (int i = 0; i < kSliceCols; ++i) {
+          if (tq_first + i < p.T) atomicAdd(dst, __uint_as_float(v[i]));
+          dst += q_stride;
+        }
       }
     };
 
@@ -324,7 +356,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       int h, tq0;
       iter_coords(it, h, tq0);
       const int st = it % kQStages;
-      const float* stats = sStats + st * 128;
+      const float* stats = sStats + st * 128 + col0;
       if (!mbar_wait(&stat_full[st], (it / kQStages) & 1, wctx, kTimeoutFullBarrier)) {
         ok = false;
         break;
@@ -334,35 +366,35 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         break;
       }
       tcgen05_fence_after();
-      float s[32], dp[32];
-      {
-        uint32_t vs[32], vd[32];
-        tmem_ld_32x32(tm_S + lane_addr + half * 32, vs);
-        tmem_ld_32x32(tm_dP + lane_addr + half * 32, vd);
-        tmem_ld_wait();
+      uint32_t vs[16], vd[16];
+      tmem_ld_32x16(tm_S + lane_addr + col0, vs);
+      tmem_ld_32x16(tm_dP + lane_addr + col0, vd);
+      float lse2[16], dlt[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          s[i] = __uint_as_float(vs[i]);
-          dp[i] = __uint_as_float(vd[i]);
-        }
+      for (int c = 0; c < 4; ++c) {
+        const float4 a = reinterpret_cast<const float4*>(stats)[c];
+        const float4 d = reinterpret_cast<const float4*>(stats + 64)[c];
+        lse2[4 * c + 0] = a.x, lse2[4 * c + 1] = a.y, lse2[4 * c + 2] = a.z, lse2[4 * c + 3] = a.w;
+        dlt[4 * c + 0] = d.x, dlt[4 * c + 1] = d.y, dlt[4 * c + 2] = d.z, dlt[4 * c + 3] = d.w;
       }
+      tmem_ld_wait();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(sd_empty);
 
+      float pr[16], ds[16];
       const bool need_mask = (p.causal && (kv0 + kKeys - 1 > tq0 + offset)) ||
                              (kv0 + kKeys > p.S) || (tq0 + kQRows > p.T);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int qi = half * 32 + i;  // query within the tile
-        float pv = exp2f(s[i] * p.scale_log2 - stats[qi]);
+      for (int i = 0; i < kSliceCols; ++i) {
+        float pv = fast_exp2(fmaf(__uint_as_float(vs[i]), p.scale_log2, -lse2[i]));
         if (need_mask) {
-          const int tq = tq0 + qi;
+          const int tq = tq0 + (int)col0 + i;
           const bool visible = (key < p.S) && (tq < p.T) && (!p.causal || key <= tq + offset);
           pv = visible ? pv : 0.f;
         }
-        s[i] = pv;
-        dp[i] = pv * (dp[i] - stats[64 + qi]) * p.scale;
+        pr[i] = pv;
+        ds[i] = pv * (__uint_as_float(vd[i]) - dlt[i]);
       }
 
       // Buffer (it & 1) of P^T / dS^T was last read by the MMAs of tile it-2, whose completion
@@ -370,17 +402,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       uint8_t* prow = sP + (it & 1) * L::kPBytes + row * 128;
       uint8_t* dsrow = sdS + (it & 1) * L::kPBytes + row * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint4 o, d;
-        o.x = pack_bf16(s[8 * c + 0], s[8 * c + 1]);
-        o.y = pack_bf16(s[8 * c + 2], s[8 * c + 3]);
-        o.z = pack_bf16(s[8 * c + 4], s[8 * c + 5]);
-        o.w = pack_bf16(s[8 * c + 6], s[8 * c + 7]);
-        d.x = pack_bf16(dp[8 * c + 0], dp[8 * c + 1]);
-        d.y = pack_bf16(dp[8 * c + 2], dp[8 * c + 3]);
-        d.z = pack_bf16(dp[8 * c + 4], dp[8 * c + 5]);
-        d.w = pack_bf16(dp[8 * c + 6], dp[8 * c + 7]);
-        const int sw = (((half * 4 + c) ^ (row & 7)) << 4);
+        o.x = pack_bf16(pr[8 * c + 0], pr[8 * c + 1]);
+        o.y = pack_bf16(pr[8 * c + 2], pr[8 * c + 3]);
+        o.z = pack_bf16(pr[8 * c + 4], pr[8 * c + 5]);
+        o.w = pack_bf16(pr[8 * c + 6], pr[8 * c + 7]);
+        d.x = pack_bf16(ds[8 * c + 0], ds[8 * c + 1]);
+        d.y = pack_bf16(ds[8 * c + 2], ds[8 * c + 3]);
+        d.z = pack_bf16(ds[8 * c + 4], ds[8 * c + 5]);
+        d.w = pack_bf16(ds[8 * c + 6], ds[8 * c + 7]);
+        const int sw = (((slice * 2 + c) ^ (row & 7)) << 4);
         *reinterpret_cast<uint4*>(prow + sw) = o;
         *reinterpret_cast<uint4*>(dsrow + sw) = d;
       }
@@ -417,8 +449,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t tm_src = which == 0 ? tm_dK : tm_dV;
         uint8_t* dst = (which == 0 ? sK : sV) + row * 128;
 #pragma unroll
+        const float out_scale = which == 0 ? p.scale : 1.f;  // dS was left unscaled
+#pragma unroll
         for (int c = 0; c < D / 32; ++c) {
-          if ((c & 1) != half) continue;  // the two warps of a row pair split the column chunks
+          if ((c & 3) != slice) continue;  // the warps of a row quartet split the column chunks
           uint32_t v[32];
           if (n_iters > 0) {
             tmem_ld_32x32(tm_src + lane_addr + c * 32, v);
@@ -430,18 +464,22 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             uint4 o;
-            o.x = pack_bf16(__uint_as_float(v[8 * q4 + 0]), __uint_as_float(v[8 * q4 + 1]));
-            o.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
-            o.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
-            o.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
+            o.x = pack_bf16(__uint_as_float(v[8 * q4 + 0]) * out_scale,
+                            __uint_as_float(v[8 * q4 + 1]) * out_scale);
+            o.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]) * out_scale,
+                            __uint_as_float(v[8 * q4 + 3]) * out_scale);
+            o.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]) * out_scale,
+                            __uint_as_float(v[8 * q4 + 5]) * out_scale);
+            o.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]) * out_scale,
+                            __uint_as_float(v[8 * q4 + 7]) * out_scale);
             const int chunk = c * 4 + q4;
             *reinterpret_cast<uint4*>(dst + (chunk >> 3) * 16384 + (((chunk & 7) ^ (row & 7)) << 4)) = o;
           }
         }
       }
       fence_proxy_async_smem();
-      ok = group_sync();  // both warps of every row pair have written their chunks
-      if (ok && half == 0 && lane == 0 && kv0 + quarter * 32 < p.S) {
+      ok = group_sync();  // all warps of every row quartet have written their chunks
+      if (ok && slice == 0 && lane == 0 && kv0 + quarter * 32 < p.S) {
 #pragma unroll
         for (int s2 = 0; s2 < kDSub; ++s2) {
           tma_store_4d(&tmdK, sK + s2 * 16384 + quarter * 32 * 128, s2 * 64, hk, kv0 + quarter * 32, b);
@@ -571,7 +609,8 @@ void attn_delta(const void* o, const void* d_o, float* delta, int B, int T, int 
 }
 
 // strides = {q_tok, q_batch, k_tok, k_batch, v_tok, v_batch, do_tok, do_batch} in elements.
-// dq: zero-initialised fp32 (B, T, H, D); dk, dv: bf16 (B, S, Hk, D) contiguous.
+// dq: zero-initialised fp32 (B, T, H, D), receives the gradient without the softmax scale;
+// dk, dv: bf16 (B, S, Hk, D) contiguous.
 void flash_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, float* dq,
                     void* dk, void* dv, const float* lse, const float* delta, int B, int T, int S,
                     int H, int Hk, int D, bool causal, float scale, const int64_t* strides,
@@ -732,7 +771,7 @@ extern "C" int ob_flash_attn_bwd_noalloc(const void* q, const void* k, const voi
                     : noalloc_launch<64>(q, k, v, dout, dq32, dk, dv, lse, delta, B, T, S, H, Hk,
                                          causal != 0, scale, status, configure, stream);
     if (rc != cudaSuccess) throw std::runtime_error(cudaGetErrorString(rc));
-    cast_f32_bf16(dq32, dq, dq_elems, stream);
+    cast_f32_bf16(dq32, dq, dq_elems, stream, scale);
   } catch (const std::exception& e) {
     std::snprintf(msg, sizeof(msg), "ob_flash_attn_bwd_noalloc: %s", e.what());
     return noalloc_fail(-3, msg, err, err_len);

@@ -150,19 +150,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       const uint32_t idesc_o = make_idesc_bf16(128, D, false, true);
+      // Descriptors at offset 0 of each buffer; the issue loops only add offsets.
+      const SmemDesc dQ = make_smem_desc_parts(smem_u32(sQ), 16, 1024);
+      const SmemDesc dK = make_smem_desc_parts(smem_u32(sK), 16, 1024);
+      const SmemDesc dP = make_smem_desc_parts(smem_u32(sP), 16, 1024);
+      const SmemDesc dV = make_smem_desc_parts(smem_u32(sV), 16384, 1024);
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(&k_full[st], ph, wctx, kTimeoutFullBarrier)) return false;
         if (!mbar_wait(&s_empty[st], ph ^ 1, wctx, kTimeoutSoftmax)) return false;
         tcgen05_fence_after();
-        const uint32_t qa = smem_u32(sQ);
-        const uint32_t ka = smem_u32(sK + st * L::kTileBytes);
+        const uint32_t k_off = st * L::kTileBytes;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k / 4) * 16384 + (k % 4) * 32;
-          umma_bf16_ss(tmem_S[st], make_smem_desc_sw128(qa + off, 16, 1024),
-                       make_smem_desc_sw128(ka + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+          if (k == 0)
+            umma_bf16_ss_c<0>(tmem_S[st], smem_desc_at(dQ, off), smem_desc_at(dK, k_off + off), idesc_s);
+          else
+            umma_bf16_ss_c<1>(tmem_S[st], smem_desc_at(dQ, off), smem_desc_at(dK, k_off + off), idesc_s);
         }
         tcgen05_commit(&s_full[st]);
         tcgen05_commit(&k_empty[st]);
@@ -179,14 +185,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!mbar_wait(p_full, j & 1, wctx, kTimeoutSoftmax)) break;
         if (!mbar_wait(&v_full[st], ph, wctx, kTimeoutFullBarrier)) break;
         tcgen05_fence_after();
-        const uint32_t pa = smem_u32(sP);
-        const uint32_t va = smem_u32(sV + st * L::kTileBytes);
+        const uint32_t v_off = st * L::kTileBytes;
+        umma_bf16_ss(tmem_O, smem_desc_at(dP, 0), smem_desc_at(dV, v_off), idesc_o, j > 0 ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < kBlockKV / 16; ++k) {
-          const uint64_t da = make_smem_desc_sw128(pa + (k / 4) * 16384 + (k % 4) * 32, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(va + k * 2048, 16384, 1024);
-          umma_bf16_ss(tmem_O, da, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-        }
+        for (int k = 1; k < kBlockKV / 16; ++k)
+          umma_bf16_ss_c<1>(tmem_O, smem_desc_at(dP, (k / 4) * 16384 + (k % 4) * 32),
+                            smem_desc_at(dV, v_off + k * 2048), idesc_o);
         tcgen05_commit(pv_done);
         tcgen05_commit(&v_empty[st]);
       }

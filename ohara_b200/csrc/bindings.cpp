@@ -360,7 +360,10 @@ std::vector<Tensor> flash_attn_bwd(const Tensor& dout_in, const Tensor& q_in, co
                      dq32.data_ptr<float>(), dk.data_ptr(), dv.data_ptr(), lse.data_ptr<float>(),
                      delta.data_ptr<float>(), (int)B, (int)T, (int)S, (int)H, (int)Hk, (int)D,
                      causal, (float)scale, strides, current_stream());
-  return {dq32.to(torch::kBFloat16), dk, dv};
+  Tensor dq = torch::empty({B, T, H, D}, q.options());
+  ob::cast_f32_bf16(dq32.data_ptr<float>(), dq.data_ptr(), dq32.numel(), current_stream(),
+                    (float)scale);
+  return {dq, dk, dv};
 }
 
 // ---- peer memory ---------------------------------------------------------------------------------

@@ -252,6 +252,21 @@ __device__ __forceinline__ void umma_bf16_ss(uint32_t tmem_d, uint64_t desc_a, u
       : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same with the accumulate flag known at compile time (no predicate set-up in the issue loop).
+template <int kAccumulate>
+__device__ __forceinline__ void umma_bf16_ss_c(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                               uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "n"(kAccumulate)
+      : "memory");
+}
+
 // D[tmem] (+)= A[tmem] * B[smem desc]; A holds bf16 pairs packed in 32-bit TMEM columns.
 __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
                                              uint32_t idesc, uint32_t accumulate) {
@@ -324,6 +339,26 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   return desc;
 }
 
+// A descriptor split into its 32-bit halves, so that the MMA issuer can step through a tile with one
+// integer add per operand instead of rebuilding the 64-bit value (the issuing thread's own
+// instruction latency, not the tensor pipe, bounds kernels that issue many small MMAs).
+struct SmemDesc {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ SmemDesc make_smem_desc_parts(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                         uint32_t sbo_bytes) {
+  const uint64_t d = make_smem_desc_sw128(smem_addr, lbo_bytes, sbo_bytes);
+  return SmemDesc{static_cast<uint32_t>(d), static_cast<uint32_t>(d >> 32)};
+}
+// The descriptor of the same layout `bytes` further into shared memory (a multiple of 16; the
+// start-address field holds address >> 4 in its low 14 bits and cannot overflow below 256 KB).
+__device__ __forceinline__ uint64_t smem_desc_at(const SmemDesc& d, uint32_t bytes) {
+  uint64_t r;
+  const uint32_t lo = d.lo + (bytes >> 4);
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(d.hi));
+  return r;
+}
+
 // Instruction descriptor for kind::f16 with bf16 A/B and fp32 accumulate.
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn_major,
                                                        bool b_mn_major) {
@@ -334,6 +369,13 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn_m
          | ((b_mn_major ? 1u : 0u) << 16)
          | (static_cast<uint32_t>(n >> 3) << 17)
          | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// 2^x in one MUFU instruction (flushes denormal results to zero, which is what a softmax wants).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

@@ -257,18 +257,19 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ da,
 // Casts and embedding
 // ------------------------------------------------------------------------------------------------
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out,
-                                     int64_t n) {
+                                     int64_t n, float scale) {
   const int64_t vecs = n >> 3;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < vecs;
        idx += (int64_t)gridDim.x * blockDim.x) {
     const float4 a = reinterpret_cast<const float4*>(in)[2 * idx];
     const float4 b = reinterpret_cast<const float4*>(in)[2 * idx + 1];
-    const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const float f[8] = {a.x * scale, a.y * scale, a.z * scale, a.w * scale,
+                        b.x * scale, b.y * scale, b.z * scale, b.w * scale};
     reinterpret_cast<bf16x8*>(out)[idx] = pack8(f);
   }
   if (blockIdx.x == 0) {
     for (int64_t i = (vecs << 3) + threadIdx.x; i < n; i += blockDim.x)
-      out[i] = __float2bfloat16_rn(in[i]);
+      out[i] = __float2bfloat16_rn(in[i] * scale);
   }
 }
 
@@ -424,11 +425,11 @@ void swiglu_bwd(const void* da, const void* g, const void* u, void* dg, void* du
   OB_LAUNCH_CHECK();
 }
 
-void cast_f32_bf16(const float* in, void* out, int64_t n, cudaStream_t stream) {
+void cast_f32_bf16(const float* in, void* out, int64_t n, cudaStream_t stream, float scale) {
   if (n == 0) return;
   const int threads = 256;
   cast_f32_bf16_kernel<<<grid_for((n + 7) / 8, threads), threads, 0, stream>>>(
-      in, (__nv_bfloat16*)out, n);
+      in, (__nv_bfloat16*)out, n, scale);
   OB_LAUNCH_CHECK();
 }
 
