@@ -28,6 +28,16 @@
 //
 // Warp roles (192 threads): warps 0-3 epilogue (TMEM lane quarter = warp index), warp 4 TMA
 // producer, warp 5 MMA issuer + TMEM allocator.
+//
+// PAIR variant (plain and batched GEMMs with N > 128): two CTAs of a cluster share one 256 x 256
+// output tile. Each loads its own 128 rows of A and one half (128 rows) of B per k-block, the
+// leader CTA issues `tcgen05.mma.cta_group::2` (M = 256) which reads both CTAs' shared memory and
+// writes 128 accumulator rows into each CTA's TMEM, and each CTA runs the epilogue of its rows.
+// Per SM and k-block this moves 32 KB of operands instead of 48 KB: the single-CTA kernel is
+// bound by operand delivery (L2 -> shared memory -> tensor core), not by the tensor pipe. The
+// loads carry no cluster multicast; the pair is coupled only through mbarriers (the leader's
+// "full" barrier counts the bytes of both producers, its commits arrive on both CTAs' "empty"
+// and "accumulator ready" barriers, both epilogues arrive on the leader's "accumulator free").
 #include "api.h"
 #include "common.cuh"
 #include "host_utils.h"
@@ -95,13 +105,14 @@ __device__ __forceinline__ bool wait_peer_flag(const unsigned int* flag, unsigne
   return true;
 }
 
-template <int BN>
+template <int BN, bool PAIR = false>
 struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
-  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;  // rows of B this CTA loads per k-block
+  static constexpr int kBBytes = kBRows * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStagingBytes = 4 /*warps*/ * 2 /*buffers*/ * 4096;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = PAIR ? 6 : ((BN == 256) ? 4 : 6);
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
 };
@@ -133,11 +144,12 @@ __device__ __forceinline__ void load_residual(const GemmParams& p, int batch, in
   }
 }
 
-template <int BN, bool OUT_F32>
+template <int BN, bool OUT_F32, bool PAIR>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BN, PAIR>;
+  constexpr int TM = PAIR ? 2 * BM : BM;  // rows of C per tile (per CTA pair when PAIR)
   constexpr int kStages = L::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -156,10 +168,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int m_tiles = (p.M + BM - 1) / BM;
+  const int m_tiles = (p.M + TM - 1) / TM;
   const int n_tiles = (p.N + BN - 1) / BN;
   const int tiles_per_batch = m_tiles * n_tiles * p.splits;
   const int total_tiles = tiles_per_batch * p.batches;
+  // Tiles are dealt to CTAs (or CTA pairs) round robin.
+  const uint32_t cta_rank = PAIR ? cluster_cta_rank() : 0u;
+  const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -168,8 +184,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     mbar_init(&tmem_full[0], 1);
     mbar_init(&tmem_full[1], 1);
-    mbar_init(&tmem_empty[0], 4);
-    mbar_init(&tmem_empty[1], 4);
+    mbar_init(&tmem_empty[0], PAIR ? 8 : 4);  // epilogue warps (of both CTAs when PAIR)
+    mbar_init(&tmem_empty[1], PAIR ? 8 : 4);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -179,11 +195,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     prefetch_tmap(&tmC);
   }
   if (warp == 5) {
-    tmem_alloc(tmem_slot, 2 * BN);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_slot, 2 * BN);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, 2 * BN);
+      tmem_relinquish();
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  // Nothing may touch the peer's barriers before the peer has initialised them.
+  if constexpr (PAIR) cluster_sync_all();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -216,7 +239,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       int ready_src = -1;  // source rank whose rows are known to have arrived
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
         int batch, mt, nt, kb_begin, kb_count, k0;
         decode(tile, batch, mt, nt, kb_begin, kb_count, k0);
         int b_batch = batch;
@@ -227,7 +250,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int za = p.a_batched ? batch : 0;
         const int zb = p.b_batched ? b_batch : 0;
         const CUtensorMap* mapA = &tmA;
-        int a_row = mt * BM;
+        int a_row = mt * TM + (int)cta_rank * BM;
+        const int b_row = nt * BN + (int)cta_rank * L::kBRows;
         if (p.comm_mode == 1) {
           const int src = a_row / p.rows_per_rank;
           if (src != ready_src) {
@@ -249,8 +273,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           uint8_t* sa = stage_base + s * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
-          mbar_expect_tx(&full_bar[s], L::kStageBytes);
           const int k = k0 + (kb_begin + kb) * BK;
+          if constexpr (PAIR) {
+            // The leader's barrier collects the bytes of both CTAs' loads.
+            const uint32_t full_addr = map_to_cta(smem_u32(&full_bar[s]), 0);
+            if (cta_rank == 0) mbar_expect_tx(&full_bar[s], 2 * L::kStageBytes);
+            if (p.a_mn) {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j)
+                tma_load_3d_pair(sa + j * (BK * 128), &tmA, full_addr, a_row + j * 64, k, za);
+            } else {
+              tma_load_3d_pair(sa, &tmA, full_addr, k, a_row, za);
+            }
+            if (p.b_mn) {
+#pragma unroll
+              for (int j = 0; j < L::kBRows / 64; ++j)
+                tma_load_3d_pair(sb + j * (BK * 128), &tmB, full_addr, b_row + j * 64, k, zb);
+            } else {
+              tma_load_3d_pair(sb, &tmB, full_addr, k, b_row, zb);
+            }
+            continue;
+          }
+          mbar_expect_tx(&full_bar[s], L::kStageBytes);
           if (p.a_mn) {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
@@ -270,20 +314,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 5) {
     // ------------------------------- MMA issuer ----------------------------------------------
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn != 0, p.b_mn != 0);
+    if (lane == 0 && cta_rank == 0) {
+      const uint32_t idesc = make_idesc_bf16(TM, BN, p.a_mn != 0, p.b_mn != 0);
+      // Descriptors of the operands in stage 0; stepping through k and stages only adds offsets.
+      const SmemDesc desc_a = make_smem_desc_parts(smem_u32(stage_base), p.a_mn ? BK * 128 : 16, 1024);
+      const SmemDesc desc_b = make_smem_desc_parts(smem_u32(stage_base + L::kABytes),
+                                                   p.b_mn ? BK * 128 : 16, 1024);
+      const uint32_t step_a = p.a_mn ? 2048 : 32;
+      const uint32_t step_b = p.b_mn ? 2048 : 32;
+      // This CTA's first non-padding tile at or after `tile`, and its number of k-blocks.
+      auto next_tile = [&](int tile, int& kb_count) -> int {
+        for (; tile < total_tiles; tile += tile_step) {
+          int batch, mt, nt, kb_begin, k0;
+          decode(tile, batch, mt, nt, kb_begin, kb_count, k0);
+          if (p.m_tile_batch == nullptr || p.m_tile_batch[mt] >= 0) return tile;
+        }
+        return total_tiles;
+      };
       uint32_t it = 0;
       uint32_t tile_iter = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int batch, mt, nt, kb_begin, kb_count, k0;
-        decode(tile, batch, mt, nt, kb_begin, kb_count, k0);
-        if (p.m_tile_batch != nullptr && p.m_tile_batch[mt] < 0) continue;
+      int kb_count = 0;
+      int tile = next_tile(first_tile, kb_count);
+      while (tile < total_tiles && ok) {
         const uint32_t acc = tile_iter & 1;
         const uint32_t acc_phase = (tile_iter >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, wctx, kTimeoutTmemEmpty)) break;
         tcgen05_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * BN;
+        int next = -1, next_kb = 0;
         for (int kb = 0; kb < kb_count; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1;
@@ -292,21 +351,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             break;
           }
           tcgen05_fence_after();
-          const uint32_t sa = smem_u32(stage_base + s * L::kStageBytes);
-          const uint32_t sb = sa + L::kABytes;
+          const uint32_t stage_off = s * L::kStageBytes;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t da = p.a_mn ? make_smem_desc_sw128(sa + k * 2048, BK * 128, 1024)
-                                       : make_smem_desc_sw128(sa + k * 32, 16, 1024);
-            const uint64_t db = p.b_mn ? make_smem_desc_sw128(sb + k * 2048, BK * 128, 1024)
-                                       : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            umma_bf16_ss(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            const uint64_t da = smem_desc_at(desc_a, stage_off + k * step_a);
+            const uint64_t db = smem_desc_at(desc_b, stage_off + k * step_b);
+            if constexpr (PAIR)
+              umma_bf16_ss_pair(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else
+              umma_bf16_ss(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
-          tcgen05_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+          // Frees the stage (in both CTAs when PAIR) once these MMAs have read it.
+          if constexpr (PAIR) {
+            const uint32_t addr = smem_u32(&empty_bar[s]);
+            tcgen05_commit_pair(map_to_cta(addr, 0));
+            tcgen05_commit_pair(map_to_cta(addr, 1));
+          } else {
+            tcgen05_commit(&empty_bar[s]);
+          }
+          // Work out the next tile while the tensor pipe is busy with this one, so that the
+          // integer divisions of the tile decode stay off the tile-to-tile critical path.
+          if (kb == 0) next = next_tile(tile + tile_step, next_kb);
         }
         if (!ok) break;
-        tcgen05_commit(&tmem_full[acc]);
+        if constexpr (PAIR) {
+          const uint32_t addr = smem_u32(&tmem_full[acc]);
+          tcgen05_commit_pair(map_to_cta(addr, 0));
+          tcgen05_commit_pair(map_to_cta(addr, 1));
+        } else {
+          tcgen05_commit(&tmem_full[acc]);
+        }
+        if (next < 0) next = next_tile(tile + tile_step, next_kb);
         ++tile_iter;
+        tile = next;
+        kb_count = next_kb;
       }
     }
   } else {
@@ -315,7 +393,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t tile_iter = 0;
     uint32_t store_iter = 0;
     constexpr int kColsPerStore = OUT_F32 ? 32 : 64;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
       int batch, mt, nt, kb_begin, kb_count, k0;
       decode(tile, batch, mt, nt, kb_begin, kb_count, k0);
       if (p.m_tile_batch != nullptr && p.m_tile_batch[mt] < 0) continue;
@@ -325,7 +403,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tcgen05_fence_after();
       const bool skip_store = (kb_count == 0) && p.reduce;
       const uint32_t taddr_row = tmem_base + acc * BN + (static_cast<uint32_t>(warp * 32) << 16);
-      const int row0 = mt * BM + warp * 32;
+      const int row0 = mt * TM + (int)cta_rank * BM + warp * 32;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += kColsPerStore) {
         const int col0 = nt * BN + c0;
@@ -417,7 +495,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // All TMEM reads of this accumulator are complete (tmem_ld_wait above): hand it back.
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (lane == 0) {
+        if constexpr (PAIR)
+          mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));  // the leader's barrier
+        else
+          mbar_arrive(&tmem_empty[acc]);
+      }
       ++tile_iter;
     }
     if (lane == 0) tma_store_wait_all<0>();
@@ -431,9 +514,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
   tcgen05_fence_before();
   __syncthreads();
+  // A CTA of a pair must outlive every access of its peer to its shared memory and barriers.
+  if constexpr (PAIR) cluster_sync_all();
   if (warp == 5) {
     tcgen05_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    if constexpr (PAIR)
+      tmem_dealloc_pair(tmem_base, 2 * BN);
+    else
+      tmem_dealloc(tmem_base, 2 * BN);
   }
 }
 
@@ -441,7 +529,7 @@ template <int BN, bool OUT_F32>
 void launch_variant(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC,
                     const GemmParams& p, int grid, cudaStream_t stream) {
   using L = SmemLayout<BN>;
-  auto kernel = gemm_bf16_kernel<BN, OUT_F32>;
+  auto kernel = gemm_bf16_kernel<BN, OUT_F32, false>;
   static bool configured = false;
   if (!configured) {
     OB_CUDA_CHECK(
@@ -450,6 +538,49 @@ void launch_variant(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensor
   }
   kernel<<<grid, kNumThreads, L::kTotal, stream>>>(tA, tB, tC, p);
   OB_LAUNCH_CHECK();
+}
+
+// CTA-pair variant: clusters of two, at most `max_pairs` of them (0 = ask the driver how many can
+// be resident, once per kernel).
+template <bool OUT_F32>
+void launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC,
+                 const GemmParams& p, long long total_tiles, int num_sms, cudaStream_t stream) {
+  using L = SmemLayout<256, true>;
+  auto kernel = gemm_bf16_kernel<256, OUT_F32, true>;
+  static int resident_pairs = 0;
+  cudaLaunchConfig_t config = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  config.blockDim = dim3(kNumThreads, 1, 1);
+  config.dynamicSmemBytes = L::kTotal;
+  config.stream = stream;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  if (resident_pairs == 0) {
+    OB_CUDA_CHECK(
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    config.gridDim = dim3(2 * (num_sms / 2), 1, 1);
+    int clusters = 0;
+    OB_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&clusters, kernel, &config));
+    resident_pairs = std::max(1, std::min(clusters, num_sms / 2));
+  }
+  const int pairs = (int)std::min<long long>(total_tiles, std::min(resident_pairs, num_sms / 2));
+  config.gridDim = dim3(2 * pairs, 1, 1);
+  OB_CUDA_CHECK(cudaLaunchKernelEx(&config, kernel, tA, tB, tC, p));
+  count_launch();
+}
+
+// The pair kernel serves plain and batched products whose output is wide enough for a 256-column
+// tile; ragged (mixture-of-experts) and fused-collective modes stay on the single-CTA kernel.
+bool pair_enabled() {
+  static const bool enabled = [] {
+    const char* e = std::getenv("OHARA_GEMM_PAIR");
+    return e == nullptr || e[0] != '0';
+  }();
+  return enabled;
 }
 
 }  // namespace
@@ -478,6 +609,8 @@ void gemm_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, 
   OB_CHECK(!reduce || out_f32, "gemm_bf16: reduce-add epilogue needs an fp32 output");
   OB_CHECK(splits >= 1 && (splits == 1 || reduce), "gemm_bf16: split-K needs the reduce epilogue");
   const int BN = (N > 128) ? 256 : 128;
+  const bool pair = pair_enabled() && BN == 256 && M > 128 && m_tile_batch == nullptr &&
+                    k_offsets == nullptr && (comm == nullptr || comm->mode == 0);
 
   GemmParams p;
   p.M = M;
@@ -552,15 +685,21 @@ void gemm_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, 
   make_tmap_3d(&tA, A, TmapDtype::BF16, a_inner, (uint64_t)a_rows, (uint64_t)a_nb, lda, strideA, 64,
                a_mn ? BK : BM, TmapSwizzle::B128);
   make_tmap_3d(&tB, B, TmapDtype::BF16, b_inner, (uint64_t)b_rows, (uint64_t)b_nb, ldb, strideB, 64,
-               b_mn ? BK : BN, TmapSwizzle::B128);
+               b_mn ? BK : (pair ? BN / 2 : BN), TmapSwizzle::B128);
   make_tmap_3d(&tC, C, out_f32 ? TmapDtype::F32 : TmapDtype::BF16, (uint64_t)N, (uint64_t)M,
                (uint64_t)batches, ldc, strideC, out_f32 ? 32 : 64, 32, TmapSwizzle::B128);
 
-  const int m_tiles = (M + BM - 1) / BM;
+  const int tile_m = pair ? 2 * BM : BM;
+  const int m_tiles = (M + tile_m - 1) / tile_m;
   const int n_tiles = (N + BN - 1) / BN;
   const long long total = (long long)m_tiles * n_tiles * splits * batches;
   const int grid = (int)std::min<long long>(total, num_sms);
-  if (BN == 256) {
+  if (pair) {
+    if (out_f32)
+      launch_pair<true>(tA, tB, tC, p, total, num_sms, stream);
+    else
+      launch_pair<false>(tA, tB, tC, p, total, num_sms, stream);
+  } else if (BN == 256) {
     if (out_f32)
       launch_variant<256, true>(tA, tB, tC, p, grid, stream);
     else
