@@ -2,13 +2,17 @@
 //
 // One CTA per (batch, head, 128-query tile). Q, K and V tiles arrive by TMA straight from the
 // (batch, seq, heads, head_dim) projection layout; S = Q K^T and O += P V run on tcgen05.mma with
-// S (double buffered) and O accumulating in TMEM. Four softmax warps own one query row per thread:
-// they read S from TMEM, keep the running max / sum in registers, write P as bf16 into swizzled
-// shared memory (the A operand of the second MMA) and rescale O in TMEM only when the running max
-// moved by more than 2^8 (lazy rescaling; the final division by the row sum makes this exact).
-// While the softmax of tile j runs, the MMA warp has already issued S for tile j+1.
+// S (double buffered) and O accumulating in TMEM. Eight softmax warps, two threads per query row:
+// warps 0-3 exponentiate key columns 0-63 of a tile, warps 4-7 columns 64-127 (the element-wise
+// work is bound by instruction latency, so it is spread over two warps per scheduler). Both
+// threads of a row scan all 128 scores for the row maximum, so they agree on it without talking to
+// each other; each keeps a partial row sum, and the two are added once, in the epilogue. P goes as
+// bf16 into swizzled shared memory (double buffered; the A operand of the second MMA), and O is
+// rescaled in TMEM only when the running max moved by more than 2^8 (lazy rescaling; the final
+// division by the row sum makes this exact). While the softmax of tile j runs, the MMA warp has
+// already issued S for tile j+1.
 //
-// Warp roles (192 threads): 0-3 softmax + epilogue, 4 TMA producer, 5 MMA issuer / TMEM owner.
+// Warp roles (320 threads): 0-7 softmax + epilogue, 8 TMA producer, 9 MMA issuer / TMEM owner.
 #include "common.cuh"
 #include "host_utils.h"
 
@@ -18,7 +22,10 @@ namespace {
 
 constexpr int kBlockQ = 128;
 constexpr int kBlockKV = 128;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kSoftmaxWarps = 8;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;
 
@@ -37,8 +44,9 @@ struct FwdSmem {
   static constexpr int kQ = 0;
   static constexpr int kK = kTileBytes;
   static constexpr int kV = kK + 2 * kTileBytes;
-  static constexpr int kP = kV + 2 * kTileBytes;
-  static constexpr int kBars = kP + kPBytes;
+  static constexpr int kP = kV + 2 * kTileBytes;   // 2 buffers of P
+  static constexpr int kSums = kP + 2 * kPBytes;   // 2 x 128 partial row sums (epilogue exchange)
+  static constexpr int kBars = kSums + 256 * 4;
   // At least 120 KB so two CTAs never share an SM (each allocates all 512 TMEM columns).
   static constexpr int kTotal = (kBars + 256 + 1024) > 120 * 1024 ? (kBars + 256 + 1024) : 120 * 1024;
 };
@@ -65,9 +73,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* v_empty = bars + 7;     // 2
   uint64_t* s_full = bars + 9;      // 2
   uint64_t* s_empty = bars + 11;    // 2
-  uint64_t* p_full = bars + 13;     // 1
-  uint64_t* pv_done = bars + 14;    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  // p_full and pv_done alternate between two barriers by tile parity: their waiters have already
+  // enabled the next completion when they start to wait, so a single barrier could complete twice
+  // before a delayed waiter looks, which a parity wait cannot tell from "not yet".
+  uint64_t* p_full = bars + 13;     // 2
+  uint64_t* pv_done = bars + 15;    // 2
+  uint64_t* grp_bar = bars + 17;    // 1 (all softmax threads, epilogue only)
+  float* sSums = reinterpret_cast<float*>(smem + L::kSums);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx wctx{abort_flag, p.status};
 
@@ -98,20 +111,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
+      mbar_init(&s_empty[i], kSoftmaxWarps);
+      mbar_init(&p_full[i], kSoftmaxWarps);
+      mbar_init(&pv_done[i], 1);
     }
-    mbar_init(p_full, 4);
-    mbar_init(pv_done, 1);
+    mbar_init(grp_bar, kSoftmaxWarps * 32);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     prefetch_tmap(&tmQ);
     prefetch_tmap(&tmK);
     prefetch_tmap(&tmV);
     prefetch_tmap(&tmO);
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -122,7 +136,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tmem_S[2] = {tmem_base, tmem_base + 128};
   const uint32_t tmem_O = tmem_base + 256;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------ TMA producer ---------------------------------------------
     if (lane == 0) {
       mbar_expect_tx(q_full, L::kTileBytes);
@@ -145,7 +159,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                       j * kBlockKV, b);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer -----------------------------------------------
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
@@ -182,26 +196,29 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(p_full, j & 1, wctx, kTimeoutSoftmax)) break;
+        if (!mbar_wait(&p_full[j & 1], (j >> 1) & 1, wctx, kTimeoutSoftmax)) break;
         if (!mbar_wait(&v_full[st], ph, wctx, kTimeoutFullBarrier)) break;
         tcgen05_fence_after();
         const uint32_t v_off = st * L::kTileBytes;
-        umma_bf16_ss(tmem_O, smem_desc_at(dP, 0), smem_desc_at(dV, v_off), idesc_o, j > 0 ? 1u : 0u);
+        const uint32_t p_off = (j & 1) * L::kPBytes;
+        umma_bf16_ss(tmem_O, smem_desc_at(dP, p_off), smem_desc_at(dV, v_off), idesc_o, j > 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 1; k < kBlockKV / 16; ++k)
-          umma_bf16_ss_c<1>(tmem_O, smem_desc_at(dP, (k / 4) * 16384 + (k % 4) * 32),
+          umma_bf16_ss_c<1>(tmem_O, smem_desc_at(dP, p_off + (k / 4) * 16384 + (k % 4) * 32),
                             smem_desc_at(dV, v_off + k * 2048), idesc_o);
-        tcgen05_commit(pv_done);
+        tcgen05_commit(&pv_done[j & 1]);
         tcgen05_commit(&v_empty[st]);
       }
     }
   } else {
     // ------------------------------ Softmax + epilogue (warps 0..3) --------------------------
-    const int row = warp * 32 + lane;  // query row within the tile == TMEM lane
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may touch
+    const int half = warp >> 2;    // which 64 key columns of a tile (and which half of head_dim)
+    const int row = quarter * 32 + lane;  // query row within the tile == TMEM lane
     const int t = t0 + row;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     float m_run = -INFINITY;  // running max, log2 domain, possibly stale (lazy rescale)
-    float l_run = 0.f;
+    float l_run = 0.f;        // partial row sum over this thread's columns
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int st = j & 1;
@@ -215,30 +232,37 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const bool need_mask =
           (p.causal && (kv0 + kBlockKV - 1 > t0 + offset)) || (kv0 + kBlockKV > p.S);
       const int limit = p.causal ? min(t + offset, p.S - 1) : (p.S - 1);  // last visible key
-      float s[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_S[st] + lane_addr + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]);
-      }
+      // Own 64 columns stay in registers; the other 64 are only scanned for the row maximum.
+      uint32_t own[64], other[64];
+      tmem_ld_32x32(tmem_S[st] + lane_addr + half * 64, reinterpret_cast<uint32_t(&)[32]>(own[0]));
+      tmem_ld_32x32(tmem_S[st] + lane_addr + half * 64 + 32,
+                    reinterpret_cast<uint32_t(&)[32]>(own[32]));
+      tmem_ld_32x32(tmem_S[st] + lane_addr + (half ^ 1) * 64,
+                    reinterpret_cast<uint32_t(&)[32]>(other[0]));
+      tmem_ld_32x32(tmem_S[st] + lane_addr + (half ^ 1) * 64 + 32,
+                    reinterpret_cast<uint32_t(&)[32]>(other[32]));
+      tmem_ld_wait();
       // S buffer is free for the MMA of tile j+2.
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[st]);
 
+      float s[64];
       float mx = -INFINITY;
+      const int own0 = kv0 + half * 64, other0 = kv0 + (half ^ 1) * 64;
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
-          if (kv0 + i > limit) s[i] = -INFINITY;
+        for (int i = 0; i < 64; ++i) {
+          s[i] = (own0 + i > limit) ? -INFINITY : __uint_as_float(own[i]);
           mx = fmaxf(mx, s[i]);
+          if (other0 + i <= limit) mx = fmaxf(mx, __uint_as_float(other[i]));
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 128; ++i) mx = fmaxf(mx, s[i]);
+        for (int i = 0; i < 64; ++i) {
+          s[i] = __uint_as_float(own[i]);
+          mx = fmaxf(mx, fmaxf(s[i], __uint_as_float(other[i])));
+        }
       }
       const float m_new = mx * p.scale_log2;
       // Lazy rescale: keep the stale max unless it is too far behind (or not set yet).
@@ -252,58 +276,74 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (m_use == -INFINITY) m_use = 0.f;  // fully masked so far: every p below is 0
       float sum = 0.f;
 #pragma unroll
-      for (int i = 0; i < 128; ++i) {
-        s[i] = exp2f(s[i] * p.scale_log2 - m_use);
+      for (int i = 0; i < 64; ++i) {
+        s[i] = fast_exp2(fmaf(s[i], p.scale_log2, -m_use));
         sum += s[i];
       }
       l_run = l_run * alpha + sum;
       m_run = (grow && m_new > -INFINITY) ? m_new : m_run;
 
-      // P smem and O are stable once the previous PV product has completed.
-      if (j > 0) {
-        if (!mbar_wait(pv_done, (j - 1) & 1, wctx, kTimeoutTmemFull)) {
+      // O may only be rescaled between two PV products. Both threads of a row take the same
+      // decision (same maximum) and each rescales its half of head_dim.
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        if (!mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, wctx, kTimeoutTmemFull)) {
           ok = false;
           break;
         }
         tcgen05_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-          for (int c = 0; c < D / 16; ++c) {
-            uint32_t v[16];
-            tmem_ld_32x16(tmem_O + lane_addr + c * 16, v);
-            tmem_ld_wait();
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[16];
+          const uint32_t addr = tmem_O + lane_addr + half * (D / 2) + c * 16;
+          tmem_ld_32x16(addr, v);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x16(tmem_O + lane_addr + c * 16, v);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st_32x16(addr, v);
+        }
+        tmem_st_wait();
+      }
+      // P buffer (j & 1) was last read by the PV product of tile j-2.
+      if (j > 1) {
+        if (!mbar_wait(&pv_done[j & 1], ((j - 2) >> 1) & 1, wctx, kTimeoutTmemFull)) {
+          ok = false;
+          break;
         }
       }
-      // Write P (bf16) as a K-major, 128B-swizzled A operand: two 64-column sub-tiles.
-      uint8_t* prow = sP + row * 128;
+      // Write P (bf16) as a K-major, 128B-swizzled A operand: this thread's 64 columns are one of
+      // the two 64-column sub-tiles.
+      uint8_t* prow = sP + (j & 1) * L::kPBytes + half * 16384 + row * 128;
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
+      for (int c = 0; c < 8; ++c) {
         uint4 o;
         o.x = pack_bf16(s[8 * c + 0], s[8 * c + 1]);
         o.y = pack_bf16(s[8 * c + 2], s[8 * c + 3]);
         o.z = pack_bf16(s[8 * c + 4], s[8 * c + 5]);
         o.w = pack_bf16(s[8 * c + 6], s[8 * c + 7]);
-        *reinterpret_cast<uint4*>(prow + (c >> 3) * 16384 + (((c & 7) ^ (row & 7)) << 4)) = o;
+        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = o;
       }
       fence_proxy_async_smem();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[j & 1]);
     }
 
-    // ---- epilogue: O / l -> bf16 -> swizzled smem (reusing the P buffer) -> TMA store ----------
-    if (ok && n_kv > 0) ok = mbar_wait(pv_done, (n_kv - 1) & 1, wctx, kTimeoutTmemFull);
+    // ---- epilogue: O / l -> bf16 -> swizzled smem (reusing P buffer 0) -> TMA store ------------
+    if (ok && n_kv > 0)
+      ok = mbar_wait(&pv_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, wctx, kTimeoutTmemFull);
+    // The two partial sums of a row meet in shared memory; the barrier is an mbarrier so that it
+    // cannot outlive the wait limit if a warp has already given up.
+    sSums[half * 128 + row] = l_run;
+    mbar_arrive(grp_bar);
+    if (!mbar_wait(grp_bar, 0, wctx, kTimeoutSoftmax)) ok = false;
     if (ok) {
       tcgen05_fence_after();
-      const float inv_l = (l_run > 0.f) ? 1.f / l_run : 0.f;
+      const float l_total = l_run + sSums[(half ^ 1) * 128 + row];
+      const float inv_l = (l_total > 0.f) ? 1.f / l_total : 0.f;
       uint8_t* orow = sP + row * 128;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int c = half * (D / 64) + cc;  // 32-column chunk of head_dim
         uint32_t v[32];
         if (n_kv > 0) {
           tmem_ld_32x32(tmem_O + lane_addr + c * 32, v);
@@ -324,16 +364,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0 && t0 + warp * 32 < p.T) {
+      mbar_arrive(grp_bar);
+      if (!mbar_wait(grp_bar, 1, wctx, kTimeoutSoftmax)) ok = false;
+      if (ok && half == 0 && lane == 0 && t0 + quarter * 32 < p.T) {
 #pragma unroll
         for (int s2 = 0; s2 < kDSub; ++s2)
-          tma_store_4d(&tmO, sP + s2 * 16384 + warp * 32 * 128, s2 * 64, h, t0 + warp * 32, b);
+          tma_store_4d(&tmO, sP + s2 * 16384 + quarter * 32 * 128, s2 * 64, h, t0 + quarter * 32, b);
         tma_store_commit();
         tma_store_wait_all<0>();
       }
-      if (t < p.T && p.lse != nullptr) {
-        const float lse2 = (l_run > 0.f) ? (m_run + log2f(l_run)) : -INFINITY;
+      if (half == 0 && t < p.T && p.lse != nullptr) {
+        const float lse2 = (l_total > 0.f) ? (m_run + log2f(l_total)) : -INFINITY;
         p.lse[((size_t)b * p.H + h) * p.T + t] = lse2 * (1.f / kLog2e);
       }
     }
@@ -345,7 +386,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
