@@ -31,6 +31,8 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--warmup", type=int, default=1)
     p.add_argument("--no-graph", action="store_true")
     p.add_argument("--int8-cache", action="store_true")
+    p.add_argument("--tp", type=int, default=1,
+                   help="tensor-parallel degree; launch with torchrun --nproc-per-node <tp>")
     return p.parse_args()
 
 
@@ -73,14 +75,28 @@ def run_ours(args):
             return {token: MODEL["vocab_size"] - 1 - i for i, token in enumerate(CHAT_SPECIAL_TOKENS)}
 
     torch.manual_seed(0)
-    engine = ChatEngine(Llama(Config(**MODEL)), Vocabulary(), device="cuda", dtype=torch.bfloat16)
+    model = Llama(Config(**MODEL))
+    device, rank0 = "cuda", True
+    if args.tp > 1:
+        # Attention heads and the feed-forward width are sharded over the ranks; the all-reduce
+        # behind each row-parallel layer is the one-shot peer-memory kernel, replayed from the
+        # same CUDA graph as the rest of the decode step.
+        from ohara_b200.runtime import EngineConfig, OharaEngine, ParallelConfig, TensorParallelPlan
+
+        runtime = OharaEngine(EngineConfig(parallel=ParallelConfig(tp=args.tp),
+                                           tensor_parallel=TensorParallelPlan.llama_default(args.tp)))
+        runtime.launch()
+        model = runtime.prepare_module(model.to(torch.bfloat16))
+        device, rank0 = runtime.device, runtime.is_global_zero
+    engine = ChatEngine(model, Vocabulary(), device=device, dtype=torch.bfloat16)
     config = SamplingConfig(max_new_tokens=args.new_tokens, **SAMPLING)
     for batch in (int(b) for b in args.batches.split(",")):
-        prompt = torch.randint(0, MODEL["vocab_size"], (batch, args.prompt_len), device="cuda")
+        prompt = torch.randint(0, MODEL["vocab_size"], (batch, args.prompt_len), device=device)
         seconds = time_generations(
             torch, lambda: engine.generate_batch(prompt, config, seed=1, cuda_graph=not args.no_graph),
             args.repeats, args.warmup)
-        report(args, "ours", batch, seconds, {"cuda_graph": not args.no_graph})
+        if rank0:
+            report(args, "ours", batch, seconds, {"cuda_graph": not args.no_graph, "tp": args.tp})
 
 
 def run_reference(args):

@@ -369,7 +369,9 @@ class ChatEngine:
             remaining -= 1
             graph = torch.cuda.CUDAGraph()
             try:
-                with torch.cuda.graph(graph):
+                # thread_local: helper threads of a process group (tensor-parallel decoding) may
+                # query events while this thread captures.
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                     step()
             except RuntimeError:
                 graph = None  # something in the step cannot be captured: fall back to eager

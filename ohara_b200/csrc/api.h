@@ -102,6 +102,14 @@ void flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float*
                     int64_t k_tok_stride, int64_t v_tok_stride, int64_t q_batch_stride,
                     int64_t k_batch_stride, int64_t v_batch_stride, cudaStream_t stream);
 
+// sinkhorn.cu: `count` row-major n x n fp32 matrices -> doubly stochastic matrices, and the
+// vector-Jacobian product of that map.
+bool sinkhorn_supported(int n, int iters);
+void sinkhorn_forward(const float* in, float* out, int64_t count, int n, int iters,
+                      cudaStream_t stream);
+void sinkhorn_backward(const float* in, const float* grad_out, float* grad_in, int64_t count, int n,
+                       int iters, cudaStream_t stream);
+
 // attention_bwd_sm100.cu
 void attn_delta(const void* o, const void* d_o, float* delta, int B, int T, int H, int D,
                 int64_t do_tok_stride, int64_t do_batch_stride, cudaStream_t stream);
@@ -128,6 +136,12 @@ void peer_all_gather(const int64_t* weights, const int64_t* pads, int64_t region
 void peer_all_reduce(const int64_t* bufs, const int64_t* pads, void* out, int64_t n, bool bf16,
                      float scale, int rank, int world, uint32_t epoch, uint64_t limit_ns,
                      cudaStream_t stream);
+// Single-block, CUDA-graph-replayable all-reduce for small messages: the epoch is kept in the
+// device word `counter`; `bufs` hold two slots of `slot_elems` elements per rank.
+void peer_all_reduce_small(const int64_t* bufs, const int64_t* pads, uint32_t* counter,
+                           const void* in, void* out, int64_t n, int64_t slot_elems, bool bf16,
+                           float scale, int rank, int world, uint64_t limit_ns,
+                           cudaStream_t stream);
 
 // cross_entropy.cu
 void cross_entropy_rows(void* logits, const int64_t* targets, float* row_loss, float* row_lse,

@@ -366,6 +366,34 @@ std::vector<Tensor> flash_attn_bwd(const Tensor& dout_in, const Tensor& q_in, co
   return {dq, dk, dv};
 }
 
+// ---- Sinkhorn -----------------------------------------------------------------------------------
+Tensor sinkhorn_fwd(const Tensor& x, int64_t iters) {
+  check_f32(x, "log_alpha");
+  TORCH_CHECK(x.is_contiguous() && x.dim() >= 2 && x.size(-1) == x.size(-2));
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t n = x.size(-1);
+  Tensor out = torch::empty_like(x);
+  ob::sinkhorn_forward(x.data_ptr<float>(), out.data_ptr<float>(), x.numel() / (n * n), (int)n,
+                       (int)iters, current_stream());
+  return out;
+}
+
+Tensor sinkhorn_bwd(const Tensor& x, const Tensor& grad_out, int64_t iters) {
+  check_f32(x, "log_alpha");
+  check_f32(grad_out, "grad_out");
+  TORCH_CHECK(x.is_contiguous() && grad_out.is_contiguous() && x.sizes() == grad_out.sizes());
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t n = x.size(-1);
+  Tensor grad_in = torch::empty_like(x);
+  ob::sinkhorn_backward(x.data_ptr<float>(), grad_out.data_ptr<float>(), grad_in.data_ptr<float>(),
+                        x.numel() / (n * n), (int)n, (int)iters, current_stream());
+  return grad_in;
+}
+
+bool sinkhorn_supported(int64_t n, int64_t iters) {
+  return ob::sinkhorn_supported((int)n, (int)iters);
+}
+
 // ---- peer memory ---------------------------------------------------------------------------------
 // Allocates `bytes` of device memory outside the caching allocator and returns (tensor view as
 // uint8, IPC handle bytes). The memory lives until peer_free(tensor.data_ptr()).
@@ -913,6 +941,23 @@ void peer_all_reduce(const std::vector<int64_t>& bufs, const std::vector<int64_t
                       current_stream());
 }
 
+// In-place small all-reduce whose epoch lives in `counter` (a 1-element int32 CUDA tensor), so the
+// launch can be captured in a CUDA graph and replayed.
+void peer_all_reduce_small(const std::vector<int64_t>& bufs, const std::vector<int64_t>& pads,
+                           Tensor& counter, Tensor& tensor, int64_t slot_elems, double scale,
+                           int64_t rank, double limit_s) {
+  TORCH_CHECK(tensor.is_cuda() && tensor.is_contiguous() && bufs.size() == pads.size());
+  TORCH_CHECK(counter.is_cuda() && counter.scalar_type() == torch::kInt32 && counter.numel() == 1);
+  const bool bf16 = tensor.scalar_type() == torch::kBFloat16;
+  TORCH_CHECK(bf16 || tensor.scalar_type() == torch::kFloat32, "all-reduce supports bf16 and fp32");
+  const c10::cuda::CUDAGuard guard(tensor.device());
+  ob::peer_all_reduce_small(bufs.data(), pads.data(),
+                            reinterpret_cast<uint32_t*>(counter.data_ptr<int32_t>()),
+                            tensor.data_ptr(), tensor.data_ptr(), tensor.numel(), slot_elems, bf16,
+                            (float)scale, (int)rank, (int)bufs.size(), (uint64_t)(limit_s * 1e9),
+                            current_stream());
+}
+
 std::vector<int64_t> status(bool clear) {
   int out[4];
   ob::status_read(out, clear);
@@ -940,6 +985,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cross_entropy_rows", &cross_entropy_rows);
   m.def("scale_by_scalar", &scale_by_scalar);
   m.def("flash_attn_fwd", &flash_attn_fwd);
+  m.def("sinkhorn_fwd", &sinkhorn_fwd);
+  m.def("sinkhorn_bwd", &sinkhorn_bwd);
+  m.def("sinkhorn_supported", &sinkhorn_supported);
   m.def("flash_attn_bwd", &flash_attn_bwd);
   m.def("peer_alloc", &peer_alloc);
   m.def("peer_open", &peer_open);
@@ -949,6 +997,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("peer_reduce_scatter_mean", &peer_reduce_scatter_mean);
   m.def("peer_all_gather", &peer_all_gather);
   m.def("peer_all_reduce", &peer_all_reduce);
+  m.def("peer_all_reduce_small", &peer_all_reduce_small);
   m.def("gemv", &gemv);
   m.def("route_topk", &route_topk);
   m.def("moe_plan", &moe_plan);

@@ -166,39 +166,60 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
 // RoPE on interleaved pairs for q (B,T,H,D) and k (B,T,Hk,D) in one launch. cos/sin are (T, D/2)
 // fp32 rows for the positions being processed. `sign` = -1 rotates by -theta (the backward pass).
 // ------------------------------------------------------------------------------------------------
+// One warp per token. When D / 8 divides 32 (every head_dim that is a power of two up to 256) a
+// lane keeps the same position inside the head for every vector it touches, so it loads its
+// cos / sin values once per token (FIXED); other head sizes reload them per vector.
+template <bool FIXED>
 __global__ void rope_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                             __nv_bfloat16* __restrict__ qo, __nv_bfloat16* __restrict__ ko,
                             const float* __restrict__ cos_t, const float* __restrict__ sin_t, int B,
                             int T, int H, int Hk, int D, float sign, int64_t q_row_stride,
                             int64_t k_row_stride, int64_t qo_row_stride, int64_t ko_row_stride) {
   const int vec_per_head = D >> 3;
-  const int64_t q_vecs = (int64_t)B * T * H * vec_per_head;
-  const int64_t total = q_vecs + (int64_t)B * T * Hk * vec_per_head;
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const bool is_q = idx < q_vecs;
-    const int64_t local = is_q ? idx : idx - q_vecs;
-    const int heads = is_q ? H : Hk;
-    const int c = (int)(local % vec_per_head);
-    const int h = (int)((local / vec_per_head) % heads);
-    const int64_t bt = local / ((int64_t)vec_per_head * heads);
-    const int t = (int)(bt % T);
-    const __nv_bfloat16* src =
-        (is_q ? q + bt * q_row_stride : k + bt * k_row_stride) + (int64_t)h * D + c * 8;
-    __nv_bfloat16* dst =
-        (is_q ? qo + bt * qo_row_stride : ko + bt * ko_row_stride) + (int64_t)h * D + c * 8;
-    float f[8], o[8];
-    unpack8(*reinterpret_cast<const bf16x8*>(src), f);
-    const float4 cs = *reinterpret_cast<const float4*>(cos_t + (size_t)t * (D >> 1) + c * 4);
-    const float4 sn = *reinterpret_cast<const float4*>(sin_t + (size_t)t * (D >> 1) + c * 4);
-    const float cc[4] = {cs.x, cs.y, cs.z, cs.w};
-    const float ssn[4] = {sn.x * sign, sn.y * sign, sn.z * sign, sn.w * sign};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      o[2 * i] = f[2 * i] * cc[i] - f[2 * i + 1] * ssn[i];
-      o[2 * i + 1] = f[2 * i] * ssn[i] + f[2 * i + 1] * cc[i];
+  const int lane = threadIdx.x & 31;
+  const int q_vecs = H * vec_per_head;
+  const int all_vecs = q_vecs + Hk * vec_per_head;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int tokens = B * T;
+  for (int bt = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; bt < tokens; bt += warps) {
+    const int t = bt % T;
+    const float* cos_row = cos_t + (size_t)t * (D >> 1);
+    const float* sin_row = sin_t + (size_t)t * (D >> 1);
+    float cc[4], ssn[4];
+    int c = FIXED ? (lane & (vec_per_head - 1)) : 0;
+    if (FIXED) {
+      const float4 cs = *reinterpret_cast<const float4*>(cos_row + c * 4);
+      const float4 sn = *reinterpret_cast<const float4*>(sin_row + c * 4);
+      cc[0] = cs.x, cc[1] = cs.y, cc[2] = cs.z, cc[3] = cs.w;
+      ssn[0] = sn.x * sign, ssn[1] = sn.y * sign, ssn[2] = sn.z * sign, ssn[3] = sn.w * sign;
     }
-    *reinterpret_cast<bf16x8*>(dst) = pack8(o);
+    const __nv_bfloat16* q_src = q + bt * q_row_stride;
+    const __nv_bfloat16* k_src = k + bt * k_row_stride;
+    __nv_bfloat16* q_dst = qo + bt * qo_row_stride;
+    __nv_bfloat16* k_dst = ko + bt * ko_row_stride;
+    for (int v = lane; v < all_vecs; v += 32) {
+      const bool is_q = v < q_vecs;
+      const int local = is_q ? v : v - q_vecs;
+      const int head = local / vec_per_head;
+      if (!FIXED) {
+        c = local - head * vec_per_head;
+        const float4 cs = *reinterpret_cast<const float4*>(cos_row + c * 4);
+        const float4 sn = *reinterpret_cast<const float4*>(sin_row + c * 4);
+        cc[0] = cs.x, cc[1] = cs.y, cc[2] = cs.z, cc[3] = cs.w;
+        ssn[0] = sn.x * sign, ssn[1] = sn.y * sign, ssn[2] = sn.z * sign, ssn[3] = sn.w * sign;
+      }
+      const int off = head * D + c * 8;
+      const __nv_bfloat16* src = (is_q ? q_src : k_src) + off;
+      __nv_bfloat16* dst = (is_q ? q_dst : k_dst) + off;
+      float f[8], o[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(src), f);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        o[2 * i] = f[2 * i] * cc[i] - f[2 * i + 1] * ssn[i];
+        o[2 * i + 1] = f[2 * i] * ssn[i] + f[2 * i + 1] * cc[i];
+      }
+      *reinterpret_cast<bf16x8*>(dst) = pack8(o);
+    }
   }
 }
 
@@ -206,22 +227,35 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
 // SwiGLU: a = silu(g) * u and its backward. g/u/dg/du may be column slices of a wider matrix, so
 // each takes a row pitch.
 // ------------------------------------------------------------------------------------------------
+// A block walks over pairs of rows and its threads over the 8-element column groups: no index
+// division, and the loads of two rows are in flight before either is consumed.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ g,
                                   const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ a,
                                   int64_t rows, int h, int64_t g_pitch, int64_t u_pitch,
                                   int64_t a_pitch) {
   const int vecs = h >> 3;
-  const int64_t total = rows * vecs;
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = idx / vecs;
-    const int c = (int)(idx - r * vecs) * 8;
-    float gf[8], uf[8], o[8];
-    unpack8(*reinterpret_cast<const bf16x8*>(g + r * g_pitch + c), gf);
-    unpack8(*reinterpret_cast<const bf16x8*>(u + r * u_pitch + c), uf);
+  for (int64_t r = (int64_t)blockIdx.x * 2; r < rows; r += (int64_t)gridDim.x * 2) {
+    const bool two = r + 1 < rows;
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      const int c = v * 8;
+      bf16x8 g_raw[2], u_raw[2];
+      g_raw[0] = *reinterpret_cast<const bf16x8*>(g + r * g_pitch + c);
+      u_raw[0] = *reinterpret_cast<const bf16x8*>(u + r * u_pitch + c);
+      if (two) {
+        g_raw[1] = *reinterpret_cast<const bf16x8*>(g + (r + 1) * g_pitch + c);
+        u_raw[1] = *reinterpret_cast<const bf16x8*>(u + (r + 1) * u_pitch + c);
+      }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = gf[i] / (1.f + __expf(-gf[i])) * uf[i];
-    *reinterpret_cast<bf16x8*>(a + r * a_pitch + c) = pack8(o);
+      for (int j = 0; j < 2; ++j) {
+        if (j == 1 && !two) break;
+        float gf[8], uf[8], o[8];
+        unpack8(g_raw[j], gf);
+        unpack8(u_raw[j], uf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = gf[i] / (1.f + __expf(-gf[i])) * uf[i];
+        *reinterpret_cast<bf16x8*>(a + (r + j) * a_pitch + c) = pack8(o);
+      }
+    }
   }
 }
 
@@ -232,24 +266,37 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ da,
                                   int64_t rows, int h, int64_t da_pitch, int64_t g_pitch,
                                   int64_t u_pitch, int64_t dg_pitch, int64_t du_pitch) {
   const int vecs = h >> 3;
-  const int64_t total = rows * vecs;
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = idx / vecs;
-    const int c = (int)(idx - r * vecs) * 8;
-    float df[8], gf[8], uf[8], og[8], ou[8];
-    unpack8(*reinterpret_cast<const bf16x8*>(da + r * da_pitch + c), df);
-    unpack8(*reinterpret_cast<const bf16x8*>(g + r * g_pitch + c), gf);
-    unpack8(*reinterpret_cast<const bf16x8*>(u + r * u_pitch + c), uf);
+  for (int64_t r = (int64_t)blockIdx.x * 2; r < rows; r += (int64_t)gridDim.x * 2) {
+    const bool two = r + 1 < rows;
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      const int c = v * 8;
+      bf16x8 d_raw[2], g_raw[2], u_raw[2];
+      d_raw[0] = *reinterpret_cast<const bf16x8*>(da + r * da_pitch + c);
+      g_raw[0] = *reinterpret_cast<const bf16x8*>(g + r * g_pitch + c);
+      u_raw[0] = *reinterpret_cast<const bf16x8*>(u + r * u_pitch + c);
+      if (two) {
+        d_raw[1] = *reinterpret_cast<const bf16x8*>(da + (r + 1) * da_pitch + c);
+        g_raw[1] = *reinterpret_cast<const bf16x8*>(g + (r + 1) * g_pitch + c);
+        u_raw[1] = *reinterpret_cast<const bf16x8*>(u + (r + 1) * u_pitch + c);
+      }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float sig = 1.f / (1.f + __expf(-gf[i]));
-      const float silu = gf[i] * sig;
-      ou[i] = df[i] * silu;
-      og[i] = df[i] * uf[i] * (sig + silu * (1.f - sig));
+      for (int j = 0; j < 2; ++j) {
+        if (j == 1 && !two) break;
+        float df[8], gf[8], uf[8], og[8], ou[8];
+        unpack8(d_raw[j], df);
+        unpack8(g_raw[j], gf);
+        unpack8(u_raw[j], uf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float sig = 1.f / (1.f + __expf(-gf[i]));
+          const float silu = gf[i] * sig;
+          ou[i] = df[i] * silu;
+          og[i] = df[i] * uf[i] * (sig + silu * (1.f - sig));
+        }
+        *reinterpret_cast<bf16x8*>(dg + (r + j) * dg_pitch + c) = pack8(og);
+        *reinterpret_cast<bf16x8*>(du + (r + j) * du_pitch + c) = pack8(ou);
+      }
     }
-    *reinterpret_cast<bf16x8*>(dg + r * dg_pitch + c) = pack8(og);
-    *reinterpret_cast<bf16x8*>(du + r * du_pitch + c) = pack8(ou);
   }
 }
 
@@ -394,9 +441,13 @@ void rope_qk(const void* q, const void* k, void* qo, void* ko, const float* cos_
              int64_t q_row_stride, int64_t k_row_stride, int64_t qo_row_stride,
              int64_t ko_row_stride, cudaStream_t stream) {
   OB_CHECK(D % 8 == 0, "rope: head_dim must be a multiple of 8");
-  const int64_t total = (int64_t)B * T * (H + Hk) * (D / 8);
+  OB_CHECK((int64_t)B * T < (1ll << 31), "rope: too many tokens");
   const int threads = 256;
-  rope_kernel<<<grid_for(total, threads), threads, 0, stream>>>(
+  const int blocks = grid_for((int64_t)B * T * 32, threads);
+  const int vec_per_head = D / 8;
+  const bool fixed = vec_per_head <= 32 && (32 % vec_per_head) == 0;
+  auto kernel = fixed ? rope_kernel<true> : rope_kernel<false>;
+  kernel<<<blocks, threads, 0, stream>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (__nv_bfloat16*)qo, (__nv_bfloat16*)ko,
       cos_t, sin_t, B, T, H, Hk, D, inverse ? -1.f : 1.f, q_row_stride, k_row_stride,
       qo_row_stride, ko_row_stride);
@@ -407,7 +458,7 @@ void swiglu_fwd(const void* g, const void* u, void* a, int64_t rows, int h, int6
                 int64_t u_pitch, int64_t a_pitch, cudaStream_t stream) {
   OB_CHECK(h % 8 == 0, "swiglu: width must be a multiple of 8");
   const int threads = 256;
-  swiglu_fwd_kernel<<<grid_for(rows * (h / 8), threads), threads, 0, stream>>>(
+  swiglu_fwd_kernel<<<grid_for((rows + 1) / 2 * threads, threads), threads, 0, stream>>>(
       (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (__nv_bfloat16*)a, rows, h, g_pitch,
       u_pitch, a_pitch);
   OB_LAUNCH_CHECK();
@@ -418,7 +469,7 @@ void swiglu_bwd(const void* da, const void* g, const void* u, void* dg, void* du
                 int64_t du_pitch, cudaStream_t stream) {
   OB_CHECK(h % 8 == 0, "swiglu: width must be a multiple of 8");
   const int threads = 256;
-  swiglu_bwd_kernel<<<grid_for(rows * (h / 8), threads), threads, 0, stream>>>(
+  swiglu_bwd_kernel<<<grid_for((rows + 1) / 2 * threads, threads), threads, 0, stream>>>(
       (const __nv_bfloat16*)da, (const __nv_bfloat16*)g, (const __nv_bfloat16*)u,
       (__nv_bfloat16*)dg, (__nv_bfloat16*)du, rows, h, da_pitch, g_pitch, u_pitch, dg_pitch,
       du_pitch);

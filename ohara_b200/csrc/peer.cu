@@ -128,13 +128,45 @@ all_reduce_oneshot_kernel(PeerTable bufs, PeerTable pads, T* __restrict__ out, i
   if (!peer_barrier(pads, rank, world, epoch, limit_ns, status)) return;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (int64_t)gridDim.x * blockDim.x) {
+    // Same summation order on every rank: the result must be bit-identical across the group
+    // (replicated activations, clipping factors and sampled tokens depend on it).
     float acc = 0.f;
-    for (int r = 0; r < world; ++r) {
-      const int src = (rank + r) % world;
+    for (int src = 0; src < world; ++src)
       acc += static_cast<float>(static_cast<const T*>(bufs.ptr[src])[i]);
-    }
     out[i] = static_cast<T>(acc * scale);
   }
+}
+
+// Graph-replayable variant for messages of a few hundred KB at most (decode-time tensor
+// parallelism): one block copies the input into this rank's slot, signals, waits for the peers and
+// sums all slots. The epoch lives in device memory and advances by one per launch, so a CUDA graph
+// that contains the launch can be replayed; every rank must run the same number of launches. The
+// two slots alternate by epoch parity: a slot is rewritten two calls after it was read, and a rank
+// cannot be more than one call ahead of a peer (it waits for the peer's signal of the current
+// call), so the peer has finished reading by then.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+all_reduce_small_kernel(PeerTable bufs, PeerTable pads, uint32_t* __restrict__ counter,
+                        const T* __restrict__ in, T* __restrict__ out, int n, int64_t slot_elems,
+                        int rank, int world, float scale, uint64_t limit_ns, int* status) {
+  __shared__ uint32_t epoch_s;
+  if (threadIdx.x == 0) epoch_s = *counter + 1;
+  __syncthreads();
+  const uint32_t epoch = epoch_s;
+  const int64_t base = (int64_t)(epoch & 1) * slot_elems;
+  T* mine = static_cast<T*>(bufs.ptr[rank]) + base;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) mine[i] = in[i];
+  __threadfence_system();
+  if (peer_barrier(pads, rank, world, epoch, limit_ns, status)) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float acc = 0.f;  // fixed order: bit-identical on every rank
+      for (int src = 0; src < world; ++src)
+        acc += static_cast<float>((static_cast<const T*>(bufs.ptr[src]) + base)[i]);
+      out[i] = static_cast<T>(acc * scale);
+    }
+  }
+  // Advance even after a timed-out wait so that the ranks stay in step once the cause is gone.
+  if (threadIdx.x == 0) *counter = epoch;
 }
 
 }  // namespace
@@ -210,6 +242,24 @@ void peer_all_reduce(const int64_t* bufs, const int64_t* pads, void* out, int64_
     all_reduce_oneshot_kernel<float><<<blocks, 512, 0, stream>>>(
         make_table(bufs, world), make_table(pads, world), static_cast<float*>(out), n, rank, world,
         scale, epoch, limit_ns, status_ptr());
+  OB_LAUNCH_CHECK();
+}
+
+void peer_all_reduce_small(const int64_t* bufs, const int64_t* pads, uint32_t* counter,
+                           const void* in, void* out, int64_t n, int64_t slot_elems, bool bf16,
+                           float scale, int rank, int world, uint64_t limit_ns,
+                           cudaStream_t stream) {
+  if (n == 0) return;
+  OB_CHECK(n <= slot_elems && n < (1ll << 30), "peer_all_reduce_small: message exceeds the slot");
+  if (bf16)
+    all_reduce_small_kernel<__nv_bfloat16><<<1, 1024, 0, stream>>>(
+        make_table(bufs, world), make_table(pads, world), counter,
+        static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), (int)n,
+        slot_elems, rank, world, scale, limit_ns, status_ptr());
+  else
+    all_reduce_small_kernel<float><<<1, 1024, 0, stream>>>(
+        make_table(bufs, world), make_table(pads, world), counter, static_cast<const float*>(in),
+        static_cast<float*>(out), (int)n, slot_elems, rank, world, scale, limit_ns, status_ptr());
   OB_LAUNCH_CHECK();
 }
 

@@ -106,6 +106,12 @@ def validate_config(cfg: Config) -> None:
         raise ValueError("moe_normalize_weights only applies to grouped MoE")
 
 
+def _plain_linears(*modules: nn.Module) -> bool:
+    """True when every module is an unmodified bias-free ``Linear`` (not a sharded or adapted
+    replacement), so that their weights can be handed to a fused op directly."""
+    return all(type(m) is Linear and m.bias is None for m in modules)
+
+
 class Attention(nn.Module):
     def __init__(self, cfg: Config):
         super().__init__()
@@ -134,9 +140,13 @@ class Attention(nn.Module):
         kv_heads = self.key.weight.shape[0] // self.head_dim
         # -1: with sequence-parallel tensor parallelism the projections gather the token blocks of
         # every rank, so they return more sequences than came in.
-        q = self.query(x).view(-1, seq_len, heads, self.head_dim)
-        k = self.key(x).view(-1, seq_len, kv_heads, self.head_dim)
-        v = self.value(x).view(-1, seq_len, kv_heads, self.head_dim)
+        if _plain_linears(self.query, self.key, self.value):
+            q, k, v = ops.linear_fanout(x, (self.query.weight, self.key.weight, self.value.weight))
+        else:  # biases, or tensor-parallel replacements of the projections
+            q, k, v = self.query(x), self.key(x), self.value(x)
+        q = q.view(-1, seq_len, heads, self.head_dim)
+        k = k.view(-1, seq_len, kv_heads, self.head_dim)
+        v = v.view(-1, seq_len, kv_heads, self.head_dim)
         if (kv_cache is not None and seq_len == 1 and len(freqs_cis) == 4
                 and decode_ops.fused_decode_supported(q, kv_cache) and v.dtype == q.dtype):
             # Decode step: RoPE + cache append in one kernel, then attention over the cache in
@@ -354,7 +364,9 @@ class Llama(nn.Module):
         if batch_size < 1:
             raise ValueError("batch_size must be at least 1")
         cfg = self.config
-        shape = (batch_size, cfg.max_sequence_length, cfg.kv_heads, cfg.head_dim)
+        # Local KV heads: a tensor-parallel shard of the model caches only its own heads.
+        kv_heads = self.layers[0].attn.key.weight.shape[0] // cfg.head_dim
+        shape = (batch_size, cfg.max_sequence_length, kv_heads, cfg.head_dim)
         weight = self.token_emb.weight
         dtype = weight.dtype
         if weight.is_cuda and dtype == torch.float32 and torch.is_autocast_enabled("cuda"):

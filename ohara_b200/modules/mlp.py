@@ -102,7 +102,12 @@ class SwiGLU(_FeedForward):
         self.dropout = _dropout(dropout)
 
     def forward(self, x: Tensor) -> Tensor:
-        return self.dropout(self.down(ops.swiglu(self.gate(x), self.up(x))))
+        if type(self.gate) is Linear and type(self.up) is Linear and self.gate.bias is None \
+                and self.up.bias is None:
+            gate, up = ops.linear_fanout(x, (self.gate.weight, self.up.weight))
+        else:  # biases, adapters or tensor-parallel replacements
+            gate, up = self.gate(x), self.up(x)
+        return self.dropout(self.down(ops.swiglu(gate, up)))
 
     def reset_parameters(self, init_std=None, factor: float = 1.0) -> None:
         self._init_in_out([self.up, self.gate], self.down, init_std, factor)

@@ -30,6 +30,7 @@ __all__ = [
     "fast_path",
     "linear",
     "linear_cross_entropy",
+    "linear_fanout",
     "matmul_nn",
     "matmul_nt",
     "matmul_tn",
@@ -227,6 +228,65 @@ class _LinearFn(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0)
         return dx, dw, db
+
+
+class _FanoutLinearFn(torch.autograd.Function):
+    """Several bias-free linears of one input. The backward pass chains the input-gradient GEMMs
+    through the GEMM's residual epilogue (``dx = dy_i @ W_i + dx``) instead of leaving autograd to
+    add one full-size gradient per branch with separate element-wise kernels."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, *weights: Tensor):
+        x16 = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        x2 = _gemm_ready(_as_2d(x16))
+        outs = tuple(matmul_nt(x2, bf16_weight(w)).view(*x.shape[:-1], w.shape[0]) for w in weights)
+        ctx.save_for_backward(x2, *weights)
+        ctx.x_shape = x.shape
+        ctx.x_dtype = x.dtype
+        return outs
+
+    @staticmethod
+    def backward(ctx, *dys: Tensor):
+        x2, *weights = ctx.saved_tensors
+        ready = [None if dy is None else _gemm_ready(_as_2d(
+            dy if dy.dtype == torch.bfloat16 else dy.to(torch.bfloat16))) for dy in dys]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            for dy2, weight in zip(ready, weights):
+                if dy2 is None:
+                    continue
+                w16 = _gemm_ready(bf16_weight(weight))
+                m, k = dy2.shape
+                n = w16.shape[-1]
+                if dx is None:
+                    dx = torch.empty((m, n), device=dy2.device, dtype=torch.bfloat16)
+                    ext().gemm(dy2, w16, dx, m, n, k, False, True, 1, False, 1.0, None, None)
+                else:  # in place: every element is read by the thread that then overwrites it
+                    ext().gemm(dy2, w16, dx, m, n, k, False, True, 1, False, 1.0, None, None,
+                               dx, 1.0)
+            if dx is not None:
+                dx = dx.view(ctx.x_shape)
+                if dx.dtype != ctx.x_dtype:
+                    dx = dx.to(ctx.x_dtype)
+        dws = []
+        for i, (dy2, weight) in enumerate(zip(ready, weights)):
+            dw = None
+            if dy2 is not None and ctx.needs_input_grad[1 + i]:
+                dw = matmul_tn(dy2, x2)
+                if dw.dtype != weight.dtype:
+                    dw = dw.to(weight.dtype)
+            dws.append(dw)
+        return (dx, *dws)
+
+
+def linear_fanout(x: Tensor, weights) -> tuple[Tensor, ...]:
+    """``tuple(x @ w.T for w in weights)``: the projections that share an input (query / key /
+    value; gate / up), with a fused input-gradient accumulation on the bf16 fast path."""
+    weights = tuple(weights)
+    if (fast_path(x) and x.shape[-1] % 8 == 0 and all(w.shape[0] % 8 == 0 for w in weights)
+            and len(weights) > 1):
+        return _FanoutLinearFn.apply(x, *weights)
+    return tuple(linear(x, w) for w in weights)
 
 
 def linear(x: Tensor, weight: Tensor, bias: Tensor | None = None) -> Tensor:

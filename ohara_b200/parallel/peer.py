@@ -52,6 +52,9 @@ class PeerRuntime:
     group. Every rank must issue the same sequence of collectives."""
 
     ONE_SHOT_BYTES = 1 << 20
+    # Up to this size the all-reduce is a single-block kernel whose epoch lives on the device: it
+    # can be captured in a CUDA graph and replayed (decode-time tensor parallelism).
+    SMALL_BYTES = 256 << 10
 
     def __init__(self, group=None, wait_limit_s: float = 10.0) -> None:
         self.group = group
@@ -61,6 +64,7 @@ class PeerRuntime:
         self.pads = SymmetricBuffer(4096, group)
         self.epoch = 0
         self._reduce_buffers = None
+        self._small = None
         # Everyone has opened everyone's pad before the first kernel may signal.
         dist.barrier(group=group)
 
@@ -77,6 +81,9 @@ class PeerRuntime:
         itself (a single NVLink round trip). Falls back to the c10d collective for tensors larger
         than ``ONE_SHOT_BYTES``, where a bandwidth-optimal algorithm wins."""
         nbytes = tensor.numel() * tensor.element_size()
+        if (nbytes <= self.SMALL_BYTES and tensor.is_contiguous()
+                and tensor.dtype in (torch.bfloat16, torch.float32)):
+            return self._all_reduce_small(tensor, average)
         if (nbytes > self.ONE_SHOT_BYTES or not tensor.is_contiguous()
                 or tensor.dtype not in (torch.bfloat16, torch.float32)):
             dist.all_reduce(tensor, group=self.group)
@@ -95,6 +102,27 @@ class PeerRuntime:
         ext().peer_all_reduce(buffer.pointers, self.pads.pointers, tensor,
                               1.0 / self.world if average else 1.0, self.rank, self.next_epoch(),
                               self.wait_limit_s)
+        return tensor
+
+
+    def _all_reduce_small(self, tensor: torch.Tensor, average: bool) -> torch.Tensor:
+        if self._small is None:
+            # Set-up is collective; it happens at the first small all-reduce, which every rank
+            # reaches at the same point of the program (never inside a graph capture: warm up
+            # one step first).
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("run one eager step before capturing a graph that all-reduces")
+            buffers = SymmetricBuffer(2 * self.SMALL_BYTES, self.group)
+            pads = SymmetricBuffer(4096, self.group)
+            counter = torch.zeros(1, dtype=torch.int32, device=buffers.device)
+            self._small = (buffers, pads, counter)
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+        buffers, pads, counter = self._small
+        slot_elems = self.SMALL_BYTES // tensor.element_size()
+        ext().peer_all_reduce_small(buffers.pointers, pads.pointers, counter, tensor, slot_elems,
+                                    1.0 / self.world if average else 1.0, self.rank,
+                                    self.wait_limit_s)
         return tensor
 
 

@@ -33,6 +33,7 @@ from .enums import Backend, PrecisionMode, ReduceType, StrategyType
 from .strategy import BaseStrategy, DDPStrategy, FSDPStrategy, SingleStrategy
 from .tensor_parallel import (
     attach_fused_workspace,
+    attach_peer_runtime,
     TensorParallelPlan,
     apply_tensor_parallel,
     gather_tensor_parallel_state,
@@ -392,6 +393,13 @@ class OharaEngine:
             attach_fused_workspace(module, LazyTPWorkspace(self._groups.get("tp"), width))
             self._tp_batch_sharding = True
             self._tp_grads_synced = True
+        elif (self.config.fused_collectives and self._device.type == "cuda"
+              and self.topology.tp <= 16 and dist.get_backend() == Backend.NCCL.value):
+            # Plain tensor parallelism: the all-reduce that ends a row-parallel layer runs as a
+            # one-shot peer-memory kernel when the message is small (decode steps).
+            from ohara_b200.parallel.peer import PeerRuntime
+
+            attach_peer_runtime(module, PeerRuntime(self._groups.get("tp")))
         return module
 
     def local_batch(self, batch: Any) -> Any:

@@ -88,14 +88,18 @@ class _ReduceFromGroup(torch.autograd.Function):
     """All-reduce(sum) forward, identity backward: exit of a row-parallel region."""
 
     @staticmethod
-    def forward(ctx, x: Tensor, group):
+    def forward(ctx, x: Tensor, group, runtime=None):
         x = x.contiguous()
+        if runtime is not None and x.is_cuda:
+            # Small messages (decode steps) go through the peer-memory one-shot kernel, larger
+            # ones fall through to the c10d collective inside it.
+            return runtime.all_reduce_(x)
         dist.all_reduce(x, group=group)
         return x
 
     @staticmethod
     def backward(ctx, grad: Tensor):
-        return grad, None
+        return grad, None, None
 
 
 class _GatherSequence(torch.autograd.Function):
@@ -163,6 +167,9 @@ class _ParallelLinear(nn.Module):
         self.bias = None
         # Set by ``attach_fused_workspace``: symmetric NVLink buffers shared by the layers of a group.
         self.workspace = None
+        # Set by ``attach_peer_runtime``: row-parallel outputs small enough for the one-shot
+        # peer-memory all-reduce (decode steps) then skip the c10d collective.
+        self.peer_runtime = None
 
     def _use_fused(self, x: Tensor, rows_local: int) -> bool:
         """Fused collective path: CUDA bf16 fast path, no bias, 128-row aligned token blocks."""
@@ -238,7 +245,7 @@ class RowParallelLinear(_ParallelLinear):
         if self.sequence_parallel:
             y = _ScatterSequence.apply(y, self.group)
         else:
-            y = _ReduceFromGroup.apply(y, self.group)
+            y = _ReduceFromGroup.apply(y, self.group, self.peer_runtime)
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)
         return y
@@ -282,6 +289,17 @@ def attach_fused_workspace(module: nn.Module, workspace) -> int:
     for child in module.modules():
         if isinstance(child, _ParallelLinear):
             child.workspace = workspace
+            attached += 1
+    return attached
+
+
+def attach_peer_runtime(module: nn.Module, runtime) -> int:
+    """Give every row-parallel linear of ``module`` the group's ``PeerRuntime``; returns the number
+    of layers attached."""
+    attached = 0
+    for child in module.modules():
+        if isinstance(child, RowParallelLinear):
+            child.peer_runtime = runtime
             attached += 1
     return attached
 
