@@ -102,6 +102,22 @@ void flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float*
                     int64_t k_tok_stride, int64_t v_tok_stride, int64_t q_batch_stride,
                     int64_t k_batch_stride, int64_t v_batch_stride, cudaStream_t stream);
 
+// muon.cu: stages of the Muon step around the Newton-Schulz GEMMs. Matrices of a group are reached
+// through a pointer table; entry k covers `per_pointer` consecutive matrices (1 for separate
+// parameters, B for one pre-stacked expert tensor).
+constexpr int kMuonMaxPointers = 128;
+struct MuonTable {
+  void* ptr[kMuonMaxPointers];
+};
+void muon_momentum(const MuonTable& grads, float* momentum, void* u, float* norm2, int batch,
+                   int64_t numel, float mu, int per_pointer, cudaStream_t stream);
+void muon_scale(void* x, const float* norm2, int batch, int64_t numel, cudaStream_t stream);
+void muon_variance(const void* x, float* v, int batch, int rows, int cols, bool by_row,
+                   cudaStream_t stream);
+void muon_apply(const MuonTable& params, const MuonTable* shadows, const void* x, const float* factor,
+                int batch, int rows, int cols, float lr, float wd, bool by_row, int per_pointer,
+                cudaStream_t stream);
+
 // sinkhorn.cu: `count` row-major n x n fp32 matrices -> doubly stochastic matrices, and the
 // vector-Jacobian product of that map.
 bool sinkhorn_supported(int n, int iters);

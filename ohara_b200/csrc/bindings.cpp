@@ -366,6 +366,76 @@ std::vector<Tensor> flash_attn_bwd(const Tensor& dout_in, const Tensor& q_in, co
   return {dq, dk, dv};
 }
 
+// ---- Muon stages --------------------------------------------------------------------------------
+ob::MuonTable muon_table(const std::vector<Tensor>& tensors, bool bf16) {
+  TORCH_CHECK(!tensors.empty() && tensors.size() <= (size_t)ob::kMuonMaxPointers,
+              "a Muon group takes 1..", ob::kMuonMaxPointers, " tensors here");
+  ob::MuonTable table = {};
+  for (size_t i = 0; i < tensors.size(); ++i) {
+    const Tensor& t = tensors[i];
+    TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.sizes() == tensors[0].sizes());
+    TORCH_CHECK(t.scalar_type() == (bf16 ? torch::kBFloat16 : torch::kFloat32));
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, "Muon tensors must be 16-byte aligned");
+    table.ptr[i] = t.data_ptr();
+  }
+  return table;
+}
+
+// momentum (B, r, c) fp32 updated in place; returns nothing: `u` (B, r, c) bf16 receives the
+// normalised Nesterov direction, ready for the Newton-Schulz iteration.
+void muon_prepare(const std::vector<Tensor>& grads, Tensor& momentum, Tensor& u, Tensor& norm2,
+                  double mu) {
+  check_f32(momentum, "momentum");
+  check_bf16(u, "u");
+  check_f32(norm2, "norm2");
+  TORCH_CHECK(momentum.is_contiguous() && u.is_contiguous() && momentum.dim() == 3 &&
+              u.sizes() == momentum.sizes());
+  const c10::cuda::CUDAGuard guard(momentum.device());
+  const int64_t batch = momentum.size(0), numel = momentum.size(1) * momentum.size(2);
+  const int per_pointer = (int)(batch / (int64_t)grads.size());
+  TORCH_CHECK((int64_t)grads.size() * per_pointer == batch && grads[0].numel() == per_pointer * numel);
+  TORCH_CHECK(norm2.numel() == batch);
+  const ob::MuonTable table = muon_table(grads, false);
+  ob::muon_momentum(table, momentum.data_ptr<float>(), u.data_ptr(), norm2.data_ptr<float>(),
+                    (int)batch, numel, (float)mu, per_pointer, current_stream());
+  ob::muon_scale(u.data_ptr(), norm2.data_ptr<float>(), (int)batch, numel, current_stream());
+}
+
+Tensor muon_variance(const Tensor& x, bool by_row) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.is_contiguous() && x.dim() == 3);
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t batch = x.size(0), rows = x.size(1), cols = x.size(2);
+  Tensor v = torch::empty({batch, by_row ? rows : 1, by_row ? 1 : cols},
+                          x.options().dtype(torch::kFloat32));
+  ob::muon_variance(x.data_ptr(), v.data_ptr<float>(), (int)batch, (int)rows, (int)cols, by_row,
+                    current_stream());
+  return v;
+}
+
+void muon_apply(const std::vector<Tensor>& params, const std::vector<Tensor>& shadows,
+                const Tensor& x, const Tensor& factor, double lr, double wd, bool by_row) {
+  check_bf16(x, "x");
+  check_f32(factor, "factor");
+  TORCH_CHECK(x.is_contiguous() && x.dim() == 3 && factor.is_contiguous());
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t batch = x.size(0), rows = x.size(1), cols = x.size(2);
+  const int per_pointer = (int)(batch / (int64_t)params.size());
+  TORCH_CHECK((int64_t)params.size() * per_pointer == batch &&
+              params[0].numel() == per_pointer * rows * cols);
+  TORCH_CHECK(factor.numel() == batch * (by_row ? rows : cols));
+  const ob::MuonTable ptable = muon_table(params, false);
+  ob::MuonTable stable = {};
+  const bool has_shadow = !shadows.empty();
+  if (has_shadow) {
+    TORCH_CHECK(shadows.size() == params.size());
+    stable = muon_table(shadows, true);
+  }
+  ob::muon_apply(ptable, has_shadow ? &stable : nullptr, x.data_ptr(), factor.data_ptr<float>(),
+                 (int)batch, (int)rows, (int)cols, (float)lr, (float)wd, by_row, per_pointer,
+                 current_stream());
+}
+
 // ---- Sinkhorn -----------------------------------------------------------------------------------
 Tensor sinkhorn_fwd(const Tensor& x, int64_t iters) {
   check_f32(x, "log_alpha");
@@ -985,6 +1055,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cross_entropy_rows", &cross_entropy_rows);
   m.def("scale_by_scalar", &scale_by_scalar);
   m.def("flash_attn_fwd", &flash_attn_fwd);
+  m.def("muon_prepare", &muon_prepare);
+  m.def("muon_variance", &muon_variance);
+  m.def("muon_apply", &muon_apply);
   m.def("sinkhorn_fwd", &sinkhorn_fwd);
   m.def("sinkhorn_bwd", &sinkhorn_bwd);
   m.def("sinkhorn_supported", &sinkhorn_supported);

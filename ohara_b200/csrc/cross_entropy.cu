@@ -4,7 +4,10 @@
 // logits never exist and no fp32 copy is made.
 //
 // One CTA per row; the row is staged in shared memory so global memory is read once and written
-// once. Rows whose target equals `ignore_index` get zero loss and zero gradient.
+// once. Rows whose target equals `ignore_index` get zero loss and zero gradient. Each logit is
+// exponentiated once: the second pass replaces the staged logits by e = exp(x - max) (bf16) while
+// it sums them in fp32, the third scales e by 1 / sum (the exponential unit, not memory, bounds
+// this kernel at a 50k vocabulary).
 #include "common.cuh"
 #include "host_utils.h"
 
@@ -67,8 +70,10 @@ __global__ void ce_rows_kernel(__nv_bfloat16* __restrict__ logits, const int64_t
     return;
   }
 
+  __shared__ float target_logit;
   float vmax = -INFINITY;
   int arg = 0;
+  const int tgt = valid ? (int)target : -1;
   for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
     const bf16x8 x = reinterpret_cast<const bf16x8*>(src)[v];
     reinterpret_cast<bf16x8*>(row_s)[v] = x;
@@ -77,6 +82,8 @@ __global__ void ce_rows_kernel(__nv_bfloat16* __restrict__ logits, const int64_t
       const float2 f = __bfloat1622float2(x.v[i]);
       if (f.x > vmax) { vmax = f.x; arg = 8 * v + 2 * i; }
       if (f.y > vmax) { vmax = f.y; arg = 8 * v + 2 * i + 1; }
+      if (8 * v + 2 * i == tgt) target_logit = f.x;
+      if (8 * v + 2 * i + 1 == tgt) target_logit = f.y;
     }
   }
   for (int i = (vecs << 3) + threadIdx.x; i < vocab; i += blockDim.x) {
@@ -84,6 +91,7 @@ __global__ void ce_rows_kernel(__nv_bfloat16* __restrict__ logits, const int64_t
     row_s[i] = x;
     const float f = __bfloat162float(x);
     if (f > vmax) { vmax = f; arg = i; }
+    if (i == tgt) target_logit = f;
   }
   const float row_max = block_reduce(vmax, scratch, true);
   if (row_correct) {
@@ -96,35 +104,51 @@ __global__ void ce_rows_kernel(__nv_bfloat16* __restrict__ logits, const int64_t
     if (threadIdx.x == 0) row_correct[row] = (valid && best == (int)target) ? 1 : 0;
   }
   __syncthreads();
+  // e = exp(x - max), summed in fp32 and written back over the staged logits as bf16.
   float sum = 0.f;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x)
-    sum += __expf(__bfloat162float(row_s[i]) - row_max);
+  for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+    bf16x8 x = reinterpret_cast<const bf16x8*>(row_s)[v];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(x.v[i]);
+      const float a = __expf(f.x - row_max), b = __expf(f.y - row_max);
+      sum += a + b;
+      x.v[i] = __floats2bfloat162_rn(a, b);
+    }
+    reinterpret_cast<bf16x8*>(row_s)[v] = x;
+  }
+  for (int i = (vecs << 3) + threadIdx.x; i < vocab; i += blockDim.x) {
+    const float a = __expf(__bfloat162float(row_s[i]) - row_max);
+    sum += a;
+    row_s[i] = __float2bfloat16_rn(a);
+  }
   const float total = block_reduce(sum, scratch, false);
   const float lse = row_max + logf(total);
   if (threadIdx.x == 0) {
-    row_loss[row] = valid ? (lse - __bfloat162float(row_s[valid ? target : 0])) : 0.f;
+    row_loss[row] = valid ? (lse - target_logit) : 0.f;
     if (row_lse) row_lse[row] = lse;
   }
   if (write_grad) {
     const float scale = valid ? (scale_ptr ? *scale_ptr : 1.f) : 0.f;
+    const float inv = scale / total;  // softmax = e / total
     for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
       const bf16x8 x = reinterpret_cast<const bf16x8*>(row_s)[v];
       bf16x8 o;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 f = __bfloat1622float2(x.v[i]);
-        float a = __expf(f.x - lse), b = __expf(f.y - lse);
+        float a = f.x * inv, b = f.y * inv;
         const int c = 8 * v + 2 * i;
-        if (c == target) a -= 1.f;
-        if (c + 1 == target) b -= 1.f;
-        o.v[i] = __floats2bfloat162_rn(a * scale, b * scale);
+        if (c == tgt) a -= scale;
+        if (c + 1 == tgt) b -= scale;
+        o.v[i] = __floats2bfloat162_rn(a, b);
       }
       reinterpret_cast<bf16x8*>(src)[v] = o;
     }
     for (int i = (vecs << 3) + threadIdx.x; i < vocab; i += blockDim.x) {
-      float a = __expf(__bfloat162float(row_s[i]) - lse);
-      if (i == target) a -= 1.f;
-      src[i] = __float2bfloat16_rn(a * scale);
+      float a = __bfloat162float(row_s[i]) * inv;
+      if (i == tgt) a -= scale;
+      src[i] = __float2bfloat16_rn(a);
     }
   }
 }

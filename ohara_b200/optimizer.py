@@ -39,6 +39,51 @@ class FusedAdamW(optim.AdamW):
     """``torch.optim.AdamW`` whose step runs the fused sm_100a kernel for fp32 CUDA parameters
     (identical update rule; other tensors fall back to the stock implementation)."""
 
+    @staticmethod
+    def _muon_step_fused(group: dict[str, Any], state: dict[str, Any], params: list[Tensor],
+                         batch: int, rows: int, cols: int) -> None:
+        """The same step on the kernels of ``csrc/muon.cu``: gradients and parameters are read
+        and written in place through pointer tables (no stacking, no copy back), the element-wise
+        work is three passes instead of about twenty."""
+        from ohara_b200.ops import refresh_bf16_weight
+        from ohara_b200.ops._ext import ext
+
+        C = ext()
+        device = params[0].device
+        momentum = float(group["momentum"])
+        u = torch.empty(batch, rows, cols, device=device, dtype=torch.bfloat16)
+        norm2 = torch.empty(batch, device=device, dtype=torch.float32)
+        C.muon_prepare([p.grad for p in params], state["momentum_buffer"], u, norm2, momentum)
+        update = _polar_express_kernels(u, int(group["ns_steps"]))
+        by_row = rows >= cols
+        variance = C.muon_variance(update, by_row)  # (B, r, 1) or (B, 1, c), fp32
+        size = cols if by_row else rows
+        second = state["second_momentum_buffer"]
+        norm_before = (variance.sum(dim=(-2, -1), keepdim=True) * size).sqrt()
+        second.lerp_(variance, 1.0 - float(group["beta2"]))
+        inv_rms = second.clamp_min(1e-10).rsqrt()
+        norm_after = ((variance * size) * inv_rms.square()).sum(dim=(-2, -1), keepdim=True).sqrt()
+        factor = (inv_rms * (norm_before / norm_after.clamp_min(1e-10))).to(torch.bfloat16).float()
+        lr = float(group["lr"]) * math.sqrt(max(1.0, rows / cols))
+        shadows = []
+        for p in params:
+            cached = getattr(p, "_ohara_bf16", None)
+            if cached is None or cached[1].shape != p.shape or cached[1].device != p.device \
+                    or not cached[1].is_contiguous():
+                shadows = []
+                break
+            shadows.append(cached[1])
+        C.muon_apply([p.detach() for p in params], shadows, update, factor.contiguous(), lr,
+                     float(group["weight_decay"]), by_row)
+        if shadows:
+            for p, shadow in zip(params, shadows):
+                refresh_bf16_weight(p, shadow)
+        else:
+            # The kernel wrote through raw pointers (no version bump): drop any compute copy.
+            for p in params:
+                if getattr(p, "_ohara_bf16", None) is not None:
+                    p._ohara_bf16 = None
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = None
@@ -166,6 +211,20 @@ def _hypersphere_update_stacked_(stacked: Tensor, updates: Tensor, learning_rate
 # --------------------------------------------------------------------------------------------------
 # Newton-Schulz (Polar Express)
 # --------------------------------------------------------------------------------------------------
+def _fused_muon_ok(params: list[Tensor], rows: int, cols: int) -> bool:
+    """Fused Muon stages: fp32 CUDA parameters and gradients, contiguous and 16-byte aligned,
+    tile-friendly sizes, at most 128 tensors in the group."""
+    if not params or len(params) > 128 or rows % 8 or cols % 8:
+        return False
+    for p in params:
+        g = p.grad
+        if not (p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and g is not None
+                and g.dtype == torch.float32 and g.is_contiguous() and g.shape == p.shape
+                and p.data_ptr() % 16 == 0 and g.data_ptr() % 16 == 0):
+            return False
+    return True
+
+
 def _polar_express_kernels(x: Tensor, steps: int) -> Tensor:
     """bf16 iteration on the tcgen05 GEMM. ``x`` is a contiguous (B, r, c) bf16 stack, already
     normalised. Gram on the short side; the symmetric products need no explicit transposes."""
@@ -353,6 +412,9 @@ class MuonAdamW(optim.Optimizer):
             shape = (batch, rows, 1) if reduce_dim == -1 else (batch, 1, cols)
             state["second_momentum_buffer"] = torch.zeros(shape, dtype=first.dtype,
                                                           device=first.device)
+        if not hyperspherical and _fused_muon_ok(params, rows, cols):
+            self._muon_step_fused(group, state, params, batch, rows, cols)
+            return
         if pre_stacked:
             grads = first.grad
             stacked = first.detach()

@@ -278,3 +278,53 @@ def test_add_rms_norm_fused_residual():
     assert rel_err(x.grad, xr.grad) < 2e-2
     assert torch.equal(x.grad, delta.grad)
     assert rel_err(w.grad, wr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("shape,count", [((256, 256), 5), ((512, 256), 3), ((256, 768), 2)])
+def test_fused_muon_stages_match_the_generic_step(monkeypatch, shape, count):
+    """Same gradients through the pointer-table kernels and through the stacked ATen expression:
+    parameters, momentum and second-moment buffers must agree after two steps."""
+    import ohara_b200.optimizer as opt_module
+    from ohara_b200.optimizer import MuonAdamW
+
+    torch.manual_seed(0)
+    base = [torch.randn(*shape, device="cuda") * 0.05 for _ in range(count)]
+    grads = [[torch.randn(*shape, device="cuda") for _ in range(count)] for _ in range(2)]
+
+    def run(fused: bool):
+        if not fused:
+            monkeypatch.setattr(opt_module, "_fused_muon_ok", lambda *a, **k: False)
+        params = [torch.nn.Parameter(b.clone()) for b in base]
+        opt = MuonAdamW([dict(params=params, kind="muon", lr=0.02, weight_decay=0.1, momentum=0.95,
+                              beta2=0.9, ns_steps=5, eps=1e-10)])
+        for step_grads in grads:
+            for p, g in zip(params, step_grads):
+                p.grad = g.clone()
+            opt.step()
+        monkeypatch.undo()
+        state = opt.state[params[0]]
+        return params, state["momentum_buffer"], state["second_momentum_buffer"]
+
+    fused_p, fused_m, fused_s = run(True)
+    ref_p, ref_m, ref_s = run(False)
+    assert torch.allclose(fused_m, ref_m, atol=1e-6)
+    assert rel_err(fused_s, ref_s) < 2e-2
+    for a, b, start in zip(fused_p, ref_p, base):
+        assert rel_err(a.detach() - start, b.detach() - start) < 3e-2
+
+
+def test_fused_muon_refreshes_the_bf16_compute_copy():
+    from ohara_b200 import ops
+    from ohara_b200.optimizer import MuonAdamW
+
+    torch.manual_seed(0)
+    params = [torch.nn.Parameter(torch.randn(256, 256, device="cuda") * 0.05) for _ in range(2)]
+    before = [ops.bf16_weight(p).clone() for p in params]
+    opt = MuonAdamW([dict(params=params, kind="muon", lr=0.05, weight_decay=0.0, momentum=0.95,
+                          beta2=0.9, ns_steps=5, eps=1e-10)])
+    for p in params:
+        p.grad = torch.randn_like(p)
+    opt.step()
+    for p, old in zip(params, before):
+        fresh = ops.bf16_weight(p)
+        assert torch.equal(fresh, p.detach().to(torch.bfloat16)) and not torch.equal(fresh, old)
