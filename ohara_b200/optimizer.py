@@ -39,51 +39,6 @@ class FusedAdamW(optim.AdamW):
     """``torch.optim.AdamW`` whose step runs the fused sm_100a kernel for fp32 CUDA parameters
     (identical update rule; other tensors fall back to the stock implementation)."""
 
-    @staticmethod
-    def _muon_step_fused(group: dict[str, Any], state: dict[str, Any], params: list[Tensor],
-                         batch: int, rows: int, cols: int) -> None:
-        """The same step on the kernels of ``csrc/muon.cu``: gradients and parameters are read
-        and written in place through pointer tables (no stacking, no copy back), the element-wise
-        work is three passes instead of about twenty."""
-        from ohara_b200.ops import refresh_bf16_weight
-        from ohara_b200.ops._ext import ext
-
-        C = ext()
-        device = params[0].device
-        momentum = float(group["momentum"])
-        u = torch.empty(batch, rows, cols, device=device, dtype=torch.bfloat16)
-        norm2 = torch.empty(batch, device=device, dtype=torch.float32)
-        C.muon_prepare([p.grad for p in params], state["momentum_buffer"], u, norm2, momentum)
-        update = _polar_express_kernels(u, int(group["ns_steps"]))
-        by_row = rows >= cols
-        variance = C.muon_variance(update, by_row)  # (B, r, 1) or (B, 1, c), fp32
-        size = cols if by_row else rows
-        second = state["second_momentum_buffer"]
-        norm_before = (variance.sum(dim=(-2, -1), keepdim=True) * size).sqrt()
-        second.lerp_(variance, 1.0 - float(group["beta2"]))
-        inv_rms = second.clamp_min(1e-10).rsqrt()
-        norm_after = ((variance * size) * inv_rms.square()).sum(dim=(-2, -1), keepdim=True).sqrt()
-        factor = (inv_rms * (norm_before / norm_after.clamp_min(1e-10))).to(torch.bfloat16).float()
-        lr = float(group["lr"]) * math.sqrt(max(1.0, rows / cols))
-        shadows = []
-        for p in params:
-            cached = getattr(p, "_ohara_bf16", None)
-            if cached is None or cached[1].shape != p.shape or cached[1].device != p.device \
-                    or not cached[1].is_contiguous():
-                shadows = []
-                break
-            shadows.append(cached[1])
-        C.muon_apply([p.detach() for p in params], shadows, update, factor.contiguous(), lr,
-                     float(group["weight_decay"]), by_row)
-        if shadows:
-            for p, shadow in zip(params, shadows):
-                refresh_bf16_weight(p, shadow)
-        else:
-            # The kernel wrote through raw pointers (no version bump): drop any compute copy.
-            for p in params:
-                if getattr(p, "_ohara_bf16", None) is not None:
-                    p._ohara_bf16 = None
-
     @torch.no_grad()
     def step(self, closure=None):
         loss = None
@@ -448,6 +403,51 @@ class MuonAdamW(optim.Optimizer):
             stacked.sub_(lr * update + lr * wd * stacked * aligned)
         if not pre_stacked:
             torch._foreach_copy_(params, list(stacked.unbind(0)))
+
+    @staticmethod
+    def _muon_step_fused(group: dict[str, Any], state: dict[str, Any], params: list[Tensor],
+                         batch: int, rows: int, cols: int) -> None:
+        """The same step on the kernels of ``csrc/muon.cu``: gradients and parameters are read
+        and written in place through pointer tables (no stacking, no copy back), the element-wise
+        work is three passes instead of about twenty."""
+        from ohara_b200.ops import refresh_bf16_weight
+        from ohara_b200.ops._ext import ext
+
+        C = ext()
+        device = params[0].device
+        momentum = float(group["momentum"])
+        u = torch.empty(batch, rows, cols, device=device, dtype=torch.bfloat16)
+        norm2 = torch.empty(batch, device=device, dtype=torch.float32)
+        C.muon_prepare([p.grad for p in params], state["momentum_buffer"], u, norm2, momentum)
+        update = _polar_express_kernels(u, int(group["ns_steps"]))
+        by_row = rows >= cols
+        variance = C.muon_variance(update, by_row)  # (B, r, 1) or (B, 1, c), fp32
+        size = cols if by_row else rows
+        second = state["second_momentum_buffer"]
+        norm_before = (variance.sum(dim=(-2, -1), keepdim=True) * size).sqrt()
+        second.lerp_(variance, 1.0 - float(group["beta2"]))
+        inv_rms = second.clamp_min(1e-10).rsqrt()
+        norm_after = ((variance * size) * inv_rms.square()).sum(dim=(-2, -1), keepdim=True).sqrt()
+        factor = (inv_rms * (norm_before / norm_after.clamp_min(1e-10))).to(torch.bfloat16).float()
+        lr = float(group["lr"]) * math.sqrt(max(1.0, rows / cols))
+        shadows = []
+        for p in params:
+            cached = getattr(p, "_ohara_bf16", None)
+            if cached is None or cached[1].shape != p.shape or cached[1].device != p.device \
+                    or not cached[1].is_contiguous():
+                shadows = []
+                break
+            shadows.append(cached[1])
+        C.muon_apply([p.detach() for p in params], shadows, update, factor.contiguous(), lr,
+                     float(group["weight_decay"]), by_row)
+        if shadows:
+            for p, shadow in zip(params, shadows):
+                refresh_bf16_weight(p, shadow)
+        else:
+            # The kernel wrote through raw pointers (no version bump): drop any compute copy.
+            for p in params:
+                if getattr(p, "_ohara_bf16", None) is not None:
+                    p._ohara_bf16 = None
 
     @torch.no_grad()
     def step(self, closure: Callable[[], float] | None = None) -> float | None:

