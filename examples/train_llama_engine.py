@@ -30,6 +30,7 @@ from ohara_b200.modules.moe import apply_qb_update
 from ohara_b200.optimizer import build_adamh, build_adamw, build_muon_adamw, build_muonh_adamh
 from ohara_b200.runtime import (
     EngineConfig,
+    FaultToleranceConfig,
     ParallelConfig,
     PrecisionConfig,
     PrecisionMode,
@@ -130,6 +131,13 @@ def parse_args() -> argparse.Namespace:
     run.add_argument("--ep", type=int, default=1)
     run.add_argument("--sequence-parallel", action="store_true")
     run.add_argument("--strategy", choices=[s.value for s in StrategyType], default="auto")
+    run.add_argument("--heartbeat-interval", type=float, default=0.0,
+                     help="seconds between heartbeats over the rendezvous store (0 = off); a rank "
+                          "whose heartbeat stops is reported before the next step is launched")
+    run.add_argument("--heartbeat-timeout", type=float, default=30.0)
+    run.add_argument("--step-timeout", type=float, default=0.0,
+                     help="abort (exit code 75) when one training step takes longer than this "
+                          "many seconds (0 = off), so that an elastic launcher can restart the job")
     run.add_argument("--precision", choices=[m.value for m in PrecisionMode],
                      default=PrecisionMode.BF16_MIXED.value)
     return p.parse_args()
@@ -308,6 +316,9 @@ def run() -> None:
         precision=PrecisionConfig(mode=PrecisionMode(args.precision)),
         parallel=ParallelConfig(tp=args.tp, cp=args.cp, ep=args.ep),
         tensor_parallel=TensorParallelPlan.llama_default(args.tp, args.sequence_parallel),
+        fault_tolerance=FaultToleranceConfig(
+            heartbeat_interval_s=args.heartbeat_interval, heartbeat_timeout_s=args.heartbeat_timeout,
+            step_timeout_s=args.step_timeout, exit_on_step_timeout=args.step_timeout > 0),
     ))
     engine.launch()
 

@@ -83,6 +83,78 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
   }
 }
 
+// Register-resident forward for rows of at most VPL * 256 elements: a warp handles two rows per
+// pass, issues every load of both rows before it touches the data and keeps the values in
+// registers between the sum of squares and the scaling (the generic kernel above reads a row
+// twice and has one row's loads in flight per warp).
+template <int VPL, bool HAS_DELTA>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                       const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                       __nv_bfloat16* __restrict__ x_out, float* __restrict__ rstd_out, int rows,
+                       int d, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int vecs = d >> 3;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int row0 = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 2; row0 < rows;
+       row0 += warps * 2) {
+    bf16x8 raw[2][VPL], extra[2][VPL];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = row0 + r;
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const int v = lane + 32 * j;
+        if (row < rows && v < vecs) {
+          raw[r][j] = reinterpret_cast<const bf16x8*>(x + (size_t)row * d)[v];
+          if (HAS_DELTA) extra[r][j] = reinterpret_cast<const bf16x8*>(delta + (size_t)row * d)[v];
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = row0 + r;
+      if (row >= rows) break;  // uniform across the warp
+      float f[VPL][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const int v = lane + 32 * j;
+        if (v < vecs) {
+          unpack8(raw[r][j], f[j]);
+          if (HAS_DELTA) {
+            float g[8];
+            unpack8(extra[r][j], g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[j][i] += g[i];
+            const bf16x8 packed = pack8(f[j]);
+            reinterpret_cast<bf16x8*>(x_out + (size_t)row * d)[v] = packed;
+            unpack8(packed, f[j]);  // normalise exactly what later kernels will read
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss += f[j][i] * f[j][i];
+        }
+      }
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss / (float)d + eps);
+      if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const int v = lane + 32 * j;
+        if (v < vecs) {
+          const float4 w0 = reinterpret_cast<const float4*>(w)[2 * v];
+          const float4 w1 = reinterpret_cast<const float4*>(w)[2 * v + 1];
+          const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = f[j][i] * rstd * ww[i];
+          reinterpret_cast<bf16x8*>(y + (size_t)row * d)[v] = pack8(o);
+        }
+      }
+    }
+  }
+}
+
 // RMSNorm backward. dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres), dw += sum_rows(dy*xhat).
 // One warp per row; every lane owns the same VPL 8-element column groups for all of its rows, so
 // x, dy and the dw partial sums stay in registers. Per-warp partials are combined through shared
@@ -394,6 +466,28 @@ void rmsnorm_fwd(const void* x, const void* delta, const float* w, void* y, void
                  int rows, int d, float eps, cudaStream_t stream) {
   OB_CHECK(d % 8 == 0, "rmsnorm: width must be a multiple of 8");
   const int threads = 256;
+  const int vpl = (d / 8 + 31) / 32;
+  if (vpl <= 4) {
+    const int blocks = grid_for((int64_t)((rows + 1) / 2) * 32, threads, 8);
+    const auto* xp = (const __nv_bfloat16*)x;
+    const auto* dp = (const __nv_bfloat16*)delta;
+    auto* yp = (__nv_bfloat16*)y;
+    auto* xo = (__nv_bfloat16*)x_out;
+#define OB_NORM_FWD(V)                                                                          \
+  if (delta != nullptr)                                                                         \
+    rmsnorm_fwd_reg_kernel<V, true><<<blocks, threads, 0, stream>>>(xp, dp, w, yp, xo, rstd,    \
+                                                                    rows, d, eps);              \
+  else                                                                                          \
+    rmsnorm_fwd_reg_kernel<V, false><<<blocks, threads, 0, stream>>>(xp, nullptr, w, yp,        \
+                                                                     nullptr, rstd, rows, d, eps)
+    if (vpl <= 1) { OB_NORM_FWD(1); }
+    else if (vpl == 2) { OB_NORM_FWD(2); }
+    else if (vpl == 3) { OB_NORM_FWD(3); }
+    else { OB_NORM_FWD(4); }
+#undef OB_NORM_FWD
+    OB_LAUNCH_CHECK();
+    return;
+  }
   const int blocks = grid_for((int64_t)rows * 32, threads, 8);
   if (delta != nullptr)
     rmsnorm_fwd_kernel<true><<<blocks, threads, 0, stream>>>(

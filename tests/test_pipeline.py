@@ -1,0 +1,70 @@
+"""Pipeline schedules on gloo ranks: gradients and loss of a 3-stage pipeline must equal those of
+the unsplit model on the whole batch, for both schedules."""
+
+import os
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+import pytest
+import torch.nn as nn
+
+from ohara_b200.parallel.pipeline import split_sequential
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_split_sequential_is_contiguous_and_balanced():
+    layers = [nn.Linear(2, 2) for _ in range(7)]
+    parts = [split_sequential(layers, 3, r) for r in range(3)]
+    assert [len(p) for p in parts] == [3, 2, 2]
+    assert [m for p in parts for m in p] == layers
+    with pytest.raises(ValueError):
+        split_sequential(layers[:2], 3, 0)
+
+
+@pytest.mark.parametrize("schedule", ["1f1b", "gpipe"])
+def test_three_stage_pipeline_matches_the_unsplit_model(tmp_path, schedule):
+    script = """
+        import torch, torch.nn as nn, torch.distributed as dist
+        from ohara_b200.parallel.pipeline import PipelineRunner, split_sequential
+        from ohara_b200.runtime.enums import PipelineScheduleType
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        torch.manual_seed(0)
+        layers = []
+        for _ in range(6):
+            layers += [nn.Linear(16, 16), nn.Tanh()]
+        layers.append(nn.Linear(16, 4))
+        full = nn.Sequential(*layers)
+        x = torch.randn(10, 16)
+        y = torch.randn(10, 4)
+        loss_fn = lambda out, target: ((out - target) ** 2).mean()
+        micro = 5
+        xs, ys = x.chunk(micro), y.chunk(micro)
+        reference = sum(loss_fn(full(a), b) for a, b in zip(xs, ys)) / micro
+        reference.backward()
+        expected = {id(p): p.grad.clone() for p in full.parameters()}
+        for p in full.parameters():
+            p.grad = None
+        stage = split_sequential(layers, world, rank)
+        runner = PipelineRunner(stage, loss_fn if rank == world - 1 else None,
+                                schedule=PipelineScheduleType("%s"),
+                                activation_shape=(2, 16), device="cpu")
+        loss = runner.step(xs if rank == 0 else None, ys if rank == world - 1 else None, micro)
+        for p in stage.parameters():
+            assert torch.allclose(p.grad, expected[id(p)], atol=1e-6), (rank, (p.grad - expected[id(p)]).abs().max())
+        if rank == world - 1:
+            assert torch.allclose(loss, reference.detach(), atol=1e-6)
+            print("PIPELINE_OK")
+        dist.barrier()
+    """ % schedule
+    path = tmp_path / "worker.py"
+    path.write_text(textwrap.dedent(script))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3",
+           "--master-addr", "127.0.0.1", "--master-port", str(30600 + os.getpid() % 300), str(path)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "PIPELINE_OK" in proc.stdout
