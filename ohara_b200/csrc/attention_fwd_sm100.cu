@@ -277,9 +277,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
-        // every other exponential on the FMA pipe instead of the MUFU
-        const float arg = fmaf(s[i], p.scale_log2, -m_use);
-        s[i] = (i & 1) ? poly_exp2(arg) : fast_exp2(arg);
+        s[i] = fast_exp2(fmaf(s[i], p.scale_log2, -m_use));
         sum += s[i];
       }
       l_run = l_run * alpha + sum;

@@ -446,24 +446,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// 2^x on the FMA and integer pipes (no MUFU): round to the nearest integer with the 1.5 * 2^23
-// trick, a degree-4 polynomial for the fraction in [-0.5, 0.5] (relative error below 1e-4, far
-// inside bf16 rounding) and the integer added into the exponent field. A softmax that alternates
-// this with `fast_exp2` keeps both pipes busy: the 16 exponentials per cycle of the MUFU are what
-// paces the forward attention kernel otherwise.
-__device__ __forceinline__ float poly_exp2(float x) {
-  x = fmaxf(x, -126.f);
-  const float magic = 12582912.f;
-  const float t = x + magic;
-  const float f = x - (t - magic);
-  float p = 0.00961813f;
-  p = fmaf(p, f, 0.05550411f);
-  p = fmaf(p, f, 0.24022651f);
-  p = fmaf(p, f, 0.69314718f);
-  p = fmaf(p, f, 1.0f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
