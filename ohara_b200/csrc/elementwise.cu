@@ -331,43 +331,33 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ g,
   }
 }
 
-__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ da,
-                                  const __nv_bfloat16* __restrict__ g,
-                                  const __nv_bfloat16* __restrict__ u,
-                                  __nv_bfloat16* __restrict__ dg, __nv_bfloat16* __restrict__ du,
-                                  int64_t rows, int h, int64_t da_pitch, int64_t g_pitch,
-                                  int64_t u_pitch, int64_t dg_pitch, int64_t du_pitch) {
+__global__ void __launch_bounds__(256, 6)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ da, const __nv_bfloat16* __restrict__ g,
+                  const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ dg,
+                  __nv_bfloat16* __restrict__ du, int64_t rows, int h, int64_t da_pitch,
+                  int64_t g_pitch, int64_t u_pitch, int64_t dg_pitch, int64_t du_pitch) {
+  // One row per pass (three loads in flight per thread): the two-row form of the forward kernel
+  // needs 95 registers here and loses more to occupancy than it gains.
   const int vecs = h >> 3;
-  for (int64_t r = (int64_t)blockIdx.x * 2; r < rows; r += (int64_t)gridDim.x * 2) {
-    const bool two = r + 1 < rows;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
       const int c = v * 8;
-      bf16x8 d_raw[2], g_raw[2], u_raw[2];
-      d_raw[0] = *reinterpret_cast<const bf16x8*>(da + r * da_pitch + c);
-      g_raw[0] = *reinterpret_cast<const bf16x8*>(g + r * g_pitch + c);
-      u_raw[0] = *reinterpret_cast<const bf16x8*>(u + r * u_pitch + c);
-      if (two) {
-        d_raw[1] = *reinterpret_cast<const bf16x8*>(da + (r + 1) * da_pitch + c);
-        g_raw[1] = *reinterpret_cast<const bf16x8*>(g + (r + 1) * g_pitch + c);
-        u_raw[1] = *reinterpret_cast<const bf16x8*>(u + (r + 1) * u_pitch + c);
-      }
+      const bf16x8 d_raw = *reinterpret_cast<const bf16x8*>(da + r * da_pitch + c);
+      const bf16x8 g_raw = *reinterpret_cast<const bf16x8*>(g + r * g_pitch + c);
+      const bf16x8 u_raw = *reinterpret_cast<const bf16x8*>(u + r * u_pitch + c);
+      float df[8], gf[8], uf[8], og[8], ou[8];
+      unpack8(d_raw, df);
+      unpack8(g_raw, gf);
+      unpack8(u_raw, uf);
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        if (j == 1 && !two) break;
-        float df[8], gf[8], uf[8], og[8], ou[8];
-        unpack8(d_raw[j], df);
-        unpack8(g_raw[j], gf);
-        unpack8(u_raw[j], uf);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float sig = 1.f / (1.f + __expf(-gf[i]));
-          const float silu = gf[i] * sig;
-          ou[i] = df[i] * silu;
-          og[i] = df[i] * uf[i] * (sig + silu * (1.f - sig));
-        }
-        *reinterpret_cast<bf16x8*>(dg + (r + j) * dg_pitch + c) = pack8(og);
-        *reinterpret_cast<bf16x8*>(du + (r + j) * du_pitch + c) = pack8(ou);
+      for (int i = 0; i < 8; ++i) {
+        const float sig = __fdividef(1.f, 1.f + __expf(-gf[i]));
+        const float silu = gf[i] * sig;
+        ou[i] = df[i] * silu;
+        og[i] = df[i] * uf[i] * (sig + silu * (1.f - sig));
       }
+      *reinterpret_cast<bf16x8*>(dg + r * dg_pitch + c) = pack8(og);
+      *reinterpret_cast<bf16x8*>(du + r * du_pitch + c) = pack8(ou);
     }
   }
 }
@@ -563,7 +553,7 @@ void swiglu_bwd(const void* da, const void* g, const void* u, void* dg, void* du
                 int64_t du_pitch, cudaStream_t stream) {
   OB_CHECK(h % 8 == 0, "swiglu: width must be a multiple of 8");
   const int threads = 256;
-  swiglu_bwd_kernel<<<grid_for((rows + 1) / 2 * threads, threads), threads, 0, stream>>>(
+  swiglu_bwd_kernel<<<grid_for(rows * threads, threads), threads, 0, stream>>>(
       (const __nv_bfloat16*)da, (const __nv_bfloat16*)g, (const __nv_bfloat16*)u,
       (__nv_bfloat16*)dg, (__nv_bfloat16*)du, rows, h, da_pitch, g_pitch, u_pitch, dg_pitch,
       du_pitch);
