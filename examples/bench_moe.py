@@ -93,9 +93,9 @@ def benchmark(model: Llama, args, peak: float, *, moe: bool) -> dict[str, float]
            "active": model.active_matmul_parameters(),
            "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9}
     if moe:
-        counts = expert_load(model, reset=False)
-        if counts is not None:
-            row["maxvio"] = float(maximal_violation(counts).mean())
+        per_layer = expert_load(model, reset=False)
+        if per_layer:
+            row["maxvio"] = sum(maximal_violation(c) for c in per_layer) / len(per_layer)
     del optimizer, model
     torch.cuda.empty_cache()
     return row

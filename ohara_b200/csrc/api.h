@@ -15,7 +15,8 @@ void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int b
                int64_t strideC, bool a_batched, bool b_batched, int b_batches, bool out_f32,
                int splits, bool reduce, float alpha, const int* m_tile_batch,
                const int* k_offsets, int64_t a_rows, int64_t b_rows, int num_sms,
-               const void* R, int64_t ldr, int64_t strideR, float beta, cudaStream_t stream);
+               const void* R, int64_t ldr, int64_t strideR, float beta, cudaStream_t stream,
+               int m_tile_rows = 128);
 
 // Fused collective of a GEMM (see gemm_sm100.cu). mode 1: gather the rows of A from `world` peers
 // (`a_maps`: device array of tensor maps built by make_peer_row_maps, `ready`: this rank's flag
@@ -37,7 +38,7 @@ void gemm_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, 
                     bool out_f32, int splits, bool reduce, float alpha, const int* m_tile_batch,
                     const int* k_offsets, int64_t a_rows, int64_t b_rows, int num_sms,
                     const void* R, int64_t ldr, int64_t strideR, float beta, const GemmComm* comm,
-                    cudaStream_t stream);
+                    cudaStream_t stream, int m_tile_rows = 128);
 // Encodes one (rows x K, K-major, pitch ld) A-operand tensor map per peer buffer into `out`
 // (host memory, 128 bytes each).
 void make_peer_row_maps(const int64_t* bases, int world, int64_t rows, int64_t K, int64_t ld,

@@ -32,7 +32,7 @@ void check_rowmajor(const Tensor& t, const char* name) {
 void gemm(const Tensor& a, const Tensor& b, Tensor& c, int64_t M, int64_t N, int64_t K, bool a_mn,
           bool b_mn, int64_t splits, bool reduce, double alpha,
           const c10::optional<Tensor>& m_tile_batch, const c10::optional<Tensor>& k_offsets,
-          const c10::optional<Tensor>& residual, double beta) {
+          const c10::optional<Tensor>& residual, double beta, int64_t m_tile_rows) {
   check_bf16(a, "a");
   check_bf16(b, "b");
   check_cuda(c, "c");
@@ -69,7 +69,8 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& c, int64_t M, int64_t N, int
   const int* koff = nullptr;
   if (m_tile_batch.has_value()) {
     TORCH_CHECK(m_tile_batch->scalar_type() == torch::kInt32 && m_tile_batch->is_cuda());
-    TORCH_CHECK(m_tile_batch->numel() >= (M + 127) / 128, "m_tile_batch is too short");
+    TORCH_CHECK(m_tile_rows >= 128 && m_tile_rows % 128 == 0, "m_tile_rows must be a multiple of 128");
+    TORCH_CHECK(m_tile_batch->numel() >= (M + m_tile_rows - 1) / m_tile_rows, "m_tile_batch is too short");
     mtb = m_tile_batch->data_ptr<int>();
   }
   if (k_offsets.has_value()) {
@@ -93,7 +94,8 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& c, int64_t M, int64_t N, int
                 a_mn, b_mn, a.stride(-2), b.stride(-2), c.stride(-2), a_batched ? a.stride(0) : 0,
                 b_batched ? b.stride(0) : 0, c_batched ? c.stride(0) : 0, a_batched, b_batched,
                 (int)b_batches, out_f32, (int)splits, reduce, (float)alpha, mtb, koff, a_rows,
-                b_rows, ob::device_sm_count(), res_ptr, ldr, stride_r, (float)beta, current_stream());
+                b_rows, ob::device_sm_count(), res_ptr, ldr, stride_r, (float)beta, current_stream(),
+                (int)m_tile_rows);
 }
 
 std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& delta, const Tensor& w,
@@ -1042,7 +1044,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("K"), py::arg("a_mn"), py::arg("b_mn"), py::arg("splits") = 1,
         py::arg("reduce") = false, py::arg("alpha") = 1.0, py::arg("m_tile_batch") = py::none(),
         py::arg("k_offsets") = py::none(), py::arg("residual") = py::none(),
-        py::arg("beta") = 1.0);
+        py::arg("beta") = 1.0, py::arg("m_tile_rows") = 128);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("rope", &rope);

@@ -59,6 +59,7 @@ struct GemmParams {
   int reduce;
   float alpha;
   const int* m_tile_batch;
+  int m_tile_rows;  // rows of A / C covered by one m_tile_batch entry (a multiple of the tile)
   const int* k_offsets;
   int* status;
   // Optional residual: C = alpha * A*B + beta * R, R bf16 with the geometry of C.
@@ -244,7 +245,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         decode(tile, batch, mt, nt, kb_begin, kb_count, k0);
         int b_batch = batch;
         if (p.m_tile_batch != nullptr) {
-          b_batch = p.m_tile_batch[mt];
+          b_batch = p.m_tile_batch[(mt * TM) / p.m_tile_rows];
           if (b_batch < 0) continue;  // padding tile: nothing to compute
         }
         const int za = p.a_batched ? batch : 0;
@@ -327,7 +328,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (; tile < total_tiles; tile += tile_step) {
           int batch, mt, nt, kb_begin, k0;
           decode(tile, batch, mt, nt, kb_begin, kb_count, k0);
-          if (p.m_tile_batch == nullptr || p.m_tile_batch[mt] >= 0) return tile;
+          if (p.m_tile_batch == nullptr || p.m_tile_batch[(mt * TM) / p.m_tile_rows] >= 0)
+            return tile;
         }
         return total_tiles;
       };
@@ -396,7 +398,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
       int batch, mt, nt, kb_begin, kb_count, k0;
       decode(tile, batch, mt, nt, kb_begin, kb_count, k0);
-      if (p.m_tile_batch != nullptr && p.m_tile_batch[mt] < 0) continue;
+      if (p.m_tile_batch != nullptr && p.m_tile_batch[(mt * TM) / p.m_tile_rows] < 0) continue;
       const uint32_t acc = tile_iter & 1;
       const uint32_t acc_phase = (tile_iter >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, wctx, kTimeoutTmemFull)) break;
@@ -573,8 +575,8 @@ void launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap
   count_launch();
 }
 
-// The pair kernel serves plain and batched products whose output is wide enough for a 256-column
-// tile; ragged (mixture-of-experts) and fused-collective modes stay on the single-CTA kernel.
+// The pair kernel serves plain, batched and ragged (mixture-of-experts) products whose output is
+// wide enough for a 256-column tile; the fused-collective modes stay on the single-CTA kernel.
 bool pair_enabled() {
   static const bool enabled = [] {
     const char* e = std::getenv("OHARA_GEMM_PAIR");
@@ -592,10 +594,12 @@ void gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int b
                int64_t strideC, bool a_batched, bool b_batched, int b_batches, bool out_f32,
                int splits, bool reduce, float alpha, const int* m_tile_batch,
                const int* k_offsets, int64_t a_rows, int64_t b_rows, int num_sms,
-               const void* R, int64_t ldr, int64_t strideR, float beta, cudaStream_t stream) {
+               const void* R, int64_t ldr, int64_t strideR, float beta, cudaStream_t stream,
+               int m_tile_rows) {
   gemm_bf16_comm(A, B, C, M, N, K, batches, a_mn, b_mn, lda, ldb, ldc, strideA, strideB, strideC,
                  a_batched, b_batched, b_batches, out_f32, splits, reduce, alpha, m_tile_batch,
-                 k_offsets, a_rows, b_rows, num_sms, R, ldr, strideR, beta, nullptr, stream);
+                 k_offsets, a_rows, b_rows, num_sms, R, ldr, strideR, beta, nullptr, stream,
+                 m_tile_rows);
 }
 
 void gemm_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, int batches,
@@ -604,13 +608,16 @@ void gemm_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, 
                     bool out_f32, int splits, bool reduce, float alpha, const int* m_tile_batch,
                     const int* k_offsets, int64_t a_rows, int64_t b_rows, int num_sms,
                     const void* R, int64_t ldr, int64_t strideR, float beta, const GemmComm* comm,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, int m_tile_rows) {
   OB_CHECK(M > 0 && N > 0 && K >= 0 && batches > 0, "gemm_bf16: bad problem size");
+  OB_CHECK(m_tile_rows >= BM && m_tile_rows % BM == 0, "gemm_bf16: m_tile_rows must be a multiple of 128");
   OB_CHECK(!reduce || out_f32, "gemm_bf16: reduce-add epilogue needs an fp32 output");
   OB_CHECK(splits >= 1 && (splits == 1 || reduce), "gemm_bf16: split-K needs the reduce epilogue");
   const int BN = (N > 128) ? 256 : 128;
-  const bool pair = pair_enabled() && BN == 256 && M > 128 && m_tile_batch == nullptr &&
-                    k_offsets == nullptr && (comm == nullptr || comm->mode == 0);
+  // Ragged modes qualify when an m_tile_batch entry never covers less than a 256-row pair tile.
+  const bool pair = pair_enabled() && BN == 256 && M > 128 &&
+                    (m_tile_batch == nullptr || m_tile_rows % (2 * BM) == 0) &&
+                    (comm == nullptr || comm->mode == 0);
 
   GemmParams p;
   p.M = M;
@@ -625,6 +632,7 @@ void gemm_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, 
   p.reduce = reduce;
   p.alpha = alpha;
   p.m_tile_batch = m_tile_batch;
+  p.m_tile_rows = m_tile_rows;
   p.k_offsets = k_offsets;
   p.status = status_ptr();
   p.R = static_cast<const __nv_bfloat16*>(R);

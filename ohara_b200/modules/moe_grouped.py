@@ -6,7 +6,7 @@ reference layout (ohara/modules/moe_grouped.py:95-117), so checkpoints interchan
 
 On CUDA the router runs as a split-bf16 tensor-core GEMM plus one top-k kernel (indices, gate
 weights, balancing threshold and expert counts in a single launch); (token, expert) pairs are
-placed into a buffer whose per-expert row groups are padded to the 128-row GEMM tile; three
+placed into a buffer whose per-expert row groups are padded to the GEMM tile height; three
 *grouped* tcgen05 GEMMs (a per-tile expert table selects the weight matrix) compute the experts, the
 SwiGLU kernel fuses the activation, and a gather kernel combines with the gate weights. On CPU a
 readable per-expert loop is used, which is also the oracle.

@@ -1,9 +1,9 @@
 """Grouped (per-expert) GEMMs for mixture-of-experts layers on the tcgen05 kernel.
 
 Tokens routed to expert ``e`` occupy a contiguous row group of a padded buffer; every group starts
-on a multiple of 128 rows (the GEMM tile height), so each tile belongs to exactly one expert and the
+on a multiple of ``TILE`` rows (the height of a GEMM pair tile), so each tile belongs to exactly one expert and the
 kernel picks the weight matrix from a per-tile expert table. Nothing here synchronises with the
-host: buffer sizes are static upper bounds (``pairs + experts * 128`` rows).
+host: buffer sizes are static upper bounds (``pairs + experts * TILE`` rows).
 """
 
 from __future__ import annotations
@@ -13,7 +13,7 @@ from torch import Tensor
 
 from ._ext import ext
 
-TILE = 128
+TILE = 256  # rows every expert segment is padded to: one CTA-pair tile of the grouped GEMM
 
 
 def build_dispatch_plan(expert_indices: Tensor, num_experts: int):
@@ -21,7 +21,7 @@ def build_dispatch_plan(expert_indices: Tensor, num_experts: int):
 
     Returns ``(token_of_row, dest_row, order, tile_expert, k_offsets, padded_rows)`` where
     ``dest_row[j]`` is the padded row of the j-th sorted pair, ``tile_expert[t]`` the expert of
-    128-row tile ``t`` (−1 for unused tiles) and ``k_offsets`` the (E+1) padded group boundaries.
+    ``TILE``-row tile ``t`` (−1 for unused tiles) and ``k_offsets`` the (E+1) padded group boundaries.
     """
     tokens, k = expert_indices.shape
     pairs = tokens * k
@@ -59,7 +59,8 @@ class _GroupedLinearFn(torch.autograd.Function):
         n = weight.shape[2]
         y = torch.empty(rows, n, device=x_pad.device, dtype=torch.bfloat16)
         # B[e] stored (K=in rows, N=out contiguous): MN-major.
-        ext().gemm(x_pad, w16, y, rows, n, k, False, True, 1, False, 1.0, tile_expert, None)
+        ext().gemm(x_pad, w16, y, rows, n, k, False, True, 1, False, 1.0, tile_expert, None,
+                   None, 1.0, TILE)
         ctx.save_for_backward(x_pad, weight, tile_expert, k_offsets)
         return y
 
@@ -76,7 +77,7 @@ class _GroupedLinearFn(torch.autograd.Function):
             dx = torch.empty_like(x_pad)
             # dx = dy @ w[e]^T: B[e] as (N'=in rows, K'=out contiguous): K-major.
             ext().gemm(dy, bf16_weight(weight), dx, rows, k, n, False, False, 1, False, 1.0,
-                       tile_expert, None)
+                       tile_expert, None, None, 1.0, TILE)
         if ctx.needs_input_grad[1]:
             dw = torch.zeros(experts, k, n, device=dy.device, dtype=torch.float32)
             # dw[e] = x_e^T @ dy_e: both operands MN-major over the expert's token range.

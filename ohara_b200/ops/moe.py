@@ -14,7 +14,7 @@ from torch import Tensor
 
 from ._ext import ext
 
-TILE = 128
+TILE = 256  # rows every expert segment is padded to: one CTA-pair tile of the grouped GEMM
 
 
 # --------------------------------------------------------------------------------------------------
@@ -107,8 +107,8 @@ def accumulate_quantile(logits: Tensor, alpha: Tensor, beta_sum: Tensor, rank: i
 # Dispatch
 # --------------------------------------------------------------------------------------------------
 def dispatch_plan(indices: Tensor, counts: Tensor):
-    """``(dest_row (N*k,), row_pair (rows,), tile_expert (rows/128,), k_offsets (E+1,))`` for int32
-    ``indices (N, k)`` and the per-expert ``counts``; every expert segment starts on a 128-row
+    """``(dest_row (N*k,), row_pair (rows,), tile_expert (rows/TILE,), k_offsets (E+1,))`` for int32
+    ``indices (N, k)`` and the per-expert ``counts``; every expert segment starts on a ``TILE``-row
     boundary and ``rows`` is a static upper bound."""
     return ext().moe_plan(indices.contiguous(), counts, TILE)
 

@@ -26,14 +26,14 @@ from torch import Tensor
 from ohara_b200.ops._ext import ext
 from ohara_b200.parallel.peer import PeerRuntime, SymmetricBuffer
 
-TILE = 128
+from ohara_b200.ops.moe import TILE  # rows every expert segment is padded to (a GEMM pair tile)
 
 
 @dataclass
 class DispatchPlan:
     dest_rank: Tensor   # (pairs,) owner rank of each (token, expert) pair
     dest_row: Tensor    # (pairs,) row in the owner's padded buffer, -1 when dropped
-    tile_expert: Tensor  # local expert of every 128-row tile of this rank's buffer (-1 unused)
+    tile_expert: Tensor  # local expert of every TILE-row block of this rank's buffer (-1 unused)
     k_offsets: Tensor   # (local experts + 1,) segment boundaries in this rank's buffer
     fill: Tensor        # (2, local experts) padding rows to clear
     rows_used: Tensor   # (1,) rows the full layout needs on this rank (above capacity = drops)
