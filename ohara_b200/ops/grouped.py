@@ -79,7 +79,8 @@ class _GroupedLinearFn(torch.autograd.Function):
             ext().gemm(dy, bf16_weight(weight), dx, rows, k, n, False, False, 1, False, 1.0,
                        tile_expert, None, None, 1.0, TILE)
         if ctx.needs_input_grad[1]:
-            dw = torch.zeros(experts, k, n, device=dy.device, dtype=torch.float32)
+            # every (expert, tile) of dw is written by the kernel, zeros for an expert without rows
+            dw = torch.empty(experts, k, n, device=dy.device, dtype=torch.float32)
             # dw[e] = x_e^T @ dy_e: both operands MN-major over the expert's token range.
             ext().gemm(x_pad, dy, dw, k, n, rows, True, True, 1, False, 1.0, None, k_offsets)
             if dw.dtype != weight.dtype:
