@@ -300,15 +300,19 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
 // each takes a row pitch.
 // ------------------------------------------------------------------------------------------------
 // A block walks over pairs of rows and its threads over the 8-element column groups: no index
-// division, and the loads of two rows are in flight before either is consumed.
+// division in the loop, and the loads of two rows are in flight before either is consumed. Rows
+// narrower than the block (fewer than blockDim.x column groups) share it: ``tpr`` threads per row,
+// blockDim.x / tpr row pairs per pass, so that no thread idles on the narrow expert layers.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ g,
                                   const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ a,
-                                  int64_t rows, int h, int64_t g_pitch, int64_t u_pitch,
+                                  int64_t rows, int h, int tpr, int64_t g_pitch, int64_t u_pitch,
                                   int64_t a_pitch) {
   const int vecs = h >> 3;
-  for (int64_t r = (int64_t)blockIdx.x * 2; r < rows; r += (int64_t)gridDim.x * 2) {
+  const int sub = threadIdx.x / tpr, v0 = threadIdx.x - sub * tpr, rpb = blockDim.x / tpr;
+  for (int64_t r = ((int64_t)blockIdx.x * rpb + sub) * 2; r < rows;
+       r += (int64_t)gridDim.x * rpb * 2) {
     const bool two = r + 1 < rows;
-    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+    for (int v = v0; v < vecs; v += tpr) {
       const int c = v * 8;
       bf16x8 g_raw[2], u_raw[2];
       g_raw[0] = *reinterpret_cast<const bf16x8*>(g + r * g_pitch + c);
@@ -334,13 +338,16 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ g,
 __global__ void __launch_bounds__(256, 6)
 swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ da, const __nv_bfloat16* __restrict__ g,
                   const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ dg,
-                  __nv_bfloat16* __restrict__ du, int64_t rows, int h, int64_t da_pitch,
-                  int64_t g_pitch, int64_t u_pitch, int64_t dg_pitch, int64_t du_pitch) {
-  // One row per pass (three loads in flight per thread): the two-row form of the forward kernel
-  // needs 95 registers here and loses more to occupancy than it gains.
+                  __nv_bfloat16* __restrict__ du, int64_t rows, int h, int tpr,
+                  int64_t da_pitch, int64_t g_pitch, int64_t u_pitch, int64_t dg_pitch,
+                  int64_t du_pitch) {
+  // One row per pass and thread group (three loads in flight per thread): the two-row form of the
+  // forward kernel needs 95 registers here and loses more to occupancy than it gains. ``tpr``
+  // threads share a row, as in the forward kernel.
   const int vecs = h >> 3;
-  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
-    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+  const int sub = threadIdx.x / tpr, v0 = threadIdx.x - sub * tpr, rpb = blockDim.x / tpr;
+  for (int64_t r = (int64_t)blockIdx.x * rpb + sub; r < rows; r += (int64_t)gridDim.x * rpb) {
+    for (int v = v0; v < vecs; v += tpr) {
       const int c = v * 8;
       const bf16x8 d_raw = *reinterpret_cast<const bf16x8*>(da + r * da_pitch + c);
       const bf16x8 g_raw = *reinterpret_cast<const bf16x8*>(g + r * g_pitch + c);
@@ -450,6 +457,14 @@ inline int grid_for(int64_t work_items, int threads, int max_blocks_per_sm = 8) 
   return (int)std::max<int64_t>(1, std::min<int64_t>(blocks, cap));
 }
 
+// Threads that share one row of ``vecs`` 16-byte groups: the smallest of 32, 64, 128, ... that
+// covers the row, capped at the block size.
+inline int threads_per_row(int vecs, int threads) {
+  int tpr = 32;
+  while (tpr < vecs && tpr < threads) tpr <<= 1;
+  return tpr;
+}
+
 }  // namespace
 
 void rmsnorm_fwd(const void* x, const void* delta, const float* w, void* y, void* x_out, float* rstd,
@@ -545,8 +560,9 @@ void swiglu_fwd(const void* g, const void* u, void* a, int64_t rows, int h, int6
                 int64_t u_pitch, int64_t a_pitch, cudaStream_t stream) {
   OB_CHECK(h % 8 == 0, "swiglu: width must be a multiple of 8");
   const int threads = 256;
-  swiglu_fwd_kernel<<<grid_for((rows + 1) / 2 * threads, threads), threads, 0, stream>>>(
-      (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (__nv_bfloat16*)a, rows, h, g_pitch,
+  const int tpr = threads_per_row(h >> 3, threads);
+  swiglu_fwd_kernel<<<grid_for((rows + 1) / 2 * tpr, threads), threads, 0, stream>>>(
+      (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (__nv_bfloat16*)a, rows, h, tpr, g_pitch,
       u_pitch, a_pitch);
   OB_LAUNCH_CHECK();
 }
@@ -556,9 +572,10 @@ void swiglu_bwd(const void* da, const void* g, const void* u, void* dg, void* du
                 int64_t du_pitch, cudaStream_t stream) {
   OB_CHECK(h % 8 == 0, "swiglu: width must be a multiple of 8");
   const int threads = 256;
-  swiglu_bwd_kernel<<<grid_for(rows * threads, threads), threads, 0, stream>>>(
+  const int tpr = threads_per_row(h >> 3, threads);
+  swiglu_bwd_kernel<<<grid_for(rows * tpr, threads), threads, 0, stream>>>(
       (const __nv_bfloat16*)da, (const __nv_bfloat16*)g, (const __nv_bfloat16*)u,
-      (__nv_bfloat16*)dg, (__nv_bfloat16*)du, rows, h, da_pitch, g_pitch, u_pitch, dg_pitch,
+      (__nv_bfloat16*)dg, (__nv_bfloat16*)du, rows, h, tpr, da_pitch, g_pitch, u_pitch, dg_pitch,
       du_pitch);
   OB_LAUNCH_CHECK();
 }

@@ -87,14 +87,15 @@ class QuantileBalancedRouter(nn.Module):
     @torch.no_grad()
     def apply_qb_update(self, group=None) -> None:
         """Fold the statistics of this optimizer step into ``router_bias`` (mean-zero)."""
-        if float(self.qb_beta_count) == 0:
-            return
-        beta = self.qb_beta_sum / self.qb_beta_count
+        # "nothing accumulated" is decided on the device (a host read here would stall the launch
+        # queue once per layer and step): with a zero count the old bias is kept.
+        seen = self.qb_beta_count > 0
+        beta = self.qb_beta_sum / self.qb_beta_count.clamp_min(1)
         if dist.is_available() and dist.is_initialized():
             dist.all_reduce(beta, op=dist.ReduceOp.SUM, group=group)
             beta /= dist.get_world_size(group=group)
         bias = -beta
-        self.router_bias.copy_(bias - bias.mean())
+        self.router_bias.copy_(torch.where(seen, bias - bias.mean(), self.router_bias))
         self.qb_beta_sum.zero_()
         self.qb_beta_count.zero_()
 

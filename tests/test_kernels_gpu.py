@@ -124,12 +124,14 @@ def test_rope_forward_backward(heads, kv_heads, dim):
     assert rel_err(k.grad, rope_reference(gk.float(), cos, sin, inverse=True)) < 1e-2
 
 
-def test_swiglu_forward_backward():
+@pytest.mark.parametrize("rows,width", [(513, 1024), (1031, 512), (77, 40), (300, 4096), (1, 8)])
+def test_swiglu_forward_backward(rows, width):
+    """Wide rows take a whole block, narrow rows share one; both against fp32 PyTorch."""
     from ohara_b200 import ops
 
-    g, u = bf(513, 1024).requires_grad_(), bf(513, 1024).requires_grad_()
+    g, u = bf(rows, width).requires_grad_(), bf(rows, width).requires_grad_()
     a = ops.swiglu(g, u)
-    da = bf(513, 1024)
+    da = bf(rows, width)
     a.backward(da)
     gr, ur = g.detach().float().requires_grad_(), u.detach().float().requires_grad_()
     ar = F.silu(gr) * ur
