@@ -306,6 +306,24 @@ def bench_sampler(kind, args, timer):
                 baseline=library)
 
 
+def bench_pscan(kind, args, timer):
+    """Linear-recurrence scan, forward + backward, against the whole-tensor doubling scan."""
+    from ohara_b200.modules.pscan import PScan, pscan
+
+    batch, length, channels = args.batch, args.seq, args.n
+    a = torch.rand(batch, length, channels, device="cuda").mul_(0.2).add_(0.8).requires_grad_()
+    x = torch.randn(batch, length, channels, device="cuda", requires_grad=True)
+    grad = torch.randn(batch, length, channels, device="cuda")
+
+    def run(fn):
+        a.grad = x.grad = None
+        fn(a, x).backward(grad)
+
+    # forward reads a, x and writes h; backward reads dh, a, h and writes da, dx
+    return dict(shape=[batch, length, channels], work=8.0 * batch * length * channels * 4,
+                kind="bytes", ours=lambda: run(pscan), baseline=lambda: run(PScan.apply))
+
+
 OPS = {
     "gemm_nt": bench_gemm, "gemm_nn": bench_gemm, "gemm_tn": bench_gemm,
     "attn_fwd": bench_attention, "attn_bwd": bench_attention,
@@ -314,6 +332,7 @@ OPS = {
     "router": bench_router, "permute_combine": bench_permute_combine,
     "grouped_gemm": bench_grouped_gemm, "quantile": bench_quantile,
     "decode_attention": bench_decode_attention, "sampler": bench_sampler,
+    "pscan": bench_pscan,
 }
 DEFAULTS = {
     "gemm_nt": dict(m=65536, n=768, k=768), "gemm_nn": dict(m=65536, n=768, k=2048),
@@ -323,6 +342,7 @@ DEFAULTS = {
     "router": dict(m=32768, n=1024), "permute_combine": dict(m=32768, n=1024),
     "grouped_gemm": dict(m=32768, n=1024, k=512), "quantile": dict(m=32768, n=1024),
     "decode_attention": dict(batch=64, seq=768), "sampler": dict(batch=64, n=50304),
+    "pscan": dict(batch=4, seq=1024, n=24576),
 }
 
 

@@ -119,6 +119,13 @@ void muon_apply(const MuonTable& params, const MuonTable* shadows, const void* x
                 int batch, int rows, int cols, float lr, float wd, bool by_row, int per_pointer,
                 cudaStream_t stream);
 
+// pscan.cu: h[t] = a[t] * h[t-1] + x[t] along dim 1 of contiguous (batch, length, channels) fp32
+// tensors, and its gradients (da, dx) from dh, in one pass over the sequence each.
+void pscan_forward(const float* a, const float* x, float* h, int64_t batch, int length,
+                   int64_t channels, cudaStream_t stream);
+void pscan_backward(const float* a, const float* h, const float* dh, float* da, float* dx,
+                    int64_t batch, int length, int64_t channels, cudaStream_t stream);
+
 // sinkhorn.cu: `count` row-major n x n fp32 matrices -> doubly stochastic matrices, and the
 // vector-Jacobian product of that map.
 bool sinkhorn_supported(int n, int iters);

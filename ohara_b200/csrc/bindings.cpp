@@ -438,6 +438,38 @@ void muon_apply(const std::vector<Tensor>& params, const std::vector<Tensor>& sh
                  current_stream());
 }
 
+// ---- linear recurrence scan ------------------------------------------------------------------------
+Tensor pscan_fwd(const Tensor& a, const Tensor& x) {
+  check_f32(a, "a");
+  check_f32(x, "x");
+  TORCH_CHECK(a.is_contiguous() && x.is_contiguous() && a.sizes() == x.sizes() && a.dim() >= 2,
+              "pscan: contiguous (B, L, ...) tensors of equal shape");
+  const c10::cuda::CUDAGuard guard(a.device());
+  Tensor h = torch::empty_like(a);
+  const int64_t batch = a.size(0), length = a.size(1);
+  const int64_t channels = batch * length == 0 ? 0 : a.numel() / (batch * length);
+  ob::pscan_forward(a.data_ptr<float>(), x.data_ptr<float>(), h.data_ptr<float>(), batch,
+                    (int)length, channels, current_stream());
+  return h;
+}
+
+std::vector<Tensor> pscan_bwd(const Tensor& a, const Tensor& h, const Tensor& dh) {
+  check_f32(a, "a");
+  check_f32(h, "h");
+  check_f32(dh, "dh");
+  TORCH_CHECK(a.is_contiguous() && h.is_contiguous() && dh.is_contiguous() &&
+                  a.sizes() == h.sizes() && a.sizes() == dh.sizes() && a.dim() >= 2,
+              "pscan: contiguous (B, L, ...) tensors of equal shape");
+  const c10::cuda::CUDAGuard guard(a.device());
+  Tensor da = torch::empty_like(a), dx = torch::empty_like(a);
+  const int64_t batch = a.size(0), length = a.size(1);
+  const int64_t channels = batch * length == 0 ? 0 : a.numel() / (batch * length);
+  ob::pscan_backward(a.data_ptr<float>(), h.data_ptr<float>(), dh.data_ptr<float>(),
+                     da.data_ptr<float>(), dx.data_ptr<float>(), batch, (int)length, channels,
+                     current_stream());
+  return {da, dx};
+}
+
 // ---- Sinkhorn -----------------------------------------------------------------------------------
 Tensor sinkhorn_fwd(const Tensor& x, int64_t iters) {
   check_f32(x, "log_alpha");
@@ -1060,6 +1092,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("muon_prepare", &muon_prepare);
   m.def("muon_variance", &muon_variance);
   m.def("muon_apply", &muon_apply);
+  m.def("pscan_fwd", &pscan_fwd);
+  m.def("pscan_bwd", &pscan_bwd);
   m.def("sinkhorn_fwd", &sinkhorn_fwd);
   m.def("sinkhorn_bwd", &sinkhorn_bwd);
   m.def("sinkhorn_supported", &sinkhorn_supported);

@@ -1,9 +1,11 @@
 """Parallel scan for first-order linear recurrences ``h[t] = a[t] * h[t-1] + x[t]`` (``h[-1] = 0``).
 
 Used by Mamba's selective scan and the RG-LRU. The reference carries a Blelloch up/down-sweep
-(ohara/modules/pscan.py:63-258); this implementation uses the Hillis-Steele doubling form, which
-needs ``ceil(log2 L)`` passes of whole-tensor operations, no padding to a power of two and no
-in-place tricks, with an explicit backward that is itself a (reversed) scan:
+(ohara/modules/pscan.py:63-258). Here CUDA tensors run the one-pass kernels of ``csrc/pscan.cu``
+(a thread owns four channels and walks the sequence; every tensor crosses HBM once, forward and
+backward); other tensors use the Hillis-Steele doubling form below, which needs ``ceil(log2 L)``
+passes of whole-tensor operations, no padding to a power of two and no in-place tricks. Both have
+an explicit backward that is itself a (reversed) scan:
 
     dx[t] = dh[t] + a[t+1] * dx[t+1]        da[t] = dx[t] * h[t-1]
 """
@@ -50,11 +52,35 @@ class PScan(torch.autograd.Function):
         return dx * h_prev, dx
 
 
+class PScanCuda(torch.autograd.Function):
+    """The same recurrence on the one-pass CUDA kernels; computes in fp32 whatever the input type."""
+
+    @staticmethod
+    def forward(ctx, a: Tensor, x: Tensor) -> Tensor:
+        from ohara_b200.ops._ext import ext
+
+        a32, x32 = a.float().contiguous(), x.float().contiguous()
+        h = ext().pscan_fwd(a32, x32)
+        ctx.save_for_backward(a32, h)
+        ctx.dtypes = (a.dtype, x.dtype)
+        return h.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_h: Tensor):
+        from ohara_b200.ops._ext import ext
+
+        a32, h = ctx.saved_tensors
+        da, dx = ext().pscan_bwd(a32, h, grad_h.float().contiguous())
+        return da.to(ctx.dtypes[0]), dx.to(ctx.dtypes[1])
+
+
 def pscan(A: Tensor, X: Tensor) -> Tensor:
     """``H`` with ``H[:, t] = A[:, t] * H[:, t-1] + X[:, t]`` for ``(B, L, D, N)`` (or any
     ``(B, L, ...)``) inputs of equal shape."""
     if A.shape != X.shape:
         raise ValueError("pscan expects coefficient and input tensors of the same shape")
+    if A.is_cuda and X.is_cuda and A.dim() >= 2 and A.dtype != torch.float64:
+        return PScanCuda.apply(A, X)
     return PScan.apply(A, X)
 
 
