@@ -272,11 +272,13 @@ class Llama(nn.Module):
         return start
 
     def enable_context_parallel(self, workspace, rank: int, world: int) -> None:
-        """Shard the sequence over a context-parallel group: this rank then receives chunk
-        ``rank`` of every sequence (``T / world`` tokens), rotary positions are the global ones
-        and every attention layer exchanges keys / values through ``workspace``
-        (:class:`ohara_b200.parallel.cp.CPWorkspace` or its lazy form)."""
+        """Shard the sequence over a context-parallel group: this rank then receives its zig-zag
+        shard of every sequence (``T / world`` tokens: block ``rank`` and block ``2 * world - 1 -
+        rank`` of ``2 * world``, see :func:`ohara_b200.parallel.cp.shard_sequence`), rotary
+        positions are the global ones and every attention layer exchanges keys / values through
+        ``workspace`` (:class:`ohara_b200.parallel.cp.CPWorkspace` or its lazy form)."""
         self._cp = (rank, world)
+        self._cp_positions = None
         for block in self.layers:
             block.attn.cp_workspace = workspace
 
@@ -312,11 +314,18 @@ class Llama(nn.Module):
         seq = x.size(1)
         cp = getattr(self, "_cp", None)
         if cp is not None and kv_cache is None:
-            start = cp[0] * seq  # this rank holds chunk `rank` of the sequence
             if cp[1] * seq > self.config.max_sequence_length:
                 raise ValueError("the full sequence exceeds max_sequence_length")
+            cached = self._cp_positions
+            if cached is None or cached.numel() != seq or cached.device != x.device:
+                from ohara_b200.parallel.cp import local_positions
+
+                cached = self._cp_positions = local_positions(cp[0], cp[1], seq, device=x.device)
         h = ops.embedding(x, self.token_emb.weight)
-        freqs = (self.freq_cos[start : start + seq], self.freq_sin[start : start + seq])
+        if cp is not None and kv_cache is None:
+            freqs = (self.freq_cos[self._cp_positions], self.freq_sin[self._cp_positions])
+        else:
+            freqs = (self.freq_cos[start : start + seq], self.freq_sin[start : start + seq])
         if kv_cache is not None and x.is_cuda and seq == 1:
             freqs = (*freqs, *self._rope_tables_f32())
         pending = None

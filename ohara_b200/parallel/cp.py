@@ -1,23 +1,32 @@
-"""Context parallelism: causal attention over a sequence sharded in contiguous chunks.
+"""Context parallelism: causal attention over a sequence sharded in a zig-zag over the ranks.
 
-Rank ``r`` of the group holds queries, keys and values of chunk ``r``. Its queries need the keys
-and values of chunks ``0 .. r``. The exchange is overlapped with attention instead of preceding it:
+The sequence is cut into ``2 * world`` blocks of ``h`` tokens; rank ``r`` holds block ``r`` (its
+*early* half) followed by block ``2 * world - 1 - r`` (its *late* half). With contiguous chunks
+the last rank would attend to ``world`` times as many keys as the first; in the zig-zag every rank
+does the same ``2 * world * h^2`` of attention work:
 
-1. every rank copies its ``(K, V)`` chunk into a symmetric staging buffer and publishes a flag;
-2. a side stream pulls the earlier chunks with the copy engines (stream-ordered wait on the
-   owner's flag, peer-to-peer copy) while
-3. the main stream already runs causal flash attention of the local queries against the *local*
-   chunk;
-4. once the remote chunks have landed, a second, non-causal flash attention pass covers them and
-   the two partial results are merged through their log-sum-exp.
+* local pass: the two halves in order are a causal sequence of their own (the early half
+  precedes the late half), so one causal flash attention over the local ``2h`` tokens covers them;
+* *near* pass: all local queries against the early halves of the ranks before this one;
+* *far* pass: the late-half queries against both halves of the ranks after this one.
 
-The backward pass runs the two flash-attention backward kernels with the merged statistics, then
-returns the key/value gradients of remote chunks to their owners with peer-to-peer copies into
+Both remote passes are non-causal (every key in them precedes every query that sees it) and are
+merged into the local result through the log-sum-exp. The exchange is overlapped with attention:
+
+1. every rank copies its ``(K, V)`` tokens into a symmetric staging buffer and publishes a flag;
+2. a side stream pulls what this rank needs with the copy engines (stream-ordered wait on the
+   owner's flag, peer-to-peer copy: half a buffer from earlier ranks, a whole one from later
+   ranks) while
+3. the main stream already runs the local pass;
+4. once the remote tokens have landed, the near and far passes run and are merged.
+
+The backward pass runs the flash-attention backward kernels with the merged statistics, then
+returns the key/value gradients of remote tokens to their owners with peer-to-peer copies into
 per-source slots that the owner sums. Staging and slot buffers are double-buffered and every reuse
 is preceded by the bounded flag barrier of :class:`PeerRuntime`.
 
-Staged layout is ``(T_local, B, 2, kv_heads, D)`` so that consecutive chunks form one sequence with
-a uniform token stride for any batch size.
+Staged layout is ``(T_local, B, 2, kv_heads, D)``: token-major, so the early half of a rank is the
+first half of its buffer and pulled pieces concatenate into one key sequence for any batch size.
 """
 
 from __future__ import annotations
@@ -32,6 +41,44 @@ from ohara_b200.ops._ext import ext
 from ohara_b200.parallel.peer import PeerRuntime, SymmetricBuffer
 
 _KV_SLOT = 0
+
+
+# -- zig-zag sharding (host-side helpers, no device needed) -------------------------------------------
+def zigzag_blocks(rank: int, world: int) -> tuple[int, int]:
+    """Indices of the two sequence blocks (out of ``2 * world``) that ``rank`` holds."""
+    return rank, 2 * world - 1 - rank
+
+
+def shard_sequence(x: Tensor, rank: int, world: int, dim: int = 1) -> Tensor:
+    """This rank's tokens of a full sequence along ``dim``: early block, then late block."""
+    length = x.shape[dim]
+    if length % (2 * world):
+        raise ValueError(f"sequence of {length} does not split into {2 * world} zig-zag blocks")
+    h = length // (2 * world)
+    early, late = zigzag_blocks(rank, world)
+    return torch.cat((x.narrow(dim, early * h, h), x.narrow(dim, late * h, h)), dim=dim)
+
+
+def unshard_sequence(shards: list[Tensor], dim: int = 1) -> Tensor:
+    """Inverse of :func:`shard_sequence` given the shards of all ranks in rank order."""
+    world = len(shards)
+    blocks: list[Tensor | None] = [None] * (2 * world)
+    for rank, shard in enumerate(shards):
+        h = shard.shape[dim] // 2
+        early, late = zigzag_blocks(rank, world)
+        blocks[early] = shard.narrow(dim, 0, h)
+        blocks[late] = shard.narrow(dim, h, h)
+    return torch.cat(blocks, dim=dim)
+
+
+def local_positions(rank: int, world: int, local_length: int, device=None) -> Tensor:
+    """Global positions (int64) of this rank's ``local_length`` tokens."""
+    if local_length % 2:
+        raise ValueError("a zig-zag shard holds an even number of tokens")
+    h = local_length // 2
+    early, late = zigzag_blocks(rank, world)
+    steps = torch.arange(h, device=device)
+    return torch.cat((early * h + steps, late * h + steps))
 
 
 class CPWorkspace:
@@ -57,15 +104,20 @@ class CPWorkspace:
         dist.barrier(group=group)
 
     def exchange_kv(self, kv_local: Tensor):
-        """Stage this rank's ``(T_local, B, 2, Hk, D)`` chunk and start pulling chunks ``0 .. rank-1``.
-        Returns ``(remote, arrived)``: a view ``(rank * T_local, B, 2, Hk, D)`` of the earlier chunks
-        in sequence order (valid until two exchanges later) and the event that marks its arrival."""
+        """Stage this rank's ``(T_local, B, 2, Hk, D)`` tokens and start pulling the early halves of
+        the ranks before this one and everything of the ranks after it. Returns ``(near, far,
+        arrived)``: views ``(rank * T_local / 2, B, 2, Hk, D)`` and ``((world - 1 - rank) * T_local,
+        B, 2, Hk, D)`` (either may be ``None``; valid until two exchanges later) and the event that
+        marks their arrival."""
         if kv_local.numel() > self.chunk_elements:
             raise ValueError("key/value chunk exceeds the workspace")
+        if kv_local.shape[0] % 2:
+            raise ValueError("a zig-zag shard holds an even number of tokens")
         self.runtime.barrier()  # every rank has finished pulling from the buffer about to be reused
         self.kv_epoch += 1
         epoch, index = self.kv_epoch, self.kv_epoch % 2
         count = kv_local.numel()
+        half = count // 2
         self.stage[index].typed(torch.bfloat16)[:count].copy_(kv_local.reshape(-1))
         ext().tp_signal(self.flags.pointers, _KV_SLOT, self.rank, epoch)
         main = torch.cuda.current_stream(self.device)
@@ -73,35 +125,59 @@ class CPWorkspace:
         staged.record(main)
         self.copy_stream.wait_event(staged)
         landing = self.gathered[index]
+        near_elements = self.rank * half
         arrived = torch.cuda.Event()
         with torch.cuda.stream(self.copy_stream):
-            # nearest chunk first: it is the last one the second attention pass reads, but the
-            # first whose owner is likely to be ready
-            for src in range(self.rank - 1, -1, -1):
+            for src in range(self.rank - 1, -1, -1):  # nearest owner first
+                ext().stream_wait_value32(self.flags.pointers[self.rank] + 4 * (_KV_SLOT + src), epoch)
+                remote = self.stage[index].typed(torch.bfloat16, rank=src)[:half]
+                landing[src * half : (src + 1) * half].copy_(remote)
+            for slot, src in enumerate(range(self.rank + 1, self.world)):
                 ext().stream_wait_value32(self.flags.pointers[self.rank] + 4 * (_KV_SLOT + src), epoch)
                 remote = self.stage[index].typed(torch.bfloat16, rank=src)[:count]
-                landing[src * count : (src + 1) * count].copy_(remote)
+                begin = near_elements + slot * count
+                landing[begin : begin + count].copy_(remote)
             arrived.record(self.copy_stream)
-        view = landing[: self.rank * count].view(self.rank * kv_local.shape[0], *kv_local.shape[1:])
-        return view, arrived
+        tokens, tail = kv_local.shape[0], kv_local.shape[1:]
+        near = far = None
+        if self.rank > 0:
+            near = landing[:near_elements].view(self.rank * (tokens // 2), *tail)
+        later = self.world - 1 - self.rank
+        if later > 0:
+            far = landing[near_elements : near_elements + later * count].view(later * tokens, *tail)
+        return near, far, arrived
 
-    def return_kv_grads(self, dkv_remote: Tensor | None, dkv_local: Tensor) -> Tensor:
-        """Send the gradients of chunks ``0 .. rank-1`` (``(rank * T_local, B, 2, Hk, D)``) to their
-        owners and return ``dkv_local`` plus what the later ranks sent for this rank's chunk."""
+    def return_kv_grads(self, dkv_near: Tensor | None, dkv_far: Tensor | None,
+                        dkv_local: Tensor) -> Tensor:
+        """Send the gradients of the near tokens (early halves of ranks ``0 .. rank-1``) and of the
+        far tokens (ranks ``rank+1 ..``) to their owners and return ``dkv_local`` plus what the
+        other ranks sent for this rank's tokens."""
         count = dkv_local.numel()
+        half = count // 2
         self.runtime.barrier()  # owners have finished summing the previous slots
         self.grad_epoch += 1
         buffer = self.grad_slots[self.grad_epoch % 2]
-        if dkv_remote is not None and self.rank > 0:
-            flat = dkv_remote.reshape(-1)
+        mine_at = self.rank * count  # this rank's slot in every owner's buffer
+        if dkv_near is not None:
+            flat = dkv_near.reshape(-1)
             for owner in range(self.rank):
-                slot = buffer.typed(torch.bfloat16, rank=owner)[self.rank * count : (self.rank + 1) * count]
-                slot.copy_(flat[owner * count : (owner + 1) * count])  # peer-to-peer copy
+                slot = buffer.typed(torch.bfloat16, rank=owner)[mine_at : mine_at + half]
+                slot.copy_(flat[owner * half : (owner + 1) * half])  # peer-to-peer copy
+        if dkv_far is not None:
+            flat = dkv_far.reshape(-1)
+            for index, owner in enumerate(range(self.rank + 1, self.world)):
+                slot = buffer.typed(torch.bfloat16, rank=owner)[mine_at : mine_at + count]
+                slot.copy_(flat[index * count : (index + 1) * count])
         self.runtime.barrier()  # all gradients have landed
-        total = dkv_local.float()
+        total = dkv_local.float().contiguous()
+        flat_total = total.view(-1)
         mine = buffer.typed(torch.bfloat16)
-        for src in range(self.rank + 1, self.world):
-            total += mine[src * count : (src + 1) * count].view_as(dkv_local).float()
+        for src in range(self.world):
+            if src == self.rank:
+                continue
+            # a later rank saw only this rank's early half, an earlier rank saw both halves
+            span = half if src > self.rank else count
+            flat_total[:span] += mine[src * count : src * count + span].float()
         return total.to(dkv_local.dtype)
 
 
@@ -130,42 +206,63 @@ def _merge(out_a: Tensor, lse_a: Tensor, out_b: Tensor, lse_b: Tensor):
     return out, lse
 
 
+def _split_kv(staged: Tensor) -> tuple[Tensor, Tensor]:
+    """``(T, B, 2, Hk, D)`` staged tokens -> strided ``(B, T, Hk, D)`` views of keys and values."""
+    return staged[:, :, 0].transpose(0, 1), staged[:, :, 1].transpose(0, 1)
+
+
+def _stack_kv(dk: Tensor, dv: Tensor) -> Tensor:
+    return torch.stack((dk, dv), dim=2).transpose(0, 1).contiguous()  # (T, B, 2, Hk, D)
+
+
 class _ContextParallelAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q: Tensor, k: Tensor, v: Tensor, workspace: CPWorkspace, scale: float):
         C = ext()
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        kv = torch.stack((k, v), dim=2).transpose(0, 1).contiguous()  # (T_local, B, 2, Hk, D)
-        remote, arrived = workspace.exchange_kv(kv)
+        h = q.shape[1] // 2
+        near, far, arrived = workspace.exchange_kv(_stack_kv(k, v))
         out, lse = C.flash_attn_fwd(q, k, v, True, scale)  # overlaps the copies
-        k_far = v_far = None
-        if workspace.rank > 0:
+        k_near = v_near = k_far = v_far = None
+        if near is not None or far is not None:
             torch.cuda.current_stream(q.device).wait_event(arrived)
-            saved = remote.clone()  # the landing buffer is recycled; backward needs these chunks
-            k_far = saved[:, :, 0].transpose(0, 1)  # (B, rank * T_local, Hk, D), strided view
-            v_far = saved[:, :, 1].transpose(0, 1)
-            out_far, lse_far = C.flash_attn_fwd(q, k_far, v_far, False, scale)
-            out, lse = _merge(out, lse, out_far, lse_far)
-            out = out.contiguous()
-            lse = lse.contiguous()
-        ctx.save_for_backward(q, k, v, out, lse, k_far, v_far)
+        if near is not None:
+            # the landing buffer is recycled; backward needs these tokens
+            k_near, v_near = _split_kv(near.clone())
+            out_near, lse_near = C.flash_attn_fwd(q, k_near, v_near, False, scale)
+            out, lse = _merge(out, lse, out_near, lse_near)
+        if far is not None:
+            k_far, v_far = _split_kv(far.clone())
+            out_far, lse_far = C.flash_attn_fwd(q[:, h:], k_far, v_far, False, scale)
+            out_late, lse_late = _merge(out[:, h:], lse[:, :, h:], out_far, lse_far)
+            out = torch.cat((out[:, :h], out_late), dim=1)
+            lse = torch.cat((lse[:, :, :h], lse_late), dim=2)
+        out, lse = out.contiguous(), lse.contiguous()
+        ctx.save_for_backward(q, k, v, out, lse, k_near, v_near, k_far, v_far)
         ctx.workspace, ctx.scale = workspace, scale
         return out
 
     @staticmethod
     def backward(ctx, dout: Tensor):
         C = ext()
-        q, k, v, out, lse, k_far, v_far = ctx.saved_tensors
+        q, k, v, out, lse, k_near, v_near, k_far, v_far = ctx.saved_tensors
         ws = ctx.workspace
+        h = q.shape[1] // 2
         dout = dout.contiguous()
         dq, dk, dv = C.flash_attn_bwd(dout, q, k, v, out, lse, True, ctx.scale)
-        dkv_far = None
+        dkv_near = dkv_far = None
+        if k_near is not None:
+            dq_near, dk_near, dv_near = C.flash_attn_bwd(dout, q, k_near, v_near, out, lse, False,
+                                                         ctx.scale)
+            dq = dq + dq_near
+            dkv_near = _stack_kv(dk_near, dv_near)
         if k_far is not None:
-            dq_far, dk_far, dv_far = C.flash_attn_bwd(dout, q, k_far, v_far, out, lse, False, ctx.scale)
-            dq = dq + dq_far
-            dkv_far = torch.stack((dk_far, dv_far), dim=2).transpose(0, 1).contiguous()
-        dkv_local = torch.stack((dk, dv), dim=2).transpose(0, 1).contiguous()
-        dkv = ws.return_kv_grads(dkv_far, dkv_local)  # (T_local, B, 2, Hk, D)
+            dq_far, dk_far, dv_far = C.flash_attn_bwd(
+                dout[:, h:], q[:, h:], k_far, v_far, out[:, h:].contiguous(),
+                lse[:, :, h:].contiguous(), False, ctx.scale)
+            dq = torch.cat((dq[:, :h], dq[:, h:] + dq_far), dim=1)
+            dkv_far = _stack_kv(dk_far, dv_far)
+        dkv = ws.return_kv_grads(dkv_near, dkv_far, _stack_kv(dk, dv))  # (T_local, B, 2, Hk, D)
         dk_total = dkv[:, :, 0].transpose(0, 1).contiguous()
         dv_total = dkv[:, :, 1].transpose(0, 1).contiguous()
         return dq, dk_total, dv_total, None, None
@@ -173,8 +270,9 @@ class _ContextParallelAttention(torch.autograd.Function):
 
 def context_parallel_attention(q: Tensor, k: Tensor, v: Tensor, workspace: CPWorkspace,
                                scale: float | None = None) -> Tensor:
-    """Causal attention for this rank's chunk: ``q (B, T_local, H, D)``, ``k/v (B, T_local, Hk, D)``
-    bf16, already rotated with their global positions. Returns ``(B, T_local, H, D)``."""
+    """Causal attention for this rank's zig-zag shard (:func:`shard_sequence`): ``q (B, T_local, H,
+    D)``, ``k/v (B, T_local, Hk, D)`` bf16, already rotated with their global positions
+    (:func:`local_positions`). Returns ``(B, T_local, H, D)``."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if isinstance(workspace, LazyCPWorkspace):
         workspace = workspace.materialize(2 * k.numel())

@@ -412,11 +412,10 @@ class OharaEngine:
             return batch
         if isinstance(batch, torch.Tensor):
             if by_sequence and batch.dim() >= 2:
-                cp, rank = self.topology.cp, self.topology.cp_rank
-                if batch.shape[1] % cp:
-                    raise ValueError(f"sequence of {batch.shape[1]} does not split over cp={cp}")
-                per = batch.shape[1] // cp
-                batch = batch[:, rank * per : (rank + 1) * per]
+                from ohara_b200.parallel.cp import shard_sequence
+
+                # zig-zag: an early and a late block per rank, equal attention work on every rank
+                batch = shard_sequence(batch, self.topology.cp_rank, self.topology.cp, dim=1)
             if not by_batch or batch.dim() == 0:
                 return batch
             tp, rank = self.topology.tp, self.topology.tp_rank

@@ -1,5 +1,5 @@
-"""Context-parallel attention on two GPUs against single-device causal attention over the whole
-sequence, forward and backward."""
+"""Context-parallel attention (zig-zag sharding) on two GPUs against single-device causal attention
+over the whole sequence, forward and backward."""
 
 import os
 import subprocess
@@ -20,7 +20,7 @@ def test_context_parallel_attention_matches_full_sequence(tmp_path):
         import torch, torch.distributed as dist
         from ohara_b200 import ops
         from ohara_b200.ops.attention import attention_reference
-        from ohara_b200.parallel.cp import CPWorkspace, context_parallel_attention
+        from ohara_b200.parallel.cp import CPWorkspace, context_parallel_attention, shard_sequence
 
         dist.init_process_group("nccl")
         rank, world = dist.get_rank(), dist.get_world_size()
@@ -33,10 +33,10 @@ def test_context_parallel_attention_matches_full_sequence(tmp_path):
             k = torch.randn(batch, world * chunk, kv_heads, dim, device="cuda").bfloat16()
             v = torch.randn(batch, world * chunk, kv_heads, dim, device="cuda").bfloat16()
             upstream = torch.randn(batch, world * chunk, heads, dim, device="cuda").bfloat16()
-            rows = slice(rank * chunk, (rank + 1) * chunk)
-            ql, kl, vl = (t[:, rows].clone().requires_grad_() for t in (q, k, v))
+            mine = lambda t: shard_sequence(t, rank, world)  # early block + late block of the zig-zag
+            ql, kl, vl = (mine(t).clone().requires_grad_() for t in (q, k, v))
             out = context_parallel_attention(ql, kl, vl, workspace)
-            out.backward(upstream[:, rows])
+            out.backward(mine(upstream))
             torch.cuda.synchronize(); ops.check_status()
 
             qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
@@ -44,10 +44,10 @@ def test_context_parallel_attention_matches_full_sequence(tmp_path):
             ref.backward(upstream.float())
             def close(a, b):
                 return (a.float() - b.float()).abs().max().item() <= 2e-2 * (b.float().abs().max().item() + 1e-6)
-            assert close(out, ref[:, rows]), "forward"
-            assert close(ql.grad, qr.grad[:, rows]), "dq"
-            assert close(kl.grad, kr.grad[:, rows]), "dk"
-            assert close(vl.grad, vr.grad[:, rows]), "dv"
+            assert close(out, mine(ref)), "forward"
+            assert close(ql.grad, mine(qr.grad)), "dq"
+            assert close(kl.grad, mine(kr.grad)), "dk"
+            assert close(vl.grad, mine(vr.grad)), "dv"
         if rank == 0:
             print("CP_OK")
         dist.destroy_process_group()
@@ -64,7 +64,7 @@ def test_context_parallel_attention_matches_full_sequence(tmp_path):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_engine_context_parallel_llama_matches_single_device(tmp_path):
-    """cp=2 through the engine: each rank runs half of every sequence; loss and gradients of a
+    """cp=2 through the engine: each rank runs its zig-zag half of every sequence; loss and gradients of a
     training step must match the model on whole sequences."""
     script = """
         import torch, torch.distributed as dist
