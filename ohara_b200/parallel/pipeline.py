@@ -151,3 +151,74 @@ def split_sequential(layers: Sequence[nn.Module], world: int, rank: int) -> nn.S
     begin = rank * base + min(rank, extra)
     end = begin + base + (1 if rank < extra else 0)
     return nn.Sequential(*layers[begin:end])
+
+
+def stage_bounds(num_layers: int, world: int, rank: int) -> tuple[int, int]:
+    """``[begin, end)`` of the transformer blocks owned by pipeline rank ``rank`` (the same
+    contiguous, balanced split as :func:`split_sequential`)."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError("bad pipeline rank / world")
+    if num_layers < world:
+        raise ValueError("fewer layers than pipeline stages")
+    base, extra = divmod(num_layers, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+class LlamaStage(nn.Module):
+    """One pipeline stage of a :class:`ohara_b200.models.llama.Llama`.
+
+    The stage keeps only its own sub-modules of ``model``: the token embedding on the first rank,
+    a contiguous run of transformer blocks, the final norm and the output projection on the last
+    rank (plus the rotary tables, which every stage needs). The first stage maps token ids
+    ``(B, T)`` to hidden states, the others map hidden states to hidden states, and the last one
+    returns logits - or, given ``targets``, the summed cross-entropy through the fused
+    projection + loss kernel, so that no logits tensor is materialised:
+
+        stage = LlamaStage(Llama(cfg), world, rank)
+        runner = PipelineRunner(stage, loss_fn=stage.loss, activation_shape=(B, T, hidden), ...)
+
+    Tied input / output embeddings would live on two different ranks and are rejected.
+    """
+
+    def __init__(self, model: nn.Module, world: int, rank: int) -> None:
+        super().__init__()
+        cfg = model.config
+        if world > 1 and model.vocab_proj.weight is model.token_emb.weight:
+            raise ValueError("pipeline stages cannot share tied embeddings: use weight_tying=False")
+        begin, end = stage_bounds(len(model.layers), world, rank)
+        self.config = cfg
+        self.is_first, self.is_last = rank == 0, rank == world - 1
+        self.layer_range = (begin, end)
+        self.token_emb = model.token_emb if self.is_first else None
+        self.layers = nn.ModuleList(list(model.layers)[begin:end])
+        self.norm = model.norm if self.is_last else None
+        self.vocab_proj = model.vocab_proj if self.is_last else None
+        self.register_buffer("freq_cos", model.freq_cos, persistent=False)
+        self.register_buffer("freq_sin", model.freq_sin, persistent=False)
+
+    def hidden(self, x: Tensor) -> Tensor:
+        """Hidden states leaving this stage (after the final norm on the last stage)."""
+        from ohara_b200 import ops
+
+        h = ops.embedding(x, self.token_emb.weight) if self.is_first else x
+        seq = h.size(1)
+        if seq > self.config.max_sequence_length:
+            raise ValueError("input exceeds max_sequence_length")
+        freqs = (self.freq_cos[:seq], self.freq_sin[:seq])
+        pending = None  # residual branch output not yet added: fused into the next norm
+        for layer in self.layers:
+            h, pending = layer.forward_deferred(h, pending, freqs, None, None)
+        if self.is_last:
+            return ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[0]
+        return h if pending is None else h + pending
+
+    def forward(self, x: Tensor) -> Tensor:
+        h = self.hidden(x)
+        return self.vocab_proj(h) if self.is_last else h
+
+    def loss(self, logits: Tensor, targets: Tensor, ignore_index: int = -1) -> Tensor:
+        """Mean cross-entropy of the last stage's logits (``loss_fn`` of the runner)."""
+        return torch.nn.functional.cross_entropy(
+            logits.float().reshape(-1, logits.size(-1)), targets.reshape(-1),
+            ignore_index=ignore_index)
