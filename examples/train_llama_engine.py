@@ -135,6 +135,9 @@ def parse_args() -> argparse.Namespace:
                      help="seconds between heartbeats over the rendezvous store (0 = off); a rank "
                           "whose heartbeat stops is reported before the next step is launched")
     run.add_argument("--heartbeat-timeout", type=float, default=30.0)
+    run.add_argument("--profile-sections", action="store_true",
+                     help="time the phases of every step on the device (CUDA events, max over "
+                          "ranks) and print the totals at the end; OHARA_NVTX=1 adds NVTX ranges")
     run.add_argument("--step-timeout", type=float, default=0.0,
                      help="abort (exit code 75) when one training step takes longer than this "
                           "many seconds (0 = off), so that an elastic launcher can restart the job")
@@ -389,6 +392,7 @@ def run() -> None:
         grad_clip_norm=args.grad_clip_norm or None, timing_warmup_steps=10,
         checkpoint_path=args.checkpoint_path, token_bytes=token_bytes,
         apply_router_balancing=apply_qb_update if balancing else None,
+        profile_sections=args.profile_sections,
     )
     start_iter = resume(args, engine, model, optimizer, trainer, train_ds) if args.resume else 0
 
@@ -406,6 +410,11 @@ def run() -> None:
     started = time.perf_counter()
     trainer.train(start_iter=start_iter)
     wall_time = time.perf_counter() - started
+    sections = trainer.section_times()  # a collective: every rank takes part
+    if sections and engine.is_global_zero:
+        print("device time per phase (max over ranks): " + ", ".join(
+            f"{name}={entry['ms'] / max(entry['calls'], 1):.2f} ms x {entry['calls']}"
+            for name, entry in sections.items()))
     final = trainer.evaluate(trainer.val_dataloader, args.eval_batches)
     if engine.is_global_zero:
         line = (f"final val_loss={final['loss']:.4f} val_ppl={final['ppl']:.2f} "

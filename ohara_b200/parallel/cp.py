@@ -39,6 +39,7 @@ from torch import Tensor
 
 from ohara_b200.ops._ext import ext
 from ohara_b200.parallel.peer import PeerRuntime, SymmetricBuffer
+from ohara_b200.utils.profiling import nvtx_annotate
 
 _KV_SLOT = 0
 
@@ -103,6 +104,7 @@ class CPWorkspace:
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
+    @nvtx_annotate("cp.exchange_kv")
     def exchange_kv(self, kv_local: Tensor):
         """Stage this rank's ``(T_local, B, 2, Hk, D)`` tokens and start pulling the early halves of
         the ranks before this one and everything of the ranks after it. Returns ``(near, far,
@@ -147,6 +149,7 @@ class CPWorkspace:
             far = landing[near_elements : near_elements + later * count].view(later * tokens, *tail)
         return near, far, arrived
 
+    @nvtx_annotate("cp.return_kv_grads")
     def return_kv_grads(self, dkv_near: Tensor | None, dkv_far: Tensor | None,
                         dkv_local: Tensor) -> Tensor:
         """Send the gradients of the near tokens (early halves of ranks ``0 .. rank-1``) and of the

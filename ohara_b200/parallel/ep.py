@@ -27,6 +27,7 @@ from ohara_b200.ops._ext import ext
 from ohara_b200.parallel.peer import PeerRuntime, SymmetricBuffer
 
 from ohara_b200.ops.moe import TILE  # rows every expert segment is padded to (a GEMM pair tile)
+from ohara_b200.utils.profiling import nvtx_annotate
 
 
 @dataclass
@@ -81,6 +82,7 @@ class EPWorkspace:
         return DispatchPlan(*parts, top_k=indices.shape[1])
 
     # -- data movement -------------------------------------------------------------------------------
+    @nvtx_annotate("ep.dispatch")
     def push_rows(self, rows: Tensor, plan: DispatchPlan, scale: Tensor | None = None) -> Tensor:
         """Send row ``t`` of ``rows (N, d)`` to the owners of its ``k`` experts (times ``scale``);
         returns this rank's padded ``(capacity_rows, d)`` buffer of received rows."""
@@ -93,6 +95,7 @@ class EPWorkspace:
         ext().ep_zero_fill(plan.fill, landed, d, self.capacity_rows)
         return landed.clone()
 
+    @nvtx_annotate("ep.combine")
     def pull_rows(self, padded: Tensor, plan: DispatchPlan, scale: Tensor | None = None,
                   other: Tensor | None = None, want_out: bool = True):
         """Adjoint of ``push_rows``: ``out[t] = sum_i scale[t, i] * padded_owner[row(t, i)]`` read

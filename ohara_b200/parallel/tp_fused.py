@@ -30,6 +30,7 @@ from torch import Tensor
 
 from ohara_b200.ops._ext import ext
 from ohara_b200.parallel.peer import SymmetricBuffer
+from ohara_b200.utils.profiling import nvtx_annotate
 
 _AG_SLOT = 0   # flag slots [0, world): "my staged rows for epoch e are complete"
 _RS_SLOT = 16  # flag slots [16, 16 + world): "my pushes for epoch e are complete"
@@ -92,6 +93,7 @@ class TPWorkspace:
         return self.gathered[index][: self.world * rows * width].view(self.world, rows, width)
 
     # -- all-gather side ----------------------------------------------------------------------------
+    @nvtx_annotate("tp.stage_rows")
     def stage(self, x_local: Tensor) -> StagedRows:
         rows, width = x_local.shape
         if rows % 128 or rows * width > self.capacity:
@@ -125,6 +127,7 @@ class TPWorkspace:
                 arrived.append(event)
         return StagedRows(index, epoch, rows, width, arrived)
 
+    @nvtx_annotate("tp.all_gather_gemm")
     def gemm_from(self, staged: StagedRows, weight16: Tensor, b_mn: bool, out_features: int) -> Tensor:
         """``all_gather(staged) @ op(weight16)``: ``(world * rows, out_features)`` bf16."""
         key = (staged.buffer, staged.rows, staged.width)
@@ -145,6 +148,7 @@ class TPWorkspace:
                             staged.epoch, self.rank, self.world, self.wait_limit_s)
         return out
 
+    @nvtx_annotate("tp.all_gather")
     def gather_from(self, staged: StagedRows) -> Tensor:
         """The gathered ``(world * rows, width)`` tensor itself (operand of a weight gradient).
         It aliases a workspace buffer that is recycled two stagings later: consume it at once."""
@@ -154,6 +158,7 @@ class TPWorkspace:
         return blocks.view(self.world * staged.rows, staged.width)
 
     # -- reduce-scatter side ------------------------------------------------------------------------
+    @nvtx_annotate("tp.gemm_reduce_scatter")
     def gemm_reduce_scatter(self, a16: Tensor, weight16: Tensor, b_mn: bool, out_features: int,
                             residual: Tensor | None = None) -> Tensor:
         """``reduce_scatter(a16 @ op(weight16))`` over row blocks: ``(rows / world, out_features)``."""

@@ -39,6 +39,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 from torch.optim import Optimizer
+from ohara_b200.utils.profiling import nvtx_annotate
 
 ALIGN = 128  # elements; keeps every region 256-byte aligned in bf16
 
@@ -269,6 +270,7 @@ class ShardedOptimizer(Optimizer):
             torch._foreach_copy_(dst, src)
 
     @torch.no_grad()
+    @nvtx_annotate("zero.reduce_scatter_gradients")
     def reduce_gradients(self) -> None:
         """Pack local gradients, reduce-scatter them and leave the mean in ``grad_local``."""
         if self._reduced:
@@ -315,6 +317,7 @@ class ShardedOptimizer(Optimizer):
                     target[key] = value
 
     @torch.no_grad()
+    @nvtx_annotate("zero.step")
     def step(self, closure=None):
         loss = None
         if closure is not None:
@@ -358,6 +361,7 @@ class ShardedOptimizer(Optimizer):
         torch._foreach_copy_(dst, src)
         self._bind_shadows()
 
+    @nvtx_annotate("zero.all_gather_weights")
     def _all_gather_flat(self, out: Tensor, mine: Tensor) -> None:
         if dist.get_backend(self.group) == "gloo":
             parts = [out[r * self.region : (r + 1) * self.region] for r in range(self.world)]

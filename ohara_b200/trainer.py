@@ -33,6 +33,7 @@ import torch.nn.functional as F
 import torch.optim as optim
 from torch.utils.data import DataLoader
 
+from ohara_b200.utils.profiling import DeviceTimer, nvtx_range
 from ohara_b200.utils.tools import BetterCycle
 
 
@@ -128,6 +129,7 @@ class Trainer:
         token_bytes: torch.Tensor | None = None,
         apply_router_balancing: Callable[[nn.Module], None] | None = None,
         fused_loss: bool | None = None,
+        profile_sections: bool = False,
     ):
         if micro_batch < 1:
             raise ValueError("micro_batch must be at least 1")
@@ -167,6 +169,11 @@ class Trainer:
         self.cudagraph_mark_step_begin = cudagraph_mark_step_begin
         self.checkpoint_path = Path(checkpoint_path)
         self.apply_router_balancing = apply_router_balancing
+        # Device time per phase of the step (CUDA events, max over ranks in ``section_times``);
+        # without it the phases are still NVTX ranges when those are switched on.
+        self.timer: DeviceTimer | None = None
+        if profile_sections:
+            self.timer = DeviceTimer(getattr(engine, "device", None))
         self.token_bytes = self.engine.to_device(token_bytes) if token_bytes is not None else None
         self.iter_loss_history: deque[float] = deque(maxlen=iter_loss_window)
         self.total_training_time_s = 0.0
@@ -401,6 +408,19 @@ class Trainer:
                         group[key] = float(hparams[key])
         return lr
 
+    def _section(self, name: str):
+        return self.timer.section(name) if self.timer is not None else nvtx_range(name)
+
+    def section_times(self, reset: bool = True) -> dict[str, dict[str, float]]:
+        """Milliseconds per phase (``forward_backward``, ``clip``, ``optimizer``) accumulated since
+        the last reset, the maximum over ranks; empty unless ``profile_sections`` was set."""
+        if self.timer is None:
+            return {}
+        summary = self.timer.summary()
+        if reset:
+            self.timer.reset()
+        return summary
+
     def _micro_step_loss(self, data: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
         """Σ cross-entropy over the supervised targets of one micro-batch (fp32 scalar)."""
         with self.engine.autocast_context():
@@ -428,7 +448,7 @@ class Trainer:
                 self.engine.no_backward_sync(self.model, enabled=micro_step < self.micro_batch - 1)
                 if self.micro_batch > 1 else nullcontext()
             )
-            with sync:
+            with sync, self._section("train.forward_backward"):
                 self._maybe_cudagraph_step_begin()
                 loss_sum = self._micro_step_loss(data, target)
                 loss_sum_total += loss_sum.detach().float()
@@ -441,16 +461,18 @@ class Trainer:
         if not math.isfinite(loss_host):
             raise RuntimeError(f"Non-finite loss detected at iter={idx}: {loss_host}")
         if self.grad_clip_norm is not None and self.grad_clip_norm > 0:
-            grad_norm = self.engine.clip_gradients(self.model, self.optimizer,
-                                                   max_norm=float(self.grad_clip_norm))
+            with self._section("train.clip"):
+                grad_norm = self.engine.clip_gradients(self.model, self.optimizer,
+                                                       max_norm=float(self.grad_clip_norm))
             if not torch.isfinite(grad_norm):
                 raise RuntimeError(
                     f"Non-finite gradient norm detected at iter={idx}: {float(grad_norm)}"
                 )
-        self.engine.optimizer_step(self.optimizer)
-        self.optimizer.zero_grad(set_to_none=True)
-        if self.apply_router_balancing is not None:
-            self.apply_router_balancing(self.model)
+        with self._section("train.optimizer"):
+            self.engine.optimizer_step(self.optimizer)
+            self.optimizer.zero_grad(set_to_none=True)
+            if self.apply_router_balancing is not None:
+                self.apply_router_balancing(self.model)
         step_loss = loss_host / valid_host
         self.last_step_loss = step_loss
         return step_loss, lr

@@ -217,3 +217,14 @@ def test_cosine_scheduler_edges():
             CosineScheduler(**{**dict(learning_rate=1.0, min_lr=0.1, warmup_iters=10, max_iters=110), **bad})
     with pytest.raises(ValueError):
         sched(-1)
+
+
+def test_profile_sections_report_every_phase_of_the_step(tmp_path):
+    trainer, _ = make_trainer(tmp_path, profile_sections=True, grad_clip_norm=1.0, max_iters=2)
+    trainer.train()
+    times = trainer.section_times()
+    assert set(times) == {"train.forward_backward", "train.clip", "train.optimizer"}
+    assert all(entry["calls"] == 2 and entry["ms"] >= 0.0 for entry in times.values())
+    assert trainer.section_times() == {}  # reset by the previous call
+    plain, _ = make_trainer(tmp_path)
+    assert plain.section_times() == {}
