@@ -44,6 +44,25 @@ from ohara_b200.utils.profiling import nvtx_annotate
 _KV_SLOT = 0
 
 
+# -- buffer arithmetic of the exchange (pure functions, checked on CPU) ---------------------------------
+def landing_layout(rank: int, world: int, count: int):
+    """Where the pulled key/value tokens land in this rank's gather buffer. ``count`` = elements of
+    one rank's staged tokens. Returns ``(near, far)``: lists of ``(source rank, offset, elements)``;
+    a near piece is the first half of the source's buffer, a far piece the whole of it. Near pieces
+    are contiguous from 0 in source order, far pieces follow them in source order."""
+    half = count // 2
+    near = [(src, src * half, half) for src in range(rank)]
+    base = rank * half
+    far = [(src, base + slot * count, count) for slot, src in enumerate(range(rank + 1, world))]
+    return near, far
+
+
+def gradient_span(owner: int, source: int, count: int) -> int:
+    """Elements of key/value gradient that ``source`` returns to ``owner``: a later rank saw only
+    the owner's early half, an earlier rank saw both halves."""
+    return count // 2 if source > owner else count
+
+
 # -- zig-zag sharding (host-side helpers, no device needed) -------------------------------------------
 def zigzag_blocks(rank: int, world: int) -> tuple[int, int]:
     """Indices of the two sequence blocks (out of ``2 * world``) that ``rank`` holds."""
@@ -128,17 +147,13 @@ class CPWorkspace:
         self.copy_stream.wait_event(staged)
         landing = self.gathered[index]
         near_elements = self.rank * half
+        near_pieces, far_pieces = landing_layout(self.rank, self.world, count)
         arrived = torch.cuda.Event()
         with torch.cuda.stream(self.copy_stream):
-            for src in range(self.rank - 1, -1, -1):  # nearest owner first
+            for src, begin, elements in near_pieces[::-1] + far_pieces:  # nearest earlier owner first
                 ext().stream_wait_value32(self.flags.pointers[self.rank] + 4 * (_KV_SLOT + src), epoch)
-                remote = self.stage[index].typed(torch.bfloat16, rank=src)[:half]
-                landing[src * half : (src + 1) * half].copy_(remote)
-            for slot, src in enumerate(range(self.rank + 1, self.world)):
-                ext().stream_wait_value32(self.flags.pointers[self.rank] + 4 * (_KV_SLOT + src), epoch)
-                remote = self.stage[index].typed(torch.bfloat16, rank=src)[:count]
-                begin = near_elements + slot * count
-                landing[begin : begin + count].copy_(remote)
+                remote = self.stage[index].typed(torch.bfloat16, rank=src)[:elements]
+                landing[begin : begin + elements].copy_(remote)
             arrived.record(self.copy_stream)
         tokens, tail = kv_local.shape[0], kv_local.shape[1:]
         near = far = None
@@ -178,8 +193,7 @@ class CPWorkspace:
         for src in range(self.world):
             if src == self.rank:
                 continue
-            # a later rank saw only this rank's early half, an earlier rank saw both halves
-            span = half if src > self.rank else count
+            span = gradient_span(self.rank, src, count)
             flat_total[:span] += mine[src * count : src * count + span].float()
         return total.to(dkv_local.dtype)
 

@@ -71,3 +71,24 @@ def test_three_passes_reproduce_causal_attention_with_equal_work(world):
         torch.testing.assert_close(out, shard_sequence(reference, rank, world), rtol=1e-5, atol=1e-5)  # the merge works in fp32
         work.append(pairs)
     assert max(work) - min(work) == 0, work  # every rank scores the same number of pairs
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+def test_landing_layout_and_gradient_spans_are_consistent(world):
+    from ohara_b200.parallel.cp import gradient_span, landing_layout
+
+    count = 64
+    for rank in range(world):
+        near, far = landing_layout(rank, world, count)
+        assert [src for src, _, _ in near] == list(range(rank))
+        assert [src for src, _, _ in far] == list(range(rank + 1, world))
+        cursor = 0
+        for _, offset, elements in near + far:  # pieces tile the buffer without gaps or overlap
+            assert offset == cursor
+            cursor += elements
+        assert cursor <= world * count  # fits the gather buffer of world * count elements
+        assert all(elements == count // 2 for _, _, elements in near)
+        assert all(elements == count for _, _, elements in far)
+        # what this rank pulled from a source is what it later returns gradients for
+        for src, _, elements in near + far:
+            assert gradient_span(src, rank, count) == elements
