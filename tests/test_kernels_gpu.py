@@ -338,7 +338,8 @@ def test_fused_muon_refreshes_the_bf16_compute_copy():
         assert torch.equal(fresh, p.detach().to(torch.bfloat16)) and not torch.equal(fresh, old)
 
 
-@pytest.mark.parametrize("shape", [(3, 37, 8, 4), (2, 130, 24), (2, 5, 7), (1, 1, 4), (2, 64, 1536, 16)])
+@pytest.mark.parametrize("shape", [(3, 37, 8, 4), (2, 130, 24), (2, 5, 7), (1, 1, 4), (2, 64, 1536, 16),
+                                   (4, 21, 32768), (5, 19, 32771)])
 def test_pscan_kernel_matches_sequential_recurrence(shape):
     """One-pass scan kernels (vector and scalar channel paths, unrolled body and tail) against the
     step-by-step recurrence in fp64, values and both gradients."""
