@@ -16,9 +16,10 @@ ROOT = Path(__file__).resolve().parent.parent
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_context_parallel_attention_matches_full_sequence(tmp_path):
-    # OHARA_CP_TEST_RANKS=4 (on four or more GPUs) makes the middle ranks run both remote passes
-    # (earlier and later owners); the default of two ranks runs one of them on each rank.
-    ranks = min(int(os.environ.get("OHARA_CP_TEST_RANKS", "2")), torch.cuda.device_count())
+    # On four or more GPUs the middle ranks run both remote passes (earlier and later owners);
+    # with two ranks each rank runs one of them. OHARA_CP_TEST_RANKS overrides the count.
+    default = 4 if torch.cuda.device_count() >= 4 else 2
+    ranks = min(int(os.environ.get("OHARA_CP_TEST_RANKS", default)), torch.cuda.device_count())
     script = """
         import torch, torch.distributed as dist
         from ohara_b200 import ops
