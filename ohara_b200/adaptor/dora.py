@@ -46,7 +46,7 @@ class DoRALinear(LowRankAdapter):
     def merge(self) -> None:
         if not self.merged and self.rank > 0:
             weight = self.linear.weight + self.delta()
-            self.linear.weight.data = weight * self._row_scale(weight)
+            self.linear.weight.copy_(weight * self._row_scale(weight))  # in place: bumps the version
             self.merged = True
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

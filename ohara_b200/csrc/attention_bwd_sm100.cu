@@ -581,12 +581,7 @@ void launch_bwd(const void* q, const void* k, const void* v, const void* d_o, fl
   p.dq = dq;
   p.status = status_ptr();
   auto kernel = flash_bwd_kernel<D>;
-  static bool configured = false;
-  if (!configured) {
-    OB_CUDA_CHECK(
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    configured = true;
-  }
+  ensure_dynamic_smem((const void*)kernel, L::kTotal);
   const int k_tiles = (S + kKeys - 1) / kKeys;
   const long long grid = (long long)k_tiles * B * Hk;
   kernel<<<(unsigned)grid, kThreads, L::kTotal, stream>>>(tQ, tK, tV, tdO, tdK, tdV, p);
@@ -649,7 +644,6 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoallocDqBytes
 
 std::mutex g_noalloc_mutex;
 unsigned char* g_noalloc_base[64] = {nullptr};  // device address of the array, per device
-bool g_noalloc_configured[64][2] = {{false}};   // kernel attribute set, per device and head_dim
 
 int noalloc_fail(int code, const char* message, char* err, size_t err_len) {
   if (err != nullptr && err_len > 0) {
@@ -663,7 +657,7 @@ template <int D>
 cudaError_t noalloc_launch(const void* q, const void* k, const void* v, const void* d_o, float* dq32,
                            void* dk, void* dv, const float* lse, const float* delta, int B, int T,
                            int S, int H, int Hk, bool causal, float scale, int* status,
-                           bool configure, cudaStream_t stream) {
+                           cudaStream_t stream) {
   using L = BwdSmem<D>;
   CUtensorMap tQ, tK, tV, tdO, tdK, tdV;
   auto make4 = [&](CUtensorMap* tm, const void* base, TmapDtype dt, int heads, int len,
@@ -694,11 +688,9 @@ cudaError_t noalloc_launch(const void* q, const void* k, const void* v, const vo
   p.dq = dq32;
   p.status = status;
   auto kernel = flash_bwd_kernel<D>;
-  if (configure) {
-    cudaError_t rc =
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
-    if (rc != cudaSuccess) return rc;
-  }
+  // Recorded per device only once the driver has accepted it, so a failed first call is retried.
+  cudaError_t rc = try_ensure_dynamic_smem((const void*)kernel, L::kTotal);
+  if (rc != cudaSuccess) return rc;
   const int k_tiles = (S + kKeys - 1) / kKeys;
   const long long grid = (long long)k_tiles * B * Hk;
   kernel<<<(unsigned)grid, kThreads, L::kTotal, stream>>>(tQ, tK, tV, tdO, tdK, tdV, p);
@@ -740,7 +732,6 @@ extern "C" int ob_flash_attn_bwd_noalloc(const void* q, const void* k, const voi
 
   // One-time set-up for this device: resolve the device address of the static array.
   unsigned char* base = nullptr;
-  bool configure = false;
   {
     std::lock_guard<std::mutex> lock(g_noalloc_mutex);
     if (g_noalloc_base[dev] == nullptr) {
@@ -754,9 +745,6 @@ extern "C" int ob_flash_attn_bwd_noalloc(const void* q, const void* k, const voi
       g_noalloc_base[dev] = static_cast<unsigned char*>(ptr);
     }
     base = g_noalloc_base[dev];
-    const int slot = D == 128 ? 1 : 0;
-    configure = !g_noalloc_configured[dev][slot];
-    g_noalloc_configured[dev][slot] = true;
   }
   float* dq32 = reinterpret_cast<float*>(base);
   float* delta = reinterpret_cast<float*>(base + kNoallocDqBytes);
@@ -767,9 +755,9 @@ extern "C" int ob_flash_attn_bwd_noalloc(const void* q, const void* k, const voi
     if (rc != cudaSuccess) throw std::runtime_error(cudaGetErrorString(rc));
     attn_delta(out, dout, delta, B, T, H, D, (int64_t)H * D, (int64_t)T * H * D, stream);
     rc = (D == 128) ? noalloc_launch<128>(q, k, v, dout, dq32, dk, dv, lse, delta, B, T, S, H, Hk,
-                                          causal != 0, scale, status, configure, stream)
+                                          causal != 0, scale, status, stream)
                     : noalloc_launch<64>(q, k, v, dout, dq32, dk, dv, lse, delta, B, T, S, H, Hk,
-                                         causal != 0, scale, status, configure, stream);
+                                         causal != 0, scale, status, stream);
     if (rc != cudaSuccess) throw std::runtime_error(cudaGetErrorString(rc));
     cast_f32_bf16(dq32, dq, dq_elems, stream, scale);
   } catch (const std::exception& e) {

@@ -421,12 +421,7 @@ void launch_fwd(const void* q, const void* k, const void* v, void* o, float* lse
   p.lse = lse;
   p.status = status_ptr();
   auto kernel = flash_fwd_kernel<D>;
-  static bool configured = false;
-  if (!configured) {
-    OB_CUDA_CHECK(
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    configured = true;
-  }
+  ensure_dynamic_smem((const void*)kernel, L::kTotal);
   const int q_tiles = (T + kBlockQ - 1) / kBlockQ;
   const long long grid = (long long)q_tiles * B * H;
   kernel<<<(unsigned)grid, kThreads, L::kTotal, stream>>>(tQ, tK, tV, tO, p);

@@ -175,12 +175,7 @@ void cross_entropy_rows(void* logits, const int64_t* targets, float* row_loss, f
   OB_CHECK(pitch % 8 == 0, "cross entropy: logits pitch must be a multiple of 8 elements");
   const size_t smem = (size_t)((vocab + 7) / 8) * 16;
   OB_CHECK(smem <= 200 * 1024, "cross entropy: vocabulary too large for the shared-memory row buffer");
-  static bool configured = false;
-  if (!configured) {
-    OB_CUDA_CHECK(cudaFuncSetAttribute(ce_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       200 * 1024));
-    configured = true;
-  }
+  ensure_dynamic_smem((const void*)ce_rows_kernel, 200 * 1024);
   ce_rows_kernel<<<(unsigned)rows, 512, smem, stream>>>((__nv_bfloat16*)logits, targets, row_loss,
                                                         row_lse, row_correct, scale_ptr, vocab,
                                                         pitch, ignore_index, write_grad ? 1 : 0);

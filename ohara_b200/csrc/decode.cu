@@ -664,7 +664,7 @@ void sample_tokens(const void* logits, bool logits_bf16, int64_t row_stride, int
   OB_CHECK(use_smem || workspace != nullptr, "vocabulary too large for shared memory: pass a workspace");
   auto launch = [&](auto kernel, auto* typed) {
     if (use_smem) {
-      OB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need));
+      ensure_dynamic_smem((const void*)kernel, need);
     }
     kernel<<<rows, kSampleThreads, use_smem ? need : 0, stream>>>(
         typed, row_stride, vocab, valid_vocab, temperature, top_k, top_p, uniforms, out_tokens,

@@ -532,12 +532,7 @@ void launch_variant(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensor
                     const GemmParams& p, int grid, cudaStream_t stream) {
   using L = SmemLayout<BN>;
   auto kernel = gemm_bf16_kernel<BN, OUT_F32, false>;
-  static bool configured = false;
-  if (!configured) {
-    OB_CUDA_CHECK(
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    configured = true;
-  }
+  ensure_dynamic_smem((const void*)kernel, L::kTotal);
   kernel<<<grid, kNumThreads, L::kTotal, stream>>>(tA, tB, tC, p);
   OB_LAUNCH_CHECK();
 }
@@ -549,7 +544,11 @@ void launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap
                  const GemmParams& p, long long total_tiles, int num_sms, cudaStream_t stream) {
   using L = SmemLayout<256, true>;
   auto kernel = gemm_bf16_kernel<256, OUT_F32, true>;
-  static int resident_pairs = 0;
+  static int resident_by_device[64] = {0};
+  int dev = 0;
+  OB_CUDA_CHECK(cudaGetDevice(&dev));
+  int& resident_pairs = resident_by_device[dev & 63];
+  ensure_dynamic_smem((const void*)kernel, L::kTotal);
   cudaLaunchConfig_t config = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -562,8 +561,6 @@ void launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap
   config.attrs = attr;
   config.numAttrs = 1;
   if (resident_pairs == 0) {
-    OB_CUDA_CHECK(
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     config.gridDim = dim3(2 * (num_sms / 2), 1, 1);
     int clusters = 0;
     OB_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&clusters, kernel, &config));

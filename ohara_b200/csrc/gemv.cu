@@ -93,7 +93,7 @@ void gemv_bf16(const void* x, const void* w, void* y, int M, int N, int K, int64
   const int blocks = std::min((N + 7) / 8, device_sm_count() * 4);
   auto launch = [&](auto kernel) {
     if (smem > 48 * 1024)
-      OB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      ensure_dynamic_smem((const void*)kernel, smem);
     kernel<<<blocks, 256, smem, stream>>>(
         static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
         static_cast<__nv_bfloat16*>(y), M, N, K, ldx, ldw, ldy);

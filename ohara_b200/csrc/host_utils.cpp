@@ -1,7 +1,9 @@
 #include "host_utils.h"
 
 #include <atomic>
+#include <map>
 #include <mutex>
+#include <utility>
 
 namespace ob {
 
@@ -110,6 +112,25 @@ std::atomic<long long> g_launches{0};
 }
 long long launch_count() { return g_launches.load(); }
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+cudaError_t try_ensure_dynamic_smem(const void* kernel, size_t bytes) {
+  static std::mutex mutex;
+  static std::map<std::pair<const void*, int>, size_t> granted;  // (kernel, device) -> bytes
+  int dev = 0;
+  cudaError_t rc = cudaGetDevice(&dev);
+  if (rc != cudaSuccess) return rc;
+  std::lock_guard<std::mutex> lock(mutex);
+  auto key = std::make_pair(kernel, dev);
+  auto it = granted.find(key);
+  if (it != granted.end() && it->second >= bytes) return cudaSuccess;
+  rc = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (rc == cudaSuccess) granted[key] = bytes;
+  return rc;
+}
+
+void ensure_dynamic_smem(const void* kernel, size_t bytes) {
+  OB_CUDA_CHECK(try_ensure_dynamic_smem(kernel, bytes));
+}
 
 int device_sm_count() {
   static int cached[64] = {0};

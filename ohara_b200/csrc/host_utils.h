@@ -59,6 +59,14 @@ void make_tmap_3d(CUtensorMap* out, const void* base, TmapDtype dtype, uint64_t 
 
 int device_sm_count();
 
+// Function attributes are per device. Opts `kernel` into `bytes` of dynamic shared memory the
+// first time it is asked for on the current device (and again if a later call needs more);
+// throws if the driver refuses. Thread-safe.
+void ensure_dynamic_smem(const void* kernel, size_t bytes);
+// Same, without throwing: returns the CUDA error instead (nothing is recorded on failure, so the
+// next call tries again).
+cudaError_t try_ensure_dynamic_smem(const void* kernel, size_t bytes);
+
 // Device status word (see status.cpp): [0] first error code, [1] block that reported it, [2] number
 // of waits that ran out of time.
 int* status_ptr();

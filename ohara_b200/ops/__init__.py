@@ -64,7 +64,9 @@ def bf16_weight(weight: Tensor) -> Tensor:
     if weight.dtype == torch.bfloat16:
         return weight.detach()
     cached = getattr(weight, "_ohara_bf16", None)
-    version = weight._version
+    # ``param.data = tensor`` swaps the storage without bumping the version counter, so the key
+    # carries the storage address as well.
+    version = (weight._version, weight.data_ptr())
     if cached is not None and cached[0] == version and cached[1].device == weight.device:
         return cached[1]
     source = weight.detach()
@@ -86,16 +88,17 @@ def _f32_weight(weight: Tensor) -> Tensor:
     if source.dtype == torch.float32:
         return source.contiguous()
     cached = getattr(weight, "_ohara_f32", None)
-    if cached is not None and cached[0] == weight._version and cached[1].device == weight.device:
+    version = (weight._version, weight.data_ptr())
+    if cached is not None and cached[0] == version and cached[1].device == weight.device:
         return cached[1]
     copy = source.float().contiguous()
-    weight._ohara_f32 = (weight._version, copy)
+    weight._ohara_f32 = (version, copy)
     return copy
 
 
 def refresh_bf16_weight(weight: Tensor, shadow: Tensor) -> None:
     """Record ``shadow`` as the up-to-date bf16 copy of ``weight`` (called by fused optimizers)."""
-    weight._ohara_bf16 = (weight._version, shadow)
+    weight._ohara_bf16 = ((weight._version, weight.data_ptr()), shadow)
 
 
 def check_status(clear: bool = True) -> None:

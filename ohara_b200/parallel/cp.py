@@ -38,7 +38,7 @@ import torch.distributed as dist
 from torch import Tensor
 
 from ohara_b200.ops._ext import ext
-from ohara_b200.parallel.peer import PeerRuntime, SymmetricBuffer
+from ohara_b200.parallel.peer import PeerRuntime, SymmetricBuffer, release_stream_waits
 from ohara_b200.utils.profiling import nvtx_annotate
 
 _KV_SLOT = 0
@@ -120,8 +120,17 @@ class CPWorkspace:
         self.copy_stream = torch.cuda.Stream(device=self.device, priority=-1)
         self.kv_epoch = 0
         self.grad_epoch = 0
+        self.poisoned = False
         torch.cuda.synchronize()
         dist.barrier(group=group)
+
+    def abort(self) -> None:
+        """Satisfy every stream-ordered wait the copy stream may be parked in (the awaited "staged"
+        flags live in this rank's own flag buffer) and mark the workspace unusable; the way out
+        for the copy engines when a peer is lost or a collective timed out."""
+        self.poisoned = True
+        release_stream_waits([self.flags.pointers[self.rank] + 4 * (_KV_SLOT + r)
+                              for r in range(self.world)], self.device)
 
     @nvtx_annotate("cp.exchange_kv")
     def exchange_kv(self, kv_local: Tensor):
@@ -130,6 +139,9 @@ class CPWorkspace:
         arrived)``: views ``(rank * T_local / 2, B, 2, Hk, D)`` and ``((world - 1 - rank) * T_local,
         B, 2, Hk, D)`` (either may be ``None``; valid until two exchanges later) and the event that
         marks their arrival."""
+        if self.poisoned:
+            raise RuntimeError("this context-parallel workspace was aborted after a lost peer or a "
+                               "timed-out collective; rebuild the engine to continue")
         if kv_local.numel() > self.chunk_elements:
             raise ValueError("key/value chunk exceeds the workspace")
         if kv_local.shape[0] % 2:

@@ -20,6 +20,28 @@ import torch.distributed as dist
 from ohara_b200.ops._ext import ext
 
 
+# Stream-ordered waits compare cyclically ("flag - awaited >= 0" as a signed 32-bit number), so
+# this value satisfies a wait for any epoch a job can reach.
+RELEASE_EPOCH = 0x7FFFFFFF
+
+
+def release_stream_waits(addresses, device=None, value: int = RELEASE_EPOCH) -> None:
+    """Write ``value`` into the 32-bit flags at ``addresses`` (device memory of *this* GPU) with
+    stream-ordered stores on a stream of their own.
+
+    A copy stream that is parked in a stream-ordered wait for a flag a lost peer will never write
+    holds up every later ``wait_event`` / ``synchronize`` of the process. The awaited flags live in
+    this rank's own memory, so the host can always satisfy them; the queued copies then run (on
+    stale data, the step is lost anyway) and the streams drain. Safe to call from another thread
+    (the step watchdog) while the main thread is blocked in ``synchronize``."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    with torch.cuda.device(device):
+        stream = torch.cuda.Stream(device=device)
+        with torch.cuda.stream(stream):
+            for address in addresses:
+                ext().stream_write_value32(int(address), int(value))
+
+
 class SymmetricBuffer:
     """``nbytes`` of device memory per rank, addressable from every rank of ``group``."""
 

@@ -29,7 +29,7 @@ import torch.distributed as dist
 from torch import Tensor
 
 from ohara_b200.ops._ext import ext
-from ohara_b200.parallel.peer import SymmetricBuffer
+from ohara_b200.parallel.peer import SymmetricBuffer, release_stream_waits
 from ohara_b200.utils.profiling import nvtx_annotate
 
 _AG_SLOT = 0   # flag slots [0, world): "my staged rows for epoch e are complete"
@@ -82,9 +82,20 @@ class TPWorkspace:
                              for _ in range(max(1, min(self.world - 1, 4)))]
         self.gather_epoch = 0
         self.scatter_epoch = 0
+        self.poisoned = False
         self._maps: dict[tuple[int, int, int], Tensor] = {}
         torch.cuda.synchronize()
         dist.barrier(group=group)  # every rank has opened every buffer before the first signal
+
+    def abort(self) -> None:
+        """Release the copy streams: satisfy every stream-ordered wait this workspace may have
+        queued on a peer's "staged" flag (they live in this rank's flag buffer) and mark the
+        workspace unusable. The kernels' own waits are bounded and have already returned with a
+        status; only the copy engines' waits need this way out. Called by the engine when a
+        collective timed out, a peer was reported lost or the step watchdog fired."""
+        self.poisoned = True
+        release_stream_waits([self._flag_address(_AG_SLOT + r) for r in range(self.world)],
+                             self.device)
 
     def _flag_address(self, slot: int) -> int:
         return self.flags.pointers[self.rank] + 4 * slot
@@ -96,6 +107,9 @@ class TPWorkspace:
     @nvtx_annotate("tp.stage_rows")
     def stage(self, x_local: Tensor) -> StagedRows:
         rows, width = x_local.shape
+        if self.poisoned:
+            raise RuntimeError("this tensor-parallel workspace was aborted after a lost peer or a "
+                               "timed-out collective; rebuild the engine to continue")
         if rows % 128 or rows * width > self.capacity:
             raise ValueError(f"cannot stage a {rows} x {width} block (rows must be a multiple of 128 "
                              f"and fit {self.capacity} elements)")

@@ -207,7 +207,10 @@ class OharaEngine:
                 interval_s=tolerance.heartbeat_interval_s, timeout_s=tolerance.heartbeat_timeout_s,
             ).start()
         if tolerance.step_timeout_s > 0:
+            # On expiry the copy streams' stream-ordered waits are released first, so that a
+            # process that is not ended here can still drain its streams.
             self.watchdog = StepWatchdog(tolerance.step_timeout_s,
+                                         on_timeout=lambda step, elapsed: self.abort_fused_waits(),
                                          hard_exit=tolerance.exit_on_step_timeout)
 
     def check_peers(self, *, refresh: bool = False) -> None:
@@ -215,13 +218,54 @@ class OharaEngine:
         on the host before it launches a step, so that no kernel or collective is issued that
         would wait for the missing rank."""
         if self.heartbeat is not None:
-            self.heartbeat.check(refresh=refresh)
+            try:
+                self.heartbeat.check(refresh=refresh)
+            except Exception:
+                self.abort_fused_waits()
+                raise
 
     def guard_step(self, index: int):
         """Context manager that arms the step watchdog (a no-op when none is configured)."""
         if self.watchdog is None:
             return nullcontext()
         return self.watchdog.step(index)
+
+    def check_device_status(self) -> None:
+        """Raise ``CollectiveTimeout`` if a kernel of this process gave up a bounded wait (a peer
+        flag that never came, a pipeline hand-off that timed out) since the last check. Reads the
+        device status word, so call it after a ``synchronize()``: the trainer does so at the end
+        of every step and before it writes a checkpoint, which keeps a step whose
+        reduce-scatter or all-gather was abandoned from being trained on or saved. On a timeout
+        the stream-ordered waits of the fused tensor / context-parallel paths are released first,
+        so that the process can still drain its streams and exit. A no-op without CUDA."""
+        if self._device.type != "cuda":
+            return
+        from ohara_b200 import ops
+        from ohara_b200.errors import CollectiveTimeout
+
+        try:
+            ops.check_status()
+        except CollectiveTimeout:
+            self.abort_fused_waits()
+            raise
+
+    def abort_fused_waits(self) -> int:
+        """Release every stream-ordered wait that the fused tensor-parallel and context-parallel
+        workspaces of the prepared module may have queued (see ``TPWorkspace.abort``). Called on
+        the timeout, peer-failure and watchdog paths; returns the number of workspaces released."""
+        module = getattr(self, "_module", None)
+        if module is None:
+            return 0
+        seen: set[int] = set()
+        for child in module.modules():
+            for name in ("workspace", "cp_workspace"):
+                workspace = getattr(child, name, None)
+                workspace = getattr(workspace, "workspace", workspace)  # lazy wrappers
+                abort = getattr(workspace, "abort", None)
+                if callable(abort) and id(workspace) not in seen:
+                    seen.add(id(workspace))
+                    abort()
+        return len(seen)
 
     def leave(self) -> None:
         """Announce that this rank stops on purpose (between steps, nothing in flight)."""

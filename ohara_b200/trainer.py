@@ -497,6 +497,7 @@ class Trainer:
                 step_loss, lr = self.train_step(idx)
                 self.engine.synchronize()
             elapsed = time.perf_counter() - started
+            self._check_device_status()  # a kernel that abandoned a wait left stale data behind
             tokens_per_sec, mfu, eta_seconds, _ = self._compute_perf_metrics(idx, elapsed)
             if idx % self.print_every == 0 and self.engine.is_global_zero:
                 line = (f"iter: {idx} | loss: {step_loss:.4f} | lr: {lr:e} | time: {elapsed:.4f}s "
@@ -551,7 +552,14 @@ class Trainer:
             state["cuda_rng_state_all"] = torch.cuda.get_rng_state_all()
         return state
 
+    def _check_device_status(self) -> None:
+        check = getattr(self.engine, "check_device_status", None)
+        if callable(check):
+            check()
+
     def save_checkpoint(self, idx: int, lr: float, step_loss: float) -> None:
+        self.engine.synchronize()
+        self._check_device_status()  # never persist weights that a timed-out collective left stale
         self.engine.save(self.checkpoint_path, self.checkpoint_state(idx, lr, step_loss))
         config = getattr(_unwrap(self.model), "config", None)
         if config is not None:

@@ -393,3 +393,31 @@ def test_mamba_trains_on_the_scan_kernel():
     assert len(grads_scan) == len(grads_seq) > 0
     for got, ref in zip(grads_scan, grads_seq):
         assert rel_err(got, ref) < 1e-3
+
+
+def test_compute_copy_follows_data_assignment_and_dora_merge():
+    """The cached bf16 compute copy of a weight is keyed on the tensor version *and* its storage
+    address: an assignment to ``.data`` (which does not bump the version) is noticed, and a DoRA
+    merge of a layer that already ran a forward multiplies by the merged weight."""
+    from ohara_b200 import ops
+    from ohara_b200.adaptor.dora import DoRALinear
+    from ohara_b200.modules.mlp import Linear
+
+    torch.manual_seed(0)
+    x = torch.randn(32, 64, device="cuda")
+    layer = DoRALinear(64, 48, rank=4, bias=False).cuda()
+    layer.linear = Linear(64, 48, bias=False).cuda()   # the kernels' linear as the wrapped layer
+    layer.reset_magnitude()
+    with torch.no_grad():
+        layer.lora_B.normal_(std=0.5)                  # a zero adapter would make the merge a no-op
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        before = layer.linear(x).float()               # caches the copy of the un-merged weight
+        layer.merge()
+        merged = layer(x).float()
+    ref = F.linear(x, layer.linear.weight).float()
+    assert rel_err(merged, ref) < 2e-2
+    assert rel_err(before, ref) > 5e-2                 # the merge did change the layer
+    weight = layer.linear.weight
+    ops.bf16_weight(weight)
+    weight.data = torch.zeros_like(weight)
+    assert float(ops.bf16_weight(weight).abs().max()) == 0.0

@@ -38,6 +38,36 @@ def test_barrier_wait_runs_out_and_reports_status():
     assert torch.ones(4, device="cuda").sum().item() == 4.0
 
 
+def test_released_stream_wait_lets_the_streams_drain():
+    """A copy stream parked in a stream-ordered wait on a flag that nothing sets (a lost peer)
+    must be freed by ``release_stream_waits``: afterwards the work queued behind the wait runs
+    and ``synchronize`` returns."""
+    import time
+
+    from ohara_b200.ops._ext import ext
+    from ohara_b200.parallel.peer import release_stream_waits
+
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    payload = torch.zeros(1024, device="cuda")
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        ext().stream_wait_value32(flags.data_ptr() + 4 * 3, 7)   # epoch 7 of peer 3: never written
+        payload.add_(1.0)                                         # queued behind the wait
+    time.sleep(0.2)
+    assert not side.query()                                       # parked, as expected
+    release_stream_waits([flags.data_ptr() + 4 * r for r in range(8)])
+    deadline = time.monotonic() + 10
+    while not side.query() and time.monotonic() < deadline:
+        time.sleep(0.01)
+    drained = side.query()
+    if not drained:                                               # second way out before failing
+        flags.fill_(0x7FFFFFFF)
+    torch.cuda.synchronize()
+    assert drained, "the stream-ordered wait was not released"
+    assert float(payload.sum()) == 1024.0
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_fused_sharded_step_matches_c10d_on_two_gpus(tmp_path):
     script = """
