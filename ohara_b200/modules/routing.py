@@ -51,6 +51,45 @@ def load_balance_aux_loss(logits: Tensor, indices: Tensor, num_experts: int) -> 
     return num_experts * torch.sum(fraction * probs)
 
 
+def global_kth_largest(values: Tensor, k: int | Tensor, group=None) -> Tensor:
+    """Per column of ``values (N, E)`` fp32, the ``k``-th largest entry over the rows of *every*
+    rank of ``group`` (each rank passes its own rows; ``k`` counts over all of them).
+
+    Exact radix select on an order-preserving integer image of the floats: four passes, most
+    significant byte first; each pass builds a per-column histogram of the current byte among the
+    entries that still match the prefix found so far, sums the histograms over the group (the
+    only communication: ``E x 256`` counters) and descends into the byte that contains the
+    ``k``-th entry. No sort, no host synchronisation, identical result on every rank.
+
+    The reference averages per-rank quantiles instead (ohara/modules/moe_grouped.py:249-251),
+    which is not the quantile of the union when ranks see differently distributed tokens."""
+    n, e = values.shape
+    bits = values.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    negative = bits >= 0x80000000
+    keys = torch.where(negative, bits ^ 0xFFFFFFFF, bits | 0x80000000)  # larger float, larger key
+    column = torch.arange(e, device=values.device).expand(n, e)
+    remaining = torch.as_tensor(k, device=values.device, dtype=torch.int64).expand(e).clone()
+    prefix = torch.zeros(e, device=values.device, dtype=torch.int64)
+    distributed = dist.is_available() and dist.is_initialized()
+    for shift in (24, 16, 8, 0):
+        alive = (keys >> (shift + 8)) == prefix if shift < 24 else torch.ones_like(keys, dtype=torch.bool)
+        byte = (keys >> shift) & 0xFF
+        hist = torch.zeros(e * 256, device=values.device, dtype=torch.int64)
+        hist.scatter_add_(0, (column * 256 + byte).reshape(-1), alive.reshape(-1).to(torch.int64))
+        if distributed:
+            dist.all_reduce(hist, group=group)
+        from_top = hist.view(e, 256).flip(1).cumsum(1)            # entries with byte >= 255 - j
+        position = (from_top >= remaining[:, None]).to(torch.int64).argmax(1)
+        above = torch.where(position > 0,
+                            from_top.gather(1, (position - 1).clamp_min(0)[:, None]).squeeze(1),
+                            torch.zeros_like(remaining))
+        remaining = remaining - above
+        prefix = (prefix << 8) | (255 - position)
+    back = torch.where(prefix >= 0x80000000, prefix ^ 0x80000000, prefix ^ 0xFFFFFFFF)
+    back = torch.where(back >= 0x80000000, back - (1 << 32), back)  # as signed 32-bit
+    return back.to(torch.int32).view(torch.float32)
+
+
 class QuantileBalancedRouter(nn.Module):
     """Mixin holding the router bias and the balancing statistics buffers."""
 
@@ -65,9 +104,23 @@ class QuantileBalancedRouter(nn.Module):
         self.register_buffer("qb_beta_count", torch.zeros(()), persistent=False)
         self.register_buffer("expert_counts", torch.zeros(e, dtype=torch.long), persistent=False)
 
+    # Set by the engine under expert parallelism: the balancing statistic then is the quantile over
+    # the tokens of every rank of this group (all of which route through the same experts), not
+    # an average of per-rank quantiles.
+    qb_global_group = None
+    qb_global = False
+    qb_global_world = 1
+
     @torch.no_grad()
     def _accumulate_qb(self, logits: Tensor, alpha: Tensor) -> None:
         tokens = logits.size(0)
+        if self.qb_global:
+            total = tokens * self.qb_global_world
+            fair_share = min(max(1, total * self.num_experts_per_tok // self.num_experts), total)
+            margin = logits.float() - alpha.float().view(-1, 1)
+            self.qb_beta_sum += global_kth_largest(margin, fair_share, self.qb_global_group)
+            self.qb_beta_count += 1
+            return
         fair_share = max(1, tokens * self.num_experts_per_tok // self.num_experts)
         fair_share = min(fair_share, tokens)
         if logits.is_cuda and logits.dtype == torch.float32:
@@ -91,7 +144,7 @@ class QuantileBalancedRouter(nn.Module):
         # queue once per layer and step): with a zero count the old bias is kept.
         seen = self.qb_beta_count > 0
         beta = self.qb_beta_sum / self.qb_beta_count.clamp_min(1)
-        if dist.is_available() and dist.is_initialized():
+        if dist.is_available() and dist.is_initialized() and not self.qb_global:
             dist.all_reduce(beta, op=dist.ReduceOp.SUM, group=group)
             beta /= dist.get_world_size(group=group)
         bias = -beta

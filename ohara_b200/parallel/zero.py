@@ -73,11 +73,24 @@ class ShardedOptimizer(Optimizer):
     """
 
     def __init__(self, optimizer: Optimizer, process_group=None, fused: bool = False,
-                 wire_dtype: torch.dtype | None = None) -> None:
+                 wire_dtype: torch.dtype | None = None, *, replicate_group=None,
+                 replicate_world: int = 1, solo: bool = False,
+                 norm_groups: dict[str, Any] | None = None) -> None:
+        """``process_group``: the ranks the state is sharded over. ``replicate_group`` (with its
+        size ``replicate_world``): ranks that hold a copy of the *same* shard (hybrid sharding,
+        ``dp_replicate x dp_shard``); their reduced shards are averaged after the reduce-scatter.
+        ``solo=True`` shards over nobody (this rank alone owns the parameters, e.g. the experts
+        of an expert-parallel rank without data-parallel replicas). ``norm_groups`` maps
+        ``"tp"`` / ``"ep"`` to the process group over which the shards of tensor-parallel /
+        expert-parallel parameters are distinct, for the global gradient norm."""
         self.inner = optimizer
         self.group = process_group
-        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        distributed = dist.is_initialized() and not solo
+        self.world = dist.get_world_size(process_group) if distributed else 1
+        self.rank = dist.get_rank(process_group) if distributed else 0
+        self.replicate_group = replicate_group
+        self.replicate_world = int(replicate_world) if dist.is_initialized() else 1
+        self.norm_groups = dict(norm_groups or {})
         self.param_groups = optimizer.param_groups
         self.defaults = optimizer.defaults
         self.state = optimizer.state  # kept for API parity; the live state is in self.local
@@ -227,7 +240,7 @@ class ShardedOptimizer(Optimizer):
             local_groups.append(clone)
         self.local: Optimizer | None = None
         if local_groups:
-            cls = type(self.inner)
+            cls = getattr(self.inner, "optimizer_class", None) or type(self.inner)
             try:
                 self.local = cls(local_groups)
             except TypeError:
@@ -290,18 +303,67 @@ class ShardedOptimizer(Optimizer):
                                            group=self.group)
             self.grad_local.copy_(shard)
             self.grad_local.div_(self.world)
+        if self.replicate_world > 1:
+            # hybrid sharding: the same shard exists once per replica group; average them
+            dist.all_reduce(self.grad_local, group=self.replicate_group)
+            self.grad_local.div_(self.replicate_world)
         self._reduced = True
+
+    def _norm_classes(self) -> dict[str, list[tuple[int, int]]]:
+        """Spans of this rank's region by how the parameter is laid out over the *other* parallel
+        dimensions: ``"whole"`` (replicated there), ``"tp"`` / ``"ep"`` (every rank of that
+        dimension holds a distinct shard, so squared norms add up over it)."""
+        cached = getattr(self, "_norm_spans", None)
+        if cached is None:
+            cached = {"whole": [], "tp": [], "ep": []}
+            for piece in self.pieces[self.rank]:
+                kind = ("tp" if hasattr(piece.param, "tensor_parallel_dim")
+                        else "ep" if getattr(piece.param, "expert_parallel", False) else "whole")
+                if kind not in self.norm_groups and kind != "whole":
+                    kind = "whole"
+                spans = cached[kind]
+                if spans and spans[-1][1] == piece.offset:
+                    spans[-1] = (spans[-1][0], piece.offset + piece.length)
+                else:
+                    spans.append((piece.offset, piece.offset + piece.length))
+            self._norm_spans = cached
+        return cached
+
+    @torch.no_grad()
+    def grad_sq_norm(self) -> Tensor:
+        """Squared l2 norm of the whole (unsharded, all tensor / expert shards included) mean
+        gradient of the parameters this optimizer manages; collective, same value on every rank
+        that takes part. Reduces the gradients first if that has not happened yet."""
+        self.reduce_gradients()
+        parts = []
+        for kind in ("whole", "tp", "ep"):
+            views = [self.grad_local[lo:hi] for lo, hi in self._norm_classes()[kind]]
+            if views:
+                norms = torch.stack(torch._foreach_norm(views)).float()
+                parts.append(norms.square().sum())
+            else:
+                parts.append(torch.zeros((), device=self.device, dtype=torch.float32))
+        sums = torch.stack(parts)
+        if self.world > 1:
+            dist.all_reduce(sums, group=self.group)
+        total = sums[0]
+        for index, kind in ((1, "tp"), (2, "ep")):
+            if kind in self.norm_groups:
+                part = sums[index].clone()
+                dist.all_reduce(part, group=self.norm_groups[kind])
+                total = total + part
+        return total
+
+    @torch.no_grad()
+    def scale_gradients_(self, scale: Tensor) -> None:
+        self.grad_local.mul_(scale)
 
     @torch.no_grad()
     def clip_grad_norm_(self, model, max_norm: float) -> Tensor:
         """Global gradient-norm clipping on the reduced shards (collective)."""
-        self.reduce_gradients()
-        total = self.grad_local.float().square().sum()
-        if self.world > 1:
-            dist.all_reduce(total, group=self.group)
-        norm = total.sqrt()
+        norm = self.grad_sq_norm().sqrt()
         scale = (max_norm / (norm + 1e-6)).clamp(max=1.0)
-        self.grad_local.mul_(scale)
+        self.scale_gradients_(scale)
         return norm
 
     def _sync_hyperparameters(self) -> None:
@@ -598,6 +660,125 @@ class ShardedOptimizer(Optimizer):
         for saved, group in zip(full["param_groups"], self.param_groups):
             group.update({k: v for k, v in saved.items() if k != "params"})
         self._load_masters(masters)
+
+
+class _GroupView:
+    """What :class:`ShardedOptimizer` needs from "the wrapped optimizer" when it manages only some
+    of that optimizer's parameters: the parameter groups (with the subset), the defaults and the
+    class to instantiate for the shard."""
+
+    def __init__(self, base: Optimizer, groups: list[dict[str, Any]]) -> None:
+        self.param_groups = groups
+        self.defaults = base.defaults
+        self.state: dict = {}
+        self.optimizer_class = getattr(base, "optimizer_class", None) or type(base)
+
+
+class HybridShardedOptimizer(Optimizer):
+    """Several :class:`ShardedOptimizer` parts, each over its own subset of the parameters and its
+    own process group, behind one optimizer.
+
+    This is what expert parallelism needs next to sharded data parallelism: the dense parameters
+    (attention, shared experts, router, embeddings) are replicated over *all* ranks that see
+    different data, expert-parallel peers included, and are sharded over that whole group; the
+    routed experts of a rank are replicated only over the ranks that hold the same experts (its
+    ``dp`` peers) — possibly over nobody — and are sharded over those alone.
+
+    ``parts`` is a list of dictionaries: ``select`` (a predicate on parameters) plus the keyword
+    arguments of :class:`ShardedOptimizer`. ``param_groups`` stays the wrapped optimizer's list, so
+    schedules keep working; hyper-parameters are copied to the parts before every step. All ranks
+    must build the parts in the same order (the parts run their collectives one after another).
+    """
+
+    def __init__(self, optimizer: Optimizer, parts: list[dict[str, Any]]) -> None:
+        self.inner = optimizer
+        self.param_groups = optimizer.param_groups
+        self.defaults = optimizer.defaults
+        self.state = optimizer.state
+        self.parts: list[ShardedOptimizer] = []
+        self._links: list[list[int]] = []  # per part: user group index of each of its groups
+        claimed: set[int] = set()
+        for spec in parts:
+            spec = dict(spec)
+            select = spec.pop("select")
+            groups, links = [], []
+            for gi, group in enumerate(self.param_groups):
+                chosen = [p for p in group["params"] if p.requires_grad and select(p)]
+                if not chosen:
+                    continue
+                overlap = claimed.intersection(id(p) for p in chosen)
+                if overlap:
+                    raise ValueError("a parameter was selected by two parts of a hybrid optimizer")
+                claimed.update(id(p) for p in chosen)
+                groups.append({**{k: v for k, v in group.items() if k != "params"},
+                               "params": chosen})
+                links.append(gi)
+            if not groups:
+                continue
+            self.parts.append(ShardedOptimizer(_GroupView(optimizer, groups), **spec))
+            self._links.append(links)
+        missing = [p for g in self.param_groups for p in g["params"]
+                   if p.requires_grad and id(p) not in claimed]
+        if missing:
+            raise ValueError(f"{len(missing)} trainable parameters belong to no part")
+        if not self.parts:
+            raise ValueError("optimizer has no trainable parameters")
+
+    @property
+    def fused(self) -> bool:
+        return any(part.fused for part in self.parts)
+
+    def _sync_hyperparameters(self) -> None:
+        for part, links in zip(self.parts, self._links):
+            for sub, gi in zip(part.param_groups, links):
+                for key, value in self.param_groups[gi].items():
+                    if key != "params":
+                        sub[key] = value
+
+    def reduce_gradients(self) -> None:
+        for part in self.parts:
+            part.reduce_gradients()
+
+    @torch.no_grad()
+    def clip_grad_norm_(self, model, max_norm: float) -> Tensor:
+        total = sum(part.grad_sq_norm() for part in self.parts)
+        norm = total.sqrt()
+        scale = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+        for part in self.parts:
+            part.scale_gradients_(scale)
+        return norm
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        self._sync_hyperparameters()
+        for part in self.parts:
+            part.step()
+        return loss
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for part in self.parts:
+            part.zero_grad(set_to_none)
+
+    def sync_master_weights(self) -> None:
+        for part in self.parts:
+            part.sync_master_weights()
+
+    def state_dict(self) -> dict[str, Any]:
+        return {"hybrid": True, "parts": [part.state_dict() for part in self.parts]}
+
+    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
+        if not state_dict.get("hybrid") or len(state_dict["parts"]) != len(self.parts):
+            raise ValueError("expected the state of a hybrid sharded optimizer with "
+                             f"{len(self.parts)} parts")
+        for part, saved in zip(self.parts, state_dict["parts"]):
+            part.load_state_dict(saved)
+        for part, links in zip(self.parts, self._links):
+            for sub, gi in zip(part.param_groups, links):
+                self.param_groups[gi].update({k: v for k, v in sub.items() if k != "params"})
 
 
 def _to_cpu(obj: Any) -> Any:

@@ -188,7 +188,27 @@ class OharaEngine:
             self._strategy = DDPStrategy(init_sync=not self.topology.tp_enabled)
         elif strategy == StrategyType.FSDP:
             fused = self.config.fused_collectives and self._device.type == "cuda"
-            self._strategy = FSDPStrategy(fused=fused, init_sync=not self.topology.tp_enabled)
+            topo = self.topology
+            # With tensor / expert parallelism the shards differ between ranks of the optimizer's
+            # group: the engine then equalises the full model before it is sharded instead.
+            composed = topo.tp_enabled or topo.ep > 1 or topo.cp > 1 or topo.pp > 1
+            self._strategy = FSDPStrategy(fused=fused, init_sync=not composed)
+            hybrid = topo.dp_replicate > 1 and topo.dp_shard > 1
+            base_size = topo.dp_shard if hybrid else topo.dp_world_size
+            norm_groups = {}
+            if topo.tp_enabled:
+                norm_groups["tp"] = self._groups.get("tp")
+            if topo.ep > 1:
+                norm_groups["ep"] = self._groups.get("ep")
+            self._strategy.configure(
+                replicate_group=self._groups.get("replicate"),
+                replicate_world=topo.dp_replicate if hybrid else 1,
+                expert_parallel=topo.ep > 1,
+                expert_group=self._groups.get("expert_shard"),
+                expert_world=base_size * topo.cp,
+                norm_groups=norm_groups,
+            )
+            self._sharded_over_cp = topo.cp > 1
         else:
             self._strategy = SingleStrategy()
         use_scaler = (
@@ -287,6 +307,19 @@ class OharaEngine:
             "ep": (("ep",), topo.ep),
             "pp": (("pp",), topo.pp),
         }
+        if self._wants_sharded_optimizer():
+            # Groups of the sharded optimizer. Context-parallel and expert-parallel peers hold
+            # replicas of the dense parameters, so those are sharded over them as well; the
+            # routed experts only over the ranks that hold the same experts. With hybrid sharding
+            # (both data-parallel dimensions > 1) ``dp_replicate`` is a replica dimension of its
+            # own, otherwise it is folded into the shard group.
+            hybrid = topo.dp_replicate > 1 and topo.dp_shard > 1
+            base = ("dp_shard",) if hybrid else ("dp_replicate", "dp_shard")
+            base_size = topo.dp_shard if hybrid else topo.dp_world_size
+            dims["shard"] = ((*base, "cp", "ep"), base_size * topo.cp * topo.ep)
+            dims["expert_shard"] = ((*base, "cp"), base_size * topo.cp)
+            if hybrid:
+                dims["replicate"] = (("dp_replicate",), topo.dp_replicate)
         me = topo.global_rank
         for name, (axes, size) in dims.items():
             if size <= 1:
@@ -298,6 +331,9 @@ class OharaEngine:
                 pg = dist.new_group(ranks=ranks)
                 if me in ranks:
                     self._groups[name] = pg
+
+    def _wants_sharded_optimizer(self) -> bool:
+        return self.config.strategy == StrategyType.FSDP
 
     # -- prepare -------------------------------------------------------------------------------
     def prepare(self, module: torch.nn.Module, *optimizers: Optimizer):
@@ -316,17 +352,33 @@ class OharaEngine:
                 module = module.to(device=self._device, dtype=torch.bfloat16)
             else:
                 module = module.to(self._device)
+        self._equalise_initial_weights(module)
         module = self._maybe_apply_tensor_parallel(module)
         self._maybe_apply_context_parallel(module)
         ignored = self._maybe_apply_expert_parallel(module)
-        if ignored:
+        if ignored and isinstance(self._strategy, DDPStrategy):
             from torch.nn.parallel import DistributedDataParallel
 
             DistributedDataParallel._set_params_and_buffers_to_ignore_for_model(module, ignored)
-        group = self._groups.get("dp_ep") if self.topology.ep > 1 else self._groups.get("dp")
+        if isinstance(self._strategy, FSDPStrategy):
+            group = self._groups.get("shard")
+        else:
+            group = self._groups.get("dp_ep") if self.topology.ep > 1 else self._groups.get("dp")
         module = self._strategy.setup_module(module, device=self._device, process_group=group)
         self._module = module
         return module
+
+    def _equalise_initial_weights(self, module: torch.nn.Module) -> None:
+        """With the sharded optimizer composed with tensor / expert / context parallelism every
+        rank first holds the whole model: broadcast rank 0's values so that all shards are cut
+        from the same weights (the per-group broadcast that plain data parallelism uses would
+        overwrite one rank's expert or tensor shard with another's)."""
+        if not isinstance(self._strategy, FSDPStrategy) or self._strategy.init_sync:
+            return
+        if not dist.is_initialized() or self.topology.world_size <= 1:
+            return
+        for tensor in list(module.parameters()) + list(module.buffers()):
+            dist.broadcast(tensor.data, src=0)
 
     def _maybe_apply_context_parallel(self, module: torch.nn.Module) -> None:
         """With ``cp > 1`` the ranks of a context-parallel group share a batch and each works on
@@ -355,9 +407,6 @@ class OharaEngine:
 
         if self._device.type != "cuda":
             raise RuntimeError("expert parallelism needs CUDA devices")
-        if isinstance(self._strategy, FSDPStrategy):
-            raise NotImplementedError("expert parallelism is not wired for the sharded optimizer; "
-                                      "use the ddp strategy")
         layers = [m for m in module.modules() if isinstance(m, GroupedMoE)]
         if not layers:
             raise ValueError("ep > 1 but the model has no grouped mixture-of-experts layer")
@@ -368,6 +417,14 @@ class OharaEngine:
                 shared[key] = LazyEPWorkspace(self._groups.get("ep"), layer.num_experts, layer.dim,
                                               self.config.expert_capacity_factor)
             layer.shard_experts(shared[key])
+            topo = self.topology
+            sharded = isinstance(self._strategy, FSDPStrategy)
+            if layer.quantile_balancing and (sharded or topo.cp == 1):
+                # balance on the quantile over the tokens of every rank that routes through
+                # these experts (or replicas of them), not on an average of per-rank quantiles
+                layer.qb_global = True
+                layer.qb_global_group = self._groups.get("shard" if sharded else "dp_ep")
+                layer.qb_global_world = topo.dp_world_size * topo.ep * (topo.cp if sharded else 1)
         self._expert_parallel = True
         return [name for name, p in module.named_parameters() if getattr(p, "expert_parallel", False)]
 
@@ -375,6 +432,8 @@ class OharaEngine:
         """Average expert gradients over the data-parallel replicas of each expert shard."""
         if not getattr(self, "_expert_parallel", False) or self.topology.dp_world_size <= 1:
             return
+        if isinstance(self._strategy, FSDPStrategy):
+            return  # the expert part of the sharded optimizer averages them itself
         group, size = self._groups.get("dp"), self.topology.dp_world_size
         for param in model.parameters():
             if getattr(param, "expert_parallel", False) and param.grad is not None:
@@ -493,6 +552,8 @@ class OharaEngine:
         sharded between them: sum every gradient over the group."""
         if not getattr(self, "_cp_sequence_sharding", False) or self._replica_grads_synced:
             return
+        if getattr(self, "_sharded_over_cp", False):
+            return  # the sharded optimizer's group contains the context-parallel peers
         group = self._groups.get("cp")
         for param in model.parameters():
             if param.grad is not None:
@@ -577,7 +638,9 @@ class OharaEngine:
             # every rank's loss is a mean over its own slice: the group mean is their average
             loss = loss / self.topology.tp
             self._tp_grads_synced = False
-        if getattr(self, "_cp_sequence_sharding", False):
+        if getattr(self, "_cp_sequence_sharding", False) and not getattr(self, "_sharded_over_cp", False):
+            # (under the sharded optimizer the reduce-scatter takes the mean over the
+            # context-parallel peers as well, so the loss keeps its scale)
             loss = loss / self.topology.cp
             self._replica_grads_synced = False
         if self._scaler.is_enabled():
@@ -690,8 +753,18 @@ class OharaEngine:
         if callable(sync):
             sync()
         if self.topology.tp_enabled:
-            return gather_tensor_parallel_state(inner, self._groups.get("tp"))
-        return inner.state_dict()
+            state = gather_tensor_parallel_state(inner, self._groups.get("tp"))
+        else:
+            state = dict(inner.state_dict())
+        if getattr(self, "_expert_parallel", False):
+            # routed experts: every rank of the expert-parallel group holds E / ep of them
+            group, world = self._groups.get("ep"), self.topology.ep
+            for name, param in inner.named_parameters():
+                if getattr(param, "expert_parallel", False) and name in state:
+                    parts = [torch.empty_like(state[name]) for _ in range(world)]
+                    dist.all_gather(parts, state[name].contiguous(), group=group)
+                    state[name] = torch.cat(parts, dim=0)
+        return state
 
     def save(self, path: str | Path, state: dict[str, Any]) -> None:
         """Rank 0 writes ``state`` atomically (temp file + rename), then everyone meets at a

@@ -1,7 +1,20 @@
 """Sharded data parallelism: the module stays a plain ``nn.Module`` (no wrapper, no prefixed
 state-dict keys); the optimizer is wrapped by :class:`ohara_b200.parallel.zero.ShardedOptimizer`,
 which owns the gradient reduce-scatter, the sharded master weights / optimizer state and the
-parameter all-gather. See ``ohara_b200/parallel/zero.py`` for the data layout."""
+parameter all-gather. See ``ohara_b200/parallel/zero.py`` for the data layout.
+
+The engine tells the strategy which process groups to use (:meth:`FSDPStrategy.configure`):
+
+* ``process_group``: the ranks the dense parameters are sharded over (``dp_shard``, together with
+  the context-parallel and expert-parallel peers, which are replicas as far as dense parameters
+  are concerned);
+* ``replicate_group``: with hybrid sharding (``dp_replicate > 1`` and ``dp_shard > 1``) the ranks
+  that hold the same shard; their reduced gradients are averaged;
+* ``expert_group``: with expert parallelism, the ranks that hold the same routed experts; the
+  expert parameters form a second part of the optimizer sharded over those ranks only;
+* ``norm_groups``: the tensor- / expert-parallel groups, over which a global gradient norm has to
+  add up the distinct shards.
+"""
 
 from __future__ import annotations
 
@@ -21,6 +34,20 @@ class FSDPStrategy(BaseStrategy):
         self.init_sync = init_sync
         self.process_group = None
         self.device: torch.device | None = None
+        self.replicate_group = None
+        self.replicate_world = 1
+        self.expert_parallel = False
+        self.expert_group = None
+        self.expert_world = 1
+        self.norm_groups: dict[str, Any] = {}
+
+    def configure(self, *, replicate_group=None, replicate_world: int = 1,
+                  expert_parallel: bool = False, expert_group=None, expert_world: int = 1,
+                  norm_groups: dict[str, Any] | None = None) -> None:
+        self.replicate_group, self.replicate_world = replicate_group, replicate_world
+        self.expert_parallel = expert_parallel
+        self.expert_group, self.expert_world = expert_group, expert_world
+        self.norm_groups = dict(norm_groups or {})
 
     def setup_module(self, module: nn.Module, *, device: torch.device,
                      process_group: Any | None = None) -> nn.Module:
@@ -36,8 +63,23 @@ class FSDPStrategy(BaseStrategy):
         return module
 
     def setup_optimizer(self, optimizer, module: nn.Module | None = None):
-        from ohara_b200.parallel.zero import ShardedOptimizer
+        from ohara_b200.parallel.zero import HybridShardedOptimizer, ShardedOptimizer
 
-        if isinstance(optimizer, ShardedOptimizer):
+        if isinstance(optimizer, (ShardedOptimizer, HybridShardedOptimizer)):
             return optimizer
-        return ShardedOptimizer(optimizer, process_group=self.process_group, fused=self.fused)
+        dense_norms = {k: v for k, v in self.norm_groups.items() if k == "tp"}
+        common = dict(fused=self.fused, replicate_group=self.replicate_group,
+                      replicate_world=self.replicate_world)
+        if not self.expert_parallel:
+            return ShardedOptimizer(optimizer, process_group=self.process_group,
+                                    norm_groups=dense_norms, **common)
+
+        def is_expert(p) -> bool:
+            return bool(getattr(p, "expert_parallel", False))
+
+        return HybridShardedOptimizer(optimizer, [
+            dict(select=lambda p: not is_expert(p), process_group=self.process_group,
+                 norm_groups=dense_norms, **common),
+            dict(select=is_expert, process_group=self.expert_group,
+                 solo=self.expert_world <= 1, norm_groups=self.norm_groups, **common),
+        ])

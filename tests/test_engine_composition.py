@@ -1,0 +1,201 @@
+"""The sharded optimizer composed with the other parallel dimensions, on gloo ranks (CPU):
+hybrid sharding (``dp_replicate x dp_shard``), tensor parallel x sharded data parallel, a hybrid
+optimizer whose "expert" part is sharded over a different group, and the global balancing
+quantile. Every case is compared with plain single-process training on the same data."""
+
+import os
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+PRELUDE = """
+import torch, torch.distributed as dist
+from torch.utils.data import DataLoader, TensorDataset
+from ohara_b200.models.llama import Config, Llama
+from ohara_b200.runtime import (EngineConfig, OharaEngine, ParallelConfig, StrategyType,
+                                TensorParallelPlan)
+from ohara_b200.optimizer import build_adamw, build_muon_adamw
+from ohara_b200.trainer import Trainer
+from ohara_b200.lr_scheduler import Scheduler
+
+torch.manual_seed(0)
+cfg = Config(vocab_size=31, max_sequence_length=8, hidden_size=16, intermediate_size=24,
+             num_attention_heads=2, num_hidden_layers=2, dropout=0.0)
+ids = torch.randint(0, 31, (8, 9))
+dataset = TensorDataset(ids[:, :-1], ids[:, 1:])
+base = Llama(cfg)
+state = {k: v.clone() for k, v in base.state_dict().items()}
+
+def reference(builder, steps=3):
+    solo = Llama(cfg); solo.load_state_dict(state)
+    opt = builder(solo)
+    for _ in range(steps):
+        loss = solo.loss_sum(ids[:, :-1], ids[:, 1:]) / ids[:, 1:].numel()
+        loss.backward(); opt.step(); opt.zero_grad()
+    return solo
+"""
+
+
+def _run(script, world, tmp_path, port_base=29300):
+    path = tmp_path / "worker.py"
+    path.write_text(textwrap.dedent(PRELUDE) + textwrap.dedent(script))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port_base + os.getpid() % 500), str(path)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    return proc.stdout
+
+
+def test_hybrid_sharding_replicate_times_shard_matches_single_process(tmp_path):
+    """Four ranks as two replicas of a two-way sharded optimizer: shards over ``dp_shard``,
+    reduced gradients averaged over ``dp_replicate``."""
+    out = _run(
+        """
+        solo = reference(build_muon_adamw)
+        engine = OharaEngine(EngineConfig(strategy=StrategyType.FSDP,
+                                          parallel=ParallelConfig(dp_replicate=2)))
+        model = Llama(cfg); model.load_state_dict(state)
+        model = engine.prepare(model)
+        (opt,) = engine.prepare_optimizers(build_muon_adamw(model))
+        assert opt.world == 2 and opt.replicate_world == 2, (opt.world, opt.replicate_world)
+        assert engine.data_parallel_world_size == 4
+        loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=2))
+        trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=1,
+                          max_iters=3, eval_iters=0, save_ckpt_iters=0, grad_clip_norm=1e9)
+        trainer.train()
+        for a, b in zip(solo.parameters(), model.parameters()):
+            assert torch.allclose(a, b, atol=2e-5), (a - b).abs().max()
+        if dist.get_rank() == 0:
+            print("HSDP_OK")
+        engine.close()
+        """,
+        4, tmp_path,
+    )
+    assert "HSDP_OK" in out
+
+
+def test_tensor_parallel_times_sharded_optimizer_matches_single_process(tmp_path):
+    """tp=2 x dp=2: every tensor-parallel rank shards its own slice of the model over its
+    data-parallel peers; the clipped global norm counts tensor shards once each."""
+    out = _run(
+        """
+        solo = Llama(cfg); solo.load_state_dict(state)
+        ref_opt = build_adamw(solo, learning_rate=0.02, weight_decay=0.1)
+        ref_norms = []
+        for _ in range(3):
+            loss = solo.loss_sum(ids[:, :-1], ids[:, 1:]) / ids[:, 1:].numel()
+            loss.backward()
+            ref_norms.append(float(torch.nn.utils.clip_grad_norm_(solo.parameters(), 0.5)))
+            ref_opt.step(); ref_opt.zero_grad()
+        engine = OharaEngine(EngineConfig(strategy=StrategyType.FSDP,
+                                          parallel=ParallelConfig(tp=2)))
+        engine.launch()
+        torch.manual_seed(100 + dist.get_rank())  # a different init on every rank:
+        model = Llama(cfg)                        # the engine equalises it with rank 0's
+        if dist.get_rank() == 0:
+            model.load_state_dict(state)
+        model = engine.prepare(model)
+        assert engine.topology.tp == 2 and engine.topology.dp_shard == 2
+        (opt,) = engine.prepare_optimizers(build_adamw(model, learning_rate=0.02, weight_decay=0.1))
+        assert opt.world == 2
+        loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=4))
+        trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=1,
+                          max_iters=3, eval_iters=0, save_ckpt_iters=0, grad_clip_norm=0.5)
+        norms = []
+        clip = engine.clip_gradients
+        def recording(model, optimizer, max_norm):
+            value = clip(model, optimizer, max_norm)
+            norms.append(float(value))
+            return value
+        engine.clip_gradients = recording
+        trainer.train()
+        for got, want in zip(norms, ref_norms):
+            assert abs(got - want) < 1e-4 * max(want, 1.0), (norms, ref_norms)
+        full = engine.full_state_dict(model)
+        for key, value in solo.state_dict().items():
+            assert torch.allclose(full[key], value, atol=3e-5), (key, (full[key] - value).abs().max())
+        if dist.get_rank() == 0:
+            print("TP_FSDP_OK")
+        engine.close()
+        """,
+        4, tmp_path, port_base=29900,
+    )
+    assert "TP_FSDP_OK" in out
+
+
+def test_hybrid_optimizer_shards_each_part_over_its_own_group(tmp_path):
+    """Two ranks; the feed-forward weights of layer 0 play the part of routed experts that only
+    this rank holds (no replicas: ``solo``), everything else is sharded over both ranks. Dense
+    gradients must be averaged over the ranks, "expert" gradients must stay local."""
+    out = _run(
+        """
+        from ohara_b200.parallel.zero import HybridShardedOptimizer
+        dist.init_process_group("gloo")
+        rank = dist.get_rank()
+        def tagged(model):
+            for p in model.layers[0].ff.parameters():
+                p.expert_parallel = True
+            return model
+        mine = ids[rank * 4:(rank + 1) * 4]
+        # reference: plain optimizer fed the gradients the hybrid one should arrive at
+        solo = tagged(Llama(cfg)); solo.load_state_dict(state)
+        ref_opt = build_muon_adamw(solo)
+        model = tagged(Llama(cfg)); model.load_state_dict(state)
+        is_expert = lambda p: bool(getattr(p, "expert_parallel", False))
+        opt = HybridShardedOptimizer(build_muon_adamw(model), [
+            dict(select=lambda p: not is_expert(p)),
+            dict(select=is_expert, solo=True, norm_groups={"ep": None}),
+        ])
+        assert [part.world for part in opt.parts] == [2, 1]
+        for step in range(3):
+            for m in (solo, model):
+                (m.loss_sum(mine[:, :-1], mine[:, 1:]) / mine[:, 1:].numel()).backward()
+            for p in solo.parameters():
+                if not is_expert(p):
+                    dist.all_reduce(p.grad); p.grad /= 2
+            sq = sum(p.grad.square().sum() for p in solo.parameters() if not is_expert(p))
+            local = sum(p.grad.square().sum() for p in solo.parameters() if is_expert(p))
+            dist.all_reduce(local)                      # distinct "experts" on every rank
+            want = float((sq + local).sqrt())
+            got = float(opt.clip_grad_norm_(model, 1e9))
+            assert abs(got - want) < 1e-4 * max(want, 1.0), (got, want)
+            ref_opt.step(); ref_opt.zero_grad(); opt.step(); opt.zero_grad()
+            for (name, a), b in zip(solo.named_parameters(), model.parameters()):
+                assert torch.allclose(a, b, atol=2e-5), (step, name, (a - b).abs().max())
+        blob = opt.state_dict()
+        opt.load_state_dict(blob)
+        if rank == 0:
+            print("HYBRID_OK")
+        dist.destroy_process_group()
+        """,
+        2, tmp_path, port_base=30500,
+    )
+    assert "HYBRID_OK" in out
+
+
+def test_global_quantile_over_ranks_is_the_quantile_of_the_union(tmp_path):
+    out = _run(
+        """
+        from ohara_b200.modules.routing import global_kth_largest
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        torch.manual_seed(7)
+        everything = torch.randn(world, 300, 6) * torch.tensor([1.0, 5.0, 0.1]).view(3, 1, 1)
+        everything[:, ::11] = 0.0
+        for k in (1, 37, 450, 900):
+            got = global_kth_largest(everything[rank], k)
+            want = torch.topk(everything.reshape(-1, 6).t(), k, dim=-1).values[:, -1]
+            assert torch.equal(got, want), (k, got, want)
+        if rank == 0:
+            print("QUANTILE_OK")
+        dist.destroy_process_group()
+        """,
+        3, tmp_path, port_base=31100,
+    )
+    assert "QUANTILE_OK" in out
