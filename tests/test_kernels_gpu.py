@@ -28,6 +28,18 @@ def rel_err(got, ref):
     return (got.float() - ref.float()).abs().max().item() / (ref.float().abs().max().item() + 1e-12)
 
 
+def assert_close(got, ref, rtol, atol_rms, name=""):
+    """Element-wise ``|got - ref| <= atol + rtol * |ref|`` with ``atol = atol_rms * rms(ref)``: a
+    small-magnitude output that is wrong by its own size fails, which a comparison against the
+    global maximum alone would let through."""
+    got, ref = got.float(), ref.float()
+    atol = atol_rms * ref.square().mean().sqrt().item()
+    excess = (got - ref).abs() - (atol + rtol * ref.abs())
+    worst = excess.max().item()
+    assert worst <= 0, (f"{name}: {int((excess > 0).sum())} of {ref.numel()} elements out of "
+                        f"tolerance, worst by {worst:.3e} (atol {atol:.3e}, rtol {rtol})")
+
+
 def bf(*shape):
     return torch.randn(*shape, device="cuda").bfloat16()
 
@@ -39,6 +51,7 @@ def test_gemm_nt(C, m, n, k):
     c = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
     C.gemm(a, b, c, m, n, k, False, False)
     assert rel_err(c, a.float() @ b.float().T) < 1e-2
+    assert_close(c, a.float() @ b.float().T, 1e-2, 1e-2, "gemm_nt")  # bf16 output rounding: 2^-8
 
 
 @pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 384, 256), (2048, 768, 2048)])
@@ -47,6 +60,7 @@ def test_gemm_nn(C, m, n, k):
     c = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
     C.gemm(a, b, c, m, n, k, False, True)
     assert rel_err(c, a.float() @ b.float()) < 1e-2
+    assert_close(c, a.float() @ b.float(), 1e-2, 1e-2, "gemm_nn")
 
 
 @pytest.mark.parametrize("m,n,k,splits", [(256, 256, 512, 1), (768, 768, 8192, 8), (776, 520, 1000, 3)])
@@ -55,6 +69,7 @@ def test_gemm_tn_splitk_reduce(C, m, n, k, splits):
     c = torch.zeros(m, n, device="cuda", dtype=torch.float32)
     C.gemm(a, b, c, m, n, k, True, True, splits, True)
     assert rel_err(c, a.float().T @ b.float()) < 2e-3
+    assert_close(c, a.float().T @ b.float(), 1e-4, 1e-4, "gemm_tn")  # fp32 out: summation order only
     # reduce epilogue accumulates into existing contents
     C.gemm(a, b, c, m, n, k, True, True, splits, True)
     assert rel_err(c, 2 * (a.float().T @ b.float())) < 2e-3
@@ -204,6 +219,11 @@ ATTN_CASES = [
     (1, 1, 300, 4, 4, 128, True),
     (1, 512, 512, 8, 2, 64, False),
     (2, 1024, 1024, 6, 6, 128, True),
+    (2, 2048, 2048, 6, 6, 128, True),    # the depth-12 benchmark shape (per sequence)
+    (1, 4096, 4096, 4, 1, 128, True),    # the 1.3B shape: four query heads per KV head
+    (1, 2048, 2048, 16, 16, 64, True),   # the mixture-of-experts model's heads
+    (1, 640, 2304, 4, 2, 64, True),      # a chunk of queries against a longer cache (S > T)
+    (1, 1000, 3000, 2, 2, 128, False),   # non-causal pass over remote keys (context parallel)
 ]
 
 
@@ -222,6 +242,11 @@ def test_flash_attention_forward_backward(b, t, s, h, hk, d, causal):
     assert rel_err(q.grad, qr.grad) < 2e-2
     assert rel_err(k.grad, kr.grad) < 2e-2
     assert rel_err(v.grad, vr.grad) < 2e-2
+    # element-wise as well: probabilities and their gradients pass through bf16 (2^-8 relative)
+    # before the second product, so the error scales with the typical output, not per element
+    for name, got, want in (("out", out, ref), ("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad),
+                            ("dv", v.grad, vr.grad)):
+        assert_close(got, want, 2e-2, 4e-2, f"attention {name} {(b, t, s, h, hk, d, causal)}")
 
 
 # -- optimizer --------------------------------------------------------------------------------------
@@ -237,7 +262,13 @@ def test_newton_schulz_kernels_match_fp32(shape):
     small = min(shape[1], shape[2])
     gram = got @ got.mT if shape[1] <= shape[2] else got.mT @ got
     eye = torch.eye(small, device="cuda")
-    assert (gram - eye).abs().max().item() < 0.35
+    # five Polar-Express steps leave singular values in about [0.7, 1.2] by design (the fp32
+    # iteration itself deviates by up to ~0.3 from the identity): hold the kernels to what the
+    # fp32 iteration achieves plus a bf16 margin instead of to a fixed loose bound
+    ref_dev = ref.to("cuda")
+    ref_gram = ref_dev @ ref_dev.mT if shape[1] <= shape[2] else ref_dev.mT @ ref_dev
+    assert (gram - eye).abs().max().item() < (ref_gram - eye).abs().max().item() + 0.06
+    assert (gram - ref_gram).abs().max().item() < 0.06
 
 
 def test_grouped_moe_matches_reference_dispatch():
