@@ -349,6 +349,7 @@ DEFAULTS = {
 def main() -> None:
     p = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     p.add_argument("--op", choices=["all", *OPS], default="all")
+    p.add_argument("--ops", default=None, help="comma-separated subset of operations (one process)")
     p.add_argument("--m", type=int, default=None)
     p.add_argument("--n", type=int, default=None)
     p.add_argument("--k", type=int, default=None)
@@ -365,7 +366,13 @@ def main() -> None:
     args = p.parse_args()
     flop_peak, byte_peak = peaks()
     timer = Timer(args.iters, args.warmup)
-    for name in (OPS if args.op == "all" else [args.op]):
+    selected = list(OPS) if args.op == "all" else [args.op]
+    if args.ops:
+        selected = [name for name in args.ops.split(",") if name]
+        unknown = [name for name in selected if name not in OPS]
+        if unknown:
+            p.error("unknown operations: " + ", ".join(unknown))
+    for name in selected:
         local = argparse.Namespace(**vars(args))
         for key, value in {"batch": 32, "seq": 2048, **DEFAULTS.get(name, {})}.items():
             if getattr(local, key) is None:

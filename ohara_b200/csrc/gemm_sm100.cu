@@ -26,8 +26,9 @@
 //     transfer of tile i overlapping the math of tile i+1.
 //   `rotate` shifts the order of the M tiles so that ranks start on different peers.
 //
-// Warp roles (192 threads): warps 0-3 epilogue (TMEM lane quarter = warp index), warp 4 TMA
-// producer, warp 5 MMA issuer + TMEM allocator.
+// Warp roles: four epilogue warps (TMEM lane quarter = warp index; eight in the PAIR variant, the
+// second four draining the upper half of the columns), then the TMA producer warp, then the MMA
+// issuer + TMEM allocator warp (192 threads, 320 in the PAIR variant).
 //
 // PAIR variant (plain and batched GEMMs with N > 128): two CTAs of a cluster share one 256 x 256
 // output tile. Each loads its own 128 rows of A and one half (128 rows) of B per k-block, the
@@ -48,7 +49,17 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
-constexpr int kNumThreads = 192;
+// Epilogue warps: four cover the 128 TMEM lanes of a CTA (a warp reads lane quarter warp % 4);
+// the CTA-pair kernel runs eight, the second four taking the upper half of the tile's columns, so
+// that the drain of an accumulator takes half as long (at K = 768 the drain, not the main loop,
+// bounded the tile rate with four).
+template <bool PAIR>
+struct Roles {
+  static constexpr int kEpilogueWarps = PAIR ? 8 : 4;
+  static constexpr int kProducerWarp = kEpilogueWarps;
+  static constexpr int kMmaWarp = kEpilogueWarps + 1;
+  static constexpr int kThreads = (kEpilogueWarps + 2) * 32;
+};
 
 struct GemmParams {
   int M, N, K;
@@ -112,8 +123,8 @@ struct SmemLayout {
   static constexpr int kBRows = PAIR ? BN / 2 : BN;  // rows of B this CTA loads per k-block
   static constexpr int kBBytes = kBRows * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStagingBytes = 4 /*warps*/ * 2 /*buffers*/ * 4096;
-  static constexpr int kStages = PAIR ? 6 : ((BN == 256) ? 4 : 6);
+  static constexpr int kStagingBytes = Roles<PAIR>::kEpilogueWarps * 2 /*buffers*/ * 4096;
+  static constexpr int kStages = PAIR ? 5 : ((BN == 256) ? 4 : 6);
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
 };
@@ -146,10 +157,11 @@ __device__ __forceinline__ void load_residual(const GemmParams& p, int batch, in
 }
 
 template <int BN, bool OUT_F32, bool PAIR>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(Roles<PAIR>::kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   using L = SmemLayout<BN, PAIR>;
+  using R = Roles<PAIR>;
   constexpr int TM = PAIR ? 2 * BM : BM;  // rows of C per tile (per CTA pair when PAIR)
   constexpr int kStages = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -185,17 +197,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     mbar_init(&tmem_full[0], 1);
     mbar_init(&tmem_full[1], 1);
-    mbar_init(&tmem_empty[0], PAIR ? 8 : 4);  // epilogue warps (of both CTAs when PAIR)
-    mbar_init(&tmem_empty[1], PAIR ? 8 : 4);
+    // epilogue warps (of both CTAs when PAIR)
+    mbar_init(&tmem_empty[0], PAIR ? 2 * R::kEpilogueWarps : R::kEpilogueWarps);
+    mbar_init(&tmem_empty[1], PAIR ? 2 * R::kEpilogueWarps : R::kEpilogueWarps);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == R::kProducerWarp && lane == 0) {
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
     prefetch_tmap(&tmC);
   }
-  if (warp == 5) {
+  if (warp == R::kMmaWarp) {
     if constexpr (PAIR) {
       tmem_alloc_pair(tmem_slot, 2 * BN);
       tmem_relinquish_pair();
@@ -234,7 +247,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     k_elem_begin = k_lo;
   };
 
-  if (warp == 4) {
+  if (warp == R::kProducerWarp) {
     // ------------------------------- TMA producer -------------------------------------------
     if (lane == 0) {
       uint32_t it = 0;
@@ -313,7 +326,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == R::kMmaWarp) {
     // ------------------------------- MMA issuer ----------------------------------------------
     if (lane == 0 && cta_rank == 0) {
       const uint32_t idesc = make_idesc_bf16(TM, BN, p.a_mn != 0, p.b_mn != 0);
@@ -390,11 +403,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------- Epilogue (warps 0..3) -----------------------------------
+    // ------------------------------- Epilogue (warps 0 .. kEpilogueWarps-1) -------------------
+    // Warp w drains TMEM lanes 32 * (w % 4) .. + 31 (rows of the tile) of the column range of its
+    // group of four warps. Chunks of 128 bytes per row go TMEM -> registers -> swizzled staging
+    // buffer -> TMA store; the TMEM load of chunk i+1 is issued before chunk i is written out, so
+    // its latency hides behind the shared-memory stores and the TMA issue of chunk i.
+    const int quarter = warp & 3;
+    const int group = warp >> 2;
+    constexpr int kGroups = R::kEpilogueWarps / 4;
+    constexpr int kGroupCols = BN / kGroups;
     uint8_t* my_staging = staging + warp * 2 * 4096;
     uint32_t tile_iter = 0;
     uint32_t store_iter = 0;
     constexpr int kColsPerStore = OUT_F32 ? 32 : 64;
+    const bool has_residual = p.R != nullptr;
     for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
       int batch, mt, nt, kb_begin, kb_count, k0;
       decode(tile, batch, mt, nt, kb_begin, kb_count, k0);
@@ -404,65 +426,101 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!mbar_wait(&tmem_full[acc], acc_phase, wctx, kTimeoutTmemFull)) break;
       tcgen05_fence_after();
       const bool skip_store = (kb_count == 0) && p.reduce;
-      const uint32_t taddr_row = tmem_base + acc * BN + (static_cast<uint32_t>(warp * 32) << 16);
-      const int row0 = mt * TM + (int)cta_rank * BM + warp * 32;
+      const bool have_acc = kb_count > 0;
+      const uint32_t taddr_row =
+          tmem_base + acc * BN + group * kGroupCols + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int row0 = mt * TM + (int)cta_rank * BM + quarter * 32;
+      const int col_base = nt * BN + group * kGroupCols;
+      // columns of this group that exist (uniform across the warp)
+      const int cols_here = min(kGroupCols, p.N - col_base);
+      const int chunks = cols_here > 0 ? (cols_here + kColsPerStore - 1) / kColsPerStore : 0;
+      // Units of 32 columns: one TMEM load each; a 128-byte row segment of the output is one unit
+      // of fp32 or two units of bf16.
+      constexpr int kUnitsPerStore = OUT_F32 ? 1 : 2;
+      constexpr int kWordsPerUnit = OUT_F32 ? 32 : 16;
+      const int units = chunks * kUnitsPerStore;
+      uint32_t v[32];
+      if (units > 0 && have_acc) tmem_ld_32x32(taddr_row, v);
+      bool released = false;
+      uint8_t* buf = nullptr;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += kColsPerStore) {
-        const int col0 = nt * BN + c0;
-        if (col0 >= p.N) break;  // uniform across the warp
-        uint8_t* buf = my_staging + (store_iter & 1) * 4096;
-        if (lane == 0) tma_store_wait_read<1>();
-        __syncwarp();
-        uint8_t* my_row = buf + lane * 128;
-        if constexpr (OUT_F32) {
-          uint32_t v[32];
-          if (kb_count > 0) {
-            tmem_ld_32x32(taddr_row + c0, v);
-            tmem_ld_wait();
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0;
-          }
-          float res[32];
-          load_residual<32>(p, batch, row0 + lane, col0, res);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 o;
-            o.x = __uint_as_float(v[4 * j + 0]) * p.alpha + res[4 * j + 0];
-            o.y = __uint_as_float(v[4 * j + 1]) * p.alpha + res[4 * j + 1];
-            o.z = __uint_as_float(v[4 * j + 2]) * p.alpha + res[4 * j + 2];
-            o.w = __uint_as_float(v[4 * j + 3]) * p.alpha + res[4 * j + 3];
-            *reinterpret_cast<float4*>(my_row + ((j ^ (lane & 7)) << 4)) = o;
-          }
+      for (int unit = 0; unit < units; ++unit) {
+        const int c0 = unit * 32;
+        const int col0 = col_base + c0;
+        uint32_t packed[kWordsPerUnit];
+        if (have_acc) {
+          tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t v[32];
-            if (kb_count > 0) {
-              tmem_ld_32x32(taddr_row + c0 + h * 32, v);
-              tmem_ld_wait();
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = 0;
-            }
-            float res[32];
-            load_residual<32>(p, batch, row0 + lane, col0 + h * 32, res);
+          for (int i = 0; i < 32; ++i) v[i] = 0;
+        }
+        if constexpr (OUT_F32) {
+          if (has_residual) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              uint4 o;
-              o.x = pack_bf16(__uint_as_float(v[8 * j + 0]) * p.alpha + res[8 * j + 0],
-                              __uint_as_float(v[8 * j + 1]) * p.alpha + res[8 * j + 1]);
-              o.y = pack_bf16(__uint_as_float(v[8 * j + 2]) * p.alpha + res[8 * j + 2],
-                              __uint_as_float(v[8 * j + 3]) * p.alpha + res[8 * j + 3]);
-              o.z = pack_bf16(__uint_as_float(v[8 * j + 4]) * p.alpha + res[8 * j + 4],
-                              __uint_as_float(v[8 * j + 5]) * p.alpha + res[8 * j + 5]);
-              o.w = pack_bf16(__uint_as_float(v[8 * j + 6]) * p.alpha + res[8 * j + 6],
-                              __uint_as_float(v[8 * j + 7]) * p.alpha + res[8 * j + 7]);
-              const int chunk = h * 4 + j;
-              *reinterpret_cast<uint4*>(my_row + ((chunk ^ (lane & 7)) << 4)) = o;
+              float res[8];
+              load_residual<8>(p, batch, row0 + lane, col0 + 8 * j, res);
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                packed[8 * j + i] =
+                    __float_as_uint(__uint_as_float(v[8 * j + i]) * p.alpha + res[i]);
             }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              packed[i] = __float_as_uint(__uint_as_float(v[i]) * p.alpha);
+          }
+        } else {
+          if (has_residual) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float res[8];
+              load_residual<8>(p, batch, row0 + lane, col0 + 8 * j, res);
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                packed[4 * j + i] =
+                    pack_bf16(__uint_as_float(v[8 * j + 2 * i]) * p.alpha + res[2 * i],
+                              __uint_as_float(v[8 * j + 2 * i + 1]) * p.alpha + res[2 * i + 1]);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              packed[i] = pack_bf16(__uint_as_float(v[2 * i]) * p.alpha,
+                                    __uint_as_float(v[2 * i + 1]) * p.alpha);
           }
         }
+        // The values of this unit now live in `packed`: start the next unit's TMEM load, or,
+        // after the last one, hand the accumulator back before the stores are even issued.
+        if (unit + 1 < units) {
+          if (have_acc) tmem_ld_32x32(taddr_row + c0 + 32, v);
+        } else {
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (PAIR)
+              mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));  // the leader's barrier
+            else
+              mbar_arrive(&tmem_empty[acc]);
+          }
+          released = true;
+        }
+        const int part = unit % kUnitsPerStore;  // which part of the 128-byte row segment
+        if (part == 0) {
+          buf = my_staging + (store_iter & 1) * 4096;
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+        }
+        uint8_t* my_row = buf + lane * 128;
+        constexpr int kVecsPerUnit = kWordsPerUnit / 4;  // 16-byte pieces of this unit
+#pragma unroll
+        for (int j = 0; j < kVecsPerUnit; ++j) {
+          const uint4 o = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2],
+                                     packed[4 * j + 3]);
+          const int piece = part * kVecsPerUnit + j;
+          *reinterpret_cast<uint4*>(my_row + ((piece ^ (lane & 7)) << 4)) = o;
+        }
+        if (part + 1 < kUnitsPerStore && unit + 1 < units) continue;  // segment not complete yet
+        const int seg_col0 = col0 - part * 32;  // first column of the 128-byte segment
         if (p.comm_mode == 2) {
           // Row block `owner` of C goes to that rank's receive slot. The 32 x 128-byte chunk is
           // read back from the staging buffer so that eight lanes store one whole 128-byte row
@@ -471,13 +529,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int owner = row0 / p.rows_per_rank;
           __nv_bfloat16* slot = p.c_peer[owner] + (long long)(row0 - owner * p.rows_per_rank) * p.c_peer_ld;
           const int sub = lane & 7;
-          const int col = col0 + sub * 8;
+          const int col = seg_col0 + sub * 8;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int r = (lane >> 3) + 4 * i;
-            const uint4 v = *reinterpret_cast<const uint4*>(buf + r * 128 + ((sub ^ (r & 7)) << 4));
+            const uint4 w = *reinterpret_cast<const uint4*>(buf + r * 128 + ((sub ^ (r & 7)) << 4));
             if (row0 + r < p.M && col < p.N)
-              *reinterpret_cast<uint4*>(slot + (long long)r * p.c_peer_ld + col) = v;
+              *reinterpret_cast<uint4*>(slot + (long long)r * p.c_peer_ld + col) = w;
           }
           __syncwarp();
           ++store_iter;
@@ -487,21 +545,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncwarp();
         if (lane == 0 && !skip_store && row0 < p.M) {
           if (p.reduce)
-            tma_reduce_add_3d(&tmC, buf, col0, row0, batch);
+            tma_reduce_add_3d(&tmC, buf, seg_col0, row0, batch);
           else
-            tma_store_3d(&tmC, buf, col0, row0, batch);
+            tma_store_3d(&tmC, buf, seg_col0, row0, batch);
           tma_store_commit();
         }
         ++store_iter;
       }
-      // All TMEM reads of this accumulator are complete (tmem_ld_wait above): hand it back.
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (PAIR)
-          mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));  // the leader's barrier
-        else
-          mbar_arrive(&tmem_empty[acc]);
+      if (!released) {
+        // no column of this group exists in this tile: nothing was read, release at once
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (PAIR)
+            mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+          else
+            mbar_arrive(&tmem_empty[acc]);
+        }
       }
       ++tile_iter;
     }
@@ -518,7 +578,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   // A CTA of a pair must outlive every access of its peer to its shared memory and barriers.
   if constexpr (PAIR) cluster_sync_all();
-  if (warp == 5) {
+  if (warp == R::kMmaWarp) {
     tcgen05_fence_after();
     if constexpr (PAIR)
       tmem_dealloc_pair(tmem_base, 2 * BN);
@@ -533,7 +593,7 @@ void launch_variant(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensor
   using L = SmemLayout<BN>;
   auto kernel = gemm_bf16_kernel<BN, OUT_F32, false>;
   ensure_dynamic_smem((const void*)kernel, L::kTotal);
-  kernel<<<grid, kNumThreads, L::kTotal, stream>>>(tA, tB, tC, p);
+  kernel<<<grid, Roles<false>::kThreads, L::kTotal, stream>>>(tA, tB, tC, p);
   OB_LAUNCH_CHECK();
 }
 
@@ -555,7 +615,7 @@ void launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
-  config.blockDim = dim3(kNumThreads, 1, 1);
+  config.blockDim = dim3(Roles<true>::kThreads, 1, 1);
   config.dynamicSmemBytes = L::kTotal;
   config.stream = stream;
   config.attrs = attr;
