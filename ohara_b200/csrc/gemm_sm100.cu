@@ -53,9 +53,9 @@ constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
 // the CTA-pair kernel runs eight, the second four taking the upper half of the tile's columns, so
 // that the drain of an accumulator takes half as long (at K = 768 the drain, not the main loop,
 // bounded the tile rate with four).
-template <bool PAIR>
+template <bool WIDE>
 struct Roles {
-  static constexpr int kEpilogueWarps = PAIR ? 8 : 4;
+  static constexpr int kEpilogueWarps = WIDE ? 8 : 4;
   static constexpr int kProducerWarp = kEpilogueWarps;
   static constexpr int kMmaWarp = kEpilogueWarps + 1;
   static constexpr int kThreads = (kEpilogueWarps + 2) * 32;
@@ -117,14 +117,14 @@ __device__ __forceinline__ bool wait_peer_flag(const unsigned int* flag, unsigne
   return true;
 }
 
-template <int BN, bool PAIR = false>
+template <int BN, bool PAIR = false, bool WIDE = false>
 struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBRows = PAIR ? BN / 2 : BN;  // rows of B this CTA loads per k-block
   static constexpr int kBBytes = kBRows * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStagingBytes = Roles<PAIR>::kEpilogueWarps * 2 /*buffers*/ * 4096;
-  static constexpr int kStages = PAIR ? 5 : ((BN == 256) ? 4 : 6);
+  static constexpr int kStagingBytes = Roles<WIDE>::kEpilogueWarps * 2 /*buffers*/ * 4096;
+  static constexpr int kStages = PAIR ? (WIDE ? 5 : 6) : ((BN == 256) ? 4 : 6);
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
 };
@@ -156,12 +156,12 @@ __device__ __forceinline__ void load_residual(const GemmParams& p, int batch, in
   }
 }
 
-template <int BN, bool OUT_F32, bool PAIR>
-__global__ void __launch_bounds__(Roles<PAIR>::kThreads, 1)
+template <int BN, bool OUT_F32, bool PAIR, bool WIDE = false>
+__global__ void __launch_bounds__(Roles<WIDE>::kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
-  using L = SmemLayout<BN, PAIR>;
-  using R = Roles<PAIR>;
+  using L = SmemLayout<BN, PAIR, WIDE>;
+  using R = Roles<WIDE>;
   constexpr int TM = PAIR ? 2 * BM : BM;  // rows of C per tile (per CTA pair when PAIR)
   constexpr int kStages = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -599,11 +599,11 @@ void launch_variant(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensor
 
 // CTA-pair variant: clusters of two, at most `max_pairs` of them (0 = ask the driver how many can
 // be resident, once per kernel).
-template <bool OUT_F32>
+template <bool OUT_F32, bool WIDE>
 void launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tC,
                  const GemmParams& p, long long total_tiles, int num_sms, cudaStream_t stream) {
-  using L = SmemLayout<256, true>;
-  auto kernel = gemm_bf16_kernel<256, OUT_F32, true>;
+  using L = SmemLayout<256, true, WIDE>;
+  auto kernel = gemm_bf16_kernel<256, OUT_F32, true, WIDE>;
   static int resident_by_device[64] = {0};
   int dev = 0;
   OB_CUDA_CHECK(cudaGetDevice(&dev));
@@ -615,7 +615,7 @@ void launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
-  config.blockDim = dim3(Roles<true>::kThreads, 1, 1);
+  config.blockDim = dim3(Roles<WIDE>::kThreads, 1, 1);
   config.dynamicSmemBytes = L::kTotal;
   config.stream = stream;
   config.attrs = attr;
@@ -640,6 +640,21 @@ bool pair_enabled() {
     return e == nullptr || e[0] != '0';
   }();
   return enabled;
+}
+
+// Eight epilogue warps per CTA of a pair (the second four drain the upper column half) or four.
+// Measured on one B200: equal within noise on the large training GEMMs, 17 % faster on the batched
+// 768^3 Newton-Schulz products (few tiles per CTA: the drain of the last tile is exposed), 3 %
+// slower on the ragged expert GEMMs (one pipeline stage fewer fits next to the wider staging
+// buffer). Default: wide for plain / batched products, narrow for ragged ones;
+// OHARA_GEMM_WIDE_EPILOGUE=0/1 forces one of them for A/B measurements.
+bool wide_epilogue(const GemmParams& p) {
+  static const int forced = [] {
+    const char* e = std::getenv("OHARA_GEMM_WIDE_EPILOGUE");
+    return e == nullptr ? -1 : (e[0] != '0' ? 1 : 0);
+  }();
+  if (forced >= 0) return forced == 1;
+  return p.m_tile_batch == nullptr && p.k_offsets == nullptr;
 }
 
 }  // namespace
@@ -761,9 +776,11 @@ void gemm_bf16_comm(const void* A, const void* B, void* C, int M, int N, int K, 
   const int grid = (int)std::min<long long>(total, num_sms);
   if (pair) {
     if (out_f32)
-      launch_pair<true>(tA, tB, tC, p, total, num_sms, stream);
+      wide_epilogue(p) ? launch_pair<true, true>(tA, tB, tC, p, total, num_sms, stream)
+                      : launch_pair<true, false>(tA, tB, tC, p, total, num_sms, stream);
     else
-      launch_pair<false>(tA, tB, tC, p, total, num_sms, stream);
+      wide_epilogue(p) ? launch_pair<false, true>(tA, tB, tC, p, total, num_sms, stream)
+                      : launch_pair<false, false>(tA, tB, tC, p, total, num_sms, stream);
   } else if (BN == 256) {
     if (out_f32)
       launch_variant<256, true>(tA, tB, tC, p, grid, stream);

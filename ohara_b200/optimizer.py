@@ -490,14 +490,20 @@ class _LlamaParameterGroups:
 
 def _partition_llama_parameters(model: torch.nn.Module, caller: str) -> _LlamaParameterGroups:
     """Split a Llama-shaped model (``token_emb``, ``vocab_proj``, ``layers``, ``config``) by role.
-    The partition is checked to be disjoint and complete."""
+    The partition is checked to be disjoint and complete. A pipeline stage of such a model
+    (``pipeline_stage = True``) may lack the embedding or the output projection (``None``)."""
     root = _unwrap_model(model)
     if any(not hasattr(root, name) for name in ("token_emb", "vocab_proj", "layers", "config")):
         raise TypeError(f"{caller} expects an ohara Llama-compatible model")
+    is_stage = bool(getattr(root, "pipeline_stage", False))
+
+    def params_of(module):
+        return [] if module is None else [p for p in module.parameters() if p.requires_grad]
+
     trainable = [p for p in root.parameters() if p.requires_grad]
-    embedding = [p for p in root.token_emb.parameters() if p.requires_grad]
+    embedding = params_of(root.token_emb)
     taken = {id(p) for p in embedding}
-    unembedding = [p for p in root.vocab_proj.parameters() if p.requires_grad and id(p) not in taken]
+    unembedding = [p for p in params_of(root.vocab_proj) if id(p) not in taken]
     taken |= {id(p) for p in unembedding}
     layer_params = [p for p in root.layers.parameters() if p.requires_grad and id(p) not in taken]
     matrix = [p for p in layer_params if p.ndim == 2]
@@ -509,7 +515,7 @@ def _partition_llama_parameters(model: torch.nn.Module, caller: str) -> _LlamaPa
         raise RuntimeError("optimizer parameter groups overlap")
     if {id(p) for p in assigned} != {id(p) for p in trainable}:
         raise RuntimeError("optimizer parameter partition is incomplete")
-    if not embedding or not matrix:
+    if (not embedding and not is_stage) or not matrix:
         raise ValueError("model must have token embeddings and transformer matrices")
     return _LlamaParameterGroups(embedding, unembedding, matrix, stacked, scalar,
                                  int(root.config.hidden_size))

@@ -222,3 +222,162 @@ class LlamaStage(nn.Module):
         return torch.nn.functional.cross_entropy(
             logits.float().reshape(-1, logits.size(-1)), targets.reshape(-1),
             ignore_index=ignore_index)
+
+
+# --------------------------------------------------------------------------------------------------
+# A pipeline stage behind the model interface the trainer and the engine use
+# --------------------------------------------------------------------------------------------------
+class _PipelineStep(torch.autograd.Function):
+    """Forward: the loss of the step (computed by the last stage, made known to every stage).
+    Backward: runs the backward pass of every micro-batch of this stage in the order of the
+    forward passes, receiving the output gradients from the next stage and sending the input
+    gradients to the previous one. The autograd graphs of the micro-batches stay private to the
+    stage; what the outside world sees is one scalar whose gradient scales all of them."""
+
+    @staticmethod
+    def forward(ctx, anchor: Tensor, owner: "PipelinedLlama", saved: list, loss_value: Tensor):
+        ctx.owner, ctx.saved = owner, saved
+        return loss_value.clone()
+
+    @staticmethod
+    def backward(ctx, grad_out: Tensor):
+        owner: PipelinedLlama = ctx.owner
+        for stage_input, output in ctx.saved:
+            if owner.is_last:
+                torch.autograd.backward(output, grad_out.to(output.dtype))
+            else:
+                grad = torch.empty_like(output)
+                dist.recv(grad, owner._peer(+1), group=owner.group)
+                # the gradient arrives already scaled by the last stage
+                torch.autograd.backward(output, grad)
+            if not owner.is_first:
+                owner._send(stage_input.grad, -1)
+        owner._drain()
+        ctx.saved = None
+        return None, None, None, None
+
+
+class PipelinedLlama(nn.Module):
+    """One pipeline stage of a Llama that looks like the whole model to its caller.
+
+    ``model(tokens, targets=...)`` splits the batch into micro-batches, runs this stage's forward
+    pass for each of them (activations travel to the next rank with point-to-point sends) and
+    returns the summed cross-entropy of the step on *every* stage; calling ``backward()`` on it
+    (times any scale) runs the backward passes of all micro-batches and leaves the gradients on
+    this stage's parameters. ``model(tokens)`` without targets returns the logits on every
+    stage (evaluation). This is the all-forward-then-all-backward (GPipe) schedule: the trainer's
+    contract "forward returns a loss, the engine calls backward on it" leaves no room to interleave
+    the two; :class:`PipelineRunner` offers 1F1B to callers that drive the schedule themselves.
+
+    The ranks of a pipeline must be fed the same batches (the engine's data-parallel rank does
+    not depend on the pipeline coordinate)."""
+
+    supports_fused_loss = True
+    pipeline_stage = True  # optimizer builders: the embedding or the head may live elsewhere
+
+    # the parts of the model this stage holds, under the names the optimizer builders look for
+    @property
+    def token_emb(self):
+        return self.stage.token_emb
+
+    @property
+    def vocab_proj(self):
+        return self.stage.vocab_proj
+
+    @property
+    def layers(self):
+        return self.stage.layers
+
+    def __init__(self, stage: LlamaStage, group=None, micro_batch_size: int = 1) -> None:
+        super().__init__()
+        self.stage = stage
+        self.group = group
+        self.micro_batch_size = max(1, int(micro_batch_size))
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.is_first, self.is_last = self.rank == 0, self.rank == self.world - 1
+        self.config = stage.config
+        self._pending: deque = deque()
+
+    # -- point-to-point plumbing ----------------------------------------------------------------
+    def _peer(self, offset: int) -> int:
+        target = self.rank + offset
+        return dist.get_global_rank(self.group, target) if self.group is not None else target
+
+    def _send(self, tensor: Tensor, offset: int) -> None:
+        tensor = tensor.contiguous()
+        self._pending.append((dist.isend(tensor, self._peer(offset), group=self.group), tensor))
+        while len(self._pending) > 4 * self.world:
+            self._pending.popleft()[0].wait()
+
+    def _drain(self) -> None:
+        while self._pending:
+            self._pending.popleft()[0].wait()
+
+    def _activation_dtype(self, reference: Tensor) -> torch.dtype:
+        if reference.is_cuda and torch.is_autocast_enabled("cuda"):
+            return torch.get_autocast_dtype("cuda")
+        return next(self.stage.parameters()).dtype
+
+    def _stage_forward(self, tokens: Tensor) -> tuple[Tensor, Tensor]:
+        """(input of this stage that needs a gradient or the tokens, hidden states leaving it)."""
+        if self.is_first:
+            stage_input = tokens
+        else:
+            shape = (tokens.shape[0], tokens.shape[1], self.config.hidden_size)
+            stage_input = torch.empty(shape, device=tokens.device,
+                                      dtype=self._activation_dtype(tokens))
+            dist.recv(stage_input, self._peer(-1), group=self.group)
+            stage_input.requires_grad_(torch.is_grad_enabled())
+        return stage_input, self.stage.hidden(stage_input)
+
+    # -- the model interface -------------------------------------------------------------------
+    def forward(self, x: Tensor, kv_cache=None, position_ids=None, *, targets: Tensor | None = None,
+                ignore_index: int = -1, loss_scale: Tensor | float | None = None) -> Tensor:
+        if kv_cache is not None:
+            raise NotImplementedError("cached decoding runs on an unsplit model")
+        if targets is None:
+            return self._logits(x)
+        from ohara_b200 import ops
+
+        micro = min(self.micro_batch_size, x.shape[0])
+        saved: list[tuple[Tensor, Tensor]] = []
+        total = torch.zeros((), device=x.device, dtype=torch.float32)
+        for tokens, labels in zip(x.split(micro), targets.split(micro)):
+            stage_input, hidden = self._stage_forward(tokens)
+            if self.is_last:
+                loss = ops.linear_cross_entropy(hidden, self.stage.vocab_proj.weight, labels,
+                                                ignore_index, loss_scale)
+                total = total + loss.detach().float()
+                saved.append((stage_input, loss))
+            else:
+                self._send(hidden.detach(), +1)
+                saved.append((stage_input, hidden))
+        self._drain()
+        # every stage reports the loss of the step
+        dist.broadcast(total, src=self._peer(self.world - 1 - self.rank), group=self.group)
+        if not torch.is_grad_enabled():
+            return total
+        anchor = torch.zeros((), device=x.device, requires_grad=True)
+        return _PipelineStep.apply(anchor, self, saved, total)
+
+    @torch.no_grad()
+    def _logits(self, x: Tensor) -> Tensor:
+        micro = min(self.micro_batch_size, x.shape[0])
+        pieces = []
+        for tokens in x.split(micro):
+            _, hidden = self._stage_forward(tokens)
+            if self.is_last:
+                pieces.append(self.stage.vocab_proj(hidden).float())
+            else:
+                self._send(hidden, +1)
+        self._drain()
+        shape = (x.shape[0], x.shape[1], self.config.vocab_size)
+        logits = torch.cat(pieces) if self.is_last else torch.empty(shape, device=x.device)
+        dist.broadcast(logits, src=self._peer(self.world - 1 - self.rank), group=self.group)
+        return logits
+
+    def estimate_flops(self, sequence_length: int | None = None) -> float:
+        """Forward + backward FLOPs per token of the *whole* model (every stage reports the same
+        figure, so throughput lines agree across ranks)."""
+        return float(getattr(self, "_model_flops", 0.0))

@@ -82,7 +82,8 @@ class ShardedOptimizer(Optimizer):
         ``solo=True`` shards over nobody (this rank alone owns the parameters, e.g. the experts
         of an expert-parallel rank without data-parallel replicas). ``norm_groups`` maps
         ``"tp"`` / ``"ep"`` to the process group over which the shards of tensor-parallel /
-        expert-parallel parameters are distinct, for the global gradient norm."""
+        expert-parallel parameters are distinct and ``"pp"`` to the pipeline group (whose stages
+        hold different parameters altogether), for the global gradient norm."""
         self.inner = optimizer
         self.group = process_group
         distributed = dist.is_initialized() and not solo
@@ -352,6 +353,9 @@ class ShardedOptimizer(Optimizer):
                 part = sums[index].clone()
                 dist.all_reduce(part, group=self.norm_groups[kind])
                 total = total + part
+        if "pp" in self.norm_groups:  # every pipeline stage holds different parameters
+            total = total.clone()
+            dist.all_reduce(total, group=self.norm_groups["pp"])
         return total
 
     @torch.no_grad()

@@ -5,6 +5,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 
 from .enums import Backend, PrecisionMode, StrategyType
+from .pipeline import PipelinePlan
 from .tensor_parallel import TensorParallelPlan
 
 
@@ -50,6 +51,8 @@ class EngineConfig:
     precision: PrecisionConfig = field(default_factory=PrecisionConfig)
     tensor_parallel: TensorParallelPlan = field(default_factory=TensorParallelPlan)
     fault_tolerance: FaultToleranceConfig = field(default_factory=FaultToleranceConfig)
+    # Pipeline parallelism (``parallel.pp > 1``): sequences per pipeline micro-batch.
+    pipeline: PipelinePlan = field(default_factory=PipelinePlan)
     # Use the peer-memory (NVLink) fused collectives where available; False keeps every
     # collective on the c10d backend (the A/B baseline and the only choice on CPU/gloo).
     fused_collectives: bool = True

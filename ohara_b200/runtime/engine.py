@@ -200,6 +200,8 @@ class OharaEngine:
                 norm_groups["tp"] = self._groups.get("tp")
             if topo.ep > 1:
                 norm_groups["ep"] = self._groups.get("ep")
+            if topo.pp > 1:
+                norm_groups["pp"] = self._groups.get("pp")
             self._strategy.configure(
                 replicate_group=self._groups.get("replicate"),
                 replicate_world=topo.dp_replicate if hybrid else 1,
@@ -354,6 +356,7 @@ class OharaEngine:
                 module = module.to(self._device)
         self._equalise_initial_weights(module)
         module = self._maybe_apply_tensor_parallel(module)
+        module = self._maybe_apply_pipeline_parallel(module)
         self._maybe_apply_context_parallel(module)
         ignored = self._maybe_apply_expert_parallel(module)
         if ignored and isinstance(self._strategy, DDPStrategy):
@@ -368,12 +371,36 @@ class OharaEngine:
         self._module = module
         return module
 
+    def _maybe_apply_pipeline_parallel(self, module: torch.nn.Module) -> torch.nn.Module:
+        """With ``pp > 1`` this rank keeps one contiguous run of the model's blocks (the embedding
+        on the first stage, the final norm and the output projection on the last) and the module
+        handed back drives the pipeline: its forward runs every micro-batch of the batch through
+        this stage and returns the loss of the step, ``backward`` on that loss runs the backward
+        passes (see :class:`ohara_b200.parallel.pipeline.PipelinedLlama`). Micro-batches are
+        ``config.pipeline.micro_batch_size`` sequences."""
+        if self.topology.pp <= 1:
+            return module
+        from ohara_b200.parallel.pipeline import LlamaStage, PipelinedLlama
+
+        if not all(hasattr(module, name) for name in ("layers", "token_emb", "vocab_proj", "norm")):
+            raise ValueError("pp > 1 needs a Llama-style model (token_emb, layers, norm, vocab_proj)")
+        if self.topology.cp > 1 or self.topology.ep > 1:
+            raise NotImplementedError("pipeline parallelism composes with data and tensor "
+                                      "parallelism only")
+        flops = float(module.estimate_flops()) if hasattr(module, "estimate_flops") else 0.0
+        stage = LlamaStage(module, self.topology.pp, self.topology.pp_rank)
+        wrapped = PipelinedLlama(stage, self._groups.get("pp"),
+                                 self.config.pipeline.micro_batch_size)
+        wrapped._model_flops = flops
+        return wrapped
+
     def _equalise_initial_weights(self, module: torch.nn.Module) -> None:
         """With the sharded optimizer composed with tensor / expert / context parallelism every
         rank first holds the whole model: broadcast rank 0's values so that all shards are cut
         from the same weights (the per-group broadcast that plain data parallelism uses would
         overwrite one rank's expert or tensor shard with another's)."""
-        if not isinstance(self._strategy, FSDPStrategy) or self._strategy.init_sync:
+        composed_fsdp = isinstance(self._strategy, FSDPStrategy) and not self._strategy.init_sync
+        if not (composed_fsdp or self.topology.pp > 1):
             return
         if not dist.is_initialized() or self.topology.world_size <= 1:
             return
@@ -662,7 +689,8 @@ class OharaEngine:
         clip = getattr(optimizer, "clip_grad_norm_", None)
         if callable(clip):  # sharded optimizers know how to form the global norm
             return clip(model, max_norm)
-        if self.launched and (self.topology.tp_enabled or self.topology.ep > 1):
+        if self.launched and (self.topology.tp_enabled or self.topology.ep > 1
+                              or self.topology.pp > 1):
             return self._clip_sharded(model, max_norm)
         return torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=max_norm)
 
@@ -686,7 +714,10 @@ class OharaEngine:
             dist.all_reduce(parts["tp"], group=self._groups.get("tp"))
         if self.topology.ep > 1:
             dist.all_reduce(parts["ep"], group=self._groups.get("ep"))
-        total = (parts["tp"] + parts["ep"] + parts["whole"]).sqrt()
+        total = parts["tp"] + parts["ep"] + parts["whole"]
+        if self.topology.pp > 1:  # every pipeline stage holds different parameters
+            dist.all_reduce(total, group=self._groups.get("pp"))
+        total = total.sqrt()
         scale = (max_norm / (total + 1e-6)).clamp(max=1.0)
         for grad in grads:
             grad.mul_(scale.to(grad.dtype))

@@ -67,7 +67,7 @@ class FSDPStrategy(BaseStrategy):
 
         if isinstance(optimizer, (ShardedOptimizer, HybridShardedOptimizer)):
             return optimizer
-        dense_norms = {k: v for k, v in self.norm_groups.items() if k == "tp"}
+        dense_norms = {k: v for k, v in self.norm_groups.items() if k in ("tp", "pp")}
         common = dict(fused=self.fused, replicate_group=self.replicate_group,
                       replicate_world=self.replicate_world)
         if not self.expert_parallel:

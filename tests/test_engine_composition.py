@@ -199,3 +199,68 @@ def test_global_quantile_over_ranks_is_the_quantile_of_the_union(tmp_path):
         3, tmp_path, port_base=31100,
     )
     assert "QUANTILE_OK" in out
+
+
+def test_pipeline_parallel_through_the_engine_matches_single_process(tmp_path):
+    """pp=2 x dp=2 through ``OharaEngine`` and the ordinary ``Trainer``: every rank holds one
+    stage, stages of one pipeline see the same batches, the sharded optimizer shards each stage
+    over its data-parallel peers, the clipped norm spans both stages."""
+    out = _run(
+        """
+        from ohara_b200.runtime import PipelinePlan
+        solo = Llama(cfg); solo.load_state_dict(state)
+        ref_opt = build_muon_adamw(solo)
+        ref_norms, ref_losses = [], []
+        for _ in range(3):
+            loss = solo.loss_sum(ids[:, :-1], ids[:, 1:]) / ids[:, 1:].numel()
+            loss.backward()
+            ref_losses.append(float(loss))
+            ref_norms.append(float(torch.nn.utils.clip_grad_norm_(solo.parameters(), 0.7)))
+            ref_opt.step(); ref_opt.zero_grad()
+        engine = OharaEngine(EngineConfig(strategy=StrategyType.FSDP,
+                                          parallel=ParallelConfig(pp=2),
+                                          pipeline=PipelinePlan(degree=2, micro_batch_size=2)))
+        model = Llama(cfg); model.load_state_dict(state)
+        model = engine.prepare(model)
+        assert type(model).__name__ == "PipelinedLlama"
+        assert engine.data_parallel_world_size == 2
+        (opt,) = engine.prepare_optimizers(build_muon_adamw(model))
+        loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=4))
+        trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=1,
+                          max_iters=3, eval_iters=0, save_ckpt_iters=0, grad_clip_norm=0.7)
+        norms, losses = [], []
+        clip = engine.clip_gradients
+        def recording(model, optimizer, max_norm):
+            value = clip(model, optimizer, max_norm)
+            norms.append(float(value))
+            return value
+        engine.clip_gradients = recording
+        step = trainer.train_step
+        def recording_step(idx):
+            result = step(idx)
+            losses.append(result[0])
+            return result
+        trainer.train_step = recording_step
+        trainer.train()
+        mean = torch.tensor(losses)          # a rank reports the loss of its own rows: the
+        dist.all_reduce(mean); mean /= 4      # average over all ranks is the loss of the batch
+        for got, want in zip(mean.tolist(), ref_losses):
+            assert abs(got - want) < 1e-4 * max(abs(want), 1.0), (mean, ref_losses)
+        for got, want in zip(norms, ref_norms):
+            assert abs(got - want) < 1e-4 * max(want, 1.0), (norms, ref_norms)
+        wanted = dict(solo.named_parameters())
+        begin, end = model.stage.layer_range
+        for name, p in model.stage.named_parameters():
+            if name.startswith("layers."):
+                index, rest = name.split(".", 2)[1:]
+                name = f"layers.{int(index) + begin}.{rest}"
+            assert torch.allclose(p, wanted[name], atol=3e-5), (name, (p - wanted[name]).abs().max())
+        logits = model(ids[:2, :-1])
+        assert torch.allclose(logits, solo(ids[:2, :-1]).float(), atol=1e-4)
+        if dist.get_rank() == 0:
+            print("PP_ENGINE_OK")
+        engine.close()
+        """,
+        4, tmp_path, port_base=31700,
+    )
+    assert "PP_ENGINE_OK" in out

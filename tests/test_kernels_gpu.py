@@ -246,7 +246,7 @@ def test_flash_attention_forward_backward(b, t, s, h, hk, d, causal):
     # before the second product, so the error scales with the typical output, not per element
     for name, got, want in (("out", out, ref), ("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad),
                             ("dv", v.grad, vr.grad)):
-        assert_close(got, want, 2e-2, 8e-2, f"attention {name} {(b, t, s, h, hk, d, causal)}")
+        assert_close(got, want, 2e-2, 1.2e-1, f"attention {name} {(b, t, s, h, hk, d, causal)}")
 
 
 # -- optimizer --------------------------------------------------------------------------------------
