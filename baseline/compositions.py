@@ -219,10 +219,12 @@ class ContextParallelEngine(_NoSyncMixin, _reference_engine_class()):
 
         if isinstance(value, (tuple, list)) and len(value) == 2:
             data = value[0].to(self._device, non_blocking=True)
-            target = value[1].to(self._device, non_blocking=True).clone()
-            with context_parallel(self._cp_mesh, buffers=[target], buffer_seq_dims=[1],
-                                  no_restore_buffers={target}):
-                pass
+            target = value[1].to(self._device, non_blocking=True)
+            if target.shape[1] == self._spec["seq_len"]:  # not cut yet (loaders call this too)
+                target = target.clone()
+                with context_parallel(self._cp_mesh, buffers=[target], buffer_seq_dims=[1],
+                                      no_restore_buffers={target}):
+                    pass
             return type(value)((data, target))
         return super().to_device(value)
 

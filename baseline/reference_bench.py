@@ -93,6 +93,12 @@ def run(args, spec: dict, clock_sampler) -> dict:
         optimizer = build_adamw(model, learning_rate=learning_rate, weight_decay=0.1,
                                 betas=(0.9, 0.95))
 
+    if any(type(p).__name__ == "DTensor" for p in model.parameters()) and not all(
+            type(p).__name__ == "DTensor" for p in model.parameters()):
+        # tensor parallel without a sharded data-parallel dimension leaves plain tensors next to
+        # DTensors, which the multi-tensor optimizer path cannot mix
+        for group in optimizer.param_groups:
+            group["foreach"] = False
     dp_rank, dp_world = compositions.data_rank(engine)
 
     def uniform_rows(gen):

@@ -563,10 +563,8 @@ void launch_bwd(const void* q, const void* k, const void* v, const void* d_o, fl
   make4(&tK, k, TmapDtype::BF16, Hk, S, strides[2], strides[3], 64, kKeys, TmapSwizzle::B128);
   make4(&tV, v, TmapDtype::BF16, Hk, S, strides[4], strides[5], 64, kKeys, TmapSwizzle::B128);
   make4(&tdO, d_o, TmapDtype::BF16, H, T, strides[6], strides[7], 64, kQRows, TmapSwizzle::B128);
-  make4(&tdK, dk, TmapDtype::BF16, Hk, S, (int64_t)Hk * D, (int64_t)S * Hk * D, 64, 32,
-        TmapSwizzle::B128);
-  make4(&tdV, dv, TmapDtype::BF16, Hk, S, (int64_t)Hk * D, (int64_t)S * Hk * D, 64, 32,
-        TmapSwizzle::B128);
+  make4(&tdK, dk, TmapDtype::BF16, Hk, S, strides[8], strides[9], 64, 32, TmapSwizzle::B128);
+  make4(&tdV, dv, TmapDtype::BF16, Hk, S, strides[10], strides[11], 64, 32, TmapSwizzle::B128);
   BwdParams p;
   p.B = B;
   p.T = T;
@@ -603,9 +601,11 @@ void attn_delta(const void* o, const void* d_o, float* delta, int B, int T, int 
   OB_LAUNCH_CHECK();
 }
 
-// strides = {q_tok, q_batch, k_tok, k_batch, v_tok, v_batch, do_tok, do_batch} in elements.
+// strides = {q_tok, q_batch, k_tok, k_batch, v_tok, v_batch, do_tok, do_batch, dk_tok, dk_batch,
+// dv_tok, dv_batch} in elements (the (heads, D) block of every tensor is contiguous).
 // dq: zero-initialised fp32 (B, T, H, D), receives the gradient without the softmax scale;
-// dk, dv: bf16 (B, S, Hk, D) contiguous.
+// dk, dv: bf16 (B, S, Hk, D) with the given token / batch strides, so that they may be column
+// slices of a wider buffer (the gradient of a fused q|k|v projection).
 void flash_attn_bwd(const void* q, const void* k, const void* v, const void* d_o, float* dq,
                     void* dk, void* dv, const float* lse, const float* delta, int B, int T, int S,
                     int H, int Hk, int D, bool causal, float scale, const int64_t* strides,

@@ -149,8 +149,12 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor&
 }
 
 // q: (B, T, H, D), k: (B, T, Hk, D) with contiguous (H, D); row (token) stride may exceed H*D.
+// Rotates q and k. Without `q_out` / `k_out` fresh contiguous tensors are returned; with them the
+// results are written there (they may be column slices of a wider buffer, e.g. the gradient of a
+// fused q|k|v projection).
 std::vector<Tensor> rope(const Tensor& q, const Tensor& k, const Tensor& cos_t, const Tensor& sin_t,
-                         bool inverse) {
+                         bool inverse, const c10::optional<Tensor>& q_out,
+                         const c10::optional<Tensor>& k_out) {
   check_bf16(q, "q");
   check_bf16(k, "k");
   check_f32(cos_t, "cos");
@@ -168,8 +172,13 @@ std::vector<Tensor> rope(const Tensor& q, const Tensor& k, const Tensor& cos_t, 
   };
   Tensor qq = token_strided(q, H) ? q : q.contiguous();
   Tensor kk = token_strided(k, Hk) ? k : k.contiguous();
-  Tensor qo = torch::empty({B, T, H, D}, q.options());
-  Tensor ko = torch::empty({B, T, Hk, D}, k.options());
+  Tensor qo = q_out.has_value() ? *q_out : torch::empty({B, T, H, D}, q.options());
+  Tensor ko = k_out.has_value() ? *k_out : torch::empty({B, T, Hk, D}, k.options());
+  check_bf16(qo, "q_out");
+  check_bf16(ko, "k_out");
+  TORCH_CHECK(qo.dim() == 4 && ko.dim() == 4 && qo.sizes() == q.sizes() && ko.sizes() == k.sizes() &&
+                  token_strided(qo, H) && token_strided(ko, Hk),
+              "rope outputs must be (B, T, heads, D) with a constant token stride");
   ob::rope_qk(qq.data_ptr(), kk.data_ptr(), qo.data_ptr(), ko.data_ptr(), cos_t.data_ptr<float>(),
               sin_t.data_ptr<float>(), (int)B, (int)T, (int)H, (int)Hk, (int)D, inverse,
               qq.stride(1), kk.stride(1), qo.stride(1), ko.stride(1), current_stream());
@@ -336,9 +345,12 @@ std::vector<Tensor> flash_attn_fwd(const Tensor& q_in, const Tensor& k_in, const
   return {o, lse};
 }
 
+// With `dk_out` / `dv_out` the key / value gradients are written there (bf16 (B, S, Hk, D) whose
+// (heads, D) block is contiguous: column slices of a wider buffer are fine).
 std::vector<Tensor> flash_attn_bwd(const Tensor& dout_in, const Tensor& q_in, const Tensor& k_in,
                                    const Tensor& v_in, const Tensor& out, const Tensor& lse,
-                                   bool causal, double scale) {
+                                   bool causal, double scale, const c10::optional<Tensor>& dk_out,
+                                   const c10::optional<Tensor>& dv_out) {
   check_bf16(dout_in, "dout");
   check_bf16(out, "out");
   check_f32(lse, "lse");
@@ -354,10 +366,16 @@ std::vector<Tensor> flash_attn_bwd(const Tensor& dout_in, const Tensor& q_in, co
   ob::attn_delta(out.data_ptr(), d_o.data_ptr(), delta.data_ptr<float>(), (int)B, (int)T, (int)H,
                  (int)D, d_o.stride(1), d_o.stride(0), current_stream());
   Tensor dq32 = torch::zeros({B, T, H, D}, q.options().dtype(torch::kFloat32));
-  Tensor dk = torch::empty({B, S, Hk, D}, k.options());
-  Tensor dv = torch::empty({B, S, Hk, D}, k.options());
-  const int64_t strides[8] = {q.stride(1), q.stride(0), k.stride(1), k.stride(0),
-                              v.stride(1), v.stride(0), d_o.stride(1), d_o.stride(0)};
+  Tensor dk = dk_out.has_value() ? *dk_out : torch::empty({B, S, Hk, D}, k.options());
+  Tensor dv = dv_out.has_value() ? *dv_out : torch::empty({B, S, Hk, D}, k.options());
+  check_bf16(dk, "dk");
+  check_bf16(dv, "dv");
+  TORCH_CHECK(attn_layout_ok(dk) && attn_layout_ok(dv) && dk.sizes() == k.sizes() &&
+                  dv.sizes() == k.sizes(),
+              "dk / dv must be (B, S, Hk, D) bf16 with contiguous (heads, D) blocks");
+  const int64_t strides[12] = {q.stride(1), q.stride(0), k.stride(1), k.stride(0),
+                               v.stride(1), v.stride(0), d_o.stride(1), d_o.stride(0),
+                               dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0)};
   ob::flash_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), d_o.data_ptr(),
                      dq32.data_ptr<float>(), dk.data_ptr(), dv.data_ptr(), lse.data_ptr<float>(),
                      delta.data_ptr<float>(), (int)B, (int)T, (int)S, (int)H, (int)Hk, (int)D,
@@ -1079,7 +1097,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("beta") = 1.0, py::arg("m_tile_rows") = 128);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
-  m.def("rope", &rope);
+  m.def("rope", &rope, py::arg("q"), py::arg("k"), py::arg("cos"), py::arg("sin"),
+        py::arg("inverse"), py::arg("q_out") = py::none(), py::arg("k_out") = py::none());
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("cast_bf16_into", &cast_bf16_into);
@@ -1097,7 +1116,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sinkhorn_fwd", &sinkhorn_fwd);
   m.def("sinkhorn_bwd", &sinkhorn_bwd);
   m.def("sinkhorn_supported", &sinkhorn_supported);
-  m.def("flash_attn_bwd", &flash_attn_bwd);
+  m.def("flash_attn_bwd", &flash_attn_bwd, py::arg("dout"), py::arg("q"), py::arg("k"),
+        py::arg("v"), py::arg("out"), py::arg("lse"), py::arg("causal"), py::arg("scale"),
+        py::arg("dk_out") = py::none(), py::arg("dv_out") = py::none());
   m.def("peer_alloc", &peer_alloc);
   m.def("peer_open", &peer_open);
   m.def("peer_close", &peer_close);

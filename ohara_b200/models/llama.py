@@ -138,9 +138,19 @@ class Attention(nn.Module):
         # this module (fewer output features) needs no patching.
         heads = self.query.weight.shape[0] // self.head_dim
         kv_heads = self.key.weight.shape[0] // self.head_dim
+        plain = _plain_linears(self.query, self.key, self.value)
+        if (plain and kv_cache is None and self.cp_workspace is None and freqs_cis[0] is not None
+                and ops.fused_projections(x) and self.head_dim in (64, 128)
+                and not (self.training and self.attn_dropout.p > 0.0)):
+            # Training / prefill fast path: one q|k|v GEMM; the rotary and attention kernels read
+            # their operands as column slices of its output and hand back one gradient for it.
+            qkv = ops.linear_cat(x, (self.query.weight, self.key.weight, self.value.weight))
+            out = ops.rope_attention(qkv, freqs_cis[0], freqs_cis[1], heads, kv_heads,
+                                     self.head_dim)
+            return self.res_dropout(self.proj(out.reshape(-1, seq_len, heads * self.head_dim)))
         # -1: with sequence-parallel tensor parallelism the projections gather the token blocks of
         # every rank, so they return more sequences than came in.
-        if _plain_linears(self.query, self.key, self.value):
+        if plain:
             q, k, v = ops.linear_fanout(x, (self.query.weight, self.key.weight, self.value.weight))
         else:  # biases, or tensor-parallel replacements of the projections
             q, k, v = self.query(x), self.key(x), self.value(x)

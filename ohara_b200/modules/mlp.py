@@ -102,8 +102,13 @@ class SwiGLU(_FeedForward):
         self.dropout = _dropout(dropout)
 
     def forward(self, x: Tensor) -> Tensor:
-        if type(self.gate) is Linear and type(self.up) is Linear and self.gate.bias is None \
-                and self.up.bias is None:
+        plain = (type(self.gate) is Linear and type(self.up) is Linear and self.gate.bias is None
+                 and self.up.bias is None)
+        if plain and ops.fused_projections(x) and self.hidden_dim % 8 == 0:
+            # one gate|up GEMM; the activation reads its two halves and returns one gradient
+            fused = ops.linear_cat(x, (self.gate.weight, self.up.weight))
+            return self.dropout(self.down(ops.swiglu_cat(fused)))
+        if plain:
             gate, up = ops.linear_fanout(x, (self.gate.weight, self.up.weight))
         else:  # biases, adapters or tensor-parallel replacements
             gate, up = self.gate(x), self.up(x)

@@ -130,6 +130,10 @@ class GroupedMoE(QuantileBalancedRouter):
         return out
 
     def _shared(self, x: Tensor) -> Tensor:
+        if (type(self.shared_gate) is Linear and type(self.shared_up) is Linear
+                and ops.fused_projections(x)):
+            fused = ops.linear_cat(x, (self.shared_gate.weight, self.shared_up.weight))
+            return self.shared_down(ops.swiglu_cat(fused))
         return self.shared_down(ops.swiglu(self.shared_gate(x), self.shared_up(x)))
 
     def forward(self, x: Tensor) -> Tensor:

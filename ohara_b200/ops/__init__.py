@@ -22,6 +22,10 @@ from ohara_b200.errors import CollectiveTimeout
 
 from ._ext import ext
 
+import os as _os
+
+_FUSE_PROJECTIONS = _os.environ.get("OHARA_FUSED_PROJECTIONS", "1") != "0"
+
 __all__ = [
     "add_rms_norm",
     "attention",
@@ -30,7 +34,10 @@ __all__ = [
     "fast_path",
     "linear",
     "linear_cross_entropy",
+    "linear_cat",
     "linear_fanout",
+    "rope_attention",
+    "swiglu_cat",
     "matmul_nn",
     "matmul_nt",
     "matmul_tn",
@@ -292,6 +299,96 @@ def linear_fanout(x: Tensor, weights) -> tuple[Tensor, ...]:
     return tuple(linear(x, w) for w in weights)
 
 
+def fused_projections(x: Tensor) -> bool:
+    """Whether projections that share the input ``x`` should run as one GEMM (the bf16 fast path;
+    ``OHARA_FUSED_PROJECTIONS=0`` keeps them separate, for A/B measurements)."""
+    return _FUSE_PROJECTIONS and fast_path(x) and x.shape[-1] % 8 == 0
+
+
+def fused_bf16_weight(weights) -> Tensor:
+    """One contiguous ``(sum of out_features, in_features)`` bf16 matrix made of the compute copies
+    of several weights that multiply the same input.
+
+    When the copies already sit next to each other in memory (the first call makes it so) this is
+    a zero-copy view; otherwise they are concatenated into a new buffer and every parameter's
+    compute copy is re-pointed at its rows of that buffer, so that optimizers that refresh the
+    copies in place keep the fused matrix current. A sharded optimizer re-points the copies at
+    its own gathered buffer after every step; then the concatenation is repeated (a few MB)."""
+    shadows = [bf16_weight(w) for w in weights]
+    first = shadows[0]
+    cols = first.shape[1]
+    rows = sum(s.shape[0] for s in shadows)
+    storage = first.untyped_storage().data_ptr()
+    expected = first.data_ptr()
+    adjacent = True
+    for shadow in shadows:
+        if (shadow.shape[1] != cols or not shadow.is_contiguous()
+                or shadow.untyped_storage().data_ptr() != storage
+                or shadow.data_ptr() != expected):
+            adjacent = False
+            break
+        expected += shadow.numel() * 2
+    if adjacent:
+        return first.as_strided((rows, cols), (cols, 1))
+    fused = torch.cat(shadows, dim=0)
+    begin = 0
+    for weight, shadow in zip(weights, shadows):
+        end = begin + shadow.shape[0]
+        if weight.dtype != torch.bfloat16:  # a bf16 parameter is its own compute copy
+            refresh_bf16_weight(weight, fused[begin:end])
+        begin = end
+    return fused
+
+
+class _LinearCatFn(torch.autograd.Function):
+    """``x @ concat(weights).T`` as ONE product: a single wide GEMM forward, a single
+    input-gradient GEMM with the long reduction (instead of one residual-chained GEMM per
+    weight) and a single weight-gradient GEMM whose row blocks are the gradients of the
+    individual weights."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, *weights: Tensor):
+        x16 = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        x2 = _gemm_ready(_as_2d(x16))
+        y = matmul_nt(x2, fused_bf16_weight(weights))
+        ctx.save_for_backward(x2, *weights)
+        ctx.x_shape = x.shape
+        ctx.x_dtype = x.dtype
+        return y.view(*x.shape[:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        x2, *weights = ctx.saved_tensors
+        dy2 = _gemm_ready(_as_2d(dy if dy.dtype == torch.bfloat16 else dy.to(torch.bfloat16)))
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = matmul_nn(dy2, fused_bf16_weight(weights)).view(ctx.x_shape)
+            if dx.dtype != ctx.x_dtype:
+                dx = dx.to(ctx.x_dtype)
+        grads: list[Tensor | None] = [None] * len(weights)
+        if any(ctx.needs_input_grad[1:]):
+            dw = matmul_tn(dy2, x2)  # (sum of out_features, in_features) fp32
+            begin = 0
+            for i, weight in enumerate(weights):
+                end = begin + weight.shape[0]
+                if ctx.needs_input_grad[1 + i]:
+                    part = dw[begin:end]
+                    grads[i] = part if part.dtype == weight.dtype else part.to(weight.dtype)
+                begin = end
+        return (dx, *grads)
+
+
+def linear_cat(x: Tensor, weights) -> Tensor:
+    """``concat([x @ w.T for w in weights], dim=-1)`` — the projections that share an input
+    (query | key | value; gate | up) — computed as one GEMM on the bf16 fast path. The consumers
+    (:func:`rope_attention`, :func:`swiglu_cat`) read their operands as column slices of the
+    result and return one gradient for all of it."""
+    weights = tuple(weights)
+    if (fast_path(x) and x.shape[-1] % 8 == 0 and all(w.shape[0] % 8 == 0 for w in weights)):
+        return _LinearCatFn.apply(x, *weights)
+    return torch.cat([F.linear(x, w) for w in weights], dim=-1)
+
+
 def linear(x: Tensor, weight: Tensor, bias: Tensor | None = None) -> Tensor:
     """``x @ weight.T + bias`` with the tcgen05 GEMM on the bf16 fast path."""
     if fast_path(x) and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0:
@@ -432,6 +529,38 @@ def swiglu(gate: Tensor, up: Tensor) -> Tensor:
     return F.silu(gate) * up
 
 
+class _SwiGLUCatFn(torch.autograd.Function):
+    """``silu(gu[:, :h]) * gu[:, h:]`` on the two column halves of one matrix; the backward pass
+    writes both gradients into the halves of one buffer, which is the gradient of ``gu``."""
+
+    @staticmethod
+    def forward(ctx, gu: Tensor):
+        gu2 = _as_2d(gu)
+        half = gu2.shape[1] // 2
+        a = ext().swiglu_fwd(gu2[:, :half], gu2[:, half:])
+        ctx.save_for_backward(gu2)
+        ctx.shape = gu.shape
+        return a.view(*gu.shape[:-1], half)
+
+    @staticmethod
+    def backward(ctx, da: Tensor):
+        (gu2,) = ctx.saved_tensors
+        half = gu2.shape[1] // 2
+        da2 = _as_2d(da.contiguous())
+        dgu = torch.empty_like(gu2, memory_format=torch.contiguous_format)
+        ext().swiglu_bwd(da2, gu2[:, :half], gu2[:, half:], dgu[:, :half], dgu[:, half:])
+        return dgu.view(ctx.shape)
+
+
+def swiglu_cat(gu: Tensor) -> Tensor:
+    """SwiGLU of a fused ``gate | up`` projection: ``silu(gu[..., :h]) * gu[..., h:]``."""
+    half = gu.shape[-1] // 2
+    if (gu.is_cuda and gu.dtype == torch.bfloat16 and half % 8 == 0 and gu.shape[-1] == 2 * half
+            and gu.is_contiguous()):
+        return _SwiGLUCatFn.apply(gu)
+    return F.silu(gu[..., :half]) * gu[..., half:]
+
+
 # --------------------------------------------------------------------------------------------------
 # Embedding
 # --------------------------------------------------------------------------------------------------
@@ -466,5 +595,5 @@ def embedding(ids: Tensor, table: Tensor) -> Tensor:
 # --------------------------------------------------------------------------------------------------
 # Attention (implemented in ops/attention.py) and fused linear + cross-entropy (ops/loss.py)
 # --------------------------------------------------------------------------------------------------
-from .attention import attention  # noqa: E402
+from .attention import attention, rope_attention  # noqa: E402
 from .loss import linear_cross_entropy  # noqa: E402

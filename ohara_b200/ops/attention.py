@@ -59,6 +59,69 @@ class _FlashAttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
+class _RopeAttentionFn(torch.autograd.Function):
+    """Rotary embedding of q and k plus causal attention on a fused ``q | k | v`` projection
+    ``(B, T, (H + 2 Hk) D)``. q, k and v are read as column slices of it (no copies); the backward
+    pass returns one gradient for the whole projection: the value gradient is stored into its
+    columns by the attention kernel, the un-rotated query / key gradients by the rotary kernel."""
+
+    @staticmethod
+    def forward(ctx, qkv: Tensor, cos: Tensor, sin: Tensor, heads: int, kv_heads: int, dim: int,
+                causal: bool, scale: float):
+        C = ext()
+        batch, seq, _ = qkv.shape
+        nq, nk = heads * dim, kv_heads * dim
+        q = qkv[..., :nq].view(batch, seq, heads, dim)
+        k = qkv[..., nq:nq + nk].view(batch, seq, kv_heads, dim)
+        v = qkv[..., nq + nk:].view(batch, seq, kv_heads, dim)
+        q_rot, k_rot = C.rope(q, k, cos, sin, False)
+        out, lse = C.flash_attn_fwd(q_rot, k_rot, v, causal, scale)
+        ctx.save_for_backward(q_rot, k_rot, qkv, out, lse, cos, sin)
+        ctx.meta = (heads, kv_heads, dim, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout: Tensor):
+        C = ext()
+        q_rot, k_rot, qkv, out, lse, cos, sin = ctx.saved_tensors
+        heads, kv_heads, dim, causal, scale = ctx.meta
+        batch, seq, _ = qkv.shape
+        nq, nk = heads * dim, kv_heads * dim
+        v = qkv[..., nq + nk:].view(batch, seq, kv_heads, dim)
+        dqkv = torch.empty_like(qkv)
+        dv = dqkv[..., nq + nk:].view(batch, seq, kv_heads, dim)
+        dk_rot = torch.empty_like(k_rot)
+        dq_rot, _, _ = C.flash_attn_bwd(dout.contiguous(), q_rot, k_rot, v, out, lse, causal, scale,
+                                        dk_rot, dv)
+        C.rope(dq_rot, dk_rot, cos, sin, True,
+               dqkv[..., :nq].view(batch, seq, heads, dim),
+               dqkv[..., nq:nq + nk].view(batch, seq, kv_heads, dim))
+        return dqkv, None, None, None, None, None, None, None
+
+
+def rope_attention(qkv: Tensor, cos: Tensor, sin: Tensor, heads: int, kv_heads: int, dim: int,
+                   causal: bool = True, scale: float | None = None) -> Tensor:
+    """Rotate and attend on a fused ``q | k | v`` projection ``(B, T, (heads + 2 kv_heads) dim)``
+    with rotary tables already sliced to the tokens' positions; returns ``(B, T, heads, dim)``."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(dim)
+    batch, seq, width = qkv.shape
+    if width != (heads + 2 * kv_heads) * dim:
+        raise ValueError("fused projection width does not match the head counts")
+    if (qkv.is_cuda and qkv.dtype == torch.bfloat16 and dim in (64, 128) and qkv.is_contiguous()
+            and width % 8 == 0):
+        cos = cos[:seq].float().contiguous()
+        sin = sin[:seq].float().contiguous()
+        return _RopeAttentionFn.apply(qkv, cos, sin, heads, kv_heads, dim, causal, float(scale))
+    from ohara_b200.embeddings_pos.rotary import apply_rope
+
+    nq, nk = heads * dim, kv_heads * dim
+    q = qkv[..., :nq].reshape(batch, seq, heads, dim)
+    k = qkv[..., nq:nq + nk].reshape(batch, seq, kv_heads, dim)
+    v = qkv[..., nq + nk:].reshape(batch, seq, kv_heads, dim)
+    q, k = apply_rope(q, k, (cos, sin))
+    return attention(q, k.to(q.dtype), v.to(q.dtype), causal=causal, scale=scale)
+
+
 def _kernel_ok(q: Tensor, k: Tensor, v: Tensor) -> bool:
     d = q.shape[-1]
     return (

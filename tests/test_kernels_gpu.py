@@ -452,3 +452,75 @@ def test_compute_copy_follows_data_assignment_and_dora_merge():
     ops.bf16_weight(weight)
     weight.data = torch.zeros_like(weight)
     assert float(ops.bf16_weight(weight).abs().max()) == 0.0
+
+
+# -- fused projections ---------------------------------------------------------------------------------
+def test_linear_cat_is_one_gemm_with_per_weight_gradients():
+    from ohara_b200 import ops
+
+    torch.manual_seed(0)
+    x = torch.randn(4, 96, 128, device="cuda", requires_grad=True)
+    weights = [torch.nn.Parameter(torch.randn(n, 128, device="cuda") * 0.1) for n in (128, 64, 64)]
+    grad = torch.randn(4, 96, 256, device="cuda").bfloat16()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = ops.linear_cat(x, weights)
+    y.backward(grad)
+    xr = x.detach().bfloat16().float().requires_grad_()
+    wr = [w.detach().bfloat16().float().requires_grad_() for w in weights]
+    ref = torch.cat([xr @ w.T for w in wr], dim=-1)
+    ref.backward(grad.float())
+    assert_close(y, ref, 1e-2, 1e-2, "linear_cat")
+    assert_close(x.grad, xr.grad, 2e-2, 2e-2, "linear_cat dx")
+    for got, want in zip(weights, wr):
+        assert_close(got.grad, want.grad, 1e-3, 1e-3, "linear_cat dw")
+    # the compute copies now share one buffer: an in-place optimizer update shows up in the fused
+    # matrix without another concatenation
+    fused = ops.fused_bf16_weight(weights)
+    assert fused.data_ptr() == ops.bf16_weight(weights[0]).data_ptr()
+    from ohara_b200.optimizer import FusedAdamW
+
+    opt = FusedAdamW([{"params": weights}], lr=0.1)
+    opt.step()
+    again = ops.fused_bf16_weight(weights)
+    assert again.data_ptr() == fused.data_ptr()
+    assert_close(again, torch.cat([w.detach() for w in weights]), 1e-2, 1e-2, "fused weight after step")
+
+
+def test_swiglu_cat_matches_reference():
+    from ohara_b200 import ops
+
+    torch.manual_seed(1)
+    gu = bf(300, 2 * 136).requires_grad_()
+    da = bf(300, 136)
+    out = ops.swiglu_cat(gu)
+    out.backward(da)
+    ref_in = gu.detach().float().requires_grad_()
+    ref = F.silu(ref_in[:, :136]) * ref_in[:, 136:]
+    ref.backward(da.float())
+    assert_close(out, ref, 1e-2, 1e-2, "swiglu_cat")
+    assert_close(gu.grad, ref_in.grad, 2e-2, 2e-2, "swiglu_cat grad")
+
+
+@pytest.mark.parametrize("b,t,h,hk,d", [(2, 384, 4, 4, 64), (1, 1000, 4, 1, 128), (2, 2048, 6, 6, 128)])
+def test_rope_attention_on_a_fused_projection(b, t, h, hk, d):
+    """q | k | v read as column slices of one tensor, one gradient for all of it."""
+    from ohara_b200 import ops
+    from ohara_b200.embeddings_pos.rotary import precompute_freqs_cis, rope_reference
+    from ohara_b200.ops.attention import attention_reference
+
+    torch.manual_seed(2)
+    cos, sin = precompute_freqs_cis(d, t, 10000.0)
+    cos, sin = cos.cuda(), sin.cuda()
+    qkv = bf(b, t, (h + 2 * hk) * d).requires_grad_()
+    dout = bf(b, t, h, d)
+    out = ops.rope_attention(qkv, cos, sin, h, hk, d)
+    out.backward(dout)
+    ref_in = qkv.detach().float().requires_grad_()
+    q = ref_in[..., :h * d].reshape(b, t, h, d)
+    k = ref_in[..., h * d:(h + hk) * d].reshape(b, t, hk, d)
+    v = ref_in[..., (h + hk) * d:].reshape(b, t, hk, d)
+    ref = attention_reference(rope_reference(q, cos, sin), rope_reference(k, cos, sin), v, True)
+    ref.backward(dout.float())
+    assert_close(out, ref, 2e-2, 8e-2, "rope_attention out")
+    assert rel_err(qkv.grad, ref_in.grad) < 2e-2
+    assert_close(qkv.grad, ref_in.grad, 2e-2, 1.2e-1, "rope_attention grad")
