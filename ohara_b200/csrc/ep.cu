@@ -125,8 +125,12 @@ __global__ void ep_zero_fill_kernel(const int* __restrict__ fill_begin, const in
   }
 }
 
-// buffers[dest_rank[j]][dest_row[j]] = scale_j * src[j / k]  (one warp per pair, 16-byte stores,
-// remote for pairs whose expert lives on another rank).
+// buffers[dest_rank[j]][dest_row[j]] = scale_j * src[j / k]: one warp per *token*. The token's row
+// is loaded once into registers (VPL 16-byte vectors per lane, all loads in flight together) and
+// stored to its k destinations, remote for pairs whose expert lives on another rank; the
+// destinations of a token are fetched by the first k lanes and broadcast. VPL = 0 is the generic
+// form for row widths that are not a multiple of 256 elements.
+template <int VPL>
 __global__ void ep_push_rows_kernel(const __nv_bfloat16* __restrict__ src,
                                     const int* __restrict__ dest_rank, const int* __restrict__ dest_row,
                                     const float* __restrict__ scale, PtrTable buffers, int64_t pairs,
@@ -135,23 +139,60 @@ __global__ void ep_push_rows_kernel(const __nv_bfloat16* __restrict__ src,
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   const int vecs = d >> 3;
-  for (int64_t j = warp; j < pairs; j += warps) {
-    const int row = dest_row[j];
-    if (row < 0) continue;
-    const bf16x8* in = reinterpret_cast<const bf16x8*>(src + (j / k) * (int64_t)d);
-    bf16x8* out = reinterpret_cast<bf16x8*>(static_cast<__nv_bfloat16*>(buffers.ptr[dest_rank[j]]) +
-                                            (int64_t)row * d);
-    const float s = scale != nullptr ? scale[j] : 1.f;
-    for (int v = lane; v < vecs; v += 32) {
-      bf16x8 x = in[v];
-      if (scale != nullptr) {
+  const int64_t tokens = pairs / k;
+  for (int64_t t = warp; t < tokens; t += warps) {
+    const bf16x8* in = reinterpret_cast<const bf16x8*>(src + t * (int64_t)d);
+    int my_row = -1, my_rank = 0;
+    float my_scale = 1.f;
+    if (lane < k) {
+      my_row = dest_row[t * k + lane];
+      my_rank = dest_rank[t * k + lane];
+      if (scale != nullptr) my_scale = scale[t * k + lane];
+    }
+    if constexpr (VPL > 0) {
+      bf16x8 x[VPL];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = __bfloat1622float2(x.v[i]);
-          x.v[i] = __floats2bfloat162_rn(f.x * s, f.y * s);
+      for (int i = 0; i < VPL; ++i) x[i] = in[lane + 32 * i];
+      for (int i = 0; i < k; ++i) {
+        const int row = __shfl_sync(0xffffffffu, my_row, i);
+        const int rank = __shfl_sync(0xffffffffu, my_rank, i);
+        const float sc = __shfl_sync(0xffffffffu, my_scale, i);
+        if (row < 0) continue;
+        bf16x8* out = reinterpret_cast<bf16x8*>(static_cast<__nv_bfloat16*>(buffers.ptr[rank]) +
+                                                (int64_t)row * d);
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+          bf16x8 y = x[v];
+          if (scale != nullptr) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const float2 f = __bfloat1622float2(y.v[c]);
+              y.v[c] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+            }
+          }
+          out[lane + 32 * v] = y;
         }
       }
-      out[v] = x;
+    } else {
+      for (int i = 0; i < k; ++i) {
+        const int row = __shfl_sync(0xffffffffu, my_row, i);
+        const int rank = __shfl_sync(0xffffffffu, my_rank, i);
+        const float sc = __shfl_sync(0xffffffffu, my_scale, i);
+        if (row < 0) continue;
+        bf16x8* out = reinterpret_cast<bf16x8*>(static_cast<__nv_bfloat16*>(buffers.ptr[rank]) +
+                                                (int64_t)row * d);
+        for (int v = lane; v < vecs; v += 32) {
+          bf16x8 y = in[v];
+          if (scale != nullptr) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const float2 f = __bfloat1622float2(y.v[c]);
+              y.v[c] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+            }
+          }
+          out[v] = y;
+        }
+      }
     }
   }
 }
@@ -262,11 +303,21 @@ void ep_zero_fill(const int* fill_begin, const int* fill_end, void* buffer, int 
 void ep_push_rows(const void* src, const int* dest_rank, const int* dest_row, const float* scale,
                   const int64_t* buffers, int world, int64_t pairs, int k, int d,
                   cudaStream_t stream) {
-  OB_CHECK(d % 8 == 0 && world <= kMaxEP, "bad push arguments");
+  OB_CHECK(d % 8 == 0 && world <= kMaxEP && k >= 1 && k <= 32 && pairs % k == 0,
+           "bad push arguments");
   if (pairs == 0) return;
-  const int blocks = (int)std::min<int64_t>((pairs + 7) / 8, device_sm_count() * 16);
-  ep_push_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(src), dest_rank,
-                                                  dest_row, scale, make_table(buffers, world), pairs, k, d);
+  const int64_t tokens = pairs / k;
+  const int blocks = (int)std::min<int64_t>((tokens + 7) / 8, device_sm_count() * 16);
+  const auto* in = static_cast<const __nv_bfloat16*>(src);
+  const PtrTable table = make_table(buffers, world);
+  const int vpl = (d % 256 == 0 && d <= 1024) ? d / 256 : 0;
+  switch (vpl) {
+    case 1: ep_push_rows_kernel<1><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d); break;
+    case 2: ep_push_rows_kernel<2><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d); break;
+    case 3: ep_push_rows_kernel<3><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d); break;
+    case 4: ep_push_rows_kernel<4><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d); break;
+    default: ep_push_rows_kernel<0><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d); break;
+  }
   OB_LAUNCH_CHECK();
 }
 

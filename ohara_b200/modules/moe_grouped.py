@@ -70,6 +70,7 @@ class GroupedMoE(QuantileBalancedRouter):
         # Set by ``shard_experts``: the NVLink workspace of the expert-parallel group. The stacked
         # expert weights then hold only this rank's ``num_experts / world`` experts.
         self.ep_workspace = None
+        self.ep_slot: int | None = None  # this layer's buffers inside the shared workspace
 
         self.w_gate = nn.Parameter(torch.empty(num_experts, dim, hidden_dim))
         self.w_up = nn.Parameter(torch.empty(num_experts, dim, hidden_dim))
@@ -160,7 +161,8 @@ class GroupedMoE(QuantileBalancedRouter):
             from ohara_b200.parallel.ep import expert_parallel_swiglu
 
             out = expert_parallel_swiglu(flat_x, indices, weights, counts, self.w_gate, self.w_up,
-                                         self.w_down, self.ep_workspace)
+                                         self.w_down, self.ep_workspace,
+                                         self.ep_slot if torch.is_grad_enabled() else None)
         elif kernels:
             out = grouped_swiglu_experts(flat_x, indices, weights, self.w_gate, self.w_up,
                                          self.w_down, counts)
@@ -183,7 +185,7 @@ class GroupedMoE(QuantileBalancedRouter):
 
     # -- expert parallelism ----------------------------------------------------------------
     @torch.no_grad()
-    def shard_experts(self, workspace) -> None:
+    def shard_experts(self, workspace, slot: int | None = None) -> None:
         """Keep only this rank's slice of the stacked expert weights and route the dispatch /
         combine through ``workspace`` (:class:`ohara_b200.parallel.ep.EPWorkspace`). The router,
         its bias and the shared experts stay replicated. Gradients of the expert weights already
@@ -202,6 +204,7 @@ class GroupedMoE(QuantileBalancedRouter):
             shard.register_hook(lambda grad, scale=1.0 / world: grad * scale)
             setattr(self, name, shard)
         self.ep_workspace = workspace
+        self.ep_slot = slot
 
     # -- init --------------------------------------------------------------------------------
     @torch.no_grad()

@@ -51,13 +51,19 @@ class _GroupedLinearFn(torch.autograd.Function):
     """``y[rows of expert e] = x[rows of expert e] @ w[e]`` with ``w (E, in, out)``."""
 
     @staticmethod
-    def forward(ctx, x_pad: Tensor, weight: Tensor, tile_expert: Tensor, k_offsets: Tensor):
+    def forward(ctx, x_pad: Tensor, weight: Tensor, tile_expert: Tensor, k_offsets: Tensor,
+                out=None):
         from . import bf16_weight
 
         w16 = bf16_weight(weight)
         rows, k = x_pad.shape
         n = weight.shape[2]
-        y = torch.empty(rows, n, device=x_pad.device, dtype=torch.bfloat16)
+        # ``out``: a callable that returns a caller-owned (rows, n) bf16 buffer, e.g. symmetric
+        # memory that peers read. It is called here, inside the function, so that the buffer is
+        # not an input of the autograd node (an input written in place and returned would make
+        # autograd copy it back through its base in the backward pass).
+        y = out() if out is not None else torch.empty(rows, n, device=x_pad.device,
+                                                      dtype=torch.bfloat16)
         # B[e] stored (K=in rows, N=out contiguous): MN-major.
         ext().gemm(x_pad, w16, y, rows, n, k, False, True, 1, False, 1.0, tile_expert, None,
                    None, 1.0, TILE)
@@ -85,11 +91,12 @@ class _GroupedLinearFn(torch.autograd.Function):
             ext().gemm(x_pad, dy, dw, k, n, rows, True, True, 1, False, 1.0, None, k_offsets)
             if dw.dtype != weight.dtype:
                 dw = dw.to(weight.dtype)
-        return dx, dw, None, None
+        return dx, dw, None, None, None
 
 
-def grouped_linear(x_pad: Tensor, weight: Tensor, tile_expert: Tensor, k_offsets: Tensor) -> Tensor:
-    return _GroupedLinearFn.apply(x_pad, weight, tile_expert, k_offsets)
+def grouped_linear(x_pad: Tensor, weight: Tensor, tile_expert: Tensor, k_offsets: Tensor,
+                   out=None) -> Tensor:
+    return _GroupedLinearFn.apply(x_pad, weight, tile_expert, k_offsets, out)
 
 
 def grouped_swiglu_experts(flat_x: Tensor, expert_indices: Tensor, expert_weights: Tensor,

@@ -13,6 +13,12 @@ Before a layer the ranks exchange their per-expert counts (a few hundred bytes w
 peer's table) and derive the same row layout from them. Every primitive is bracketed by the
 bounded flag barrier of :class:`PeerRuntime`, which is what makes the shared buffers safe to
 recycle; all ranks must issue the same sequence of calls.
+
+Copies are avoided where the data has to outlive the exchange anyway: a layer that passes its
+``slot`` gets a landing buffer and an outbox of its own. The rows pushed to this rank in the
+forward pass are what autograd keeps for the weight gradients, so they stay where they landed; the
+down-projection writes the expert outputs straight into the layer's outbox, from where the peers
+pull them in the forward pass and again (for the gate-weight gradients) in the backward pass.
 """
 
 from __future__ import annotations
@@ -66,6 +72,9 @@ class EPWorkspace:
         self.tables = SymmetricBuffer(self.world * num_experts * 4, group)
         self.landing = SymmetricBuffer(capacity_rows * width * 2, group)   # rows pushed to me
         self.outbox = SymmetricBuffer(capacity_rows * width * 2, group)    # rows peers pull from me
+        # per-layer buffers (see the module docstring), created at the layer's first forward pass
+        self.landing_slots: dict[int, SymmetricBuffer] = {}
+        self.outbox_slots: dict[int, SymmetricBuffer] = {}
         self.device = self.tables.device
         torch.cuda.synchronize()
         dist.barrier(group=group)
@@ -81,19 +90,56 @@ class EPWorkspace:
                               self.capacity_rows)
         return DispatchPlan(*parts, top_k=indices.shape[1])
 
+    # -- per-layer buffers -----------------------------------------------------------------------------
+    def _slot(self, table: dict[int, SymmetricBuffer], slot: int) -> SymmetricBuffer:
+        """The layer's own symmetric buffer; the first request creates it (a collective: every
+        rank reaches a layer's first forward pass at the same point of the program)."""
+        buffer = table.get(slot)
+        if buffer is None:
+            buffer = table[slot] = SymmetricBuffer(self.capacity_rows * self.width * 2, self.group)
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+        return buffer
+
+    def outbox_rows(self, slot: int, d: int) -> Tensor:
+        """This rank's ``(capacity_rows, d)`` outbox of layer ``slot``: the buffer to compute the
+        expert outputs into, so that the peers can pull them without a copy."""
+        buffer = self._slot(self.outbox_slots, slot)
+        return buffer.typed(torch.bfloat16)[: self.capacity_rows * d].view(self.capacity_rows, d)
+
+    def _published(self, padded: Tensor) -> SymmetricBuffer | None:
+        """The outbox ``padded`` already lives in, if any."""
+        for buffer in self.outbox_slots.values():
+            if buffer.local.data_ptr() == padded.data_ptr():
+                return buffer
+        return None
+
     # -- data movement -------------------------------------------------------------------------------
     @nvtx_annotate("ep.dispatch")
-    def push_rows(self, rows: Tensor, plan: DispatchPlan, scale: Tensor | None = None) -> Tensor:
+    def push_rows(self, rows: Tensor, plan: DispatchPlan, scale: Tensor | None = None,
+                  slot: int | None = None) -> Tensor:
         """Send row ``t`` of ``rows (N, d)`` to the owners of its ``k`` experts (times ``scale``);
-        returns this rank's padded ``(capacity_rows, d)`` buffer of received rows."""
+        returns this rank's padded ``(capacity_rows, d)`` buffer of received rows.
+
+        With ``slot`` the rows land in that layer's own buffer and the returned tensor *is* that
+        buffer (valid until the layer's next forward pass). Without it they land in the shared
+        buffer, which the next push overwrites: the caller must consume the result before it
+        issues another exchange (the backward pass does: the gradient rows feed the expert GEMMs
+        of the same layer at once)."""
         d = rows.shape[1]
-        self.runtime.barrier()  # every rank has copied out what it received last time
+        if slot is None:
+            target = self.landing
+            self.runtime.barrier()  # every rank has consumed what it received last time
+        else:
+            # no rank can still be reading this layer's buffer: its last readers ran a whole
+            # step ago, and the barriers of ``plan`` lie between them and this push
+            target = self._slot(self.landing_slots, slot)
         ext().ep_push_rows(rows.contiguous(), plan.dest_rank, plan.dest_row, scale,
-                           self.landing.pointers, plan.top_k)
+                           target.pointers, plan.top_k)
         self.runtime.barrier()  # all rows have landed
-        landed = self.landing.typed(torch.bfloat16)[: self.capacity_rows * d].view(self.capacity_rows, d)
+        landed = target.typed(torch.bfloat16)[: self.capacity_rows * d].view(self.capacity_rows, d)
         ext().ep_zero_fill(plan.fill, landed, d, self.capacity_rows)
-        return landed.clone()
+        return landed
 
     @nvtx_annotate("ep.combine")
     def pull_rows(self, padded: Tensor, plan: DispatchPlan, scale: Tensor | None = None,
@@ -101,10 +147,13 @@ class EPWorkspace:
         """Adjoint of ``push_rows``: ``out[t] = sum_i scale[t, i] * padded_owner[row(t, i)]`` read
         from the owners' buffers; with ``other (N, d)`` also the per-pair dot products."""
         d = padded.shape[1]
-        mine = self.outbox.typed(torch.bfloat16)[: self.capacity_rows * d].view(self.capacity_rows, d)
-        mine.copy_(padded)
+        source = self._published(padded)
+        if source is None:  # not in an outbox yet: publish a copy in the shared one
+            source = self.outbox
+            mine = source.typed(torch.bfloat16)[: self.capacity_rows * d].view(self.capacity_rows, d)
+            mine.copy_(padded)
         self.runtime.barrier()  # everyone's rows are published
-        out, dots = ext().ep_pull_combine(self.outbox.pointers, plan.dest_rank, plan.dest_row, scale,
+        out, dots = ext().ep_pull_combine(source.pointers, plan.dest_rank, plan.dest_row, scale,
                                           other, plan.top_k, d, want_out)
         self.runtime.barrier()  # everyone has finished reading before the outbox is reused
         return out, dots
@@ -136,14 +185,18 @@ class LazyEPWorkspace:
 
 class _DispatchFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x16: Tensor, plan: DispatchPlan, workspace: EPWorkspace) -> Tensor:
+    def forward(ctx, x16: Tensor, plan: DispatchPlan, workspace: EPWorkspace,
+                slot: int | None = None) -> Tensor:
         ctx.plan, ctx.workspace = plan, workspace
-        return workspace.push_rows(x16, plan)
+        landed = workspace.push_rows(x16, plan, slot=slot)
+        # without a buffer of its own the layer must keep a copy: the shared landing buffer is
+        # overwritten by the next exchange, the rows are needed again for the weight gradients
+        return landed if slot is not None else landed.clone()
 
     @staticmethod
     def backward(ctx, dx_pad: Tensor):
         dx, _ = ctx.workspace.pull_rows(dx_pad.contiguous(), ctx.plan)
-        return dx, None, None
+        return dx, None, None, None
 
 
 class _CombineFn(torch.autograd.Function):
@@ -169,11 +222,13 @@ class _CombineFn(torch.autograd.Function):
 
 def expert_parallel_swiglu(flat_x: Tensor, indices: Tensor, weights: Tensor, counts: Tensor,
                            w_gate: Tensor, w_up: Tensor, w_down: Tensor,
-                           workspace: EPWorkspace) -> Tensor:
+                           workspace: EPWorkspace, slot: int | None = None) -> Tensor:
     """Routed SwiGLU experts with the expert dimension sharded over the group.
 
     ``indices (N, k)`` are *global* expert ids chosen by this rank's router for its own tokens;
-    ``w_gate / w_up (E_local, d, h)`` and ``w_down (E_local, h, d)`` are this rank's experts."""
+    ``w_gate / w_up (E_local, d, h)`` and ``w_down (E_local, h, d)`` are this rank's experts.
+    ``slot`` (a small integer unique to the calling layer) gives the layer its own landing
+    buffer and outbox, which removes the copies out of and into the shared ones."""
     from ohara_b200.ops import swiglu
     from ohara_b200.ops.grouped import grouped_linear
 
@@ -182,9 +237,11 @@ def expert_parallel_swiglu(flat_x: Tensor, indices: Tensor, weights: Tensor, cou
     if isinstance(workspace, LazyEPWorkspace):
         workspace = workspace.materialize(indices.numel())
     plan = workspace.plan(indices, counts)
-    x_pad = _DispatchFn.apply(x16.contiguous(), plan, workspace)
+    x_pad = _DispatchFn.apply(x16.contiguous(), plan, workspace, slot)
     gate = grouped_linear(x_pad, w_gate, plan.tile_expert, plan.k_offsets)
     up = grouped_linear(x_pad, w_up, plan.tile_expert, plan.k_offsets)
     hidden = swiglu(gate, up)
-    y_pad = grouped_linear(hidden, w_down, plan.tile_expert, plan.k_offsets)
+    width = w_down.shape[2]
+    out = (lambda: workspace.outbox_rows(slot, width)) if slot is not None else None
+    y_pad = grouped_linear(hidden, w_down, plan.tile_expert, plan.k_offsets, out)
     return _CombineFn.apply(y_pad, weights.float(), plan, workspace)

@@ -438,12 +438,12 @@ class OharaEngine:
         if not layers:
             raise ValueError("ep > 1 but the model has no grouped mixture-of-experts layer")
         shared: dict[tuple[int, int], LazyEPWorkspace] = {}
-        for layer in layers:
+        for index, layer in enumerate(layers):
             key = (layer.num_experts, layer.dim)
             if key not in shared:
                 shared[key] = LazyEPWorkspace(self._groups.get("ep"), layer.num_experts, layer.dim,
                                               self.config.expert_capacity_factor)
-            layer.shard_experts(shared[key])
+            layer.shard_experts(shared[key], slot=index)
             topo = self.topology
             sharded = isinstance(self._strategy, FSDPStrategy)
             if layer.quantile_balancing and (sharded or topo.cp == 1):
