@@ -15,7 +15,7 @@ replica is fixed, ``value`` is the whole-job tokens/s):
 ``tp4_fsdp2_1p3b``
     24 layers, d_model 2048, 16 query / 4 KV heads x 128, SwiGLU hidden 5632, vocab 50304,
     sequence 4096, 128 sequences per data-parallel replica and step (256 at 8 GPUs) in
-    micro-batches of 8; AdamW; tensor parallel (sequence-parallel layout, collectives fused into
+    micro-batches of 16; AdamW; tensor parallel (sequence-parallel layout, collectives fused into
     the GEMMs) of degree min(4, N) x sharded optimizer over the rest.
 ``cp8_32k``
     the same 1.3B model at sequence 32768, one sequence per context-parallel group and step;
@@ -73,7 +73,7 @@ CONFIGS: dict[str, dict] = {
     ),
     "tp4_fsdp2_1p3b": dict(
         name="llama-1.3B (24L d2048 16q/4kv x128 ffn5632 V50304)",
-        model=LLAMA_1P3B, seq_len=4096, rows=8, micro_steps=16, optimizer="adamw", data="uniform",
+        model=LLAMA_1P3B, seq_len=4096, rows=16, micro_steps=8, optimizer="adamw", data="uniform",
         tp=4,
     ),
     "cp8_32k": dict(

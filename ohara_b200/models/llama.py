@@ -148,6 +148,18 @@ class Attention(nn.Module):
             out = ops.rope_attention(qkv, freqs_cis[0], freqs_cis[1], heads, kv_heads,
                                      self.head_dim)
             return self.res_dropout(self.proj(out.reshape(-1, seq_len, heads * self.head_dim)))
+        if (not plain and kv_cache is None and self.cp_workspace is None
+                and freqs_cis[0] is not None and self.head_dim in (64, 128)
+                and not (self.training and self.attn_dropout.p > 0.0)):
+            # The same with the projections sharded over a tensor-parallel group: one gather of
+            # the token blocks and one GEMM for this rank's heads of q | k | v.
+            from ohara_b200.runtime.tensor_parallel import fused_column_parallel
+
+            qkv = fused_column_parallel(x, (self.query, self.key, self.value))
+            if qkv is not None:
+                out = ops.rope_attention(qkv, freqs_cis[0], freqs_cis[1], heads, kv_heads,
+                                         self.head_dim)
+                return self.res_dropout(self.proj(out.reshape(-1, seq_len, heads * self.head_dim)))
         # -1: with sequence-parallel tensor parallelism the projections gather the token blocks of
         # every rank, so they return more sequences than came in.
         if plain:

@@ -108,6 +108,13 @@ class SwiGLU(_FeedForward):
             # one gate|up GEMM; the activation reads its two halves and returns one gradient
             fused = ops.linear_cat(x, (self.gate.weight, self.up.weight))
             return self.dropout(self.down(ops.swiglu_cat(fused)))
+        if not plain and self.hidden_dim % 8 == 0:
+            from ohara_b200.runtime.tensor_parallel import ColumnParallelLinear, fused_column_parallel
+
+            if type(self.gate) is ColumnParallelLinear and (self.gate.weight.shape[0] % 8 == 0):
+                fused = fused_column_parallel(x, (self.gate, self.up))
+                if fused is not None:  # one gather + one GEMM for this rank's gate | up columns
+                    return self.dropout(self.down(ops.swiglu_cat(fused)))
         if plain:
             gate, up = ops.linear_fanout(x, (self.gate.weight, self.up.weight))
         else:  # biases, adapters or tensor-parallel replacements

@@ -251,6 +251,33 @@ class RowParallelLinear(_ParallelLinear):
         return y
 
 
+def fused_column_parallel(x: Tensor, layers) -> Tensor | None:
+    """The outputs of several column-parallel layers that share the input ``x``, concatenated
+    along the last dimension and computed by ONE gather + GEMM, when every layer is a bias-free
+    :class:`ColumnParallelLinear` on the fused sequence-parallel path; ``None`` otherwise (the
+    caller then runs the layers one by one). ``x`` is ``(B_local, T, in)``; the result is
+    ``(world * B_local, T, sum of local out_features)``."""
+    from ohara_b200 import ops
+
+    first = layers[0]
+    if not all(type(layer) is ColumnParallelLinear and layer.bias is None
+               and layer.sequence_parallel and layer.workspace is not None
+               and layer.group is first.group for layer in layers):
+        return None
+    if not ops.fused_projections(x):
+        return None
+    rows_local = x.numel() // x.shape[-1]
+    if not first._use_fused(x, rows_local):
+        return None
+    for layer in layers:  # the first fused call may have materialised the group's workspace
+        layer.workspace = first.workspace
+    from ohara_b200.parallel.tp_fused import column_parallel_fused_cat
+
+    y = column_parallel_fused_cat(x.reshape(-1, x.shape[-1]),
+                                  tuple(layer.weight for layer in layers), first.workspace)
+    return y.view(x.shape[0] * first.tp_world, *x.shape[1:-1], y.shape[-1])
+
+
 def apply_tensor_parallel(module: nn.Module, tp_group, plan: TensorParallelPlan,
                           tp_rank: int | None = None, tp_world: int | None = None) -> nn.Module:
     """Replace every ``nn.Linear`` matched by ``plan`` with its sharded counterpart, in place."""
