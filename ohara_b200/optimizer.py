@@ -367,6 +367,10 @@ class MuonAdamW(optim.Optimizer):
             shape = (batch, rows, 1) if reduce_dim == -1 else (batch, 1, cols)
             state["second_momentum_buffer"] = torch.zeros(shape, dtype=first.dtype,
                                                           device=first.device)
+        tp_dim = getattr(first, "tensor_parallel_dim", None)
+        if tp_dim is not None and self._tensor_parallel_world() > 1:
+            self._muon_step_tensor_parallel(group, state, params, int(tp_dim))
+            return
         if not hyperspherical and _fused_muon_ok(params, rows, cols):
             self._muon_step_fused(group, state, params, batch, rows, cols)
             return
@@ -403,6 +407,74 @@ class MuonAdamW(optim.Optimizer):
             stacked.sub_(lr * update + lr * wd * stacked * aligned)
         if not pre_stacked:
             torch._foreach_copy_(params, list(stacked.unbind(0)))
+
+    # -- Muon on tensor-parallel shards ------------------------------------------------------------
+    # Set by the engine (``OharaEngine.prepare_optimizers``): the process group over which the
+    # matrices of this optimizer are sharded. Kept off the param groups so that state dicts stay
+    # plain data.
+    tensor_parallel_group = None
+    tensor_parallel_world = 1
+
+    def _tensor_parallel_world(self) -> int:
+        return int(getattr(self, "tensor_parallel_world", 1) or 1)
+
+    def _muon_step_tensor_parallel(self, group: dict[str, Any], state: dict[str, Any],
+                                   params: list[Tensor], tp_dim: int) -> None:
+        """The Muon step when every matrix of the group is a shard (rows for ``tp_dim`` 0, columns
+        for 1) of a matrix spread over a tensor-parallel group. The orthogonalisation of a shard
+        is not the shard of the orthogonalised matrix, so the momentum-corrected gradients are
+        gathered over the group, the Newton-Schulz iteration and the row / column statistics run
+        on the whole matrices (redundantly on every rank of the group: a few small GEMMs), and
+        each rank applies its own slice. Momentum stays sharded; the factored second moment is a
+        vector over whole rows or columns and is kept in full on every rank. Identical, up to
+        summation order, to the step on the unsharded matrices. (The reference rejects this
+        combination: examples/train_llama_engine.py:280-281.)"""
+        import torch.distributed as dist
+
+        if bool(group.get("hypersphere", False)):
+            raise NotImplementedError("hyperspherical Muon on tensor-parallel shards is not "
+                                      "implemented (the norms span the whole matrix)")
+        world, pg = self._tensor_parallel_world(), self.tensor_parallel_group
+        rank = dist.get_rank(pg)
+        first = params[0]
+        pre_stacked = len(params) == 1 and first.ndim == 3
+        grads = first.grad if pre_stacked else torch.stack([p.grad for p in params])
+        stacked = first.detach() if pre_stacked else torch.stack([p.detach() for p in params])
+        grads = grads.to(first.dtype)
+        momentum = float(group["momentum"])
+        buf = state["momentum_buffer"]
+        buf.lerp_(grads, 1.0 - momentum)
+        local = grads.lerp(buf, momentum).contiguous()
+        parts = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(parts, local, group=pg)
+        whole = torch.cat(parts, dim=1 + tp_dim)
+        update = _polar_express(whole, int(group["ns_steps"]))
+        rows, cols = whole.shape[-2:]
+        reduce_dim = -1 if rows >= cols else -2
+        shape = (whole.shape[0], rows, 1) if reduce_dim == -1 else (whole.shape[0], 1, cols)
+        second = state.get("second_momentum_buffer")
+        if second is None or tuple(second.shape) != shape:
+            second = state["second_momentum_buffer"] = torch.zeros(shape, dtype=first.dtype,
+                                                                   device=first.device)
+        beta2 = float(group["beta2"])
+        variance = update.float().square().mean(dim=reduce_dim, keepdim=True)
+        size = update.size(reduce_dim)
+        norm_before = (variance.sum(dim=(-2, -1), keepdim=True) * size).sqrt()
+        second.lerp_(variance.to(second.dtype), 1.0 - beta2)
+        inv_rms = second.clamp_min(1e-10).rsqrt()
+        norm_after = ((variance * size) * inv_rms.float().square()).sum(
+            dim=(-2, -1), keepdim=True).sqrt()
+        update = update * (inv_rms * (norm_before / norm_after.clamp_min(1e-10))).to(update.dtype)
+        lr = float(group["lr"]) * math.sqrt(max(1.0, rows / cols))
+        wd = float(group["weight_decay"])
+        mine = update.chunk(world, dim=1 + tp_dim)[rank].to(stacked.dtype)
+        aligned = (mine * stacked) >= 0
+        stacked.sub_(lr * mine + lr * wd * stacked * aligned)
+        if not pre_stacked:
+            torch._foreach_copy_(params, list(stacked.unbind(0)))
+        for p in params:  # written without a version bump on the compute copies
+            if getattr(p, "_ohara_bf16", None) is not None:
+                p._ohara_bf16 = None
 
     @staticmethod
     def _muon_step_fused(group: dict[str, Any], state: dict[str, Any], params: list[Tensor],

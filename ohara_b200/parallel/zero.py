@@ -228,6 +228,9 @@ class ShardedOptimizer(Optimizer):
                 if len(entry) == 1 and first.shape is not None:
                     view = view.view(first.shape)
                 param = torch.nn.Parameter(view, requires_grad=True)
+                if len(entry) == 1 and hasattr(first.param, "tensor_parallel_dim"):
+                    # whole-matrix algorithms need to know that this is a tensor-parallel shard
+                    param.tensor_parallel_dim = first.param.tensor_parallel_dim
                 if len(entry) == 1:
                     param._shard_piece = first
                 else:
@@ -246,6 +249,9 @@ class ShardedOptimizer(Optimizer):
                 self.local = cls(local_groups)
             except TypeError:
                 self.local = cls(local_groups, **{k: v for k, v in self.inner.defaults.items()})
+            for name in ("tensor_parallel_group", "tensor_parallel_world"):
+                if hasattr(self.inner, name):
+                    setattr(self.local, name, getattr(self.inner, name))
 
     # -- fused peer-memory path ----------------------------------------------------------------
     def _try_enable_fused(self) -> None:

@@ -470,6 +470,11 @@ class OharaEngine:
     def prepare_optimizers(self, *optimizers: Optimizer):
         self.launch()
         module = getattr(self, "_module", None)
+        if self.topology.tp_enabled:
+            # whole-matrix algorithms (Muon) gather the shards of a matrix over this group
+            for opt in optimizers:
+                opt.tensor_parallel_group = self._groups.get("tp")
+                opt.tensor_parallel_world = self.topology.tp
         wrapped = tuple(self._strategy.setup_optimizer(opt, module) for opt in optimizers)
         for opt in wrapped:
             if callable(getattr(opt, "sync_master_weights", None)):

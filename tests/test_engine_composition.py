@@ -264,3 +264,32 @@ def test_pipeline_parallel_through_the_engine_matches_single_process(tmp_path):
         4, tmp_path, port_base=31700,
     )
     assert "PP_ENGINE_OK" in out
+
+
+def test_muon_on_tensor_parallel_shards_matches_the_unsharded_step(tmp_path):
+    """tp=2 x dp=2 with the Muon hybrid: the orthogonalisation runs on whole matrices gathered
+    over the tensor-parallel group, every rank applies its slice; weights must follow the
+    single-process run."""
+    out = _run(
+        """
+        solo = reference(build_muon_adamw)
+        engine = OharaEngine(EngineConfig(strategy=StrategyType.FSDP,
+                                          parallel=ParallelConfig(tp=2)))
+        model = Llama(cfg); model.load_state_dict(state)
+        model = engine.prepare(model)
+        (opt,) = engine.prepare_optimizers(build_muon_adamw(model))
+        assert opt.local.tensor_parallel_world == 2
+        loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=4))
+        trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=1,
+                          max_iters=3, eval_iters=0, save_ckpt_iters=0)
+        trainer.train()
+        full = engine.full_state_dict(model)
+        for key, value in solo.state_dict().items():
+            assert torch.allclose(full[key], value, atol=5e-5), (key, (full[key] - value).abs().max())
+        if dist.get_rank() == 0:
+            print("TP_MUON_OK")
+        engine.close()
+        """,
+        4, tmp_path, port_base=32300,
+    )
+    assert "TP_MUON_OK" in out
