@@ -76,15 +76,20 @@ def run_ours(args):
 
     torch.manual_seed(0)
     model = Llama(Config(**MODEL))
-    device, rank0 = "cuda", True
+    device, rank0, heads_split = "cuda", True, True
     if args.tp > 1:
         # Attention heads and the feed-forward width are sharded over the ranks; the all-reduce
         # behind each row-parallel layer is the one-shot peer-memory kernel, replayed from the
         # same CUDA graph as the rest of the decode step.
         from ohara_b200.runtime import EngineConfig, OharaEngine, ParallelConfig, TensorParallelPlan
 
+        # When the degree does not divide the head count (6 heads on 4 or 8 ranks) only the
+        # feed-forward layers and the output head are sharded and attention is replicated.
+        heads_split = MODEL["num_attention_heads"] % args.tp == 0
+        plan = (TensorParallelPlan.llama_default(args.tp) if heads_split
+                else TensorParallelPlan.mlp_and_head(args.tp))
         runtime = OharaEngine(EngineConfig(parallel=ParallelConfig(tp=args.tp),
-                                           tensor_parallel=TensorParallelPlan.llama_default(args.tp)))
+                                           tensor_parallel=plan))
         runtime.launch()
         model = runtime.prepare_module(model.to(torch.bfloat16))
         device, rank0 = runtime.device, runtime.is_global_zero
@@ -96,7 +101,9 @@ def run_ours(args):
             torch, lambda: engine.generate_batch(prompt, config, seed=1, cuda_graph=not args.no_graph),
             args.repeats, args.warmup)
         if rank0:
-            report(args, "ours", batch, seconds, {"cuda_graph": not args.no_graph, "tp": args.tp})
+            plan_name = "none" if args.tp == 1 else ("heads+mlp" if heads_split else "mlp+head")
+            report(args, "ours", batch, seconds,
+                   {"cuda_graph": not args.no_graph, "tp": args.tp, "tp_plan": plan_name})
 
 
 def run_reference(args):

@@ -374,6 +374,9 @@ class Llama(nn.Module):
         """``scale * Σ CE(logits, targets)`` over supervised targets, with the output projection
         fused into the loss (no logits tensor). Adds any MoE auxiliary losses (also scaled)."""
         hidden = self.forward_hidden(x)
+        if hasattr(self.vocab_proj.weight, "tensor_parallel_dim"):
+            raise NotImplementedError("the fused loss needs the whole output projection: a "
+                                      "vocabulary-sharded head (mlp_and_head plan) is for inference")
         loss = ops.linear_cross_entropy(hidden, self.vocab_proj.weight, targets, ignore_index, scale)
         aux = self.auxiliary_loss()
         if aux is not None:

@@ -54,3 +54,6 @@ class ParallelDimension(StrEnum):
 class TensorParallelStyle(StrEnum):
     COLWISE = "colwise"
     ROWWISE = "rowwise"
+    # column-parallel with the outputs of all ranks concatenated again (an output head whose
+    # logits every rank needs in full)
+    COLWISE_GATHERED = "colwise_gathered"

@@ -59,6 +59,24 @@ class TensorParallelPlan:
             ],
         )
 
+    @classmethod
+    def mlp_and_head(cls, degree: int) -> "TensorParallelPlan":
+        """Shard only the feed-forward layers and the output head; attention stays replicated.
+        For models whose head count the degree does not divide (a 6-head model on 8 ranks):
+        the SwiGLU width and the vocabulary still split evenly, and they hold most of the
+        weights a decode step has to stream."""
+        col, row = TensorParallelStyle.COLWISE, TensorParallelStyle.ROWWISE
+        return cls(
+            degree=degree,
+            sequence_parallel=False,
+            rules=[
+                TensorParallelRule("layers.*.ff.up", col),
+                TensorParallelRule("layers.*.ff.gate", col),
+                TensorParallelRule("layers.*.ff.down", row),
+                TensorParallelRule("vocab_proj", TensorParallelStyle.COLWISE_GATHERED),
+            ],
+        )
+
     def style_for(self, module_fqn: str) -> TensorParallelStyle | None:
         for rule in self.rules:
             if fnmatch.fnmatch(module_fqn, rule.module_pattern):
@@ -100,6 +118,30 @@ class _ReduceFromGroup(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad: Tensor):
         return grad, None, None
+
+
+class _GatherFeatures(torch.autograd.Function):
+    """All-gather along the last dimension forward, own slice backward (gathered column-parallel
+    output)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, group):
+        ctx.group = group
+        world = dist.get_world_size(group)
+        ctx.rank, ctx.width = dist.get_rank(group), x.shape[-1]
+        x = x.contiguous()
+        if x.is_cuda:  # one collective into one buffer: also what a CUDA-graph capture wants
+            stacked = torch.empty((world, *x.shape), device=x.device, dtype=x.dtype)
+            dist.all_gather_into_tensor(stacked, x, group=group)
+            return stacked.movedim(0, -2).reshape(*x.shape[:-1], world * x.shape[-1])
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x, group=group)
+        return torch.cat(parts, dim=-1)
+
+    @staticmethod
+    def backward(ctx, grad: Tensor):
+        begin = ctx.rank * ctx.width
+        return grad[..., begin:begin + ctx.width].contiguous(), None
 
 
 class _GatherSequence(torch.autograd.Function):
@@ -198,8 +240,9 @@ class ColumnParallelLinear(_ParallelLinear):
     """Output features split over the group; input replicated (or sequence-sharded with SP)."""
 
     def __init__(self, source: nn.Linear, group, rank: int, world: int,
-                 sequence_parallel: bool = False) -> None:
+                 sequence_parallel: bool = False, gather_output: bool = False) -> None:
         super().__init__(source, group, rank, world, 0, sequence_parallel)
+        self.gather_output = gather_output
         if source.bias is not None:
             self.bias = nn.Parameter(source.bias.detach().chunk(world)[rank].clone())
             self.bias.tensor_parallel_dim = 0
@@ -217,7 +260,8 @@ class ColumnParallelLinear(_ParallelLinear):
             x = _GatherSequence.apply(x, self.group)
         else:
             x = _CopyToGroup.apply(x, self.group)
-        return ops.linear(x, self.weight, self.bias)
+        y = ops.linear(x, self.weight, self.bias)
+        return _GatherFeatures.apply(y, self.group) if self.gather_output else y
 
 
 class RowParallelLinear(_ParallelLinear):
@@ -293,10 +337,15 @@ def apply_tensor_parallel(module: nn.Module, tp_group, plan: TensorParallelPlan,
         style = plan.style_for(fqn)
         if style is None:
             continue
-        cls = ColumnParallelLinear if style == TensorParallelStyle.COLWISE else RowParallelLinear
         parent_name, _, leaf = fqn.rpartition(".")
         parent = module.get_submodule(parent_name) if parent_name else module
-        setattr(parent, leaf, cls(child, tp_group, rank, world, plan.sequence_parallel))
+        if style == TensorParallelStyle.ROWWISE:
+            replacement = RowParallelLinear(child, tp_group, rank, world, plan.sequence_parallel)
+        else:
+            replacement = ColumnParallelLinear(
+                child, tp_group, rank, world, plan.sequence_parallel,
+                gather_output=style == TensorParallelStyle.COLWISE_GATHERED)
+        setattr(parent, leaf, replacement)
         replaced += 1
     if replaced == 0:
         raise ValueError(

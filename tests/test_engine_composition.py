@@ -293,3 +293,34 @@ def test_muon_on_tensor_parallel_shards_matches_the_unsharded_step(tmp_path):
         4, tmp_path, port_base=32300,
     )
     assert "TP_MUON_OK" in out
+
+
+def test_feed_forward_and_head_only_tensor_parallel_plan(tmp_path):
+    """Four ranks on a model with two heads: the head count does not split, so only the
+    feed-forward layers and the output head are sharded; logits must equal the unsharded model's
+    on every rank."""
+    out = _run(
+        """
+        engine = OharaEngine(EngineConfig(parallel=ParallelConfig(tp=4),
+                                          tensor_parallel=TensorParallelPlan.mlp_and_head(4)))
+        cfg32 = Config(vocab_size=32, max_sequence_length=8, hidden_size=16, intermediate_size=24,
+                       num_attention_heads=2, num_hidden_layers=2, dropout=0.0)
+        torch.manual_seed(3)
+        whole = Llama(cfg32).eval()
+        model = Llama(cfg32); model.load_state_dict(whole.state_dict())
+        model = engine.prepare_module(model).eval()
+        assert model.layers[0].ff.up.weight.shape == (24 // 4, 16)
+        assert model.vocab_proj.weight.shape == (32 // 4, 16)
+        assert model.layers[0].attn.query.weight.shape == (16, 16)       # attention replicated
+        with torch.no_grad():
+            got = model(ids[:, :-1])
+            want = whole(ids[:, :-1])
+        assert got.shape == want.shape
+        assert torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
+        if dist.get_rank() == 0:
+            print("MLP_HEAD_TP_OK")
+        engine.close()
+        """,
+        4, tmp_path, port_base=32900,
+    )
+    assert "MLP_HEAD_TP_OK" in out
