@@ -110,6 +110,19 @@ def bench_bandwidth(kind, args, timer):
         vocab = args.k
         hidden, weight = bf(rows, d), bf(vocab, d)
         target = torch.randint(0, vocab, (rows,), device="cuda")
+        if kind == "linear_ce_train":
+            # training form: the fused op also produces both gradients in its forward pass; the
+            # library arm runs forward + backward
+            hidden.requires_grad_()
+            weight.requires_grad_()
+
+            def library():
+                hidden.grad = weight.grad = None
+                F.cross_entropy((hidden @ weight.t()).float(), target, reduction="sum").backward()
+
+            ours = lambda: ops.linear_cross_entropy(hidden, weight, target, -1, 1.0)  # noqa: E731
+            return dict(shape=[rows, d, vocab], work=6.0 * rows * d * vocab, kind="flops",
+                        ours=ours, baseline=library)
         ours = lambda: ops.linear_cross_entropy(hidden, weight, target, -1, 1.0)  # noqa: E731
         base = lambda: F.cross_entropy((hidden @ weight.t()).float(), target, reduction="sum")  # noqa: E731
         return dict(shape=[rows, d, vocab], work=2.0 * rows * d * vocab, kind="flops", ours=ours,
@@ -328,6 +341,7 @@ OPS = {
     "gemm_nt": bench_gemm, "gemm_nn": bench_gemm, "gemm_tn": bench_gemm,
     "attn_fwd": bench_attention, "attn_bwd": bench_attention,
     "rmsnorm": bench_bandwidth, "swiglu": bench_bandwidth, "linear_ce": bench_bandwidth,
+    "linear_ce_train": bench_bandwidth,
     "rope": bench_rope, "adamw": bench_adamw, "newton_schulz": bench_newton_schulz,
     "router": bench_router, "permute_combine": bench_permute_combine,
     "grouped_gemm": bench_grouped_gemm, "quantile": bench_quantile,
@@ -338,6 +352,7 @@ DEFAULTS = {
     "gemm_nt": dict(m=65536, n=768, k=768), "gemm_nn": dict(m=65536, n=768, k=2048),
     "gemm_tn": dict(m=768, n=2048, k=65536), "rmsnorm": dict(m=65536, n=768),
     "swiglu": dict(m=65536, n=2048), "linear_ce": dict(m=8192, n=768, k=50304),
+    "linear_ce_train": dict(m=8192, n=768, k=50304),
     "adamw": dict(m=50304, n=768), "newton_schulz": dict(m=768, n=768, batch=48),
     "router": dict(m=32768, n=1024), "permute_combine": dict(m=32768, n=1024),
     "grouped_gemm": dict(m=32768, n=1024, k=512), "quantile": dict(m=32768, n=1024),
