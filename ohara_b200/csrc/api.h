@@ -64,10 +64,11 @@ void ep_plan(const int* table, const int* indices, int experts, int world, int r
 void ep_zero_fill(const int* fill_begin, const int* fill_end, void* buffer, int local_experts, int d,
                   int capacity_rows, cudaStream_t stream);
 void ep_push_rows(const void* src, const int* dest_rank, const int* dest_row, const float* scale,
-                  const int64_t* buffers, int world, int64_t pairs, int k, int d, cudaStream_t stream);
+                  const int64_t* buffers, int world, int64_t pairs, int k, int d, int capacity,
+                  cudaStream_t stream);
 void ep_pull_combine(const int64_t* buffers, int world, const int* dest_rank, const int* dest_row,
                      const float* scale, const void* other, void* out, float* dot, int64_t tokens,
-                     int k, int d, cudaStream_t stream);
+                     int k, int d, int capacity, cudaStream_t stream);
 
 // stream_ops.cpp
 void stream_wait_value32(cudaStream_t stream, uint64_t addr, uint32_t value);
@@ -131,8 +132,10 @@ void pscan_backward(const float* a, const float* h, const float* dh, float* da, 
 bool sinkhorn_supported(int n, int iters);
 void sinkhorn_forward(const float* in, float* out, int64_t count, int n, int iters,
                       cudaStream_t stream);
-void sinkhorn_backward(const float* in, const float* grad_out, float* grad_in, int64_t count, int n,
-                       int iters, cudaStream_t stream);
+// `tape`: scratch of `count * sinkhorn_tape_floats(n, iters)` floats (may be null when that is 0).
+int64_t sinkhorn_tape_floats(int n, int iters);
+void sinkhorn_backward(const float* in, const float* grad_out, float* grad_in, float* tape,
+                       int64_t count, int n, int iters, cudaStream_t stream);
 
 // attention_bwd_sm100.cu
 void attn_delta(const void* o, const void* d_o, float* delta, int B, int T, int H, int D,

@@ -507,8 +507,13 @@ Tensor sinkhorn_bwd(const Tensor& x, const Tensor& grad_out, int64_t iters) {
   const c10::cuda::CUDAGuard guard(x.device());
   const int64_t n = x.size(-1);
   Tensor grad_in = torch::empty_like(x);
+  const int64_t count = x.numel() / (n * n);
+  const int64_t tape_floats = ob::sinkhorn_tape_floats((int)n, (int)iters);
+  Tensor tape;
+  if (tape_floats > 0) tape = torch::empty({count, tape_floats}, x.options());
   ob::sinkhorn_backward(x.data_ptr<float>(), grad_out.data_ptr<float>(), grad_in.data_ptr<float>(),
-                        x.numel() / (n * n), (int)n, (int)iters, current_stream());
+                        tape_floats > 0 ? tape.data_ptr<float>() : nullptr, count, (int)n,
+                        (int)iters, current_stream());
   return grad_in;
 }
 
@@ -882,8 +887,11 @@ void ep_zero_fill(const Tensor& fill, Tensor& buffer, int64_t d, int64_t capacit
                    (int)d, (int)capacity_rows, current_stream());
 }
 
+// `capacity_rows`: rows of every rank's buffer; a destination at or beyond it (or a rank outside the
+// table) is recorded in the status word as a bad argument and skipped. -1 = unknown (no upper check).
 void ep_push_rows(const Tensor& src, const Tensor& dest_rank, const Tensor& dest_row,
-                  const c10::optional<Tensor>& scale, const std::vector<int64_t>& buffers, int64_t k) {
+                  const c10::optional<Tensor>& scale, const std::vector<int64_t>& buffers, int64_t k,
+                  int64_t capacity_rows) {
   check_bf16(src, "src");
   check_i32(dest_rank, "dest_rank");
   check_i32(dest_row, "dest_row");
@@ -897,13 +905,13 @@ void ep_push_rows(const Tensor& src, const Tensor& dest_rank, const Tensor& dest
   const c10::cuda::CUDAGuard guard(src.device());
   ob::ep_push_rows(src.data_ptr(), dest_rank.data_ptr<int>(), dest_row.data_ptr<int>(), scale_ptr,
                    buffers.data(), (int)buffers.size(), dest_row.numel(), (int)k, (int)src.size(1),
-                   current_stream());
+                   capacity_rows < 0 ? 0x7fffffff : (int)capacity_rows, current_stream());
 }
 
 std::vector<Tensor> ep_pull_combine(const std::vector<int64_t>& buffers, const Tensor& dest_rank,
                                     const Tensor& dest_row, const c10::optional<Tensor>& scale,
                                     const c10::optional<Tensor>& other, int64_t k, int64_t d,
-                                    bool want_out) {
+                                    bool want_out, int64_t capacity_rows) {
   check_i32(dest_rank, "dest_rank");
   check_i32(dest_row, "dest_row");
   const c10::cuda::CUDAGuard guard(dest_row.device());
@@ -928,7 +936,7 @@ std::vector<Tensor> ep_pull_combine(const std::vector<int64_t>& buffers, const T
                       dest_row.data_ptr<int>(), scale_ptr, other_ptr,
                       want_out ? out.data_ptr() : nullptr,
                       other.has_value() ? dot.data_ptr<float>() : nullptr, tokens, (int)k, (int)d,
-                      current_stream());
+                      capacity_rows < 0 ? 0x7fffffff : (int)capacity_rows, current_stream());
   return {out, dot};
 }
 
@@ -1140,8 +1148,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ep_publish_counts", &ep_publish_counts);
   m.def("ep_plan", &ep_plan);
   m.def("ep_zero_fill", &ep_zero_fill);
-  m.def("ep_push_rows", &ep_push_rows);
-  m.def("ep_pull_combine", &ep_pull_combine);
+  m.def("ep_push_rows", &ep_push_rows, py::arg("src"), py::arg("dest_rank"), py::arg("dest_row"),
+        py::arg("scale"), py::arg("buffers"), py::arg("k"), py::arg("capacity_rows") = -1);
+  m.def("ep_pull_combine", &ep_pull_combine, py::arg("buffers"), py::arg("dest_rank"),
+        py::arg("dest_row"), py::arg("scale"), py::arg("other"), py::arg("k"), py::arg("d"),
+        py::arg("want_out"), py::arg("capacity_rows") = -1);
   m.def("peer_row_maps", &peer_row_maps);
   m.def("gemm_gather_a", &gemm_gather_a);
   m.def("gemm_push_c", &gemm_push_c);

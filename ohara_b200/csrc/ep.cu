@@ -134,7 +134,7 @@ template <int VPL>
 __global__ void ep_push_rows_kernel(const __nv_bfloat16* __restrict__ src,
                                     const int* __restrict__ dest_rank, const int* __restrict__ dest_row,
                                     const float* __restrict__ scale, PtrTable buffers, int64_t pairs,
-                                    int k, int d) {
+                                    int k, int d, int world, int capacity, int* status) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -148,6 +148,12 @@ __global__ void ep_push_rows_kernel(const __nv_bfloat16* __restrict__ src,
       my_row = dest_row[t * k + lane];
       my_rank = dest_rank[t * k + lane];
       if (scale != nullptr) my_scale = scale[t * k + lane];
+      // A destination outside the peers' buffers would be a store into memory that is not ours
+      // to write: record it in the status word and drop the pair instead.
+      if (my_row >= 0 && (my_row >= capacity || my_rank < 0 || my_rank >= world)) {
+        report_status(status, kBadArgument);
+        my_row = -1;
+      }
     }
     if constexpr (VPL > 0) {
       bf16x8 x[VPL];
@@ -204,7 +210,8 @@ __global__ void ep_pull_combine_kernel(PtrTable buffers, const int* __restrict__
                                        const float* __restrict__ scale,
                                        const __nv_bfloat16* __restrict__ other,
                                        __nv_bfloat16* __restrict__ out, float* __restrict__ dot,
-                                       int64_t tokens, int k, int d) {
+                                       int64_t tokens, int k, int d, int world, int capacity,
+                                       int* status) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
   const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -231,6 +238,10 @@ __global__ void ep_pull_combine_kernel(PtrTable buffers, const int* __restrict__
         const int64_t j = t * k + i;
         const int row = dest_row[j];
         if (row < 0) continue;
+        if (row >= capacity || dest_rank[j] < 0 || dest_rank[j] >= world) {
+          if (v == lane && lane == 0) report_status(status, kBadArgument);  // skip, do not read
+          continue;
+        }
         const bf16x8 r = reinterpret_cast<const bf16x8*>(
             static_cast<const __nv_bfloat16*>(buffers.ptr[dest_rank[j]]) + (int64_t)row * d)[v];
         const float s = scale != nullptr ? scale[j] : 1.f;
@@ -301,7 +312,7 @@ void ep_zero_fill(const int* fill_begin, const int* fill_end, void* buffer, int 
 }
 
 void ep_push_rows(const void* src, const int* dest_rank, const int* dest_row, const float* scale,
-                  const int64_t* buffers, int world, int64_t pairs, int k, int d,
+                  const int64_t* buffers, int world, int64_t pairs, int k, int d, int capacity,
                   cudaStream_t stream) {
   OB_CHECK(d % 8 == 0 && world <= kMaxEP && k >= 1 && k <= 32 && pairs % k == 0,
            "bad push arguments");
@@ -312,24 +323,24 @@ void ep_push_rows(const void* src, const int* dest_rank, const int* dest_row, co
   const PtrTable table = make_table(buffers, world);
   const int vpl = (d % 256 == 0 && d <= 1024) ? d / 256 : 0;
   switch (vpl) {
-    case 1: ep_push_rows_kernel<1><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d); break;
-    case 2: ep_push_rows_kernel<2><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d); break;
-    case 3: ep_push_rows_kernel<3><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d); break;
-    case 4: ep_push_rows_kernel<4><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d); break;
-    default: ep_push_rows_kernel<0><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d); break;
+    case 1: ep_push_rows_kernel<1><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d, world, capacity, status_ptr()); break;
+    case 2: ep_push_rows_kernel<2><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d, world, capacity, status_ptr()); break;
+    case 3: ep_push_rows_kernel<3><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d, world, capacity, status_ptr()); break;
+    case 4: ep_push_rows_kernel<4><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d, world, capacity, status_ptr()); break;
+    default: ep_push_rows_kernel<0><<<blocks, 256, 0, stream>>>(in, dest_rank, dest_row, scale, table, pairs, k, d, world, capacity, status_ptr()); break;
   }
   OB_LAUNCH_CHECK();
 }
 
 void ep_pull_combine(const int64_t* buffers, int world, const int* dest_rank, const int* dest_row,
                      const float* scale, const void* other, void* out, float* dot, int64_t tokens,
-                     int k, int d, cudaStream_t stream) {
+                     int k, int d, int capacity, cudaStream_t stream) {
   OB_CHECK(d % 8 == 0 && world <= kMaxEP && k >= 1 && k <= kMaxTopK, "bad combine arguments");
   if (tokens == 0) return;
   const int blocks = (int)std::min<int64_t>((tokens + 7) / 8, device_sm_count() * 16);
   ep_pull_combine_kernel<<<blocks, 256, 0, stream>>>(
       make_table(buffers, world), dest_rank, dest_row, scale, static_cast<const __nv_bfloat16*>(other),
-      static_cast<__nv_bfloat16*>(out), dot, tokens, k, d);
+      static_cast<__nv_bfloat16*>(out), dot, tokens, k, d, world, capacity, status_ptr());
   OB_LAUNCH_CHECK();
 }
 

@@ -3,9 +3,10 @@ hyper-connections; reference: experiments/mHC/sinkhorn.py:15-20 and its Triton k
 
 ``sinkhorn_log(log_alpha, iters)``: subtract the maximum of each matrix, then ``iters`` times
 subtract the row log-sum-exp and the column log-sum-exp, and return ``exp`` of the result. CUDA
-tensors with matrices of 2 to 4 rows run the register-resident kernel of ``csrc/sinkhorn.cu``
-(forward and an exact vector-Jacobian product); everything else runs the PyTorch expression below,
-which is also the oracle of the kernel's tests.
+tensors run the kernels of ``csrc/sinkhorn.cu`` (forward and an exact vector-Jacobian product):
+matrices of 2 to 4 rows live in the registers of one thread, matrices of 5 to 64 rows (the range of
+the reference's fused Triton kernel) in the shared memory of one block. Everything else runs the
+PyTorch expression below, which is also the oracle of the kernels' tests.
 """
 
 from __future__ import annotations

@@ -135,7 +135,7 @@ class EPWorkspace:
             # step ago, and the barriers of ``plan`` lie between them and this push
             target = self._slot(self.landing_slots, slot)
         ext().ep_push_rows(rows.contiguous(), plan.dest_rank, plan.dest_row, scale,
-                           target.pointers, plan.top_k)
+                           target.pointers, plan.top_k, self.capacity_rows)
         self.runtime.barrier()  # all rows have landed
         landed = target.typed(torch.bfloat16)[: self.capacity_rows * d].view(self.capacity_rows, d)
         ext().ep_zero_fill(plan.fill, landed, d, self.capacity_rows)
@@ -154,7 +154,7 @@ class EPWorkspace:
             mine.copy_(padded)
         self.runtime.barrier()  # everyone's rows are published
         out, dots = ext().ep_pull_combine(source.pointers, plan.dest_rank, plan.dest_row, scale,
-                                          other, plan.top_k, d, want_out)
+                                          other, plan.top_k, d, want_out, self.capacity_rows)
         self.runtime.barrier()  # everyone has finished reading before the outbox is reused
         return out, dots
 

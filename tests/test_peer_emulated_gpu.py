@@ -145,3 +145,28 @@ def test_context_parallel_merge_of_two_key_sets_equals_attention_over_their_unio
     assert (merged.float() - want.float()).abs().max() <= 2e-2 * want.float().abs().max()
     whole, lse_whole = C.flash_attn_fwd(q, k, v, False, scale)
     assert torch.allclose(lse, lse_whole, atol=2e-2, rtol=1e-3)
+
+
+def test_out_of_range_destination_is_reported_and_skipped(C):
+    """A (rank, row) destination outside the peers' buffers must not be written to: the push
+    records a bad-argument status, skips the pair and leaves every buffer untouched; the combine
+    skips the read."""
+    from ohara_b200 import ops
+
+    d, capacity = 64, 256
+    x = torch.ones(4, d, device="cuda").bfloat16()
+    buffers = [torch.zeros(capacity, d, device="cuda").bfloat16() for _ in range(2)]
+    dest_rank = torch.tensor([0, 1, 5, 1], dtype=torch.int32, device="cuda")    # rank 5 does not exist
+    dest_row = torch.tensor([3, capacity, 7, 9], dtype=torch.int32, device="cuda")  # row == capacity
+    C.ep_push_rows(x, dest_rank, dest_row, None, [b.data_ptr() for b in buffers], 1, capacity)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="bad kernel argument"):
+        ops.check_status()
+    assert float(buffers[0][3].sum()) == d and float(buffers[1][9].sum()) == d   # the valid pairs
+    assert float(buffers[0].sum()) == d and float(buffers[1].sum()) == d         # nothing else
+    out, _ = C.ep_pull_combine([b.data_ptr() for b in buffers], dest_rank, dest_row, None, None, 1, d,
+                               True, capacity)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="bad kernel argument"):
+        ops.check_status()
+    assert out.float().sum(1).tolist() == [d, 0.0, 0.0, d]

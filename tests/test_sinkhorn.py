@@ -1,5 +1,5 @@
 """Sinkhorn normalisation: the PyTorch expression on CPU (properties) and, on a GPU, the
-register-resident kernel against it (values and gradients)."""
+register-resident and block-resident kernels against it (values and gradients)."""
 
 import pytest
 import torch
@@ -20,11 +20,13 @@ def test_reference_is_doubly_stochastic_and_shift_invariant():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("n,iters", [(2, 5), (3, 12), (4, 20), (4, 1)])
+@pytest.mark.parametrize("n,iters", [(2, 5), (3, 12), (4, 20), (4, 1), (5, 8), (8, 20), (16, 10),
+                                     (33, 6), (64, 12)])
 def test_kernel_matches_reference_values_and_gradients(n, iters):
     torch.manual_seed(1)
-    x = (torch.randn(3, 129, n, n, device="cuda") * 2).requires_grad_()
-    w = torch.randn(3, 129, n, n, device="cuda")
+    count = 129 if n <= 8 else 17
+    x = (torch.randn(3, count, n, n, device="cuda") * 2).requires_grad_()
+    w = torch.randn(3, count, n, n, device="cuda")
     out = sinkhorn_log(x, iters)
     (out * w).sum().backward()
     xr = x.detach().double().requires_grad_()
@@ -35,6 +37,6 @@ def test_kernel_matches_reference_values_and_gradients(n, iters):
 
 
 @pytest.mark.gpu
-def test_larger_matrices_fall_back_to_the_expression():
-    x = torch.randn(10, 8, 8, device="cuda")
+def test_matrices_beyond_the_kernels_fall_back_to_the_expression():
+    x = torch.randn(4, 80, 80, device="cuda")
     assert torch.allclose(sinkhorn_log(x, 10), sinkhorn_reference(x, 10), atol=1e-6)
