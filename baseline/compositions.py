@@ -320,21 +320,11 @@ def _dispatch_all_to_all(self, flat_x, expert_indices, expert_weights):
 
 
 def apply_router_skew(model, spec: dict, cfg, device) -> None:
-    """The same fixed selection bias as the other arm: the first eight experts of every layer are
-    favoured so that they receive about half of the top-k picks."""
+    """The same fixed selection bias as the other arm (calibrated the same way, on this arm's own
+    router logits): the first eight experts of every layer receive about half of the top-k picks."""
     from ohara.modules.moe_grouped import GroupedMoE
 
-    from bench import skew_offset
+    from bench import calibrate_router_skew
 
-    m = spec["model"]
-    offset = skew_offset(m["moe_num_experts"], m["moe_experts_per_tok"], 8, 0.5)
-    inner = model.module if hasattr(model, "module") else model
-    probe = torch.randint(0, cfg.vocab_size, (2, min(spec["seq_len"], 512)), device=device)
-    with torch.no_grad():
-        flat = inner.token_emb(probe).reshape(-1, cfg.hidden_size).float()
-        flat = flat / flat.square().mean(-1, keepdim=True).sqrt().clamp_min(1e-6)
-        for layer in inner.modules():
-            if isinstance(layer, GroupedMoE):
-                spread = float((flat @ layer.router.weight.float().t()).std())
-                layer.router_bias.zero_()
-                layer.router_bias[:8] = offset * spread
+    probe = torch.randint(0, cfg.vocab_size, (2, min(spec["seq_len"], 2048)), device=device)
+    calibrate_router_skew(model, GroupedMoE, probe, spec["model"]["moe_experts_per_tok"])

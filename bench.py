@@ -270,22 +270,57 @@ def synthetic_conversations(count: int, vocab_size: int, seed: int) -> list[dict
     return conversations
 
 
-def skew_offset(num_experts: int, top_k: int, favoured: int, share: float) -> float:
-    """Offset ``c`` (in units of the router logits' standard deviation) to add to ``favoured``
-    experts so that, for i.i.d. normal logits, they receive ``share`` of the top-k picks."""
-    import torch
+def calibrate_router_skew(model, moe_class, probe_tokens, top_k: int, favoured: int = 8,
+                          share: float = 0.5) -> list[float]:
+    """Set a fixed selection bias on the first ``favoured`` experts of every mixture-of-experts
+    layer of ``model`` so that they receive ``share`` of the top-k picks, and return the offsets.
 
-    gen = torch.Generator().manual_seed(0)
-    logits = torch.randn(20000, num_experts, generator=gen)
-    lo, hi = 0.0, 8.0
-    for _ in range(30):
-        mid = (lo + hi) / 2
-        shifted = logits.clone()
-        shifted[:, :favoured] += mid
-        picks = shifted.topk(top_k, dim=-1).indices
-        got = float((picks < favoured).float().mean())
-        lo, hi = (mid, hi) if got < share else (lo, mid)
-    return (lo + hi) / 2
+    One forward pass over ``probe_tokens`` records what every layer's router actually sees; the
+    offset of a layer is then found by bisection on that layer's own logits (at random init the
+    hidden states of different tokens share a large common component, so the logits are far from
+    i.i.d. and a closed-form offset misses the target by a factor of two). With several ranks the
+    offsets are averaged so that the replicated bias stays identical everywhere. Used by both
+    arms; ``moe_class`` is the arm's own grouped mixture-of-experts module."""
+    import torch
+    import torch.distributed as dist
+
+    layers = [m for m in model.modules() if isinstance(m, moe_class)]
+    seen: dict[int, torch.Tensor] = {}
+    hooks = [layer.register_forward_pre_hook(
+        lambda mod, args, i=i: seen.__setitem__(i, args[0].detach().reshape(-1, args[0].shape[-1])))
+        for i, layer in enumerate(layers)]
+    was_training = model.training
+    model.eval()
+    try:
+        with torch.no_grad():
+            for layer in layers:
+                layer.router_bias.zero_()
+            device_type = probe_tokens.device.type
+            with torch.autocast(device_type, dtype=torch.bfloat16, enabled=device_type == "cuda"):
+                model(probe_tokens)
+    finally:
+        for hook in hooks:
+            hook.remove()
+        model.train(was_training)
+    offsets = []
+    with torch.no_grad():
+        for i, layer in enumerate(layers):
+            logits = seen[i].float() @ layer.router.weight.float().t()
+            lo, hi = 0.0, 16.0 * float(logits.std().clamp_min(1e-6))
+            for _ in range(24):
+                mid = (lo + hi) / 2
+                shifted = logits.clone()
+                shifted[:, :favoured] += mid
+                got = float((shifted.topk(top_k, dim=-1).indices < favoured).float().mean())
+                lo, hi = (mid, hi) if got < share else (lo, mid)
+            offset = torch.tensor((lo + hi) / 2, device=logits.device)
+            if dist.is_available() and dist.is_initialized():
+                dist.all_reduce(offset)
+                offset /= dist.get_world_size()
+            layer.router_bias.zero_()
+            layer.router_bias[:favoured] = offset
+            offsets.append(float(offset))
+    return offsets
 
 
 # --------------------------------------------------------------------------------------------------
@@ -344,23 +379,15 @@ def run_ours(args) -> dict:
 
     skew = None
     if spec.get("skewed"):
-        # A fixed selection bias on the first eight experts of every layer, sized from the spread
-        # of that layer's router logits on a probe batch; the balancing update stays off so that
-        # the skew persists.
+        # A fixed selection bias on the first eight experts of every layer, calibrated on the
+        # layer's own router logits of a probe batch; the balancing update stays off so that the
+        # skew persists.
         from ohara_b200.modules.moe_grouped import GroupedMoE
 
-        offset = skew_offset(m["moe_num_experts"], m["moe_experts_per_tok"], 8, 0.5)
-        layers = [mod for mod in model.modules() if isinstance(mod, GroupedMoE)]
-        probe = torch.randint(0, vocab, (2, min(seq, 512)), device=device)
-        with torch.no_grad():
-            # the router reads RMS-normalised hidden states: unit-RMS rows stand in for them
-            flat = model.token_emb(probe).reshape(-1, cfg.hidden_size).float()
-            flat = flat / flat.square().mean(-1, keepdim=True).sqrt().clamp_min(1e-6)
-            for layer in layers:
-                spread = float((flat @ layer.router.weight.float().t()).std())
-                layer.router_bias.zero_()
-                layer.router_bias[:8] = offset * spread
-        skew = {"favoured_experts": 8, "target_share": 0.5, "offset_sigma": offset}
+        probe = torch.randint(0, vocab, (2, min(seq, 2048)), device=device)
+        offsets = calibrate_router_skew(model, GroupedMoE, probe, m["moe_experts_per_tok"])
+        skew = {"favoured_experts": 8, "target_share": 0.5,
+                "offset_first_layer": offsets[0], "offset_last_layer": offsets[-1]}
 
     dp_rank, dp_world = engine.data_parallel_rank, engine.data_parallel_world_size
 
