@@ -320,11 +320,10 @@ def _dispatch_all_to_all(self, flat_x, expert_indices, expert_weights):
 
 
 def apply_router_skew(model, spec: dict, cfg, device) -> None:
-    """The same fixed selection bias as the other arm (calibrated the same way, on this arm's own
-    router logits): the first eight experts of every layer receive about half of the top-k picks."""
+    """The same forced selection bias as the other arm: half of every token's picks go to a few
+    experts of the first rank."""
     from ohara.modules.moe_grouped import GroupedMoE
 
-    from bench import calibrate_router_skew
+    from bench import force_router_skew
 
-    probe = torch.randint(0, cfg.vocab_size, (2, min(spec["seq_len"], 2048)), device=device)
-    calibrate_router_skew(model, GroupedMoE, probe, spec["model"]["moe_experts_per_tok"])
+    force_router_skew(model, GroupedMoE, spec["model"]["moe_experts_per_tok"])
