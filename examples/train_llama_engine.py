@@ -135,6 +135,9 @@ def parse_args() -> argparse.Namespace:
                      help="seconds between heartbeats over the rendezvous store (0 = off); a rank "
                           "whose heartbeat stops is reported before the next step is launched")
     run.add_argument("--heartbeat-timeout", type=float, default=30.0)
+    run.add_argument("--activation-checkpointing", action="store_true",
+                     help="recompute every block in the backward pass instead of keeping its "
+                          "activations (less memory, about a third more compute)")
     run.add_argument("--profile-sections", action="store_true",
                      help="time the phases of every step on the device (CUDA events, max over "
                           "ranks) and print the totals at the end; OHARA_NVTX=1 adds NVTX ranges")
@@ -319,6 +322,7 @@ def run() -> None:
         precision=PrecisionConfig(mode=PrecisionMode(args.precision)),
         parallel=ParallelConfig(tp=args.tp, cp=args.cp, ep=args.ep),
         tensor_parallel=TensorParallelPlan.llama_default(args.tp, args.sequence_parallel),
+        activation_checkpointing=args.activation_checkpointing,
         fault_tolerance=FaultToleranceConfig(
             heartbeat_interval_s=args.heartbeat_interval, heartbeat_timeout_s=args.heartbeat_timeout,
             step_timeout_s=args.step_timeout, exit_on_step_timeout=args.step_timeout > 0),

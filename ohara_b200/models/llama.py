@@ -251,6 +251,21 @@ class Block(nn.Module):
         return x, self.ff(h)
 
 
+def _recompute_contexts():
+    from contextlib import nullcontext
+
+    from ohara_b200.modules.routing import recomputing
+
+    return nullcontext(), recomputing()
+
+
+def _checkpointed_block(layer: "Block", h: Tensor, pending: Tensor | None, freqs):
+    from torch.utils.checkpoint import checkpoint
+
+    return checkpoint(layer.forward_deferred, h, pending, freqs, use_reentrant=False,
+                      context_fn=_recompute_contexts)
+
+
 class Llama(nn.Module):
     def __init__(self, cfg: Config, *args, **kwargs) -> None:
         super().__init__(*args, **kwargs)
@@ -266,6 +281,9 @@ class Llama(nn.Module):
         self.register_buffer("freq_cos", cos)
         self.register_buffer("freq_sin", sin)
         self.mask = None  # kept for API parity; masks are never materialised here
+        # Extension over the reference: recompute every block's activations in the backward pass
+        # instead of keeping them (see enable_activation_checkpointing).
+        self.activation_checkpointing = False
         self.apply(self._init_weights)
         if cfg.init_style == "nanochat":
             self._init_nanochat_weights()
@@ -351,12 +369,26 @@ class Llama(nn.Module):
         if kv_cache is not None and x.is_cuda and seq == 1:
             freqs = (*freqs, *self._rope_tables_f32())
         pending = None
+        recompute = (self.activation_checkpointing and kv_cache is None and self.training
+                     and torch.is_grad_enabled())
         for idx, layer in enumerate(self.layers):
+            if recompute:
+                h, pending = _checkpointed_block(layer, h, pending, freqs)
+                continue
             cache = kv_cache[idx] if kv_cache is not None else None
             h, pending = layer.forward_deferred(
                 h, pending, freqs, cache, start if cache is not None else None
             )
         return ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[0]
+
+    def enable_activation_checkpointing(self, enabled: bool = True) -> "Llama":
+        """Keep only each block's input during the forward pass of a training step and run the
+        block a second time in the backward pass to rebuild what its gradients need. Activation
+        memory drops from everything a block saves (norm outputs, q/k/v, attention output and
+        log-sum-exp, gate/up/activation, routed rows) to one residual-stream tensor pair per
+        block, for about a third more compute. Routers do not count the recomputed tokens."""
+        self.activation_checkpointing = bool(enabled)
+        return self
 
     supports_fused_loss = True
 

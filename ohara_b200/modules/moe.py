@@ -15,6 +15,7 @@ from ohara_b200.modules.routing import (  # noqa: F401  (public re-exports)
     QuantileBalancedRouter,
     apply_qb_update,
     expert_load,
+    is_recomputing,
     maximal_violation,
     route_tokens,
     router_logits,
@@ -55,7 +56,7 @@ class MoE(QuantileBalancedRouter):
             self.quantile_balancing,
         )
         out = self._dispatch(flat, indices, weights.to(x.dtype))
-        if self.training:
+        if self.training and not is_recomputing():
             if self.quantile_balancing:
                 self._accumulate_qb(logits.detach(), alpha.detach())
             self._record_load(indices.detach())

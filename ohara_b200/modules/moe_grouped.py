@@ -29,6 +29,7 @@ from ohara_b200.ops.grouped import grouped_swiglu_experts
 from ohara_b200.modules.mlp import Linear
 from ohara_b200.modules.routing import (
     QuantileBalancedRouter,
+    is_recomputing,
     load_balance_aux_loss,
     route_tokens,
     router_logits,
@@ -171,16 +172,23 @@ class GroupedMoE(QuantileBalancedRouter):
         if self.num_shared_experts > 0:
             out = out + self._shared(flat_x).to(out.dtype)
         if self.training:
+            # The recomputation pass of an activation-checkpointed block repeats the operations of
+            # the first pass (autograd matches the tensors they save one by one) but leaves the
+            # layer's state alone: the tokens were counted the first time.
+            first_pass = not is_recomputing()
             if self.aux_loss_coef > 0.0:
-                self.aux_loss = self.aux_loss_coef * load_balance_aux_loss(
+                aux_loss = self.aux_loss_coef * load_balance_aux_loss(
                     logits, indices.long(), self.num_experts
                 )
-            if self.quantile_balancing:
-                self._accumulate_qb(logits.detach(), alpha.detach())
-            if counts is not None:
-                self.expert_counts += counts
-            else:
-                self._record_load(indices.detach())
+                if first_pass:
+                    self.aux_loss = aux_loss
+            if first_pass:
+                if self.quantile_balancing:
+                    self._accumulate_qb(logits.detach(), alpha.detach())
+                if counts is not None:
+                    self.expert_counts += counts
+                else:
+                    self._record_load(indices.detach())
         return out.view(batch, seq, dim)
 
     # -- expert parallelism ----------------------------------------------------------------

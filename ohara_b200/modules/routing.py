@@ -21,6 +21,29 @@ def router_logits(flat: Tensor, weight: Tensor) -> Tensor:
         return torch.nn.functional.linear(flat.float(), weight.float())
 
 
+_RECOMPUTING = False
+
+
+class recomputing:
+    """Context manager for the second forward pass of an activation-checkpointed block: routers
+    inside it do not count the tokens again (load, balancing statistics)."""
+
+    def __enter__(self):
+        global _RECOMPUTING
+        self._previous = _RECOMPUTING
+        _RECOMPUTING = True
+        return self
+
+    def __exit__(self, *exc):
+        global _RECOMPUTING
+        _RECOMPUTING = self._previous
+        return False
+
+
+def is_recomputing() -> bool:
+    return _RECOMPUTING
+
+
 def route_tokens(logits: Tensor, router_bias: Tensor, k: int, gate_fn: str,
                  quantile_balancing: bool, normalize_sigmoid: bool = False):
     """Return ``(expert_indices (N,k), expert_weights (N,k) fp32, alpha (N,1) | None)``."""

@@ -59,3 +59,6 @@ class EngineConfig:
     # Expert parallelism: rows a rank can receive for its experts in one layer, as a multiple of
     # its fair share; pairs beyond it are dropped.
     expert_capacity_factor: float = 2.0
+    # Recompute every transformer block in the backward pass instead of keeping its activations
+    # (models that offer ``enable_activation_checkpointing``).
+    activation_checkpointing: bool = False

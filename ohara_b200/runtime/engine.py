@@ -355,6 +355,12 @@ class OharaEngine:
             else:
                 module = module.to(self._device)
         self._equalise_initial_weights(module)
+        if self.config.activation_checkpointing:
+            enable = getattr(module, "enable_activation_checkpointing", None)
+            if not callable(enable):
+                raise ValueError("activation_checkpointing needs a model that offers "
+                                 "enable_activation_checkpointing() (Llama)")
+            enable(True)
         module = self._maybe_apply_tensor_parallel(module)
         module = self._maybe_apply_pipeline_parallel(module)
         self._maybe_apply_context_parallel(module)

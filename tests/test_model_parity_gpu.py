@@ -84,3 +84,35 @@ def test_grouped_moe_llama_matches_the_fp32_cpu_model():
     worst = _compare(cfg, grad_tol=0.25, loss_tol=1e-2)
     dense = [err for name, err in worst.items() if ".ff.w_" not in name and "router" not in name]
     assert max(dense) <= 0.12, max(dense)
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_activation_checkpointing_reproduces_the_plain_step_on_the_kernels(moe):
+    """The recomputation pass runs the same kernels on the same inputs, so the loss and every
+    gradient of the checkpointed step equal the plain step's bit for bit (dense) or up to the
+    order of the atomic adds of the routed combine (MoE)."""
+    extra = dict(moe_num_experts=8, moe_experts_per_tok=2, moe_grouped=True,
+                 moe_num_shared_experts=1, moe_aux_loss_coef=0.01) if moe else {}
+    cfg = Config(vocab_size=512, max_sequence_length=256, hidden_size=256, intermediate_size=128,
+                 num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=3, dropout=0.0,
+                 **extra)
+    _, plain = _pair(cfg)
+    recomputed = copy.deepcopy(plain).enable_activation_checkpointing()
+    plain.train(), recomputed.train()
+    torch.manual_seed(1)
+    ids = torch.randint(0, cfg.vocab_size, (3, 193)).cuda()
+    loss_a, grads_a = _step(plain, ids, autocast=True)
+    loss_b, grads_b = _step(recomputed, ids, autocast=True)
+    torch.cuda.synchronize()
+    from ohara_b200 import ops
+    from ohara_b200.modules.routing import expert_load
+
+    ops.check_status()
+    assert abs(loss_a - loss_b) <= 1e-6 * abs(loss_a)
+    assert set(grads_a) == set(grads_b)
+    for name, want in grads_a.items():
+        err = float((grads_b[name] - want).norm() / want.norm().clamp_min(1e-12))
+        assert err <= (2e-2 if moe else 1e-3), f"{name}: {err:.4f}"
+    if moe:
+        for a, b in zip(expert_load(plain), expert_load(recomputed)):
+            assert torch.equal(a, b)
