@@ -352,6 +352,11 @@ class Llama(nn.Module):
             return ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[0]
         start = self._check_inputs(x, kv_cache, position_ids)
         seq = x.size(1)
+        if getattr(self, "_param_sharding", None) is not None:
+            if kv_cache is not None:
+                raise NotImplementedError("decoding with a KV cache needs whole parameters: "
+                                          "load the full state dict into an unsharded model")
+            return self._forward_hidden_sharded(x, seq)
         cp = getattr(self, "_cp", None)
         if cp is not None and kv_cache is None:
             if cp[1] * seq > self.config.max_sequence_length:
@@ -379,6 +384,25 @@ class Llama(nn.Module):
             h, pending = layer.forward_deferred(
                 h, pending, freqs, cache, start if cache is not None else None
             )
+        return ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[0]
+
+    def _forward_hidden_sharded(self, x: Tensor, seq: int) -> Tensor:
+        """The same pass with the parameters sharded per block
+        (:mod:`ohara_b200.parallel.param_shard`): every unit is gathered just before it runs and
+        released after it; the final norm and the output projection stay gathered for the loss
+        and the start of the backward pass."""
+        sharding = self._param_sharding
+        h = sharding.run_unit("embed", lambda ids: ops.embedding(ids, self.token_emb.weight), x)
+        freqs = (self.freq_cos[:seq], self.freq_sin[:seq])
+        recompute = self.activation_checkpointing and self.training and torch.is_grad_enabled()
+        pending = None
+        for idx, layer in enumerate(self.layers):
+            if recompute:
+                block = lambda a, b, layer=layer: _checkpointed_block(layer, a, b, freqs)  # noqa: E731
+            else:
+                block = lambda a, b, layer=layer: layer.forward_deferred(a, b, freqs)  # noqa: E731
+            h, pending = sharding.run_unit(f"layers.{idx}", block, h, pending)
+        sharding.enter_unit("embed" if sharding.tied else "head")
         return ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[0]
 
     def enable_activation_checkpointing(self, enabled: bool = True) -> "Llama":

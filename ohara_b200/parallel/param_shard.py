@@ -1,0 +1,501 @@
+"""Parameter sharding per transformer block (what FSDP2's ``fully_shard`` does), for models that are
+too large to keep a full copy of their weights on every GPU.
+
+:class:`ohara_b200.parallel.zero.ShardedOptimizer` shards the optimizer state and the master
+weights but leaves a full copy of the parameters and of the gradients on every rank. Here a rank
+keeps, between uses, only ``1 / world`` of every parameter:
+
+* the model is cut into *units* (the embedding, every block, the final norm + output projection);
+* each unit's parameters are one flat fp32 vector, padded to ``world`` equal regions; rank ``r``
+  owns region ``r`` as its master shard and holds optimizer state for that region only;
+* before a unit runs (forward, and again backward) its vector is all-gathered into a transient
+  buffer and the unit's ``nn.Parameter`` objects are pointed at views of it; the gather of the next
+  unit (the previous one in the backward pass) is issued before the current unit computes, so it
+  overlaps; after use the parameters are pointed back at a shape-only placeholder and the buffer
+  is released;
+* when the last gradient of a unit has been accumulated, the unit's gradients are packed,
+  reduce-scattered (mean) and added to the rank's fp32 gradient shard, and the full gradients are
+  dropped. Every parameter of a unit must therefore receive a gradient on every rank in every
+  backward pass (true for the dense and the grouped-MoE Llama).
+
+At most two units are gathered at a time (three around the hand-over), so the parameter memory of a
+rank is ``total / world`` plus about two blocks instead of ``total``.
+
+The collectives are the process group's ``all_gather_into_tensor`` / ``reduce_scatter_tensor``
+(NCCL on GPUs, gloo on CPUs, where the reduce-scatter is an all-reduce plus a slice). The reference
+has nothing of the kind (``dp_shard`` is arithmetic only: ohara/runtime/topology.py:33-38).
+
+Limits: data parallelism only (no tensor / context / expert / pipeline composition), element-wise
+optimizers only (AdamW; a whole-matrix algorithm would need each matrix on one rank), fp32 on the
+wire. A resharded parameter keeps its shape, ``numel()`` and ``ndim`` but reads as one repeated
+element: take state dicts through :meth:`ParameterSharding.full_state_dict`.
+"""
+
+from __future__ import annotations
+
+from contextlib import contextmanager
+from typing import Any, Callable, Iterable
+
+import torch
+import torch.distributed as dist
+from torch import Tensor, nn
+from torch.optim import Optimizer
+
+ALIGN = 64  # elements: every parameter starts 256 bytes into the flat vector at the least
+
+
+class _Unit:
+    """One all-gather / reduce-scatter granule."""
+
+    def __init__(self, name: str, params: list[nn.Parameter], world: int, rank: int,
+                 reshard_after_forward: bool) -> None:
+        self.name = name
+        self.params = params
+        self.reshard_after_forward = reshard_after_forward
+        self.shapes = [tuple(p.shape) for p in params]
+        self.numels = [p.numel() for p in params]
+        self.offsets: list[int] = []
+        cursor = 0
+        for n in self.numels:
+            self.offsets.append(cursor)
+            cursor += (n + ALIGN - 1) // ALIGN * ALIGN
+        chunk = world * ALIGN
+        self.total = max((cursor + chunk - 1) // chunk * chunk, chunk)
+        self.region = self.total // world
+        device = params[0].device
+        flat = torch.zeros(self.total, device=device, dtype=torch.float32)
+        for p, off, n in zip(params, self.offsets, self.numels):
+            flat[off : off + n].copy_(p.detach().reshape(-1).float())
+        self.master = flat[rank * self.region : (rank + 1) * self.region].clone()
+        self.grad: Tensor | None = None          # reduced mean gradient of this rank's region
+        self.full: Tensor | None = None          # gathered vector while the unit is unsharded
+        self.work: Any | None = None             # pending all-gather
+        self.bound = False                       # parameters point at ``full``
+        self.trainable = sum(1 for p in params if p.requires_grad)
+        self.remaining = self.trainable          # gradients still to come in this backward pass
+        self.placeholders = [torch.zeros(1, device=device, dtype=torch.float32).expand(shape)
+                             for shape in self.shapes]
+
+    @property
+    def gathered(self) -> bool:
+        return self.full is not None and self.work is None
+
+
+def _drop_compute_copies(param: nn.Parameter) -> None:
+    """Forget the bf16 / fp32 compute copies that the kernels' front-ends cache on a parameter:
+    they belong to the buffer the parameter pointed at before."""
+    for name in ("_ohara_bf16", "_ohara_f32"):
+        if getattr(param, name, None) is not None:
+            setattr(param, name, None)
+
+
+class _PreBackward(torch.autograd.Function):
+    """Identity on a unit's outputs; its backward runs before the unit's own backward and makes
+    sure the unit's parameters are gathered by then."""
+
+    @staticmethod
+    def forward(ctx, sharding, unit, *tensors):
+        ctx.sharding, ctx.unit = sharding, unit
+        return tuple(t.view_as(t) for t in tensors)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        ctx.sharding._pre_backward(ctx.unit)
+        return (None, None, *grads)
+
+
+class ParameterSharding:
+    """Shards ``units`` (``[(name, [parameters]), ...]`` in execution order) over ``group``.
+
+    The model drives it: ``run_unit(name, fn, *args)`` around every unit that is released after
+    its forward pass, ``enter_unit(name)`` before a unit that stays gathered until its gradients
+    are complete, and ``finish_backward()`` after ``loss.backward()`` (``OharaEngine.backward``
+    does that)."""
+
+    def __init__(self, units: Iterable[tuple[str, list[nn.Parameter]]], group=None, *,
+                 keep_gathered: Iterable[str] = (), prefetch: bool = True) -> None:
+        self.group = group
+        distributed = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if distributed else 1
+        self.rank = dist.get_rank(group) if distributed else 0
+        self.prefetch = prefetch
+        keep = set(keep_gathered)
+        seen: set[int] = set()
+        self.units: list[_Unit] = []
+        self.by_name: dict[str, _Unit] = {}
+        self.unit_of_param: dict[int, _Unit] = {}
+        for name, params in units:
+            fresh = [p for p in params if id(p) not in seen]
+            if not fresh:
+                continue
+            seen.update(id(p) for p in fresh)
+            unit = _Unit(name, fresh, self.world, self.rank, name not in keep)
+            unit.index = len(self.units)
+            self.units.append(unit)
+            self.by_name[name] = unit
+            for p in fresh:
+                self.unit_of_param[id(p)] = unit
+                if p.requires_grad:
+                    p.register_post_accumulate_grad_hook(self._on_gradient)
+        self.unsharded_bytes = sum(sum(u.numels) for u in self.units) * 4
+        self.peak_gathered_bytes = 0
+        for unit in self.units:
+            self._release(unit)
+
+    # -- gather / release ------------------------------------------------------------------------
+    def _issue(self, unit: _Unit, asynchronous: bool) -> None:
+        if unit.full is not None:
+            return
+        unit.full = torch.empty(unit.total, device=unit.master.device, dtype=torch.float32)
+        if self.world == 1:
+            unit.full.copy_(unit.master)
+            return
+        work = dist.all_gather_into_tensor(unit.full, unit.master, group=self.group,
+                                           async_op=asynchronous)
+        unit.work = work if asynchronous else None
+
+    def _bind(self, unit: _Unit) -> None:
+        if unit.work is not None:
+            unit.work.wait()
+            unit.work = None
+        for p, off, n, shape in zip(unit.params, unit.offsets, unit.numels, unit.shapes):
+            view = unit.full[off : off + n].view(shape)
+            # Vectors (norm weights) get their own small tensor: kernels keep a reference to the
+            # fp32 vector for their backward pass, and a view would keep the whole gathered
+            # buffer alive until then.
+            p.data = view.clone() if len(shape) <= 1 else view
+            _drop_compute_copies(p)
+        unit.bound = True
+        gathered = sum(u.total for u in self.units if u.full is not None) * 4
+        self.peak_gathered_bytes = max(self.peak_gathered_bytes, gathered)
+
+    def unshard(self, unit: _Unit) -> None:
+        """Gather ``unit`` now (waits for a prefetch in flight) and point its parameters at it."""
+        if unit.gathered and unit.bound:
+            return
+        self._issue(unit, asynchronous=False)
+        self._bind(unit)
+
+    def _release(self, unit: _Unit) -> None:
+        if unit.work is not None:
+            unit.work.wait()
+            unit.work = None
+        for p, placeholder in zip(unit.params, unit.placeholders):
+            p.data = placeholder
+            _drop_compute_copies(p)
+        unit.full = None
+        unit.bound = False
+
+    def _neighbour(self, unit: _Unit, step: int) -> _Unit | None:
+        index = unit.index + step
+        return self.units[index] if 0 <= index < len(self.units) else None
+
+    # -- what the model calls --------------------------------------------------------------------
+    def enter_unit(self, name: str) -> None:
+        """Gather a unit that stays gathered until its gradients are complete."""
+        unit = self.by_name[name]
+        self.unshard(unit)
+        following = self._neighbour(unit, +1)
+        if self.prefetch and following is not None:
+            self._issue(following, asynchronous=True)
+
+    def run_unit(self, name: str, fn: Callable, *args):
+        """``fn(*args)`` with the unit's parameters gathered; released again afterwards."""
+        unit = self.by_name[name]
+        self.unshard(unit)
+        following = self._neighbour(unit, +1)
+        if self.prefetch and following is not None:
+            self._issue(following, asynchronous=True)
+        out = fn(*args)
+        if torch.is_grad_enabled():
+            # backward of the marker runs before the unit's own backward: gather (a unit that
+            # stayed gathered is there already) and prefetch the unit before it
+            single = isinstance(out, Tensor)
+            items = (out,) if single else tuple(out)
+            live = [i for i, t in enumerate(items) if isinstance(t, Tensor) and t.requires_grad]
+            if live:
+                marked = _PreBackward.apply(self, unit, *[items[i] for i in live])
+                items = list(items)
+                for i, t in zip(live, marked):
+                    items[i] = t
+                out = items[0] if single else tuple(items)
+        if unit.reshard_after_forward or not torch.is_grad_enabled():
+            self._release(unit)
+        return out
+
+    def _pre_backward(self, unit: _Unit) -> None:
+        self.unshard(unit)
+        previous = self._neighbour(unit, -1)
+        if self.prefetch and previous is not None and previous.trainable:
+            self._issue(previous, asynchronous=True)
+
+    # -- gradients -------------------------------------------------------------------------------
+    def _on_gradient(self, param: nn.Parameter) -> None:
+        unit = self.unit_of_param[id(param)]
+        unit.remaining -= 1
+        if unit.remaining == 0:
+            self._reduce(unit)
+
+    @torch.no_grad()
+    def _reduce(self, unit: _Unit) -> None:
+        """Pack the unit's gradients, reduce-scatter the mean into this rank's gradient shard,
+        drop the full gradients and release the unit."""
+        if unit.trainable and any(p.grad is not None for p in unit.params):
+            flat = torch.zeros(unit.total, device=unit.master.device, dtype=torch.float32)
+            for p, off, n in zip(unit.params, unit.offsets, unit.numels):
+                if p.grad is not None:
+                    flat[off : off + n].copy_(p.grad.reshape(-1))
+                    p.grad = None
+            if self.world == 1:
+                shard = flat
+            elif dist.get_backend(self.group) == "gloo":  # gloo has no reduce-scatter
+                dist.all_reduce(flat, group=self.group)
+                shard = flat[self.rank * unit.region : (self.rank + 1) * unit.region].clone()
+            else:
+                shard = torch.empty(unit.region, device=flat.device, dtype=torch.float32)
+                dist.reduce_scatter_tensor(shard, flat, group=self.group)
+            if self.world > 1:
+                shard.div_(self.world)
+            unit.grad = shard if unit.grad is None else unit.grad.add_(shard)
+        unit.remaining = unit.trainable
+        self._release(unit)
+
+    def finish_backward(self) -> None:
+        """After ``backward()``: units whose gradients did not all arrive (unused parameters), or
+        that were gathered by a prefetch and never used, are reduced and released here."""
+        for unit in reversed(self.units):
+            if unit.full is not None or unit.remaining != unit.trainable:
+                self._reduce(unit)
+
+    def release_all(self) -> None:
+        """Release every gathered unit (after an evaluation or generation pass)."""
+        for unit in self.units:
+            if unit.full is not None:
+                self._release(unit)
+
+    # -- whole-model access ------------------------------------------------------------------------
+    @contextmanager
+    def gathered(self):
+        """All parameters readable (and writable: changes are copied back into the master shards
+        on exit)."""
+        for unit in self.units:
+            self.unshard(unit)
+        try:
+            yield
+        finally:
+            with torch.no_grad():
+                for unit in self.units:
+                    for p, off, n, shape in zip(unit.params, unit.offsets, unit.numels,
+                                                unit.shapes):
+                        if len(shape) <= 1:  # vectors are bound as copies (see _bind)
+                            unit.full[off : off + n].copy_(p.detach().reshape(-1))
+                    lo = self.rank * unit.region
+                    unit.master.copy_(unit.full[lo : lo + unit.region])
+                    self._release(unit)
+
+    def full_state_dict(self, module: nn.Module) -> dict[str, Tensor]:
+        """``module.state_dict()`` with every parameter whole (collective; clones)."""
+        with self.gathered():
+            return {k: v.detach().clone() for k, v in module.state_dict().items()}
+
+    def load_full_state_dict(self, module: nn.Module, state: dict[str, Tensor], strict: bool = True):
+        with self.gathered():
+            return module.load_state_dict(state, strict=strict)
+
+    def memory_report(self) -> dict[str, int]:
+        """Bytes of parameter storage: what a rank keeps between uses, the most it held gathered
+        at one time so far, and what an unsharded copy takes."""
+        persistent = sum(u.region for u in self.units) * 4
+        return {"persistent_bytes_per_rank": persistent,
+                "peak_gathered_bytes": self.peak_gathered_bytes,
+                "unsharded_bytes": self.unsharded_bytes}
+
+
+def shard_llama(model: nn.Module, group=None, prefetch: bool = True) -> ParameterSharding:
+    """Cut a Llama into units (embedding, blocks, final norm + output projection), shard them over
+    ``group`` and attach the result as ``model._param_sharding``; the model's forward pass then
+    gathers and releases the units as it goes."""
+    if not all(hasattr(model, name) for name in ("token_emb", "layers", "norm", "vocab_proj")):
+        raise ValueError("parameter sharding needs a Llama-style model")
+    tied = model.vocab_proj.weight is model.token_emb.weight
+    units: list[tuple[str, list[nn.Parameter]]] = []
+    keep = ["head"]
+    if tied:
+        # one unit for the shared matrix: it is used first and last, so it stays gathered
+        units.append(("embed", [model.token_emb.weight, *model.norm.parameters()]))
+        keep.append("embed")
+    else:
+        units.append(("embed", list(model.token_emb.parameters())))
+    from ohara_b200.modules.moe import MoE
+
+    for index, layer in enumerate(model.layers):
+        if any(isinstance(m, MoE) for m in layer.modules()):
+            # an expert no token of this rank chose gets no gradient, and the ranks would then
+            # disagree on when the unit's reduce-scatter runs
+            raise NotImplementedError("parameter sharding needs every parameter to receive a "
+                                      "gradient on every rank: use the grouped MoE")
+        units.append((f"layers.{index}", list(layer.parameters())))
+    if len(model.layers) > 0:
+        # the last block's backward starts right after its forward: keep it gathered
+        keep.append(f"layers.{len(model.layers) - 1}")
+    if not tied:
+        units.append(("head", [*model.norm.parameters(), *model.vocab_proj.parameters()]))
+    covered = {id(p) for _, params in units for p in params}
+    missing = [name for name, p in model.named_parameters() if id(p) not in covered]
+    if missing:
+        raise ValueError(f"parameters outside every unit: {missing[:4]}")
+    sharding = ParameterSharding(units, group, keep_gathered=keep, prefetch=prefetch)
+    sharding.tied = tied
+    model._param_sharding = sharding
+    return sharding
+
+
+class ParameterShardedOptimizer(Optimizer):
+    """Runs ``optimizer``'s algorithm on this rank's master shards of a :class:`ParameterSharding`.
+
+    ``optimizer`` was built on the model's parameters; its groups (learning rate, weight decay
+    ...) are kept as the user-visible ``param_groups`` and mirrored onto a local optimizer of the
+    same class over 1-D views of the master shards. Element-wise algorithms only."""
+
+    def __init__(self, optimizer: Optimizer, sharding: ParameterSharding) -> None:
+        self.inner = optimizer
+        self.sharding = sharding
+        self.param_groups = optimizer.param_groups
+        self.defaults = optimizer.defaults
+        self.state = optimizer.state
+        local_groups = []
+        self._spans: list[list[tuple[_Unit, int, int, nn.Parameter]]] = []
+        for group in self.param_groups:
+            if group.get("kind") == "muon" or group.get("hypersphere", False):
+                raise NotImplementedError(
+                    "parameter sharding cuts matrices at arbitrary elements: use an element-wise "
+                    "optimizer (AdamW), or the sharded optimizer without parameter sharding")
+            wanted = {id(p) for p in group["params"]}
+            spans: list[tuple[_Unit, int, int, nn.Parameter]] = []
+            for unit in sharding.units:
+                lo, hi = sharding.rank * unit.region, (sharding.rank + 1) * unit.region
+                pieces: list[list[int]] = []
+                for p, off, n in zip(unit.params, unit.offsets, unit.numels):
+                    if id(p) not in wanted:
+                        continue
+                    a, b = max(off, lo), min(off + n, hi)
+                    if a >= b:
+                        continue
+                    if pieces and pieces[-1][1] == a - lo:
+                        pieces[-1][1] = b - lo
+                    else:
+                        pieces.append([a - lo, b - lo])
+                for a, b in pieces:
+                    shard = nn.Parameter(unit.master[a:b], requires_grad=True)
+                    spans.append((unit, a, b, shard))
+            self._spans.append(spans)
+            if spans:
+                clone = {k: v for k, v in group.items() if k != "params"}
+                clone["params"] = [s[3] for s in spans]
+                local_groups.append(clone)
+        self._local_of_group = []
+        index = 0
+        for spans in self._spans:
+            self._local_of_group.append(index if spans else None)
+            index += 1 if spans else 0
+        self.local: Optimizer | None = None
+        if local_groups:
+            cls = getattr(optimizer, "optimizer_class", None) or type(optimizer)
+            try:
+                self.local = cls(local_groups)
+            except TypeError:
+                self.local = cls(local_groups, **dict(optimizer.defaults))
+
+    # -- step ------------------------------------------------------------------------------------
+    def _sync_hyperparameters(self) -> None:
+        if self.local is None:
+            return
+        for group, local_index in zip(self.param_groups, self._local_of_group):
+            if local_index is None:
+                continue
+            target = self.local.param_groups[local_index]
+            for key, value in group.items():
+                if key != "params":
+                    target[key] = value
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        self.sharding.finish_backward()
+        self._sync_hyperparameters()
+        if self.local is not None:
+            for spans in self._spans:
+                for unit, a, b, shard in spans:
+                    shard.grad = (unit.grad[a:b] if unit.grad is not None
+                                  else torch.zeros_like(shard))
+            self.local.step()
+            for spans in self._spans:
+                for _, _, _, shard in spans:
+                    shard.grad = None
+        return loss
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for unit in self.sharding.units:
+            unit.grad = None
+            for p in unit.params:
+                p.grad = None
+
+    @torch.no_grad()
+    def grad_sq_norm(self) -> Tensor:
+        self.sharding.finish_backward()
+        device = self.sharding.units[0].master.device
+        total = torch.zeros((), device=device, dtype=torch.float32)
+        for unit in self.sharding.units:
+            if unit.grad is not None:
+                total += unit.grad.square().sum()
+        if self.sharding.world > 1:
+            dist.all_reduce(total, group=self.sharding.group)
+        return total
+
+    @torch.no_grad()
+    def clip_grad_norm_(self, model, max_norm: float) -> Tensor:
+        norm = self.grad_sq_norm().sqrt()
+        scale = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+        for unit in self.sharding.units:
+            if unit.grad is not None:
+                unit.grad.mul_(scale)
+        return norm
+
+    def sync_master_weights(self) -> None:
+        """Nothing to do: the master shards are the only copy (state dicts go through
+        ``ParameterSharding.full_state_dict``)."""
+
+    # -- checkpoints -----------------------------------------------------------------------------
+    def state_dict(self) -> dict[str, Any]:
+        """Every rank's shard of the optimizer state, gathered (collective; identical on all
+        ranks, so the rank that writes the checkpoint has all of it). Reloads at the same world
+        size; the weights themselves travel in the model's full state dict."""
+        from ohara_b200.parallel.zero import _to_cpu
+
+        local = _to_cpu(self.local.state_dict()) if self.local is not None else None
+        shards: list[Any] = [local]
+        if self.sharding.world > 1:
+            shards = [None] * self.sharding.world
+            dist.all_gather_object(shards, local, group=self.sharding.group)
+        return {
+            "param_sharded": True,
+            "world": self.sharding.world,
+            "shards": shards,
+            "param_groups": [{k: v for k, v in g.items() if k != "params"}
+                             for g in self.param_groups],
+        }
+
+    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
+        if not state_dict.get("param_sharded"):
+            raise ValueError("not a parameter-sharded optimizer state")
+        if state_dict["world"] != self.sharding.world:
+            raise ValueError(f"a parameter-sharded optimizer state reloads at the world size it "
+                             f"was saved from ({state_dict['world']}), not {self.sharding.world}")
+        mine = state_dict["shards"][self.sharding.rank]
+        if self.local is not None and mine is not None:
+            self.local.load_state_dict(mine)
+        for group, saved in zip(self.param_groups, state_dict["param_groups"]):
+            group.update(saved)

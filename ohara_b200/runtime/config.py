@@ -62,3 +62,6 @@ class EngineConfig:
     # Recompute every transformer block in the backward pass instead of keeping its activations
     # (models that offer ``enable_activation_checkpointing``).
     activation_checkpointing: bool = False
+    # StrategyType.FSDP only: shard the parameters themselves per transformer block (gathered
+    # just before a block runs, released after it) instead of the optimizer state alone.
+    shard_parameters: bool = False

@@ -192,8 +192,13 @@ class OharaEngine:
             # With tensor / expert parallelism the shards differ between ranks of the optimizer's
             # group: the engine then equalises the full model before it is sharded instead.
             composed = topo.tp_enabled or topo.ep > 1 or topo.cp > 1 or topo.pp > 1
-            self._strategy = FSDPStrategy(fused=fused, init_sync=not composed)
             hybrid = topo.dp_replicate > 1 and topo.dp_shard > 1
+            if self.config.shard_parameters and (composed or hybrid):
+                raise NotImplementedError("shard_parameters composes with plain data "
+                                          "parallelism only (no tp / cp / ep / pp, no hybrid "
+                                          "sharding)")
+            self._strategy = FSDPStrategy(fused=fused, init_sync=not composed,
+                                          shard_parameters=self.config.shard_parameters)
             base_size = topo.dp_shard if hybrid else topo.dp_world_size
             norm_groups = {}
             if topo.tp_enabled:
@@ -685,6 +690,9 @@ class OharaEngine:
             self._scaler.scale(loss).backward()
         else:
             loss.backward()
+        sharding = getattr(getattr(self, "_module", None), "_param_sharding", None)
+        if sharding is not None:
+            sharding.finish_backward()  # units whose gradients did not all arrive
 
     def no_sync(self, module: torch.nn.Module, enabled: bool = True):
         return self._strategy.no_sync(module, enabled=enabled)
@@ -791,6 +799,9 @@ class OharaEngine:
         """Unsharded, wrapper-free state dict of ``module`` (collective when TP/FSDP is active):
         what the reference's ``Llama`` can load directly."""
         inner = module.module if hasattr(module, "module") else module
+        sharding = getattr(inner, "_param_sharding", None)
+        if sharding is not None:
+            return sharding.full_state_dict(inner)
         sync = getattr(getattr(self, "_sharded_optimizer", None), "sync_master_weights", None)
         if callable(sync):
             sync()
@@ -829,7 +840,10 @@ class OharaEngine:
         for key, obj in state.items():
             if key not in payload:
                 continue
-            if hasattr(obj, "load_state_dict"):
+            sharding = getattr(obj, "_param_sharding", None)
+            if sharding is not None:  # parameters sharded per block: load through the gather
+                sharding.load_full_state_dict(obj, payload[key])
+            elif hasattr(obj, "load_state_dict"):
                 obj.load_state_dict(payload[key])
             else:
                 state[key] = payload[key]

@@ -1,7 +1,9 @@
 """Sharded data parallelism: the module stays a plain ``nn.Module`` (no wrapper, no prefixed
 state-dict keys); the optimizer is wrapped by :class:`ohara_b200.parallel.zero.ShardedOptimizer`,
 which owns the gradient reduce-scatter, the sharded master weights / optimizer state and the
-parameter all-gather. See ``ohara_b200/parallel/zero.py`` for the data layout.
+parameter all-gather. See ``ohara_b200/parallel/zero.py`` for the data layout. With
+``shard_parameters=True`` the parameters themselves are sharded per transformer block
+(``ohara_b200/parallel/param_shard.py``) and the optimizer runs on the master shards.
 
 The engine tells the strategy which process groups to use (:meth:`FSDPStrategy.configure`):
 
@@ -29,9 +31,11 @@ from .base import BaseStrategy
 class FSDPStrategy(BaseStrategy):
     name = "fsdp"
 
-    def __init__(self, *, fused: bool = True, init_sync: bool = True) -> None:
+    def __init__(self, *, fused: bool = True, init_sync: bool = True,
+                 shard_parameters: bool = False) -> None:
         self.fused = fused
         self.init_sync = init_sync
+        self.shard_parameters = shard_parameters
         self.process_group = None
         self.device: torch.device | None = None
         self.replicate_group = None
@@ -60,6 +64,10 @@ class FSDPStrategy(BaseStrategy):
             src = dist.get_global_rank(process_group, 0) if process_group is not None else 0
             for tensor in list(module.parameters()) + list(module.buffers()):
                 dist.broadcast(tensor.data, src=src, group=process_group)
+        if self.shard_parameters:
+            from ohara_b200.parallel.param_shard import shard_llama
+
+            shard_llama(module, process_group)
         return module
 
     def setup_optimizer(self, optimizer, module: nn.Module | None = None):
@@ -67,6 +75,13 @@ class FSDPStrategy(BaseStrategy):
 
         if isinstance(optimizer, (ShardedOptimizer, HybridShardedOptimizer)):
             return optimizer
+        sharding = getattr(module, "_param_sharding", None)
+        if sharding is not None:
+            from ohara_b200.parallel.param_shard import ParameterShardedOptimizer
+
+            if isinstance(optimizer, ParameterShardedOptimizer):
+                return optimizer
+            return ParameterShardedOptimizer(optimizer, sharding)
         dense_norms = {k: v for k, v in self.norm_groups.items() if k in ("tp", "pp")}
         common = dict(fused=self.fused, replicate_group=self.replicate_group,
                       replicate_world=self.replicate_world)

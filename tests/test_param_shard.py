@@ -1,0 +1,237 @@
+"""Parameter sharding per transformer block: gathered just in time, released after use, gradients
+reduce-scattered per unit. Single-process cases check the bookkeeping; gloo ranks check that
+training matches a single process on the same data."""
+
+import copy
+import os
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
+import pytest
+import torch
+
+from ohara_b200 import Config, Llama
+from ohara_b200.optimizer import build_adamw, build_muon_adamw
+from ohara_b200.parallel.param_shard import ParameterShardedOptimizer, shard_llama
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _config(**extra) -> Config:
+    return Config(vocab_size=37, max_sequence_length=16, hidden_size=32, intermediate_size=40,
+                  num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=3, dropout=0.0,
+                  **extra)
+
+
+def _train(model, optimizer, tokens, steps, micro=1, finish=None):
+    losses = []
+    for _ in range(steps):
+        for part in tokens.chunk(micro):
+            loss = model(part[:, :-1], targets=part[:, 1:]) / tokens[:, 1:].numel()
+            loss.backward()
+            if finish is not None:
+                finish()
+            losses.append(float(loss.detach()))
+        optimizer.step()
+        optimizer.zero_grad()
+    return losses
+
+
+@pytest.mark.parametrize("variant", ["dense", "tied", "moe", "checkpointed", "micro"])
+def test_sharded_model_trains_like_the_plain_model(variant):
+    extra = {}
+    if variant == "tied":
+        extra["weight_tying"] = True
+    if variant == "moe":
+        extra.update(moe_num_experts=4, moe_experts_per_tok=2, moe_grouped=True,
+                     moe_num_shared_experts=1, moe_aux_loss_coef=0.01)
+    torch.manual_seed(0)
+    plain = Llama(_config(**extra))
+    sharded = copy.deepcopy(plain)
+    if variant == "checkpointed":
+        sharded.enable_activation_checkpointing()
+    tokens = torch.randint(0, 37, (4, 13))
+    micro = 2 if variant == "micro" else 1
+    plain_opt = build_adamw(plain, learning_rate=1e-2, weight_decay=0.1)
+    sharding = shard_llama(sharded)
+    sharded_opt = ParameterShardedOptimizer(
+        build_adamw(sharded, learning_rate=1e-2, weight_decay=0.1), sharding)
+    plain.train(), sharded.train()
+    want = _train(plain, plain_opt, tokens, 3, micro)
+    got = _train(sharded, sharded_opt, tokens, 3, micro, finish=sharding.finish_backward)
+    assert got == pytest.approx(want, rel=1e-5, abs=1e-6)
+    state = sharding.full_state_dict(sharded)
+    for name, value in plain.state_dict().items():
+        torch.testing.assert_close(state[name], value, rtol=1e-5, atol=1e-6, msg=name)
+
+
+def test_parameters_are_placeholders_between_uses_and_keep_their_shape():
+    torch.manual_seed(0)
+    model = Llama(_config())
+    shapes = {n: tuple(p.shape) for n, p in model.named_parameters()}
+    count = sum(p.numel() for p in model.parameters())
+    sharding = shard_llama(model)
+    for name, p in model.named_parameters():
+        assert tuple(p.shape) == shapes[name] and p.ndim == len(shapes[name])
+        assert p.untyped_storage().nbytes() == 4, name            # one element, expanded
+    assert sum(p.numel() for p in model.parameters()) == count
+    # decay / no-decay partition by dimensionality still works on the placeholders
+    optimizer = build_adamw(model, learning_rate=1e-3, weight_decay=0.1)
+    assert sum(len(g["params"]) for g in optimizer.param_groups) == len(shapes)
+    tokens = torch.randint(0, 37, (2, 9))
+    model.train()
+    loss = model(tokens[:, :-1], targets=tokens[:, 1:])
+    gathered_after_forward = [u.name for u in sharding.units if u.full is not None]
+    assert gathered_after_forward == ["layers.2", "head"]       # the last block and the head stay
+    loss.backward()
+    sharding.finish_backward()
+    assert all(u.full is None for u in sharding.units)
+    assert all(p.grad is None for p in model.parameters())        # full gradients are dropped
+    assert all(u.grad is not None and u.grad.numel() == u.region for u in sharding.units)
+    report = sharding.memory_report()
+    assert report["unsharded_bytes"] == count * 4
+    largest_two = sum(sorted(u.total for u in sharding.units)[-2:]) * 4
+    assert report["peak_gathered_bytes"] <= largest_two + max(u.total for u in sharding.units) * 4
+
+
+def test_evaluation_pass_releases_the_blocks():
+    torch.manual_seed(0)
+    model = Llama(_config())
+    reference = copy.deepcopy(model).eval()
+    sharding = shard_llama(model)
+    model.eval()
+    tokens = torch.randint(0, 37, (2, 9))
+    with torch.no_grad():
+        torch.testing.assert_close(model(tokens), reference(tokens))
+    assert [u.name for u in sharding.units if u.full is not None] == ["head"]
+    sharding.release_all()
+    assert all(u.full is None for u in sharding.units)
+
+
+def test_whole_matrix_optimizers_and_loop_moe_are_rejected():
+    torch.manual_seed(0)
+    model = Llama(_config())
+    sharding = shard_llama(model)
+    with pytest.raises(NotImplementedError):
+        ParameterShardedOptimizer(build_muon_adamw(model), sharding)
+    loop = Llama(_config(moe_num_experts=4, moe_experts_per_tok=2))
+    with pytest.raises(NotImplementedError):
+        shard_llama(loop)
+
+
+def test_state_dict_round_trip_and_clipping():
+    torch.manual_seed(0)
+    model = Llama(_config())
+    plain = copy.deepcopy(model)
+    sharding = shard_llama(model)
+    optimizer = ParameterShardedOptimizer(build_adamw(model, learning_rate=1e-2, weight_decay=0.0), sharding)
+    plain_opt = build_adamw(plain, learning_rate=1e-2, weight_decay=0.0)
+    tokens = torch.randint(0, 37, (2, 9))
+    model.train(), plain.train()
+    for m in (model, plain):
+        m(tokens[:, :-1], targets=tokens[:, 1:]).backward()
+    norm = optimizer.clip_grad_norm_(model, 0.5)
+    want = torch.nn.utils.clip_grad_norm_(plain.parameters(), 0.5)
+    torch.testing.assert_close(norm, want, rtol=1e-5, atol=1e-6)
+    optimizer.step(), plain_opt.step()
+    saved = copy.deepcopy(optimizer.state_dict())
+    full = sharding.full_state_dict(model)
+    for name, value in plain.state_dict().items():
+        torch.testing.assert_close(full[name], value, rtol=1e-5, atol=1e-6, msg=name)
+    # a fresh sharded model restored from the full weights and the optimizer shard continues alike
+    again = Llama(_config())
+    again_sharding = shard_llama(again)
+    again_sharding.load_full_state_dict(again, full)
+    again_opt = ParameterShardedOptimizer(build_adamw(again, learning_rate=1e-2, weight_decay=0.0), again_sharding)
+    again_opt.load_state_dict(saved)
+    again.train()
+    for m, o in ((model, optimizer), (again, again_opt)):
+        o.zero_grad()
+        m(tokens[:, :-1], targets=tokens[:, 1:]).backward()
+        o.step()
+    a, b = sharding.full_state_dict(model), again_sharding.full_state_dict(again)
+    for name in a:
+        torch.testing.assert_close(a[name], b[name], rtol=1e-6, atol=1e-7, msg=name)
+
+
+WORKER = """
+import torch, torch.distributed as dist
+from torch.utils.data import DataLoader, TensorDataset
+from ohara_b200.models.llama import Config, Llama
+from ohara_b200.runtime import EngineConfig, OharaEngine, StrategyType
+from ohara_b200.optimizer import build_adamw
+from ohara_b200.trainer import Trainer
+from ohara_b200.lr_scheduler import Scheduler
+
+torch.manual_seed(0)
+cfg = Config(vocab_size=31, max_sequence_length=8, hidden_size=16, intermediate_size=24,
+             num_attention_heads=2, num_hidden_layers=3, dropout=0.0)
+ids = torch.randint(0, 31, (8, 9))
+dataset = TensorDataset(ids[:, :-1], ids[:, 1:])
+state = {k: v.clone() for k, v in Llama(cfg).state_dict().items()}
+
+solo = Llama(cfg); solo.load_state_dict(state)
+ref_opt = build_adamw(solo, learning_rate=0.02, weight_decay=0.1)
+ref_norms = []
+for _ in range(4):
+    loss = solo.loss_sum(ids[:, :-1], ids[:, 1:]) / ids[:, 1:].numel()
+    loss.backward()
+    ref_norms.append(float(torch.nn.utils.clip_grad_norm_(solo.parameters(), 0.5)))
+    ref_opt.step(); ref_opt.zero_grad()
+
+engine = OharaEngine(EngineConfig(strategy=StrategyType.FSDP, shard_parameters=True,
+                                  activation_checkpointing=CHECKPOINT))
+model = Llama(cfg); model.load_state_dict(state)
+model = engine.prepare(model)
+(opt,) = engine.prepare_optimizers(build_adamw(model, learning_rate=0.02, weight_decay=0.1))
+assert type(opt).__name__ == "ParameterShardedOptimizer"
+world = dist.get_world_size()
+report = model._param_sharding.memory_report()
+assert report["persistent_bytes_per_rank"] * world < report["unsharded_bytes"] * 1.25 + 4096 * world
+loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=8 // world // MICRO))
+trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=MICRO,
+                  max_iters=4, eval_iters=0, save_ckpt_iters=0, grad_clip_norm=0.5)
+norms = []
+clip = opt.clip_grad_norm_
+opt.clip_grad_norm_ = lambda m, n: (norms.append(float(clip(m, n))), norms[-1])[1] and torch.tensor(norms[-1])
+trainer.train()
+assert all(abs(a - b) < 1e-4 * max(1.0, abs(b)) for a, b in zip(norms, ref_norms)), (norms, ref_norms)
+full = engine.full_state_dict(model)
+for name, value in solo.state_dict().items():
+    assert torch.allclose(full[name], value, atol=3e-5), (name, (full[name] - value).abs().max())
+assert all(u.full is None for u in model._param_sharding.units)
+
+# checkpoint written by rank 0, restored into a fresh sharded model + optimizer on every rank
+import os, tempfile
+folder = engine.broadcast(tempfile.mkdtemp() if dist.get_rank() == 0 else None)
+path = os.path.join(folder, "ckpt.pt")
+engine.save(path, trainer.checkpoint_state(4, 0.02, 0.0))
+fresh = engine.prepare(Llama(cfg))
+(fresh_opt,) = engine.prepare_optimizers(build_adamw(fresh, learning_rate=0.02, weight_decay=0.1))
+engine.load(path, {"model": fresh, "optimizer": fresh_opt})
+restored = engine.full_state_dict(fresh)
+for name, value in full.items():
+    assert torch.equal(restored[name], value), name
+a, b = opt.local.state_dict()["state"], fresh_opt.local.state_dict()["state"]
+assert a.keys() == b.keys() and len(a) > 0
+for key in a:
+    assert torch.equal(a[key]["exp_avg"], b[key]["exp_avg"])
+if dist.get_rank() == 0:
+    print("PARAM_SHARD_OK", report)
+engine.close()
+"""
+
+
+@pytest.mark.parametrize("world,micro,checkpoint", [(2, 1, False), (4, 2, False), (2, 1, True)])
+def test_gloo_ranks_match_single_process_training(tmp_path, world, micro, checkpoint):
+    path = tmp_path / "worker.py"
+    path.write_text(textwrap.dedent(WORKER).replace("MICRO", str(micro))
+                    .replace("CHECKPOINT", str(checkpoint)))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29800 + os.getpid() % 150), str(path)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "PARAM_SHARD_OK" in proc.stdout
