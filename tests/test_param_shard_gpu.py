@@ -47,7 +47,7 @@ def test_sharded_model_on_one_gpu_follows_the_plain_model(checkpoint):
     sharded_opt = ParameterShardedOptimizer(
         build_adamw(sharded, learning_rate=3e-3, weight_decay=0.1), sharding)
     plain.train(), sharded.train()
-    batches = [torch.randint(0, 512, (4, 193), device="cuda") for _ in range(4)]
+    batches = [torch.randint(0, 512, (4, 193), device="cuda")] * 5   # one batch, seen five times
     want = _losses(plain, plain_opt, batches)
     got = _losses(sharded, sharded_opt, batches, finish=sharding.finish_backward)
     torch.cuda.synchronize()
@@ -55,7 +55,7 @@ def test_sharded_model_on_one_gpu_follows_the_plain_model(checkpoint):
     # same kernels on the same values: the curves agree to the order of the bf16 rounding of
     # the refreshed weights (a stale compute copy would leave the loss where it started)
     assert got == pytest.approx(want, rel=2e-3)
-    assert got[-1] < got[0]
+    assert got[-1] < got[0] - 0.05
     assert all(u.full is None for u in sharding.units)
     full = sharding.full_state_dict(sharded)
     for name, value in plain.state_dict().items():
