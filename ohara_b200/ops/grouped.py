@@ -11,8 +11,11 @@ from __future__ import annotations
 import torch
 from torch import Tensor
 
+from ohara_b200.utils.checks import debug_checks_enabled, validate_dispatch_plan
+
 from ._ext import ext
 
+_DEBUG_CHECKS = debug_checks_enabled()
 TILE = 256  # rows every expert segment is padded to: one CTA-pair tile of the grouped GEMM
 
 
@@ -114,6 +117,8 @@ def grouped_swiglu_experts(flat_x: Tensor, expert_indices: Tensor, expert_weight
     if counts is None:
         counts = torch.bincount(indices.reshape(-1), minlength=num_experts).int()
     dest_row, row_pair, tile_expert, k_offsets = moe.dispatch_plan(indices, counts)
+    if _DEBUG_CHECKS:  # OHARA_DEBUG_CHECKS=1: read the tables back and verify them (synchronises)
+        validate_dispatch_plan(indices, dest_row, row_pair, tile_expert, k_offsets, TILE)
     x_pad = moe.permute_rows(x16, dest_row, row_pair, k)
     gate = grouped_linear(x_pad, w_gate, tile_expert, k_offsets)
     up = grouped_linear(x_pad, w_up, tile_expert, k_offsets)

@@ -33,7 +33,10 @@ from ohara_b200.ops._ext import ext
 from ohara_b200.parallel.peer import PeerRuntime, SymmetricBuffer
 
 from ohara_b200.ops.moe import TILE  # rows every expert segment is padded to (a GEMM pair tile)
+from ohara_b200.utils.checks import debug_checks_enabled, validate_expert_parallel_plan
 from ohara_b200.utils.profiling import nvtx_annotate
+
+_DEBUG_CHECKS = debug_checks_enabled()
 
 
 @dataclass
@@ -88,7 +91,13 @@ class EPWorkspace:
         table = self.tables.typed(torch.int32)
         parts = ext().ep_plan(table, indices.contiguous(), self.rank, self.world, TILE,
                               self.capacity_rows)
-        return DispatchPlan(*parts, top_k=indices.shape[1])
+        plan = DispatchPlan(*parts, top_k=indices.shape[1])
+        if _DEBUG_CHECKS:  # OHARA_DEBUG_CHECKS=1: verify the tables on the host (synchronises)
+            validate_expert_parallel_plan(
+                indices, plan.dest_rank, plan.dest_row, plan.tile_expert, plan.k_offsets,
+                world=self.world, num_experts=self.num_experts,
+                capacity_rows=self.capacity_rows, tile=TILE)
+        return plan
 
     # -- per-layer buffers -----------------------------------------------------------------------------
     def _slot(self, table: dict[int, SymmetricBuffer], slot: int) -> SymmetricBuffer:

@@ -96,6 +96,11 @@ def test_expert_parallel_plan_dispatch_and_combine(C):
     assert torch.equal(tables[0], tables[1])  # every rank ends up with the same table
     plans = [C.ep_plan(tables[rank], indices[rank].contiguous(), rank, world, TILE, capacity)
              for rank in range(world)]
+    from ohara_b200.utils.checks import validate_expert_parallel_plan
+
+    for rank in range(world):  # the host-side validator agrees with what the kernels built
+        validate_expert_parallel_plan(indices[rank], *plans[rank][:4], world=world,
+                                      num_experts=experts, capacity_rows=capacity, tile=TILE)
     landing = [torch.full((capacity, d), float("nan"), device="cuda").bfloat16() for _ in range(world)]
     for rank in range(world):
         dest_rank, dest_row = plans[rank][0], plans[rank][1]
@@ -170,3 +175,25 @@ def test_out_of_range_destination_is_reported_and_skipped(C):
     with pytest.raises(RuntimeError, match="bad kernel argument"):
         ops.check_status()
     assert out.float().sum(1).tolist() == [d, 0.0, 0.0, d]
+
+
+@pytest.mark.parametrize("tokens,experts,k", [(700, 6, 2), (1, 5, 2), (4096, 64, 8)])
+def test_dispatch_plan_tables_satisfy_the_host_side_validator(C, tokens, experts, k):
+    """The tables of the single-GPU routing plan (and of a plan whose small capacity drops pairs
+    under expert parallelism) pass the checks that ``OHARA_DEBUG_CHECKS=1`` switches on."""
+    from ohara_b200.ops.moe import TILE, dispatch_plan
+    from ohara_b200.utils.checks import validate_dispatch_plan, validate_expert_parallel_plan
+
+    torch.manual_seed(3)
+    indices = torch.stack([torch.randperm(experts, device="cuda")[:k] for _ in range(tokens)]).int()
+    counts = torch.bincount(indices.reshape(-1).long(), minlength=experts).int()
+    validate_dispatch_plan(indices, *dispatch_plan(indices, counts), TILE)
+    if experts % 2 == 0:
+        world, capacity = 2, 2 * TILE   # far too small for 4096 x 8 pairs: most are dropped
+        tables = [torch.zeros(world * experts, dtype=torch.int32, device="cuda") for _ in range(world)]
+        for rank in range(world):
+            C.ep_publish_counts([t.data_ptr() for t in tables], counts, rank)
+        for rank in range(world):
+            plan = C.ep_plan(tables[rank], indices.contiguous(), rank, world, TILE, capacity)
+            validate_expert_parallel_plan(indices, *plan[:4], world=world, num_experts=experts,
+                                          capacity_rows=capacity, tile=TILE)
