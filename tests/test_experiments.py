@@ -130,3 +130,188 @@ def test_small_modules():
     assert torch.allclose(proj.project_back(low), grad, atol=1e-4)
     tall = GaLoreProjector(rank=3)
     assert tall.project(grad.t().contiguous(), 0).shape == (20, 3)
+
+
+# --------------------------------------------------------------------------------------------------
+# Recurrent models, attention variants, feed-forward variants, data, optimizers
+# --------------------------------------------------------------------------------------------------
+def test_griffin_hawk_and_mqa_models_train_and_the_recurrence_steps_like_the_scan():
+    import pytest
+    from experiments.griffin_and_hawk.model import (HawkAndGriffin, HawkState, HnGConfig, hawk_step,
+                                                    state_floats_per_sequence)
+    from ohara_b200.modules.linear_rnn import Hawk
+
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 50, (2, 16))
+    for kind in ("mqa", "hawk", "griffin"):
+        cfg = HnGConfig(model_type=kind, vocab_size=50, seq_len=32, dim=32, num_heads=4,
+                        num_kv_heads=1, num_layers=2, sliding_window_attention=kind == "griffin",
+                        window_size=4)
+        model = HawkAndGriffin(cfg)
+        logits = model(tokens)
+        assert logits.shape == (2, 16, 50)
+        changed = tokens.clone()
+        changed[:, 10:] = (changed[:, 10:] + 1) % 50
+        assert torch.allclose(model(changed)[:, :10], logits[:, :10], atol=1e-5)  # causal
+        torch.nn.functional.cross_entropy(logits.flatten(0, 1), tokens.flatten()).backward()
+        assert all(p.grad is not None for p in model.parameters())
+        sizes = state_floats_per_sequence(cfg, 4096)
+        assert (sizes["recurrent_state"] > 0) == (kind != "mqa")
+        assert (sizes["kv_cache"] > 0) == (kind != "hawk")
+    with pytest.raises(ValueError):
+        HawkAndGriffin(HnGConfig(model_type="owl", vocab_size=8, dim=16, num_heads=2, num_layers=1))
+    # a window of 4 hides position 0 from position 8
+    local = HawkAndGriffin(HnGConfig(model_type="mqa", vocab_size=50, seq_len=32, dim=32,
+                                     num_heads=4, num_layers=1, sliding_window_attention=True,
+                                     window_size=4)).eval()
+    far = tokens.clone()
+    far[:, 0] = (far[:, 0] + 1) % 50
+    assert torch.allclose(local(far)[:, 8:], local(tokens)[:, 8:], atol=1e-5)
+    mixer = Hawk(dim=16, expansion_factor=1.5, kernel_size=4)
+    x = torch.randn(2, 9, 16)
+    state, outs = HawkState.zeros(mixer, 2), []
+    for t in range(9):
+        out, state = hawk_step(mixer, x[:, t], state)
+        outs.append(out)
+    assert torch.allclose(torch.stack(outs, 1), mixer(x), atol=1e-5)
+
+
+def test_partial_kv_attention_variants_are_causal_and_cache_less():
+    from experiments.partial_kv.pkv import ATTENTION, PartialKVAttention, cache_floats_per_token
+    from ohara_b200.embeddings_pos.rotary import precompute_freqs_cis
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 10, 32)
+    later = x.clone()
+    later[:, 6:] += 1.0
+    for kind, cls in ATTENTION.items():
+        layer = cls(32, 4).eval()
+        cos, sin = precompute_freqs_cis(4 if kind == "partial_kv" else 8, 32)
+        freqs = (cos[:10], sin[:10])
+        out = layer(x, freqs)
+        assert out.shape == x.shape
+        assert torch.allclose(layer(later, freqs)[:, :6], out[:, :6], atol=1e-5)
+    sizes = {kind: cache_floats_per_token(kind, 32, 2) for kind in ATTENTION}
+    assert sizes == {"attention": 128, "kattention": 64, "partial_kv": 96}
+    layer = PartialKVAttention(32, 4)
+    cos, sin = precompute_freqs_cis(4, 32)
+    key, shared, value = layer.cached(x, (cos[:10], sin[:10]))
+    assert key.shape == shared.shape == value.shape == (2, 10, 4, 4)
+
+
+def test_xglu_springnet_deglu_and_the_state_shift_loss():
+    from experiments.deglu.deglu import DeGLU
+    from experiments.mihawk.state_shift import state_prediction_loss, states_shift
+    from experiments.springnet.springnet import SpringMLP
+    from experiments.xglu.xglu import XGLU
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 6, 32)
+    layer = XGLU(32, xglu_rank=8)
+    assert layer(x).shape == x.shape and layer.parameter_saving() > 0
+    layer(x).sum().backward()
+    assert layer.compress.weight.grad.abs().sum() > 0
+    spring = SpringMLP(32, 48, spring_steps=5)
+    out, step = spring(x)
+    assert out.shape == x.shape and step.shape == (2, 6, 1)
+    sizes = spring.step_sizes(x)
+    assert bool((sizes[1:] <= sizes[:-1]).all()) and float(sizes.max()) < 1.0   # a damped motion
+    (out.square().mean() + step.mean()).backward()
+    assert spring.decay[0].weight.grad is not None
+    deglu = DeGLU(32, 64, mask_blocks=4)
+    hidden = torch.randn(5, 64)
+    mask = deglu.get_mask(hidden)
+    assert set(mask.unique().tolist()) <= {0.0, 1.0} and float(mask.sum()) % 16 == 0
+    assert float(mask.sum()) >= 16 and deglu(x).shape == x.shape
+    states = torch.arange(10.0).view(1, 10, 1)
+    assert states_shift(states, 2)[0, :, 0].tolist() == [2, 3, 4, 5, 6, 7, 8, 9, 0, 0]
+    assert states_shift(states, 0) is states
+    # every state is 2 below its successor two steps on; 8 of 10 positions count
+    assert abs(float(state_prediction_loss(states, 2)) - 4.0 * 8 / 10) < 1e-6
+
+
+def test_game_of_life_rule_dataset_and_token_layout():
+    from experiments.lifelm.life import (SEP, LifeDataset, boards_to_tokens, next_state,
+                                         next_state_loops)
+
+    torch.manual_seed(0)
+    boards = (torch.rand(3, 7, 9) < 0.4).long()
+    stepped = next_state(boards)
+    for b in range(3):
+        assert torch.equal(stepped[b], next_state_loops(boards[b]))
+    blinker = torch.zeros(5, 5, dtype=torch.long)
+    blinker[2, 1:4] = 1
+    assert torch.equal(next_state(next_state(blinker)), blinker)
+    assert not torch.equal(next_state(blinker), blinker)
+    pairs = list(LifeDataset(size=6, samples=40, seed=1))
+    assert len(pairs) == 40
+    assert all(torch.equal(next_state(a), b) for a, b in pairs)
+    tokens, mask = boards_to_tokens(*pairs[0])
+    assert tokens.shape == (73,) and int(tokens[36]) == SEP and int(mask.sum()) == 36
+    assert not bool(mask[:37].any())
+
+
+def test_dense_mlp_decomposes_into_experts_that_sum_to_it():
+    from experiments.mlp_decomp_to_moe.make_moe import (balanced_kmeans, decompose_gated_mlp,
+                                                        split_weights_into_experts)
+    from ohara_b200.modules.mlp import SwiGLU
+
+    torch.manual_seed(0)
+    points = torch.cat([torch.randn(40, 8) + 6 * torch.eye(8)[i] for i in range(4)])
+    labels = balanced_kmeans(points, 4)
+    assert torch.bincount(labels).tolist() == [40] * 4
+    # well separated blobs are recovered
+    assert all(len(set(labels[i * 40:(i + 1) * 40].tolist())) == 1 for i in range(4))
+    parts = split_weights_into_experts(torch.randn(64, 16), 8)
+    assert [p.shape for p in parts] == [(8, 16)] * 8
+    mlp = SwiGLU(16, 64)
+    x = torch.randn(3, 5, 16)
+    everything = decompose_gated_mlp(mlp, num_experts=8, top_k=8)
+    assert torch.allclose(everything(x), mlp(x), atol=1e-5)
+    some = decompose_gated_mlp(mlp, num_experts=8, top_k=2)
+    assert some(x).shape == x.shape and not torch.allclose(some(x), mlp(x), atol=1e-5)
+
+
+def test_galore_adamw_keeps_low_rank_moments_and_trains():
+    from experiments.galore.galore import GaLoreAdamW, galore_param_groups
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(24, 32), nn.Tanh(), nn.Linear(32, 24))
+    optimizer = GaLoreAdamW(galore_param_groups(model, rank=4, update_proj_gap=5), lr=3e-2)
+    x = torch.randn(64, 24)
+    losses = []
+    for _ in range(30):
+        loss = (model(x) - x).square().mean()
+        optimizer.zero_grad()
+        loss.backward()
+        optimizer.step()
+        losses.append(float(loss.detach()))
+    assert losses[-1] < 0.7 * losses[0]
+    assert optimizer.state[model[0].weight]["exp_avg"].shape == (32, 4)   # out >= in: (out, rank)
+    assert optimizer.state[model[2].weight]["exp_avg"].shape == (4, 32)   # out < in: (rank, in)
+    full = 2 * sum(p.numel() for p in model.parameters())
+    assert optimizer.state_numbers() < 0.5 * full
+
+
+def test_monkey_patcher_swaps_linears_and_keeps_the_function():
+    from experiments.template.monkey_patcher import DMLinear, patch_linears
+
+    torch.manual_seed(0)
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.up, self.down = nn.Linear(8, 16), nn.Linear(16, 8, bias=False)
+            self.inner = nn.Sequential(nn.Linear(8, 8))
+
+        def forward(self, x):
+            return self.inner(self.down(torch.relu(self.up(x))))
+
+    net, x = Net(), torch.randn(4, 8)
+    before = net(x)
+    assert patch_linears(net, {"up", "down"}) == ["up", "down"]
+    assert isinstance(net.up, DMLinear) and isinstance(net.inner[0], nn.Linear)
+    assert not isinstance(net.inner[0], DMLinear)
+    assert torch.allclose(net(x), before, atol=1e-5)
+    assert patch_linears(net) == ["inner.0"]
+    assert torch.allclose(net(x), before, atol=1e-5)
