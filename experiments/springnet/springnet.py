@@ -16,6 +16,8 @@ from ohara_b200.modules.mlp import MLP
 
 
 class SpringMLP(nn.Module):
+    includes_residual = True  # the output is the input moved, not an update to add to it
+
     def __init__(self, d_model: int, hidden_dim: int, spring_steps: int = 10,
                  dropout: float = 0.0, bias: bool = False) -> None:
         super().__init__()

@@ -1,0 +1,115 @@
+"""The template language model of the experiments: a pre-norm decoder whose attention and
+feed-forward layers are pluggable (reference: experiments/template/model.py:20-272 and the copies
+of it that every experiment folder carries with one layer swapped).
+
+``TemplateLM(cfg, attention=..., feed_forward=...)`` takes factories ``(cfg) -> nn.Module``; the
+attention module is called as ``attention(x, freqs)``, the feed-forward as ``ff(x)`` and may return
+``(output, auxiliary_loss)``, in which case the auxiliary terms are averaged into
+``model.auxiliary_loss`` (SpringMLP does that). ``VARIANTS`` names the combinations the experiment
+folders study; ``build(variant, cfg)`` makes one."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable
+
+import torch
+import torch.nn as nn
+from torch import Tensor
+
+from ohara_b200.embeddings_pos.rotary import precompute_freqs_cis
+from ohara_b200.modules.mlp import MLP_MAP
+from ohara_b200.modules.norm import RMSNorm
+
+
+@dataclass
+class TemplateConfig:
+    vocab_size: int = 256
+    seq_len: int = 256
+    d_model: int = 128
+    hidden_dim: int = 344
+    num_heads: int = 4
+    num_layers: int = 4
+    dropout: float = 0.0
+    bias: bool = False
+    weight_tying: bool = False
+    mlp: str = "swiglu"
+    rope_dim: int | None = None   # rotary width; default head_dim
+
+
+class _Block(nn.Module):
+    def __init__(self, cfg: TemplateConfig, attention: Callable, feed_forward: Callable) -> None:
+        super().__init__()
+        self.attn, self.ff = attention(cfg), feed_forward(cfg)
+        self.norm1, self.norm2 = RMSNorm(cfg.d_model), RMSNorm(cfg.d_model)
+
+    def forward(self, x: Tensor, freqs) -> tuple[Tensor, Tensor | None]:
+        x = x + self.attn(self.norm1(x), freqs)
+        out = self.ff(self.norm2(x))
+        out, aux = out if isinstance(out, tuple) else (out, None)
+        # a layer that iterates on its input (SpringMLP) returns the updated state itself
+        return (out if getattr(self.ff, "includes_residual", False) else x + out), aux
+
+
+class TemplateLM(nn.Module):
+    def __init__(self, cfg: TemplateConfig, attention: Callable | None = None,
+                 feed_forward: Callable | None = None) -> None:
+        super().__init__()
+        from experiments.partial_kv.pkv import FullAttention
+
+        attention = attention or (lambda c: FullAttention(c.d_model, c.num_heads, c.dropout, c.bias))
+        feed_forward = feed_forward or (lambda c: MLP_MAP[c.mlp](c.d_model, c.hidden_dim))
+        self.config = cfg
+        self.token_emb = nn.Embedding(cfg.vocab_size, cfg.d_model)
+        self.layers = nn.ModuleList(_Block(cfg, attention, feed_forward) for _ in range(cfg.num_layers))
+        self.norm = RMSNorm(cfg.d_model)
+        self.vocab_proj = nn.Linear(cfg.d_model, cfg.vocab_size, bias=False)
+        if cfg.weight_tying:
+            self.token_emb.weight = self.vocab_proj.weight
+        cos, sin = precompute_freqs_cis(cfg.rope_dim or cfg.d_model // cfg.num_heads, cfg.seq_len)
+        self.register_buffer("freq_cos", cos, persistent=False)
+        self.register_buffer("freq_sin", sin, persistent=False)
+        self.auxiliary_loss: Tensor | None = None
+
+    def forward(self, tokens: Tensor) -> Tensor:
+        steps = tokens.shape[1]
+        freqs = (self.freq_cos[:steps], self.freq_sin[:steps])
+        x = self.token_emb(tokens)
+        extras = []
+        for layer in self.layers:
+            x, aux = layer(x, freqs)
+            if aux is not None:
+                extras.append(aux.mean())
+        self.auxiliary_loss = torch.stack(extras).mean() if extras else None
+        return self.vocab_proj(self.norm(x))
+
+
+def _variants() -> dict[str, Callable[[TemplateConfig], TemplateLM]]:
+    from experiments.deglu.deglu import DeGLU
+    from experiments.partial_kv.pkv import KeyValueTiedAttention, PartialKVAttention
+    from experiments.springnet.springnet import SpringMLP
+    from experiments.xglu.xglu import XGLU
+
+    def with_rope(cfg: TemplateConfig, width: int) -> TemplateConfig:
+        return TemplateConfig(**{**cfg.__dict__, "rope_dim": width})
+
+    return {
+        "baseline": lambda c: TemplateLM(c),
+        "kattention": lambda c: TemplateLM(
+            c, attention=lambda k: KeyValueTiedAttention(k.d_model, k.num_heads, k.dropout, k.bias)),
+        "partial_kv": lambda c: TemplateLM(
+            with_rope(c, c.d_model // c.num_heads // 2),
+            attention=lambda k: PartialKVAttention(k.d_model, k.num_heads, k.dropout, k.bias)),
+        "xglu": lambda c: TemplateLM(
+            c, feed_forward=lambda k: XGLU(k.d_model, k.hidden_dim, xglu_rank=max(8, k.d_model // 8))),
+        "deglu": lambda c: TemplateLM(c, feed_forward=lambda k: DeGLU(k.d_model, k.hidden_dim - k.hidden_dim % 4)),
+        "springnet": lambda c: TemplateLM(
+            c, feed_forward=lambda k: SpringMLP(k.d_model, k.hidden_dim, spring_steps=4)),
+    }
+
+
+VARIANTS = tuple(_variants())
+
+
+def build(variant: str, cfg: TemplateConfig) -> TemplateLM:
+    return _variants()[variant](cfg)

@@ -315,3 +315,59 @@ def test_monkey_patcher_swaps_linears_and_keeps_the_function():
     assert torch.allclose(net(x), before, atol=1e-5)
     assert patch_linears(net) == ["inner.0"]
     assert torch.allclose(net(x), before, atol=1e-5)
+
+
+def test_bitlora_starts_as_the_base_layer_trains_only_adapters_and_merges():
+    from experiments.bitnet.bitlora import BitLora, apply_bitlora
+
+    torch.manual_seed(0)
+    net = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 6))
+    x = torch.randn(5, 8)
+    base = apply_bitlinear(nn.Sequential(*[m if not isinstance(m, nn.Linear) else
+                                            _clone_linear(m) for m in net]))(x)
+    apply_bitlora(net, rank=2, lora_alpha=4.0)
+    assert all(isinstance(m, BitLora) for m in net if isinstance(m, nn.Linear))
+    assert torch.allclose(net(x), base, atol=1e-6)             # B = 0: nothing changes yet
+    trainable = {n for n, p in net.named_parameters() if p.requires_grad}
+    assert trainable == {"0.lora_A", "0.lora_B", "2.lora_A", "2.lora_B"}
+    net(x).square().mean().backward()
+    assert net[0].lora_B.grad.abs().sum() > 0 and net[0].weight.grad is None
+    with torch.no_grad():
+        net[0].lora_B.normal_()
+    adapted = net(x)
+    net[0].merge()
+    assert net[0].merged and torch.allclose(net(x), adapted, atol=1e-5)
+
+
+def _clone_linear(linear: nn.Linear) -> nn.Linear:
+    copy = nn.Linear(linear.in_features, linear.out_features, linear.bias is not None)
+    copy.load_state_dict(linear.state_dict())
+    return copy
+
+
+def test_connection_types_of_the_mhc_model_and_template_variants_run_and_learn():
+    from experiments.mhc.model import MHCConfig, MHCModel
+    from experiments.template.model import VARIANTS, TemplateConfig, build
+    from experiments.train_experiment import main
+
+    torch.manual_seed(0)
+    tokens = torch.randint(0, 40, (2, 12))
+    for kind in ("residual", "hc", "mhc"):
+        model = MHCModel(MHCConfig(vocab_size=40, max_sequence_length=32, hidden_size=32,
+                                   intermediate_size=48, num_attention_heads=4,
+                                   num_hidden_layers=2, expansion_rate=3, connection_type=kind))
+        logits = model(tokens)
+        logits.sum().backward()
+        assert logits.shape == (2, 12, 40)
+        assert all(p.grad is not None for p in model.parameters())
+    cfg = TemplateConfig(vocab_size=40, seq_len=32, d_model=32, hidden_dim=48, num_heads=4,
+                         num_layers=2)
+    assert set(VARIANTS) == {"baseline", "kattention", "partial_kv", "xglu", "deglu", "springnet"}
+    for variant in VARIANTS:
+        model = build(variant, cfg)
+        assert model(tokens).shape == (2, 12, 40)
+        assert (model.auxiliary_loss is not None) == (variant == "springnet")
+    for name in ("griffin", "life"):
+        result = main(["--model", name, "--steps", "30", "--batch", "8", "--seq-len", "48",
+                       "--dim", "32", "--layers", "2", "--log-every", "0", "--device", "cpu"])
+        assert result["last_loss"] < 0.9 * result["first_loss"], result
