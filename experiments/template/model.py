@@ -90,6 +90,44 @@ def _variants() -> dict[str, Callable[[TemplateConfig], TemplateLM]]:
     from experiments.springnet.springnet import SpringMLP
     from experiments.xglu.xglu import XGLU
 
+    from experiments.misc.small_modules import Pattention, XLinear, relu_squared
+    from experiments.mixture_of_depth.mod import MixtureOfDepth
+    from experiments.template.monkey_patcher import patch_linears
+
+    class ReLUSquaredMLP(nn.Module):
+        def __init__(self, dim: int, hidden: int) -> None:
+            super().__init__()
+            self.up, self.down = nn.Linear(dim, hidden, bias=False), nn.Linear(hidden, dim, bias=False)
+
+        def forward(self, x: Tensor) -> Tensor:
+            return self.down(relu_squared(self.up(x)))
+
+    class DepthRoutedMLP(nn.Module):
+        """Half of the tokens of a sequence go through the MLP, chosen by a router; in training
+        the auxiliary router that decoding relies on is fitted alongside."""
+
+        includes_residual = True
+
+        def __init__(self, dim: int, hidden: int) -> None:
+            super().__init__()
+            self.routed = MixtureOfDepth(MLP_MAP["swiglu"](dim, hidden), dim, capacity_factor=0.5)
+
+        def forward(self, x: Tensor):
+            out, aux = self.routed(x, auxiliary_loss=self.training)
+            return out if aux is None else (out, aux)
+
+    def hypersphere(cfg: TemplateConfig) -> TemplateLM:
+        model = TemplateLM(cfg)
+
+        def to_xlinear(linear: nn.Linear) -> XLinear:
+            new = XLinear(linear.in_features, linear.out_features, linear.bias is not None)
+            new.load_state_dict(linear.state_dict())
+            return new
+
+        for layer in model.layers:  # the blocks' projections; embedding and head stay plain
+            patch_linears(layer, build=to_xlinear)
+        return model
+
     def with_rope(cfg: TemplateConfig, width: int) -> TemplateConfig:
         return TemplateConfig(**{**cfg.__dict__, "rope_dim": width})
 
@@ -105,6 +143,12 @@ def _variants() -> dict[str, Callable[[TemplateConfig], TemplateLM]]:
         "deglu": lambda c: TemplateLM(c, feed_forward=lambda k: DeGLU(k.d_model, k.hidden_dim - k.hidden_dim % 4)),
         "springnet": lambda c: TemplateLM(
             c, feed_forward=lambda k: SpringMLP(k.d_model, k.hidden_dim, spring_steps=4)),
+        "tokenformer": lambda c: TemplateLM(
+            c, feed_forward=lambda k: Pattention(k.d_model, k.d_model, num_tokens=k.hidden_dim)),
+        "relu2": lambda c: TemplateLM(c, feed_forward=lambda k: ReLUSquaredMLP(k.d_model, k.hidden_dim)),
+        "mixture_of_depth": lambda c: TemplateLM(
+            c, feed_forward=lambda k: DepthRoutedMLP(k.d_model, k.hidden_dim)),
+        "hypersphere": hypersphere,
     }
 
 

@@ -10,8 +10,9 @@ repeating structure, so that the loss has something to learn), AdamW with warm-u
 bf16 autocast on CUDA. Prints the loss every ``--log-every`` steps and a final JSON line with the
 first and last smoothed loss, parameters and tokens per second. Models: ``mqa`` / ``hawk`` /
 ``griffin``; ``residual`` / ``hc`` / ``mhc``; the template variants ``baseline`` / ``kattention`` /
-``partial_kv`` / ``xglu`` / ``deglu`` / ``springnet``; ``life`` trains the template baseline on
-Game of Life transitions with the loss on the next board only."""
+``partial_kv`` / ``xglu`` / ``deglu`` / ``springnet`` / ``tokenformer`` / ``relu2`` /
+``mixture_of_depth`` / ``hypersphere``; ``life`` trains the template baseline on Game of Life
+transitions with the loss on the next board only."""
 
 from __future__ import annotations
 

@@ -362,11 +362,16 @@ def test_connection_types_of_the_mhc_model_and_template_variants_run_and_learn()
         assert all(p.grad is not None for p in model.parameters())
     cfg = TemplateConfig(vocab_size=40, seq_len=32, d_model=32, hidden_dim=48, num_heads=4,
                          num_layers=2)
-    assert set(VARIANTS) == {"baseline", "kattention", "partial_kv", "xglu", "deglu", "springnet"}
+    assert set(VARIANTS) == {"baseline", "kattention", "partial_kv", "xglu", "deglu", "springnet",
+                             "tokenformer", "relu2", "mixture_of_depth", "hypersphere"}
     for variant in VARIANTS:
         model = build(variant, cfg)
-        assert model(tokens).shape == (2, 12, 40)
-        assert (model.auxiliary_loss is not None) == (variant == "springnet")
+        logits = model(tokens)
+        assert logits.shape == (2, 12, 40)
+        assert (model.auxiliary_loss is not None) == (variant in ("springnet", "mixture_of_depth"))
+        logits.sum().backward()
+    from experiments.misc.small_modules import XLinear as _X
+    assert sum(isinstance(m, _X) for m in build("hypersphere", cfg).modules()) == 2 * 7
     for name in ("griffin", "life"):
         result = main(["--model", name, "--steps", "30", "--batch", "8", "--seq-len", "48",
                        "--dim", "32", "--layers", "2", "--log-every", "0", "--device", "cpu"])
