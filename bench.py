@@ -17,6 +17,11 @@ replica is fixed, ``value`` is the whole-job tokens/s):
     sequence 4096, 128 sequences per data-parallel replica and step (256 at 8 GPUs) in
     micro-batches of 16; AdamW; tensor parallel (sequence-parallel layout, collectives fused into
     the GEMMs) of degree min(4, N) x sharded optimizer over the rest.
+``fsdp_1p3b`` / ``fsdp_1p3b_sharded_parameters``
+    the same 1.3B model under plain data parallelism (4 sequences of 4096 x 4 micro-batches per
+    GPU; AdamW): sharded optimizer with full parameters on every GPU, or the parameters themselves
+    sharded per block and gathered just in time (``EngineConfig(shard_parameters=True)``); the
+    JSON line of the second carries the parameter bytes a rank keeps and the most it gathered.
 ``cp8_32k``
     the same 1.3B model at sequence 32768, one sequence per context-parallel group and step;
     context parallel over all N GPUs (zig-zag shards, KV exchange under flash attention), sharded
@@ -97,6 +102,13 @@ CONFIGS: dict[str, dict] = {
         seq_len=2048, rows=32, micro_steps=1, optimizer="muon_adamw", data="chat",
     ),
 }
+CONFIGS["fsdp_1p3b"] = dict(
+    name="llama-1.3B (24L d2048 16q/4kv x128 ffn5632 V50304), data parallel",
+    model=LLAMA_1P3B, seq_len=4096, rows=4, micro_steps=4, optimizer="adamw", data="uniform",
+)
+CONFIGS["fsdp_1p3b_sharded_parameters"] = dict(CONFIGS["fsdp_1p3b"], shard_parameters=True,
+                                               name=CONFIGS["fsdp_1p3b"]["name"]
+                                               + ", parameters sharded per block")
 CONFIGS["moe_ep8_skewed"] = dict(CONFIGS["moe_ep8"], skewed=True,
                                  name=CONFIGS["moe_ep8"]["name"] + ", skewed router (half of each token's picks forced onto experts of one rank)")
 
@@ -325,6 +337,7 @@ def run_ours(args) -> dict:
             spec["tp"], sequence_parallel=torch.cuda.is_available())
         if spec["tp"] > 1 else TensorParallelPlan(),
         expert_capacity_factor=1.25 if spec["ep"] > 1 else 2.0,
+        shard_parameters=bool(spec.get("shard_parameters")) and world_env > 1,
     ))
     engine.launch()
     device = engine.device
@@ -522,6 +535,8 @@ def run_ours(args) -> dict:
         "skew": skew,
         "expert_load": load,
         "peak_memory_gib": memory,
+        "parameter_memory": (model._param_sharding.memory_report()
+                             if getattr(model, "_param_sharding", None) is not None else None),
         "world": world,
         "is_rank0": engine.is_global_zero,
         "version": getattr(ohara_b200, "__version__", "0"),
@@ -641,7 +656,7 @@ def main() -> None:
             "final_loss": res["loss"],
             "peak_memory_gib": res["peak_memory_gib"],
         }
-        for key in ("skew", "expert_load"):
+        for key in ("skew", "expert_load", "parameter_memory"):
             if res.get(key):
                 line[key] = res[key]
         if res["spec"]["data"] == "chat":

@@ -71,3 +71,15 @@ def test_tiny_reference_arms_run():
     assert line["config"]["parallelism"] == "tp2 (DTensor) x fully_shard2"
     line = _bench("--impl", "reference", "--config", "moe_ep8", world=2, port=30900)
     assert line["config"]["parallelism"].startswith("ep2")
+
+
+def test_tiny_data_parallel_config_with_sharded_parameters_on_two_ranks():
+    plain = _bench("--config", "fsdp_1p3b", world=2, port=31500)
+    sharded = _bench("--config", "fsdp_1p3b_sharded_parameters", world=2, port=32100)
+    assert plain["config"]["parallelism"] == sharded["config"]["parallelism"] == "fsdp2"
+    assert "parameter_memory" not in plain
+    memory = sharded["parameter_memory"]
+    assert memory["persistent_bytes_per_rank"] < 0.75 * memory["unsharded_bytes"]
+    assert 0 < memory["peak_gathered_bytes"] < memory["unsharded_bytes"]
+    # the same data, model and optimizer: both arrive at the same loss
+    assert abs(plain["final_loss"] - sharded["final_loss"]) < 2e-3 * plain["final_loss"]
