@@ -135,6 +135,9 @@ def parse_args() -> argparse.Namespace:
                      help="seconds between heartbeats over the rendezvous store (0 = off); a rank "
                           "whose heartbeat stops is reported before the next step is launched")
     run.add_argument("--heartbeat-timeout", type=float, default=30.0)
+    run.add_argument("--context-parallel-mode", choices=["ring", "ulysses"], default="ring",
+                     help="with --cp > 1: key/value exchange under the flash kernels (ring) or "
+                          "all-to-all between sequence shards and head shards (ulysses)")
     run.add_argument("--shard-parameters", action="store_true",
                      help="with --strategy fsdp: shard the parameters per transformer block "
                           "(gathered just before a block runs) instead of the optimizer state "
@@ -328,6 +331,7 @@ def run() -> None:
         tensor_parallel=TensorParallelPlan.llama_default(args.tp, args.sequence_parallel),
         activation_checkpointing=args.activation_checkpointing,
         shard_parameters=args.shard_parameters,
+        context_parallel_mode=args.context_parallel_mode,
         fault_tolerance=FaultToleranceConfig(
             heartbeat_interval_s=args.heartbeat_interval, heartbeat_timeout_s=args.heartbeat_timeout,
             step_timeout_s=args.step_timeout, exit_on_step_timeout=args.step_timeout > 0),

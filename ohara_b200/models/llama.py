@@ -181,6 +181,14 @@ class Attention(nn.Module):
                              "activations on CUDA, head_dim 64 or 128, a bf16 or int8 cache")
         q, k = apply_rope(q, k, freqs_cis[:2])
         if self.cp_workspace is not None and kv_cache is None:
+            from ohara_b200.parallel.ulysses import UlyssesWorkspace, ulysses_attention
+
+            if isinstance(self.cp_workspace, UlyssesWorkspace):
+                # all-to-all mode: whole sequence, this rank's heads, ordinary causal attention
+                out = ulysses_attention(q, k.to(q.dtype), v.to(q.dtype), self.cp_workspace,
+                                        self.attn_dropout.p, self.training)
+                out = out.reshape(-1, seq_len, heads * self.head_dim)
+                return self.res_dropout(self.proj(out))
             from ohara_b200.parallel.cp import context_parallel_attention
 
             bf = torch.bfloat16

@@ -62,6 +62,10 @@ class EngineConfig:
     # Recompute every transformer block in the backward pass instead of keeping its activations
     # (models that offer ``enable_activation_checkpointing``).
     activation_checkpointing: bool = False
+    # How attention sees the whole sequence under context parallelism (cp > 1): "ring" exchanges
+    # keys / values over NVLink peer memory under the flash kernels; "ulysses" re-partitions
+    # q / k / v from sequence shards to head shards with all-to-alls (needs heads >= cp).
+    context_parallel_mode: str = "ring"
     # StrategyType.FSDP only: shard the parameters themselves per transformer block (gathered
     # just before a block runs, released after it) instead of the optimizer state alone.
     shard_parameters: bool = False

@@ -424,11 +424,24 @@ class OharaEngine:
         if self.topology.cp <= 1:
             return
         enable = getattr(module, "enable_context_parallel", None)
-        if not callable(enable) or self._device.type != "cuda":
-            raise RuntimeError("cp > 1 needs a CUDA device and a model with enable_context_parallel")
-        from ohara_b200.parallel.cp import LazyCPWorkspace
+        if not callable(enable):
+            raise RuntimeError("cp > 1 needs a model with enable_context_parallel")
+        mode = self.config.context_parallel_mode
+        if mode == "ulysses":
+            # all-to-all over heads: the process group's collective, so CPU ranks work as well
+            from ohara_b200.parallel.ulysses import UlyssesWorkspace
 
-        enable(LazyCPWorkspace(self._groups.get("cp")), self.topology.cp_rank, self.topology.cp)
+            workspace = UlyssesWorkspace(self._groups.get("cp"))
+        elif mode == "ring":
+            if self._device.type != "cuda":
+                raise RuntimeError("the key/value-exchange mode of context parallelism needs CUDA "
+                                   "devices (context_parallel_mode='ulysses' runs anywhere)")
+            from ohara_b200.parallel.cp import LazyCPWorkspace
+
+            workspace = LazyCPWorkspace(self._groups.get("cp"))
+        else:
+            raise ValueError(f"unknown context_parallel_mode {mode!r} (ring or ulysses)")
+        enable(workspace, self.topology.cp_rank, self.topology.cp)
         self._cp_sequence_sharding = True
         self._replica_grads_synced = True
 
