@@ -27,7 +27,8 @@ has nothing of the kind (``dp_shard`` is arithmetic only: ohara/runtime/topology
 
 Limits: data parallelism only (no tensor / context / expert / pipeline composition), element-wise
 optimizers only (AdamW; a whole-matrix algorithm would need each matrix on one rank), fp32 on the
-wire. A resharded parameter keeps its shape, ``numel()`` and ``ndim`` but reads as one repeated
+wire. Checkpoints (the model's full state dict plus the optimizer state stored per unit as whole
+vectors) reload at any world size. A resharded parameter keeps its shape, ``numel()`` and ``ndim`` but reads as one repeated
 element: take state dicts through :meth:`ParameterSharding.full_state_dict`.
 """
 
@@ -470,20 +471,39 @@ class ParameterShardedOptimizer(Optimizer):
 
     # -- checkpoints -----------------------------------------------------------------------------
     def state_dict(self) -> dict[str, Any]:
-        """Every rank's shard of the optimizer state, gathered (collective; identical on all
-        ranks, so the rank that writes the checkpoint has all of it). Reloads at the same world
-        size; the weights themselves travel in the model's full state dict."""
-        from ohara_b200.parallel.zero import _to_cpu
-
-        local = _to_cpu(self.local.state_dict()) if self.local is not None else None
-        shards: list[Any] = [local]
-        if self.sharding.world > 1:
-            shards = [None] * self.sharding.world
-            dist.all_gather_object(shards, local, group=self.sharding.group)
+        """The optimizer state laid out per unit as whole flat vectors (collective; identical on
+        all ranks, so the rank that writes the checkpoint has all of it). The layout does not
+        depend on the number of ranks: a checkpoint reloads at any world size. The weights
+        themselves travel in the model's full state dict."""
+        sharding = self.sharding
+        mine = []
+        for index, spans in enumerate(self._spans):
+            for unit, a, b, shard in spans:
+                state = self.local.state.get(shard, {}) if self.local is not None else {}
+                vectors = {k: v.detach().reshape(-1).cpu() for k, v in state.items()
+                           if torch.is_tensor(v) and v.dim() > 0 and v.numel() == b - a}
+                scalars = {k: (v.detach().cpu() if torch.is_tensor(v) else v)
+                           for k, v in state.items() if k not in vectors}
+                mine.append((index, unit.name, sharding.rank * unit.region + a, vectors, scalars))
+        everyone: list[Any] = [mine]
+        if sharding.world > 1:
+            everyone = [None] * sharding.world
+            dist.all_gather_object(everyone, mine, group=sharding.group)
+        units: dict[str, dict[str, Tensor]] = {}
+        scalars_of_group: dict[int, dict[str, Any]] = {}
+        for pieces in everyone:
+            for index, name, begin, vectors, scalars in pieces:
+                total = sharding.by_name[name].total
+                for key, vector in vectors.items():
+                    full = units.setdefault(name, {}).setdefault(
+                        key, torch.zeros(total, dtype=vector.dtype))
+                    full[begin : begin + vector.numel()] = vector
+                if scalars:
+                    scalars_of_group.setdefault(index, scalars)
         return {
             "param_sharded": True,
-            "world": self.sharding.world,
-            "shards": shards,
+            "units": units,
+            "group_scalars": scalars_of_group,
             "param_groups": [{k: v for k, v in g.items() if k != "params"}
                              for g in self.param_groups],
         }
@@ -491,11 +511,23 @@ class ParameterShardedOptimizer(Optimizer):
     def load_state_dict(self, state_dict: dict[str, Any]) -> None:
         if not state_dict.get("param_sharded"):
             raise ValueError("not a parameter-sharded optimizer state")
-        if state_dict["world"] != self.sharding.world:
-            raise ValueError(f"a parameter-sharded optimizer state reloads at the world size it "
-                             f"was saved from ({state_dict['world']}), not {self.sharding.world}")
-        mine = state_dict["shards"][self.sharding.rank]
-        if self.local is not None and mine is not None:
-            self.local.load_state_dict(mine)
+        sharding = self.sharding
+        for index, spans in enumerate(self._spans):
+            scalars = state_dict["group_scalars"].get(index, {})
+            for unit, a, b, shard in spans:
+                saved = state_dict["units"].get(unit.name)
+                if not saved:
+                    continue
+                begin = sharding.rank * unit.region + a
+                state = self.local.state[shard]
+                for key, full in saved.items():
+                    # the tail padding of a unit depends on the world size it was saved at
+                    piece = torch.zeros(b - a, dtype=full.dtype)
+                    available = max(0, min(b - a, full.numel() - begin))
+                    piece[:available] = full[begin : begin + available]
+                    state[key] = piece.to(shard.device).view_as(shard)
+                for key, value in scalars.items():
+                    state[key] = value.clone() if torch.is_tensor(value) else value
         for group, saved in zip(self.param_groups, state_dict["param_groups"]):
             group.update(saved)
+        self._sync_hyperparameters()

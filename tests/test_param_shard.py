@@ -235,3 +235,68 @@ def test_gloo_ranks_match_single_process_training(tmp_path, world, micro, checkp
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "PARAM_SHARD_OK" in proc.stdout
+
+
+RESHARD_WORKER = """
+import sys, torch, torch.distributed as dist
+from ohara_b200.models.llama import Config, Llama
+from ohara_b200.runtime import EngineConfig, OharaEngine, StrategyType
+from ohara_b200.optimizer import build_adamw
+
+torch.manual_seed(0)
+cfg = Config(vocab_size=31, max_sequence_length=8, hidden_size=16, intermediate_size=24,
+             num_attention_heads=2, num_hidden_layers=3, dropout=0.0)
+ids = torch.randint(0, 31, (8, 9))
+engine = OharaEngine(EngineConfig(strategy=StrategyType.FSDP, shard_parameters=True))
+model = engine.prepare(Llama(cfg))
+(opt,) = engine.prepare_optimizers(build_adamw(model, learning_rate=0.02, weight_decay=0.1))
+rank, world = dist.get_rank(), dist.get_world_size()
+rows = ids[rank * (8 // world):(rank + 1) * (8 // world)]
+model.train()
+for _ in range(2):
+    loss = model(rows[:, :-1], targets=rows[:, 1:]) / rows[:, 1:].numel()
+    engine.backward(loss); opt.step(); opt.zero_grad()
+engine.save(sys.argv[1], {"model": engine.full_state_dict(model), "optimizer": opt.state_dict(),
+                          "ids": ids})
+engine.close()
+"""
+
+
+def test_checkpoint_of_two_ranks_continues_in_one_process(tmp_path):
+    """The optimizer state is stored per unit as whole vectors, so a run saved on two ranks
+    resumes on one (and the resumed run equals four uninterrupted single-process steps)."""
+    path, checkpoint = tmp_path / "worker.py", tmp_path / "ckpt.pt"
+    path.write_text(textwrap.dedent(RESHARD_WORKER))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(31200 + os.getpid() % 150), str(path),
+           str(checkpoint)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    saved = torch.load(checkpoint, weights_only=False)
+    ids = saved["ids"]
+    cfg = Config(vocab_size=31, max_sequence_length=8, hidden_size=16, intermediate_size=24,
+                 num_attention_heads=2, num_hidden_layers=3, dropout=0.0)
+    torch.manual_seed(0)                      # the worker's random stream: tokens, then weights
+    assert torch.equal(torch.randint(0, 31, (8, 9)), ids)
+    plain = Llama(cfg)
+    plain_opt = build_adamw(plain, learning_rate=0.02, weight_decay=0.1)
+    plain.train()
+    for _ in range(4):
+        (plain(ids[:, :-1], targets=ids[:, 1:]) / ids[:, 1:].numel()).backward()
+        plain_opt.step()
+        plain_opt.zero_grad()
+    resumed = Llama(cfg)
+    sharding = shard_llama(resumed)
+    sharding.load_full_state_dict(resumed, saved["model"])
+    optimizer = ParameterShardedOptimizer(
+        build_adamw(resumed, learning_rate=0.02, weight_decay=0.1), sharding)
+    optimizer.load_state_dict(saved["optimizer"])
+    resumed.train()
+    for _ in range(2):
+        (resumed(ids[:, :-1], targets=ids[:, 1:]) / ids[:, 1:].numel()).backward()
+        optimizer.step()
+        optimizer.zero_grad()
+    final = sharding.full_state_dict(resumed)
+    for name, value in plain.state_dict().items():
+        torch.testing.assert_close(final[name], value, rtol=1e-4, atol=3e-5, msg=name)
