@@ -217,3 +217,91 @@ def test_configs_round_trip_through_state_dicts():
     mixed = config_from_state_dict(single.state_dict())
     assert mixed.moe_layer_interval == 3
     Llama(mixed).load_state_dict(single.state_dict())
+
+
+# -- further behaviours of the reference suite (tests/test_moe_grouped.py:150-463) ---------------------
+def test_gradients_reach_router_experts_and_shared_mlp_once_the_output_projection_is_nonzero():
+    moe = layer()
+    x = torch.randn(2, 6, 16, requires_grad=True)
+    moe(x).square().sum().backward()
+    for name in ("w_gate", "w_up", "w_down"):
+        assert getattr(moe, name).grad.abs().sum() > 0, name
+    assert moe.router.weight.grad.abs().sum() > 0
+    assert moe.shared_gate.weight.grad.abs().sum() > 0 and x.grad.abs().sum() > 0
+    assert not moe.router_bias.requires_grad and moe.router_bias.grad is None
+
+
+def test_statistics_accumulate_only_in_training_and_disabled_balancing_keeps_a_zero_bias():
+    moe = layer()
+    x = torch.randn(4, 8, 16)
+    moe.eval()
+    moe(x)
+    assert int(moe.expert_counts.sum()) == 0 and int(moe.qb_beta_count) == 0
+    moe.train()
+    moe(x)
+    assert int(moe.expert_counts.sum()) == 4 * 8 * 2 and int(moe.qb_beta_count) == 1
+    plain = layer(quantile_balancing=False)
+    plain.train()
+    for _ in range(3):
+        plain(torch.randn(4, 8, 16))
+        plain.apply_qb_update()
+    assert torch.all(plain.router_bias == 0)
+
+
+def test_model_level_helpers_see_grouped_layers_and_each_token_picks_distinct_experts():
+    model = tiny_llama(40, moe_num_experts=4, moe_experts_per_tok=2, moe_grouped=True)
+    model.train()
+    model(torch.randint(0, model.config.vocab_size, (2, 8)))
+    loads = expert_load(model, reset=False)
+    assert len(loads) == model.config.num_hidden_layers
+    assert all(int(c.sum()) == 2 * 8 * 2 for c in loads)
+    assert maximal_violation(loads[0]) >= 0.0
+    apply_qb_update(model)                                    # walks the grouped layers too
+    assert any(bool((b.ff.router_bias != 0).any()) for b in model.layers)
+    moe = layer(num_experts_per_tok=3)
+    indices, _, _, _ = moe._route(torch.randn(50, 16))
+    assert all(len(set(row.tolist())) == 3 for row in indices)
+
+
+def test_llama_refuses_grouped_only_options_without_the_grouped_layer():
+    with pytest.raises(ValueError):
+        Llama(Config(moe_num_experts=4, moe_grouped=False, moe_num_shared_experts=1))
+    with pytest.raises(ValueError):
+        Llama(Config(moe_num_experts=0, moe_grouped=True))
+
+
+def test_checkpoint_shapes_recover_mixed_dense_and_moe_layouts_and_default_routing_choices():
+    mixed = tiny_llama(40, moe_num_experts=4, moe_experts_per_tok=2, moe_grouped=True,
+                       moe_layer_interval=2, moe_num_shared_experts=2, num_hidden_layers=4)
+    cfg = config_from_state_dict(mixed.state_dict())
+    assert (cfg.moe_num_experts, cfg.moe_layer_interval, cfg.moe_num_shared_experts) == (4, 2, 2)
+    assert cfg.moe_grouped and cfg.moe_experts_per_tok == 2            # the default when not given
+    rebuilt = Llama(cfg)
+    rebuilt.load_state_dict(mixed.state_dict())
+    single = tiny_llama(40, moe_num_experts=4, moe_grouped=True, moe_layer_interval=3,
+                        num_hidden_layers=3)                           # one MoE layer out of three
+    assert config_from_state_dict(single.state_dict()).moe_layer_interval == 3
+    chosen = config_from_state_dict(mixed.state_dict(), moe_experts_per_tok=3, moe_gate_fn="sigmoid",
+                                    moe_normalize_weights=False)
+    assert (chosen.moe_experts_per_tok, chosen.moe_gate_fn, chosen.moe_normalize_weights) == (
+        3, "sigmoid", False)
+    dense = config_from_state_dict(tiny_llama(40).state_dict())
+    assert dense.moe_num_experts == 0
+    looped = config_from_state_dict(tiny_llama(40, moe_num_experts=4, moe_experts_per_tok=2).state_dict())
+    assert looped.moe_num_experts == 4 and not looped.moe_grouped
+
+
+def test_a_muon_step_moves_the_expert_stacks_and_keeps_them_finite():
+    model = tiny_llama(40, moe_num_experts=4, moe_experts_per_tok=2, moe_grouped=True)
+    optimizer = build_muon_adamw(model)
+    listed = [p for g in optimizer.param_groups for p in g["params"]]
+    assert {id(p) for p in listed} == {id(p) for p in model.parameters()}
+    before = model.layers[0].ff.w_down.detach().clone()
+    tokens = torch.randint(0, model.config.vocab_size, (2, 9))
+    for _ in range(2):
+        logits = model(tokens[:, :-1])
+        torch.nn.functional.cross_entropy(logits.flatten(0, 1), tokens[:, 1:].flatten()).backward()
+        optimizer.step()
+        optimizer.zero_grad()
+    after = model.layers[0].ff.w_down.detach()
+    assert torch.isfinite(after).all() and not torch.equal(after, before)
