@@ -401,7 +401,18 @@ class Llama(nn.Module):
         and the start of the backward pass."""
         sharding = self._param_sharding
         h = sharding.run_unit("embed", lambda ids: ops.embedding(ids, self.token_emb.weight), x)
-        freqs = (self.freq_cos[:seq], self.freq_sin[:seq])
+        cp = getattr(self, "_cp", None)
+        if cp is not None:
+            if cp[1] * seq > self.config.max_sequence_length:
+                raise ValueError("the full sequence exceeds max_sequence_length")
+            cached = self._cp_positions
+            if cached is None or cached.numel() != seq or cached.device != x.device:
+                from ohara_b200.parallel.cp import local_positions
+
+                cached = self._cp_positions = local_positions(cp[0], cp[1], seq, device=x.device)
+            freqs = (self.freq_cos[cached], self.freq_sin[cached])
+        else:
+            freqs = (self.freq_cos[:seq], self.freq_sin[:seq])
         recompute = self.activation_checkpointing and self.training and torch.is_grad_enabled()
         pending = None
         for idx, layer in enumerate(self.layers):

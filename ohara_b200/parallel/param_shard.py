@@ -25,8 +25,9 @@ The collectives are the process group's ``all_gather_into_tensor`` / ``reduce_sc
 (NCCL on GPUs, gloo on CPUs, where the reduce-scatter is an all-reduce plus a slice). The reference
 has nothing of the kind (``dp_shard`` is arithmetic only: ohara/runtime/topology.py:33-38).
 
-Limits: data parallelism only (no tensor / context / expert / pipeline composition), element-wise
-optimizers only (AdamW; a whole-matrix algorithm would need each matrix on one rank), fp32 on the
+Limits: composes with tensor and context parallelism (the units are then this rank's tensor
+shards, sharded over its data-parallel and context-parallel peers), not with expert or pipeline
+parallelism or hybrid sharding; element-wise optimizers only (AdamW; a whole-matrix algorithm would need each matrix on one rank), fp32 on the
 wire. Checkpoints (the model's full state dict plus the optimizer state stored per unit as whole
 vectors) reload at any world size. A resharded parameter keeps its shape, ``numel()`` and ``ndim`` but reads as one repeated
 element: take state dicts through :meth:`ParameterSharding.full_state_dict`.
@@ -114,9 +115,12 @@ class ParameterSharding:
     does that)."""
 
     def __init__(self, units: Iterable[tuple[str, list[nn.Parameter]]], group=None, *,
-                 keep_gathered: Iterable[str] = (), prefetch: bool = True) -> None:
+                 keep_gathered: Iterable[str] = (), prefetch: bool = True,
+                 solo: bool = False) -> None:
+        """``solo``: shard over nobody although a process group exists (every other rank of the
+        job holds different tensors, e.g. the tensor-parallel peers)."""
         self.group = group
-        distributed = dist.is_available() and dist.is_initialized()
+        distributed = dist.is_available() and dist.is_initialized() and not solo
         self.world = dist.get_world_size(group) if distributed else 1
         self.rank = dist.get_rank(group) if distributed else 0
         self.prefetch = prefetch
@@ -138,6 +142,10 @@ class ParameterSharding:
                 self.unit_of_param[id(p)] = unit
                 if p.requires_grad:
                     p.register_post_accumulate_grad_hook(self._on_gradient)
+        # Set by the engine under sequence-parallel tensor parallelism: the ranks of this group
+        # see different tokens, so gradients of parameters that are NOT tensor-parallel shards
+        # are partial sums and are added up over it before the data-parallel reduction.
+        self.partial_gradient_group = None
         self.unsharded_bytes = sum(sum(u.numels) for u in self.units) * 4
         self.peak_gathered_bytes = 0
         for unit in self.units:
@@ -247,6 +255,10 @@ class ParameterSharding:
                 if p.grad is not None:
                     flat[off : off + n].copy_(p.grad.reshape(-1))
                     p.grad = None
+            if self.partial_gradient_group is not None:
+                for p, off, n in zip(unit.params, unit.offsets, unit.numels):
+                    if not hasattr(p, "tensor_parallel_dim"):
+                        dist.all_reduce(flat[off : off + n], group=self.partial_gradient_group)
             if self.world == 1:
                 shard = flat
             elif dist.get_backend(self.group) == "gloo":  # gloo has no reduce-scatter
@@ -312,7 +324,8 @@ class ParameterSharding:
                 "unsharded_bytes": self.unsharded_bytes}
 
 
-def shard_llama(model: nn.Module, group=None, prefetch: bool = True) -> ParameterSharding:
+def shard_llama(model: nn.Module, group=None, prefetch: bool = True,
+                solo: bool = False) -> ParameterSharding:
     """Cut a Llama into units (embedding, blocks, final norm + output projection), shard them over
     ``group`` and attach the result as ``model._param_sharding``; the model's forward pass then
     gathers and releases the units as it goes."""
@@ -345,7 +358,7 @@ def shard_llama(model: nn.Module, group=None, prefetch: bool = True) -> Paramete
     missing = [name for name, p in model.named_parameters() if id(p) not in covered]
     if missing:
         raise ValueError(f"parameters outside every unit: {missing[:4]}")
-    sharding = ParameterSharding(units, group, keep_gathered=keep, prefetch=prefetch)
+    sharding = ParameterSharding(units, group, keep_gathered=keep, prefetch=prefetch, solo=solo)
     sharding.tied = tied
     model._param_sharding = sharding
     return sharding
@@ -358,9 +371,23 @@ class ParameterShardedOptimizer(Optimizer):
     ...) are kept as the user-visible ``param_groups`` and mirrored onto a local optimizer of the
     same class over 1-D views of the master shards. Element-wise algorithms only."""
 
-    def __init__(self, optimizer: Optimizer, sharding: ParameterSharding) -> None:
+    def __init__(self, optimizer: Optimizer, sharding: ParameterSharding,
+                 norm_groups: dict[str, Any] | None = None) -> None:
+        """``norm_groups["tp"]``: the tensor-parallel group, over which the squared norms of
+        tensor-parallel shards add up for the global gradient norm (replicated parameters are
+        counted once)."""
         self.inner = optimizer
         self.sharding = sharding
+        self.norm_groups = dict(norm_groups or {})
+        self._tp_spans: dict[str, list[tuple[int, int]]] = {}
+        for unit in sharding.units:
+            lo, hi = sharding.rank * unit.region, (sharding.rank + 1) * unit.region
+            spans = []
+            for p, off, n in zip(unit.params, unit.offsets, unit.numels):
+                a, b = max(off, lo), min(off + n, hi)
+                if a < b and hasattr(p, "tensor_parallel_dim"):
+                    spans.append((a - lo, b - lo))
+            self._tp_spans[unit.name] = spans
         self.param_groups = optimizer.param_groups
         self.defaults = optimizer.defaults
         self.state = optimizer.state
@@ -448,13 +475,20 @@ class ParameterShardedOptimizer(Optimizer):
     def grad_sq_norm(self) -> Tensor:
         self.sharding.finish_backward()
         device = self.sharding.units[0].master.device
-        total = torch.zeros((), device=device, dtype=torch.float32)
+        sums = torch.zeros(2, device=device, dtype=torch.float32)   # everything, tensor shards
         for unit in self.sharding.units:
-            if unit.grad is not None:
-                total += unit.grad.square().sum()
+            if unit.grad is None:
+                continue
+            sums[0] += unit.grad.square().sum()
+            for a, b in self._tp_spans[unit.name]:
+                sums[1] += unit.grad[a:b].square().sum()
         if self.sharding.world > 1:
-            dist.all_reduce(total, group=self.sharding.group)
-        return total
+            dist.all_reduce(sums, group=self.sharding.group)
+        if "tp" not in self.norm_groups:
+            return sums[0]
+        shards = sums[1].clone()
+        dist.all_reduce(shards, group=self.norm_groups["tp"])   # distinct on every tp rank
+        return sums[0] - sums[1] + shards
 
     @torch.no_grad()
     def clip_grad_norm_(self, model, max_norm: float) -> Tensor:

@@ -193,10 +193,9 @@ class OharaEngine:
             # group: the engine then equalises the full model before it is sharded instead.
             composed = topo.tp_enabled or topo.ep > 1 or topo.cp > 1 or topo.pp > 1
             hybrid = topo.dp_replicate > 1 and topo.dp_shard > 1
-            if self.config.shard_parameters and (composed or hybrid):
-                raise NotImplementedError("shard_parameters composes with plain data "
-                                          "parallelism only (no tp / cp / ep / pp, no hybrid "
-                                          "sharding)")
+            if self.config.shard_parameters and (topo.ep > 1 or topo.pp > 1 or hybrid):
+                raise NotImplementedError("shard_parameters composes with data, tensor and "
+                                          "context parallelism (no ep / pp, no hybrid sharding)")
             self._strategy = FSDPStrategy(fused=fused, init_sync=not composed,
                                           shard_parameters=self.config.shard_parameters)
             base_size = topo.dp_shard if hybrid else topo.dp_world_size
@@ -214,6 +213,7 @@ class OharaEngine:
                 expert_group=self._groups.get("expert_shard"),
                 expert_world=base_size * topo.cp,
                 norm_groups=norm_groups,
+                shard_world=base_size * topo.cp * topo.ep,
             )
             self._sharded_over_cp = topo.cp > 1
         else:
@@ -378,7 +378,17 @@ class OharaEngine:
             group = self._groups.get("shard")
         else:
             group = self._groups.get("dp_ep") if self.topology.ep > 1 else self._groups.get("dp")
+        replicas = self.topology.dp_world_size * (self.topology.ep if self.topology.ep > 1 else 1)
+        if isinstance(self._strategy, DDPStrategy) and replicas <= 1:
+            # every other rank of the job is a tensor- / context- / pipeline-parallel peer: there
+            # is nothing to replicate over, and the default group would average different shards
+            self._module = module
+            return module
         module = self._strategy.setup_module(module, device=self._device, process_group=group)
+        sharding = getattr(module, "_param_sharding", None)
+        if sharding is not None and getattr(self, "_tp_batch_sharding", False):
+            # sequence-parallel layout: replicated parameters hold partial gradients per tp rank
+            sharding.partial_gradient_group = self._groups.get("tp")
         self._module = module
         return module
 
@@ -814,7 +824,11 @@ class OharaEngine:
         inner = module.module if hasattr(module, "module") else module
         sharding = getattr(inner, "_param_sharding", None)
         if sharding is not None:
-            return sharding.full_state_dict(inner)
+            if not self.topology.tp_enabled:
+                return sharding.full_state_dict(inner)
+            with sharding.gathered():  # whole tensor shards first, then whole matrices
+                return {k: v.detach().clone() for k, v in gather_tensor_parallel_state(
+                    inner, self._groups.get("tp")).items()}
         sync = getattr(getattr(self, "_sharded_optimizer", None), "sync_master_weights", None)
         if callable(sync):
             sync()

@@ -44,10 +44,19 @@ class FSDPStrategy(BaseStrategy):
         self.expert_group = None
         self.expert_world = 1
         self.norm_groups: dict[str, Any] = {}
+        self.shard_world: int | None = None
+
+    @property
+    def solo(self) -> bool:
+        return self.shard_world is not None and self.shard_world <= 1
 
     def configure(self, *, replicate_group=None, replicate_world: int = 1,
                   expert_parallel: bool = False, expert_group=None, expert_world: int = 1,
-                  norm_groups: dict[str, Any] | None = None) -> None:
+                  norm_groups: dict[str, Any] | None = None, shard_world: int | None = None) -> None:
+        """``shard_world``: size of the group the dense parameters are sharded over. When it is 1
+        although the job has several ranks (all of them tensor-parallel peers, say) the optimizer
+        shards over nobody: falling back to the default group would mix different tensor shards."""
+        self.shard_world = shard_world
         self.replicate_group, self.replicate_world = replicate_group, replicate_world
         self.expert_parallel = expert_parallel
         self.expert_group, self.expert_world = expert_group, expert_world
@@ -59,7 +68,7 @@ class FSDPStrategy(BaseStrategy):
 
         self.process_group = process_group
         self.device = device
-        if self.init_sync and dist.is_initialized():
+        if self.init_sync and dist.is_initialized() and not self.solo:
             # Replicas must start from identical weights, as DDP guarantees.
             src = dist.get_global_rank(process_group, 0) if process_group is not None else 0
             for tensor in list(module.parameters()) + list(module.buffers()):
@@ -67,7 +76,7 @@ class FSDPStrategy(BaseStrategy):
         if self.shard_parameters:
             from ohara_b200.parallel.param_shard import shard_llama
 
-            shard_llama(module, process_group)
+            shard_llama(module, process_group, solo=self.solo)
         return module
 
     def setup_optimizer(self, optimizer, module: nn.Module | None = None):
@@ -81,20 +90,22 @@ class FSDPStrategy(BaseStrategy):
 
             if isinstance(optimizer, ParameterShardedOptimizer):
                 return optimizer
-            return ParameterShardedOptimizer(optimizer, sharding)
+            return ParameterShardedOptimizer(
+                optimizer, sharding,
+                norm_groups={k: v for k, v in self.norm_groups.items() if k == "tp"})
         dense_norms = {k: v for k, v in self.norm_groups.items() if k in ("tp", "pp")}
         common = dict(fused=self.fused, replicate_group=self.replicate_group,
                       replicate_world=self.replicate_world)
         if not self.expert_parallel:
             return ShardedOptimizer(optimizer, process_group=self.process_group,
-                                    norm_groups=dense_norms, **common)
+                                    norm_groups=dense_norms, solo=self.solo, **common)
 
         def is_expert(p) -> bool:
             return bool(getattr(p, "expert_parallel", False))
 
         return HybridShardedOptimizer(optimizer, [
             dict(select=lambda p: not is_expert(p), process_group=self.process_group,
-                 norm_groups=dense_norms, **common),
+                 norm_groups=dense_norms, solo=self.solo, **common),
             dict(select=is_expert, process_group=self.expert_group,
                  solo=self.expert_world <= 1, norm_groups=self.norm_groups, **common),
         ])

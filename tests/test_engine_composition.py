@@ -324,3 +324,33 @@ def test_feed_forward_and_head_only_tensor_parallel_plan(tmp_path):
         4, tmp_path, port_base=32900,
     )
     assert "MLP_HEAD_TP_OK" in out
+
+
+def test_tensor_parallel_ranks_without_data_parallel_peers_are_not_treated_as_replicas(tmp_path):
+    """tp = world: there is no data-parallel group. Neither the sharded optimizer nor the DDP
+    wrapper may fall back to the default group, which would average different tensor shards."""
+    for strategy in ("FSDP", "DDP"):
+        out = _run(
+            f"""
+            solo = reference(lambda m: build_adamw(m, learning_rate=0.02, weight_decay=0.1))
+            engine = OharaEngine(EngineConfig(strategy=StrategyType.{strategy},
+                                              parallel=ParallelConfig(tp=2),
+                                              tensor_parallel=TensorParallelPlan.llama_default(2)))
+            model = Llama(cfg); model.load_state_dict(state)
+            model = engine.prepare(model)
+            (opt,) = engine.prepare_optimizers(build_adamw(model, learning_rate=0.02, weight_decay=0.1))
+            assert getattr(opt, "world", 1) == 1
+            loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=8))
+            trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=1,
+                              max_iters=3, eval_iters=0, save_ckpt_iters=0)
+            trainer.train()
+            full = engine.full_state_dict(model)
+            for name, value in solo.state_dict().items():
+                assert torch.allclose(full[name], value, atol=2e-5), (name, (full[name] - value).abs().max())
+            if dist.get_rank() == 0:
+                print("TP_ONLY_OK")
+            engine.close()
+            """,
+            2, tmp_path, port_base=29900,
+        )
+        assert "TP_ONLY_OK" in out

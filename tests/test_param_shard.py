@@ -300,3 +300,72 @@ def test_checkpoint_of_two_ranks_continues_in_one_process(tmp_path):
     final = sharding.full_state_dict(resumed)
     for name, value in plain.state_dict().items():
         torch.testing.assert_close(final[name], value, rtol=1e-4, atol=3e-5, msg=name)
+
+
+COMPOSED_WORKER = """
+import torch, torch.distributed as dist
+from torch.utils.data import DataLoader, TensorDataset
+from ohara_b200.models.llama import Config, Llama
+from ohara_b200.runtime import (EngineConfig, OharaEngine, ParallelConfig, StrategyType,
+                                TensorParallelPlan)
+from ohara_b200.optimizer import build_adamw
+from ohara_b200.trainer import Trainer
+from ohara_b200.lr_scheduler import Scheduler
+
+torch.manual_seed(0)
+cfg = Config(vocab_size=32, max_sequence_length=16, hidden_size=16, intermediate_size=24,
+             num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=2, dropout=0.0)
+ids = torch.randint(0, 32, (8, 17))
+dataset = TensorDataset(ids[:, :-1], ids[:, 1:])
+state = {k: v.clone() for k, v in Llama(cfg).state_dict().items()}
+solo = Llama(cfg); solo.load_state_dict(state)
+ref_opt = build_adamw(solo, learning_rate=0.02, weight_decay=0.1)
+ref_norms = []
+for _ in range(3):
+    loss = solo.loss_sum(ids[:, :-1], ids[:, 1:]) / ids[:, 1:].numel()
+    loss.backward()
+    ref_norms.append(float(torch.nn.utils.clip_grad_norm_(solo.parameters(), 0.5)))
+    ref_opt.step(); ref_opt.zero_grad()
+
+engine = OharaEngine(EngineConfig(
+    strategy=StrategyType.FSDP, shard_parameters=True, context_parallel_mode="ulysses",
+    parallel=ParallelConfig(tp=TP, cp=CP),
+    tensor_parallel=TensorParallelPlan.llama_default(TP) if TP > 1 else TensorParallelPlan()))
+model = Llama(cfg); model.load_state_dict(state)
+model = engine.prepare(model)
+(opt,) = engine.prepare_optimizers(build_adamw(model, learning_rate=0.02, weight_decay=0.1))
+assert type(opt).__name__ == "ParameterShardedOptimizer"
+dp = engine.data_parallel_world_size
+assert dp == dist.get_world_size() // (TP * CP)
+loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=8 // dp))
+trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=1,
+                  max_iters=3, eval_iters=0, save_ckpt_iters=0, grad_clip_norm=0.5)
+norms = []
+clip = opt.clip_grad_norm_
+def recording(m, n):
+    value = clip(m, n); norms.append(float(value)); return value
+opt.clip_grad_norm_ = recording
+trainer.train()
+assert all(abs(a - b) < 1e-4 * max(1.0, abs(b)) for a, b in zip(norms, ref_norms)), (norms, ref_norms)
+full = engine.full_state_dict(model)
+for name, value in solo.state_dict().items():
+    assert full[name].shape == value.shape, name
+    assert torch.allclose(full[name], value, atol=3e-5), (name, (full[name] - value).abs().max())
+if dist.get_rank() == 0:
+    print("COMPOSED_OK")
+engine.close()
+"""
+
+
+@pytest.mark.parametrize("world,tp,cp", [(4, 2, 1), (4, 1, 2), (2, 2, 1)])
+def test_sharded_parameters_compose_with_tensor_and_context_parallelism(tmp_path, world, tp, cp):
+    """The units are this rank's tensor shards, sharded over its data- and context-parallel
+    peers; the clipped global norm counts tensor shards once each."""
+    path = tmp_path / "worker.py"
+    path.write_text(textwrap.dedent(COMPOSED_WORKER).replace("TP", str(tp)).replace("CP", str(cp)))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(31700 + os.getpid() % 150), str(path)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "COMPOSED_OK" in proc.stdout
