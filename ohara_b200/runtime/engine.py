@@ -861,7 +861,22 @@ class OharaEngine:
         self.barrier()
 
     def load(self, path: str | Path, state: dict[str, Any] | None = None) -> dict[str, Any]:
-        payload: dict[str, Any] = torch.load(Path(path), map_location=self._device, weights_only=False)
+        try:
+            payload: dict[str, Any] = torch.load(Path(path), map_location=self._device,
+                                                 weights_only=False)
+        except FileNotFoundError:
+            raise
+        except Exception as error:  # noqa: BLE001 - a damaged file surfaces as many different errors
+            # (zip, pickle, EOF ...): name the file, keep the cause. ``save`` never leaves such a
+            # file behind (it renames a complete temporary file), so this is damage from outside.
+            from ohara_b200.errors import CheckpointError
+
+            raise CheckpointError(f"{path} is not a readable checkpoint "
+                                  f"({type(error).__name__}: {error})") from error
+        if not isinstance(payload, dict):
+            from ohara_b200.errors import CheckpointError
+
+            raise CheckpointError(f"{path} holds a {type(payload).__name__}, not a checkpoint")
         if state is None:
             return payload
         for key, obj in state.items():

@@ -369,3 +369,44 @@ def test_step_watchdog_expiry_releases_fused_waits():
             time.sleep(0.05)
     assert released
     engine.close()
+
+
+def test_interrupted_save_keeps_the_previous_checkpoint_and_damaged_files_are_named(tmp_path, monkeypatch):
+    """Host-side failure injection around checkpoints: a crash in the middle of a save leaves the
+    last complete file in place and no temporary file behind; a truncated or foreign file raises
+    ``CheckpointError`` with the path instead of loading garbage."""
+    import torch
+
+    from ohara_b200 import OharaEngine
+    from ohara_b200.errors import CheckpointError
+
+    engine = OharaEngine()
+    path = tmp_path / "run" / "ckpt.pt"
+    engine.save(path, {"idx": 1, "weights": torch.arange(4.0)})
+    real_save = torch.save
+
+    def dies_half_way(obj, file, *args, **kwargs):
+        real_save(obj, file, *args, **kwargs)
+        with open(file, "r+b") as handle:          # the temporary file is incomplete ...
+            handle.truncate(10)
+        raise OSError("disk full")                # ... when the process is interrupted
+
+    monkeypatch.setattr(torch, "save", dies_half_way)
+    with pytest.raises(OSError, match="disk full"):
+        engine.save(path, {"idx": 2, "weights": torch.zeros(4)})
+    monkeypatch.setattr(torch, "save", real_save)
+    assert [p.name for p in path.parent.iterdir()] == ["ckpt.pt"]      # no temporary file left
+    assert engine.load(path)["idx"] == 1                                 # the old one is intact
+
+    whole = path.read_bytes()
+    path.write_bytes(whole[: len(whole) // 2])
+    with pytest.raises(CheckpointError, match="ckpt.pt"):
+        engine.load(path)
+    path.write_bytes(b"not a checkpoint at all")
+    with pytest.raises(CheckpointError):
+        engine.load(path)
+    real_save([1, 2, 3], path)
+    with pytest.raises(CheckpointError, match="list"):
+        engine.load(path)
+    with pytest.raises(FileNotFoundError):
+        engine.load(tmp_path / "missing.pt")
