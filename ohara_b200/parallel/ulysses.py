@@ -77,7 +77,7 @@ def sequence_to_heads(x: Tensor, workspace: UlyssesWorkspace) -> Tensor:
     with this rank's heads of every token, rank after rank."""
     batch, steps, heads, dim = x.shape
     world = workspace.world
-    blocks = x.view(batch, steps, world, heads // world, dim).permute(2, 0, 1, 3, 4)
+    blocks = x.reshape(batch, steps, world, heads // world, dim).permute(2, 0, 1, 3, 4)
     received = _Exchange.apply(blocks, workspace.group)            # (source, B, t, h, D)
     return received.permute(1, 0, 2, 3, 4).reshape(batch, world * steps, heads // world, dim)
 
@@ -87,7 +87,7 @@ def heads_to_sequence(x: Tensor, workspace: UlyssesWorkspace) -> Tensor:
     batch, total, heads, dim = x.shape
     world = workspace.world
     steps = total // world
-    blocks = x.view(batch, world, steps, heads, dim).permute(1, 0, 2, 3, 4)
+    blocks = x.reshape(batch, world, steps, heads, dim).permute(1, 0, 2, 3, 4)
     received = _Exchange.apply(blocks, workspace.group)            # (head group, B, t, h, D)
     return received.permute(1, 2, 0, 3, 4).reshape(batch, steps, world * heads, dim)
 
