@@ -328,13 +328,13 @@ for _ in range(3):
     ref_opt.step(); ref_opt.zero_grad()
 
 engine = OharaEngine(EngineConfig(
-    strategy=StrategyType.FSDP, shard_parameters=True, context_parallel_mode="ulysses",
-    parallel=ParallelConfig(tp=TP, cp=CP),
+    strategy=StrategyType.FSDP, shard_parameters=SHARD, context_parallel_mode="ulysses",
+    activation_checkpointing=RECOMPUTE, parallel=ParallelConfig(tp=TP, cp=CP),
     tensor_parallel=TensorParallelPlan.llama_default(TP) if TP > 1 else TensorParallelPlan()))
 model = Llama(cfg); model.load_state_dict(state)
 model = engine.prepare(model)
 (opt,) = engine.prepare_optimizers(build_adamw(model, learning_rate=0.02, weight_decay=0.1))
-assert type(opt).__name__ == "ParameterShardedOptimizer"
+assert (type(opt).__name__ == "ParameterShardedOptimizer") == SHARD
 dp = engine.data_parallel_world_size
 assert dp == dist.get_world_size() // (TP * CP)
 loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=8 // dp))
@@ -357,12 +357,20 @@ engine.close()
 """
 
 
-@pytest.mark.parametrize("world,tp,cp", [(4, 2, 1), (4, 1, 2), (2, 2, 1)])
-def test_sharded_parameters_compose_with_tensor_and_context_parallelism(tmp_path, world, tp, cp):
+@pytest.mark.parametrize("world,tp,cp,shard,recompute", [
+    (4, 2, 1, True, False), (4, 1, 2, True, False), (2, 2, 1, True, False),
+    (4, 2, 1, True, True),      # sharded parameters + recomputed blocks under tensor parallelism
+    (2, 2, 1, False, True),     # activation checkpointing with tensor-parallel collectives inside
+    (2, 1, 2, False, True),     # ... and with the all-to-alls of context parallelism inside
+])
+def test_sharded_parameters_compose_with_tensor_and_context_parallelism(tmp_path, world, tp, cp,
+                                                                        shard, recompute):
     """The units are this rank's tensor shards, sharded over its data- and context-parallel
-    peers; the clipped global norm counts tensor shards once each."""
+    peers; the clipped global norm counts tensor shards once each. Recomputed blocks repeat their
+    collectives in the backward pass, on every rank at the same point."""
     path = tmp_path / "worker.py"
-    path.write_text(textwrap.dedent(COMPOSED_WORKER).replace("TP", str(tp)).replace("CP", str(cp)))
+    path.write_text(textwrap.dedent(COMPOSED_WORKER).replace("TP", str(tp)).replace("CP", str(cp))
+                    .replace("SHARD", str(shard)).replace("RECOMPUTE", str(recompute)))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(31700 + os.getpid() % 150), str(path)]
