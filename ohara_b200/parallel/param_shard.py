@@ -26,8 +26,8 @@ The collectives are the process group's ``all_gather_into_tensor`` / ``reduce_sc
 has nothing of the kind (``dp_shard`` is arithmetic only: ohara/runtime/topology.py:33-38).
 
 Limits: composes with tensor and context parallelism (the units are then this rank's tensor
-shards, sharded over its data-parallel and context-parallel peers), not with expert or pipeline
-parallelism or hybrid sharding; element-wise optimizers only (AdamW; a whole-matrix algorithm would need each matrix on one rank), fp32 on the
+shards, sharded over its data-parallel and context-parallel peers) and with hybrid sharding, not
+with expert or pipeline parallelism; element-wise optimizers only (AdamW; a whole-matrix algorithm would need each matrix on one rank), fp32 on the
 wire. Checkpoints (the model's full state dict plus the optimizer state stored per unit as whole
 vectors) reload at any world size. A resharded parameter keeps its shape, ``numel()`` and ``ndim`` but reads as one repeated
 element: take state dicts through :meth:`ParameterSharding.full_state_dict`.
@@ -116,10 +116,14 @@ class ParameterSharding:
 
     def __init__(self, units: Iterable[tuple[str, list[nn.Parameter]]], group=None, *,
                  keep_gathered: Iterable[str] = (), prefetch: bool = True,
-                 solo: bool = False) -> None:
+                 solo: bool = False, replicate_group=None, replicate_world: int = 1) -> None:
         """``solo``: shard over nobody although a process group exists (every other rank of the
-        job holds different tensors, e.g. the tensor-parallel peers)."""
+        job holds different tensors, e.g. the tensor-parallel peers). ``replicate_group`` (of
+        ``replicate_world`` ranks): hybrid sharding, the ranks that hold the same shard as this
+        one in other replica groups; reduced gradient shards are averaged over it."""
         self.group = group
+        self.replicate_group = replicate_group
+        self.replicate_world = int(replicate_world) if dist.is_initialized() else 1
         distributed = dist.is_available() and dist.is_initialized() and not solo
         self.world = dist.get_world_size(group) if distributed else 1
         self.rank = dist.get_rank(group) if distributed else 0
@@ -269,6 +273,9 @@ class ParameterSharding:
                 dist.reduce_scatter_tensor(shard, flat, group=self.group)
             if self.world > 1:
                 shard.div_(self.world)
+            if self.replicate_world > 1:
+                dist.all_reduce(shard, group=self.replicate_group)
+                shard.div_(self.replicate_world)
             unit.grad = shard if unit.grad is None else unit.grad.add_(shard)
         unit.remaining = unit.trainable
         self._release(unit)
@@ -324,8 +331,8 @@ class ParameterSharding:
                 "unsharded_bytes": self.unsharded_bytes}
 
 
-def shard_llama(model: nn.Module, group=None, prefetch: bool = True,
-                solo: bool = False) -> ParameterSharding:
+def shard_llama(model: nn.Module, group=None, prefetch: bool = True, solo: bool = False,
+                replicate_group=None, replicate_world: int = 1) -> ParameterSharding:
     """Cut a Llama into units (embedding, blocks, final norm + output projection), shard them over
     ``group`` and attach the result as ``model._param_sharding``; the model's forward pass then
     gathers and releases the units as it goes."""
@@ -358,7 +365,8 @@ def shard_llama(model: nn.Module, group=None, prefetch: bool = True,
     missing = [name for name, p in model.named_parameters() if id(p) not in covered]
     if missing:
         raise ValueError(f"parameters outside every unit: {missing[:4]}")
-    sharding = ParameterSharding(units, group, keep_gathered=keep, prefetch=prefetch, solo=solo)
+    sharding = ParameterSharding(units, group, keep_gathered=keep, prefetch=prefetch, solo=solo,
+                                 replicate_group=replicate_group, replicate_world=replicate_world)
     sharding.tied = tied
     model._param_sharding = sharding
     return sharding

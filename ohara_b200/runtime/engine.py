@@ -193,9 +193,9 @@ class OharaEngine:
             # group: the engine then equalises the full model before it is sharded instead.
             composed = topo.tp_enabled or topo.ep > 1 or topo.cp > 1 or topo.pp > 1
             hybrid = topo.dp_replicate > 1 and topo.dp_shard > 1
-            if self.config.shard_parameters and (topo.ep > 1 or topo.pp > 1 or hybrid):
-                raise NotImplementedError("shard_parameters composes with data, tensor and "
-                                          "context parallelism (no ep / pp, no hybrid sharding)")
+            if self.config.shard_parameters and (topo.ep > 1 or topo.pp > 1):
+                raise NotImplementedError("shard_parameters composes with data (plain or hybrid), "
+                                          "tensor and context parallelism, not with ep / pp")
             self._strategy = FSDPStrategy(fused=fused, init_sync=not composed,
                                           shard_parameters=self.config.shard_parameters)
             base_size = topo.dp_shard if hybrid else topo.dp_world_size

@@ -76,7 +76,9 @@ class FSDPStrategy(BaseStrategy):
         if self.shard_parameters:
             from ohara_b200.parallel.param_shard import shard_llama
 
-            shard_llama(module, process_group, solo=self.solo)
+            shard_llama(module, process_group, solo=self.solo,
+                        replicate_group=self.replicate_group,
+                        replicate_world=self.replicate_world)
         return module
 
     def setup_optimizer(self, optimizer, module: nn.Module | None = None):

@@ -329,7 +329,7 @@ for _ in range(3):
 
 engine = OharaEngine(EngineConfig(
     strategy=StrategyType.FSDP, shard_parameters=SHARD, context_parallel_mode="ulysses",
-    activation_checkpointing=RECOMPUTE, parallel=ParallelConfig(tp=TP, cp=CP),
+    activation_checkpointing=RECOMPUTE, parallel=ParallelConfig(tp=TP, cp=CP, dp_replicate=REPLICAS),
     tensor_parallel=TensorParallelPlan.llama_default(TP) if TP > 1 else TensorParallelPlan()))
 model = Llama(cfg); model.load_state_dict(state)
 model = engine.prepare(model)
@@ -357,20 +357,22 @@ engine.close()
 """
 
 
-@pytest.mark.parametrize("world,tp,cp,shard,recompute", [
-    (4, 2, 1, True, False), (4, 1, 2, True, False), (2, 2, 1, True, False),
-    (4, 2, 1, True, True),      # sharded parameters + recomputed blocks under tensor parallelism
-    (2, 2, 1, False, True),     # activation checkpointing with tensor-parallel collectives inside
-    (2, 1, 2, False, True),     # ... and with the all-to-alls of context parallelism inside
+@pytest.mark.parametrize("world,tp,cp,shard,recompute,replicas", [
+    (4, 2, 1, True, False, 1), (4, 1, 2, True, False, 1), (2, 2, 1, True, False, 1),
+    (4, 1, 1, True, False, 2),  # hybrid sharding: two replicas of a two-way sharded model
+    (4, 2, 1, True, True, 1),   # sharded parameters + recomputed blocks under tensor parallelism
+    (2, 2, 1, False, True, 1),  # activation checkpointing with tensor-parallel collectives inside
+    (2, 1, 2, False, True, 1),  # ... and with the all-to-alls of context parallelism inside
 ])
 def test_sharded_parameters_compose_with_tensor_and_context_parallelism(tmp_path, world, tp, cp,
-                                                                        shard, recompute):
+                                                                        shard, recompute, replicas):
     """The units are this rank's tensor shards, sharded over its data- and context-parallel
     peers; the clipped global norm counts tensor shards once each. Recomputed blocks repeat their
     collectives in the backward pass, on every rank at the same point."""
     path = tmp_path / "worker.py"
     path.write_text(textwrap.dedent(COMPOSED_WORKER).replace("TP", str(tp)).replace("CP", str(cp))
-                    .replace("SHARD", str(shard)).replace("RECOMPUTE", str(recompute)))
+                    .replace("SHARD", str(shard)).replace("RECOMPUTE", str(recompute))
+                    .replace("REPLICAS", str(replicas)))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(31700 + os.getpid() % 150), str(path)]
