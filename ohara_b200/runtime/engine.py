@@ -883,13 +883,68 @@ class OharaEngine:
             if key not in payload:
                 continue
             sharding = getattr(obj, "_param_sharding", None)
-            if sharding is not None:  # parameters sharded per block: load through the gather
-                sharding.load_full_state_dict(obj, payload[key])
+            if isinstance(obj, torch.nn.Module):
+                # checkpoints hold whole tensors (``full_state_dict``): cut out what this rank
+                # keeps of tensor-parallel matrices and expert stacks
+                local = self._local_slice_of_state(obj, payload[key])
+                if sharding is not None:  # parameters sharded per block: load through the gather
+                    sharding.load_full_state_dict(obj, local)
+                else:
+                    obj.load_state_dict(local)
             elif hasattr(obj, "load_state_dict"):
-                obj.load_state_dict(payload[key])
+                saved = payload[key]
+                if isinstance(saved, dict) and saved.get("model_parallel"):
+                    topo = self.topology
+                    if (saved["tp"], saved["ep"]) != (topo.tp, topo.ep):
+                        raise ValueError(
+                            f"optimizer state of a tp={saved['tp']} ep={saved['ep']} run cannot be "
+                            f"loaded into tp={topo.tp} ep={topo.ep}")
+                    saved = saved["states"][(topo.tp_rank, topo.ep_rank)]
+                obj.load_state_dict(saved)
             else:
                 state[key] = payload[key]
         return payload
+
+    def optimizer_state_dict(self, optimizer: Optimizer) -> dict[str, Any]:
+        """``optimizer.state_dict()`` for a checkpoint that one rank writes (collective). Ranks
+        with different tensor-parallel or expert-parallel coordinates hold optimizer state for
+        different shards, so their states are collected, one per coordinate (from the first
+        data-parallel replica of each); :meth:`load` hands every rank its own again."""
+        state = optimizer.state_dict()
+        topo = self.topology
+        if not self.launched or not (topo.tp_enabled or topo.ep > 1):
+            return state
+        mine = (topo.tp_rank, topo.ep_rank)
+        first_replica = topo.dp_rank == 0 and topo.cp_rank == 0
+        gathered: list[Any] = [None] * topo.world_size
+        dist.all_gather_object(gathered, (mine, state if first_replica else None))
+        states = {coordinate: entry for coordinate, entry in gathered if entry is not None}
+        return {"model_parallel": True, "tp": topo.tp, "ep": topo.ep, "states": states}
+
+    def _local_slice_of_state(self, module: torch.nn.Module,
+                              state: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+        """The inverse of :meth:`full_state_dict` for one rank: tensor-parallel parameters keep
+        their ``1 / tp`` slice along the sharded dimension, expert-parallel stacks their
+        ``E / ep`` experts; everything else is passed through. Tensors that already have the
+        local shape are left alone, so a state dict saved from a sharded module loads too."""
+        inner = module.module if hasattr(module, "module") else module
+        topo = self.topology
+        if not (topo.tp_enabled or getattr(self, "_expert_parallel", False)):
+            return state
+        local = dict(state)
+        for name, param in inner.named_parameters():
+            tensor = state.get(name)
+            if tensor is None or tuple(tensor.shape) == tuple(param.shape):
+                continue
+            dim = getattr(param, "tensor_parallel_dim", None)
+            if dim is not None and tensor.shape[dim] == param.shape[dim] * topo.tp:
+                width = param.shape[dim]
+                tensor = tensor.narrow(dim, topo.tp_rank * width, width)
+            if getattr(param, "expert_parallel", False) and tensor.shape[0] == param.shape[0] * topo.ep:
+                count = param.shape[0]
+                tensor = tensor.narrow(0, topo.ep_rank * count, count)
+            local[name] = tensor
+        return local
 
     def log_dict(self, payload: dict[str, Any], step: int | None = None) -> None:
         if not self.is_global_zero:

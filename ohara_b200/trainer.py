@@ -540,7 +540,9 @@ class Trainer:
         model_state = full_state(self.model) if callable(full_state) else self.model.state_dict()
         state = {
             "model": model_state,
-            "optimizer": self.optimizer.state_dict(),
+            "optimizer": (self.engine.optimizer_state_dict(self.optimizer)
+                          if callable(getattr(self.engine, "optimizer_state_dict", None))
+                          else self.optimizer.state_dict()),
             "idx": idx,
             "lr": lr,
             "train_step_loss": step_loss,

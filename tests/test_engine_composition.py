@@ -354,3 +354,48 @@ def test_tensor_parallel_ranks_without_data_parallel_peers_are_not_treated_as_re
             2, tmp_path, port_base=29900,
         )
         assert "TP_ONLY_OK" in out
+
+
+import pytest
+
+
+@pytest.mark.parametrize("shard_parameters", [False, True])
+def test_checkpoint_of_a_tensor_parallel_run_resumes_in_a_fresh_engine_model(tmp_path, shard_parameters):
+    """``engine.save`` writes whole tensors; ``engine.load`` cuts this rank's tensor-parallel slices
+    back out, so a run resumed after two steps ends where four uninterrupted steps end."""
+    out = _run(
+        f"""
+        import os, tempfile
+        solo = reference(lambda m: build_adamw(m, learning_rate=0.02, weight_decay=0.1), steps=4)
+
+        def make():
+            model = Llama(cfg); model.load_state_dict(state)
+            model = engine.prepare(model)
+            (opt,) = engine.prepare_optimizers(build_adamw(model, learning_rate=0.02, weight_decay=0.1))
+            loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=4))
+            trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=1,
+                              max_iters=2, eval_iters=0, save_ckpt_iters=0)
+            return model, opt, trainer
+
+        engine = OharaEngine(EngineConfig(strategy=StrategyType.FSDP, parallel=ParallelConfig(tp=2),
+                                          shard_parameters={shard_parameters},
+                                          tensor_parallel=TensorParallelPlan.llama_default(2)))
+        model, opt, trainer = make()
+        trainer.train()
+        folder = engine.broadcast(tempfile.mkdtemp() if dist.get_rank() == 0 else None)
+        path = os.path.join(folder, "ckpt.pt")
+        engine.save(path, trainer.checkpoint_state(2, 0.02, 0.0))
+        model, opt, trainer = make()                      # fresh weights and optimizer state
+        engine.load(path, {{"model": model, "optimizer": opt}})
+        trainer.train()                                   # two more steps on the same batches
+        full = engine.full_state_dict(model)
+        for name, value in solo.state_dict().items():
+            assert full[name].shape == value.shape, name
+            assert torch.allclose(full[name], value, atol=3e-5), (name, (full[name] - value).abs().max())
+        if dist.get_rank() == 0:
+            print("TP_RESUME_OK")
+        engine.close()
+        """,
+        4, tmp_path, port_base=30100,
+    )
+    assert "TP_RESUME_OK" in out
