@@ -73,6 +73,14 @@ _REDUCE_OPS = {
 }
 
 
+def _stage_to_model_name(name: str, first_layer: int) -> str:
+    """``layers.<i>.…`` of a pipeline stage is ``layers.<first_layer + i>.…`` of the model."""
+    if name.startswith("layers."):
+        index, rest = name.split(".", 2)[1:]
+        return f"layers.{int(index) + first_layer}.{rest}"
+    return name
+
+
 class OharaEngine:
     def __init__(self, config: EngineConfig | None = None, loggers: list[Any] | None = None) -> None:
         self.config = config or EngineConfig()
@@ -832,10 +840,14 @@ class OharaEngine:
         sync = getattr(getattr(self, "_sharded_optimizer", None), "sync_master_weights", None)
         if callable(sync):
             sync()
+        stage = getattr(inner, "stage", None) if getattr(inner, "pipeline_stage", False) else None
+        source = stage if stage is not None else inner
         if self.topology.tp_enabled:
-            state = gather_tensor_parallel_state(inner, self._groups.get("tp"))
+            state = gather_tensor_parallel_state(source, self._groups.get("tp"))
         else:
-            state = dict(inner.state_dict())
+            state = dict(source.state_dict())
+        if stage is not None:
+            return self._gather_pipeline_state(stage, state)
         if getattr(self, "_expert_parallel", False):
             # routed experts: every rank of the expert-parallel group holds E / ep of them
             group, world = self._groups.get("ep"), self.topology.ep
@@ -889,21 +901,41 @@ class OharaEngine:
                 local = self._local_slice_of_state(obj, payload[key])
                 if sharding is not None:  # parameters sharded per block: load through the gather
                     sharding.load_full_state_dict(obj, local)
+                elif getattr(obj, "pipeline_stage", False):
+                    obj.stage.load_state_dict(local)
                 else:
                     obj.load_state_dict(local)
             elif hasattr(obj, "load_state_dict"):
                 saved = payload[key]
                 if isinstance(saved, dict) and saved.get("model_parallel"):
                     topo = self.topology
-                    if (saved["tp"], saved["ep"]) != (topo.tp, topo.ep):
+                    layout = (saved["tp"], saved["ep"], saved.get("pp", 1))
+                    if layout != (topo.tp, topo.ep, topo.pp):
                         raise ValueError(
-                            f"optimizer state of a tp={saved['tp']} ep={saved['ep']} run cannot be "
-                            f"loaded into tp={topo.tp} ep={topo.ep}")
-                    saved = saved["states"][(topo.tp_rank, topo.ep_rank)]
+                            f"optimizer state of a (tp, ep, pp) = {layout} run cannot be loaded "
+                            f"into (tp, ep, pp) = {(topo.tp, topo.ep, topo.pp)}")
+                    saved = saved["states"][(topo.tp_rank, topo.ep_rank, topo.pp_rank)]
                 obj.load_state_dict(saved)
             else:
                 state[key] = payload[key]
         return payload
+
+    def _gather_pipeline_state(self, stage, state: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+        """Whole-model state dict from the stages' ones (collective over the pipeline group):
+        block indices become the model's own, the embedding comes from the first stage, the final
+        norm and the output projection from the last, the rotary tables from this stage."""
+        begin, _ = stage.layer_range
+        renamed = {}
+        for name, tensor in state.items():
+            renamed[_stage_to_model_name(name, begin)] = tensor.detach().cpu()
+        parts: list[Any] = [None] * self.topology.pp
+        dist.all_gather_object(parts, renamed, group=self._groups.get("pp"))
+        merged: dict[str, torch.Tensor] = {}
+        for part in parts:
+            merged.update(part)
+        merged["freq_cos"] = stage.freq_cos.detach().cpu()
+        merged["freq_sin"] = stage.freq_sin.detach().cpu()
+        return merged
 
     def optimizer_state_dict(self, optimizer: Optimizer) -> dict[str, Any]:
         """``optimizer.state_dict()`` for a checkpoint that one rank writes (collective). Ranks
@@ -912,14 +944,15 @@ class OharaEngine:
         data-parallel replica of each); :meth:`load` hands every rank its own again."""
         state = optimizer.state_dict()
         topo = self.topology
-        if not self.launched or not (topo.tp_enabled or topo.ep > 1):
+        if not self.launched or not (topo.tp_enabled or topo.ep > 1 or topo.pp > 1):
             return state
-        mine = (topo.tp_rank, topo.ep_rank)
+        mine = (topo.tp_rank, topo.ep_rank, topo.pp_rank)
         first_replica = topo.dp_rank == 0 and topo.cp_rank == 0
         gathered: list[Any] = [None] * topo.world_size
         dist.all_gather_object(gathered, (mine, state if first_replica else None))
         states = {coordinate: entry for coordinate, entry in gathered if entry is not None}
-        return {"model_parallel": True, "tp": topo.tp, "ep": topo.ep, "states": states}
+        return {"model_parallel": True, "tp": topo.tp, "ep": topo.ep, "pp": topo.pp,
+                "states": states}
 
     def _local_slice_of_state(self, module: torch.nn.Module,
                               state: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
@@ -929,6 +962,13 @@ class OharaEngine:
         local shape are left alone, so a state dict saved from a sharded module loads too."""
         inner = module.module if hasattr(module, "module") else module
         topo = self.topology
+        if getattr(inner, "pipeline_stage", False):
+            # keep what this stage holds, under the stage's own (local) block indices
+            stage = inner.stage
+            begin, _ = stage.layer_range
+            wanted = {_stage_to_model_name(name, begin): name for name in stage.state_dict()}
+            state = {wanted[name]: tensor for name, tensor in state.items() if name in wanted}
+            inner = stage
         if not (topo.tp_enabled or getattr(self, "_expert_parallel", False)):
             return state
         local = dict(state)

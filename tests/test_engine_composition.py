@@ -399,3 +399,49 @@ def test_checkpoint_of_a_tensor_parallel_run_resumes_in_a_fresh_engine_model(tmp
         4, tmp_path, port_base=30100,
     )
     assert "TP_RESUME_OK" in out
+
+
+def test_checkpoint_of_a_pipeline_run_is_a_whole_model_and_resumes(tmp_path):
+    """pp=2 x dp=2: the saved model state has the whole model's keys (it loads into a plain
+    Llama), the optimizer state is kept per stage, and a fresh engine model resumes from it."""
+    out = _run(
+        """
+        import os, tempfile
+        from ohara_b200.runtime import PipelinePlan
+        solo = reference(lambda m: build_adamw(m, learning_rate=0.02, weight_decay=0.1), steps=4)
+        half = reference(lambda m: build_adamw(m, learning_rate=0.02, weight_decay=0.1), steps=2)
+
+        def make():
+            model = Llama(cfg); model.load_state_dict(state)
+            model = engine.prepare(model)
+            (opt,) = engine.prepare_optimizers(build_adamw(model, learning_rate=0.02, weight_decay=0.1))
+            loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=4))
+            trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=1,
+                              max_iters=2, eval_iters=0, save_ckpt_iters=0)
+            return model, opt, trainer
+
+        engine = OharaEngine(EngineConfig(strategy=StrategyType.FSDP, parallel=ParallelConfig(pp=2),
+                                          pipeline=PipelinePlan(degree=2, micro_batch_size=2)))
+        model, opt, trainer = make()
+        trainer.train()
+        full = engine.full_state_dict(model)
+        assert set(full) == set(half.state_dict()), set(full) ^ set(half.state_dict())
+        plain = Llama(cfg); plain.load_state_dict(full)              # loads into the plain model
+        for name, value in half.state_dict().items():
+            assert torch.allclose(full[name], value, atol=3e-5), name
+        folder = engine.broadcast(tempfile.mkdtemp() if dist.get_rank() == 0 else None)
+        path = os.path.join(folder, "ckpt.pt")
+        engine.save(path, trainer.checkpoint_state(2, 0.02, 0.0))
+        model, opt, trainer = make()
+        engine.load(path, {"model": model, "optimizer": opt})
+        trainer.train()
+        full = engine.full_state_dict(model)
+        for name, value in solo.state_dict().items():
+            assert torch.allclose(full[name], value, atol=3e-5), (name, (full[name] - value).abs().max())
+        if dist.get_rank() == 0:
+            print("PP_RESUME_OK")
+        engine.close()
+        """,
+        4, tmp_path, port_base=30300,
+    )
+    assert "PP_RESUME_OK" in out
