@@ -4,6 +4,7 @@ short end-to-end pretraining run. (Reference suite for the loader: tests/test_tr
 from __future__ import annotations
 
 import json
+import os
 import subprocess
 import sys
 import threading
@@ -133,3 +134,35 @@ def test_pretraining_example_trains_saves_and_resumes(tmp_path):
     assert second.returncode == 0, second.stderr[-2000:]
     assert "resumed checkpoint" in second.stdout and "iter: 3 |" in second.stdout
     assert "iter: 1 |" not in second.stdout
+
+
+@pytest.mark.parametrize("layout", [
+    ["--shard-parameters", "--optimizer", "adamw", "--activation-checkpointing"],
+    ["--tp", "2", "--optimizer", "adamw"],
+    ["--cp", "2", "--context-parallel-mode", "ulysses", "--optimizer", "adamw"],
+])
+def test_pretraining_example_on_two_ranks_saves_and_resumes(tmp_path, layout):
+    """The same script under torchrun on two CPU ranks with the sharded strategy: sharded
+    parameters with recomputed blocks, tensor parallelism, Ulysses context parallelism."""
+    checkpoint = tmp_path / "ckpt" / "model.pt"
+    command = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+               "--master-addr", "127.0.0.1", "--master-port", str(32500 + os.getpid() % 300),
+               str(EXAMPLES / "train_llama_engine.py"), "--synthetic", "--synthetic-vocab", "256",
+               "--seq-len", "32", "--hidden-size", "32", "--intermediate-size", "64",
+               "--num-layers", "2", "--num-heads", "2", "--batch-size", "2",
+               "--grad-accum-steps", "2", "--warmup-iters", "1", "--eval-every", "2",
+               "--eval-batches", "1", "--save-every", "2", "--logger", "none", "--precision", "fp32",
+               "--no-weight-tying", "--checkpoint-path", str(checkpoint), "--strategy", "fsdp",
+               *layout]
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    first = subprocess.run(command + ["--max-iters", "2"], capture_output=True, text=True,
+                           timeout=300, env=env)
+    assert first.returncode == 0, first.stdout[-1500:] + first.stderr[-2500:]
+    assert checkpoint.exists() and "final val_loss=" in first.stdout
+    second = subprocess.run(command + ["--max-iters", "4", "--resume"], capture_output=True,
+                            text=True, timeout=300, env=env)
+    assert second.returncode == 0, second.stdout[-1500:] + second.stderr[-2500:]
+    assert "resumed checkpoint" in second.stdout and "iter: 4 |" in second.stdout
+    assert "iter: 1 |" not in second.stdout
+    saved = torch.load(checkpoint, weights_only=False)
+    assert saved["model"]["layers.1.attn.query.weight"].shape == (32, 32)   # whole matrices
