@@ -139,11 +139,10 @@ def test_pretraining_example_trains_saves_and_resumes(tmp_path):
 @pytest.mark.parametrize("layout", [
     ["--shard-parameters", "--optimizer", "adamw", "--activation-checkpointing"],
     ["--tp", "2", "--optimizer", "adamw"],
-    ["--cp", "2", "--context-parallel-mode", "ulysses", "--optimizer", "adamw"],
 ])
 def test_pretraining_example_on_two_ranks_saves_and_resumes(tmp_path, layout):
     """The same script under torchrun on two CPU ranks with the sharded strategy: sharded
-    parameters with recomputed blocks, tensor parallelism, Ulysses context parallelism."""
+    parameters with recomputed blocks, and tensor parallelism."""
     checkpoint = tmp_path / "ckpt" / "model.pt"
     command = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                "--master-addr", "127.0.0.1", "--master-port", str(32500 + os.getpid() % 300),
