@@ -16,7 +16,6 @@ the reference leaves that as a TODO (griffin_and_hawk.py:86).
 
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 
 import torch
