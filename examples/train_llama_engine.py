@@ -141,7 +141,10 @@ def parse_args() -> argparse.Namespace:
     run.add_argument("--shard-parameters", action="store_true",
                      help="with --strategy fsdp: shard the parameters per transformer block "
                           "(gathered just before a block runs) instead of the optimizer state "
-                          "alone; AdamW only")
+                          "alone")
+    run.add_argument("--shard-parameters-layout", choices=["auto", "even", "matrix"], default="auto",
+                     help="even: equal ranges (AdamW); matrix: whole matrices at one owner (Muon); "
+                          "auto picks by --optimizer")
     run.add_argument("--activation-checkpointing", action="store_true",
                      help="recompute every block in the backward pass instead of keeping its "
                           "activations (less memory, about a third more compute)")
@@ -331,6 +334,8 @@ def run() -> None:
         tensor_parallel=TensorParallelPlan.llama_default(args.tp, args.sequence_parallel),
         activation_checkpointing=args.activation_checkpointing,
         shard_parameters=args.shard_parameters,
+        shard_parameters_layout=(args.shard_parameters_layout if args.shard_parameters_layout != "auto"
+                                 else ("even" if args.optimizer == "adamw" else "matrix")),
         context_parallel_mode=args.context_parallel_mode,
         fault_tolerance=FaultToleranceConfig(
             heartbeat_interval_s=args.heartbeat_interval, heartbeat_timeout_s=args.heartbeat_timeout,

@@ -25,12 +25,20 @@ The collectives are the process group's ``all_gather_into_tensor`` / ``reduce_sc
 (NCCL on GPUs, gloo on CPUs, where the reduce-scatter is an all-reduce plus a slice). The reference
 has nothing of the kind (``dp_shard`` is arithmetic only: ohara/runtime/topology.py:33-38).
 
+Two layouts. ``"even"`` cuts a unit's concatenated parameters into equal ranges wherever the cut
+falls (least padding; element-wise optimizers such as AdamW). ``"matrix"`` places every parameter
+of a block inside one rank's range, so the owner of a matrix holds all of it and whole-matrix
+algorithms (Muon, AdamH / MuonH) run there without any gather, at the price of ranges as large as
+the fullest rank's share (up to about 2x padding for a block over 8 ranks); the embedding and the
+head, which those recipes update element-wise, are still cut evenly.
+
 Limits: composes with tensor and context parallelism (the units are then this rank's tensor
 shards, sharded over its data-parallel and context-parallel peers) and with hybrid sharding, not
-with expert or pipeline parallelism; element-wise optimizers only (AdamW; a whole-matrix algorithm would need each matrix on one rank), fp32 on the
-wire. Checkpoints (the model's full state dict plus the optimizer state stored per unit as whole
-vectors) reload at any world size. A resharded parameter keeps its shape, ``numel()`` and ``ndim`` but reads as one repeated
-element: take state dicts through :meth:`ParameterSharding.full_state_dict`.
+with expert or pipeline parallelism; fp32 on the wire. Checkpoints (the model's full state dict
+plus the optimizer state stored per unit as whole vectors and per matrix for the whole-matrix
+groups) reload at any world size. A resharded parameter keeps its shape, ``numel()`` and ``ndim``
+but reads as one repeated element: take state dicts through
+:meth:`ParameterSharding.full_state_dict`.
 """
 
 from __future__ import annotations
@@ -50,20 +58,38 @@ class _Unit:
     """One all-gather / reduce-scatter granule."""
 
     def __init__(self, name: str, params: list[nn.Parameter], world: int, rank: int,
-                 reshard_after_forward: bool) -> None:
+                 reshard_after_forward: bool, whole_tensors: bool = False) -> None:
+        """``whole_tensors``: lay the unit out so that every parameter lies inside ONE rank's
+        region (largest first, each to the rank with the least so far) instead of cutting the
+        concatenation into equal ranges. Regions are then as large as the fullest rank's share,
+        which costs padding (up to about 2x for a transformer block over 8 ranks) and buys
+        whole matrices at their owners, as Muon needs."""
         self.name = name
         self.params = params
         self.reshard_after_forward = reshard_after_forward
+        self.whole_tensors = whole_tensors and world > 1
         self.shapes = [tuple(p.shape) for p in params]
         self.numels = [p.numel() for p in params]
-        self.offsets: list[int] = []
-        cursor = 0
-        for n in self.numels:
-            self.offsets.append(cursor)
-            cursor += (n + ALIGN - 1) // ALIGN * ALIGN
-        chunk = world * ALIGN
-        self.total = max((cursor + chunk - 1) // chunk * chunk, chunk)
-        self.region = self.total // world
+        aligned = [(n + ALIGN - 1) // ALIGN * ALIGN for n in self.numels]
+        if self.whole_tensors:
+            load = [0] * world
+            placed: list[tuple[int, int]] = [(0, 0)] * len(params)
+            for index in sorted(range(len(params)), key=lambda i: (-aligned[i], i)):
+                owner = min(range(world), key=lambda r: (load[r], r))
+                placed[index] = (owner, load[owner])
+                load[owner] += aligned[index]
+            self.region = max(max(load), ALIGN)
+            self.total = self.region * world
+            self.offsets = [owner * self.region + at for owner, at in placed]
+        else:
+            self.offsets = []
+            cursor = 0
+            for size in aligned:
+                self.offsets.append(cursor)
+                cursor += size
+            chunk = world * ALIGN
+            self.total = max((cursor + chunk - 1) // chunk * chunk, chunk)
+            self.region = self.total // world
         device = params[0].device
         flat = torch.zeros(self.total, device=device, dtype=torch.float32)
         for p, off, n in zip(params, self.offsets, self.numels):
@@ -116,8 +142,10 @@ class ParameterSharding:
 
     def __init__(self, units: Iterable[tuple[str, list[nn.Parameter]]], group=None, *,
                  keep_gathered: Iterable[str] = (), prefetch: bool = True,
-                 solo: bool = False, replicate_group=None, replicate_world: int = 1) -> None:
-        """``solo``: shard over nobody although a process group exists (every other rank of the
+                 solo: bool = False, replicate_group=None, replicate_world: int = 1,
+                 whole_tensor_units: Iterable[str] = ()) -> None:
+        """``whole_tensor_units``: names of units laid out with every parameter inside one rank's
+        region (see :class:`_Unit`). ``solo``: shard over nobody although a process group exists (every other rank of the
         job holds different tensors, e.g. the tensor-parallel peers). ``replicate_group`` (of
         ``replicate_world`` ranks): hybrid sharding, the ranks that hold the same shard as this
         one in other replica groups; reduced gradient shards are averaged over it."""
@@ -129,6 +157,7 @@ class ParameterSharding:
         self.rank = dist.get_rank(group) if distributed else 0
         self.prefetch = prefetch
         keep = set(keep_gathered)
+        whole = set(whole_tensor_units)
         seen: set[int] = set()
         self.units: list[_Unit] = []
         self.by_name: dict[str, _Unit] = {}
@@ -138,7 +167,8 @@ class ParameterSharding:
             if not fresh:
                 continue
             seen.update(id(p) for p in fresh)
-            unit = _Unit(name, fresh, self.world, self.rank, name not in keep)
+            unit = _Unit(name, fresh, self.world, self.rank, name not in keep,
+                         whole_tensors=name in whole)
             unit.index = len(self.units)
             self.units.append(unit)
             self.by_name[name] = unit
@@ -332,7 +362,8 @@ class ParameterSharding:
 
 
 def shard_llama(model: nn.Module, group=None, prefetch: bool = True, solo: bool = False,
-                replicate_group=None, replicate_world: int = 1) -> ParameterSharding:
+                replicate_group=None, replicate_world: int = 1,
+                layout: str = "even") -> ParameterSharding:
     """Cut a Llama into units (embedding, blocks, final norm + output projection), shard them over
     ``group`` and attach the result as ``model._param_sharding``; the model's forward pass then
     gathers and releases the units as it goes."""
@@ -365,8 +396,14 @@ def shard_llama(model: nn.Module, group=None, prefetch: bool = True, solo: bool 
     missing = [name for name, p in model.named_parameters() if id(p) not in covered]
     if missing:
         raise ValueError(f"parameters outside every unit: {missing[:4]}")
+    if layout not in ("even", "matrix"):
+        raise ValueError(f"unknown parameter-sharding layout {layout!r} (even or matrix)")
+    # "matrix": the blocks keep every matrix whole at one owner (what Muon needs); the embedding
+    # and the head, which element-wise algorithms update, are still cut evenly
+    whole = [name for name, _ in units if name.startswith("layers.")] if layout == "matrix" else []
     sharding = ParameterSharding(units, group, keep_gathered=keep, prefetch=prefetch, solo=solo,
-                                 replicate_group=replicate_group, replicate_world=replicate_world)
+                                 replicate_group=replicate_group, replicate_world=replicate_world,
+                                 whole_tensor_units=whole)
     sharding.tied = tied
     model._param_sharding = sharding
     return sharding
@@ -377,7 +414,8 @@ class ParameterShardedOptimizer(Optimizer):
 
     ``optimizer`` was built on the model's parameters; its groups (learning rate, weight decay
     ...) are kept as the user-visible ``param_groups`` and mirrored onto a local optimizer of the
-    same class over 1-D views of the master shards. Element-wise algorithms only."""
+    same class over views of the master shards: 1-D ranges for element-wise groups, whole
+    matrices at their owners for whole-matrix groups (which need the ``"matrix"`` layout)."""
 
     def __init__(self, optimizer: Optimizer, sharding: ParameterSharding,
                  norm_groups: dict[str, Any] | None = None) -> None:
@@ -401,15 +439,34 @@ class ParameterShardedOptimizer(Optimizer):
         self.state = optimizer.state
         local_groups = []
         self._spans: list[list[tuple[_Unit, int, int, nn.Parameter]]] = []
+        self._whole_matrix_group: list[bool] = []
         for group in self.param_groups:
-            if group.get("kind") == "muon" or group.get("hypersphere", False):
-                raise NotImplementedError(
-                    "parameter sharding cuts matrices at arbitrary elements: use an element-wise "
-                    "optimizer (AdamW), or the sharded optimizer without parameter sharding")
+            whole_matrices = group.get("kind") == "muon" or bool(group.get("hypersphere", False))
+            self._whole_matrix_group.append(whole_matrices)
             wanted = {id(p) for p in group["params"]}
             spans: list[tuple[_Unit, int, int, nn.Parameter]] = []
             for unit in sharding.units:
                 lo, hi = sharding.rank * unit.region, (sharding.rank + 1) * unit.region
+                if whole_matrices:
+                    # the owner of a matrix updates all of it: every matrix of the group must lie
+                    # inside one rank's region (the "matrix" layout of the blocks)
+                    for p, off, n, shape in zip(unit.params, unit.offsets, unit.numels,
+                                                unit.shapes):
+                        if id(p) not in wanted:
+                            continue
+                        if off // unit.region != (off + n - 1) // unit.region:
+                            raise NotImplementedError(
+                                "a whole-matrix algorithm (Muon, AdamH / MuonH) needs every "
+                                "matrix at one owner: shard the parameters with the 'matrix' "
+                                "layout (EngineConfig(shard_parameters_layout='matrix'))")
+                        if lo <= off < hi:
+                            shard = nn.Parameter(unit.master[off - lo : off - lo + n].view(shape),
+                                                 requires_grad=True)
+                            if hasattr(p, "tensor_parallel_dim"):  # tensor-parallel Muon needs it
+                                shard.tensor_parallel_dim = p.tensor_parallel_dim
+                            shard._matrix_id = (unit.name, unit.offsets.index(off))
+                            spans.append((unit, off - lo, off - lo + n, shard))
+                    continue
                 pieces: list[list[int]] = []
                 for p, off, n in zip(unit.params, unit.offsets, unit.numels):
                     if id(p) not in wanted:
@@ -441,6 +498,9 @@ class ParameterShardedOptimizer(Optimizer):
                 self.local = cls(local_groups)
             except TypeError:
                 self.local = cls(local_groups, **dict(optimizer.defaults))
+            for name in ("tensor_parallel_group", "tensor_parallel_world"):
+                if hasattr(optimizer, name):
+                    setattr(self.local, name, getattr(optimizer, name))
 
     # -- step ------------------------------------------------------------------------------------
     def _sync_hyperparameters(self) -> None:
@@ -465,7 +525,7 @@ class ParameterShardedOptimizer(Optimizer):
         if self.local is not None:
             for spans in self._spans:
                 for unit, a, b, shard in spans:
-                    shard.grad = (unit.grad[a:b] if unit.grad is not None
+                    shard.grad = (unit.grad[a:b].view_as(shard) if unit.grad is not None
                                   else torch.zeros_like(shard))
             self.local.step()
             for spans in self._spans:
@@ -519,7 +579,18 @@ class ParameterShardedOptimizer(Optimizer):
         themselves travel in the model's full state dict."""
         sharding = self.sharding
         mine = []
+        matrices: dict[tuple[str, int], dict[str, Tensor]] = {}
         for index, spans in enumerate(self._spans):
+            if self._whole_matrix_group[index]:
+                # one stacked buffer per state entry, keyed on the group's first matrix, one row
+                # per owned matrix in group order: store the rows per matrix
+                if spans and self.local is not None:
+                    stacked = self.local.state.get(spans[0][3], {})
+                    for row, (_, _, _, shard) in enumerate(spans):
+                        matrices[shard._matrix_id] = {
+                            k: v[row].detach().cpu() for k, v in stacked.items()
+                            if torch.is_tensor(v) and v.dim() > 0 and v.shape[0] == len(spans)}
+                continue
             for unit, a, b, shard in spans:
                 state = self.local.state.get(shard, {}) if self.local is not None else {}
                 vectors = {k: v.detach().reshape(-1).cpu() for k, v in state.items()
@@ -531,6 +602,9 @@ class ParameterShardedOptimizer(Optimizer):
         if sharding.world > 1:
             everyone = [None] * sharding.world
             dist.all_gather_object(everyone, mine, group=sharding.group)
+            parts: list[Any] = [None] * sharding.world
+            dist.all_gather_object(parts, matrices, group=sharding.group)
+            matrices = {key: value for part in parts for key, value in part.items()}
         units: dict[str, dict[str, Tensor]] = {}
         scalars_of_group: dict[int, dict[str, Any]] = {}
         for pieces in everyone:
@@ -545,6 +619,7 @@ class ParameterShardedOptimizer(Optimizer):
         return {
             "param_sharded": True,
             "units": units,
+            "matrices": matrices,
             "group_scalars": scalars_of_group,
             "param_groups": [{k: v for k, v in g.items() if k != "params"}
                              for g in self.param_groups],
@@ -555,6 +630,15 @@ class ParameterShardedOptimizer(Optimizer):
             raise ValueError("not a parameter-sharded optimizer state")
         sharding = self.sharding
         for index, spans in enumerate(self._spans):
+            if self._whole_matrix_group[index]:
+                saved_rows = [state_dict.get("matrices", {}).get(shard._matrix_id)
+                              for _, _, _, shard in spans]
+                if spans and all(saved_rows) and self.local is not None:
+                    first = spans[0][3]
+                    for key in saved_rows[0]:
+                        self.local.state[first][key] = torch.stack(
+                            [rows[key] for rows in saved_rows]).to(first.device)
+                continue
             scalars = state_dict["group_scalars"].get(index, {})
             for unit, a, b, shard in spans:
                 saved = state_dict["units"].get(unit.name)

@@ -69,3 +69,5 @@ class EngineConfig:
     # StrategyType.FSDP only: shard the parameters themselves per transformer block (gathered
     # just before a block runs, released after it) instead of the optimizer state alone.
     shard_parameters: bool = False
+    # "even": equal ranges (AdamW); "matrix": every matrix of a block whole at one owner (Muon)
+    shard_parameters_layout: str = "even"

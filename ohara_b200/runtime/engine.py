@@ -205,7 +205,8 @@ class OharaEngine:
                 raise NotImplementedError("shard_parameters composes with data (plain or hybrid), "
                                           "tensor and context parallelism, not with ep / pp")
             self._strategy = FSDPStrategy(fused=fused, init_sync=not composed,
-                                          shard_parameters=self.config.shard_parameters)
+                                          shard_parameters=self.config.shard_parameters,
+                                          shard_parameters_layout=self.config.shard_parameters_layout)
             base_size = topo.dp_shard if hybrid else topo.dp_world_size
             norm_groups = {}
             if topo.tp_enabled:

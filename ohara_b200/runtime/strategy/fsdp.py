@@ -32,10 +32,11 @@ class FSDPStrategy(BaseStrategy):
     name = "fsdp"
 
     def __init__(self, *, fused: bool = True, init_sync: bool = True,
-                 shard_parameters: bool = False) -> None:
+                 shard_parameters: bool = False, shard_parameters_layout: str = "even") -> None:
         self.fused = fused
         self.init_sync = init_sync
         self.shard_parameters = shard_parameters
+        self.shard_parameters_layout = shard_parameters_layout
         self.process_group = None
         self.device: torch.device | None = None
         self.replicate_group = None
@@ -78,7 +79,8 @@ class FSDPStrategy(BaseStrategy):
 
             shard_llama(module, process_group, solo=self.solo,
                         replicate_group=self.replicate_group,
-                        replicate_world=self.replicate_world)
+                        replicate_world=self.replicate_world,
+                        layout=self.shard_parameters_layout)
         return module
 
     def setup_optimizer(self, optimizer, module: nn.Module | None = None):

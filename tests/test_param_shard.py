@@ -110,15 +110,49 @@ def test_evaluation_pass_releases_the_blocks():
     assert all(u.full is None for u in sharding.units)
 
 
-def test_whole_matrix_optimizers_and_loop_moe_are_rejected():
+def test_loop_moe_is_rejected_and_muon_runs_on_one_process_with_either_layout():
     torch.manual_seed(0)
-    model = Llama(_config())
-    sharding = shard_llama(model)
-    with pytest.raises(NotImplementedError):
-        ParameterShardedOptimizer(build_muon_adamw(model), sharding)
     loop = Llama(_config(moe_num_experts=4, moe_experts_per_tok=2))
     with pytest.raises(NotImplementedError):
         shard_llama(loop)
+    with pytest.raises(ValueError):
+        shard_llama(Llama(_config()), layout="diagonal")
+    # one process owns everything, so whole-matrix groups are fine whatever the layout
+    tokens = torch.randint(0, 37, (4, 13))
+    base = Llama(_config())
+    plain = copy.deepcopy(base)
+    want = _train(plain.train(), build_muon_adamw(plain), tokens, 3)
+    for layout in ("even", "matrix"):
+        model = copy.deepcopy(base)
+        sharding = shard_llama(model, layout=layout)
+        optimizer = ParameterShardedOptimizer(build_muon_adamw(model), sharding)
+        got = _train(model.train(), optimizer, tokens, 3, finish=sharding.finish_backward)
+        assert got == pytest.approx(want, rel=1e-5, abs=1e-6)
+
+
+def test_matrix_layout_keeps_every_block_parameter_inside_one_region():
+    from ohara_b200.parallel.param_shard import _Unit
+
+    torch.manual_seed(0)
+    block = Llama(_config()).layers[0]
+    params = list(block.parameters())
+    for world in (2, 3, 8):
+        units = [_Unit("layers.0", params, world, rank, True, whole_tensors=True)
+                 for rank in range(world)]
+        unit = units[0]
+        assert unit.total == unit.region * world
+        spans = sorted((off, off + n) for off, n in zip(unit.offsets, unit.numels))
+        assert all(a_end <= b_begin for (_, a_end), (b_begin, _) in zip(spans, spans[1:]))  # disjoint
+        for off, n in zip(unit.offsets, unit.numels):
+            assert off // unit.region == (off + n - 1) // unit.region                   # one owner
+        # the masters of the ranks tile the flat vector
+        flat = torch.cat([u.master for u in units])
+        for p, off, n in zip(params, unit.offsets, unit.numels):
+            assert torch.equal(flat[off:off + n], p.detach().reshape(-1))
+        even = _Unit("layers.0", params, world, 0, True)
+        assert unit.total >= even.total
+        owners = {off // unit.region for off in unit.offsets}
+        assert len(owners) == min(world, len(params)) or world > len(params)
 
 
 def test_state_dict_round_trip_and_clipping():
@@ -379,3 +413,77 @@ def test_sharded_parameters_compose_with_tensor_and_context_parallelism(tmp_path
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "COMPOSED_OK" in proc.stdout
+
+
+MUON_WORKER = """
+import sys, torch, torch.distributed as dist
+from torch.utils.data import DataLoader, TensorDataset
+from ohara_b200.models.llama import Config, Llama
+from ohara_b200.runtime import EngineConfig, OharaEngine, ParallelConfig, StrategyType, TensorParallelPlan
+from ohara_b200.optimizer import build_muon_adamw
+from ohara_b200.trainer import Trainer
+from ohara_b200.lr_scheduler import Scheduler
+
+torch.manual_seed(0)
+cfg = Config(vocab_size=32, max_sequence_length=16, hidden_size=16, intermediate_size=24,
+             num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=3, dropout=0.0)
+ids = torch.randint(0, 32, (8, 17))
+dataset = TensorDataset(ids[:, :-1], ids[:, 1:])
+state = {k: v.clone() for k, v in Llama(cfg).state_dict().items()}
+
+def solo_after(steps):
+    solo = Llama(cfg); solo.load_state_dict(state)
+    opt = build_muon_adamw(solo)
+    for _ in range(steps):
+        loss = solo.loss_sum(ids[:, :-1], ids[:, 1:]) / ids[:, 1:].numel()
+        loss.backward(); opt.step(); opt.zero_grad()
+    return solo
+
+engine = OharaEngine(EngineConfig(
+    strategy=StrategyType.FSDP, shard_parameters=True, shard_parameters_layout="matrix",
+    parallel=ParallelConfig(tp=TP),
+    tensor_parallel=TensorParallelPlan.llama_default(TP) if TP > 1 else TensorParallelPlan()))
+
+def make():
+    model = Llama(cfg); model.load_state_dict(state)
+    model = engine.prepare(model)
+    (opt,) = engine.prepare_optimizers(build_muon_adamw(model))
+    dp = engine.data_parallel_world_size
+    loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=8 // dp))
+    trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=1,
+                      max_iters=2, eval_iters=0, save_ckpt_iters=0)
+    return model, opt, trainer
+
+def close_to(model, solo):
+    full = engine.full_state_dict(model)
+    for name, value in solo.state_dict().items():
+        assert torch.allclose(full[name], value, atol=5e-5), (name, (full[name] - value).abs().max())
+
+model, opt, trainer = make()
+assert any(group.get("kind") == "muon" for group in opt.param_groups)
+trainer.train()
+close_to(model, solo_after(2))
+engine.save(sys.argv[1], trainer.checkpoint_state(2, 0.02, 0.0))
+model, opt, trainer = make()
+engine.load(sys.argv[1], {"model": model, "optimizer": opt})
+trainer.train()
+close_to(model, solo_after(4))
+if dist.get_rank() == 0:
+    print("MUON_SHARDED_OK")
+engine.close()
+"""
+
+
+@pytest.mark.parametrize("world,tp", [(2, 1), (4, 1), (4, 2)])
+def test_muon_on_sharded_parameters_matches_single_process_and_resumes(tmp_path, world, tp):
+    """The "matrix" layout keeps whole matrices at their owners, so Muon runs there without a
+    gather; the momentum buffers are checkpointed per matrix and a fresh model resumes."""
+    path = tmp_path / "worker.py"
+    path.write_text(textwrap.dedent(MUON_WORKER).replace("TP", str(tp)))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(32000 + os.getpid() % 150), str(path),
+           str(tmp_path / "ckpt.pt")]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "MUON_SHARDED_OK" in proc.stdout
