@@ -258,7 +258,7 @@ engine.close()
 """
 
 
-@pytest.mark.parametrize("world,micro,checkpoint", [(2, 1, False), (4, 2, False), (2, 1, True)])
+@pytest.mark.parametrize("world,micro,checkpoint", [(4, 2, False), (2, 1, True)])
 def test_gloo_ranks_match_single_process_training(tmp_path, world, micro, checkpoint):
     path = tmp_path / "worker.py"
     path.write_text(textwrap.dedent(WORKER).replace("MICRO", str(micro))
@@ -474,7 +474,7 @@ engine.close()
 """
 
 
-@pytest.mark.parametrize("world,tp", [(2, 1), (4, 1), (4, 2)])
+@pytest.mark.parametrize("world,tp", [(4, 1), (4, 2)])
 def test_muon_on_sharded_parameters_matches_single_process_and_resumes(tmp_path, world, tp):
     """The "matrix" layout keeps whole matrices at their owners, so Muon runs there without a
     gather; the momentum buffers are checkpointed per matrix and a fresh model resumes."""
