@@ -156,7 +156,13 @@ class GroupedMoE(QuantileBalancedRouter):
             indices, weights, logits, alpha = self._route(flat_x)
         if self.capacity_factor is not None:
             weights = self._apply_capacity(indices.long(), weights)
-        if self.ep_workspace is not None:
+        if getattr(self.ep_workspace, "uses_process_group", False):
+            # process-group all-to-all (ranks without peer memory, e.g. CPU ranks)
+            from ohara_b200.parallel.ep_c10d import expert_parallel_swiglu_c10d
+
+            out = expert_parallel_swiglu_c10d(flat_x, indices, weights.to(flat_x.dtype), self.w_gate,
+                                              self.w_up, self.w_down, self.ep_workspace)
+        elif self.ep_workspace is not None:
             if counts is None:
                 raise RuntimeError("expert parallelism needs the CUDA bf16 path (router kernels)")
             from ohara_b200.parallel.ep import expert_parallel_swiglu

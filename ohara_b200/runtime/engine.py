@@ -73,6 +73,16 @@ _REDUCE_OPS = {
 }
 
 
+def _strip_wrapper_prefixes(name: str) -> str:
+    changed = True
+    while changed:
+        changed = False
+        for prefix in ("module.", "_orig_mod."):
+            if name.startswith(prefix):
+                name, changed = name[len(prefix):], True
+    return name
+
+
 def _stage_to_model_name(name: str, first_layer: int) -> str:
     """``layers.<i>.…`` of a pipeline stage is ``layers.<first_layer + i>.…`` of the model."""
     if name.startswith("layers."):
@@ -475,17 +485,21 @@ class OharaEngine:
         from ohara_b200.modules.moe_grouped import GroupedMoE
         from ohara_b200.parallel.ep import LazyEPWorkspace
 
-        if self._device.type != "cuda":
-            raise RuntimeError("expert parallelism needs CUDA devices")
         layers = [m for m in module.modules() if isinstance(m, GroupedMoE)]
         if not layers:
             raise ValueError("ep > 1 but the model has no grouped mixture-of-experts layer")
-        shared: dict[tuple[int, int], LazyEPWorkspace] = {}
+        peer_memory = self._device.type == "cuda"
+        shared: dict[tuple[int, int], Any] = {}
         for index, layer in enumerate(layers):
             key = (layer.num_experts, layer.dim)
-            if key not in shared:
+            if key not in shared and peer_memory:
                 shared[key] = LazyEPWorkspace(self._groups.get("ep"), layer.num_experts, layer.dim,
                                               self.config.expert_capacity_factor)
+            elif key not in shared:
+                # no peer memory (CPU ranks): the same layer over the group's all-to-all
+                from ohara_b200.parallel.ep_c10d import C10dEPWorkspace
+
+                shared[key] = C10dEPWorkspace(self._groups.get("ep"), layer.num_experts)
             layer.shard_experts(shared[key], slot=index)
             topo = self.topology
             sharded = isinstance(self._strategy, FSDPStrategy)
@@ -895,17 +909,22 @@ class OharaEngine:
         for key, obj in state.items():
             if key not in payload:
                 continue
-            sharding = getattr(obj, "_param_sharding", None)
+            sharding = getattr(obj.module if hasattr(obj, "module") else obj, "_param_sharding", None)
             if isinstance(obj, torch.nn.Module):
                 # checkpoints hold whole tensors (``full_state_dict``): cut out what this rank
                 # keeps of tensor-parallel matrices and expert stacks
-                local = self._local_slice_of_state(obj, payload[key])
+                # wrapper-free keys, whatever wrote the file (a DDP- or torch.compile-wrapped
+                # module prefixes its keys, as the reference's checkpoints do)
+                saved = {_strip_wrapper_prefixes(name): tensor
+                         for name, tensor in payload[key].items()}
+                inner = obj.module if hasattr(obj, "module") else obj
+                local = self._local_slice_of_state(inner, saved)
                 if sharding is not None:  # parameters sharded per block: load through the gather
-                    sharding.load_full_state_dict(obj, local)
-                elif getattr(obj, "pipeline_stage", False):
-                    obj.stage.load_state_dict(local)
+                    sharding.load_full_state_dict(inner, local)
+                elif getattr(inner, "pipeline_stage", False):
+                    inner.stage.load_state_dict(local)
                 else:
-                    obj.load_state_dict(local)
+                    inner.load_state_dict(local)
             elif hasattr(obj, "load_state_dict"):
                 saved = payload[key]
                 if isinstance(saved, dict) and saved.get("model_parallel"):

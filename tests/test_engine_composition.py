@@ -445,3 +445,68 @@ def test_checkpoint_of_a_pipeline_run_is_a_whole_model_and_resumes(tmp_path):
         4, tmp_path, port_base=30300,
     )
     assert "PP_RESUME_OK" in out
+
+
+@pytest.mark.parametrize("world,ep", [(2, 2), (4, 2)])
+def test_expert_parallel_training_on_cpu_ranks_matches_single_process_and_resumes(tmp_path, world, ep):
+    """ep=2 (x dp=2): every rank keeps half of the routed experts and exchanges rows with
+    all-to-alls (the process-group form of the expert-parallel layer); dense parameters are sharded
+    over all ranks, experts over the ranks that hold the same ones; the checkpoint holds all
+    experts and one optimizer state per expert-parallel coordinate."""
+    out = _run(
+        f"""
+        import os, tempfile
+        moe_cfg = Config(vocab_size=31, max_sequence_length=8, hidden_size=16, intermediate_size=24,
+                         num_attention_heads=2, num_hidden_layers=2, dropout=0.0, moe_num_experts=4,
+                         moe_experts_per_tok=2, moe_grouped=True, moe_num_shared_experts=1)
+        moe_state = {{k: v.clone() for k, v in Llama(moe_cfg).state_dict().items()}}
+        for name in moe_state:                         # the routed output projections start at zero
+            if name.endswith("w_down"):
+                moe_state[name].normal_(std=0.1)
+
+        def solo_after(steps):
+            solo = Llama(moe_cfg); solo.load_state_dict(moe_state)
+            opt = build_adamw(solo, learning_rate=0.02, weight_decay=0.1)
+            for _ in range(steps):
+                loss = solo.loss_sum(ids[:, :-1], ids[:, 1:]) / ids[:, 1:].numel()
+                loss.backward(); opt.step(); opt.zero_grad()
+            return solo
+
+        engine = OharaEngine(EngineConfig(strategy=StrategyType.FSDP, parallel=ParallelConfig(ep={ep})))
+
+        def make():
+            model = Llama(moe_cfg); model.load_state_dict(moe_state)
+            model = engine.prepare(model)
+            (opt,) = engine.prepare_optimizers(build_adamw(model, learning_rate=0.02, weight_decay=0.1))
+            replicas = engine.data_parallel_world_size
+            loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=8 // replicas))
+            trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=1,
+                              max_iters=2, eval_iters=0, save_ckpt_iters=0)
+            return model, opt, trainer
+
+        def close_to(model, solo):
+            full = engine.full_state_dict(model)
+            for name, value in solo.state_dict().items():
+                assert full[name].shape == value.shape, (name, full[name].shape, value.shape)
+                assert torch.allclose(full[name], value, atol=3e-5), (name, (full[name] - value).abs().max())
+
+        model, opt, trainer = make()
+        assert engine.data_parallel_world_size == {world}
+        assert model.layers[0].ff.w_gate.shape[0] == 4 // {ep}
+        assert type(opt).__name__ == "HybridShardedOptimizer"
+        trainer.train()
+        close_to(model, solo_after(2))
+        folder = engine.broadcast(tempfile.mkdtemp() if dist.get_rank() == 0 else None)
+        path = os.path.join(folder, "ckpt.pt")
+        engine.save(path, trainer.checkpoint_state(2, 0.02, 0.0))
+        model, opt, trainer = make()
+        engine.load(path, {{"model": model, "optimizer": opt}})
+        trainer.train()
+        close_to(model, solo_after(4))
+        if dist.get_rank() == 0:
+            print("EP_CPU_OK")
+        engine.close()
+        """,
+        world, tmp_path, port_base=30500,
+    )
+    assert "EP_CPU_OK" in out

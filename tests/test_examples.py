@@ -137,12 +137,14 @@ def test_pretraining_example_trains_saves_and_resumes(tmp_path):
 
 
 @pytest.mark.parametrize("layout", [
-    ["--shard-parameters", "--optimizer", "adamw", "--activation-checkpointing"],
-    ["--tp", "2", "--optimizer", "adamw"],
+    ["--strategy", "fsdp", "--shard-parameters", "--optimizer", "adamw", "--activation-checkpointing"],
+    ["--strategy", "fsdp", "--tp", "2", "--optimizer", "adamw"],
+    ["--strategy", "ddp"],
 ])
 def test_pretraining_example_on_two_ranks_saves_and_resumes(tmp_path, layout):
-    """The same script under torchrun on two CPU ranks with the sharded strategy: sharded
-    parameters with recomputed blocks, and tensor parallelism."""
+    """The same script under torchrun on two CPU ranks: sharded parameters with recomputed
+    blocks, tensor parallelism under the sharded strategy, and plain DDP (whose wrapper must take
+    the wrapper-free checkpoint back)."""
     checkpoint = tmp_path / "ckpt" / "model.pt"
     command = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                "--master-addr", "127.0.0.1", "--master-port", str(32500 + os.getpid() % 300),
@@ -151,8 +153,7 @@ def test_pretraining_example_on_two_ranks_saves_and_resumes(tmp_path, layout):
                "--num-layers", "2", "--num-heads", "2", "--batch-size", "2",
                "--grad-accum-steps", "2", "--warmup-iters", "1", "--eval-every", "2",
                "--eval-batches", "1", "--save-every", "2", "--logger", "none", "--precision", "fp32",
-               "--no-weight-tying", "--checkpoint-path", str(checkpoint), "--strategy", "fsdp",
-               *layout]
+               "--no-weight-tying", "--checkpoint-path", str(checkpoint), *layout]
     env = dict(os.environ, OMP_NUM_THREADS="1")
     first = subprocess.run(command + ["--max-iters", "2"], capture_output=True, text=True,
                            timeout=300, env=env)
