@@ -83,3 +83,10 @@ def test_tiny_data_parallel_config_with_sharded_parameters_on_two_ranks():
     assert 0 < memory["peak_gathered_bytes"] < memory["unsharded_bytes"]
     # the same data, model and optimizer: both arrive at the same loss
     assert abs(plain["final_loss"] - sharded["final_loss"]) < 2e-3 * plain["final_loss"]
+
+
+def test_tiny_expert_parallel_configuration_on_two_ranks():
+    line = _bench("--config", "moe_ep8_skewed", world=2, port=32700)
+    assert line["config"]["parallelism"] == "ep2"
+    assert line["skew"]["target_share"] == 0.5 and 3.0 < line["final_loss"] < 8.0
+    assert line["expert_load"]["dropped_pair_fraction_last_step"] > 0.0   # the skew overflows
