@@ -74,6 +74,19 @@ class PScanCuda(torch.autograd.Function):
         return da.to(ctx.dtypes[0]), dx.to(ctx.dtypes[1])
 
 
+def npo2(length: int) -> int:
+    """The smallest power of two that is at least ``length``."""
+    return 1 << max(0, int(length) - 1).bit_length()
+
+
+def pad_npo2(X: Tensor) -> Tensor:
+    """Zero-pad dim 1 of ``(B, L, D, N)`` to the next power of two. Nothing here needs it (the
+    scans take any length); kept because callers of the reference's scan pad with it
+    (ohara/modules/pscan.py:39-60)."""
+    extra = npo2(X.size(1)) - X.size(1)
+    return torch.nn.functional.pad(X, (0, 0, 0, 0, 0, extra)) if extra else X
+
+
 def pscan(A: Tensor, X: Tensor) -> Tensor:
     """``H`` with ``H[:, t] = A[:, t] * H[:, t-1] + X[:, t]`` for ``(B, L, D, N)`` (or any
     ``(B, L, ...)``) inputs of equal shape."""

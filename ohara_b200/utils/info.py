@@ -34,6 +34,19 @@ class Summary:
         return "\n".join(lines)
 
 
+class Model(nn.Module):
+    """A module that only holds ``model``. The reference wraps models in a Lightning module of
+    this name to reuse Lightning's summary (ohara/utils/info.py:7-10); there is no Lightning
+    here, the class is kept for callers that construct it."""
+
+    def __init__(self, model: nn.Module, *args, **kwargs) -> None:
+        super().__init__()
+        self.model = model
+
+    def forward(self, *args, **kwargs):
+        return self.model(*args, **kwargs)
+
+
 def model_summary(model: nn.Module, print_summary: bool = False) -> dict:
     summary = Summary(model)
     if print_summary:

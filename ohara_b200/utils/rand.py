@@ -19,3 +19,9 @@ def name_pool() -> tuple[str, ...]:
 def random_name() -> str:
     stamp = datetime.now().strftime("%Y_%m_%d_%H_%M_%S")
     return f"{random.choice(name_pool())}-{stamp}"
+
+
+def pokemon_names() -> tuple[str, ...]:
+    """Name of this function in the reference (ohara/utils/rand.py:14); the pool here is this
+    package's own list of run names."""
+    return name_pool()

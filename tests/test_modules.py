@@ -262,3 +262,29 @@ def test_cycle_and_run_names():
     cycle.close()
     assert cycle._iterator is None and next(cycle) == 1
     assert re.fullmatch(r"[a-z0-9_\-]+-\d{4}(_\d{2}){5}", random_name(), flags=re.I)
+
+
+def test_small_helpers_of_the_public_surface():
+    """Names the reference exports that nothing else here needs: rotary table broadcasting,
+    power-of-two padding for scans, the model holder of the summary utility, the name pool."""
+    import torch
+
+    from ohara_b200.embeddings_pos.rotary import precompute_freqs_cis, reshape_for_broadcast
+    from ohara_b200.modules.pscan import npo2, pad_npo2
+    from ohara_b200.utils.info import Model, model_summary
+    from ohara_b200.utils.rand import pokemon_names, random_name
+
+    cos, _ = precompute_freqs_cis(8, 6)
+    x = torch.zeros(2, 6, 3, 4)
+    assert reshape_for_broadcast(cos, x).shape == (1, 6, 1, 4)
+    with pytest.raises(ValueError):
+        reshape_for_broadcast(cos, torch.zeros(2, 5, 3, 4))
+    assert [npo2(n) for n in (1, 2, 3, 8, 9, 1000)] == [1, 2, 4, 8, 16, 1024]
+    padded = pad_npo2(torch.ones(2, 5, 3, 1))
+    assert padded.shape == (2, 8, 3, 1) and float(padded[:, 5:].abs().sum()) == 0
+    assert pad_npo2(torch.ones(1, 4, 2, 2)).shape == (1, 4, 2, 2)
+    holder = Model(torch.nn.Linear(3, 2))
+    assert holder(torch.zeros(1, 3)).shape == (1, 2)
+    assert model_summary(holder)["total_parameters"] == "8"
+    names = pokemon_names()
+    assert len(names) > 10 and random_name().split("-")[0] in names
