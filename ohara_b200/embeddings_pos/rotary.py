@@ -40,15 +40,15 @@ def rope_reference(x: Tensor, cos: Tensor, sin: Tensor, inverse: bool = False) -
     return rotated.flatten(-2).to(x.dtype)
 
 
-def reshape_for_broadcast(freqs: Tensor, x: Tensor) -> Tensor:
+def reshape_for_broadcast(freqs_cis: Tensor, x: Tensor) -> Tensor:
     """View a ``(seq_len, width)`` table so that it broadcasts against ``x (batch, seq_len, ...,
     width)``: the sequence and the last dimension are kept, every other one becomes 1 (helper of
     the reference's public surface: ohara/embeddings_pos/rotary.py:41-52)."""
-    if x.dim() < 2 or tuple(freqs.shape) != (x.shape[1], x.shape[-1]):
-        raise ValueError(f"table of shape {tuple(freqs.shape)} does not match input "
+    if x.dim() < 2 or tuple(freqs_cis.shape) != (x.shape[1], x.shape[-1]):
+        raise ValueError(f"table of shape {tuple(freqs_cis.shape)} does not match input "
                          f"{tuple(x.shape)} (expected {(x.shape[1], x.shape[-1])})")
     last = x.dim() - 1
-    return freqs.view([size if axis in (1, last) else 1 for axis, size in enumerate(x.shape)])
+    return freqs_cis.view([size if axis in (1, last) else 1 for axis, size in enumerate(x.shape)])
 
 
 def apply_rope(q: Tensor, k: Tensor, cis: tuple[Tensor, Tensor]) -> tuple[Tensor, Tensor]:

@@ -11,9 +11,10 @@ from torch import Tensor
 from .pscan import pscan
 
 
-def scan(a: Tensor, x: Tensor) -> Tensor:
-    """Linear recurrence over dim 1 for ``(B, L, D)`` tensors."""
-    return pscan(a, x)
+def scan(x: Tensor, h: Tensor) -> Tensor:
+    """Linear recurrence over dim 1 for ``(B, L, D)`` tensors: ``x`` holds the coefficients and
+    ``h`` the driven inputs (the reference's parameter names, ohara/modules/linear_rnn.py:16-20)."""
+    return pscan(x, h)
 
 
 def _trunc_normal(weight: Tensor, std: float, bound: float | None = None) -> None:

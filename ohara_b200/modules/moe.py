@@ -62,6 +62,17 @@ class MoE(QuantileBalancedRouter):
             self._record_load(indices.detach())
         return out.view(batch, seq, dim)
 
+    @torch.no_grad()
+    def reset_parameters(self, init_std: float | None = None) -> None:
+        """Truncated-normal router (std ``dim ** -0.5`` unless given), zero selection bias, and
+        every expert's own ``reset_parameters`` (reference: ohara/modules/moe.py:164-177)."""
+        std = init_std or self.dim ** -0.5
+        nn.init.trunc_normal_(self.gate.weight, mean=0.0, std=std, a=-3 * std, b=3 * std)
+        self.router_bias.zero_()
+        for expert in self.experts:
+            if hasattr(expert, "reset_parameters"):
+                expert.reset_parameters(init_std=init_std)
+
     def _dispatch(self, flat: Tensor, indices: Tensor, weights: Tensor) -> Tensor:
         k = self.num_experts_per_tok
         pair_expert = indices.reshape(-1)

@@ -74,9 +74,9 @@ class PScanCuda(torch.autograd.Function):
         return da.to(ctx.dtypes[0]), dx.to(ctx.dtypes[1])
 
 
-def npo2(length: int) -> int:
-    """The smallest power of two that is at least ``length``."""
-    return 1 << max(0, int(length) - 1).bit_length()
+def npo2(len: int) -> int:  # noqa: A002 - the reference's parameter name
+    """The smallest power of two that is at least ``len``."""
+    return 1 << max(0, int(len) - 1).bit_length()
 
 
 def pad_npo2(X: Tensor) -> Tensor:

@@ -183,19 +183,19 @@ class QuantileBalancedRouter(nn.Module):
         return counts
 
 
-def apply_qb_update(model: nn.Module) -> None:
-    """Run ``apply_qb_update`` on every balancing MoE layer of ``model``."""
-    for module in model.modules():
-        if isinstance(module, QuantileBalancedRouter) and module.quantile_balancing:
-            module.apply_qb_update()
+def apply_qb_update(module: nn.Module) -> None:
+    """Run ``apply_qb_update`` on every balancing MoE layer of ``module``."""
+    for layer in module.modules():
+        if isinstance(layer, QuantileBalancedRouter) and layer.quantile_balancing:
+            layer.apply_qb_update()
 
 
-def expert_load(model: nn.Module, reset: bool = True) -> list[Tensor]:
+def expert_load(module: nn.Module, reset: bool = True) -> list[Tensor]:
     """Tokens routed to each expert since the last reset, one tensor per MoE layer."""
     return [
-        module.expert_load(reset=reset)
-        for module in model.modules()
-        if isinstance(module, QuantileBalancedRouter)
+        layer.expert_load(reset=reset)
+        for layer in module.modules()
+        if isinstance(layer, QuantileBalancedRouter)
     ]
 
 

@@ -37,11 +37,11 @@ class DatasetPreprocessor:
         self.num_proc = num_proc if num_proc else max((os.cpu_count() or 4) - 3, 1)
 
     # -- hooks ---------------------------------------------------------------------------------
-    def tokenize_fn(self, batch):
-        return self.tokenizer(batch["text"], max_length=self.max_length, truncation=True)
+    def tokenize_fn(self, x):
+        return self.tokenizer(x["text"], max_length=self.max_length, truncation=True)
 
-    def filter_fn(self, row) -> bool:
-        return len(row["input_ids"]) >= self.min_length
+    def filter_fn(self, x) -> bool:
+        return len(x["input_ids"]) >= self.min_length
 
     def _storage_name(self) -> str:
         return (f"{self.dataset_name.replace('/', '-')}--"
@@ -101,5 +101,5 @@ class OpenHermesDatasetPreprocessor(DatasetPreprocessor):
         return (self._load(split).map(to_chat, num_proc=self.num_proc)
                 .shuffle(seed=self.shuffle_seed).filter(self.filter_fn, num_proc=self.num_proc))
 
-    def filter_fn(self, row) -> bool:
-        return self.min_length <= len(row["input_ids"]) <= self.max_length
+    def filter_fn(self, x) -> bool:
+        return self.min_length <= len(x["input_ids"]) <= self.max_length

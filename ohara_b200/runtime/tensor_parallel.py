@@ -322,9 +322,19 @@ def fused_column_parallel(x: Tensor, layers) -> Tensor | None:
     return y.view(x.shape[0] * first.tp_world, *x.shape[1:-1], y.shape[-1])
 
 
-def apply_tensor_parallel(module: nn.Module, tp_group, plan: TensorParallelPlan,
-                          tp_rank: int | None = None, tp_world: int | None = None) -> nn.Module:
-    """Replace every ``nn.Linear`` matched by ``plan`` with its sharded counterpart, in place."""
+def apply_tensor_parallel(module: nn.Module, tp_group=None, plan: TensorParallelPlan | None = None,
+                          tp_rank: int | None = None, tp_world: int | None = None, *,
+                          tp_mesh=None) -> nn.Module:
+    """Replace every ``nn.Linear`` matched by ``plan`` with its sharded counterpart, in place.
+    ``tp_mesh`` (the reference's argument: a one-dimensional ``DeviceMesh``,
+    ohara/runtime/tensor_parallel.py:65-69) is accepted in place of ``tp_group``; only its
+    process group is used, the layers here are not DTensor modules."""
+    if tp_mesh is not None:
+        if tp_group is not None:
+            raise ValueError("pass tp_group or tp_mesh, not both")
+        tp_group = tp_mesh.get_group()
+    if plan is None:
+        raise ValueError("apply_tensor_parallel needs a TensorParallelPlan")
     plan.validate()
     world = tp_world if tp_world is not None else dist.get_world_size(tp_group)
     rank = tp_rank if tp_rank is not None else dist.get_rank(tp_group)
