@@ -116,6 +116,44 @@ def _variants() -> dict[str, Callable[[TemplateConfig], TemplateLM]]:
             out, aux = self.routed(x, auxiliary_loss=self.training)
             return out if aux is None else (out, aux)
 
+    class LatentAttention(nn.Module):
+        """Multi-head latent attention (it carries its own rotary tables) behind the template's
+        ``attention(x, freqs)`` interface."""
+
+        def __init__(self, cfg: TemplateConfig) -> None:
+            super().__init__()
+            from experiments.mla.mla import MLAConfig, MultiHeadLatentAttention
+
+            head = cfg.d_model // cfg.num_heads
+            self.inner = MultiHeadLatentAttention(MLAConfig(
+                d_model=cfg.d_model, num_heads=cfg.num_heads, v_head_dim=head,
+                nope_head_dim=head // 2, rope_head_dim=head // 2, q_lora_rank=cfg.d_model // 2,
+                kv_lora_rank=cfg.d_model // 4, max_sequence_length=cfg.seq_len))
+
+        def forward(self, x: Tensor, freqs) -> Tensor:
+            return self.inner(x)
+
+    class ParameterTokenAttention(nn.Module):
+        """Attention whose four projections are parameter-token attention layers, so that the
+        whole block is made of attention over learned tokens (the Tokenformer block)."""
+
+        def __init__(self, cfg: TemplateConfig) -> None:
+            super().__init__()
+            from experiments.partial_kv.pkv import _attend, _heads
+            from ohara_b200.embeddings_pos.rotary import apply_rope
+
+            self._attend, self._heads, self._rope = _attend, _heads, apply_rope
+            self.num_heads = cfg.num_heads
+            tokens = cfg.d_model
+            self.query, self.key, self.value, self.proj = (
+                Pattention(cfg.d_model, cfg.d_model, tokens) for _ in range(4))
+
+        def forward(self, x: Tensor, freqs) -> Tensor:
+            q, k = self._rope(self._heads(self.query(x), self.num_heads),
+                              self._heads(self.key(x), self.num_heads), freqs)
+            v = self._heads(self.value(x), self.num_heads)
+            return self.proj(self._attend(q, k, v, 0.0, self.training))
+
     def hypersphere(cfg: TemplateConfig) -> TemplateLM:
         model = TemplateLM(cfg)
 
@@ -145,6 +183,10 @@ def _variants() -> dict[str, Callable[[TemplateConfig], TemplateLM]]:
             c, feed_forward=lambda k: SpringMLP(k.d_model, k.hidden_dim, spring_steps=4)),
         "tokenformer": lambda c: TemplateLM(
             c, feed_forward=lambda k: Pattention(k.d_model, k.d_model, num_tokens=k.hidden_dim)),
+        "tokenformer_full": lambda c: TemplateLM(
+            c, attention=ParameterTokenAttention,
+            feed_forward=lambda k: Pattention(k.d_model, k.d_model, num_tokens=k.hidden_dim)),
+        "mla": lambda c: TemplateLM(c, attention=LatentAttention),
         "relu2": lambda c: TemplateLM(c, feed_forward=lambda k: ReLUSquaredMLP(k.d_model, k.hidden_dim)),
         "mixture_of_depth": lambda c: TemplateLM(
             c, feed_forward=lambda k: DepthRoutedMLP(k.d_model, k.hidden_dim)),

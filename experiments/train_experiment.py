@@ -10,7 +10,8 @@ repeating structure, so that the loss has something to learn), AdamW with warm-u
 bf16 autocast on CUDA. Prints the loss every ``--log-every`` steps and a final JSON line with the
 first and last smoothed loss, parameters and tokens per second. Models: ``mqa`` / ``hawk`` /
 ``griffin``; ``residual`` / ``hc`` / ``mhc``; the template variants ``baseline`` / ``kattention`` /
-``partial_kv`` / ``xglu`` / ``deglu`` / ``springnet`` / ``tokenformer`` / ``relu2`` /
+``partial_kv`` / ``xglu`` / ``deglu`` / ``springnet`` / ``tokenformer`` / ``tokenformer_full`` /
+``mla`` / ``relu2`` /
 ``mixture_of_depth`` / ``hypersphere``; ``life`` trains the template baseline on Game of Life
 transitions with the loss on the next board only."""
 

@@ -363,7 +363,8 @@ def test_connection_types_of_the_mhc_model_and_template_variants_run_and_learn()
     cfg = TemplateConfig(vocab_size=40, seq_len=32, d_model=32, hidden_dim=48, num_heads=4,
                          num_layers=2)
     assert set(VARIANTS) == {"baseline", "kattention", "partial_kv", "xglu", "deglu", "springnet",
-                             "tokenformer", "relu2", "mixture_of_depth", "hypersphere"}
+                             "tokenformer", "tokenformer_full", "mla", "relu2", "mixture_of_depth",
+                             "hypersphere"}
     for variant in VARIANTS:
         model = build(variant, cfg)
         logits = model(tokens)
