@@ -139,27 +139,65 @@ def build_adamw(model: torch.nn.Module, *, learning_rate: float, weight_decay: f
 # --------------------------------------------------------------------------------------------------
 # Hyperspherical (constant-norm) updates
 # --------------------------------------------------------------------------------------------------
+def _whole_norms(tensors: list[Tensor], sharded: list[bool] | None, group) -> list[Tensor]:
+    """Frobenius norms of ``tensors``; where ``sharded[i]`` the tensor is one shard of a matrix
+    spread over ``group`` and the norm is that of the whole matrix (squared norms summed over the
+    group, one all-reduce for all of them)."""
+    norms = list(torch._foreach_norm(tensors))
+    if not sharded or not any(sharded):  # (``group=None`` is the default process group)
+        return norms
+    import torch.distributed as dist
+
+    picked = [i for i, flag in enumerate(sharded) if flag]
+    squares = torch.stack([norms[i].float().square() for i in picked])
+    dist.all_reduce(squares, group=group)
+    for slot, i in enumerate(picked):
+        norms[i] = squares[slot].sqrt().to(norms[i].dtype)
+    return norms
+
+
 def _hypersphere_update_(params: list[Tensor], directions: list[Tensor], learning_rate: float, *,
-                         eps: float = 1e-10) -> None:
-    """``p <- p - lr·u·‖p‖/‖u‖`` then rescale back to the original Frobenius norm, per tensor."""
+                         eps: float = 1e-10, sharded: list[bool] | None = None,
+                         group=None) -> None:
+    """``p <- p - lr·u·‖p‖/‖u‖`` then rescale back to the original Frobenius norm, per tensor.
+    With ``group`` and ``sharded`` the flagged tensors are tensor-parallel shards and every norm
+    is taken over the whole matrix."""
     if not params:
         return
-    p_norms = torch._foreach_norm(params)
-    u_norms = torch._foreach_clamp_min(torch._foreach_norm(directions), eps)
+    p_norms = _whole_norms(params, sharded, group)
+    u_norms = torch._foreach_clamp_min(_whole_norms(directions, sharded, group), eps)
     steps = torch._foreach_div(p_norms, u_norms)
     torch._foreach_mul_(steps, learning_rate)
     torch._foreach_add_(params, torch._foreach_mul(directions, steps), alpha=-1)
-    new_norms = torch._foreach_clamp_min(torch._foreach_norm(params), eps)
+    new_norms = torch._foreach_clamp_min(_whole_norms(params, sharded, group), eps)
     torch._foreach_mul_(params, torch._foreach_div(p_norms, new_norms))
 
 
+def _stacked_norms(stacked: Tensor, group) -> Tensor:
+    """Norms of whole matrices from a stack of their shards (sum of squares over ``group``)."""
+    import torch.distributed as dist
+
+    squares = stacked.float().square().sum(dim=(-2, -1), keepdim=True)
+    dist.all_reduce(squares, group=group)
+    return squares.sqrt().to(stacked.dtype)
+
+
 def _hypersphere_update_stacked_(stacked: Tensor, updates: Tensor, learning_rate: float, *,
-                                 eps: float = 1e-10) -> None:
-    """Same rule for a ``(batch, rows, cols)`` stack, one norm per matrix."""
-    p_norms = torch.linalg.matrix_norm(stacked, keepdim=True)
-    u_norms = torch.linalg.matrix_norm(updates, keepdim=True).clamp_min(eps)
+                                 eps: float = 1e-10, sharded: bool = False, group=None) -> None:
+    """Same rule for a ``(batch, rows, cols)`` stack, one norm per matrix; with ``sharded`` the
+    stack holds tensor-parallel shards and the norms are those of the whole matrices, summed
+    over ``group`` (``None``: the default process group)."""
+    if sharded:
+        p_norms = _stacked_norms(stacked, group)
+        u_norms = _stacked_norms(updates, group).clamp_min(eps)
+    else:
+        p_norms = torch.linalg.matrix_norm(stacked, keepdim=True)
+        u_norms = torch.linalg.matrix_norm(updates, keepdim=True).clamp_min(eps)
     stacked.sub_(updates * (p_norms * learning_rate / u_norms))
-    new_norms = torch.linalg.matrix_norm(stacked, keepdim=True).clamp_min(eps)
+    if sharded:
+        new_norms = _stacked_norms(stacked, group).clamp_min(eps)
+    else:
+        new_norms = torch.linalg.matrix_norm(stacked, keepdim=True).clamp_min(eps)
     stacked.mul_(p_norms / new_norms)
 
 
@@ -335,10 +373,15 @@ class MuonAdamW(optim.Optimizer):
         denoms = torch._foreach_sqrt(torch._foreach_div(exp_avg_sqs, 1.0 - beta2**step))
         torch._foreach_add_(denoms, eps)
         directions = torch._foreach_div(torch._foreach_div(exp_avgs, 1.0 - beta1**step), denoms)
+        # tensor-parallel shards: the sphere is that of the whole matrix
+        distributed = self._tensor_parallel_world() > 1
+        sharded = [distributed and hasattr(p, "tensor_parallel_dim") for p in params]
         if len(params) == 1 and params[0].ndim == 3:
-            _hypersphere_update_stacked_(params[0], directions[0], float(group["lr"]))
+            _hypersphere_update_stacked_(params[0], directions[0], float(group["lr"]),
+                                         sharded=sharded[0], group=self.tensor_parallel_group)
         else:
-            _hypersphere_update_(params, directions, float(group["lr"]))
+            _hypersphere_update_(params, directions, float(group["lr"]), sharded=sharded,
+                                 group=self.tensor_parallel_group)
 
     # -- Muon / MuonH ------------------------------------------------------------------------
     def _muon_step(self, group: dict[str, Any]) -> None:
@@ -431,9 +474,7 @@ class MuonAdamW(optim.Optimizer):
         combination: examples/train_llama_engine.py:280-281.)"""
         import torch.distributed as dist
 
-        if bool(group.get("hypersphere", False)):
-            raise NotImplementedError("hyperspherical Muon on tensor-parallel shards is not "
-                                      "implemented (the norms span the whole matrix)")
+        hyperspherical = bool(group.get("hypersphere", False))
         world, pg = self._tensor_parallel_world(), self.tensor_parallel_group
         rank = dist.get_rank(pg)
         first = params[0]
@@ -449,6 +490,17 @@ class MuonAdamW(optim.Optimizer):
         dist.all_gather(parts, local, group=pg)
         whole = torch.cat(parts, dim=1 + tp_dim)
         update = _polar_express(whole, int(group["ns_steps"]))
+        if hyperspherical:
+            # MuonH: a constant-norm step along the orthogonalised direction; every norm is that
+            # of the whole matrix, so the shards stay on the whole matrix's sphere
+            mine = update.chunk(world, dim=1 + tp_dim)[rank].to(stacked.dtype).contiguous()
+            _hypersphere_update_stacked_(stacked, mine, float(group["lr"]), sharded=True, group=pg)
+            if not pre_stacked:
+                torch._foreach_copy_(params, list(stacked.unbind(0)))
+            for p in params:
+                if getattr(p, "_ohara_bf16", None) is not None:
+                    p._ohara_bf16 = None
+            return
         rows, cols = whole.shape[-2:]
         reduce_dim = -1 if rows >= cols else -2
         shape = (whole.shape[0], rows, 1) if reduce_dim == -1 else (whole.shape[0], 1, cols)

@@ -179,7 +179,8 @@ class ParameterSharding:
         # Set by the engine under sequence-parallel tensor parallelism: the ranks of this group
         # see different tokens, so gradients of parameters that are NOT tensor-parallel shards
         # are partial sums and are added up over it before the data-parallel reduction.
-        self.partial_gradient_group = None
+        self.partial_gradient_group = None   # (``None`` is also the default group: see the flag)
+        self.partial_gradients = False
         self.unsharded_bytes = sum(sum(u.numels) for u in self.units) * 4
         self.peak_gathered_bytes = 0
         for unit in self.units:
@@ -289,7 +290,7 @@ class ParameterSharding:
                 if p.grad is not None:
                     flat[off : off + n].copy_(p.grad.reshape(-1))
                     p.grad = None
-            if self.partial_gradient_group is not None:
+            if self.partial_gradients:
                 for p, off, n in zip(unit.params, unit.offsets, unit.numels):
                     if not hasattr(p, "tensor_parallel_dim"):
                         dist.all_reduce(flat[off : off + n], group=self.partial_gradient_group)

@@ -408,6 +408,7 @@ class OharaEngine:
         if sharding is not None and getattr(self, "_tp_batch_sharding", False):
             # sequence-parallel layout: replicated parameters hold partial gradients per tp rank
             sharding.partial_gradient_group = self._groups.get("tp")
+            sharding.partial_gradients = True
         self._module = module
         return module
 

@@ -9,6 +9,7 @@ import sys
 import textwrap
 from pathlib import Path
 
+import pytest
 import torch
 
 ROOT = Path(__file__).resolve().parent.parent
@@ -266,20 +267,30 @@ def test_pipeline_parallel_through_the_engine_matches_single_process(tmp_path):
     assert "PP_ENGINE_OK" in out
 
 
-def test_muon_on_tensor_parallel_shards_matches_the_unsharded_step(tmp_path):
+@pytest.mark.parametrize("builder,strategy,world", [
+    ("build_muon_adamw", "FSDP", 4), ("build_muonh_adamh", "FSDP", 4),
+    ("build_muonh_adamh", "DDP", 2),   # tp = world: the tensor-parallel group is the default group
+])
+def test_muon_on_tensor_parallel_shards_matches_the_unsharded_step(tmp_path, builder, strategy, world):
     """tp=2 x dp=2 with the Muon hybrid: the orthogonalisation runs on whole matrices gathered
     over the tensor-parallel group, every rank applies its slice; weights must follow the
-    single-process run."""
+    single-process run. The hyperspherical recipe (MuonH on hidden matrices, AdamH on the head)
+    takes every norm over the whole matrix, so the shards stay on the whole matrix's sphere."""
     out = _run(
-        """
-        solo = reference(build_muon_adamw)
-        engine = OharaEngine(EngineConfig(strategy=StrategyType.FSDP,
+        f"""
+        from ohara_b200.optimizer import build_muonh_adamh
+        # the trainer's schedule is expressed in the builder's base rate (0.02 below)
+        build = ({builder} if "{builder}" == "build_muon_adamw"
+                 else (lambda m: build_muonh_adamh(m, learning_rate=0.02)))
+        solo = reference(build)
+        engine = OharaEngine(EngineConfig(strategy=StrategyType.{strategy},
                                           parallel=ParallelConfig(tp=2)))
         model = Llama(cfg); model.load_state_dict(state)
         model = engine.prepare(model)
-        (opt,) = engine.prepare_optimizers(build_muon_adamw(model))
-        assert opt.local.tensor_parallel_world == 2
-        loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=4))
+        (opt,) = engine.prepare_optimizers(build(model))
+        assert getattr(opt, "local", opt).tensor_parallel_world == 2
+        loader = engine.prepare_dataloaders(
+            DataLoader(dataset, batch_size=8 // engine.data_parallel_world_size))
         trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=1,
                           max_iters=3, eval_iters=0, save_ckpt_iters=0)
         trainer.train()
@@ -290,7 +301,7 @@ def test_muon_on_tensor_parallel_shards_matches_the_unsharded_step(tmp_path):
             print("TP_MUON_OK")
         engine.close()
         """,
-        4, tmp_path, port_base=32300,
+        world, tmp_path, port_base=32300,
     )
     assert "TP_MUON_OK" in out
 
@@ -354,9 +365,6 @@ def test_tensor_parallel_ranks_without_data_parallel_peers_are_not_treated_as_re
             2, tmp_path, port_base=29900,
         )
         assert "TP_ONLY_OK" in out
-
-
-import pytest
 
 
 @pytest.mark.parametrize("shard_parameters", [False, True])
