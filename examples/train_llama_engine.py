@@ -143,8 +143,9 @@ def parse_args() -> argparse.Namespace:
                           "(gathered just before a block runs) instead of the optimizer state "
                           "alone")
     run.add_argument("--shard-parameters-layout", choices=["auto", "even", "matrix"], default="auto",
-                     help="even: equal ranges (AdamW); matrix: whole matrices at one owner (Muon); "
-                          "auto picks by --optimizer")
+                     help="even: equal ranges (AdamW); matrix: whole matrices at one owner (Muon; "
+                          "AdamH / MuonH are not supported with sharded parameters); auto picks by "
+                          "--optimizer")
     run.add_argument("--activation-checkpointing", action="store_true",
                      help="recompute every block in the backward pass instead of keeping its "
                           "activations (less memory, about a third more compute)")

@@ -27,8 +27,9 @@ has nothing of the kind (``dp_shard`` is arithmetic only: ohara/runtime/topology
 
 Two layouts. ``"even"`` cuts a unit's concatenated parameters into equal ranges wherever the cut
 falls (least padding; element-wise optimizers such as AdamW). ``"matrix"`` places every parameter
-of a block inside one rank's range, so the owner of a matrix holds all of it and whole-matrix
-algorithms (Muon, AdamH / MuonH) run there without any gather, at the price of ranges as large as
+of a block inside one rank's range, so the owner of a matrix holds all of it and Muon runs
+there without any gather (the hyperspherical recipes are not supported: they also treat the
+output projection as a whole matrix, and the head is cut evenly), at the price of ranges as large as
 the fullest rank's share (up to about 2x padding for a block over 8 ranks); the embedding and the
 head, which those recipes update element-wise, are still cut evenly.
 
@@ -456,10 +457,16 @@ class ParameterShardedOptimizer(Optimizer):
                         if id(p) not in wanted:
                             continue
                         if off // unit.region != (off + n - 1) // unit.region:
+                            if unit.whole_tensors:
+                                raise RuntimeError(f"{unit.name}: a parameter straddles regions")
                             raise NotImplementedError(
-                                "a whole-matrix algorithm (Muon, AdamH / MuonH) needs every "
-                                "matrix at one owner: shard the parameters with the 'matrix' "
-                                "layout (EngineConfig(shard_parameters_layout='matrix'))")
+                                f"a whole-matrix algorithm needs every matrix of its groups at "
+                                f"one owner, but unit '{unit.name}' is cut evenly. Muon on the "
+                                f"blocks' matrices works with the 'matrix' layout "
+                                f"(EngineConfig(shard_parameters_layout='matrix')); the "
+                                f"hyperspherical recipes (AdamH / MuonH) also put the output "
+                                f"projection on a sphere, which the evenly cut head unit does "
+                                f"not support")
                         if lo <= off < hi:
                             shard = nn.Parameter(unit.master[off - lo : off - lo + n].view(shape),
                                                  requires_grad=True)
