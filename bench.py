@@ -338,6 +338,9 @@ def run_ours(args) -> dict:
         if spec["tp"] > 1 else TensorParallelPlan(),
         expert_capacity_factor=1.25 if spec["ep"] > 1 else 2.0,
         shard_parameters=bool(spec.get("shard_parameters")) and world_env > 1,
+        # the key/value exchange under the flash kernels needs peer memory; CPU ranks (functional
+        # checks at toy size) cut the sequence the same way and exchange with all-to-alls
+        context_parallel_mode="ring" if torch.cuda.is_available() else "ulysses",
     ))
     engine.launch()
     device = engine.device

@@ -85,6 +85,11 @@ def test_tiny_data_parallel_config_with_sharded_parameters_on_two_ranks():
     assert abs(plain["final_loss"] - sharded["final_loss"]) < 2e-3 * plain["final_loss"]
 
 
+def test_tiny_context_parallel_configuration_on_two_ranks():
+    line = _bench("--config", "cp8_32k", world=2, port=33300)
+    assert line["config"]["parallelism"] == "cp2" and 3.0 < line["final_loss"] < 8.0
+
+
 def test_tiny_expert_parallel_configuration_on_two_ranks():
     line = _bench("--config", "moe_ep8_skewed", world=2, port=32700)
     assert line["config"]["parallelism"] == "ep2"
