@@ -14,8 +14,8 @@ everything else about context parallelism (how a batch is cut, rotary positions,
 the sharded optimizer over the group) is shared between the two modes; after the first all-to-all
 the tokens are put into natural order with one gather so that the causal mask is the usual one.
 
-The reference has neither mode (SURVEY of its runtime: ``cp`` is arithmetic in
-ohara/runtime/topology.py:33-38 and nothing consumes it).
+The reference has neither mode (``cp`` is arithmetic in ohara/runtime/topology.py:33-38 and
+nothing consumes it).
 """
 
 from __future__ import annotations
