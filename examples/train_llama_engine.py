@@ -32,6 +32,7 @@ from ohara_b200.runtime import (
     EngineConfig,
     FaultToleranceConfig,
     ParallelConfig,
+    PipelinePlan,
     PrecisionConfig,
     PrecisionMode,
     StrategyType,
@@ -129,6 +130,12 @@ def parse_args() -> argparse.Namespace:
     run.add_argument("--tp", type=int, default=int(os.environ.get("OHARA_TP", "1")))
     run.add_argument("--cp", type=int, default=1)
     run.add_argument("--ep", type=int, default=1)
+    run.add_argument("--pp", type=int, default=1,
+                     help="pipeline stages (GPipe order through the trainer; needs --no-weight-tying)")
+    run.add_argument("--pp-micro-batch-size", type=int, default=1,
+                     help="sequences per pipeline micro-batch")
+    run.add_argument("--dp-replicate", type=int, default=1,
+                     help="with --strategy fsdp: replica groups of a hybrid-sharded run")
     run.add_argument("--sequence-parallel", action="store_true")
     run.add_argument("--strategy", choices=[s.value for s in StrategyType], default="auto")
     run.add_argument("--heartbeat-interval", type=float, default=0.0,
@@ -331,7 +338,10 @@ def run() -> None:
     engine = OharaEngine(EngineConfig(
         strategy=StrategyType(args.strategy),
         precision=PrecisionConfig(mode=PrecisionMode(args.precision)),
-        parallel=ParallelConfig(tp=args.tp, cp=args.cp, ep=args.ep),
+        parallel=ParallelConfig(tp=args.tp, cp=args.cp, ep=args.ep, pp=args.pp,
+                                dp_replicate=args.dp_replicate),
+        pipeline=(PipelinePlan(degree=args.pp, micro_batch_size=args.pp_micro_batch_size)
+                  if args.pp > 1 else PipelinePlan()),
         tensor_parallel=TensorParallelPlan.llama_default(args.tp, args.sequence_parallel),
         activation_checkpointing=args.activation_checkpointing,
         shard_parameters=args.shard_parameters,
