@@ -586,6 +586,12 @@ class OharaEngine:
             attach_fused_workspace(module, LazyTPWorkspace(self._groups.get("tp"), width))
             self._tp_batch_sharding = True
             self._tp_grads_synced = True
+        elif plan.sequence_parallel:
+            # The same layout over the process group's all-gather / reduce-scatter (CPU ranks, or
+            # fused collectives switched off): every tensor-parallel rank still keeps only its
+            # B / tp sequences between the parallel regions.
+            self._tp_batch_sharding = True
+            self._tp_grads_synced = True
         elif (self.config.fused_collectives and self._device.type == "cuda"
               and self.topology.tp <= 16 and dist.get_backend() == Backend.NCCL.value):
             # Plain tensor parallelism: the all-reduce that ends a row-parallel layer runs as a

@@ -4,8 +4,10 @@ The plan object and ``llama_default`` rules match the reference (ohara/runtime/t
 14-90): fnmatch patterns mapping module names to COLWISE / ROWWISE. The implementation does not use
 DTensor: matched ``nn.Linear`` modules are replaced in place by :class:`ColumnParallelLinear` /
 :class:`RowParallelLinear`, which keep the local weight shard under the same state-dict key and
-place the collectives explicitly (identity/all-reduce pairs, or all-gather/reduce-scatter pairs on
-the sequence dimension when ``sequence_parallel`` is on). Attention derives its local head count
+place the collectives explicitly (identity/all-reduce pairs, or, when ``sequence_parallel`` is on,
+all-gather/reduce-scatter pairs over token blocks: between the parallel regions every rank keeps
+``B / tp`` whole sequences, along dim 0, in the fused peer-memory form and in the process-group
+form alike). Attention derives its local head count
 from the projection width, so query and KV heads are split across ranks (GQA included).
 """
 
@@ -144,44 +146,54 @@ class _GatherFeatures(torch.autograd.Function):
         return grad[..., begin:begin + ctx.width].contiguous(), None
 
 
+def _reduce_scatter_blocks(x: Tensor, group) -> Tensor:
+    """Sum ``x`` over the group and keep this rank's block of dim 0 (gloo has no reduce-scatter:
+    there it is an all-reduce and a slice)."""
+    world = dist.get_world_size(group)
+    chunks = [c.contiguous() for c in x.chunk(world, dim=0)]
+    if dist.get_backend(group) == "gloo":
+        summed = x.contiguous().clone()
+        dist.all_reduce(summed, group=group)
+        return summed.chunk(world, dim=0)[dist.get_rank(group)].contiguous()
+    out = torch.empty_like(chunks[0])
+    dist.reduce_scatter(out, chunks, group=group)
+    return out
+
+
+def _gather_blocks(x: Tensor, group) -> Tensor:
+    world = dist.get_world_size(group)
+    parts = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(parts, x.contiguous(), group=group)
+    return torch.cat(parts, dim=0)
+
+
 class _GatherSequence(torch.autograd.Function):
-    """All-gather along dim 1 forward, reduce-scatter backward (sequence-parallel entry)."""
+    """Sequence-parallel entry over the process group: all-gather the ranks' token blocks along
+    dim 0 forward, reduce-scatter backward. The blocks are whole sequences (``B / tp`` of them per
+    rank), the same layout as the fused gather-GEMM, so the two paths are interchangeable."""
 
     @staticmethod
     def forward(ctx, x: Tensor, group):
         ctx.group = group
-        world = dist.get_world_size(group)
-        parts = [torch.empty_like(x) for _ in range(world)]
-        dist.all_gather(parts, x.contiguous(), group=group)
-        return torch.cat(parts, dim=1)
+        return _gather_blocks(x, group)
 
     @staticmethod
     def backward(ctx, grad: Tensor):
-        world = dist.get_world_size(ctx.group)
-        chunks = [c.contiguous() for c in grad.chunk(world, dim=1)]
-        out = torch.empty_like(chunks[0])
-        dist.reduce_scatter(out, chunks, group=ctx.group)
-        return out, None
+        return _reduce_scatter_blocks(grad, ctx.group), None
 
 
 class _ScatterSequence(torch.autograd.Function):
-    """Reduce-scatter along dim 1 forward, all-gather backward (sequence-parallel exit)."""
+    """Sequence-parallel exit: sum the partial products over the group and keep this rank's token
+    block of dim 0 forward, all-gather backward."""
 
     @staticmethod
     def forward(ctx, x: Tensor, group):
         ctx.group = group
-        world = dist.get_world_size(group)
-        chunks = [c.contiguous() for c in x.chunk(world, dim=1)]
-        out = torch.empty_like(chunks[0])
-        dist.reduce_scatter(out, chunks, group=group)
-        return out
+        return _reduce_scatter_blocks(x, group)
 
     @staticmethod
     def backward(ctx, grad: Tensor):
-        world = dist.get_world_size(ctx.group)
-        parts = [torch.empty_like(grad) for _ in range(world)]
-        dist.all_gather(parts, grad.contiguous(), group=ctx.group)
-        return torch.cat(parts, dim=1), None
+        return _gather_blocks(grad, ctx.group), None
 
 
 # --------------------------------------------------------------------------------------------------

@@ -518,3 +518,54 @@ def test_expert_parallel_training_on_cpu_ranks_matches_single_process_and_resume
         world, tmp_path, port_base=30500,
     )
     assert "EP_CPU_OK" in out
+
+
+@pytest.mark.parametrize("strategy,shard_parameters,world", [
+    ("FSDP", False, 4), ("DDP", False, 2), ("FSDP", True, 2)])
+def test_sequence_parallel_layout_over_the_process_group(tmp_path, strategy, shard_parameters, world):
+    """``sequence_parallel=True`` without peer memory: every tensor-parallel rank works on its
+    B / tp sequences between the parallel regions (the engine slices the batch and scales the
+    loss), column-parallel layers all-gather the token blocks, row-parallel layers reduce-scatter
+    them, and replicated parameters (norms, embedding) sum their partial gradients over the
+    group: under DDP, under the sharded optimizer and under sharded parameters (tp = world in the
+    two-rank cases, where the tensor-parallel group is the default group)."""
+    out = _run(
+        f"""
+        solo = Llama(cfg); solo.load_state_dict(state)
+        ref_opt = build_adamw(solo, learning_rate=0.02, weight_decay=0.1)
+        ref_norms = []
+        for _ in range(3):
+            loss = solo.loss_sum(ids[:, :-1], ids[:, 1:]) / ids[:, 1:].numel()
+            loss.backward()
+            ref_norms.append(float(torch.nn.utils.clip_grad_norm_(solo.parameters(), 0.5)))
+            ref_opt.step(); ref_opt.zero_grad()
+        engine = OharaEngine(EngineConfig(
+            strategy=StrategyType.{strategy}, shard_parameters={shard_parameters},
+            parallel=ParallelConfig(tp=2),
+            tensor_parallel=TensorParallelPlan.llama_default(2, sequence_parallel=True)))
+        model = Llama(cfg); model.load_state_dict(state)
+        model = engine.prepare(model)
+        (opt,) = engine.prepare_optimizers(build_adamw(model, learning_rate=0.02, weight_decay=0.1))
+        batch = 8 // engine.data_parallel_world_size
+        local = engine.local_batch((ids[:batch, :-1], ids[:batch, 1:]))
+        assert local[0].shape[0] == batch // 2                      # this rank's sequences
+        loader = engine.prepare_dataloaders(DataLoader(dataset, batch_size=batch))
+        trainer = Trainer(engine, model, opt, loader, loader, Scheduler(0.02), micro_batch=1,
+                          max_iters=3, eval_iters=0, save_ckpt_iters=0, grad_clip_norm=0.5)
+        norms = []
+        clip = engine.clip_gradients
+        def recording(m, o, max_norm):
+            value = clip(m, o, max_norm); norms.append(float(value)); return value
+        engine.clip_gradients = recording
+        trainer.train()
+        assert all(abs(a - b) < 1e-4 * max(1.0, b) for a, b in zip(norms, ref_norms)), (norms, ref_norms)
+        full = engine.full_state_dict(model)
+        for name, value in solo.state_dict().items():
+            assert torch.allclose(full[name], value, atol=3e-5), (name, (full[name] - value).abs().max())
+        if dist.get_rank() == 0:
+            print("SP_C10D_OK")
+        engine.close()
+        """,
+        world, tmp_path, port_base=30700,
+    )
+    assert "SP_C10D_OK" in out
