@@ -137,14 +137,13 @@ def test_pretraining_example_trains_saves_and_resumes(tmp_path):
 
 
 @pytest.mark.parametrize("layout", [
-    ["--strategy", "fsdp", "--shard-parameters", "--optimizer", "adamw", "--activation-checkpointing"],
     ["--strategy", "ddp"],
     ["--strategy", "fsdp", "--pp", "2", "--optimizer", "adamw"],
 ])
 def test_pretraining_example_on_two_ranks_saves_and_resumes(tmp_path, layout):
-    """The same script under torchrun on two CPU ranks: sharded parameters with recomputed
-    blocks under the sharded strategy, plain DDP (whose wrapper must take the wrapper-free
-    checkpoint back), and two pipeline stages (whose checkpoint is the whole model)."""
+    """The same script under torchrun on two CPU ranks: plain DDP (whose wrapper must take the
+    wrapper-free checkpoint back) and two pipeline stages (whose checkpoint is the whole
+    model)."""
     checkpoint = tmp_path / "ckpt" / "model.pt"
     command = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                "--master-addr", "127.0.0.1", "--master-port", str(32500 + os.getpid() % 300),

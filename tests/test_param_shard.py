@@ -395,7 +395,6 @@ engine.close()
     (4, 1, 2, True, False, 1), (2, 2, 1, True, False, 1),
     (4, 1, 1, True, False, 2),  # hybrid sharding: two replicas of a two-way sharded model
     (4, 2, 1, True, True, 1),   # sharded parameters + recomputed blocks under tensor parallelism
-    (2, 1, 2, False, True, 1),  # ... and with the all-to-alls of context parallelism inside
 ])
 def test_sharded_parameters_compose_with_tensor_and_context_parallelism(tmp_path, world, tp, cp,
                                                                         shard, recompute, replicas):
