@@ -196,6 +196,8 @@ class LlamaStage(nn.Module):
         self.vocab_proj = model.vocab_proj if self.is_last else None
         self.register_buffer("freq_cos", model.freq_cos, persistent=False)
         self.register_buffer("freq_sin", model.freq_sin, persistent=False)
+        # recompute the blocks in the backward pass if the model was asked to
+        self.activation_checkpointing = bool(getattr(model, "activation_checkpointing", False))
 
     def hidden(self, x: Tensor) -> Tensor:
         """Hidden states leaving this stage (after the final norm on the last stage)."""
@@ -207,8 +209,14 @@ class LlamaStage(nn.Module):
             raise ValueError("input exceeds max_sequence_length")
         freqs = (self.freq_cos[:seq], self.freq_sin[:seq])
         pending = None  # residual branch output not yet added: fused into the next norm
+        recompute = self.activation_checkpointing and self.training and torch.is_grad_enabled()
         for layer in self.layers:
-            h, pending = layer.forward_deferred(h, pending, freqs, None, None)
+            if recompute:
+                from ohara_b200.models.llama import _checkpointed_block
+
+                h, pending = _checkpointed_block(layer, h, pending, freqs)
+            else:
+                h, pending = layer.forward_deferred(h, pending, freqs, None, None)
         if self.is_last:
             return ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[0]
         return h if pending is None else h + pending

@@ -107,12 +107,13 @@ def test_llama_split_in_three_stages_matches_the_whole_model(tmp_path):
                      num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=5, dropout=0.0,
                      weight_tying=False)
         torch.manual_seed(0)
-        full = Llama(cfg)
+        full = Llama(cfg).enable_activation_checkpointing()   # stages recompute their blocks too
         ids = torch.randint(0, 96, (8, 25))
         x, y = ids[:, :-1], ids[:, 1:]
         micro = 4
         xs, ys = x.chunk(micro), y.chunk(micro)
         stage = LlamaStage(full, world, rank)
+        assert stage.activation_checkpointing
         reference = sum(stage.loss(full(a), b) for a, b in zip(xs, ys)) / micro
         reference.backward()
         expected = {name: p.grad.clone() for name, p in full.named_parameters()}
