@@ -202,6 +202,9 @@ class OharaEngine:
         self._dp_world_size = self.topology.dp_world_size * self.topology.ep if data_parallel else 1
         self._dp_rank = (self.topology.dp_rank * self.topology.ep + self.topology.ep_rank
                          if data_parallel else 0)
+        if self.config.shard_parameters and strategy != StrategyType.FSDP:
+            raise ValueError("shard_parameters needs the sharded strategy (StrategyType.FSDP); "
+                             f"this engine resolved to {strategy.value!r}")
         if strategy == StrategyType.DDP:
             self._strategy = DDPStrategy(init_sync=not self.topology.tp_enabled)
         elif strategy == StrategyType.FSDP:
