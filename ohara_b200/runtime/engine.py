@@ -492,7 +492,7 @@ class OharaEngine:
         layers = [m for m in module.modules() if isinstance(m, GroupedMoE)]
         if not layers:
             raise ValueError("ep > 1 but the model has no grouped mixture-of-experts layer")
-        peer_memory = self._device.type == "cuda"
+        peer_memory = self._device.type == "cuda" and self.config.fused_collectives
         shared: dict[tuple[int, int], Any] = {}
         for index, layer in enumerate(layers):
             key = (layer.num_experts, layer.dim)
@@ -500,7 +500,8 @@ class OharaEngine:
                 shared[key] = LazyEPWorkspace(self._groups.get("ep"), layer.num_experts, layer.dim,
                                               self.config.expert_capacity_factor)
             elif key not in shared:
-                # no peer memory (CPU ranks): the same layer over the group's all-to-all
+                # no peer memory (CPU ranks, or fused collectives switched off): the same layer
+                # over the group's all-to-all
                 from ohara_b200.parallel.ep_c10d import C10dEPWorkspace
 
                 shared[key] = C10dEPWorkspace(self._groups.get("ep"), layer.num_experts)
