@@ -15,8 +15,9 @@ keeps, between uses, only ``1 / world`` of every parameter:
   is released;
 * when the last gradient of a unit has been accumulated, the unit's gradients are packed,
   reduce-scattered (mean) and added to the rank's fp32 gradient shard, and the full gradients are
-  dropped. Every parameter of a unit must therefore receive a gradient on every rank in every
-  backward pass (true for the dense and the grouped-MoE Llama).
+  dropped. A unit some of whose parameters may stay without a gradient on some ranks (the loop
+  MoE: experts no token chose) is reduced at the end of the backward pass instead, by every rank
+  in turn.
 
 At most two units are gathered at a time (three around the hand-over), so the parameter memory of a
 rank is ``total / world`` plus about two blocks instead of ``total``.
@@ -100,6 +101,11 @@ class _Unit:
         self.full: Tensor | None = None          # gathered vector while the unit is unsharded
         self.work: Any | None = None             # pending all-gather
         self.bound = False                       # parameters point at ``full``
+        # Some parameters may get no gradient on some ranks (experts no token chose): the ranks
+        # then cannot agree, from their own gradients, on when the unit is complete, so its
+        # reduction waits for the end of the backward pass, where every rank does it in turn.
+        self.deferred = False
+        self.used = False                        # ran in a forward pass with gradients enabled
         self.trainable = sum(1 for p in params if p.requires_grad)
         self.remaining = self.trainable          # gradients still to come in this backward pass
         self.placeholders = [torch.zeros(1, device=device, dtype=torch.float32).expand(shape)
@@ -253,6 +259,7 @@ class ParameterSharding:
             self._issue(following, asynchronous=True)
         out = fn(*args)
         if torch.is_grad_enabled():
+            unit.used = True
             # backward of the marker runs before the unit's own backward: gather (a unit that
             # stayed gathered is there already) and prefetch the unit before it
             single = isinstance(out, Tensor)
@@ -278,14 +285,16 @@ class ParameterSharding:
     def _on_gradient(self, param: nn.Parameter) -> None:
         unit = self.unit_of_param[id(param)]
         unit.remaining -= 1
-        if unit.remaining == 0:
+        if unit.remaining == 0 and not unit.deferred:
             self._reduce(unit)
 
     @torch.no_grad()
-    def _reduce(self, unit: _Unit) -> None:
+    def _reduce(self, unit: _Unit, always: bool = False) -> None:
         """Pack the unit's gradients, reduce-scatter the mean into this rank's gradient shard,
-        drop the full gradients and release the unit."""
-        if unit.trainable and any(p.grad is not None for p in unit.params):
+        drop the full gradients and release the unit. ``always``: take part in the collective
+        even if this rank has no gradient for the unit (its peers may)."""
+        unit.used = False
+        if unit.trainable and (always or any(p.grad is not None for p in unit.params)):
             flat = torch.zeros(unit.total, device=unit.master.device, dtype=torch.float32)
             for p, off, n in zip(unit.params, unit.offsets, unit.numels):
                 if p.grad is not None:
@@ -316,7 +325,9 @@ class ParameterSharding:
         """After ``backward()``: units whose gradients did not all arrive (unused parameters), or
         that were gathered by a prefetch and never used, are reduced and released here."""
         for unit in reversed(self.units):
-            if unit.full is not None or unit.remaining != unit.trainable:
+            if unit.deferred and unit.used:
+                self._reduce(unit, always=True)
+            elif unit.full is not None or unit.remaining != unit.trainable:
                 self._reduce(unit)
 
     def release_all(self) -> None:
@@ -382,13 +393,13 @@ def shard_llama(model: nn.Module, group=None, prefetch: bool = True, solo: bool 
         units.append(("embed", list(model.token_emb.parameters())))
     from ohara_b200.modules.moe import MoE
 
+    deferred: list[str] = []
     for index, layer in enumerate(model.layers):
-        if any(isinstance(m, MoE) for m in layer.modules()):
-            # an expert no token of this rank chose gets no gradient, and the ranks would then
-            # disagree on when the unit's reduce-scatter runs
-            raise NotImplementedError("parameter sharding needs every parameter to receive a "
-                                      "gradient on every rank: use the grouped MoE")
         units.append((f"layers.{index}", list(layer.parameters())))
+        if any(isinstance(m, MoE) for m in layer.modules()):
+            # an expert no token of this rank chose gets no gradient: reduce at the end of the
+            # backward pass, when every rank knows the unit is as complete as it will get
+            deferred.append(f"layers.{index}")
     if len(model.layers) > 0:
         # the last block's backward starts right after its forward: keep it gathered
         keep.append(f"layers.{len(model.layers) - 1}")
@@ -406,6 +417,8 @@ def shard_llama(model: nn.Module, group=None, prefetch: bool = True, solo: bool 
     sharding = ParameterSharding(units, group, keep_gathered=keep, prefetch=prefetch, solo=solo,
                                  replicate_group=replicate_group, replicate_world=replicate_world,
                                  whole_tensor_units=whole)
+    for name in deferred:
+        sharding.by_name[name].deferred = True
     sharding.tied = tied
     model._param_sharding = sharding
     return sharding

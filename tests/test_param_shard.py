@@ -110,11 +110,10 @@ def test_evaluation_pass_releases_the_blocks():
     assert all(u.full is None for u in sharding.units)
 
 
-def test_loop_moe_is_rejected_and_muon_runs_on_one_process_with_either_layout():
+def test_loop_moe_units_are_deferred_and_muon_runs_on_one_process_with_either_layout():
     torch.manual_seed(0)
     loop = Llama(_config(moe_num_experts=4, moe_experts_per_tok=2))
-    with pytest.raises(NotImplementedError):
-        shard_llama(loop)
+    assert all(u.deferred == u.name.startswith("layers.") for u in shard_llama(loop).units)
     with pytest.raises(ValueError):
         shard_llama(Llama(_config()), layout="diagonal")
     # one process owns everything, so whole-matrix groups are fine whatever the layout
@@ -485,3 +484,61 @@ def test_muon_on_sharded_parameters_matches_single_process_and_resumes(tmp_path,
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "MUON_SHARDED_OK" in proc.stdout
+
+
+LOOP_MOE_WORKER = """
+import torch, torch.distributed as dist
+from ohara_b200.models.llama import Config, Llama
+from ohara_b200.runtime import EngineConfig, OharaEngine, StrategyType
+from ohara_b200.optimizer import build_adamw
+
+torch.manual_seed(0)
+cfg = Config(vocab_size=31, max_sequence_length=8, hidden_size=16, intermediate_size=24,
+             num_attention_heads=2, num_hidden_layers=2, dropout=0.0, moe_num_experts=6,
+             moe_experts_per_tok=1, moe_quantile_balancing=False)
+ids = torch.randint(0, 31, (2, 5))                      # one short sequence per rank
+state = {k: v.clone() for k, v in Llama(cfg).state_dict().items()}
+solo = Llama(cfg); solo.load_state_dict(state)
+ref_opt = build_adamw(solo, learning_rate=0.02, weight_decay=0.0)
+engine = OharaEngine(EngineConfig(strategy=StrategyType.FSDP, shard_parameters=True))
+model = Llama(cfg); model.load_state_dict(state)
+model = engine.prepare(model)
+(opt,) = engine.prepare_optimizers(build_adamw(model, learning_rate=0.02, weight_decay=0.0))
+rank = dist.get_rank()
+model.train(); solo.train()
+idle = 0
+for _ in range(3):
+    loss = solo.loss_sum(ids[:, :-1], ids[:, 1:]) / ids[:, 1:].numel()
+    loss.backward()
+    for p in solo.parameters():      # a reduced gradient is zero, not absent, for an idle expert
+        if p.grad is None:
+            p.grad = torch.zeros_like(p)
+    ref_opt.step(); ref_opt.zero_grad()
+    mine = ids[rank:rank + 1]
+    loss = model(mine[:, :-1], targets=mine[:, 1:]) / mine[:, 1:].numel()
+    engine.backward(loss)
+    opt.step(); opt.zero_grad()
+from ohara_b200.modules.routing import expert_load
+idle = sum(int((counts == 0).sum()) for counts in expert_load(model))
+assert idle > 0, "every expert was used: the case under test did not occur"
+full = engine.full_state_dict(model)
+for name, value in solo.state_dict().items():
+    assert torch.allclose(full[name], value, atol=3e-5), (name, (full[name] - value).abs().max())
+if rank == 0:
+    print("LOOP_MOE_SHARDED_OK")
+engine.close()
+"""
+
+
+def test_experts_without_tokens_on_a_rank_do_not_desynchronise_the_reduction(tmp_path):
+    """Loop MoE, one routed expert per token, four tokens per rank and six experts: on every rank
+    some experts get no gradient. Their blocks are reduced at the end of the backward pass by
+    every rank in turn, and training follows the single-process run."""
+    path = tmp_path / "worker.py"
+    path.write_text(textwrap.dedent(LOOP_MOE_WORKER))
+    env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(32200 + os.getpid() % 150), str(path)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "LOOP_MOE_SHARDED_OK" in proc.stdout
