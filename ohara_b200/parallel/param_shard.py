@@ -382,6 +382,8 @@ def shard_llama(model: nn.Module, group=None, prefetch: bool = True, solo: bool 
     gathers and releases the units as it goes."""
     if not all(hasattr(model, name) for name in ("token_emb", "layers", "norm", "vocab_proj")):
         raise ValueError("parameter sharding needs a Llama-style model")
+    if getattr(model, "_param_sharding", None) is not None:
+        raise RuntimeError("this model's parameters are sharded already")
     tied = model.vocab_proj.weight is model.token_emb.weight
     units: list[tuple[str, list[nn.Parameter]]] = []
     keep = ["head"]
