@@ -500,8 +500,8 @@ def run_ours(args) -> dict:
         from ohara_b200.modules.routing import expert_load
 
         counts = expert_load(model)
-        if counts:
-            total = torch.stack([c.float() for c in counts]).sum(0)
+        if counts is not None:
+            total = counts.float().sum(0)
             if dist.is_initialized():
                 dist.all_reduce(total)
             top = total.topk(min(8, total.numel())).values.sum() / total.sum().clamp_min(1)

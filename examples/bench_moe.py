@@ -94,8 +94,8 @@ def benchmark(model: Llama, args, peak: float, *, moe: bool) -> dict[str, float]
            "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9}
     if moe:
         per_layer = expert_load(model, reset=False)
-        if per_layer:
-            row["maxvio"] = sum(maximal_violation(c) for c in per_layer) / len(per_layer)
+        if per_layer is not None:
+            row["maxvio"] = float(maximal_violation(per_layer).mean())
     del optimizer, model
     torch.cuda.empty_cache()
     return row

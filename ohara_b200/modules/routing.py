@@ -190,19 +190,22 @@ def apply_qb_update(module: nn.Module) -> None:
             layer.apply_qb_update()
 
 
-def expert_load(module: nn.Module, reset: bool = True) -> list[Tensor]:
-    """Tokens routed to each expert since the last reset, one tensor per MoE layer."""
-    return [
+def expert_load(module: nn.Module, reset: bool = True) -> Tensor | None:
+    """Tokens routed to each expert since the last reset for every MoE layer of ``module``,
+    stacked ``(num_moe_layers, num_experts)``; ``None`` without MoE layers (reference:
+    ohara/modules/moe.py:194-203)."""
+    counts = [
         layer.expert_load(reset=reset)
         for layer in module.modules()
         if isinstance(layer, QuantileBalancedRouter)
     ]
+    return torch.stack(counts) if counts else None
 
 
-def maximal_violation(counts: Tensor) -> float:
-    """MaxVio = max_e load_e / mean load − 1; zero means perfectly balanced."""
+def maximal_violation(counts: Tensor) -> Tensor:
+    """MaxVio = max_e load_e / mean load − 1 along the last dimension (one value per layer for a
+    stacked count table); zero means perfectly balanced. Rows without any token give zero."""
     counts = counts.float()
-    mean = counts.mean()
-    if mean <= 0:
-        return 0.0
-    return float((counts.max() - mean) / mean)
+    mean = counts.mean(dim=-1, keepdim=True)
+    violation = (counts.max(dim=-1, keepdim=True).values - mean) / mean.clamp_min(1e-12)
+    return torch.where(mean > 0, violation, torch.zeros_like(violation)).squeeze(-1)

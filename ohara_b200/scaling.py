@@ -448,7 +448,7 @@ def write_scaling_svg(path: str | Path, rows: Sequence[Mapping[str, float]],
         '.grid{stroke:#e5e7eb;stroke-width:1}</style>',
     ]
     log_p = [math.log10(float(r["params_effective"])) for r in usable]
-    p1 = _Panel(65, 55, 340, 290, f"iso-FLOP curves ({metric})", "log10 effective parameters",
+    p1 = _Panel(65, 55, 340, 290, f"Iso-FLOP curves ({metric})", "log10 effective parameters",
                 metric, log_p, [float(r[metric]) for r in usable])
     svg += p1.frame()
     for index, budget in enumerate(budgets):

@@ -145,3 +145,14 @@ def tokenizer_info(tokenizer) -> dict[str, Any]:
         "bos_token_id": tokenizer.bos_token_id,
         "special_tokens": list(getattr(tokenizer, "all_special_tokens", []) or []),
     }
+
+
+def __getattr__(name: str):
+    """``AutoTokenizer`` is reachable as an attribute of this module, as in the reference (where
+    it is imported at the top: ohara/tokenizer.py), without importing ``transformers`` until it
+    is asked for."""
+    if name == "AutoTokenizer":
+        from transformers import AutoTokenizer
+
+        return AutoTokenizer
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

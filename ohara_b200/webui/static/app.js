@@ -3,7 +3,7 @@
 "use strict";
 
 const $ = (id) => document.getElementById(id);
-const transcript = $("transcript");
+const transcript = $("messages");
 const knobs = ["temperature", "top_p", "top_k", "max_new_tokens"];
 let messages = [];
 let controller = null;
@@ -114,7 +114,7 @@ async function send(text) {
   }
 }
 
-$("composer").addEventListener("submit", (event) => {
+$("composer-form").addEventListener("submit", (event) => {
   event.preventDefault();
   const text = $("prompt").value.trim();
   if (!text || controller) return;
@@ -124,7 +124,7 @@ $("composer").addEventListener("submit", (event) => {
 $("prompt").addEventListener("keydown", (event) => {
   if (event.key === "Enter" && !event.shiftKey) {
     event.preventDefault();
-    $("composer").requestSubmit();
+    $("composer-form").requestSubmit();
   }
 });
 $("stop").addEventListener("click", () => controller && controller.abort());
