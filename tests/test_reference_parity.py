@@ -1,0 +1,200 @@
+"""Every model family against the reference package itself, when it is installed next to the
+baseline (``baseline/_ref``): identical state-dict keys and shapes, and, loaded with the
+reference's weights, identical outputs on the fp32 CPU path."""
+
+import dataclasses
+import importlib
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+REFERENCE = ROOT / "baseline" / "_ref"
+pytestmark = pytest.mark.skipif(not (REFERENCE / "ohara").is_dir(),
+                                reason="reference package is not installed")
+
+FAMILIES = {"llama": ("Config", "Llama"), "gpt": ("Config", "GPT"), "gemma": ("GemmaConfig", "Gemma"),
+            "phi": ("PhiConfig", "Phi"), "retnet": ("Config", "RetNet"),
+            "roformer": ("Config", "RoFormer"), "transformer": ("Config", "ModelingLM")}
+SMALL = {"vocab": 128, "layers": 2, "width": 64, "ffn": 128, "heads": 4, "kv_heads": 2,
+         "head_dim": 16, "context": 32}
+
+
+@pytest.fixture(scope="module")
+def reference_on_path():
+    added = [str(ROOT / "baseline" / "stubs"), str(REFERENCE)]
+    sys.path[:0] = added
+    yield
+    for entry in added:
+        sys.path.remove(entry)
+
+
+def _small(config_class) -> dict:
+    """Toy sizes for whatever this family calls its fields."""
+    chosen = {}
+    for field in dataclasses.fields(config_class):
+        name = field.name.lower()
+        if "vocab" in name:
+            chosen[field.name] = SMALL["vocab"]
+        elif name in ("num_hidden_layers", "num_layers", "n_layers", "n_layer"):
+            chosen[field.name] = SMALL["layers"]
+        elif name in ("hidden_size", "d_model", "dim", "n_embd"):
+            chosen[field.name] = SMALL["width"]
+        elif name in ("intermediate_size", "hidden_dim"):
+            chosen[field.name] = SMALL["ffn"]
+        elif name in ("num_attention_heads", "num_heads", "n_head", "n_heads"):
+            chosen[field.name] = SMALL["heads"]
+        elif name in ("num_key_value_heads", "num_kv_heads"):
+            chosen[field.name] = SMALL["kv_heads"]
+        elif name == "head_dim":
+            chosen[field.name] = SMALL["head_dim"]
+        elif "seq" in name or name in ("block_size", "max_position_embeddings"):
+            chosen[field.name] = SMALL["context"]
+    return chosen
+
+
+@pytest.mark.parametrize("family", sorted(FAMILIES))
+def test_family_has_the_reference_layout_and_reproduces_its_outputs(reference_on_path, family):
+    config_name, model_name = FAMILIES[family]
+    theirs = importlib.import_module(f"ohara.models.{family}")
+    ours = importlib.import_module(f"ohara_b200.models.{family}")
+    sizes = _small(getattr(theirs, config_name))
+    torch.manual_seed(0)
+    reference = getattr(theirs, model_name)(getattr(theirs, config_name)(**sizes)).eval()
+    model = getattr(ours, model_name)(getattr(ours, config_name)(**sizes)).eval()
+    want, have = reference.state_dict(), model.state_dict()
+    assert set(want) == set(have)
+    assert all(tuple(want[k].shape) == tuple(have[k].shape) for k in want)
+    model.load_state_dict(want)
+    tokens = torch.randint(0, SMALL["vocab"], (2, 8))
+    with torch.no_grad():
+        a, b = reference(tokens), model(tokens)
+    a, b = (a[0] if isinstance(a, tuple) else a), (b[0] if isinstance(b, tuple) else b)
+    torch.testing.assert_close(b, a, rtol=1e-5, atol=2e-6)
+
+
+def test_mamba_layers_and_their_recurrent_step_reproduce_the_reference(reference_on_path):
+    theirs = importlib.import_module("ohara.models.mamba")
+    ours = importlib.import_module("ohara_b200.models.mamba")
+    torch.manual_seed(0)
+    reference = theirs.Mamba(theirs.MambaConfig(d_model=64, n_layers=2)).eval()
+    model = ours.Mamba(ours.MambaConfig(d_model=64, n_layers=2)).eval()
+    model.load_state_dict(reference.state_dict())
+    x = torch.randn(2, 8, 64)
+
+    def stepwise(m):
+        caches = [(None, torch.zeros(2, m.config.d_inner, m.config.d_conv - 1))
+                  for _ in range(m.config.n_layers)]
+        outputs = []
+        for t in range(x.shape[1]):
+            y, caches = m.step(x[:, t], caches)
+            outputs.append(y)
+        return torch.stack(outputs, 1)
+
+    with torch.no_grad():
+        torch.testing.assert_close(model(x), reference(x), rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(stepwise(model), stepwise(reference), rtol=1e-5, atol=2e-6)
+        torch.testing.assert_close(stepwise(model), model(x), rtol=1e-4, atol=2e-6)
+
+
+def _twin_llamas(**extra):
+    theirs = importlib.import_module("ohara.models.llama")
+    ours = importlib.import_module("ohara_b200.models.llama")
+    sizes = dict(vocab_size=96, max_sequence_length=32, hidden_size=48, intermediate_size=96,
+                 num_attention_heads=4, num_key_value_heads=2, num_hidden_layers=2, dropout=0.0,
+                 weight_tying=False, **extra)
+    torch.manual_seed(0)
+    reference = theirs.Llama(theirs.Config(**sizes))
+    model = ours.Llama(ours.Config(**sizes))
+    model.load_state_dict(reference.state_dict())
+    return reference, model
+
+
+@pytest.mark.parametrize("builder", ["build_adamw", "build_muon_adamw", "build_adamh",
+                                     "build_muonh_adamh"])
+def test_optimizer_recipes_follow_the_reference_step_for_step(reference_on_path, builder):
+    theirs = importlib.import_module("ohara.optimizer")
+    ours = importlib.import_module("ohara_b200.optimizer")
+    reference, model = _twin_llamas()
+    kwargs = dict(learning_rate=3e-3, weight_decay=0.1) if builder == "build_adamw" else {}
+    optimizers = (getattr(theirs, builder)(reference, **kwargs), getattr(ours, builder)(model, **kwargs))
+    assert [(g.get("name"), g.get("kind"), len(g["params"])) for g in optimizers[0].param_groups] == \
+        [(g.get("name"), g.get("kind"), len(g["params"])) for g in optimizers[1].param_groups]
+    tokens = torch.randint(0, 96, (4, 17))
+    for _ in range(3):
+        for net, optimizer in zip((reference, model), optimizers):
+            logits = net(tokens[:, :-1])
+            loss = torch.nn.functional.cross_entropy(logits.flatten(0, 1), tokens[:, 1:].flatten())
+            optimizer.zero_grad(set_to_none=True)
+            loss.backward()
+            optimizer.step()
+    # (entries whose gradient is of the order of Adam's epsilon, behind the zero-initialised
+    # output projections, differ by a fraction of a percent of one learning-rate-sized step
+    # between formulations of the same update)
+    for (name, want), have in zip(reference.state_dict().items(), model.state_dict().values()):
+        torch.testing.assert_close(have, want, rtol=1e-4, atol=5e-5, msg=name)
+
+
+@pytest.mark.parametrize("grouped", [False, True])
+def test_mixture_of_experts_models_route_and_balance_like_the_reference(reference_on_path, grouped):
+    reference, model = _twin_llamas(moe_num_experts=4, moe_experts_per_tok=2, moe_grouped=grouped,
+                                    **({"moe_num_shared_experts": 1} if grouped else {}))
+    with torch.no_grad():   # the routed output projections start at zero: give them values
+        for name, p in reference.named_parameters():
+            if name.endswith("w_down") or ".down.weight" in name:
+                p.normal_(std=0.05)
+    model.load_state_dict(reference.state_dict())
+    theirs_moe = importlib.import_module("ohara.modules.moe")
+    ours_moe = importlib.import_module("ohara_b200.modules.moe")
+    tokens = torch.randint(0, 96, (3, 12))
+    reference.train(), model.train()
+    for step in range(3):
+        with torch.no_grad():
+            a, b = reference(tokens), model(tokens)
+        # a token whose two best experts are tied to within rounding may be routed differently;
+        # every other token must agree
+        same = (a - b).abs().amax(-1) <= 2e-5
+        assert (step > 0 or bool(same.all())) and float(same.float().mean()) >= 0.9
+        theirs_moe.apply_qb_update(reference)
+        ours_moe.apply_qb_update(model)
+        for theirs_block, ours_block in zip(reference.layers, model.layers):
+            torch.testing.assert_close(ours_block.ff.router_bias, theirs_block.ff.router_bias,
+                                       rtol=1e-3, atol=1e-5)
+    loads = ours_moe.expert_load(model), theirs_moe.expert_load(reference)
+    assert loads[0].shape == loads[1].shape and int(loads[0].sum()) == int(loads[1].sum())
+    assert float((loads[0] - loads[1]).abs().sum()) <= 0.1 * float(loads[1].sum())
+
+
+def test_chat_rendering_and_sampling_agree_with_the_reference(reference_on_path):
+    theirs_chat = importlib.import_module("ohara.chat")
+    ours_chat = importlib.import_module("ohara_b200.chat")
+    theirs_engine = importlib.import_module("ohara.chat_engine")
+    ours_engine = importlib.import_module("ohara_b200.chat_engine")
+    assert theirs_chat.CHAT_SPECIAL_TOKENS == ours_chat.CHAT_SPECIAL_TOKENS
+    sys.path.insert(0, str(ROOT / "tests"))
+    from helpers import chat_tokenizer
+
+    tokenizer = chat_tokenizer()
+    messages = [
+        {"role": "system", "content": "be brief"}, {"role": "user", "content": "two plus two"},
+        {"role": "assistant", "content": [{"type": "text", "text": "let me see "},
+                                          {"type": "python", "text": "2+2"},
+                                          {"type": "python_output", "text": "4"},
+                                          {"type": "text", "text": "four"}]},
+        {"role": "user", "content": "thanks"}, {"role": "assistant", "content": "welcome"}]
+    for limit in (2048, 12):
+        assert ours_chat.render_conversation(tokenizer, messages, max_tokens=limit) == \
+            theirs_chat.render_conversation(tokenizer, messages, max_tokens=limit)
+    assert ours_chat.render_for_completion(tokenizer, messages) == \
+        theirs_chat.render_for_completion(tokenizer, messages)
+    logits = torch.randn(3, 2, 50, generator=torch.Generator().manual_seed(0))   # (batch, seq, vocab)
+    for settings in (dict(temperature=0.0), dict(temperature=0.8, top_k=5),
+                     dict(temperature=1.2, top_p=0.7), dict(temperature=1.0, top_k=10, top_p=0.9)):
+        picks = []
+        for module in (theirs_engine, ours_engine):
+            config = module.SamplingConfig(max_new_tokens=4, **settings)
+            generator = torch.Generator().manual_seed(5)
+            picks.append(module.sample_next_token(logits, config, generator))
+        assert torch.equal(picks[0], picks[1]), settings
