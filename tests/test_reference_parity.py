@@ -198,3 +198,88 @@ def test_chat_rendering_and_sampling_agree_with_the_reference(reference_on_path)
             generator = torch.Generator().manual_seed(5)
             picks.append(module.sample_next_token(logits, config, generator))
         assert torch.equal(picks[0], picks[1]), settings
+
+
+def test_planner_packer_and_token_files_are_interchangeable(reference_on_path, tmp_path):
+    import dataclasses as dc
+
+    theirs_scaling = importlib.import_module("ohara.scaling")
+    ours_scaling = importlib.import_module("ohara_b200.scaling")
+    for depth, budget in ((6, 1e15), (12, 3e17), (20, 1e19)):
+        plans = [module.plan_scaling_run(depth=depth, flops_budget=budget, vocab_size=50304,
+                                         sequence_length=1024, world_size=8)
+                 for module in (theirs_scaling, ours_scaling)]
+        assert dc.asdict(plans[0]) == dc.asdict(plans[1])
+
+    sys.path.insert(0, str(ROOT / "tests"))
+    from helpers import chat_tokenizer
+
+    tokenizer = chat_tokenizer()
+    conversations = [{"messages": [
+        {"role": "user", "content": " ".join(f"w{i * 7 + j}" for j in range(3 + i % 5))},
+        {"role": "assistant", "content": " ".join(f"a{i + j}" for j in range(2 + i % 7))}]}
+        for i in range(40)]
+    packed = []
+    for name in ("ohara.sft", "ohara_b200.sft"):
+        dataset = importlib.import_module(name).ConversationDataset(
+            conversations, tokenizer, max_length=32, seed=3, data_rank=1, data_world_size=2)
+        rows = iter(dataset)
+        packed.append([next(rows) for _ in range(6)])
+    for (x_a, y_a), (x_b, y_b) in zip(*packed):
+        assert torch.equal(x_a, x_b) and torch.equal(y_a, y_b)
+
+    theirs_bin = importlib.import_module("ohara.tokenbin")
+    ours_bin = importlib.import_module("ohara_b200.tokenbin")
+    documents = [" ".join(f"t{(i * 13 + j) % 90}" for j in range(5 + i % 9)) for i in range(60)]
+    written = {}
+    for label, module in (("theirs", theirs_bin), ("ours", ours_bin)):
+        path = tmp_path / f"{label}.bin"
+        module.write_token_bin(documents, tokenizer, path, log=False)
+        written[label] = path
+    assert written["theirs"].read_bytes() == written["ours"].read_bytes()
+    assert theirs_bin.read_token_bin_metadata(written["ours"]) == \
+        ours_bin.read_token_bin_metadata(written["theirs"])
+    blocks = []
+    for module, path in ((theirs_bin, written["ours"]), (ours_bin, written["theirs"])):
+        dataset = module.TokenBinDataset(path, max_length=16, shuffle=True, seed=7, infinite=False)
+        blocks.append([tuple(t.tolist() for t in pair) for pair in dataset])
+    assert blocks[0] == blocks[1] and len(blocks[0]) > 3
+
+
+def test_trainer_and_generation_follow_the_reference(reference_on_path):
+    from torch.utils.data import DataLoader, TensorDataset
+
+    reference, model = _twin_llamas()
+    tokens = torch.randint(0, 96, (16, 17), generator=torch.Generator().manual_seed(2))
+    for package, net in (("ohara", reference), ("ohara_b200", model)):
+        pkg = importlib.import_module(package)
+        optimizer_module = importlib.import_module(f"{package}.optimizer")
+        scheduler_module = importlib.import_module(f"{package}.lr_scheduler")
+        engine = pkg.OharaEngine()
+        net = engine.prepare(net)
+        optimizer = optimizer_module.build_adamw(net, learning_rate=1e-2, weight_decay=0.1)
+        (optimizer,) = engine.prepare_optimizers(optimizer)
+        loader = engine.prepare_dataloaders(
+            DataLoader(TensorDataset(tokens[:, :-1], tokens[:, 1:]), batch_size=4))
+        trainer = pkg.Trainer(engine, net, optimizer, loader, loader,
+                              scheduler_module.Scheduler(1e-2), micro_batch=2, max_iters=4,
+                              eval_iters=0, save_ckpt_iters=0, print_every=10**9)
+        trainer.train()
+    for (name, want), have in zip(reference.state_dict().items(), model.state_dict().values()):
+        torch.testing.assert_close(have, want, rtol=1e-4, atol=5e-5, msg=name)
+
+    sys.path.insert(0, str(ROOT / "tests"))
+    from helpers import chat_tokenizer
+
+    tokenizer = chat_tokenizer()
+    reference, model = _twin_llamas()
+    outputs = []
+    for package, net in (("ohara.chat_engine", reference), ("ohara_b200.chat_engine", model)):
+        module = importlib.import_module(package)
+        chat = module.ChatEngine(net.eval(), tokenizer, device="cpu")
+        config = module.SamplingConfig(temperature=0.9, top_k=20, top_p=0.95, max_new_tokens=10)
+        messages = [{"role": "user", "content": "w1 w2 w3"}]
+        outputs.append((chat.render_prompt(messages), chat.generate(messages, config, seed=11),
+                        chat.generate(messages, module.SamplingConfig(temperature=0.0,
+                                                                      max_new_tokens=8))))
+    assert outputs[0] == outputs[1] and outputs[0][1] and outputs[0][2]
