@@ -2,7 +2,8 @@
 
 Weights are quantised to {-1, 0, +1} times one scale per tensor (absolute-mean scaling),
 activations to int8 per row (absolute-max scaling); both through straight-through estimators, so
-the full-precision "shadow" weights keep receiving gradients.
+the full-precision "shadow" weights keep receiving gradients. The quantisers and the layer's
+function live in ``ohara_b200.ops.bitnet``; on a GPU the layer runs its kernels.
 """
 
 from __future__ import annotations
@@ -13,23 +14,11 @@ import torch.nn.functional as F
 from torch import Tensor
 
 from ohara_b200.modules.norm import RMSNorm
+from ohara_b200.ops.bitnet import activation_quant_reference as activation_quant
+from ohara_b200.ops.bitnet import bit_linear
+from ohara_b200.ops.bitnet import weight_quant_reference as weight_quant
 
-
-def activation_quant(x: Tensor) -> Tensor:
-    """Per-row int8 fake quantisation; the backward pass sees the identity."""
-    scale = 127.0 / x.abs().amax(dim=-1, keepdim=True).clamp_min(1e-5)
-    quantised = (x * scale).round().clamp(-128, 127) / scale
-    return x + (quantised - x).detach()
-
-
-def weight_quant(w: Tensor) -> tuple[Tensor, Tensor]:
-    """Ternary fake quantisation. Returns the weight normalised to {-1, 0, 1} (with the
-    straight-through gradient of ``w``) and the scale to multiply the product by."""
-    inv = 1.0 / w.abs().mean().clamp_min(1e-5)
-    ternary = (w * inv).round().clamp(-1, 1) / inv
-    w_ste = w + (ternary - w).detach()
-    scale = w_ste.abs().max().detach()
-    return w_ste / scale, scale
+__all__ = ["BitLinear", "activation_quant", "apply_bitlinear", "bit_linear", "weight_quant"]
 
 
 class BitLinear(nn.Linear):
@@ -38,6 +27,8 @@ class BitLinear(nn.Linear):
         self.rms_norm = RMSNorm(self.in_features)
 
     def forward(self, x: Tensor) -> Tensor:
+        if x.is_cuda:  # quantiser kernels around the tensor-core GEMM, same gradients
+            return bit_linear(x, self.weight, self.rms_norm.weight, self.bias, self.rms_norm.eps)
         w, scale = weight_quant(self.weight)
         out = F.linear(activation_quant(self.rms_norm(x)), w) * scale
         return out if self.bias is None else out + self.bias

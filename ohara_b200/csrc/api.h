@@ -137,6 +137,20 @@ int64_t sinkhorn_tape_floats(int n, int iters);
 void sinkhorn_backward(const float* in, const float* grad_out, float* grad_in, float* tape,
                        int64_t count, int n, int iters, cudaStream_t stream);
 
+// quantize.cu: quantisers of BitNet b1.58 layers.
+// q (bf16, integer values in [-128, 127]) and dequant (one factor per row) from x (bf16, rows x d);
+// with `norm_weight` the row is RMS-normalised first and `rstd` (may be null) receives 1 / rms.
+void bitnet_act_quant(const void* x, const float* norm_weight, void* q, float* dequant, float* rstd,
+                      int rows, int d, float eps, cudaStream_t stream);
+// ternary (bf16 in {-1, 0, 1}) and scale[0] = max(mean |w|, 1e-5) from n weights (fp32 or bf16);
+// `partials`: scratch of `bitnet_partial_count()` floats.
+int bitnet_partial_count();
+void bitnet_weight_quant(const void* w, bool w_is_f32, int64_t n, void* ternary, float* scale,
+                         float* partials, cudaStream_t stream);
+// out (bf16) = acc (fp32, rows x n) * row_factor[row] * weight_scale[0] (+ bias[col], may be null).
+void bitnet_scale_rows(const float* acc, const float* row_factor, const float* weight_scale,
+                       const float* bias, void* out, int64_t rows, int n, cudaStream_t stream);
+
 // attention_bwd_sm100.cu
 void attn_delta(const void* o, const void* d_o, float* delta, int B, int T, int H, int D,
                 int64_t do_tok_stride, int64_t do_batch_stride, cudaStream_t stream);

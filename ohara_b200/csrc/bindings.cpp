@@ -521,6 +521,76 @@ bool sinkhorn_supported(int64_t n, int64_t iters) {
   return ob::sinkhorn_supported((int)n, (int)iters);
 }
 
+// ---- BitNet quantisers ---------------------------------------------------------------------------
+// (q, dequant, rstd) of a 2-D bf16 tensor; `norm_weight` (fp32, width) fuses the RMS norm in, and
+// rstd is then the per-row 1 / rms (an empty tensor otherwise).
+std::vector<Tensor> bitnet_act_quant(const Tensor& x, const c10::optional<Tensor>& norm_weight,
+                                     double eps) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && x.size(1) % 8 == 0 &&
+                  reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0,
+              "act_quant expects a contiguous, 16-byte aligned (rows, width % 8 == 0) tensor");
+  TORCH_CHECK(x.size(0) < (1ll << 31), "act_quant: too many rows");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const float* w = nullptr;
+  if (norm_weight.has_value()) {
+    check_f32(*norm_weight, "norm_weight");
+    TORCH_CHECK(norm_weight->is_contiguous() && norm_weight->numel() == x.size(1) &&
+                    reinterpret_cast<uintptr_t>(norm_weight->data_ptr()) % 16 == 0,
+                "norm_weight must be a contiguous, 16-byte aligned vector of the row width");
+    w = norm_weight->data_ptr<float>();
+  }
+  Tensor q = torch::empty_like(x);
+  Tensor dequant = torch::empty({x.size(0)}, x.options().dtype(torch::kFloat32));
+  Tensor rstd = torch::empty({w != nullptr ? x.size(0) : 0}, dequant.options());
+  ob::bitnet_act_quant(x.data_ptr(), w, q.data_ptr(), dequant.data_ptr<float>(),
+                       w != nullptr ? rstd.data_ptr<float>() : nullptr, (int)x.size(0),
+                       (int)x.size(1), (float)eps, current_stream());
+  return {q, dequant, rstd};
+}
+
+// (ternary bf16 of w's shape, scale (1,) fp32) of a contiguous fp32 or bf16 weight.
+std::vector<Tensor> bitnet_weight_quant(const Tensor& w) {
+  check_cuda(w, "w");
+  const bool f32 = w.scalar_type() == torch::kFloat32;
+  TORCH_CHECK(f32 || w.scalar_type() == torch::kBFloat16, "w must be float32 or bfloat16");
+  TORCH_CHECK(w.is_contiguous(), "w must be contiguous");
+  const c10::cuda::CUDAGuard guard(w.device());
+  Tensor ternary = torch::empty(w.sizes(), w.options().dtype(torch::kBFloat16));
+  Tensor scale = torch::empty({1}, w.options().dtype(torch::kFloat32));
+  Tensor partials = torch::empty({ob::bitnet_partial_count()}, scale.options());
+  ob::bitnet_weight_quant(w.data_ptr(), f32, w.numel(), ternary.data_ptr(), scale.data_ptr<float>(),
+                          partials.data_ptr<float>(), current_stream());
+  return {ternary, scale};
+}
+
+Tensor bitnet_scale_rows(const Tensor& acc, const Tensor& row_factor, const Tensor& weight_scale,
+                         const c10::optional<Tensor>& bias) {
+  check_f32(acc, "acc");
+  check_f32(row_factor, "row_factor");
+  check_f32(weight_scale, "weight_scale");
+  TORCH_CHECK(acc.dim() == 2 && acc.is_contiguous() && acc.size(1) % 4 == 0 &&
+                  reinterpret_cast<uintptr_t>(acc.data_ptr()) % 16 == 0,
+              "scale_rows expects a contiguous, 16-byte aligned (rows, width % 4 == 0) tensor");
+  TORCH_CHECK(row_factor.is_contiguous() && row_factor.numel() == acc.size(0) &&
+                  weight_scale.numel() == 1,
+              "one factor per row and one weight scale expected");
+  const c10::cuda::CUDAGuard guard(acc.device());
+  const float* b = nullptr;
+  if (bias.has_value()) {
+    check_f32(*bias, "bias");
+    TORCH_CHECK(bias->is_contiguous() && bias->numel() == acc.size(1) &&
+                    reinterpret_cast<uintptr_t>(bias->data_ptr()) % 16 == 0,
+                "bias must be a contiguous, 16-byte aligned vector of the row width");
+    b = bias->data_ptr<float>();
+  }
+  Tensor out = torch::empty(acc.sizes(), acc.options().dtype(torch::kBFloat16));
+  ob::bitnet_scale_rows(acc.data_ptr<float>(), row_factor.data_ptr<float>(),
+                        weight_scale.data_ptr<float>(), b, out.data_ptr(), acc.size(0),
+                        (int)acc.size(1), current_stream());
+  return out;
+}
+
 // ---- peer memory ---------------------------------------------------------------------------------
 // Allocates `bytes` of device memory outside the caching allocator and returns (tensor view as
 // uint8, IPC handle bytes). The memory lives until peer_free(tensor.data_ptr()).
@@ -1124,6 +1194,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sinkhorn_fwd", &sinkhorn_fwd);
   m.def("sinkhorn_bwd", &sinkhorn_bwd);
   m.def("sinkhorn_supported", &sinkhorn_supported);
+  m.def("bitnet_act_quant", &bitnet_act_quant);
+  m.def("bitnet_weight_quant", &bitnet_weight_quant);
+  m.def("bitnet_scale_rows", &bitnet_scale_rows);
   m.def("flash_attn_bwd", &flash_attn_bwd, py::arg("dout"), py::arg("q"), py::arg("k"),
         py::arg("v"), py::arg("out"), py::arg("lse"), py::arg("causal"), py::arg("scale"),
         py::arg("dk_out") = py::none(), py::arg("dv_out") = py::none());
