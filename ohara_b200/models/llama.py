@@ -351,6 +351,9 @@ class Llama(nn.Module):
             kv_cache is not None and isinstance(position_ids, Tensor) and position_ids.is_cuda
             and position_ids.dtype == torch.int32 and position_ids.numel() == 1 and x.size(1) == 1
         )
+        if kv_cache is not None and getattr(self, "_param_sharding", None) is not None:
+            raise NotImplementedError("decoding with a KV cache needs whole parameters: "
+                                      "load the full state dict into an unsharded model")
         if device_position:
             h = ops.embedding(x, self.token_emb.weight)
             freqs = (None, None, *self._rope_tables_f32())
@@ -361,9 +364,6 @@ class Llama(nn.Module):
         start = self._check_inputs(x, kv_cache, position_ids)
         seq = x.size(1)
         if getattr(self, "_param_sharding", None) is not None:
-            if kv_cache is not None:
-                raise NotImplementedError("decoding with a KV cache needs whole parameters: "
-                                          "load the full state dict into an unsharded model")
             return self._forward_hidden_sharded(x, seq)
         cp = getattr(self, "_cp", None)
         if cp is not None and kv_cache is None:
@@ -421,7 +421,8 @@ class Llama(nn.Module):
             else:
                 block = lambda a, b, layer=layer: layer.forward_deferred(a, b, freqs)  # noqa: E731
             h, pending = sharding.run_unit(f"layers.{idx}", block, h, pending)
-        sharding.enter_unit("embed" if sharding.tied else "head")
+        # (nothing runs after this unit in the forward pass: no gather of a following one)
+        sharding.enter_unit("embed" if sharding.tied else "head", prefetch_next=False)
         return ops.add_rms_norm(h, pending, self.norm.weight, self.norm.eps)[0]
 
     def enable_activation_checkpointing(self, enabled: bool = True) -> "Llama":
@@ -442,7 +443,16 @@ class Llama(nn.Module):
         wrapper that only forwards ``__call__`` (DDP) can still use the fused loss."""
         if targets is not None:
             return self.loss_sum(x, targets, ignore_index, loss_scale)
-        return self.vocab_proj(self.forward_hidden(x, kv_cache, position_ids))
+        logits = self.vocab_proj(self.forward_hidden(x, kv_cache, position_ids))
+        self._release_after_inference()
+        return logits
+
+    def _release_after_inference(self) -> None:
+        """With sharded parameters and no backward pass to come (evaluation), nothing else would
+        release the unit that stays gathered for the loss."""
+        sharding = getattr(self, "_param_sharding", None)
+        if sharding is not None and not torch.is_grad_enabled():
+            sharding.release_all()
 
     def loss_sum(self, x: Tensor, targets: Tensor, ignore_index: int = -1,
                  scale: Tensor | float | None = None) -> Tensor:
@@ -458,6 +468,7 @@ class Llama(nn.Module):
             valid = (targets != ignore_index).sum().clamp_min(1).to(loss.dtype)
             aux = aux * valid  # per-token coefficient under a sum-reduced loss
             loss = loss + (aux if scale is None else aux * scale)
+        self._release_after_inference()
         return loss
 
     def auxiliary_loss(self) -> Tensor | None:

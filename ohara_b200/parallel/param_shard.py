@@ -242,12 +242,13 @@ class ParameterSharding:
         return self.units[index] if 0 <= index < len(self.units) else None
 
     # -- what the model calls --------------------------------------------------------------------
-    def enter_unit(self, name: str) -> None:
-        """Gather a unit that stays gathered until its gradients are complete."""
+    def enter_unit(self, name: str, prefetch_next: bool = True) -> None:
+        """Gather a unit that stays gathered until its gradients are complete (or, without a
+        backward pass, until ``release_all``)."""
         unit = self.by_name[name]
         self.unshard(unit)
         following = self._neighbour(unit, +1)
-        if self.prefetch and following is not None:
+        if self.prefetch and prefetch_next and following is not None:
             self._issue(following, asynchronous=True)
 
     def run_unit(self, name: str, fn: Callable, *args):

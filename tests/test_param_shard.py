@@ -105,9 +105,12 @@ def test_evaluation_pass_releases_the_blocks():
     tokens = torch.randint(0, 37, (2, 9))
     with torch.no_grad():
         torch.testing.assert_close(model(tokens), reference(tokens))
-    assert [u.name for u in sharding.units if u.full is not None] == ["head"]
-    sharding.release_all()
+        assert all(u.full is None for u in sharding.units)      # the head too, once it was used
+        want = reference.loss_sum(tokens[:, :-1], tokens[:, 1:])
+        torch.testing.assert_close(model.loss_sum(tokens[:, :-1], tokens[:, 1:]), want)
     assert all(u.full is None for u in sharding.units)
+    with pytest.raises(NotImplementedError, match="whole parameters"):
+        model(tokens[:, :1], model.build_kv_cache(batch_size=2), 0)
 
 
 def test_loop_moe_units_are_deferred_and_muon_runs_on_one_process_with_either_layout():
