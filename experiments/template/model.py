@@ -166,6 +166,14 @@ def _variants() -> dict[str, Callable[[TemplateConfig], TemplateLM]]:
             patch_linears(layer, build=to_xlinear)
         return model
 
+    def bitnet(cfg: TemplateConfig) -> TemplateLM:
+        from experiments.bitnet.bitnet import apply_bitlinear
+
+        model = TemplateLM(cfg)
+        for layer in model.layers:  # 1.58-bit projections in the blocks; embedding and head stay plain
+            apply_bitlinear(layer)
+        return model
+
     def with_rope(cfg: TemplateConfig, width: int) -> TemplateConfig:
         return TemplateConfig(**{**cfg.__dict__, "rope_dim": width})
 
@@ -191,6 +199,7 @@ def _variants() -> dict[str, Callable[[TemplateConfig], TemplateLM]]:
         "mixture_of_depth": lambda c: TemplateLM(
             c, feed_forward=lambda k: DepthRoutedMLP(k.d_model, k.hidden_dim)),
         "hypersphere": hypersphere,
+        "bitnet": bitnet,
     }
 
 

@@ -11,9 +11,8 @@ bf16 autocast on CUDA. Prints the loss every ``--log-every`` steps and a final J
 first and last smoothed loss, parameters and tokens per second. Models: ``mqa`` / ``hawk`` /
 ``griffin``; ``residual`` / ``hc`` / ``mhc``; the template variants ``baseline`` / ``kattention`` /
 ``partial_kv`` / ``xglu`` / ``deglu`` / ``springnet`` / ``tokenformer`` / ``tokenformer_full`` /
-``mla`` / ``relu2`` /
-``mixture_of_depth`` / ``hypersphere``; ``life`` trains the template baseline on Game of Life
-transitions with the loss on the next board only."""
+``mla`` / ``relu2`` / ``mixture_of_depth`` / ``hypersphere`` / ``bitnet``; ``life`` trains the
+template baseline on Game of Life transitions with the loss on the next board only."""
 
 from __future__ import annotations
 

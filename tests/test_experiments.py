@@ -364,7 +364,7 @@ def test_connection_types_of_the_mhc_model_and_template_variants_run_and_learn()
                          num_layers=2)
     assert set(VARIANTS) == {"baseline", "kattention", "partial_kv", "xglu", "deglu", "springnet",
                              "tokenformer", "tokenformer_full", "mla", "relu2", "mixture_of_depth",
-                             "hypersphere"}
+                             "hypersphere", "bitnet"}
     for variant in VARIANTS:
         model = build(variant, cfg)
         logits = model(tokens)
@@ -373,6 +373,8 @@ def test_connection_types_of_the_mhc_model_and_template_variants_run_and_learn()
         logits.sum().backward()
     from experiments.misc.small_modules import XLinear as _X
     assert sum(isinstance(m, _X) for m in build("hypersphere", cfg).modules()) == 2 * 7
+    from experiments.bitnet.bitnet import BitLinear
+    assert sum(isinstance(m, BitLinear) for m in build("bitnet", cfg).modules()) == 2 * 7
     for name in ("griffin", "life"):
         result = main(["--model", name, "--steps", "30", "--batch", "8", "--seq-len", "48",
                        "--dim", "32", "--layers", "2", "--log-every", "0", "--device", "cpu"])
