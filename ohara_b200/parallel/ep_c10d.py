@@ -80,9 +80,9 @@ def expert_parallel_swiglu_c10d(flat_x: Tensor, indices: Tensor, weights: Tensor
         incoming.view(-1))
     result = torch.zeros_like(received)
     for expert in range(local):
+        # (an expert without rows still goes through the products, with empty operands: its
+        # weights then get a zero gradient instead of none, which data-parallel wrappers need)
         rows = (expert_of_row == expert).nonzero(as_tuple=True)[0]
-        if rows.numel() == 0:
-            continue
         x = received[rows]
         gate, up, down = (w[expert].to(x.dtype) for w in (w_gate, w_up, w_down))
         result = result.index_add(0, rows, (F.silu(x @ gate) * (x @ up)) @ down)
