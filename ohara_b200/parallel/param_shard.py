@@ -14,8 +14,8 @@ keeps, between uses, only ``1 / world`` of every parameter:
   overlaps; after use the parameters are pointed back at a shape-only placeholder and the buffer
   is released;
 * when the last gradient of a unit has been accumulated, the unit's gradients are packed,
-  reduce-scattered (mean) and added to the rank's fp32 gradient shard, and the full gradients are
-  dropped. A unit some of whose parameters may stay without a gradient on some ranks (the loop
+  reduce-scattered (mean, asynchronously: the previous block's backward pass runs meanwhile) and
+  added to the rank's fp32 gradient shard, and the full gradients are dropped. A unit some of whose parameters may stay without a gradient on some ranks (the loop
   MoE: experts no token chose) is reduced at the end of the backward pass instead, by every rank
   in turn.
 
@@ -188,6 +188,7 @@ class ParameterSharding:
         # are partial sums and are added up over it before the data-parallel reduction.
         self.partial_gradient_group = None   # (``None`` is also the default group: see the flag)
         self.partial_gradients = False
+        self._reductions: list[tuple[_Unit, Any, Tensor | None, Tensor]] = []   # in flight
         self.unsharded_bytes = sum(sum(u.numels) for u in self.units) * 4
         self.peak_gathered_bytes = 0
         for unit in self.units:
@@ -306,21 +307,41 @@ class ParameterSharding:
                     if not hasattr(p, "tensor_parallel_dim"):
                         dist.all_reduce(flat[off : off + n], group=self.partial_gradient_group)
             if self.world == 1:
-                shard = flat
-            elif dist.get_backend(self.group) == "gloo":  # gloo has no reduce-scatter
-                dist.all_reduce(flat, group=self.group)
-                shard = flat[self.rank * unit.region : (self.rank + 1) * unit.region].clone()
+                self._accumulate(unit, flat)
             else:
-                shard = torch.empty(unit.region, device=flat.device, dtype=torch.float32)
-                dist.reduce_scatter_tensor(shard, flat, group=self.group)
-            if self.world > 1:
-                shard.div_(self.world)
-            if self.replicate_world > 1:
-                dist.all_reduce(shard, group=self.replicate_group)
-                shard.div_(self.replicate_world)
-            unit.grad = shard if unit.grad is None else unit.grad.add_(shard)
+                # Asynchronous: the backward pass of the next block runs while this block's
+                # gradients are on the wire. At most two reductions are in flight (each holds one
+                # block-sized buffer); older ones are completed first.
+                while len(self._reductions) >= 2:
+                    self._complete(self._reductions.pop(0))
+                if dist.get_backend(self.group) == "gloo":  # gloo has no reduce-scatter
+                    work = dist.all_reduce(flat, group=self.group, async_op=True)
+                    shard = None
+                else:
+                    shard = torch.empty(unit.region, device=flat.device, dtype=torch.float32)
+                    work = dist.reduce_scatter_tensor(shard, flat, group=self.group, async_op=True)
+                self._reductions.append((unit, work, shard, flat))
         unit.remaining = unit.trainable
         self._release(unit)
+
+    def _complete(self, reduction) -> None:
+        """Wait for a reduce-scatter in flight and add its mean to the unit's gradient shard."""
+        unit, work, shard, flat = reduction
+        work.wait()
+        if shard is None:  # an all-reduce of the whole vector stood in for the reduce-scatter
+            shard = flat[self.rank * unit.region : (self.rank + 1) * unit.region].clone()
+        shard.div_(self.world)
+        self._accumulate(unit, shard)
+
+    def _accumulate(self, unit: _Unit, shard: Tensor) -> None:
+        if self.replicate_world > 1:
+            dist.all_reduce(shard, group=self.replicate_group)
+            shard.div_(self.replicate_world)
+        unit.grad = shard if unit.grad is None else unit.grad.add_(shard)
+
+    def _drain_reductions(self) -> None:
+        while self._reductions:
+            self._complete(self._reductions.pop(0))
 
     def finish_backward(self) -> None:
         """After ``backward()``: units whose gradients did not all arrive (unused parameters), or
@@ -330,6 +351,7 @@ class ParameterSharding:
                 self._reduce(unit, always=True)
             elif unit.full is not None or unit.remaining != unit.trainable:
                 self._reduce(unit)
+        self._drain_reductions()
 
     def release_all(self) -> None:
         """Release every gathered unit (after an evaluation or generation pass)."""
@@ -558,6 +580,7 @@ class ParameterShardedOptimizer(Optimizer):
         return loss
 
     def zero_grad(self, set_to_none: bool = True) -> None:
+        self.sharding._drain_reductions()
         for unit in self.sharding.units:
             unit.grad = None
             for p in unit.params:
