@@ -142,9 +142,12 @@ def load_pretrained(path: Path, vocab_size: int, seq_len: int | None, **moe_hint
 
 def load_conversations(args):
     if args.conversations is not None:
-        rows = [json.loads(line)["messages"]
+        rows = [json.loads(line)
                 for line in Path(args.conversations).read_text(encoding="utf-8").splitlines()
                 if line.strip()]
+        if not rows or not all(isinstance(row, dict) and "messages" in row for row in rows):
+            raise ValueError(f"{args.conversations}: every line must be an object with a "
+                             f"'messages' list")
         random.Random(args.seed).shuffle(rows)
         held_out = max(1, len(rows) // 20)
         return rows[held_out:], rows[:held_out]

@@ -165,3 +165,66 @@ def test_pretraining_example_on_two_ranks_saves_and_resumes(tmp_path, layout):
     assert "iter: 1 |" not in second.stdout
     saved = torch.load(checkpoint, weights_only=False)
     assert saved["model"]["layers.1.attn.query.weight"].shape == (32, 32)   # whole matrices
+
+
+def test_finetuning_example_runs_from_a_pretrained_checkpoint_to_a_chat_reply(tmp_path):
+    """pretrain (synthetic ids) -> train_sft.py on a local JSONL with a local tokenizer -> the
+    checkpoint and the tokenizer saved beside it answer through ChatEngine."""
+    import random
+
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    from transformers import PreTrainedTokenizerFast
+
+    rng = random.Random(0)
+    words = [f"w{i}" for i in range(60)] + "what is plus answer".split() + [str(i) for i in range(19)]
+    corpus = [" ".join(rng.choice(words) for _ in range(20)) for _ in range(300)]
+    raw = Tokenizer(models.BPE(unk_token="<unk>"))
+    raw.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    raw.decoder = decoders.ByteLevel()
+    raw.train_from_iterator(corpus, trainers.BpeTrainer(
+        vocab_size=320, special_tokens=["<unk>", "<|endoftext|>"],
+        initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
+    PreTrainedTokenizerFast(tokenizer_object=raw, unk_token="<unk>", eos_token="<|endoftext|>",
+                            bos_token="<|endoftext|>").save_pretrained(tmp_path / "tok")
+    with open(tmp_path / "conversations.jsonl", "w") as handle:
+        for _ in range(80):
+            a, b = rng.randint(0, 9), rng.randint(0, 9)
+            handle.write(json.dumps({"messages": [
+                {"role": "user", "content": f"what is {a} plus {b}"},
+                {"role": "assistant", "content": f"answer {a + b}"}]}) + "\n")
+
+    base, tuned = tmp_path / "base.pt", tmp_path / "ckpt" / "sft.pt"
+    pretrain = [sys.executable, str(EXAMPLES / "train_llama_engine.py"), "--synthetic",
+                "--synthetic-vocab", "320", "--seq-len", "48", "--hidden-size", "32",
+                "--intermediate-size", "64", "--num-layers", "2", "--num-heads", "2",
+                "--batch-size", "2", "--max-iters", "2", "--warmup-iters", "1", "--eval-every", "0",
+                "--save-every", "2", "--logger", "none", "--precision", "fp32",
+                "--checkpoint-path", str(base)]
+    done = subprocess.run(pretrain, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0 and base.exists(), done.stderr[-2000:]
+    finetune = [sys.executable, str(EXAMPLES / "train_sft.py"), "--pretrained-checkpoint", str(base),
+                "--checkpoint-path", str(tuned), "--tokenizer", str(tmp_path / "tok"),
+                "--tokenizer-local-files-only", "--conversations",
+                str(tmp_path / "conversations.jsonl"), "--seq-len", "48", "--batch-size", "4",
+                "--max-iters", "6", "--eval-every", "3", "--eval-batches", "1", "--save-every", "6",
+                "--logger", "none", "--precision", "fp32",
+                "--result-json", str(tmp_path / "sft.json")]
+    done = subprocess.run(finetune, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stdout[-1500:] + done.stderr[-2500:]
+    assert "after SFT: val_loss=" in done.stdout and tuned.exists()
+    assert (tuned.parent / "sft" / "ohara_chat.json").exists()
+
+    bad = tmp_path / "bad.jsonl"
+    bad.write_text(json.dumps([{"role": "user", "content": "hi"}]) + "\n")
+    refused = subprocess.run(finetune[:finetune.index("--conversations") + 1] + [str(bad)]
+                             + finetune[finetune.index("--conversations") + 2:],
+                             capture_output=True, text=True, timeout=300)
+    assert refused.returncode != 0 and "'messages'" in refused.stderr
+
+    from ohara_b200.chat_engine import ChatEngine, SamplingConfig
+
+    engine = ChatEngine.from_checkpoint(tuned, device="cpu")
+    assert engine.model.config.vocab_size >= 320 + 6        # the chat tokens were added
+    reply = engine.generate([{"role": "user", "content": "what is 2 plus 3"}],
+                            SamplingConfig(temperature=0.0, max_new_tokens=4))
+    assert isinstance(reply, str)
