@@ -48,6 +48,7 @@ def _optional(name: str, line: str) -> float | None:
 
 def parse_log(path: Path, history_points: int = 300, total_override: int | None = None) -> dict[str, Any]:
     """Summarise a training log: stage, progress, pace, latest metrics and a thinned loss curve."""
+    path = Path(path)
     now = datetime.now().astimezone()
     state: dict[str, Any] = {
         "stage": "waiting", "iter": 0, "total_iters": None, "loss": None,
