@@ -143,4 +143,16 @@ def attention(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, scale: float
     use_dropout = dropout_p > 0.0 and training
     if _kernel_ok(q, k, v) and not use_dropout:
         return _FlashAttnFn.apply(q, k, v, causal, float(scale))
+    if not q.is_cuda and (not causal or q.shape[1] == k.shape[1]):
+        # CPU tensors: PyTorch's fused attention, as the reference model uses
+        # (ohara/models/llama.py:115-123). Its causal mask is aligned to the first key, which is
+        # the mask wanted here only when queries and keys cover the same positions.
+        group = q.shape[2] // k.shape[2]
+        kt, vt = k.transpose(1, 2), v.transpose(1, 2)
+        if group > 1:
+            kt, vt = kt.repeat_interleave(group, dim=1), vt.repeat_interleave(group, dim=1)
+        out = torch.nn.functional.scaled_dot_product_attention(
+            q.transpose(1, 2), kt, vt, dropout_p=dropout_p if use_dropout else 0.0,
+            is_causal=causal, scale=scale)
+        return out.transpose(1, 2)
     return attention_reference(q, k, v, causal, scale, dropout_p, training)

@@ -95,3 +95,16 @@ def test_tiny_expert_parallel_configuration_on_two_ranks():
     assert line["config"]["parallelism"] == "ep2"
     assert line["skew"]["target_share"] == 0.5 and 3.0 < line["final_loss"] < 8.0
     assert line["expert_load"]["dropped_pair_fraction_last_step"] > 0.0   # the skew overflows
+
+
+def test_cpu_configuration_of_the_benchmark_set_reports_the_known_losses():
+    """The tiny fp32 Llama of the benchmark set: its first loss is fixed by the seed (the value
+    the reference package gives for the same loop)."""
+    proc = subprocess.run([sys.executable, str(ROOT / "examples" / "bench_cpu_tiny_llama.py"),
+                           "--steps", "4", "--threads", "2"], capture_output=True, text=True,
+                          timeout=300, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    line = json.loads([row for row in proc.stdout.splitlines() if row.startswith("{")][-1])
+    assert line["impl"] == "ours" and line["device"] == "cpu" and line["value"] > 0
+    assert line["first_loss"] == pytest.approx(9.065635, abs=2e-5)
+    assert line["last_loss"] < line["first_loss"] + 0.05
