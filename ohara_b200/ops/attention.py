@@ -143,16 +143,23 @@ def attention(q: Tensor, k: Tensor, v: Tensor, causal: bool = True, scale: float
     use_dropout = dropout_p > 0.0 and training
     if _kernel_ok(q, k, v) and not use_dropout:
         return _FlashAttnFn.apply(q, k, v, causal, float(scale))
-    if not q.is_cuda and (not causal or q.shape[1] == k.shape[1]):
+    if not q.is_cuda:
         # CPU tensors: PyTorch's fused attention, as the reference model uses
-        # (ohara/models/llama.py:115-123). Its causal mask is aligned to the first key, which is
-        # the mask wanted here only when queries and keys cover the same positions.
+        # (ohara/models/llama.py:115-123). Its own causal mask is aligned to the first key, which
+        # is the mask wanted here only when queries and keys cover the same positions; a single
+        # query at the end of a cache sees every key, and any other offset gets an explicit mask.
+        steps, keys = q.shape[1], k.shape[1]
+        mask = None
+        if causal and steps != keys and steps > 1:
+            mask = (torch.arange(keys, device=q.device)[None, :]
+                    <= torch.arange(keys - steps, keys, device=q.device)[:, None])
         group = q.shape[2] // k.shape[2]
         kt, vt = k.transpose(1, 2), v.transpose(1, 2)
         if group > 1:
             kt, vt = kt.repeat_interleave(group, dim=1), vt.repeat_interleave(group, dim=1)
         out = torch.nn.functional.scaled_dot_product_attention(
-            q.transpose(1, 2), kt, vt, dropout_p=dropout_p if use_dropout else 0.0,
-            is_causal=causal, scale=scale)
+            q.transpose(1, 2), kt, vt, attn_mask=mask,
+            dropout_p=dropout_p if use_dropout else 0.0,
+            is_causal=causal and steps == keys, scale=scale)
         return out.transpose(1, 2)
     return attention_reference(q, k, v, causal, scale, dropout_p, training)
