@@ -112,7 +112,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
             cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
             cmd = [
                 cxx,
-                "-O2",
+                "-O3",
                 "-std=c++17",
                 "-fPIC",
                 f"-I{SRC_DIR}",

@@ -6,6 +6,13 @@
 
 #include "api.h"
 
+// cpu_scan.cpp: the linear recurrence on host tensors
+namespace ob_cpu {
+torch::Tensor pscan_cpu_fwd(const torch::Tensor& a, const torch::Tensor& x);
+std::vector<torch::Tensor> pscan_cpu_bwd(const torch::Tensor& a, const torch::Tensor& h,
+                                         const torch::Tensor& dh);
+}  // namespace ob_cpu
+
 namespace {
 
 using torch::Tensor;
@@ -1191,6 +1198,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("muon_apply", &muon_apply);
   m.def("pscan_fwd", &pscan_fwd);
   m.def("pscan_bwd", &pscan_bwd);
+  m.def("pscan_cpu_fwd", &ob_cpu::pscan_cpu_fwd);
+  m.def("pscan_cpu_bwd", &ob_cpu::pscan_cpu_bwd);
   m.def("sinkhorn_fwd", &sinkhorn_fwd);
   m.def("sinkhorn_bwd", &sinkhorn_bwd);
   m.def("sinkhorn_supported", &sinkhorn_supported);

@@ -3,7 +3,9 @@
 Used by Mamba's selective scan and the RG-LRU. The reference carries a Blelloch up/down-sweep
 (ohara/modules/pscan.py:63-258). Here CUDA tensors run the one-pass kernels of ``csrc/pscan.cu``
 (a thread owns four channels and walks the sequence; every tensor crosses HBM once, forward and
-backward); other tensors use the Hillis-Steele doubling form below, which needs ``ceil(log2 L)``
+backward); fp32 CPU tensors run the same one-pass recurrence in the extension's host kernel
+(``csrc/cpu_scan.cpp``) when the extension is built; other tensors use the Hillis-Steele doubling
+form below, which needs ``ceil(log2 L)``
 passes of whole-tensor operations, no padding to a power of two and no in-place tricks. Both have
 an explicit backward that is itself a (reversed) scan:
 
@@ -74,6 +76,48 @@ class PScanCuda(torch.autograd.Function):
         return da.to(ctx.dtypes[0]), dx.to(ctx.dtypes[1])
 
 
+class PScanNative(torch.autograd.Function):
+    """The recurrence on fp32 CPU tensors in one pass of the extension's host kernel
+    (``csrc/cpu_scan.cpp``: a task owns a block of channels of one batch row and walks the
+    sequence once), forward and backward."""
+
+    @staticmethod
+    def forward(ctx, a: Tensor, x: Tensor) -> Tensor:
+        from ohara_b200.ops._ext import ext
+
+        a32, x32 = a.contiguous(), x.contiguous()
+        h = ext().pscan_cpu_fwd(a32, x32)
+        ctx.save_for_backward(a32, h)
+        return h
+
+    @staticmethod
+    def backward(ctx, grad_h: Tensor):
+        from ohara_b200.ops._ext import ext
+
+        a32, h = ctx.saved_tensors
+        da, dx = ext().pscan_cpu_bwd(a32, h, grad_h.contiguous())
+        return da, dx
+
+
+_NATIVE_CPU: bool | None = None
+
+
+def _native_cpu_scan() -> bool:
+    """Whether the built extension is there to run CPU scans (never triggers a build: a CPU-only
+    installation without the shared object uses the PyTorch form)."""
+    global _NATIVE_CPU
+    if _NATIVE_CPU is None:
+        try:
+            from ohara_b200 import build_ext
+            from ohara_b200.ops import _ext
+
+            _NATIVE_CPU = build_ext.ext_path().exists() and _ext.available() and hasattr(
+                _ext.ext(), "pscan_cpu_fwd")
+        except Exception:  # noqa: BLE001 - any failure to load means "use the PyTorch form"
+            _NATIVE_CPU = False
+    return _NATIVE_CPU
+
+
 def npo2(len: int) -> int:  # noqa: A002 - the reference's parameter name
     """The smallest power of two that is at least ``len``."""
     return 1 << max(0, int(len) - 1).bit_length()
@@ -94,6 +138,9 @@ def pscan(A: Tensor, X: Tensor) -> Tensor:
         raise ValueError("pscan expects coefficient and input tensors of the same shape")
     if A.is_cuda and X.is_cuda and A.dim() >= 2 and A.dtype != torch.float64:
         return PScanCuda.apply(A, X)
+    if (not A.is_cuda and not X.is_cuda and A.dtype == torch.float32 and X.dtype == torch.float32
+            and A.dim() >= 2 and _native_cpu_scan()):
+        return PScanNative.apply(A, X)
     return PScan.apply(A, X)
 
 

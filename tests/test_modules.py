@@ -210,6 +210,37 @@ def test_parallel_scan_matches_the_recurrence_with_gradients():
         assert torch.allclose(g_fast, g_slow, atol=1e-9)
 
 
+@pytest.mark.parametrize("shape", [(2, 7, 5), (3, 33, 300), (2, 64, 40, 30), (1, 1, 3), (2, 5, 1100)])
+def test_host_scan_kernel_matches_the_recurrence_with_gradients(shape):
+    """fp32 CPU tensors run the one-pass kernel of the extension (when it is built); whole and
+    partial channel blocks, one step, non-contiguous inputs."""
+    from ohara_b200.modules.pscan import PScan, _native_cpu_scan
+
+    if not _native_cpu_scan():
+        pytest.skip("the extension is not built")
+    torch.manual_seed(0)
+    a = torch.rand(shape).transpose(0, 1).contiguous().transpose(0, 1).requires_grad_()
+    x = torch.randn(shape, requires_grad=True)
+    upstream = torch.randn(shape)
+    got = pscan(a, x)
+    got_grads = torch.autograd.grad(got, (a, x), upstream)
+    a64, x64 = a.detach().double().requires_grad_(), x.detach().double().requires_grad_()
+    want = sequential_scan(a64, x64)
+    want_grads = torch.autograd.grad(want, (a64, x64), upstream.double())
+    torch.testing.assert_close(got.double(), want, rtol=1e-5, atol=1e-5)
+    for have, ref in zip(got_grads, want_grads):
+        torch.testing.assert_close(have.double(), ref, rtol=1e-5, atol=1e-5)
+    doubling = PScan.apply(a.detach(), x.detach())          # the PyTorch form agrees as well
+    torch.testing.assert_close(doubling, got.detach(), rtol=1e-5, atol=1e-5)
+    threads = torch.get_num_threads()
+    torch.set_num_threads(1)                                  # one thread: the serial path
+    try:
+        with torch.no_grad():
+            torch.testing.assert_close(pscan(a, x), got.detach(), rtol=0, atol=0)
+    finally:
+        torch.set_num_threads(threads)
+
+
 def test_recurrent_blocks_are_causal():
     for block in (RG_LRU(16), Hawk(dim=16)):
         block.eval()
