@@ -114,3 +114,62 @@ def tiny_llama(vocab_size: int, *, context: int = 64, seed: int = 0, **overrides
 def exchange(question: str, answer) -> dict:
     return {"messages": [{"role": "user", "content": question},
                          {"role": "assistant", "content": answer}]}
+
+
+def run_ranks(script, world: int, *, port: int, env: dict | None = None, timeout: float = 400.0,
+              args: tuple = ()):
+    """Run ``script`` as ``world`` processes with the rendezvous variables ``torchrun`` would set
+    (RANK, LOCAL_RANK, WORLD_SIZE, MASTER_ADDR, MASTER_PORT), without the launcher process in
+    between. Returns ``(returncode, stdout, stderr)`` with the outputs of all ranks joined; if a
+    rank fails or the time runs out, the ranks still running are stopped (by their own PIDs)."""
+    import os
+    import subprocess
+    import sys
+    import tempfile
+    import time
+
+    base = dict(os.environ if env is None else env)
+    base.update(WORLD_SIZE=str(world), LOCAL_WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                MASTER_PORT=str(port))
+    logs, procs = [], []
+    for rank in range(world):
+        out = tempfile.TemporaryFile(mode="w+")
+        err = tempfile.TemporaryFile(mode="w+")
+        logs.append((out, err))
+        procs.append(subprocess.Popen(
+            [sys.executable, str(script), *map(str, args)], stdout=out, stderr=err,
+            env=dict(base, RANK=str(rank), LOCAL_RANK=str(rank), GROUP_RANK="0")))
+    deadline = time.monotonic() + timeout
+    code = 0
+    while True:
+        states = [proc.poll() for proc in procs]
+        failed = [state for state in states if state not in (None, 0)]
+        if failed:
+            code = failed[0]
+            break
+        if all(state == 0 for state in states):
+            break
+        if time.monotonic() > deadline:
+            code = -9
+            break
+        time.sleep(0.05)
+    for proc in procs:
+        if proc.poll() is None:
+            proc.kill()
+        proc.wait()
+    stdout, stderr = [], []
+    for out, err in logs:
+        for handle, sink in ((out, stdout), (err, stderr)):
+            handle.seek(0)
+            sink.append(handle.read())
+            handle.close()
+    return code, "".join(stdout), "".join(stderr)
+
+
+def launch_ranks(script, world: int, *, port: int, env: dict | None = None, timeout: float = 400.0,
+                 args: tuple = ()):
+    """:func:`run_ranks` with the result shaped like ``subprocess.CompletedProcess``."""
+    import subprocess
+
+    code, stdout, stderr = run_ranks(script, world, port=port, env=env, timeout=timeout, args=args)
+    return subprocess.CompletedProcess([str(script), *map(str, args)], code, stdout, stderr)

@@ -10,6 +10,8 @@ import textwrap
 from pathlib import Path
 
 import pytest
+
+from helpers import launch_ranks
 import torch
 
 ROOT = Path(__file__).resolve().parent.parent
@@ -46,9 +48,7 @@ def _run(script, world, tmp_path, port_base=29300):
     path = tmp_path / "worker.py"
     path.write_text(textwrap.dedent(PRELUDE) + textwrap.dedent(script))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port_base + os.getpid() % 500), str(path)]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    proc = launch_ranks(path, world, port=port_base + os.getpid() % 500, env=env, timeout=400)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     return proc.stdout
 

@@ -10,6 +10,8 @@ import textwrap
 from pathlib import Path
 
 import pytest
+
+from helpers import launch_ranks
 import torch
 
 from ohara_b200 import Config, Llama
@@ -266,9 +268,7 @@ def test_gloo_ranks_match_single_process_training(tmp_path, world, micro, checkp
     path.write_text(textwrap.dedent(WORKER).replace("MICRO", str(micro))
                     .replace("CHECKPOINT", str(checkpoint)))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(29800 + os.getpid() % 150), str(path)]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    proc = launch_ranks(path, world, port=29800 + os.getpid() % 150, env=env, timeout=400)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "PARAM_SHARD_OK" in proc.stdout
 
@@ -304,10 +304,8 @@ def test_checkpoint_of_two_ranks_continues_in_one_process(tmp_path):
     path, checkpoint = tmp_path / "worker.py", tmp_path / "ckpt.pt"
     path.write_text(textwrap.dedent(RESHARD_WORKER))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-           "--master-addr", "127.0.0.1", "--master-port", str(31200 + os.getpid() % 150), str(path),
-           str(checkpoint)]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    proc = launch_ranks(path, 2, port=31200 + os.getpid() % 150, env=env, timeout=400,
+                        args=(str(checkpoint),))
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     saved = torch.load(checkpoint, weights_only=False)
     ids = saved["ids"]
@@ -408,9 +406,7 @@ def test_sharded_parameters_compose_with_tensor_and_context_parallelism(tmp_path
                     .replace("SHARD", str(shard)).replace("RECOMPUTE", str(recompute))
                     .replace("REPLICAS", str(replicas)))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(31700 + os.getpid() % 150), str(path)]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    proc = launch_ranks(path, world, port=31700 + os.getpid() % 150, env=env, timeout=400)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "COMPOSED_OK" in proc.stdout
 
@@ -481,10 +477,8 @@ def test_muon_on_sharded_parameters_matches_single_process_and_resumes(tmp_path,
     path = tmp_path / "worker.py"
     path.write_text(textwrap.dedent(MUON_WORKER).replace("TP", str(tp)))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(32000 + os.getpid() % 150), str(path),
-           str(tmp_path / "ckpt.pt")]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    proc = launch_ranks(path, world, port=32000 + os.getpid() % 150, env=env, timeout=400,
+                        args=(str(tmp_path / "ckpt.pt"),))
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "MUON_SHARDED_OK" in proc.stdout
 
@@ -540,8 +534,6 @@ def test_experts_without_tokens_on_a_rank_do_not_desynchronise_the_reduction(tmp
     path = tmp_path / "worker.py"
     path.write_text(textwrap.dedent(LOOP_MOE_WORKER))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-           "--master-addr", "127.0.0.1", "--master-port", str(32200 + os.getpid() % 150), str(path)]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
+    proc = launch_ranks(path, 2, port=32200 + os.getpid() % 150, env=env, timeout=400)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "LOOP_MOE_SHARDED_OK" in proc.stdout

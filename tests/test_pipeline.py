@@ -8,6 +8,8 @@ import textwrap
 from pathlib import Path
 
 import pytest
+
+from helpers import launch_ranks
 import torch.nn as nn
 
 from ohara_b200.parallel.pipeline import split_sequential
@@ -63,9 +65,7 @@ def test_three_stage_pipeline_matches_the_unsplit_model(tmp_path, schedule):
     path = tmp_path / "worker.py"
     path.write_text(textwrap.dedent(script))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3",
-           "--master-addr", "127.0.0.1", "--master-port", str(30600 + os.getpid() % 300), str(path)]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    proc = launch_ranks(path, 3, port=30600 + os.getpid() % 300, env=env, timeout=300)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "PIPELINE_OK" in proc.stdout
 
@@ -139,8 +139,6 @@ def test_llama_split_in_three_stages_matches_the_whole_model(tmp_path):
     path = tmp_path / "worker.py"
     path.write_text(textwrap.dedent(script))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3",
-           "--master-addr", "127.0.0.1", "--master-port", str(30950 + os.getpid() % 40), str(path)]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    proc = launch_ranks(path, 3, port=30950 + os.getpid() % 40, env=env, timeout=300)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert "LLAMA_PIPELINE_OK" in proc.stdout

@@ -7,6 +7,8 @@ import textwrap
 from pathlib import Path
 
 import pytest
+
+from helpers import launch_ranks
 import torch
 
 from ohara_b200.runtime import (
@@ -120,9 +122,7 @@ def _run_ranks(script: str, world: int, tmp_path, timeout=240):
     path = tmp_path / "worker.py"
     path.write_text(textwrap.dedent(script))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 500), str(path)]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    proc = launch_ranks(path, world, port=29500 + os.getpid() % 500, env=env, timeout=timeout)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     return proc.stdout
 

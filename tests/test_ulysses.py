@@ -17,11 +17,11 @@ def _run(script: str, world: int, tmp_path, port: int) -> str:
     path = tmp_path / "worker.py"
     path.write_text(textwrap.dedent(script))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port + os.getpid() % 150), str(path)]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
-    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
-    return proc.stdout
+    from helpers import run_ranks
+
+    code, stdout, stderr = run_ranks(path, world, port=port + os.getpid() % 150, env=env)
+    assert code == 0, stdout[-3000:] + stderr[-3000:]
+    return stdout
 
 
 def test_exchanges_are_inverses_and_attention_matches_the_whole_sequence(tmp_path):

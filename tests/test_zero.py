@@ -9,6 +9,7 @@ from pathlib import Path
 
 import torch
 
+from helpers import launch_ranks
 from ohara_b200.models.llama import Config, Llama
 from ohara_b200.optimizer import build_adamw, build_muon_adamw
 from ohara_b200.parallel.zero import ShardedOptimizer
@@ -46,9 +47,7 @@ def _run(script, world, tmp_path):
     path = tmp_path / "worker.py"
     path.write_text(textwrap.dedent(script))
     env = dict(os.environ, PYTHONPATH=str(ROOT), OMP_NUM_THREADS="1")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(29000 + os.getpid() % 500), str(path)]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    proc = launch_ranks(path, world, port=29000 + os.getpid() % 500, env=env, timeout=300)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     return proc.stdout
 
