@@ -68,7 +68,7 @@ def test_weight_quantiser(shape, dtype):
     _steps_apart(ternary, want, 1e-4)
 
 
-@pytest.mark.parametrize("rows,n_in,n_out,bias", [(256, 128, 128, False), (1000, 768, 520, True),
+@pytest.mark.parametrize("rows,n_in,n_out,bias", [(256, 128, 128, False), (1024, 768, 512, True),
                                                   (2048, 768, 3072, False)])
 def test_bit_linear_layer_forward_and_backward(rows, n_in, n_out, bias):
     from ohara_b200.ops.bitnet import bit_linear, bit_linear_reference
