@@ -979,9 +979,13 @@ class OharaEngine:
             return state
         mine = (topo.tp_rank, topo.ep_rank, topo.pp_rank)
         first_replica = topo.dp_rank == 0 and topo.cp_rank == 0
-        gathered: list[Any] = [None] * topo.world_size
-        dist.all_gather_object(gathered, (mine, state if first_replica else None))
-        states = {coordinate: entry for coordinate, entry in gathered if entry is not None}
+        # only the rank that writes the file collects the states: with all-gather every rank would
+        # hold the optimizer state of the whole model in host memory
+        writer = self.is_global_zero
+        gathered: list[Any] | None = [None] * topo.world_size if writer else None
+        dist.gather_object((mine, state if first_replica else None), gathered, dst=0)
+        states = ({coordinate: entry for coordinate, entry in gathered if entry is not None}
+                  if writer else {mine: state})
         return {"model_parallel": True, "tp": topo.tp, "ep": topo.ep, "pp": topo.pp,
                 "states": states}
 
