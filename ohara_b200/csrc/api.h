@@ -137,6 +137,11 @@ int64_t sinkhorn_tape_floats(int n, int iters);
 void sinkhorn_backward(const float* in, const float* grad_out, float* grad_in, float* tape,
                        int64_t count, int n, int iters, cudaStream_t stream);
 
+// multimem.cu: out = scale * (sum over the ranks of a multicast group) of `bytes` bytes of bf16 or
+// fp32 values at the multicast address (one switch-side reduction per 16 bytes; no waits inside).
+void multimem_sum(const void* multicast, void* out, int64_t bytes, bool bf16, float scale,
+                  cudaStream_t stream);
+
 // quantize.cu: quantisers of BitNet b1.58 layers.
 // q (bf16, integer values in [-128, 127]) and dequant (one factor per row) from x (bf16, rows x d);
 // with `norm_weight` the row is RMS-normalised first and `rstd` (may be null) receives 1 / rms.

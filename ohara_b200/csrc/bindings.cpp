@@ -528,6 +528,20 @@ bool sinkhorn_supported(int64_t n, int64_t iters) {
   return ob::sinkhorn_supported((int)n, (int)iters);
 }
 
+// ---- multicast reduction --------------------------------------------------------------------------
+// out <- scale * sum over the ranks of the bytes at `multicast_ptr` (the multicast address of a
+// symmetric buffer every rank has filled and fenced with a barrier before this call).
+void multimem_sum(int64_t multicast_ptr, Tensor& out, double scale) {
+  check_cuda(out, "out");
+  const bool bf16 = out.scalar_type() == torch::kBFloat16;
+  TORCH_CHECK(bf16 || out.scalar_type() == torch::kFloat32, "out must be bfloat16 or float32");
+  TORCH_CHECK(out.is_contiguous(), "out must be contiguous");
+  TORCH_CHECK(multicast_ptr != 0, "no multicast address: the devices do not support multicast");
+  const c10::cuda::CUDAGuard guard(out.device());
+  ob::multimem_sum(reinterpret_cast<const void*>(multicast_ptr), out.data_ptr(),
+                   out.numel() * out.element_size(), bf16, (float)scale, current_stream());
+}
+
 // ---- BitNet quantisers ---------------------------------------------------------------------------
 // (q, dequant, rstd) of a 2-D bf16 tensor; `norm_weight` (fp32, width) fuses the RMS norm in, and
 // rstd is then the per-row 1 / rms (an empty tensor otherwise).
@@ -1203,6 +1217,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sinkhorn_fwd", &sinkhorn_fwd);
   m.def("sinkhorn_bwd", &sinkhorn_bwd);
   m.def("sinkhorn_supported", &sinkhorn_supported);
+  m.def("multimem_sum", &multimem_sum);
   m.def("bitnet_act_quant", &bitnet_act_quant);
   m.def("bitnet_weight_quant", &bitnet_weight_quant);
   m.def("bitnet_scale_rows", &bitnet_scale_rows);
