@@ -228,3 +228,25 @@ def test_finetuning_example_runs_from_a_pretrained_checkpoint_to_a_chat_reply(tm
     reply = engine.generate([{"role": "user", "content": "what is 2 plus 3"}],
                             SamplingConfig(temperature=0.0, max_new_tokens=4))
     assert isinstance(reply, str)
+
+
+def test_sharded_run_of_two_ranks_resumes_on_one_rank_from_the_command_line(tmp_path):
+    """Elastic restart: a run under the sharded optimizer saved by two ranks continues on one
+    (the optimizer state is resharded on load, the data stream skips what was consumed)."""
+    checkpoint = tmp_path / "ckpt" / "model.pt"
+    script = [str(EXAMPLES / "train_llama_engine.py"), "--synthetic", "--synthetic-vocab", "256",
+              "--seq-len", "32", "--hidden-size", "32", "--intermediate-size", "64",
+              "--num-layers", "2", "--num-heads", "2", "--batch-size", "2", "--warmup-iters", "1",
+              "--eval-every", "0", "--save-every", "2", "--logger", "none", "--precision", "fp32",
+              "--strategy", "fsdp", "--checkpoint-path", str(checkpoint)]
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    launcher = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                "--master-addr", "127.0.0.1", "--master-port", str(29650 + os.getpid() % 40)]
+    first = subprocess.run(launcher + script + ["--max-iters", "2"], env=env, capture_output=True,
+                           text=True, timeout=300)
+    assert first.returncode == 0 and checkpoint.exists(), first.stderr[-2000:]
+    second = subprocess.run([sys.executable] + script + ["--max-iters", "4", "--resume"], env=env,
+                            capture_output=True, text=True, timeout=300)
+    assert second.returncode == 0, second.stderr[-2000:]
+    assert "resumed checkpoint" in second.stdout and "at iter=2" in second.stdout
+    assert "iter: 4 |" in second.stdout and "iter: 1 |" not in second.stdout
