@@ -2,8 +2,8 @@
 
 * ``relu_squared`` - ReLU(x)^2 as an explicit autograd function (experiments/relu_next/
   model_relu_next.py:41-63), and ``silulu = silu(x) + relu(x)^2``.
-* ``XLinear`` - a linear layer whose rows are normalised to unit length and rescaled by their norm
-  after the product, separating direction from magnitude (experiments/hypersphere/hs.py:9-30).
+* ``XLinear`` - a linear layer that multiplies by its weight rows normalised to unit length, so
+  only the direction of a row matters (experiments/hypersphere/hs.py:9-30).
 * ``Pattention`` - "parameter-token attention": the input attends over learned key / value tokens
   with a GELU + L2 normalisation instead of a softmax, so that tokens can be appended (zero
   initialised) without changing the function (experiments/tokenformer/pattention.py:11-96).
@@ -43,9 +43,10 @@ def silulu(x: Tensor) -> Tensor:
 
 class XLinear(nn.Linear):
     def forward(self, x: Tensor) -> Tensor:
+        # The reference multiplies the product by the row norms of the *normalised* weight, which
+        # are one: the layer's function is the product with unit-length rows (plus the bias).
         norm = self.weight.norm(dim=-1, keepdim=True)
-        out = F.linear(x, self.weight / norm) * norm.squeeze(-1)
-        return out if self.bias is None else out + self.bias
+        return F.linear(x, self.weight / norm, self.bias)
 
 
 def gelu_l2_norm(x: Tensor, dim: int = -1) -> Tensor:

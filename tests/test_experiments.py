@@ -118,7 +118,11 @@ def test_small_modules():
     assert torch.allclose(silulu(x), torch.nn.functional.silu(x) + torch.relu(x).square())
     plain, xl = nn.Linear(6, 3), XLinear(6, 3)
     xl.load_state_dict(plain.state_dict())
-    assert torch.allclose(xl(x), plain(x), atol=1e-5)  # same function, different parametrisation
+    unit = plain.weight / plain.weight.norm(dim=-1, keepdim=True)
+    assert torch.allclose(xl(x), torch.nn.functional.linear(x, unit, plain.bias), atol=1e-6)
+    with torch.no_grad():
+        xl.weight.mul_(3.0)                       # only the direction of a row matters
+    assert torch.allclose(xl(x), torch.nn.functional.linear(x, unit, plain.bias), atol=1e-5)
     pat = Pattention(6, 4, num_tokens=10)
     before = pat(x)
     pat.expand_tokens(14)
