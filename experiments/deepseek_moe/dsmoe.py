@@ -33,7 +33,12 @@ class DSMoE(nn.Module):
         self.shared_experts = nn.ModuleList(
             block(hidden_size, intermediate_size) for _ in range(num_shared_experts))
         self.gate = nn.Linear(hidden_size, num_experts, bias=False)
-        self.register_buffer("expert_biases", torch.zeros(num_experts))
+        # (the name is the reference's, so that its state dicts load here: dsmoe.py:122)
+        self.register_buffer("e_expert_biases", torch.zeros(num_experts))
+
+    @property
+    def expert_biases(self) -> Tensor:
+        return self.e_expert_biases
 
     def forward(self, x: Tensor) -> tuple[Tensor, Tensor, Tensor]:
         """Returns ``(output, auxiliary loss, maximal load violation)``."""
@@ -58,5 +63,5 @@ class DSMoE(nn.Module):
             aux = self.num_experts * (load * probs.mean(0)).sum()
         if self.training and self.aux_free_loadbalancing:
             frequency = counts.float() / indices.numel()
-            self.expert_biases += self.expert_update_rate * torch.sign(frequency.mean() - frequency)
+            self.e_expert_biases += self.expert_update_rate * torch.sign(frequency.mean() - frequency)
         return out.view(shape), aux, maximal_violation(counts)
