@@ -54,19 +54,21 @@ def test_experiment_modules_compute_what_the_reference_files_compute():
         import ohara_alias  # noqa: F401  (their files import ``ohara``: give them this package)
     except ImportError:
         pass
+    stubs = []
     for missing in ("lightning", "wandb", "datasets"):
         if missing not in sys.modules:
             try:
                 __import__(missing)
             except Exception:  # noqa: BLE001 - any failure means "stub it"
                 sys.modules[missing] = types.ModuleType(missing)
+                stubs.append(missing)
     try:
         _compare_experiment_modules(theirs, ours)
     finally:  # leave no alias behind for tests that import the real reference package
         sys.meta_path[:] = [finder for finder in sys.meta_path
                             if type(finder).__module__ != "ohara_alias"]
-        for name in [n for n in sys.modules if n == "ohara" or n.startswith("ohara.")]:
-            del sys.modules[name]
+        for name in [n for n in sys.modules if n == "ohara" or n.startswith("ohara.")] + stubs:
+            sys.modules.pop(name, None)
 
 
 def _compare_experiment_modules(theirs: Path, ours: Path) -> None:
