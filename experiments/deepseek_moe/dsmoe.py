@@ -5,6 +5,10 @@ weights come from the unbiased scores (sigmoid, normalised over the selected exp
 balanced either without an auxiliary loss - after every training forward the bias of an
 under-loaded expert goes up by ``expert_update_rate`` and that of an over-loaded one goes down
 (sign update) - or with the classic load x importance auxiliary loss.
+
+One deliberate difference: the reference weights the picked experts with the ``k`` largest
+unbiased scores in order (dsmoe.py:181), which are the picked experts' own scores only while the
+biases do not change the pick; here an expert is always weighted with its own score.
 """
 
 from __future__ import annotations

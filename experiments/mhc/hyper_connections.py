@@ -25,20 +25,32 @@ class ManifoldHyperConnections(nn.Module):
         self.dim, self.rate, self.sinkhorn_iters = dim, rate, sinkhorn_iters
         flat = dim * rate
         self.norm = RMSNorm(flat)
-        self.phi = nn.Parameter(torch.zeros(flat, 2 * rate + rate * rate))
+        # (parameter names and shapes are the reference's, so its state dicts load here)
+        self.phi_pre = nn.Parameter(torch.zeros(flat, rate))
+        self.phi_post = nn.Parameter(torch.zeros(flat, rate))
+        self.phi_res = nn.Parameter(torch.zeros(flat, rate * rate))
         self.b_pre = nn.Parameter(torch.zeros(rate))
         self.b_post = nn.Parameter(torch.zeros(rate))
         self.b_res = nn.Parameter(torch.zeros(rate, rate))
-        self.alpha = nn.Parameter(torch.full((3,), 0.01))  # small gates at initialisation
+        self.alpha_pre = nn.Parameter(torch.full((1,), 0.01))  # small gates at initialisation
+        self.alpha_post = nn.Parameter(torch.full((1,), 0.01))
+        self.alpha_res = nn.Parameter(torch.full((1,), 0.01))
+
+    def raw_mixing(self, streams: Tensor) -> tuple[Tensor, Tensor, Tensor]:
+        """The three predictions before their squashing functions: ``pre`` and ``post``
+        ``(b, t, rate)``, ``res`` ``(b, t, rate, rate)``."""
+        b, t, r, _ = streams.shape
+        # one product for the three projections
+        proj = self.norm(streams.flatten(2)) @ torch.cat((self.phi_pre, self.phi_post, self.phi_res), dim=1)
+        pre = self.alpha_pre * proj[..., :r] + self.b_pre
+        post = self.alpha_post * proj[..., r:2 * r] + self.b_post
+        res = (self.alpha_res * proj[..., 2 * r:]).view(b, t, r, r) + self.b_res
+        return pre, post, res
 
     def forward(self, streams: Tensor) -> tuple[Tensor, Tensor, Tensor]:
         """``streams``: (batch, seq, rate, dim) -> ``h_pre`` (b, t, rate), ``h_post`` (b, t, rate),
         ``h_res`` (b, t, rate, rate)."""
-        b, t, r, _ = streams.shape
-        proj = self.norm(streams.flatten(2)) @ self.phi
-        pre = self.alpha[0] * proj[..., :r] + self.b_pre
-        post = self.alpha[1] * proj[..., r:2 * r] + self.b_post
-        res = (self.alpha[2] * proj[..., 2 * r:]).view(b, t, r, r) + self.b_res
+        pre, post, res = self.raw_mixing(streams)
         return torch.sigmoid(pre), 2.0 * torch.sigmoid(post), sinkhorn_log(res, self.sinkhorn_iters)
 
 

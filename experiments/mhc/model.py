@@ -59,12 +59,9 @@ class _Connected(nn.Module):
         if self.kind == "mhc":
             return connections(streams)
         # unconstrained: the raw prediction plus the identity instead of the Sinkhorn projection
-        b, t, r, _ = streams.shape
-        proj = connections.norm(streams.flatten(2)) @ connections.phi
-        pre = connections.alpha[0] * proj[..., :r] + connections.b_pre
-        post = connections.alpha[1] * proj[..., r:2 * r] + connections.b_post
-        res = (connections.alpha[2] * proj[..., 2 * r:]).view(b, t, r, r) + connections.b_res
-        return torch.sigmoid(pre), 2.0 * torch.sigmoid(post), res + torch.eye(r, device=res.device)
+        pre, post, res = connections.raw_mixing(streams)
+        identity = torch.eye(streams.shape[2], device=res.device)
+        return torch.sigmoid(pre), 2.0 * torch.sigmoid(post), res + identity
 
     def forward(self, streams: Tensor, *args) -> Tensor:
         if self.kind == "residual":

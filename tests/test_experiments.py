@@ -82,8 +82,10 @@ def test_hyper_connections_produce_valid_mixing_objects():
     torch.manual_seed(0)
     hc = ManifoldHyperConnections(dim=8, rate=4, sinkhorn_iters=30)
     with torch.no_grad():
-        hc.phi.normal_(std=0.5)
-        hc.alpha.fill_(1.0)
+        for phi in (hc.phi_pre, hc.phi_post, hc.phi_res):
+            phi.normal_(std=0.5)
+        for alpha in (hc.alpha_pre, hc.alpha_post, hc.alpha_res):
+            alpha.fill_(1.0)
     streams = torch.randn(2, 5, 4, 8)
     h_pre, h_post, h_res = hc(streams)
     assert h_pre.shape == (2, 5, 4) and (0 < h_pre).all() and (h_pre < 1).all()
@@ -94,7 +96,7 @@ def test_hyper_connections_produce_valid_mixing_objects():
     out = block(streams)
     assert out.shape == streams.shape
     out.sum().backward()
-    assert block.connections.phi.grad is not None
+    assert block.connections.phi_res.grad is not None
 
 
 def test_mixture_of_depth_touches_only_the_selected_tokens():
