@@ -24,7 +24,9 @@ def _trunc_normal(weight: Tensor, std: float, bound: float | None = None) -> Non
 
 class RG_LRU(nn.Module):
     """``h_t = a_t h_{t-1} + sqrt(1 - a_t²) (i_t ⊙ x_t)`` with ``a_t = exp(-c softplus(Λ) r_t)``,
-    input gate ``i_t`` and recurrence gate ``r_t`` sigmoid projections of ``x_t``, ``c = 8``."""
+    input gate ``i_t`` and recurrence gate ``r_t`` sigmoid projections of ``x_t``, ``c = 8``.
+    The recurrence runs over the time steps, as in the paper (the reference transposes steps and
+    width before its scan, ohara/modules/linear_rnn.py:40, which makes its unit memoryless)."""
 
     def __init__(self, dim: int):
         super().__init__()
