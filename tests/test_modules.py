@@ -250,6 +250,10 @@ def test_recurrent_blocks_are_causal():
         x2 = x.clone()
         x2[:, -1] += 1
         assert torch.allclose(block(x2)[:, :-1], base[:, :-1], atol=1e-5)
+        x3 = x.clone()
+        x3[:, 2] += 1
+        later = (block(x3) - base)[:, 3:].abs().amax(dim=(0, 2))
+        assert (later > 1e-4).all()          # and it has a memory: later steps see the change
 
 
 # -- adapters ----------------------------------------------------------------------------------------
