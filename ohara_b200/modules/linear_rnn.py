@@ -26,7 +26,11 @@ class RG_LRU(nn.Module):
     """``h_t = a_t h_{t-1} + sqrt(1 - a_t²) (i_t ⊙ x_t)`` with ``a_t = exp(-c softplus(Λ) r_t)``,
     input gate ``i_t`` and recurrence gate ``r_t`` sigmoid projections of ``x_t``, ``c = 8``.
     The recurrence runs over the time steps, as in the paper (the reference transposes steps and
-    width before its scan, ohara/modules/linear_rnn.py:40, which makes its unit memoryless)."""
+    width before its scan, ohara/modules/linear_rnn.py:40, which makes its unit memoryless).
+    ``scan_over_width = True`` (class or instance attribute) reproduces the reference's function,
+    for checkpoints that were trained with it."""
+
+    scan_over_width = False
 
     def __init__(self, dim: int):
         super().__init__()
@@ -41,6 +45,8 @@ class RG_LRU(nn.Module):
         recurrence = self.gate_proj(x).sigmoid()
         alpha = (-self.C * F.softplus(self.forget_lambda) * recurrence).exp()
         driven = (1 - alpha**2 + 1e-6).sqrt() * self.input_proj(x).sigmoid() * x
+        if self.scan_over_width:
+            return scan(alpha.mT.contiguous(), driven.mT.contiguous()).mT
         return scan(alpha, driven)
 
     def reset_parameters(self, init_std=None) -> None:

@@ -283,3 +283,17 @@ def test_trainer_and_generation_follow_the_reference(reference_on_path):
                         chat.generate(messages, module.SamplingConfig(temperature=0.0,
                                                                       max_new_tokens=8))))
     assert outputs[0] == outputs[1] and outputs[0][1] and outputs[0][2]
+
+
+def test_recurrent_unit_follows_the_paper_and_can_reproduce_the_reference(reference_on_path):
+    """The reference's RG-LRU scans over the width (its unit has no memory); this package's scans
+    over time, and a switch gives the reference's function for checkpoints trained with it."""
+    theirs = importlib.import_module("ohara.modules.linear_rnn")
+    ours = importlib.import_module("ohara_b200.modules.linear_rnn")
+    torch.manual_seed(0)
+    reference, unit = theirs.Hawk(dim=16), ours.Hawk(dim=16)
+    unit.load_state_dict(reference.state_dict())
+    x = torch.randn(2, 9, 16)
+    assert not torch.allclose(unit(x), reference(x), atol=1e-4)
+    unit.linear_rnn.scan_over_width = True
+    torch.testing.assert_close(unit(x), reference(x), rtol=1e-5, atol=1e-6)
