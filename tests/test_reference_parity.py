@@ -297,3 +297,63 @@ def test_recurrent_unit_follows_the_paper_and_can_reproduce_the_reference(refere
     assert not torch.allclose(unit(x), reference(x), atol=1e-4)
     unit.linear_rnn.scan_over_width = True
     torch.testing.assert_close(unit(x), reference(x), rtol=1e-5, atol=1e-6)
+
+
+def test_schedules_losses_adaptors_positions_and_caches_match(reference_on_path):
+    def pair(module):
+        return (importlib.import_module("ohara." + module),
+                importlib.import_module("ohara_b200." + module))
+
+    torch.manual_seed(0)
+    theirs, ours = pair("lr_scheduler")
+    a, b = theirs.CosineScheduler(3e-4, 3e-5, 10, 100), ours.CosineScheduler(3e-4, 3e-5, 10, 100)
+    assert all(a(i) == b(i) for i in range(130))
+    theirs, ours = pair("scaling")
+    for name, arguments, steps in (("WarmupStableDecayScheduler", (0.02, 200), 201),
+                                   ("MuonMomentumScheduler", (300,), 301),
+                                   ("CosineWeightDecayScheduler", (0.1, 100), 101)):
+        a, b = getattr(theirs, name)(*arguments), getattr(ours, name)(*arguments)
+        assert all(a(i) == b(i) for i in range(steps)), name
+
+    theirs, ours = pair("dpo")
+    logps = [torch.randn(6) for _ in range(4)]
+    for name in ("dpo_loss_from_logps", "ipo_loss_from_logps", "cdpo_loss_from_logps"):
+        for want, got in zip(getattr(theirs, name)(*logps, 0.3), getattr(ours, name)(*logps, 0.3)):
+            torch.testing.assert_close(got, want)
+    logits, labels = torch.randn(2, 7, 11), torch.randint(0, 11, (2, 7))
+    labels[0, :3] = theirs.IGNORE_INDEX
+    torch.testing.assert_close(ours.sequence_logps(logits, labels),
+                               theirs.sequence_logps(logits, labels))
+
+    theirs, ours = pair("swa")
+    q, k, v = (torch.randn(2, 16, 8) for _ in range(3))
+    torch.testing.assert_close(ours.sliding_window_attention_with_mask(q, k, v, 4),
+                               theirs.sliding_window_attention_with_mask(q, k, v, 4))
+
+    x = torch.randn(3, 16)
+    for module, name in (("adaptor.lora", "LoRALinear"), ("adaptor.dora", "DoRALinear")):
+        theirs, ours = pair(module)
+        a, b = (getattr(m, name)(16, 8, rank=4, lora_alpha=2) for m in (theirs, ours))
+        with torch.no_grad():
+            for parameter in a.parameters():
+                parameter.add_(torch.randn_like(parameter) * 0.1)
+        b.load_state_dict(a.state_dict())
+        torch.testing.assert_close(b(x), a(x))
+
+    theirs, ours = pair("embeddings_pos.alibi")
+    assert torch.equal(theirs.get_alibi_mask(8, 4), ours.get_alibi_mask(8, 4))
+    theirs, ours = pair("embeddings_pos.xpos")
+    for recurrent in (False, True):
+        for want, got in zip(theirs.XPos(16, 4)(6, recurrent=recurrent),
+                             ours.XPos(16, 4)(6, recurrent=recurrent)):
+            torch.testing.assert_close(torch.as_tensor(got), torch.as_tensor(want))
+
+    theirs, ours = pair("modules.kv_cache")
+    for int8 in (False, True):
+        a, b = (m.KVCache((2, 16, 2, 8), max_seq_length=16, int8=int8) for m in (theirs, ours))
+        position = 0
+        for steps in (5, 1, 1):
+            keys, values = torch.randn(2, steps, 2, 8), torch.randn(2, steps, 2, 8)
+            for want, got in zip(a.forward(keys, values, position), b.forward(keys, values, position)):
+                torch.testing.assert_close(got, want)
+            position += steps
