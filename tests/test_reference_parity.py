@@ -343,10 +343,17 @@ def test_schedules_losses_adaptors_positions_and_caches_match(reference_on_path)
     theirs, ours = pair("embeddings_pos.alibi")
     assert torch.equal(theirs.get_alibi_mask(8, 4), ours.get_alibi_mask(8, 4))
     theirs, ours = pair("embeddings_pos.xpos")
+    def tensors(value):
+        if torch.is_tensor(value):
+            return [value]
+        return [t for item in value for t in tensors(item)]
+
     for recurrent in (False, True):
-        for want, got in zip(theirs.XPos(16, 4)(6, recurrent=recurrent),
-                             ours.XPos(16, 4)(6, recurrent=recurrent)):
-            torch.testing.assert_close(torch.as_tensor(got), torch.as_tensor(want))
+        want = tensors(theirs.XPos(16, 4)(6, recurrent=recurrent))
+        got = tensors(ours.XPos(16, 4)(6, recurrent=recurrent))
+        assert len(want) == len(got) > 0
+        for a, b in zip(want, got):
+            torch.testing.assert_close(b, a)
 
     theirs, ours = pair("modules.kv_cache")
     for int8 in (False, True):
