@@ -77,9 +77,11 @@ class GLU(_FeedForward):
         super().__init__()
         self.dim = dim
         self.hidden_dim = hidden_dim or default_hidden_dim(dim, multiple_of)
+        # (created in the reference's order, up / gate / down, so that the same seed gives the
+        # same initial weights: ohara/modules/mlp.py:90-92; SwiGLU's order is up / down / gate)
         self.up = Linear(dim, self.hidden_dim, bias=bias)
-        self.down = Linear(self.hidden_dim, dim, bias=bias)
         self.gate = Linear(dim, self.hidden_dim, bias=bias)
+        self.down = Linear(self.hidden_dim, dim, bias=bias)
         self.activation = ACT2FN[activation_fn]
         self.dropout = _dropout(dropout)
 

@@ -63,10 +63,17 @@ def test_family_has_the_reference_layout_and_reproduces_its_outputs(reference_on
     sizes = _small(getattr(theirs, config_name))
     torch.manual_seed(0)
     reference = getattr(theirs, model_name)(getattr(theirs, config_name)(**sizes)).eval()
+    torch.manual_seed(0)
     model = getattr(ours, model_name)(getattr(ours, config_name)(**sizes)).eval()
     want, have = reference.state_dict(), model.state_dict()
-    assert set(want) == set(have)
+    assert list(want) == list(have)                  # same names, created in the same order ...
     assert all(tuple(want[k].shape) == tuple(have[k].shape) for k in want)
+    for name in want:                                # ... so one seed gives the same initial model
+        assert torch.equal(want[name], have[name]), name
+    with torch.no_grad():
+        for tensor in have.values():
+            if tensor.is_floating_point():
+                tensor.add_(1.0)                     # (make sure the load below does the work)
     model.load_state_dict(want)
     tokens = torch.randint(0, SMALL["vocab"], (2, 8))
     with torch.no_grad():
