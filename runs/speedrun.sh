@@ -9,6 +9,7 @@
 #   DEPTH (12)  NPROC (all visible GPUs)  DEVICE_BATCH_SIZE (32)  SEQ_LEN (2048)
 #   TOKEN_RATIO tokens per effective parameter (12)  SHARDS ClimbMix shards to stage (24)
 #   TRAIN_DOCS / VAL_DOCS  TOKENIZER  DATA_DIR  CKPT_DIR  SFT_ITERS (800)
+#   NUM_WORKERS dataloader processes per rank (1; use 0 with --resume so that the stream position is exact)
 #   STRATEGY multi-GPU strategy: fsdp = sharded optimizer over NVLink peer memory (default), ddp
 #   SERVE start the chat UI at the end (1)  PORT (8080)
 set -euo pipefail
@@ -24,6 +25,7 @@ TOKENIZER="${TOKENIZER:-EleutherAI/gpt-neo-125m}"
 DATA_DIR="${DATA_DIR:-./data/scaling_corpus}"
 CKPT_DIR="${CKPT_DIR:-./ckpt}"
 STRATEGY="${STRATEGY:-fsdp}"
+NUM_WORKERS="${NUM_WORKERS:-1}"
 SERVE="${SERVE:-1}"
 PORT="${PORT:-8080}"
 SFT_ITERS="${SFT_ITERS:-800}"
@@ -97,6 +99,7 @@ $LAUNCH examples/train_llama_engine.py \
   --matrix-learning-rate "${MATRIX_LR}" --embedding-learning-rate "${EMBEDDING_LR}" \
   --unembedding-learning-rate "${UNEMBEDDING_LR}" --scalar-learning-rate "${SCALAR_LR}" \
   --weight-decay "${WEIGHT_DECAY}" --evaluate-bpb --strategy "${STRATEGY}" \
+  --num-workers "${NUM_WORKERS}" \
   --eval-every 250 --save-every 500 --checkpoint-path "${BASE_CKPT}" \
   --result-json "runs/base_${RUN}.json"
 
@@ -106,6 +109,7 @@ $LAUNCH examples/train_sft.py \
   --pretrained-checkpoint "${BASE_CKPT}" --checkpoint-path "${SFT_CKPT}" \
   --tokenizer "${TOKENIZER}" --seq-len "${SEQ_LEN}" --batch-size "${DEVICE_BATCH_SIZE}" \
   --grad-accum-steps "${GRAD_ACCUM}" --max-iters "${SFT_ITERS}" \
+  --num-workers "${NUM_WORKERS}" \
   --result-json "runs/sft_${RUN}.json"
 
 echo
