@@ -371,3 +371,54 @@ def test_schedules_losses_adaptors_positions_and_caches_match(reference_on_path)
             for want, got in zip(a.forward(keys, values, position), b.forward(keys, values, position)):
                 torch.testing.assert_close(got, want)
             position += steps
+
+
+def test_streaming_text_dataset_cuts_the_same_blocks(reference_on_path, monkeypatch):
+    """Both packages read a (stubbed) ``datasets`` stream: same calls into the library, same
+    token blocks with and without shuffling, per-rank sharding and a resume offset."""
+    import random
+    import types
+
+    sys.path.insert(0, str(ROOT / "tests"))
+    from helpers import WordTokenizer
+
+    documents = [{"text": " ".join(f"w{(i * 7 + j) % 50}" for j in range(5 + i % 11))}
+                 for i in range(60)]
+
+    class Stream:
+        def __init__(self, rows):
+            self.rows = rows
+
+        def __iter__(self):
+            return iter(self.rows)
+
+        def shuffle(self, seed=None, buffer_size=None):
+            rows = list(self.rows)
+            random.Random(seed).shuffle(rows)
+            return Stream(rows)
+
+    calls = []
+
+    def load_dataset(*args, **kwargs):
+        calls.append((args, tuple(sorted(kwargs.items()))))
+        return Stream(documents)
+
+    stub = types.ModuleType("datasets")
+    stub.load_dataset, stub.load_from_disk = load_dataset, (lambda *a, **k: None)
+    monkeypatch.setitem(sys.modules, "datasets", stub)
+    blocks = {}
+    for package in ("ohara", "ohara_b200"):
+        module = importlib.import_module(package + ".dataset")
+        monkeypatch.setattr(module, "load_dataset", load_dataset, raising=False)
+        for shuffle in (False, True):
+            for rank, world, start in ((None, None, 2), (1, 2, 0)):
+                dataset = module.StreamingTextDataset(
+                    "some/corpus", WordTokenizer(), split="train", max_length=16, shuffle=shuffle,
+                    seed=3, data_rank=rank, data_world_size=world, start_block=start)
+                rows = iter(dataset)
+                blocks[(package, shuffle, rank)] = [tuple(t.tolist() for t in next(rows))
+                                                    for _ in range(6)]
+    for (package, shuffle, rank), rows in blocks.items():
+        if package == "ohara":
+            assert rows == blocks[("ohara_b200", shuffle, rank)], (shuffle, rank)
+    assert calls[: len(calls) // 2] == calls[len(calls) // 2:]
