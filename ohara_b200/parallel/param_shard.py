@@ -15,7 +15,8 @@ keeps, between uses, only ``1 / world`` of every parameter:
   is released;
 * when the last gradient of a unit has been accumulated, the unit's gradients are packed,
   reduce-scattered (mean, asynchronously: the previous block's backward pass runs meanwhile) and
-  added to the rank's fp32 gradient shard, and the full gradients are dropped. A unit some of whose parameters may stay without a gradient on some ranks (the loop
+  added to the rank's fp32 gradient shard, and the full gradients are dropped. A unit some of
+  whose parameters may stay without a gradient on some ranks (the loop
   MoE: experts no token chose) is reduced at the end of the backward pass instead, by every rank
   in turn.
 
@@ -152,7 +153,8 @@ class ParameterSharding:
                  solo: bool = False, replicate_group=None, replicate_world: int = 1,
                  whole_tensor_units: Iterable[str] = ()) -> None:
         """``whole_tensor_units``: names of units laid out with every parameter inside one rank's
-        region (see :class:`_Unit`). ``solo``: shard over nobody although a process group exists (every other rank of the
+        region (see :class:`_Unit`). ``solo``: shard over nobody although a process group
+        exists (every other rank of the
         job holds different tensors, e.g. the tensor-parallel peers). ``replicate_group`` (of
         ``replicate_world`` ranks): hybrid sharding, the ranks that hold the same shard as this
         one in other replica groups; reduced gradient shards are averaged over it."""

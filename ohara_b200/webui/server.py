@@ -98,7 +98,8 @@ class ChatRequestHandler(BaseHTTPRequestHandler):
         try:
             return json.loads(self.rfile.read(length).decode("utf-8"))
         except (UnicodeDecodeError, json.JSONDecodeError) as error:
-            raise BadRequest(str(error)) from error  # the parser's own message, as the reference replies
+            # (the parser's own message, as the reference replies)
+            raise BadRequest(str(error)) from error
 
     def _serve_static(self, relative: str) -> None:
         root = STATIC_DIR.resolve()
